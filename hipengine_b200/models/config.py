@@ -1,0 +1,171 @@
+"""Model geometry for the supported decoder families.
+
+One dataclass covers plain dense decoders, the Qwen3.5-family hybrid
+(Gated-DeltaNet linear attention + gated full attention, dense or MoE FFN) and
+Gemma 4 (sliding-window/global attention + MoE).  The three pinned Qwen3.5
+geometries mirror the identities the reference pins in
+``hipengine/kernels/policy.py:103-153``; the Gemma 4 26B-A4B numbers come from
+``docs/model-cards/MODEL-GEMMA4.md:128-155`` of the reference.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field, replace
+from typing import Any, Dict, Optional, Tuple
+
+
+@dataclass(frozen=True)
+class ModelConfig:
+    arch: str = "qwen35"                 # general.architecture of the GGUF file
+    n_layers: int = 4
+    hidden: int = 256
+    vocab: int = 4096
+    n_heads: int = 4
+    n_kv_heads: int = 2
+    head_dim: int = 64
+    ffn: int = 768
+    rms_eps: float = 1e-6
+    rope_theta: float = 1e6
+    rope_dim: int = 64                   # rotated dims per head (partial rotary when < head_dim)
+    # attention flavour
+    gated_attention: bool = False        # attn_q projects [Q | gate] per head; out *= sigmoid(gate)
+    qk_norm: bool = False
+    attn_scale: Optional[float] = None   # None -> head_dim ** -0.5
+    # hybrid schedule: layer i is full attention iff (i + 1) % full_attention_interval == 0
+    full_attention_interval: int = 0     # 0 -> every layer is full attention
+    # Gated DeltaNet (linear attention) geometry
+    ssm_groups: int = 0                  # number of K heads
+    ssm_v_heads: int = 0                 # number of V heads (= time_step_rank)
+    ssm_state: int = 128                 # Dk = Dv
+    conv_kernel: int = 4
+    # MoE
+    n_experts: int = 0
+    n_experts_used: int = 0
+    expert_ffn: int = 0
+    shared_ffn: int = 0
+    # Gemma-style extras
+    sliding_window: int = 0
+    swa_pattern: int = 0                 # every swa_pattern-th layer is global, the rest sliding
+    global_head_dim: int = 0
+    global_kv_heads: int = 0
+    final_softcap: float = 0.0
+    embed_scale: float = 1.0
+    act: str = "silu"                    # "silu" | "gelu_tanh"
+    tie_embeddings: bool = False
+    # MTP / NextN draft blocks appended after the main stack
+    nextn_layers: int = 0
+    max_context: int = 8192
+
+    # ---- derived
+    @property
+    def is_hybrid(self) -> bool:
+        return self.full_attention_interval > 0
+
+    @property
+    def is_moe(self) -> bool:
+        return self.n_experts > 0
+
+    @property
+    def ssm_inner(self) -> int:
+        return self.ssm_v_heads * self.ssm_state
+
+    @property
+    def linear_qkv_width(self) -> int:
+        return 2 * self.ssm_groups * self.ssm_state + self.ssm_inner
+
+    @property
+    def q_width(self) -> int:
+        return self.n_heads * self.head_dim
+
+    @property
+    def kv_width(self) -> int:
+        return self.n_kv_heads * self.head_dim
+
+    @property
+    def q_proj_width(self) -> int:
+        return self.q_width * (2 if self.gated_attention else 1)
+
+    def is_full_attention_layer(self, i: int) -> bool:
+        if not self.is_hybrid:
+            return True
+        return (i + 1) % self.full_attention_interval == 0
+
+    def layer_kinds(self) -> Tuple[str, ...]:
+        return tuple("full" if self.is_full_attention_layer(i) else "linear" for i in range(self.n_layers))
+
+    @property
+    def n_full_layers(self) -> int:
+        return sum(1 for k in self.layer_kinds() if k == "full")
+
+    @property
+    def n_linear_layers(self) -> int:
+        return self.n_layers - self.n_full_layers
+
+    def scale(self) -> float:
+        return self.attn_scale if self.attn_scale is not None else self.head_dim ** -0.5
+
+    def kv_bytes_per_token(self, elem_bytes: int = 2) -> int:
+        return self.n_full_layers * 2 * self.n_kv_heads * self.head_dim * elem_bytes
+
+    def recurrent_state_bytes(self) -> int:
+        gdn = self.n_linear_layers * self.ssm_v_heads * self.ssm_state * self.ssm_state * 4
+        conv = self.n_linear_layers * self.linear_qkv_width * self.conv_kernel * 4
+        return gdn + conv
+
+    def with_layers(self, n_layers: int) -> "ModelConfig":
+        return replace(self, n_layers=n_layers)
+
+
+# BASELINE config 1: tiny dense decoder used on the CPU reference backend.
+TINY_DENSE = ModelConfig(arch="qwen3", n_layers=4, hidden=256, vocab=4096, n_heads=4, n_kv_heads=2,
+                         head_dim=64, ffn=768, rms_eps=1e-6, rope_theta=1e6, rope_dim=64)
+
+# Dense hybrid 27B: 64 layers [3 GDN + 1 gated full attention] x 16.
+QWEN35_27B = ModelConfig(arch="qwen35", n_layers=64, hidden=5120, vocab=248320, n_heads=24, n_kv_heads=4,
+                         head_dim=256, ffn=17408, rms_eps=1e-6, rope_theta=1e7, rope_dim=64,
+                         gated_attention=True, qk_norm=True, full_attention_interval=4,
+                         ssm_groups=16, ssm_v_heads=48, ssm_state=128, conv_kernel=4,
+                         max_context=262144)
+
+# MoE hybrid 35B-A3B: 40 layers, 256 experts top-8 + shared expert.
+QWEN35_35B_A3B = ModelConfig(arch="qwen35moe", n_layers=40, hidden=2048, vocab=248320, n_heads=16, n_kv_heads=2,
+                             head_dim=256, ffn=0, rms_eps=1e-6, rope_theta=1e7, rope_dim=64,
+                             gated_attention=True, qk_norm=True, full_attention_interval=4,
+                             ssm_groups=16, ssm_v_heads=32, ssm_state=128, conv_kernel=4,
+                             n_experts=256, n_experts_used=8, expert_ffn=512, shared_ffn=512,
+                             max_context=262144)
+
+# Small hybrid used by tests and the smoke entry (same structure, toy widths).
+TINY_HYBRID = ModelConfig(arch="qwen35", n_layers=4, hidden=512, vocab=2048, n_heads=4, n_kv_heads=2,
+                          head_dim=256, ffn=1024, rope_theta=1e7, rope_dim=64, gated_attention=True,
+                          qk_norm=True, full_attention_interval=4, ssm_groups=2, ssm_v_heads=4,
+                          ssm_state=128, conv_kernel=4, max_context=4096)
+
+TINY_HYBRID_MOE = ModelConfig(arch="qwen35moe", n_layers=4, hidden=512, vocab=2048, n_heads=4, n_kv_heads=2,
+                              head_dim=256, ffn=0, rope_theta=1e7, rope_dim=64, gated_attention=True,
+                              qk_norm=True, full_attention_interval=4, ssm_groups=2, ssm_v_heads=4,
+                              ssm_state=128, conv_kernel=4, n_experts=16, n_experts_used=4,
+                              expert_ffn=256, shared_ffn=256, max_context=4096)
+
+# Gemma 4 26B-A4B: 30 layers, 5 sliding (window 1024) : 1 global.
+GEMMA4_26B_A4B = ModelConfig(arch="gemma4", n_layers=30, hidden=2816, vocab=262144, n_heads=16, n_kv_heads=8,
+                             head_dim=256, ffn=2112, rms_eps=1e-6, rope_theta=1e6, rope_dim=256,
+                             qk_norm=True, attn_scale=1.0, sliding_window=1024, swa_pattern=6,
+                             global_head_dim=512, global_kv_heads=2, n_experts=128, n_experts_used=8,
+                             expert_ffn=704, final_softcap=30.0, embed_scale=2816 ** 0.5,
+                             act="gelu_tanh", tie_embeddings=True, max_context=262144)
+
+TINY_GEMMA4 = ModelConfig(arch="gemma4", n_layers=6, hidden=256, vocab=2048, n_heads=4, n_kv_heads=2,
+                          head_dim=64, ffn=512, rope_theta=1e6, rope_dim=64, qk_norm=True, attn_scale=1.0,
+                          sliding_window=32, swa_pattern=6, global_head_dim=128, global_kv_heads=1,
+                          n_experts=8, n_experts_used=2, expert_ffn=128, final_softcap=30.0,
+                          embed_scale=16.0, act="gelu_tanh", tie_embeddings=True, max_context=2048)
+
+NAMED_CONFIGS: Dict[str, ModelConfig] = {
+    "tiny-dense": TINY_DENSE,
+    "tiny-hybrid": TINY_HYBRID,
+    "tiny-hybrid-moe": TINY_HYBRID_MOE,
+    "tiny-gemma4": TINY_GEMMA4,
+    "qwen35-27b": QWEN35_27B,
+    "qwen35-35b-a3b": QWEN35_35B_A3B,
+    "gemma4-26b-a4b": GEMMA4_26B_A4B,
+}
