@@ -1,0 +1,260 @@
+"""Headline benchmark: dense hybrid 27B decoder, GGUF Q4_K_M weights, bf16 KV, batch 1,
+4096-token prefill then 256 decode tokens, tensor-parallel over N GPUs of one node.
+
+One "step" is one complete request (prefill + decode).  `value` is decode tokens/s (whole job); prefill
+tokens/s, TTFT and ITL are reported beside it.  Weights are random N(0, 0.02) quantized on the device
+(no network for checkpoints), prompts are uniform random ids.  The weight stream of one decode step
+(~15 GB) is far larger than L2, so no explicit L2 flush is needed between iterations.
+
+    python bench.py --gpus 1 --steps 3 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference ...      # the unmodified reference (prints why it is unavailable here)
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+BASELINE_DECODE_TOK_S = 30.8     # reference README: Qwen3.8-27B Q4_K_M TG on Radeon Pro W7900
+BASELINE_PREFILL_TOK_S = 898.6   # same row, PP
+
+
+def reference_arm(args) -> int:
+    reason = ("reference cannot run here: pip install needs the hatchling build backend, which is not in the "
+              "offline wheelhouse, and its GGUF kernels are HIP gfx1100/gfx1151 only (its CUDA backend is "
+              "sm_120a Maple/Moonshine with no GGUF consumer, no sm_100 path, no NCCL)")
+    print(json.dumps({"impl": "reference", "unavailable": reason}))
+    return 0
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for ln in self.proc.stdout:
+            self.lines.append(ln.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="qwen35-27b")
+    ap.add_argument("--prompt-len", type=int, default=4096)
+    ap.add_argument("--gen-len", type=int, default=256)
+    ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the layer stack (marks the run invalid)")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-graphs", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+    if args.warmup < 3 and not args.layers:
+        args.warmup = 3
+
+    import torch
+    import torch.distributed as dist
+    from hipengine_b200.core import native
+    from hipengine_b200.loading.synth import build_random_model
+    from hipengine_b200.models.config import NAMED_CONFIGS
+    from hipengine_b200.ops import kernels as K
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    if not native.lib_available():
+        raise SystemExit("native library missing: run `python -c 'import __graft_entry__ as g; g.build()'` first")
+
+    cfg = NAMED_CONFIGS[args.model]
+    if args.layers:
+        cfg = cfg.with_layers(args.layers)
+    ctx_max = args.prompt_len + args.gen_len + 16
+    t_build0 = time.time()
+    if world > 1:
+        from hipengine_b200.parallel.tp import build_tp_executor
+        ex = build_tp_executor(cfg, seed=0, device=dev, max_slots=1, max_context=ctx_max)
+    else:
+        from hipengine_b200.models.executor import HybridExecutor
+        weights = build_random_model(cfg, seed=0, device=dev, recipe="q4_k_m")
+        ex = HybridExecutor(weights, device=dev, max_slots=1, max_context=ctx_max)
+        del weights
+    from hipengine_b200.models.decode_graph import DecodeGraphRunner
+    runner = DecodeGraphRunner(ex, max_rows=1, use_graphs=not args.no_graphs)
+    torch.cuda.synchronize()
+    build_s = time.time() - t_build0
+
+    gen = torch.Generator().manual_seed(1234)
+    prompts = [torch.randint(0, cfg.vocab, (args.prompt_len,), generator=gen).tolist()
+               for _ in range(args.steps + args.warmup)]
+
+    def one_request(prompt, ev):
+        ex.reset_slot(0)
+        ev[0].record()
+        logits = ex.prefill(0, prompt)
+        ex.greedy(logits, runner.next_ids[:1])
+        runner.slot[:1].zero_()
+        runner.pos[:1].fill_(len(prompt) - 1)
+        runner.ctx_len[:1].fill_(len(prompt))
+        runner.publish(1)                       # first token -> tokens[0], pos -> len(prompt)
+        ev[1].record()
+        for _ in range(args.gen_len - 1):
+            runner.step(1, ctx_max)
+        ev[2].record()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    mk = lambda: [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    for i in range(args.warmup):
+        one_request(prompts[i], mk())
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    k0 = K.launch_count()
+    evs = [mk() for _ in range(args.steps)]
+    barrier()
+    t0 = time.time()
+    for i in range(args.steps):
+        one_request(prompts[args.warmup + i], evs[i])
+    barrier()
+    wall_s = time.time() - t0
+    launches = K.launch_count() - k0
+    clocks = sampler.stop() if rank == 0 else {}
+
+    prefill_ms = sum(e[0].elapsed_time(e[1]) for e in evs)
+    decode_ms = sum(e[1].elapsed_time(e[2]) for e in evs)
+    t = torch.tensor([prefill_ms, decode_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    prefill_ms, decode_ms = t.tolist()
+    n_dec = (args.gen_len - 1) * args.steps
+    decode_tok_s = n_dec / (decode_ms / 1e3)
+    prefill_tok_s = args.prompt_len * args.steps / (prefill_ms / 1e3)
+
+    e2e = None
+    if not args.no_e2e and rank == 0 and world == 1:
+        try:
+            e2e = run_e2e(args, cfg, ex, prompts)
+        except Exception as exc:  # the device-timed line must still be printed
+            e2e = {"error": f"{type(exc).__name__}: {exc}"}
+
+    if rank == 0:
+        line = {
+            "metric": "decode_tok_s (27B dense hybrid Q4_K_M, bf16 KV, batch 1, 4096 prefill + 256 decode)",
+            "value": round(decode_tok_s, 3), "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round((prefill_ms + decode_ms) / args.steps, 3),
+            "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": round(decode_tok_s / BASELINE_DECODE_TOK_S, 3), "dtype": "bf16",
+            "data": "synthetic (random-init N(0,0.02) weights quantized to Q4_K_M-style GGUF blocks, uniform random prompt ids)",
+            "config": {"model": args.model, "global_batch": 1, "seq_len": args.prompt_len, "gen_len": args.gen_len,
+                       "parallelism": f"tp{world}", "layers": cfg.n_layers, "l2": "inputs larger than L2 (weight stream ~15 GB/step)",
+                       "cuda_graphs": not args.no_graphs},
+            "prefill_tok_s": round(prefill_tok_s, 2),
+            "prefill_vs_baseline": round(prefill_tok_s / BASELINE_PREFILL_TOK_S, 3),
+            "ttft_ms": round(prefill_ms / args.steps, 3),
+            "itl_ms": round(decode_ms / n_dec, 4),
+            "wall_s": round(wall_s, 3), "build_s": round(build_s, 2),
+            "clocks": clocks, "gpu_launches": int(launches),
+        }
+        if e2e is not None:
+            line["e2e"] = e2e
+        if args.layers:
+            line["invalid"] = "truncated layer stack (debug run)"
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+def run_e2e(args, cfg, ex, prompts):
+    """Same request through the public API: pinned-host prompt -> LLM.generate -> token ids read back."""
+    import torch
+    from hipengine_b200.llm import LLM, SamplingParams
+    llm = LLM.from_executor(ex) if hasattr(LLM, "from_executor") else None
+    if llm is None:
+        return {"error": "public API not wired"}
+    sp = SamplingParams(max_tokens=args.gen_len, temperature=0.0, ignore_eos=True)
+    pinned = [torch.tensor(p, dtype=torch.int64).pin_memory() for p in prompts]
+    for i in range(min(2, args.warmup)):
+        llm.generate_detailed(pinned[i].tolist(), sp)
+    dec_s = pre_s = 0.0
+    h2d = d2h = 0
+    for i in range(args.steps):
+        out = llm.generate_detailed(pinned[args.warmup + i].tolist(), sp)[0]
+        dec_s += out.telemetry.decode_seconds
+        pre_s += out.telemetry.prefill_seconds
+        h2d += out.telemetry.h2d_bytes
+        d2h += out.telemetry.d2h_bytes
+    n_dec = (args.gen_len - 1) * args.steps
+    return {"value": round(n_dec / dec_s, 3), "unit": "tok/s",
+            "prefill_tok_s": round(args.prompt_len * args.steps / pre_s, 2),
+            "h2d_bytes_per_step": h2d // args.steps, "d2h_bytes_per_step": d2h // args.steps}
+
+
+if __name__ == "__main__":
+    sys.exit(main())

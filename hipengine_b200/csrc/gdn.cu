@@ -1,0 +1,216 @@
+// Gated DeltaNet (linear attention): prepare (L2-norm q,k + gates), the recurrent scan over packed
+// segments (decode rows, verify chains and prefill share one kernel), and the gated output RMSNorm.
+//
+// Per V head the state S is [Dk x Dv] fp32 and each step is
+//     S <- decay*S ;  kv = k^T S ;  delta = beta*(v - kv) ;  S <- S + k (x) delta ;  o = q^T S
+// (hipengine/kernels/hip_gfx1100/linear_attn/gdn.hip:126-330; oracle hipengine/kernels/cpu_reference/ops.py:1967-2012).
+// Columns of S are independent, so a head is split into Dv/32 column slices, one CTA each: with 48 heads x 4
+// slices a single request already fills the 148 SMs.  Inside a CTA a column is owned by 4 lanes of one warp
+// (rows r = lane%4 + 4*i), so the two reductions per token are two xor-shuffles and no block barrier.
+// GGUF head order: V head h reads K head h % num_k_heads (gdn.hip:106-118).
+#include "common.cuh"
+
+using namespace he;
+
+namespace {
+
+struct GdnPrepArgs {
+  float* qkv;            // [T][C] conv output, q and k normalised in place
+  const float* a;        // [T][a_stride]
+  const float* b;        // [T][b_stride]
+  long long a_stride, b_stride;
+  const float* ssm_a;    // [Hv]  (negative coefficient)
+  const float* dt_bias;  // [Hv]
+  float* decay;          // [T][Hv]
+  float* beta;           // [T][Hv]
+  int C, G, Hv, S, T;
+};
+
+// grid T, block 256
+__global__ void __launch_bounds__(256) gdn_prepare_kernel(const GdnPrepArgs p) {
+  const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  float* row = p.qkv + (size_t)t * p.C;
+  const float qscale = rsqrtf((float)p.S);
+  for (int h = warp; h < 2 * p.G; h += nwarp) {
+    float* v = row + (size_t)h * p.S;
+    float ss = 0.f;
+    for (int i = lane; i < p.S; i += 32) ss += v[i] * v[i];
+    ss = warp_sum(ss);
+    float inv = 1.f / fmaxf(sqrtf(ss), 1e-6f);
+    if (h < p.G) inv *= qscale;
+    for (int i = lane; i < p.S; i += 32) v[i] *= inv;
+  }
+  for (int h = threadIdx.x; h < p.Hv; h += blockDim.x) {
+    const float av = p.a[(size_t)t * p.a_stride + h], bv = p.b[(size_t)t * p.b_stride + h];
+    p.beta[(size_t)t * p.Hv + h] = sigmoid_f(bv);
+    p.decay[(size_t)t * p.Hv + h] = __expf(p.ssm_a[h] * softplus20_f(av + p.dt_bias[h]));
+  }
+}
+
+struct GdnScanArgs {
+  const float* qkv;       // [T][C]  prepared conv output: q | k | v
+  const float* decay;     // [T][Hv]
+  const float* beta;      // [T][Hv]
+  float* state;           // [n_slots][Hv][Dk][Dv]
+  const int* seg_start;   // [n_seg+1]
+  const int* seg_slot;    // [n_seg]
+  float* out;             // [T][Hv][Dv]
+  float* journal;         // optional [T][Hv][Dk][Dv] state after each token
+  int C, G, Hv, T, n_seg;
+  int write_state;        // 1: store the final state back to `state`
+};
+
+constexpr int DK = 128;       // state rows (key dim)
+constexpr int DV = 128;       // state cols (value dim)
+constexpr int SLICE = 32;     // columns per CTA
+constexpr int TCH = 16;       // tokens staged per shared-memory chunk
+
+// grid (n_seg, Hv, DV/SLICE), block 128
+__global__ void __launch_bounds__(128) gdn_scan_kernel(const GdnScanArgs p) {
+  __shared__ float sq[TCH][DK];
+  __shared__ float sk[TCH][DK];
+  __shared__ float sv[TCH][SLICE];
+  __shared__ float sdec[TCH], sbeta[TCH];
+  const int sg = blockIdx.x, h = blockIdx.y, sl = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int col = sl * SLICE + warp * 8 + (lane >> 2);  // column of S owned (with 3 other lanes)
+  const int ks = lane & 3;                              // rows ks + 4*i
+  const int kh = h % p.G;
+  const int s0 = p.seg_start[sg], s1 = p.seg_start[sg + 1];
+  float* Sg = p.state + (((size_t)p.seg_slot[sg] * p.Hv + h) * DK) * DV;
+  float S[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) S[i] = Sg[(size_t)(ks + 4 * i) * DV + col];
+
+  const size_t q_off = (size_t)kh * DK, k_off = (size_t)p.G * DK + (size_t)kh * DK;
+  const size_t v_off = (size_t)2 * p.G * DK + (size_t)h * DV + sl * SLICE;
+
+  for (int c0 = s0; c0 < s1; c0 += TCH) {
+    const int n = min(TCH, s1 - c0);
+    __syncthreads();
+    for (int i = tid; i < n * DK; i += 128) {
+      const int tt = i / DK, d = i % DK;
+      const float* row = p.qkv + (size_t)(c0 + tt) * p.C;
+      sq[tt][d] = row[q_off + d];
+      sk[tt][d] = row[k_off + d];
+    }
+    for (int i = tid; i < n * SLICE; i += 128) {
+      const int tt = i / SLICE, d = i % SLICE;
+      sv[tt][d] = p.qkv[(size_t)(c0 + tt) * p.C + v_off + d];
+    }
+    if (tid < n) {
+      sdec[tid] = p.decay[(size_t)(c0 + tid) * p.Hv + h];
+      sbeta[tid] = p.beta[(size_t)(c0 + tid) * p.Hv + h];
+    }
+    __syncthreads();
+    for (int tt = 0; tt < n; ++tt) {
+      const float dec = sdec[tt], bet = sbeta[tt];
+      float kv = 0.f;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        S[i] *= dec;
+        kv += sk[tt][ks + 4 * i] * S[i];
+      }
+      kv += __shfl_xor_sync(0xffffffffu, kv, 1);
+      kv += __shfl_xor_sync(0xffffffffu, kv, 2);
+      const float delta = (sv[tt][warp * 8 + (lane >> 2)] - kv) * bet;
+      float o = 0.f;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        S[i] += sk[tt][ks + 4 * i] * delta;
+        o += sq[tt][ks + 4 * i] * S[i];
+      }
+      o += __shfl_xor_sync(0xffffffffu, o, 1);
+      o += __shfl_xor_sync(0xffffffffu, o, 2);
+      if (ks == 0) p.out[((size_t)(c0 + tt) * p.Hv + h) * DV + col] = o;
+      if (p.journal != nullptr) {
+        float* J = p.journal + (((size_t)(c0 + tt) * p.Hv + h) * DK) * DV;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) J[(size_t)(ks + 4 * i) * DV + col] = S[i];
+      }
+    }
+  }
+  if (p.write_state) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) Sg[(size_t)(ks + 4 * i) * DV + col] = S[i];
+  }
+}
+
+// out[t][h][:] = RMSNorm(o[t][h][:]) * w * SiLU(z[t][h][:])  -> bf16.  One warp per (t, h).
+__global__ void gdn_gated_norm_kernel(const float* __restrict__ o, const void* __restrict__ z, int z_dtype,
+                                      long long z_stride, const float* __restrict__ w,
+                                      __nv_bfloat16* __restrict__ out, long long out_stride, int T, int Hv, int Dv,
+                                      float eps) {
+  const long long gw = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (gw >= (long long)T * Hv) return;
+  const int t = (int)(gw / Hv), h = (int)(gw % Hv);
+  const float* orow = o + ((size_t)t * Hv + h) * Dv;
+  float ss = 0.f;
+  for (int i = lane; i < Dv; i += 32) ss += orow[i] * orow[i];
+  ss = warp_sum(ss);
+  const float inv = rsqrtf(ss / (float)Dv + eps);
+  for (int i = lane; i < Dv; i += 32) {
+    const size_t zi = (size_t)t * z_stride + (size_t)h * Dv + i;
+    const float zv = z_dtype == 0 ? reinterpret_cast<const float*>(z)[zi]
+                                  : bf16_to_f32(reinterpret_cast<const __nv_bfloat16*>(z)[zi]);
+    out[(size_t)t * out_stride + (size_t)h * Dv + i] = f32_to_bf16(orow[i] * inv * w[i] * silu_f(zv));
+  }
+}
+
+// Copy one journalled state row into the canonical slot (speculative commit): dst[slot] = journal[row].
+__global__ void gdn_commit_kernel(float* __restrict__ state, const float* __restrict__ journal,
+                                  const int* __restrict__ seg_slot, const int* __restrict__ commit_row,
+                                  long long per_slot) {
+  const int sg = blockIdx.y;
+  const int row = commit_row[sg];
+  if (row < 0) return;
+  const float4* src = reinterpret_cast<const float4*>(journal + (size_t)row * per_slot);
+  float4* dst = reinterpret_cast<float4*>(state + (size_t)seg_slot[sg] * per_slot);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < per_slot / 4;
+       i += (long long)gridDim.x * blockDim.x)
+    dst[i] = src[i];
+}
+
+}  // namespace
+
+HE_API int he_gdn_prepare(const GdnPrepArgs* args, cudaStream_t stream) {
+  if (args->T <= 0) return 0;
+  gdn_prepare_kernel<<<args->T, 256, 0, stream>>>(*args);
+  HE_LAUNCH_CHECK();
+  return 0;
+}
+HE_API int he_gdn_prep_args_size() { return (int)sizeof(GdnPrepArgs); }
+
+HE_API int he_gdn_scan(const GdnScanArgs* args, cudaStream_t stream) {
+  if (args->T <= 0 || args->n_seg <= 0) return 0;
+  dim3 grid(args->n_seg, args->Hv, DV / SLICE);
+  gdn_scan_kernel<<<grid, 128, 0, stream>>>(*args);
+  HE_LAUNCH_CHECK();
+  return 0;
+}
+HE_API int he_gdn_scan_args_size() { return (int)sizeof(GdnScanArgs); }
+
+HE_API int he_gdn_gated_norm(const void* o, const void* z, int z_dtype, long long z_stride, const void* w, void* out,
+                             long long out_stride, int T, int Hv, int Dv, float eps, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  const long long warps = (long long)T * Hv;
+  gdn_gated_norm_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, stream>>>(
+      (const float*)o, z, z_dtype, z_stride, (const float*)w, (__nv_bfloat16*)out, out_stride, T, Hv, Dv, eps);
+  HE_LAUNCH_CHECK();
+  return 0;
+}
+
+// state[seg_slot[s]] = journal[commit_row[s]] for each segment s with commit_row[s] >= 0.
+// per_slot = floats per slot (Hv*Dk*Dv for GDN state, C*(KW-1) for conv state); must be a multiple of 4.
+HE_API int he_state_commit(void* state, const void* journal, const void* seg_slot, const void* commit_row, int n_seg,
+                           long long per_slot, cudaStream_t stream) {
+  if (n_seg <= 0) return 0;
+  if (per_slot % 4 != 0) return -HE_ERR_BAD_ARG;
+  dim3 grid(64, n_seg);
+  gdn_commit_kernel<<<grid, 256, 0, stream>>>((float*)state, (const float*)journal, (const int*)seg_slot,
+                                              (const int*)commit_row, per_slot);
+  HE_LAUNCH_CHECK();
+  return 0;
+}

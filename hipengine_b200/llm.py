@@ -1,0 +1,310 @@
+"""Public Python API: ``LLM`` and ``SamplingParams``.
+
+Surface parity with the reference (``hipengine/llm.py:196-343`` for the sampling
+dataclass, ``:365-394`` for constructor kwargs, ``:538-1578`` for methods):
+``generate``, ``generate_detailed``, ``stream``, ``stream_detailed``, ``chat``,
+``tokenize/detokenize/count_tokens``, ``prepare``, ``reset``, ``close``,
+``resident_capacity_estimate``, ``engine_service_health``, ``live_loop_snapshot``.
+Construction resolves model metadata -> weights -> executor -> engine service;
+one driver thread owns the device (``hipengine/generation/engine_service.py:207-297``).
+"""
+from __future__ import annotations
+
+import threading
+import time
+from dataclasses import dataclass, field, replace
+from pathlib import Path
+from typing import Any, Dict, Iterable, Iterator, List, Mapping, Optional, Sequence, Tuple, Union
+
+import torch
+
+from .config import EngineConfig, ExecutionProfile, KVConfig, SchedulerConfig, SpeculativeConfig
+from .generation.types import (FinishDetails, GenerationOutput, GenerationRequest, GenerationStreamChunk,
+                               normalize_logit_bias, normalize_stop_sequences)
+
+
+class ResidentPreparationError(RuntimeError):
+    """Raised when the engine cannot become resident (weights / KV / scratch do not fit, or no device)."""
+
+
+@dataclass(frozen=True)
+class SamplingParams:
+    """Every sampler / finish / constraint knob of a request (``hipengine/llm.py:196-343``)."""
+    max_tokens: int = 16
+    temperature: float = 0.0
+    top_p: float = 1.0
+    top_k: int = 0
+    min_p: float = 0.0
+    repetition_penalty: float = 1.0
+    presence_penalty: float = 0.0
+    frequency_penalty: float = 0.0
+    logit_bias: Any = ()
+    suppress_token_ids: Tuple[int, ...] = ()
+    min_tokens: int = 0
+    eos_token_id: Optional[int] = None
+    stop_token_ids: Tuple[int, ...] = ()
+    stop_token_sequences: Tuple[Tuple[int, ...], ...] = ()
+    forced_tokens_pending: Tuple[int, ...] = ()
+    json_object_close_forcing: bool = False
+    tool_call_constraint: Any = None
+    grammar: Optional[Mapping[str, Any]] = None
+    thinking_close_token_ids: Tuple[int, ...] = ()
+    thinking_hard_token_cap: Optional[int] = None
+    thinking_soft_close_window: int = 0
+    ignore_eos: bool = False
+    kv_storage: str = "auto"
+    seed: Optional[int] = None
+    row_seeds: Tuple[int, ...] = ()
+    deadline_at: Optional[float] = None
+    cancellation_token: Any = field(default=None, compare=False, repr=False)
+    resident_session_key: Optional[str] = field(default=None, compare=False, repr=False)
+    speculative_mtp: bool = False
+    logprobs: bool = False
+    top_logprobs: int = 0
+
+    def __post_init__(self) -> None:
+        s = object.__setattr__
+        s(self, "max_tokens", int(self.max_tokens))
+        s(self, "temperature", float(self.temperature))
+        s(self, "top_p", float(self.top_p))
+        s(self, "top_k", int(self.top_k))
+        s(self, "min_p", float(self.min_p))
+        s(self, "logit_bias", normalize_logit_bias(self.logit_bias))
+        s(self, "suppress_token_ids", tuple(int(t) for t in self.suppress_token_ids))
+        s(self, "stop_token_ids", tuple(int(t) for t in self.stop_token_ids))
+        s(self, "stop_token_sequences", normalize_stop_sequences(self.stop_token_sequences))
+        s(self, "forced_tokens_pending", tuple(int(t) for t in self.forced_tokens_pending))
+        s(self, "row_seeds", tuple(int(t) for t in self.row_seeds))
+        s(self, "top_logprobs", int(self.top_logprobs))
+        if self.max_tokens < 0:
+            raise ValueError("max_tokens must be >= 0")
+        if self.temperature < 0:
+            raise ValueError("temperature must be >= 0")
+        if not (0.0 < self.top_p <= 1.0):
+            raise ValueError("top_p must be in (0, 1]")
+        if self.top_k < 0:
+            raise ValueError("top_k must be >= 0")
+        if not (0.0 <= self.min_p <= 1.0):
+            raise ValueError("min_p must be in [0, 1]")
+        if self.repetition_penalty <= 0:
+            raise ValueError("repetition_penalty must be > 0")
+        if not (0 <= self.top_logprobs <= 20):
+            raise ValueError("top_logprobs must be in [0, 20]")
+        if self.grammar is not None:
+            raise ValueError("user-supplied grammars are rejected before generation")
+
+    @property
+    def greedy(self) -> bool:
+        return self.temperature == 0.0
+
+
+PromptLike = Union[str, Sequence[int]]
+
+
+class LLM:
+    """Load a model and generate.
+
+    ``model`` may be a GGUF path / directory, a ``ModelWeights`` object, or the name of a built-in
+    random-init geometry (``"tiny-hybrid"``, ``"qwen35-27b"``, ...; see ``models.config.NAMED_CONFIGS``).
+    """
+
+    def __init__(self, model: Any, *, backend: str = "auto", quant: Optional[str] = None,
+                 execution_profile: Any = None, max_active_requests: int = 8,
+                 max_sequence_length: Optional[int] = None, prefix_cache: str = "radix",
+                 speculative_mtp_serving: str = "off", speculative_candidate_budget: int = 3,
+                 kv_storage: str = "bf16", tensor_parallel: int = 1, expert_parallel: int = 1,
+                 engine_command_timeout_seconds: float = 300.0, seed: int = 0, tokenizer: Any = None,
+                 engine_config: Optional[EngineConfig] = None, device: Optional[str] = None,
+                 weights_recipe: str = "q4_k_m"):
+        self.model = model
+        self.backend = self._resolve_backend(backend, device)
+        self.profile = ExecutionProfile.parse(execution_profile)
+        base = engine_config or EngineConfig.from_env()
+        self.config = replace(
+            base,
+            max_sequence_length=int(max_sequence_length or base.max_sequence_length),
+            profile=self.profile,
+            scheduler=replace(base.scheduler, max_active_requests=int(max_active_requests)),
+            kv=replace(base.kv, storage=kv_storage, prefix_cache=prefix_cache),
+            speculative=replace(base.speculative, mode="mtp" if speculative_mtp_serving not in ("off", None) else "off",
+                                draft_depth=int(speculative_candidate_budget)),
+            parallel=replace(base.parallel, tp=int(tensor_parallel), ep=int(expert_parallel)),
+            command_timeout_seconds=float(engine_command_timeout_seconds),
+        )
+        self._seed = seed
+        self._weights_recipe = weights_recipe
+        self._tokenizer = tokenizer
+        self._engine = None
+        self._lock = threading.Lock()
+        self._closed = False
+        self._weights = None
+
+    # ------------------------------------------------------------------ construction
+    @staticmethod
+    def _resolve_backend(backend: str, device: Optional[str]) -> str:
+        if backend in ("auto", None):
+            return "cuda_sm100a" if torch.cuda.is_available() else "cpu_reference"
+        if backend not in ("cuda_sm100a", "cpu_reference"):
+            raise ValueError(f"unknown backend {backend!r}; expected cuda_sm100a or cpu_reference")
+        if backend == "cuda_sm100a" and not torch.cuda.is_available():
+            raise ResidentPreparationError("backend cuda_sm100a requested but no CUDA device is visible")
+        return backend
+
+    def _load_weights(self):
+        if self._weights is not None:
+            return self._weights
+        from .loading.weights import ModelWeights
+        m = self.model
+        dev = "cuda" if self.backend == "cuda_sm100a" else "cpu"
+        if isinstance(m, ModelWeights):
+            self._weights = m
+        elif isinstance(m, (str, Path)) and Path(str(m)).exists():
+            from .loading.model_loader import load_gguf_model
+            self._weights = load_gguf_model(m, device=dev, pin=(dev == "cuda"))
+        elif isinstance(m, str):
+            from .loading.synth import build_random_model
+            from .models.config import NAMED_CONFIGS
+            if m not in NAMED_CONFIGS:
+                raise FileNotFoundError(f"model {m!r} is neither a local GGUF path nor a built-in geometry "
+                                        f"({sorted(NAMED_CONFIGS)}); nothing is ever downloaded")
+            self._weights = build_random_model(NAMED_CONFIGS[m], seed=self._seed, device=dev,
+                                               recipe=self._weights_recipe)
+        else:
+            raise TypeError(f"unsupported model argument {type(m)}")
+        return self._weights
+
+    def _get_engine(self):
+        if self._closed:
+            raise RuntimeError("LLM is closed")
+        if self._engine is None:
+            with self._lock:
+                if self._engine is None:
+                    from .generation.engine_service import build_engine
+                    self._engine = build_engine(self._load_weights(), self.backend, self.config, self._get_tokenizer())
+        return self._engine
+
+    def _get_tokenizer(self):
+        if self._tokenizer is None:
+            from .tokenization.gguf_tokenizer import tokenizer_from_metadata
+            w = self._load_weights()
+            self._tokenizer = tokenizer_from_metadata(w.metadata, w.config.vocab)
+        return self._tokenizer
+
+    def prepare(self) -> Dict[str, Any]:
+        """Make the engine resident now (weights uploaded, KV pool and scratch reserved)."""
+        t0 = time.time()
+        eng = self._get_engine()
+        info = eng.capacity()
+        info["prepare_seconds"] = time.time() - t0
+        return info
+
+    # ------------------------------------------------------------------ requests
+    def _request(self, prompt: PromptLike, sp: SamplingParams, index: int) -> GenerationRequest:
+        if isinstance(prompt, str):
+            ids = self.tokenize(prompt)
+            text = prompt
+        else:
+            ids = [int(t) for t in prompt]
+            text = None
+        return GenerationRequest.from_sampling(ids, sp, prompt_text=text, row_index=index)
+
+    def generate_detailed(self, prompts: Union[PromptLike, Sequence[PromptLike]],
+                          sampling_params: Optional[Union[SamplingParams, Sequence[SamplingParams]]] = None
+                          ) -> List[GenerationOutput]:
+        single = isinstance(prompts, str) or (len(prompts) > 0 and isinstance(prompts[0], int))
+        plist = [prompts] if single else list(prompts)
+        if sampling_params is None:
+            sps = [SamplingParams()] * len(plist)
+        elif isinstance(sampling_params, SamplingParams):
+            sps = [sampling_params] * len(plist)
+        else:
+            sps = list(sampling_params)
+            if len(sps) != len(plist):
+                raise ValueError("one SamplingParams per prompt expected")
+        reqs = [self._request(p, sp, i) for i, (p, sp) in enumerate(zip(plist, sps))]
+        outs = self._get_engine().generate(reqs)
+        tok = self._get_tokenizer()
+        for o in outs:
+            if o.text is None:
+                o.text = tok.decode(o.token_ids)
+        return outs
+
+    def generate(self, prompts, sampling_params=None) -> List[str]:
+        return [o.text for o in self.generate_detailed(prompts, sampling_params)]
+
+    def generate_token_ids(self, prompts, sampling_params=None) -> List[List[int]]:
+        return [o.token_ids for o in self.generate_detailed(prompts, sampling_params)]
+
+    def stream_detailed(self, prompt: PromptLike, sampling_params: Optional[SamplingParams] = None
+                        ) -> Iterator[GenerationStreamChunk]:
+        req = self._request(prompt, sampling_params or SamplingParams(), 0)
+        tok = self._get_tokenizer()
+        dec = tok.stream_decoder()
+        for ch in self._get_engine().stream(req):
+            if ch.text is None:
+                ch.text = dec.feed(ch.token_ids) + (dec.flush() if ch.finished else "")
+            yield ch
+
+    def stream(self, prompt: PromptLike, sampling_params: Optional[SamplingParams] = None) -> Iterator[str]:
+        for ch in self.stream_detailed(prompt, sampling_params):
+            if ch.text:
+                yield ch.text
+
+    def stream_many_detailed(self, prompts: Sequence[PromptLike], sampling_params=None):
+        """Concurrent streams: yields (index, chunk) as chunks arrive."""
+        sps = sampling_params if isinstance(sampling_params, (list, tuple)) else [sampling_params or SamplingParams()] * len(prompts)
+        reqs = [self._request(p, sp, i) for i, (p, sp) in enumerate(zip(prompts, sps))]
+        yield from self._get_engine().stream_many(reqs)
+
+    def chat(self, messages: Sequence[Mapping[str, Any]], sampling_params: Optional[SamplingParams] = None,
+             tools: Optional[Sequence[Mapping[str, Any]]] = None, enable_thinking: bool = True) -> GenerationOutput:
+        from .chat.templates import render_chat
+        prompt = render_chat(messages, tools=tools, enable_thinking=enable_thinking,
+                             arch=self._load_weights().config.arch)
+        return self.generate_detailed(prompt, sampling_params or SamplingParams(max_tokens=256))[0]
+
+    def generate_speculative_mtp_detailed(self, prompts, sampling_params=None) -> List[GenerationOutput]:
+        sps = sampling_params or SamplingParams()
+        if isinstance(sps, SamplingParams):
+            sps = replace(sps, speculative_mtp=True)
+        return self.generate_detailed(prompts, sps)
+
+    # ------------------------------------------------------------------ tokenizer helpers
+    def tokenize(self, text: str) -> List[int]:
+        return self._get_tokenizer().encode(text)
+
+    def detokenize(self, ids: Sequence[int]) -> str:
+        return self._get_tokenizer().decode(list(ids))
+
+    def count_tokens(self, text: str) -> int:
+        return len(self.tokenize(text))
+
+    # ------------------------------------------------------------------ introspection / lifecycle
+    def resident_capacity_estimate(self) -> Dict[str, Any]:
+        return self._get_engine().capacity()
+
+    def engine_service_health(self) -> Dict[str, Any]:
+        if self._engine is None:
+            return {"state": "not_started", "healthy": True}
+        return self._engine.health()
+
+    def live_loop_snapshot(self) -> Dict[str, Any]:
+        if self._engine is None:
+            return {}
+        return self._engine.snapshot()
+
+    def reset(self) -> None:
+        if self._engine is not None:
+            self._engine.reset()
+
+    def close(self) -> None:
+        self._closed = True
+        if self._engine is not None:
+            self._engine.close()
+            self._engine = None
+
+    def __enter__(self) -> "LLM":
+        return self
+
+    def __exit__(self, *exc) -> None:
+        self.close()

@@ -1,0 +1,362 @@
+"""GPU executor for the Qwen3.5-family hybrid decoders and plain dense decoders.
+
+One object owns the device-resident weights (in kernel layouts), the paged KV
+pool tensors, the per-slot recurrent state (conv window + Gated-DeltaNet state)
+and all scratch.  ``forward`` runs a packed batch of rows that may mix requests
+("segments"): decode rows, speculative verify chains and prefill chunks all go
+through the same call, differing only in how many rows a segment has.
+
+Kernel sequence per layer follows the reference executors
+(``hipengine/runtime/qwen35_gguf_layer_attn.py:474-1147`` for linear / full
+attention, ``hipengine/runtime/qwen35_gguf_layer_ffn.py:301-1278`` for dense and
+MoE FFN) but the fusion boundaries are chosen for B200: for <= 8 rows each
+projection is a single fused [RMSNorm + int8 quantize + dp4a GEMV + epilogue]
+launch; above that the projections run on the tcgen05 GEMM.
+"""
+from __future__ import annotations
+
+import math
+import os
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..loading.weights import ModelWeights, QTensor, ffn_norm_slot
+from ..ops import kernels as K
+from ..ops.kernels import DeviceWeight, GemvSegment
+from ..quant.ggml import GGMLType
+from .config import ModelConfig
+
+PAGE = 16
+GEMV_MAX_ROWS = 8
+
+
+@dataclass
+class BatchDesc:
+    """Device-side description of one packed forward batch of T rows in n_seg segments."""
+    tokens: torch.Tensor      # [T] int64
+    slot: torch.Tensor        # [T] int32   state/block-table slot of each row
+    pos: torch.Tensor         # [T] int32   absolute position of each row
+    ctx_len: torch.Tensor     # [T] int32   keys visible to the row (pos + 1)
+    seg_start: torch.Tensor   # [n_seg + 1] int32
+    seg_slot: torch.Tensor    # [n_seg] int32
+    tok_seg: torch.Tensor     # [T] int32
+    T: int
+    n_seg: int
+    max_ctx: int              # host upper bound of ctx_len (sizes the split-K grid)
+
+
+def make_batch(segments: Sequence[Tuple[int, int, Sequence[int]]], device) -> BatchDesc:
+    """segments: (slot, start_pos, token_ids) per request.  Builds the packed descriptor (one H2D copy each)."""
+    toks: List[int] = []
+    slot: List[int] = []
+    pos: List[int] = []
+    seg_start = [0]
+    seg_slot: List[int] = []
+    tok_seg: List[int] = []
+    max_ctx = 1
+    for si, (s, p0, ids) in enumerate(segments):
+        n = len(ids)
+        toks += list(ids)
+        slot += [s] * n
+        pos += list(range(p0, p0 + n))
+        tok_seg += [si] * n
+        seg_start.append(seg_start[-1] + n)
+        seg_slot.append(s)
+        max_ctx = max(max_ctx, p0 + n)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=device)
+    pos_t = i32(pos)
+    return BatchDesc(torch.tensor(toks, dtype=torch.int64, device=device), i32(slot), pos_t, pos_t + 1,
+                     i32(seg_start), i32(seg_slot), i32(tok_seg), len(toks), len(segments), max_ctx)
+
+
+class _Scratch:
+    """Grow-only named scratch tensors (no allocation on the steady-state path)."""
+
+    def __init__(self, device):
+        self.device = device
+        self.bufs: Dict[str, torch.Tensor] = {}
+
+    def get(self, name: str, shape, dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= s
+        cur = self.bufs.get(name)
+        if cur is None or cur.numel() < n or cur.dtype != dtype:
+            cur = torch.empty(max(n, 1), dtype=dtype, device=self.device)
+            self.bufs[name] = cur
+        return cur[:n].view(*shape)
+
+
+class HybridExecutor:
+    def __init__(self, weights: ModelWeights, device="cuda", max_slots: int = 4, max_context: int = 4608,
+                 n_pages: Optional[int] = None, gemm_impl: Optional[str] = None):
+        self.cfg = cfg = weights.config
+        self.device = torch.device(device)
+        self.max_slots = max_slots
+        self.max_context = max_context
+        self.max_pages_per_slot = (max_context + PAGE - 1) // PAGE
+        self.n_pages = n_pages if n_pages is not None else max_slots * self.max_pages_per_slot + 1
+        self.gemm_impl = gemm_impl or os.environ.get("HE_GEMM", "tcgen05")
+        self.scratch = _Scratch(self.device)
+        self.dw: Dict[str, DeviceWeight] = {}
+        self.f32: Dict[str, torch.Tensor] = {}
+        self._load(weights)
+        self._alloc_state()
+
+    # ------------------------------------------------------------------ weights
+    def _load(self, weights: ModelWeights) -> None:
+        for name, t in weights.tensors.items():
+            raw = t.raw.to(self.device)
+            if t.ggml_type == GGMLType.F32 and (len(t.shape) == 1 or name.endswith(("ssm_a", "ssm_dt.bias",
+                                                                                  "ssm_conv1d.weight"))):
+                self.f32[name] = raw.view(torch.float32).reshape(t.shape).contiguous()
+                continue
+            if len(t.shape) == 3:
+                E, Nn, Kk = t.shape
+                self.dw[name] = K.to_device_weight(raw, t.ggml_type, E * Nn, Kk)
+                continue
+            if t.ggml_type == GGMLType.F32:
+                self.f32[name] = raw.view(torch.float32).reshape(t.shape).contiguous()
+            self.dw[name] = K.to_device_weight(raw, t.ggml_type, t.n_rows, t.n_cols)
+        if "output.weight" not in self.dw:
+            self.dw["output.weight"] = self.dw["token_embd.weight"]
+
+    def W(self, i: int, slot: str) -> DeviceWeight:
+        return self.dw[f"blk.{i}.{slot}"]
+
+    def F(self, i: int, slot: str) -> torch.Tensor:
+        return self.f32[f"blk.{i}.{slot}"]
+
+    # ------------------------------------------------------------------ state
+    def _alloc_state(self) -> None:
+        cfg, dev = self.cfg, self.device
+        kinds = cfg.layer_kinds()
+        n_blocks = cfg.n_layers + cfg.nextn_layers
+        self.kv: Dict[int, torch.Tensor] = {}
+        self.conv_state: Dict[int, torch.Tensor] = {}
+        self.gdn_state: Dict[int, torch.Tensor] = {}
+        for i in range(n_blocks):
+            full = True if i >= cfg.n_layers else kinds[i] == "full"
+            if full:
+                self.kv[i] = torch.zeros(self.n_pages, 2, cfg.n_kv_heads, PAGE, cfg.head_dim, dtype=torch.bfloat16,
+                                         device=dev)
+            else:
+                self.conv_state[i] = torch.zeros(self.max_slots, cfg.linear_qkv_width, cfg.conv_kernel - 1,
+                                                 dtype=torch.float32, device=dev)
+                self.gdn_state[i] = torch.zeros(self.max_slots, cfg.ssm_v_heads, cfg.ssm_state, cfg.ssm_state,
+                                                dtype=torch.float32, device=dev)
+        # default identity paging: slot s owns pages [1 + s*mp, 1 + (s+1)*mp); page 0 is a scratch sink
+        mp = self.max_pages_per_slot
+        bt = torch.arange(self.max_slots * mp, dtype=torch.int32).reshape(self.max_slots, mp) + 1
+        if self.n_pages < self.max_slots * mp + 1:
+            bt = bt.clamp(max=self.n_pages - 1)
+        self.block_table = bt.to(dev)
+        self.am_v = torch.empty(GEMV_MAX_ROWS * 64 * 64, dtype=torch.float32, device=dev)
+        self.am_i = torch.empty(GEMV_MAX_ROWS * 64 * 64, dtype=torch.int32, device=dev)
+
+    def reset_slot(self, slot: int) -> None:
+        for t in self.conv_state.values():
+            t[slot].zero_()
+        for t in self.gdn_state.values():
+            t[slot].zero_()
+
+    def state_bytes(self) -> int:
+        tot = 0
+        for d in (self.kv, self.conv_state, self.gdn_state):
+            tot += sum(t.numel() * t.element_size() for t in d.values())
+        return tot
+
+    # ------------------------------------------------------------------ linear algebra dispatch
+    def _gemm(self, x: torch.Tensor, w: DeviceWeight, out: torch.Tensor, row0: int = 0, rows: Optional[int] = None,
+              tag: str = "w") -> torch.Tensor:
+        """out[T, rows] (bf16) = x[T, K] (bf16) @ W[row0:row0+rows, :]^T on the tensor cores."""
+        rows = w.n_rows - row0 if rows is None else rows
+        if self.gemm_impl == "tcgen05":
+            from ..ops import gemm as G
+            return G.gemm_quant(x, w, out, self.scratch, row0=row0, rows=rows)
+        wb = self.scratch.get("deq_" + tag, (rows, w.n_cols), torch.bfloat16)
+        K.dequant_bf16(w, wb, row0=row0, rows=rows)
+        torch.matmul(x, wb.t(), out=out)
+        return out
+
+    # ------------------------------------------------------------------ layers
+    def _attention_full(self, i: int, h: torch.Tensor, b: BatchDesc, small: bool) -> None:
+        cfg, sc = self.cfg, self.scratch
+        T = b.T
+        H, Hkv, D = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
+        qw = cfg.q_proj_width
+        if small:
+            qf = sc.get("q_f32", (T, qw), torch.float32)
+            kf = sc.get("k_f32", (T, cfg.kv_width), torch.float32)
+            vf = sc.get("v_f32", (T, cfg.kv_width), torch.float32)
+            K.gemv(h, [GemvSegment(self.W(i, "attn_q.weight"), qf), GemvSegment(self.W(i, "attn_k.weight"), kf),
+                       GemvSegment(self.W(i, "attn_v.weight"), vf)], norm_w=self.F(i, "attn_norm.weight"),
+                   eps=cfg.rms_eps)
+        else:
+            xn = sc.get("xn", (T, cfg.hidden), torch.bfloat16)
+            K.rmsnorm_rows(h, self.F(i, "attn_norm.weight"), xn, cfg.rms_eps)
+            qf = self._gemm(xn, self.W(i, "attn_q.weight"), sc.get("q_bf", (T, qw), torch.bfloat16), tag="q")
+            kf = self._gemm(xn, self.W(i, "attn_k.weight"), sc.get("k_bf", (T, cfg.kv_width), torch.bfloat16), tag="k")
+            vf = self._gemm(xn, self.W(i, "attn_v.weight"), sc.get("v_bf", (T, cfg.kv_width), torch.bfloat16), tag="k")
+        q_out = sc.get("q_out", (T, H, D), torch.bfloat16)
+        gate = sc.get("gate_out", (T, H, D), torch.bfloat16) if cfg.gated_attention else None
+        qn = self.f32.get(f"blk.{i}.attn_q_norm.weight") if cfg.qk_norm else None
+        kn = self.f32.get(f"blk.{i}.attn_k_norm.weight") if cfg.qk_norm else None
+        K.qkv_post(qf, kf, vf, qn, kn, q_out, gate, self.kv[i], self.block_table, b.slot, b.pos, H, Hkv, D, PAGE,
+                   cfg.gated_attention, cfg.rope_dim, cfg.rope_theta, cfg.rms_eps)
+        attn = sc.get("attn_out", (T, H * D), torch.bfloat16)
+        self._attend(i, q_out, gate, b, attn)
+        if small:
+            K.gemv(attn, [GemvSegment(self.W(i, "attn_output.weight"), h, K.EPI_ADD_F32)])
+        else:
+            y = self._gemm(attn, self.W(i, "attn_output.weight"), sc.get("y_bf", (T, cfg.hidden), torch.bfloat16),
+                           tag="o")
+            K.resid_add_bf16(h, y)
+
+    def _attend(self, i: int, q_out: torch.Tensor, gate: Optional[torch.Tensor], b: BatchDesc,
+                out: torch.Tensor) -> None:
+        cfg = self.cfg
+        T = b.T
+        H, Hkv, D = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
+        if T > GEMV_MAX_ROWS and b.n_seg == 1 and os.environ.get("HE_PREFILL_ATTN", "flash") == "flash":
+            from ..ops import attention as A
+            if A.flash_prefill_available(D):
+                A.flash_prefill(q_out, gate, self.kv[i], self.block_table, b, out, H, Hkv, D, PAGE, cfg.scale())
+                return
+        split_len = 128 if b.max_ctx <= 8192 else 256
+        max_splits = max(1, (b.max_ctx + split_len - 1) // split_len)
+        part = self.scratch.get("attn_part", (K.attn_decode_scratch_floats(T, H, max_splits, D),), torch.float32)
+        K.attn_decode(q_out, gate, self.kv[i], self.block_table, b.slot, b.ctx_len, part, out, H, Hkv, D, PAGE,
+                      split_len, max_splits, cfg.scale())
+
+    def _attention_linear(self, i: int, h: torch.Tensor, b: BatchDesc, small: bool,
+                          journal: Optional[dict] = None) -> None:
+        cfg, sc = self.cfg, self.scratch
+        T = b.T
+        G, Hv, S, C = cfg.ssm_groups, cfg.ssm_v_heads, cfg.ssm_state, cfg.linear_qkv_width
+        inner = cfg.ssm_inner
+        a_p = sc.get("a_proj", (T, Hv), torch.float32)
+        b_p = sc.get("b_proj", (T, Hv), torch.float32)
+        if small:
+            qkv = sc.get("qkv_f32", (T, C), torch.float32)
+            z = sc.get("z_f32", (T, inner), torch.float32)
+            K.gemv(h, [GemvSegment(self.W(i, "attn_qkv.weight"), qkv), GemvSegment(self.W(i, "attn_gate.weight"), z),
+                       GemvSegment(self.W(i, "ssm_alpha.weight"), a_p), GemvSegment(self.W(i, "ssm_beta.weight"), b_p)],
+                   norm_w=self.F(i, "attn_norm.weight"), eps=cfg.rms_eps)
+        else:
+            xn = sc.get("xn", (T, cfg.hidden), torch.bfloat16)
+            K.rmsnorm_rows(h, self.F(i, "attn_norm.weight"), xn, cfg.rms_eps)
+            qkv = self._gemm(xn, self.W(i, "attn_qkv.weight"), sc.get("qkv_bf", (T, C), torch.bfloat16), tag="q")
+            z = self._gemm(xn, self.W(i, "attn_gate.weight"), sc.get("z_bf", (T, inner), torch.bfloat16), tag="q")
+            K.small_gemm_f32(xn, self.F(i, "ssm_alpha.weight"), a_p)
+            K.small_gemm_f32(xn, self.F(i, "ssm_beta.weight"), b_p)
+        conv = sc.get("conv_out", (T, C), torch.float32)
+        cj = journal["conv"][i] if journal is not None else None
+        K.conv1d(qkv, self.F(i, "ssm_conv1d.weight"), self.conv_state[i], b.seg_start, b.seg_slot, b.tok_seg, conv, C,
+                 update_state=journal is None, journal=cj)
+        decay = sc.get("decay", (T, Hv), torch.float32)
+        beta = sc.get("beta", (T, Hv), torch.float32)
+        K.gdn_prepare(conv, a_p, b_p, self.F(i, "ssm_a").reshape(-1), self.F(i, "ssm_dt.bias").reshape(-1), decay, beta,
+                      G, Hv, S)
+        o = sc.get("gdn_o", (T, Hv, S), torch.float32)
+        gj = journal["gdn"][i] if journal is not None else None
+        K.gdn_scan(conv, decay, beta, self.gdn_state[i], b.seg_start, b.seg_slot, o, G, Hv,
+                   write_state=journal is None, journal=gj)
+        og = sc.get("gdn_og", (T, inner), torch.bfloat16)
+        K.gdn_gated_norm(o, z, self.F(i, "ssm_norm.weight").reshape(-1), og, Hv, S, cfg.rms_eps)
+        if small:
+            K.gemv(og, [GemvSegment(self.W(i, "ssm_out.weight"), h, K.EPI_ADD_F32)])
+        else:
+            y = self._gemm(og, self.W(i, "ssm_out.weight"), sc.get("y_bf", (T, cfg.hidden), torch.bfloat16), tag="o")
+            K.resid_add_bf16(h, y)
+
+    def _ffn(self, i: int, h: torch.Tensor, b: BatchDesc, small: bool) -> None:
+        cfg, sc = self.cfg, self.scratch
+        T = b.T
+        norm_w = self.F(i, ffn_norm_slot(cfg))
+        if cfg.is_moe:
+            from . import moe as M
+            M.moe_ffn(self, i, h, T, norm_w, small)
+            return
+        Fd = cfg.ffn
+        epi = K.EPI_SILU_MUL if cfg.act == "silu" else K.EPI_GELU_MUL
+        if small:
+            act = sc.get("ffn_act", (T, Fd), torch.bfloat16)
+            K.gemv(h, [GemvSegment(self.W(i, "ffn_gate.weight"), act, epi, self.W(i, "ffn_up.weight"))],
+                   norm_w=norm_w, eps=cfg.rms_eps)
+            K.gemv(act, [GemvSegment(self.W(i, "ffn_down.weight"), h, K.EPI_ADD_F32)])
+        else:
+            xn = sc.get("xn", (T, cfg.hidden), torch.bfloat16)
+            K.rmsnorm_rows(h, norm_w, xn, cfg.rms_eps)
+            gu = sc.get("ffn_gu", (T, 2 * Fd), torch.bfloat16)
+            self._gemm(xn, self.W(i, "ffn_gate.weight"), gu[:, :Fd], tag="g")
+            self._gemm(xn, self.W(i, "ffn_up.weight"), gu[:, Fd:], tag="g")
+            act = sc.get("ffn_act", (T, Fd), torch.bfloat16)
+            K.act_mul(gu, act, cfg.act)
+            y = self._gemm(act, self.W(i, "ffn_down.weight"), sc.get("y_bf", (T, cfg.hidden), torch.bfloat16), tag="d")
+            K.resid_add_bf16(h, y)
+
+    # ------------------------------------------------------------------ whole model
+    def forward(self, b: BatchDesc, journal: Optional[dict] = None, h_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Runs all layers over the packed rows; returns the fp32 residual stream [T, hidden] (pre output_norm)."""
+        cfg = self.cfg
+        T = b.T
+        small = T <= GEMV_MAX_ROWS
+        h = h_out if h_out is not None else self.scratch.get("h", (T, cfg.hidden), torch.float32)
+        K.embed(self.dw["token_embd.weight"], b.tokens, h, cfg.embed_scale)
+        for i in range(cfg.n_layers):
+            if cfg.is_full_attention_layer(i):
+                self._attention_full(i, h, b, small)
+            else:
+                self._attention_linear(i, h, b, small, journal)
+            self._ffn(i, h, b, small)
+        return h
+
+    def logits(self, h_rows: torch.Tensor, out: Optional[torch.Tensor] = None,
+               hidden_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """output_norm + lm_head over the given residual rows [R, hidden] -> fp32 logits [R, vocab]."""
+        cfg = self.cfg
+        R = h_rows.shape[0]
+        head = self.dw["output.weight"]
+        if out is None:
+            out = self.scratch.get("logits", (R, cfg.vocab), torch.float32)
+        if hidden_out is not None:
+            K.rmsnorm_rows(h_rows, self.f32["output_norm.weight"], hidden_out, cfg.rms_eps)
+        if R <= GEMV_MAX_ROWS:
+            K.gemv(h_rows, [GemvSegment(head, out)], norm_w=self.f32["output_norm.weight"], eps=cfg.rms_eps)
+        else:
+            xn = self.scratch.get("xn_head", (R, cfg.hidden), torch.bfloat16)
+            K.rmsnorm_rows(h_rows, self.f32["output_norm.weight"], xn, cfg.rms_eps)
+            lb = self._gemm(xn, head, self.scratch.get("logits_bf", (R, cfg.vocab), torch.bfloat16), tag="head")
+            out.copy_(lb)
+        if cfg.final_softcap > 0:
+            K.softcap_(out, cfg.final_softcap)
+        return out
+
+    def greedy(self, logits: torch.Tensor, out_ids: torch.Tensor) -> torch.Tensor:
+        return K.argmax_rows(logits, self.am_v, self.am_i, out_ids)
+
+    # ------------------------------------------------------------------ convenience (tests, smoke, bench)
+    @torch.no_grad()
+    def prefill(self, slot: int, tokens: Sequence[int], start_pos: int = 0, chunk: int = 4096) -> torch.Tensor:
+        """Prefill one request; returns the fp32 logits of its last row [1, vocab]."""
+        last_h = None
+        for c0 in range(0, len(tokens), chunk):
+            ids = tokens[c0:c0 + chunk]
+            b = make_batch([(slot, start_pos + c0, ids)], self.device)
+            h = self.forward(b)
+            last_h = h[b.T - 1:b.T]
+        return self.logits(last_h)
+
+    @torch.no_grad()
+    def forward_logits(self, slot: int, tokens: Sequence[int], start_pos: int = 0) -> torch.Tensor:
+        """All-row logits for one segment (teacher-forced comparison against the reference)."""
+        b = make_batch([(slot, start_pos, tokens)], self.device)
+        h = self.forward(b)
+        out = torch.empty(b.T, self.cfg.vocab, dtype=torch.float32, device=self.device)
+        for r0 in range(0, b.T, GEMV_MAX_ROWS):
+            r1 = min(b.T, r0 + GEMV_MAX_ROWS)
+            self.logits(h[r0:r1], out=out[r0:r1])
+        return out

@@ -1,0 +1,27 @@
+"""Prefill (flash) attention launcher.  The decode/split-K launcher lives in ``ops.kernels``."""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from ..core import native as N
+
+
+def flash_prefill_available(head_dim: int) -> bool:
+    try:
+        return head_dim in (64, 128, 256) and hasattr(N.lib(), "he_flash_prefill")
+    except Exception:
+        return False
+
+
+def flash_prefill(q, gate, kv_cache, block_table, b, out, H, Hkv, D, page, scale, window: int = 0) -> None:
+    """Causal paged GQA attention over one segment's rows (append-then-attend) with the sigmoid gate fused."""
+    L = N.lib()
+    N.check(L.he_flash_prefill(C.c_void_p(q.data_ptr()), C.c_void_p(None if gate is None else gate.data_ptr()),
+                               C.c_void_p(kv_cache.data_ptr()), C.c_void_p(block_table.data_ptr()),
+                               C.c_void_p(b.slot.data_ptr()), C.c_void_p(b.pos.data_ptr()),
+                               C.c_void_p(out.data_ptr()), C.c_int(b.T), C.c_int(H), C.c_int(Hkv), C.c_int(D),
+                               C.c_int(page), C.c_int(block_table.shape[1]), C.c_float(scale), C.c_int(window),
+                               C.c_void_p(torch.cuda.current_stream().cuda_stream)), "he_flash_prefill")

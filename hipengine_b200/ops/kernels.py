@@ -1,0 +1,403 @@
+"""Python launchers for the sm_100a kernel library (thin ctypes wrappers over ``csrc/*.cu``).
+
+Every function here launches hand-written CUDA on the current torch stream and
+raises if the native library is missing -- there is no PyTorch fallback on the
+hot path.  Argument structs mirror the C structs field for field.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from ..core import native as N
+from ..quant.ggml import GGMLType
+
+c_vp = C.c_void_p
+c_ll = C.c_longlong
+
+EPI_F32, EPI_BF16, EPI_ADD_F32, EPI_SILU_MUL, EPI_GELU_MUL = 0, 1, 2, 3, 4
+
+
+class _GemvSeg(C.Structure):
+    _fields_ = [("w", c_vp), ("w2", c_vp), ("out", c_vp), ("out_stride", c_ll), ("n_rows", C.c_int),
+                ("qtype", C.c_int), ("qtype2", C.c_int), ("epi", C.c_int)]
+
+
+class _GemvArgs(C.Structure):
+    _fields_ = [("seg", _GemvSeg * 4), ("n_seg", C.c_int), ("K", C.c_int), ("R", C.c_int), ("x_dtype", C.c_int),
+                ("x", c_vp), ("x_stride", c_ll), ("norm_w", c_vp), ("eps", C.c_float), ("need_xf", C.c_int)]
+
+
+class _QkvArgs(C.Structure):
+    _fields_ = [("q", c_vp), ("k", c_vp), ("v", c_vp), ("in_dtype", C.c_int),
+                ("q_stride", c_ll), ("k_stride", c_ll), ("v_stride", c_ll),
+                ("q_norm", c_vp), ("k_norm", c_vp), ("v_norm", C.c_int),
+                ("q_out", c_vp), ("gate_out", c_vp), ("kv_cache", c_vp), ("block_table", c_vp),
+                ("slot", c_vp), ("pos", c_vp), ("max_pages", C.c_int),
+                ("H", C.c_int), ("Hkv", C.c_int), ("D", C.c_int), ("page", C.c_int), ("gated", C.c_int),
+                ("rope_dim", C.c_int), ("theta", C.c_float), ("eps", C.c_float), ("q_scale", C.c_float)]
+
+
+class _ConvArgs(C.Structure):
+    _fields_ = [("x", c_vp), ("in_dtype", C.c_int), ("x_stride", c_ll), ("w", c_vp), ("state", c_vp),
+                ("seg_start", c_vp), ("seg_slot", c_vp), ("tok_seg", c_vp), ("out", c_vp), ("journal", c_vp),
+                ("C", C.c_int), ("KW", C.c_int), ("T", C.c_int), ("n_seg", C.c_int)]
+
+
+class _GdnPrepArgs(C.Structure):
+    _fields_ = [("qkv", c_vp), ("a", c_vp), ("b", c_vp), ("a_stride", c_ll), ("b_stride", c_ll),
+                ("ssm_a", c_vp), ("dt_bias", c_vp), ("decay", c_vp), ("beta", c_vp),
+                ("C", C.c_int), ("G", C.c_int), ("Hv", C.c_int), ("S", C.c_int), ("T", C.c_int)]
+
+
+class _GdnScanArgs(C.Structure):
+    _fields_ = [("qkv", c_vp), ("decay", c_vp), ("beta", c_vp), ("state", c_vp), ("seg_start", c_vp),
+                ("seg_slot", c_vp), ("out", c_vp), ("journal", c_vp),
+                ("C", C.c_int), ("G", C.c_int), ("Hv", C.c_int), ("T", C.c_int), ("n_seg", C.c_int),
+                ("write_state", C.c_int)]
+
+
+class _AttnDecArgs(C.Structure):
+    _fields_ = [("q", c_vp), ("gate", c_vp), ("kv_cache", c_vp), ("block_table", c_vp), ("slot", c_vp),
+                ("ctx_len", c_vp), ("partial", c_vp), ("out", c_vp),
+                ("R", C.c_int), ("H", C.c_int), ("Hkv", C.c_int), ("D", C.c_int), ("page", C.c_int),
+                ("max_pages", C.c_int), ("split_len", C.c_int), ("max_splits", C.c_int), ("window", C.c_int),
+                ("scale", C.c_float)]
+
+
+_CHECKED = False
+
+
+def _check_abi() -> None:
+    """Struct sizes must agree with the compiled library (catches drift between Python and C)."""
+    global _CHECKED
+    if _CHECKED:
+        return
+    L = N.lib()
+    pairs = [("he_gemv_args_size", _GemvArgs), ("he_qkv_args_size", _QkvArgs), ("he_conv_args_size", _ConvArgs),
+             ("he_gdn_prep_args_size", _GdnPrepArgs), ("he_gdn_scan_args_size", _GdnScanArgs),
+             ("he_attn_dec_args_size", _AttnDecArgs)]
+    for fn, st in pairs:
+        got = getattr(L, fn)()
+        if got != C.sizeof(st):
+            raise RuntimeError(f"ABI mismatch for {st.__name__}: C={got} Python={C.sizeof(st)}")
+    _CHECKED = True
+
+
+def launch_count() -> int:
+    """Number of kernels of this library launched so far in this process (graph replays included)."""
+    return N.launch_count()
+
+
+def add_launches(n: int) -> None:
+    N.add_launches(n)
+
+
+def _p(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return 0
+    if t.dtype == torch.bfloat16:
+        return 1
+    raise TypeError(f"unsupported activation dtype {t.dtype}")
+
+
+def _stream() -> c_vp:
+    return c_vp(torch.cuda.current_stream().cuda_stream)
+
+
+# ----------------------------------------------------------------------------- device weights
+
+@dataclass
+class DeviceWeight:
+    """A weight matrix in its device layout (Q4_K as stored; Q6_K / Q8_0 planar; float types as stored)."""
+    qtype: int
+    n_rows: int
+    n_cols: int
+    data: torch.Tensor  # uint8 / float storage on the device
+
+    @property
+    def ptr(self) -> int:
+        return self.data.data_ptr()
+
+
+_KERNEL_QTYPES = (GGMLType.Q4_K, GGMLType.Q6_K, GGMLType.Q8_0, GGMLType.F32, GGMLType.F16, GGMLType.BF16)
+
+
+def to_device_weight(raw: torch.Tensor, qtype: int, n_rows: int, n_cols: int) -> DeviceWeight:
+    """Repack GGUF bytes (uint8 [rows, row_bytes], already on the device) into the kernel layout."""
+    qtype = GGMLType(qtype)
+    if qtype not in _KERNEL_QTYPES:
+        # formats without a native kernel are widened to bf16 once at load time
+        from ..quant.ggml import dequantize_torch
+        w = dequantize_torch(raw, qtype, n_rows, n_cols).to(torch.bfloat16).contiguous()
+        return DeviceWeight(int(GGMLType.BF16), n_rows, n_cols, w)
+    raw = raw.contiguous()
+    if qtype in (GGMLType.Q6_K, GGMLType.Q8_0):
+        _check_abi()
+        out = torch.empty(raw.numel(), dtype=torch.uint8, device=raw.device)
+        N.check(N.lib().he_repack(c_vp(raw.data_ptr()), c_vp(out.data_ptr()), C.c_int(int(qtype)),
+                                  c_ll(n_rows), c_ll(n_cols), _stream()), "he_repack")
+        return DeviceWeight(int(qtype), n_rows, n_cols, out)
+    return DeviceWeight(int(qtype), n_rows, n_cols, raw)
+
+
+def unpack_device_weight(dw: DeviceWeight) -> torch.Tensor:
+    """Inverse of ``to_device_weight`` for the planar layouts (lossless; used by round-trip tests)."""
+    t = GGMLType(dw.qtype)
+    d = dw.data.reshape(-1)
+    if t == GGMLType.Q6_K:
+        nblk = dw.n_rows * dw.n_cols // 256
+        ql = d[:nblk * 128].reshape(nblk, 128)
+        qh = d[nblk * 128:nblk * 192].reshape(nblk, 64)
+        sc = d[nblk * 192:nblk * 208].reshape(nblk, 16)
+        dd = d[nblk * 208:nblk * 210].reshape(nblk, 2)
+        return torch.cat([ql, qh, sc, dd], dim=1).reshape(dw.n_rows, -1)
+    if t == GGMLType.Q8_0:
+        nblk = dw.n_rows * dw.n_cols // 32
+        qs = d[:nblk * 32].reshape(nblk, 32)
+        dd = d[nblk * 32:nblk * 34].reshape(nblk, 2)
+        return torch.cat([dd, qs], dim=1).reshape(dw.n_rows, -1)
+    return dw.data.reshape(dw.n_rows, -1)
+
+
+# ----------------------------------------------------------------------------- GEMV
+
+@dataclass
+class GemvSegment:
+    w: DeviceWeight
+    out: torch.Tensor          # [R, >= n_rows] fp32 or bf16 (row stride = out.stride(0))
+    epi: int = EPI_F32
+    w2: Optional[DeviceWeight] = None
+
+
+def gemv(x: torch.Tensor, segs: Sequence[GemvSegment], norm_w: Optional[torch.Tensor] = None,
+         eps: float = 1e-6) -> None:
+    """Fused [RMSNorm] + int8 activation quantize + quantized GEMV + epilogue for 1..8 rows."""
+    _check_abi()
+    R, K = x.shape
+    a = _GemvArgs()
+    need_xf = 0
+    for i, s in enumerate(segs):
+        sg = a.seg[i]
+        sg.w = s.w.ptr
+        sg.w2 = s.w2.ptr if s.w2 is not None else None
+        sg.out = s.out.data_ptr()
+        sg.out_stride = s.out.stride(0) if s.out.dim() > 1 else s.out.numel()
+        sg.n_rows = s.w.n_rows
+        sg.qtype = s.w.qtype
+        sg.qtype2 = s.w2.qtype if s.w2 is not None else 0
+        sg.epi = s.epi
+        assert s.w.n_cols == K, (s.w.n_cols, K)
+        if s.w.qtype in (0, 1, 30) or (s.w2 is not None and s.w2.qtype in (0, 1, 30)):
+            need_xf = 1
+    a.n_seg = len(segs)
+    a.K = K
+    a.R = R
+    a.x_dtype = _dt(x)
+    a.x = x.data_ptr()
+    a.x_stride = x.stride(0)
+    a.norm_w = _p(norm_w)
+    a.eps = eps
+    a.need_xf = need_xf
+    N.check(N.lib().he_gemv(C.byref(a), C.c_int(N.num_sms()), _stream()), "he_gemv")
+
+
+def dequant_bf16(w: DeviceWeight, out: Optional[torch.Tensor] = None, row0: int = 0,
+                 rows: Optional[int] = None) -> torch.Tensor:
+    rows = w.n_rows - row0 if rows is None else rows
+    if out is None:
+        out = torch.empty(rows, w.n_cols, dtype=torch.bfloat16, device=w.data.device)
+    N.check(N.lib().he_dequant_bf16(c_vp(w.ptr), c_vp(out.data_ptr()), C.c_int(w.qtype), c_ll(row0), c_ll(rows),
+                                    c_ll(w.n_rows), C.c_int(w.n_cols), _stream()), "he_dequant_bf16")
+    return out
+
+
+def embed(w: DeviceWeight, ids: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    assert ids.dtype == torch.int64 and out.dtype == torch.float32
+    N.check(N.lib().he_embed(c_vp(w.ptr), C.c_int(w.qtype), c_ll(w.n_rows), C.c_int(w.n_cols), c_vp(ids.data_ptr()),
+                             c_vp(out.data_ptr()), C.c_float(scale), C.c_int(ids.numel()), _stream()), "he_embed")
+    return out
+
+
+# ----------------------------------------------------------------------------- row-wise layers
+
+def rmsnorm_rows(x: torch.Tensor, w: Optional[torch.Tensor], out: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    T, H = x.shape
+    assert x.dtype == torch.float32
+    N.check(N.lib().he_rmsnorm_rows(c_vp(x.data_ptr()), c_vp(_p(w)), c_vp(out.data_ptr()),
+                                    C.c_int(1 if out.dtype == torch.bfloat16 else 0), C.c_int(T), C.c_int(H),
+                                    C.c_float(eps), c_ll(x.stride(0)), c_ll(out.stride(0)), _stream()),
+            "he_rmsnorm_rows")
+    return out
+
+
+def act_mul(gu: torch.Tensor, out: torch.Tensor, act: str = "silu") -> torch.Tensor:
+    T, F2 = gu.shape
+    N.check(N.lib().he_act_mul(c_vp(gu.data_ptr()), c_vp(out.data_ptr()), c_ll(T), C.c_int(F2 // 2),
+                               C.c_int(0 if act == "silu" else 1), _stream()), "he_act_mul")
+    return out
+
+
+def resid_add_bf16(h: torch.Tensor, y: torch.Tensor) -> None:
+    assert h.dtype == torch.float32 and y.dtype == torch.bfloat16 and h.numel() == y.numel()
+    N.check(N.lib().he_resid_add_bf16(c_vp(h.data_ptr()), c_vp(y.data_ptr()), c_ll(h.numel()), _stream()),
+            "he_resid_add_bf16")
+
+
+def qkv_post(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_norm, k_norm, q_out: torch.Tensor,
+             gate_out: Optional[torch.Tensor], kv_cache: torch.Tensor, block_table: torch.Tensor,
+             slot: torch.Tensor, pos: torch.Tensor, H: int, Hkv: int, D: int, page: int, gated: bool,
+             rope_dim: int, theta: float, eps: float, q_scale: float = 1.0, v_norm: bool = False) -> None:
+    _check_abi()
+    T = q.shape[0]
+    a = _QkvArgs()
+    a.q, a.k, a.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
+    a.in_dtype = _dt(q)
+    a.q_stride, a.k_stride, a.v_stride = q.stride(0), k.stride(0), v.stride(0)
+    a.q_norm, a.k_norm, a.v_norm = _p(q_norm), _p(k_norm), int(v_norm)
+    a.q_out, a.gate_out = q_out.data_ptr(), _p(gate_out)
+    a.kv_cache, a.block_table = kv_cache.data_ptr(), block_table.data_ptr()
+    a.slot, a.pos = slot.data_ptr(), pos.data_ptr()
+    a.max_pages = block_table.shape[1]
+    a.H, a.Hkv, a.D, a.page, a.gated = H, Hkv, D, page, int(gated)
+    a.rope_dim, a.theta, a.eps, a.q_scale = rope_dim, theta, eps, q_scale
+    N.check(N.lib().he_qkv_post(C.byref(a), C.c_int(T), _stream()), "he_qkv_post")
+
+
+def conv1d(x: torch.Tensor, w: torch.Tensor, state: torch.Tensor, seg_start: torch.Tensor, seg_slot: torch.Tensor,
+           tok_seg: torch.Tensor, out: torch.Tensor, channels: int, update_state: bool = True,
+           journal: Optional[torch.Tensor] = None) -> None:
+    _check_abi()
+    a = _ConvArgs()
+    a.x, a.in_dtype, a.x_stride = x.data_ptr(), _dt(x), x.stride(0)
+    a.w, a.state = w.data_ptr(), state.data_ptr()
+    a.seg_start, a.seg_slot, a.tok_seg = seg_start.data_ptr(), seg_slot.data_ptr(), tok_seg.data_ptr()
+    a.out, a.journal = out.data_ptr(), _p(journal)
+    a.C, a.KW, a.T, a.n_seg = channels, w.shape[1], x.shape[0], seg_slot.numel()
+    N.check(N.lib().he_conv1d(C.byref(a), C.c_int(int(update_state)), _stream()),
+            "he_conv1d+state" if update_state else "he_conv1d")
+
+
+def gdn_prepare(qkv: torch.Tensor, a_proj: torch.Tensor, b_proj: torch.Tensor, ssm_a: torch.Tensor,
+                dt_bias: torch.Tensor, decay: torch.Tensor, beta: torch.Tensor, G: int, Hv: int, S: int) -> None:
+    _check_abi()
+    p = _GdnPrepArgs()
+    p.qkv, p.a, p.b = qkv.data_ptr(), a_proj.data_ptr(), b_proj.data_ptr()
+    p.a_stride, p.b_stride = a_proj.stride(0), b_proj.stride(0)
+    p.ssm_a, p.dt_bias, p.decay, p.beta = ssm_a.data_ptr(), dt_bias.data_ptr(), decay.data_ptr(), beta.data_ptr()
+    p.C, p.G, p.Hv, p.S, p.T = qkv.shape[1], G, Hv, S, qkv.shape[0]
+    N.check(N.lib().he_gdn_prepare(C.byref(p), _stream()), "he_gdn_prepare")
+
+
+def gdn_scan(qkv: torch.Tensor, decay: torch.Tensor, beta: torch.Tensor, state: torch.Tensor,
+             seg_start: torch.Tensor, seg_slot: torch.Tensor, out: torch.Tensor, G: int, Hv: int,
+             write_state: bool = True, journal: Optional[torch.Tensor] = None) -> None:
+    _check_abi()
+    p = _GdnScanArgs()
+    p.qkv, p.decay, p.beta, p.state = qkv.data_ptr(), decay.data_ptr(), beta.data_ptr(), state.data_ptr()
+    p.seg_start, p.seg_slot, p.out, p.journal = seg_start.data_ptr(), seg_slot.data_ptr(), out.data_ptr(), _p(journal)
+    p.C, p.G, p.Hv, p.T, p.n_seg, p.write_state = qkv.shape[1], G, Hv, qkv.shape[0], seg_slot.numel(), int(write_state)
+    N.check(N.lib().he_gdn_scan(C.byref(p), _stream()), "he_gdn_scan")
+
+
+def gdn_gated_norm(o: torch.Tensor, z: torch.Tensor, w: torch.Tensor, out: torch.Tensor, Hv: int, Dv: int,
+                   eps: float) -> None:
+    T = o.shape[0]
+    N.check(N.lib().he_gdn_gated_norm(c_vp(o.data_ptr()), c_vp(z.data_ptr()), C.c_int(_dt(z)), c_ll(z.stride(0)),
+                                      c_vp(w.data_ptr()), c_vp(out.data_ptr()), c_ll(out.stride(0)), C.c_int(T),
+                                      C.c_int(Hv), C.c_int(Dv), C.c_float(eps), _stream()), "he_gdn_gated_norm")
+
+
+def state_commit(state: torch.Tensor, journal: torch.Tensor, seg_slot: torch.Tensor, commit_row: torch.Tensor,
+                 per_slot: int) -> None:
+    N.check(N.lib().he_state_commit(c_vp(state.data_ptr()), c_vp(journal.data_ptr()), c_vp(seg_slot.data_ptr()),
+                                    c_vp(commit_row.data_ptr()), C.c_int(seg_slot.numel()), c_ll(per_slot), _stream()),
+            "he_state_commit")
+
+
+# ----------------------------------------------------------------------------- attention
+
+def attn_decode_scratch_floats(R: int, H: int, max_splits: int, D: int) -> int:
+    return R * H * max_splits * (D + 2)
+
+
+def attn_decode(q: torch.Tensor, gate: Optional[torch.Tensor], kv_cache: torch.Tensor, block_table: torch.Tensor,
+                slot: torch.Tensor, ctx_len: torch.Tensor, partial: torch.Tensor, out: torch.Tensor, H: int, Hkv: int,
+                D: int, page: int, split_len: int, max_splits: int, scale: float, window: int = 0) -> None:
+    _check_abi()
+    a = _AttnDecArgs()
+    a.q, a.gate, a.kv_cache = q.data_ptr(), _p(gate), kv_cache.data_ptr()
+    a.block_table, a.slot, a.ctx_len = block_table.data_ptr(), slot.data_ptr(), ctx_len.data_ptr()
+    a.partial, a.out = partial.data_ptr(), out.data_ptr()
+    a.R, a.H, a.Hkv, a.D, a.page = q.shape[0], H, Hkv, D, page
+    a.max_pages = block_table.shape[1]
+    a.split_len, a.max_splits, a.window, a.scale = split_len, max_splits, window, scale
+    assert partial.numel() >= attn_decode_scratch_floats(a.R, H, max_splits, D)
+    N.check(N.lib().he_attn_decode(C.byref(a), _stream()), "he_attn_decode")
+
+
+# ----------------------------------------------------------------------------- sampling
+
+class SampleParams(C.Structure):
+    _fields_ = [("temperature", C.c_float), ("top_k", C.c_int), ("top_p", C.c_float), ("min_p", C.c_float),
+                ("seed", C.c_ulonglong), ("counter", C.c_ulonglong)]
+
+
+def argmax_rows(logits: torch.Tensor, scratch_v: torch.Tensor, scratch_i: torch.Tensor, out_ids: torch.Tensor,
+                out_val: Optional[torch.Tensor] = None) -> torch.Tensor:
+    R, V = logits.shape
+    N.check(N.lib().he_argmax_rows(c_vp(logits.data_ptr()), c_ll(logits.stride(0)), C.c_int(R), C.c_int(V),
+                                   c_vp(scratch_v.data_ptr()), c_vp(scratch_i.data_ptr()), c_vp(out_ids.data_ptr()),
+                                   c_vp(_p(out_val)), _stream()), "he_argmax_rows")
+    return out_ids
+
+
+def sample_rows(logits: torch.Tensor, params_dev: torch.Tensor, out_ids: torch.Tensor,
+                out_logprob: Optional[torch.Tensor] = None) -> torch.Tensor:
+    R, V = logits.shape
+    N.check(N.lib().he_sample_rows(c_vp(logits.data_ptr()), c_ll(logits.stride(0)), C.c_int(R), C.c_int(V),
+                                   c_vp(params_dev.data_ptr()), c_vp(out_ids.data_ptr()), c_vp(_p(out_logprob)),
+                                   _stream()), "he_sample_rows")
+    return out_ids
+
+
+def pack_sample_params(rows: Sequence[Tuple[float, int, float, float, int, int]], device) -> torch.Tensor:
+    arr = (SampleParams * len(rows))()
+    for i, (t, k, p, mp, seed, ctr) in enumerate(rows):
+        arr[i].temperature, arr[i].top_k, arr[i].top_p, arr[i].min_p = t, k, p, mp
+        arr[i].seed, arr[i].counter = seed & (2 ** 64 - 1), ctr & (2 ** 64 - 1)
+    host = torch.frombuffer(bytearray(bytes(arr)), dtype=torch.uint8)
+    return host.to(device)
+
+
+def topn_logprobs(logits: torch.Tensor, n: int, temperature: float, chosen: Optional[torch.Tensor]):
+    R, V = logits.shape
+    ids = torch.empty(R, max(n, 1), dtype=torch.int32, device=logits.device)
+    lps = torch.empty(R, max(n, 1), dtype=torch.float32, device=logits.device)
+    clp = torch.empty(R, dtype=torch.float32, device=logits.device)
+    N.check(N.lib().he_topn_logprobs(c_vp(logits.data_ptr()), c_ll(logits.stride(0)), C.c_int(R), C.c_int(V),
+                                     C.c_int(n), C.c_float(temperature), c_vp(_p(chosen)), c_vp(ids.data_ptr()),
+                                     c_vp(lps.data_ptr()), c_vp(clp.data_ptr()), _stream()), "he_topn_logprobs")
+    return ids[:, :n], lps[:, :n], clp
+
+
+def softcap_(x: torch.Tensor, cap: float) -> None:
+    N.check(N.lib().he_softcap(c_vp(x.data_ptr()), c_ll(x.numel()), C.c_float(cap), _stream()), "he_softcap")
+
+
+def small_gemm_f32(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[T, N] (fp32) = x[T, K] @ w[N, K]^T with fp32 weights (router / ssm_alpha / ssm_beta at prefill)."""
+    T, K = x.shape
+    Nn = w.shape[0]
+    assert w.dtype == torch.float32 and out.dtype == torch.float32
+    N.check(N.lib().he_small_gemm_f32(c_vp(x.data_ptr()), C.c_int(_dt(x)), c_ll(x.stride(0)), c_vp(w.data_ptr()),
+                                      c_vp(out.data_ptr()), c_ll(out.stride(0)), C.c_int(T), C.c_int(Nn), C.c_int(K),
+                                      _stream()), "he_small_gemm_f32")
+    return out
