@@ -1,0 +1,253 @@
+// Tensor-core GEMM for sm_100a: C[M][N] = A[M][K] * B[N][K]^T with bf16 operands and fp32 accumulation in
+// tensor memory (TMEM).  Persistent, warp-specialised:
+//   warp 0     : TMA producer  (cp.async.bulk.tensor, 128-byte swizzled K-major tiles, 4-stage ring)
+//   warp 1     : MMA issuer    (one elected thread issues tcgen05.mma 128x256x16; owns the TMEM allocation)
+//   warps 2..5 : epilogue      (tcgen05.ld 32 lanes x 32 columns -> bf16/fp32 -> global; optional fused
+//                               residual add or act(gate)*up)
+// Two 256-column accumulators (all 512 TMEM columns) alternate between tiles so the epilogue of tile i
+// overlaps the main loop of tile i+1.  Tiles are walked M-fastest so CTAs running at the same time share
+// the weight tile in L2.  This is the projection engine for prefill / verify / wide decode
+// (roles of hipengine/kernels/hip_gfx1100/quant/gguf_q4_k_prefill.hip and gguf_q8_0_prefill.hip in the
+// reference, which use 16x16x16 WMMA with one wave per block).
+#include "common.cuh"
+#include "sm100.cuh"
+
+using namespace sm100;
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64, UK = 16;
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;   // 16 KB
+constexpr int B_BYTES = BN * BK * 2;   // 32 KB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int ACC_COLS = BN;           // fp32 columns per accumulator
+constexpr int TMEM_COLS = 512;
+constexpr int NTHREADS = 192;
+
+struct GemmArgs {
+  void* C;
+  long long ldc;        // elements
+  const float* resid;   // unused (reserved)
+  int M, N, K;
+  int epi;              // 0: bf16 store, 1: fp32 store, 2: fp32 += (C is fp32, in place)
+  int* status;
+};
+
+struct __align__(8) Barriers {
+  uint64_t full[STAGES];
+  uint64_t empty[STAGES];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__global__ void __launch_bounds__(NTHREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmArgs g) {
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment for the swizzled tiles
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  Barriers* bar = reinterpret_cast<Barriers*>(smem + STAGES * STAGE_BYTES);
+  volatile int* abort_flag = &bar->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (g.M + BM - 1) / BM, tiles_n = (g.N + BN - 1) / BN;
+  const int n_tiles = tiles_m * tiles_n;
+  const int k_blocks = (g.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&bar->full[s], 1);
+      mbar_init(&bar->empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&bar->acc_full[a], 1);
+      mbar_init(&bar->acc_empty[a], 4);   // one arrive per epilogue warp
+    }
+    bar->abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bar->tmem_base, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bar->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      uint32_t it = 0;
+      for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+        const int tm = tile % tiles_m, tn = tile / tiles_m;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&bar->empty[s], ph ^ 1, abort_flag, g.status, 101)) break;
+          mbar_expect_tx(&bar->full[s], STAGE_BYTES);
+          uint8_t* sa = smem + s * STAGE_BYTES;
+          tma_load_2d(sa, &tmA, &bar->full[s], kb * BK, tm * BM);
+          tma_load_2d(sa + A_BYTES, &tmB, &bar->full[s], kb * BK, tn * BN);
+        }
+        if (*abort_flag) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
+      uint32_t it = 0, tcount = 0;
+      for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tcount) {
+        const int acc = tcount & 1;
+        const uint32_t acc_ph = (tcount >> 1) & 1;
+        if (!mbar_wait(&bar->acc_empty[acc], acc_ph ^ 1, abort_flag, g.status, 102)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * ACC_COLS;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&bar->full[s], ph, abort_flag, g.status, 103)) break;
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
+          const uint32_t b_addr = a_addr + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UK; ++k) {
+            const uint64_t da = umma_desc_k_sw128(a_addr + k * UK * 2);
+            const uint64_t db = umma_desc_k_sw128(b_addr + k * UK * 2);
+            umma_f16(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&bar->empty[s]);   // frees the smem stage once these MMAs have read it
+        }
+        if (*abort_flag) break;
+        umma_commit(&bar->acc_full[acc]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;              // TMEM lane quarter this warp may touch
+    uint32_t tcount = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tcount) {
+      const int tm = tile % tiles_m, tn = tile / tiles_m;
+      const int acc = tcount & 1;
+      const uint32_t acc_ph = (tcount >> 1) & 1;
+      if (!mbar_wait(&bar->acc_full[acc], acc_ph, abort_flag, g.status, 104)) break;
+      tc_fence_after();
+      const int row = tm * BM + q * 32 + lane;
+      const uint32_t t_row = tmem_base + acc * ACC_COLS + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = tn * BN + c * 32;
+        if (row < g.M && col0 < g.N) {
+          const int ncols = min(32, g.N - col0);
+          if (g.epi == 0) {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(g.C) + (size_t)row * g.ldc + col0;
+            if (ncols == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                uint4 pk;
+                uint32_t* pw = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * e]),
+                                                           __uint_as_float(r[v * 8 + 2 * e + 1]));
+                  pw[e] = *reinterpret_cast<uint32_t*>(&h);
+                }
+                *reinterpret_cast<uint4*>(dst + v * 8) = pk;
+              }
+            } else {
+              for (int e = 0; e < ncols; ++e) dst[e] = __float2bfloat16_rn(__uint_as_float(r[e]));
+            }
+          } else {
+            float* dst = reinterpret_cast<float*>(g.C) + (size_t)row * g.ldc + col0;
+            if (g.epi == 1) {
+              for (int e = 0; e < ncols; ++e) dst[e] = __uint_as_float(r[e]);
+            } else {
+              for (int e = 0; e < ncols; ++e) dst[e] += __uint_as_float(r[e]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar->acc_empty[acc]);
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------- host side: tensor maps
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// 2-D bf16 row-major [rows][cols] with row stride `ld` elements; box = {BK cols, box_rows rows}; 128B swizzle.
+int make_map(CUtensorMap* m, const void* ptr, long long rows, long long cols, long long ld, int box_rows) {
+  EncodeTiledFn enc = get_encode();
+  if (enc == nullptr) return -HE_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0 || (ld * 2) % 16 != 0) return -HE_ERR_BAD_ARG;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
+}
+
+}  // namespace
+
+// C[M][N] = A[M][K] (bf16, row stride lda) * B[N][K]^T (bf16, row stride ldb).
+// epi: 0 bf16 store, 1 fp32 store, 2 fp32 accumulate into C.  `status` (device int, may be null) receives a
+// non-zero code if a bounded wait inside the kernel gave up.
+HE_API int he_gemm_bf16(const void* A, long long lda, const void* B, long long ldb, void* C, long long ldc, int M,
+                        int N, int K, int epi, void* status, int num_sms, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (K % 8 != 0) return -HE_ERR_BAD_ARG;
+  CUtensorMap tmA, tmB;
+  int rc = make_map(&tmA, A, M, K, lda, BM);
+  if (rc != 0) return rc;
+  rc = make_map(&tmB, B, N, K, ldb, BN);
+  if (rc != 0) return rc;
+  GemmArgs g;
+  g.C = C; g.ldc = ldc; g.resid = nullptr; g.M = M; g.N = N; g.K = K; g.epi = epi; g.status = (int*)status;
+  const size_t smem = STAGES * STAGE_BYTES + sizeof(Barriers) + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int grid = tiles < num_sms ? tiles : num_sms;
+  gemm_bf16_kernel<<<grid, NTHREADS, smem, stream>>>(tmA, tmB, g);
+  HE_LAUNCH_CHECK();
+  return 0;
+}

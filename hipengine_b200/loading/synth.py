@@ -77,6 +77,9 @@ class _Builder:
     def randn(self, *shape, std=1.0) -> torch.Tensor:
         return torch.randn(*shape, generator=self.gen, device=self.device, dtype=torch.float32) * std
 
+    def ones(self, *shape) -> torch.Tensor:
+        return torch.ones(*shape, device=self.device, dtype=torch.float32)
+
     def rand(self, *shape) -> torch.Tensor:
         return torch.rand(*shape, generator=self.gen, device=self.device, dtype=torch.float32)
 
@@ -91,7 +94,7 @@ def build_random_model(cfg: ModelConfig, seed: int = 0, device="cpu", recipe: st
     base, hi = b.base_type(), b.hi_type()
     H = cfg.hidden
     b.matrix("token_embd.weight", (cfg.vocab, H), base)
-    b.f32("output_norm.weight", torch.ones(H))
+    b.f32("output_norm.weight", b.ones(H))
     if not cfg.tie_embeddings:
         b.matrix("output.weight", (cfg.vocab, H), hi)
     n_blocks = cfg.n_layers + cfg.nextn_layers
@@ -100,16 +103,16 @@ def build_random_model(cfg: ModelConfig, seed: int = 0, device="cpu", recipe: st
         full = True if is_nextn else cfg.is_full_attention_layer(i)
         more = use_more_bits(min(i, cfg.n_layers - 1), cfg.n_layers)
         p = f"blk.{i}."
-        b.f32(p + "attn_norm.weight", torch.ones(H) + b.randn(H, std=0.02))
-        b.f32(p + ffn_norm_slot(cfg), torch.ones(H) + b.randn(H, std=0.02))
+        b.f32(p + "attn_norm.weight", b.ones(H) + b.randn(H, std=0.02))
+        b.f32(p + ffn_norm_slot(cfg), b.ones(H) + b.randn(H, std=0.02))
         if full:
             b.matrix(p + "attn_q.weight", (cfg.q_proj_width, H), base)
             b.matrix(p + "attn_k.weight", (cfg.kv_width, H), base)
             b.matrix(p + "attn_v.weight", (cfg.kv_width, H), hi if more else base)
             b.matrix(p + "attn_output.weight", (H, cfg.q_width), base)
             if cfg.qk_norm:
-                b.f32(p + "attn_q_norm.weight", torch.ones(cfg.head_dim) + b.randn(cfg.head_dim, std=0.02))
-                b.f32(p + "attn_k_norm.weight", torch.ones(cfg.head_dim) + b.randn(cfg.head_dim, std=0.02))
+                b.f32(p + "attn_q_norm.weight", b.ones(cfg.head_dim) + b.randn(cfg.head_dim, std=0.02))
+                b.f32(p + "attn_k_norm.weight", b.ones(cfg.head_dim) + b.randn(cfg.head_dim, std=0.02))
         else:
             Hv, inner, C = cfg.ssm_v_heads, cfg.ssm_inner, cfg.linear_qkv_width
             b.matrix(p + "attn_qkv.weight", (C, H), base)
@@ -119,7 +122,7 @@ def build_random_model(cfg: ModelConfig, seed: int = 0, device="cpu", recipe: st
             b.f32(p + "ssm_beta.weight", b.randn(Hv, H, std=std))
             b.f32(p + "ssm_conv1d.weight", b.randn(C, cfg.conv_kernel, std=0.5))
             b.f32(p + "ssm_dt.bias", b.randn(Hv, std=0.5))
-            b.f32(p + "ssm_norm.weight", torch.ones(cfg.ssm_state) + b.randn(cfg.ssm_state, std=0.02))
+            b.f32(p + "ssm_norm.weight", b.ones(cfg.ssm_state) + b.randn(cfg.ssm_state, std=0.02))
             b.matrix(p + "ssm_out.weight", (H, inner), base)
         if cfg.is_moe:
             E, F = cfg.n_experts, cfg.expert_ffn
@@ -139,8 +142,8 @@ def build_random_model(cfg: ModelConfig, seed: int = 0, device="cpu", recipe: st
             b.matrix(p + "ffn_down.weight", (H, cfg.ffn), hi if more else base)
         if is_nextn:
             b.matrix(p + "nextn.eh_proj.weight", (H, 2 * H), GGMLType.Q8_0 if recipe != "f16" else base)
-            b.f32(p + "nextn.enorm.weight", torch.ones(H))
-            b.f32(p + "nextn.hnorm.weight", torch.ones(H))
+            b.f32(p + "nextn.enorm.weight", b.ones(H))
+            b.f32(p + "nextn.hnorm.weight", b.ones(H))
     meta = config_to_metadata(cfg)
     meta["general.name"] = f"random-init {cfg.arch} seed={seed} recipe={recipe}"
     return ModelWeights(cfg, b.out, meta)

@@ -1,0 +1,59 @@
+"""tcgen05 / TMEM GEMM launchers (``csrc/gemm_sm100.cu``).
+
+``gemm_bf16`` multiplies bf16 activations by a bf16 weight; ``gemm_quant`` multiplies by a weight kept in
+its GGUF-derived device layout (Q4_K / Q6_K / Q8_0 / float).  Kernels report a failed bounded wait through
+a device status word; ``check_status`` reads it (a sync) and raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from ..core import native as N
+from .kernels import DeviceWeight, _stream, dequant_bf16
+
+_STATUS = {}
+
+
+def status_word(device) -> torch.Tensor:
+    key = torch.device(device).index or 0
+    if key not in _STATUS:
+        _STATUS[key] = torch.zeros(4, dtype=torch.int32, device=device)
+    return _STATUS[key]
+
+
+def check_status(device="cuda") -> None:
+    st = status_word(device)
+    v = int(st[0].item())
+    if v != 0:
+        st.zero_()
+        raise RuntimeError(f"sm_100a GEMM kernel reported status {v} (a bounded wait gave up)")
+
+
+def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: Optional[int] = None) -> torch.Tensor:
+    """out[M, N] = x[M, K] @ w[N, K]^T.  x, w bf16 (row strides allowed); out bf16 or fp32."""
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    M, K = x.shape
+    Nn = w.shape[0]
+    assert w.shape[1] == K and x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    if epi is None:
+        epi = 0 if out.dtype == torch.bfloat16 else 1
+    st = status_word(x.device)
+    N.check(N.lib().he_gemm_bf16(C.c_void_p(x.data_ptr()), C.c_longlong(x.stride(0)), C.c_void_p(w.data_ptr()),
+                                 C.c_longlong(w.stride(0)), C.c_void_p(out.data_ptr()), C.c_longlong(out.stride(0)),
+                                 C.c_int(M), C.c_int(Nn), C.c_int(K), C.c_int(epi), C.c_void_p(st.data_ptr()),
+                                 C.c_int(N.num_sms()), _stream()), "he_gemm_bf16")
+    return out
+
+
+def gemm_quant(x: torch.Tensor, w: DeviceWeight, out: torch.Tensor, scratch, row0: int = 0,
+               rows: Optional[int] = None, epi: Optional[int] = None) -> torch.Tensor:
+    """out[M, rows] = x[M, K] @ W[row0:row0+rows]^T for a quantized device-layout weight."""
+    rows = w.n_rows - row0 if rows is None else rows
+    if w.qtype == 30 and row0 == 0 and rows == w.n_rows:   # already bf16
+        return gemm_bf16(x, w.data.view(torch.bfloat16).reshape(w.n_rows, w.n_cols), out, epi)
+    wb = scratch.get("gemm_deq", (rows, w.n_cols), torch.bfloat16)
+    dequant_bf16(w, wb, row0=row0, rows=rows)
+    return gemm_bf16(x, wb, out, epi)
