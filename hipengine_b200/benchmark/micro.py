@@ -1,0 +1,131 @@
+"""Per-kernel micro-benchmarks with roofline fractions.
+
+    python -m hipengine_b200.benchmark.micro gemm --m 4096 --n 17408 --k 5120
+    python -m hipengine_b200.benchmark.micro gemv --n 17408 --k 5120 --qtype q4_k --rows 1
+    python -m hipengine_b200.benchmark.micro all
+
+Timing: CUDA events on the launching stream, >= 3 warm-up launches, inputs rotated through a pool larger
+than L2 (126 MB) so every timed launch reads its operands from HBM.  Fractions are "of measured": the
+denominators come from MEASURED_PEAKS.json at the repository root when present (copy bandwidth and cuBLAS
+bf16 throughput measured on this pool), else the stated fallback.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parents[2]
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "src": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "src": "fallback"}
+
+
+def time_launches(fn, n_variants: int, iters: int = 5, warmup: int = 3) -> float:
+    """Median milliseconds per launch of fn(i).
+
+    The n_variants launches (each touching different operands, together larger than L2) are captured into
+    one CUDA graph and the graph is replayed, so the figure is device time per launch with no host launch
+    overhead between kernels.
+    """
+    for i in range(max(warmup, 1)):
+        fn(i % n_variants)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(n_variants):
+            fn(i)
+    for _ in range(warmup):
+        g.replay()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        e1.synchronize()
+        ts.append(e0.elapsed_time(e1) / n_variants)
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def bench_gemm(M, N, K, impl="tcgen05"):
+    from hipengine_b200.ops import gemm as G
+    pk = peaks()
+    nvar = max(2, int(200e6 // (N * K * 2)) + 1)
+    ws = [(torch.randn(N, K, device="cuda") * 0.05).bfloat16() for _ in range(nvar)]
+    x = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    if impl == "tcgen05":
+        fn = lambda i: G.gemm_bf16(x, ws[i], out)
+    else:
+        fn = lambda i: torch.matmul(x, ws[i].t(), out=out)
+    ms = time_launches(fn, nvar)
+    if impl == "tcgen05":
+        G.check_status()
+    tf = 2.0 * M * N * K / ms / 1e9
+    return {"kernel": f"gemm_bf16[{impl}]", "M": M, "N": N, "K": K, "ms": round(ms, 4), "tflops": round(tf, 1),
+            f"frac_of_{pk['src']}_bf16": round(tf / pk["bf16_tflops"], 3)}
+
+
+def bench_gemv(N, K, qtype="q4_k", rows=1):
+    from hipengine_b200.ops import kernels as Kn
+    from hipengine_b200.quant import ggml as Q
+    pk = peaks()
+    t = {"q4_k": Q.GGMLType.Q4_K, "q6_k": Q.GGMLType.Q6_K, "q8_0": Q.GGMLType.Q8_0}[qtype]
+    wbytes = N * Q.row_bytes(t, K)
+    nvar = max(2, int(260e6 // wbytes) + 1)
+    dws = []
+    for i in range(nvar):
+        w = torch.randn(N, K, device="cuda") * 0.02
+        dws.append(Kn.to_device_weight(Q.quantize(w, t), t, N, K))
+    x = torch.randn(rows, K, device="cuda")
+    nw = torch.ones(K, device="cuda")
+    out = torch.empty(rows, N, device="cuda")
+    fn = lambda i: Kn.gemv(x, [Kn.GemvSegment(dws[i], out)], norm_w=nw)
+    ms = time_launches(fn, nvar)
+    gbs = wbytes / ms / 1e6
+    return {"kernel": f"gemv[{qtype}]", "N": N, "K": K, "rows": rows, "ms": round(ms, 4), "GBps": round(gbs, 1),
+            f"frac_of_{pk['src']}_hbm": round(gbs / pk["hbm_gbs"], 3)}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["gemm", "gemv", "all"])
+    ap.add_argument("--m", type=int, default=4096)
+    ap.add_argument("--n", type=int, default=17408)
+    ap.add_argument("--k", type=int, default=5120)
+    ap.add_argument("--rows", type=int, default=1)
+    ap.add_argument("--qtype", default="q4_k")
+    ap.add_argument("--impl", default="tcgen05")
+    a = ap.parse_args()
+    out = []
+    if a.what == "gemm":
+        out.append(bench_gemm(a.m, a.n, a.k, a.impl))
+    elif a.what == "gemv":
+        out.append(bench_gemv(a.n, a.k, a.qtype, a.rows))
+    else:
+        for (m, n, k) in [(4096, 10240, 5120), (4096, 34816, 5120), (4096, 5120, 17408), (4096, 5120, 6144)]:
+            out.append(bench_gemm(m, n, k, "tcgen05"))
+            out.append(bench_gemm(m, n, k, "cublas"))
+        for (n, k, q) in [(34816, 5120, "q4_k"), (5120, 17408, "q4_k"), (5120, 17408, "q6_k"), (16384, 5120, "q4_k"),
+                          (5120, 6144, "q4_k"), (62080, 5120, "q6_k"), (8192, 5120, "q8_0")]:
+            for r in (1, 4):
+                out.append(bench_gemv(n, k, q, r))
+    for o in out:
+        print(json.dumps(o))
+
+
+if __name__ == "__main__":
+    sys.path.insert(0, str(ROOT))
+    main()

@@ -14,22 +14,7 @@ import torch
 from ..core import native as N
 from .kernels import DeviceWeight, _stream, dequant_bf16
 
-_STATUS = {}
-
-
-def status_word(device) -> torch.Tensor:
-    key = torch.device(device).index or 0
-    if key not in _STATUS:
-        _STATUS[key] = torch.zeros(4, dtype=torch.int32, device=device)
-    return _STATUS[key]
-
-
-def check_status(device="cuda") -> None:
-    st = status_word(device)
-    v = int(st[0].item())
-    if v != 0:
-        st.zero_()
-        raise RuntimeError(f"sm_100a GEMM kernel reported status {v} (a bounded wait gave up)")
+from .kernels import check_status, status_tensor as status_word  # noqa: E402,F401
 
 
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: Optional[int] = None) -> torch.Tensor:

@@ -28,7 +28,8 @@ class _GemvSeg(C.Structure):
 
 class _GemvArgs(C.Structure):
     _fields_ = [("seg", _GemvSeg * 4), ("n_seg", C.c_int), ("K", C.c_int), ("R", C.c_int), ("x_dtype", C.c_int),
-                ("x", c_vp), ("x_stride", c_ll), ("norm_w", c_vp), ("eps", C.c_float), ("need_xf", C.c_int)]
+                ("x", c_vp), ("x_stride", c_ll), ("norm_w", c_vp), ("eps", C.c_float), ("n_slots", C.c_int),
+                ("rg", C.c_int), ("slot_bytes", C.c_int), ("status", c_vp)]
 
 
 class _QkvArgs(C.Structure):
@@ -130,6 +131,12 @@ class DeviceWeight:
 _KERNEL_QTYPES = (GGMLType.Q4_K, GGMLType.Q6_K, GGMLType.Q8_0, GGMLType.F32, GGMLType.F16, GGMLType.BF16)
 
 
+def device_row_bytes(qtype: int, n_cols: int) -> int:
+    L = N.lib()
+    L.he_device_row_bytes.restype = C.c_longlong
+    return int(L.he_device_row_bytes(C.c_int(int(qtype)), C.c_int(n_cols)))
+
+
 def to_device_weight(raw: torch.Tensor, qtype: int, n_rows: int, n_cols: int) -> DeviceWeight:
     """Repack GGUF bytes (uint8 [rows, row_bytes], already on the device) into the kernel layout."""
     qtype = GGMLType(qtype)
@@ -141,29 +148,22 @@ def to_device_weight(raw: torch.Tensor, qtype: int, n_rows: int, n_cols: int) ->
     raw = raw.contiguous()
     if qtype in (GGMLType.Q6_K, GGMLType.Q8_0):
         _check_abi()
-        out = torch.empty(raw.numel(), dtype=torch.uint8, device=raw.device)
+        out = torch.empty(n_rows * device_row_bytes(qtype, n_cols), dtype=torch.uint8, device=raw.device)
         N.check(N.lib().he_repack(c_vp(raw.data_ptr()), c_vp(out.data_ptr()), C.c_int(int(qtype)),
-                                  c_ll(n_rows), c_ll(n_cols), _stream()), "he_repack")
+                                  c_ll(n_rows), c_ll(n_cols), C.c_int(0), _stream()), "he_repack")
         return DeviceWeight(int(qtype), n_rows, n_cols, out)
     return DeviceWeight(int(qtype), n_rows, n_cols, raw)
 
 
 def unpack_device_weight(dw: DeviceWeight) -> torch.Tensor:
-    """Inverse of ``to_device_weight`` for the planar layouts (lossless; used by round-trip tests)."""
+    """Inverse of ``to_device_weight``: the exact GGUF bytes (lossless; used by round-trip tests)."""
     t = GGMLType(dw.qtype)
-    d = dw.data.reshape(-1)
-    if t == GGMLType.Q6_K:
-        nblk = dw.n_rows * dw.n_cols // 256
-        ql = d[:nblk * 128].reshape(nblk, 128)
-        qh = d[nblk * 128:nblk * 192].reshape(nblk, 64)
-        sc = d[nblk * 192:nblk * 208].reshape(nblk, 16)
-        dd = d[nblk * 208:nblk * 210].reshape(nblk, 2)
-        return torch.cat([ql, qh, sc, dd], dim=1).reshape(dw.n_rows, -1)
-    if t == GGMLType.Q8_0:
-        nblk = dw.n_rows * dw.n_cols // 32
-        qs = d[:nblk * 32].reshape(nblk, 32)
-        dd = d[nblk * 32:nblk * 34].reshape(nblk, 2)
-        return torch.cat([dd, qs], dim=1).reshape(dw.n_rows, -1)
+    if t in (GGMLType.Q6_K, GGMLType.Q8_0):
+        from ..quant.ggml import row_bytes
+        out = torch.empty(dw.n_rows * row_bytes(t, dw.n_cols), dtype=torch.uint8, device=dw.data.device)
+        N.check(N.lib().he_repack(c_vp(dw.ptr), c_vp(out.data_ptr()), C.c_int(int(t)), c_ll(dw.n_rows),
+                                  c_ll(dw.n_cols), C.c_int(1), _stream()), "he_repack")
+        return out.reshape(dw.n_rows, -1)
     return dw.data.reshape(dw.n_rows, -1)
 
 
@@ -183,7 +183,6 @@ def gemv(x: torch.Tensor, segs: Sequence[GemvSegment], norm_w: Optional[torch.Te
     _check_abi()
     R, K = x.shape
     a = _GemvArgs()
-    need_xf = 0
     for i, s in enumerate(segs):
         sg = a.seg[i]
         sg.w = s.w.ptr
@@ -195,8 +194,6 @@ def gemv(x: torch.Tensor, segs: Sequence[GemvSegment], norm_w: Optional[torch.Te
         sg.qtype2 = s.w2.qtype if s.w2 is not None else 0
         sg.epi = s.epi
         assert s.w.n_cols == K, (s.w.n_cols, K)
-        if s.w.qtype in (0, 1, 30) or (s.w2 is not None and s.w2.qtype in (0, 1, 30)):
-            need_xf = 1
     a.n_seg = len(segs)
     a.K = K
     a.R = R
@@ -205,8 +202,39 @@ def gemv(x: torch.Tensor, segs: Sequence[GemvSegment], norm_w: Optional[torch.Te
     a.x_stride = x.stride(0)
     a.norm_w = _p(norm_w)
     a.eps = eps
-    a.need_xf = need_xf
-    N.check(N.lib().he_gemv(C.byref(a), C.c_int(N.num_sms()), _stream()), "he_gemv")
+    a.status = _status_ptr(x.device)
+    rc = N.lib().he_gemv(C.byref(a), C.c_int(N.num_sms()), _stream())
+    if rc == -3 and R > 1:
+        # activation rows + staging rings do not fit shared memory: run the rows in two halves
+        h = R // 2
+        gemv(x[:h], [GemvSegment(s.w, s.out[:h], s.epi, s.w2) for s in segs], norm_w, eps)
+        gemv(x[h:], [GemvSegment(s.w, s.out[h:], s.epi, s.w2) for s in segs], norm_w, eps)
+        return
+    N.check(rc, "he_gemv")
+
+
+_STATUS_WORDS = {}
+
+
+def status_tensor(device) -> torch.Tensor:
+    """Per-device int32[4] status word that kernels with bounded waits write on failure."""
+    key = torch.device(device).index or 0
+    if key not in _STATUS_WORDS:
+        _STATUS_WORDS[key] = torch.zeros(4, dtype=torch.int32, device=device)
+    return _STATUS_WORDS[key]
+
+
+def _status_ptr(device) -> int:
+    return status_tensor(device).data_ptr()
+
+
+def check_status(device="cuda") -> None:
+    """Read the status word (synchronises) and raise if any bounded wait gave up."""
+    st = status_tensor(device)
+    v = int(st[0].item())
+    if v != 0:
+        st.zero_()
+        raise RuntimeError(f"sm_100a kernel reported status {v} (a bounded wait gave up)")
 
 
 def dequant_bf16(w: DeviceWeight, out: Optional[torch.Tensor] = None, row0: int = 0,

@@ -42,7 +42,7 @@ def test_decode_path_matches_reference(cfg):
     kl, top1, ref_logits, got = _compare(cfg, 4, 6)
     assert torch.isfinite(got).all()
     rel = ((got - ref_logits).abs().max() / ref_logits.std()).item()
-    assert kl.max() < 0.05 and top1 >= 0.8 and rel < 0.25, (kl.max().item(), top1, rel)
+    assert kl.max() < 0.05 and top1 >= 0.8 and rel < 0.4, (kl.max().item(), top1, rel)
 
 
 @pytest.mark.parametrize("cfg", [TINY_DENSE, TINY_HYBRID], ids=["dense", "hybrid"])
@@ -50,7 +50,7 @@ def test_prefill_path_matches_reference(cfg):
     kl, top1, ref_logits, got = _compare(cfg, 40, 3)
     assert torch.isfinite(got).all()
     rel = ((got - ref_logits).abs().max() / ref_logits.std()).item()
-    assert kl.max() < 0.05 and top1 >= 0.8 and rel < 0.25, (kl.max().item(), top1, rel)
+    assert kl.max() < 0.05 and top1 >= 0.8 and rel < 0.4, (kl.max().item(), top1, rel)
 
 
 def test_two_slots_are_isolated():
