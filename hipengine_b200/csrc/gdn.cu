@@ -66,22 +66,25 @@ constexpr int DV = 128;       // state cols (value dim)
 constexpr int SLICE = 32;     // columns per CTA
 constexpr int TCH = 16;       // tokens staged per shared-memory chunk
 
-// grid (n_seg, Hv, DV/SLICE), block 128
+constexpr int KPAD = DK + DK / 8;   // 4 pad floats per 32 so the 4 row groups of a column land in different banks
+
+// grid (n_seg, Hv, DV/SLICE), block 128.  Lane (col = lane/4, ks = lane%4) owns rows ks*32 .. ks*32+31 of one column.
 __global__ void __launch_bounds__(128) gdn_scan_kernel(const GdnScanArgs p) {
-  __shared__ float sq[TCH][DK];
-  __shared__ float sk[TCH][DK];
+  __shared__ __align__(16) float sq[TCH][KPAD];
+  __shared__ __align__(16) float sk[TCH][KPAD];
   __shared__ float sv[TCH][SLICE];
   __shared__ float sdec[TCH], sbeta[TCH];
   const int sg = blockIdx.x, h = blockIdx.y, sl = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int col = sl * SLICE + warp * 8 + (lane >> 2);  // column of S owned (with 3 other lanes)
-  const int ks = lane & 3;                              // rows ks + 4*i
+  const int cw = warp * 8 + (lane >> 2);                // column inside the slice
+  const int col = sl * SLICE + cw;                      // column of S owned (with 3 other lanes)
+  const int ks = lane & 3;
   const int kh = h % p.G;
   const int s0 = p.seg_start[sg], s1 = p.seg_start[sg + 1];
   float* Sg = p.state + (((size_t)p.seg_slot[sg] * p.Hv + h) * DK) * DV;
   float S[32];
 #pragma unroll
-  for (int i = 0; i < 32; ++i) S[i] = Sg[(size_t)(ks + 4 * i) * DV + col];
+  for (int i = 0; i < 32; ++i) S[i] = Sg[(size_t)(ks * 32 + i) * DV + col];
 
   const size_t q_off = (size_t)kh * DK, k_off = (size_t)p.G * DK + (size_t)kh * DK;
   const size_t v_off = (size_t)2 * p.G * DK + (size_t)h * DV + sl * SLICE;
@@ -89,11 +92,12 @@ __global__ void __launch_bounds__(128) gdn_scan_kernel(const GdnScanArgs p) {
   for (int c0 = s0; c0 < s1; c0 += TCH) {
     const int n = min(TCH, s1 - c0);
     __syncthreads();
-    for (int i = tid; i < n * DK; i += 128) {
-      const int tt = i / DK, d = i % DK;
+    for (int i = tid; i < n * (DK / 4); i += 128) {
+      const int tt = i / (DK / 4), d4 = (i % (DK / 4)) * 4;
       const float* row = p.qkv + (size_t)(c0 + tt) * p.C;
-      sq[tt][d] = row[q_off + d];
-      sk[tt][d] = row[k_off + d];
+      const int dst = d4 + (d4 >> 5) * 4;
+      *reinterpret_cast<float4*>(&sq[tt][dst]) = *reinterpret_cast<const float4*>(row + q_off + d4);
+      *reinterpret_cast<float4*>(&sk[tt][dst]) = *reinterpret_cast<const float4*>(row + k_off + d4);
     }
     for (int i = tid; i < n * SLICE; i += 128) {
       const int tt = i / SLICE, d = i % SLICE;
@@ -106,20 +110,29 @@ __global__ void __launch_bounds__(128) gdn_scan_kernel(const GdnScanArgs p) {
     __syncthreads();
     for (int tt = 0; tt < n; ++tt) {
       const float dec = sdec[tt], bet = sbeta[tt];
+      float kr[32];
+#pragma unroll
+      for (int i4 = 0; i4 < 8; ++i4) {
+        const float4 kv4 = *reinterpret_cast<const float4*>(&sk[tt][ks * 36 + i4 * 4]);
+        kr[i4 * 4] = kv4.x; kr[i4 * 4 + 1] = kv4.y; kr[i4 * 4 + 2] = kv4.z; kr[i4 * 4 + 3] = kv4.w;
+      }
       float kv = 0.f;
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
         S[i] *= dec;
-        kv += sk[tt][ks + 4 * i] * S[i];
+        kv += kr[i] * S[i];
       }
       kv += __shfl_xor_sync(0xffffffffu, kv, 1);
       kv += __shfl_xor_sync(0xffffffffu, kv, 2);
-      const float delta = (sv[tt][warp * 8 + (lane >> 2)] - kv) * bet;
+      const float delta = (sv[tt][cw] - kv) * bet;
       float o = 0.f;
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        S[i] += sk[tt][ks + 4 * i] * delta;
-        o += sq[tt][ks + 4 * i] * S[i];
+      for (int i4 = 0; i4 < 8; ++i4) {
+        const float4 q4 = *reinterpret_cast<const float4*>(&sq[tt][ks * 36 + i4 * 4]);
+        S[i4 * 4] += kr[i4 * 4] * delta;         o += q4.x * S[i4 * 4];
+        S[i4 * 4 + 1] += kr[i4 * 4 + 1] * delta; o += q4.y * S[i4 * 4 + 1];
+        S[i4 * 4 + 2] += kr[i4 * 4 + 2] * delta; o += q4.z * S[i4 * 4 + 2];
+        S[i4 * 4 + 3] += kr[i4 * 4 + 3] * delta; o += q4.w * S[i4 * 4 + 3];
       }
       o += __shfl_xor_sync(0xffffffffu, o, 1);
       o += __shfl_xor_sync(0xffffffffu, o, 2);
@@ -127,13 +140,13 @@ __global__ void __launch_bounds__(128) gdn_scan_kernel(const GdnScanArgs p) {
       if (p.journal != nullptr) {
         float* J = p.journal + (((size_t)(c0 + tt) * p.Hv + h) * DK) * DV;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) J[(size_t)(ks + 4 * i) * DV + col] = S[i];
+        for (int i = 0; i < 32; ++i) J[(size_t)(ks * 32 + i) * DV + col] = S[i];
       }
     }
   }
   if (p.write_state) {
 #pragma unroll
-    for (int i = 0; i < 32; ++i) Sg[(size_t)(ks + 4 * i) * DV + col] = S[i];
+    for (int i = 0; i < 32; ++i) Sg[(size_t)(ks * 32 + i) * DV + col] = S[i];
   }
 }
 

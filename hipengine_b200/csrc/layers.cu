@@ -171,28 +171,53 @@ struct ConvArgs {
   int C, KW, T, n_seg;
 };
 
+// one thread per (token, 8 channels)
 __global__ void conv_fwd_kernel(const ConvArgs a) {
+  const int C8 = a.C >> 3;
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= (long long)a.T * a.C) return;
-  const int t = (int)(i / a.C), c = (int)(i % a.C);
+  if (i >= (long long)a.T * C8) return;
+  const int t = (int)(i / C8), c = (int)(i % C8) * 8;
   const int sg = a.tok_seg[t];
   const int s0 = a.seg_start[sg];
   const int local = t - s0;
   const int KW = a.KW;
   const float* st = a.state + ((size_t)a.seg_slot[sg] * a.C + c) * (KW - 1);
-  float acc = 0.f;
-  float win[4];
-#pragma unroll 4
+  float acc[8], win[4][8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
   for (int k = 0; k < KW; ++k) {
     const int idx = local + k;  // index into [state(KW-1) ++ x_seg]
-    const float v = idx < KW - 1 ? st[idx] : load_in(a.x, a.in_dtype, (size_t)(s0 + idx - (KW - 1)) * a.x_stride + c);
-    win[k] = v;
-    acc += v * a.w[(size_t)c * KW + k];
+    if (idx < KW - 1) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) win[k][e] = st[(size_t)e * (KW - 1) + idx];
+    } else {
+      const size_t off = (size_t)(s0 + idx - (KW - 1)) * a.x_stride + c;
+      if (a.in_dtype == 0) {
+        const float4 v0 = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.x) + off);
+        const float4 v1 = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.x) + off + 4);
+        win[k][0] = v0.x; win[k][1] = v0.y; win[k][2] = v0.z; win[k][3] = v0.w;
+        win[k][4] = v1.x; win[k][5] = v1.y; win[k][6] = v1.z; win[k][7] = v1.w;
+      } else {
+        const uint4 u = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.x) + off);
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(h2[e]);
+          win[k][2 * e] = f.x; win[k][2 * e + 1] = f.y;
+        }
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] += win[k][e] * a.w[(size_t)(c + e) * KW + k];
   }
-  a.out[(size_t)t * a.C + c] = silu_f(acc);
+  float* o = a.out + (size_t)t * a.C + c;
+  *reinterpret_cast<float4*>(o) = make_float4(silu_f(acc[0]), silu_f(acc[1]), silu_f(acc[2]), silu_f(acc[3]));
+  *reinterpret_cast<float4*>(o + 4) = make_float4(silu_f(acc[4]), silu_f(acc[5]), silu_f(acc[6]), silu_f(acc[7]));
   if (a.journal != nullptr) {
-    float* j = a.journal + ((size_t)t * a.C + c) * (KW - 1);
-    for (int k = 1; k < KW; ++k) j[k - 1] = win[k];
+    for (int e = 0; e < 8; ++e) {
+      float* j = a.journal + ((size_t)t * a.C + c + e) * (KW - 1);
+      for (int k = 1; k < KW; ++k) j[k - 1] = win[k][e];
+    }
   }
 }
 
@@ -271,7 +296,8 @@ HE_API int he_conv1d(const ConvArgs* args, int update_state, cudaStream_t stream
   const ConvArgs& a = *args;
   if (a.T <= 0) return 0;
   if (a.KW < 2 || a.KW > 4) return -HE_ERR_BAD_ARG;
-  const long long n = (long long)a.T * a.C;
+  if (a.C % 8 != 0) return -HE_ERR_BAD_ARG;
+  const long long n = (long long)a.T * (a.C / 8);
   conv_fwd_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(a);
   HE_LAUNCH_CHECK();
   if (update_state) {

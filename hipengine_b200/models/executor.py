@@ -45,6 +45,7 @@ class BatchDesc:
     T: int
     n_seg: int
     max_ctx: int              # host upper bound of ctx_len (sizes the split-K grid)
+    segs_host: Optional[List[Tuple[int, int, int]]] = None   # (slot, start_pos, n_rows) per segment, when known
 
 
 def make_batch(segments: Sequence[Tuple[int, int, Sequence[int]]], device) -> BatchDesc:
@@ -68,7 +69,8 @@ def make_batch(segments: Sequence[Tuple[int, int, Sequence[int]]], device) -> Ba
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=device)
     pos_t = i32(pos)
     return BatchDesc(torch.tensor(toks, dtype=torch.int64, device=device), i32(slot), pos_t, pos_t + 1,
-                     i32(seg_start), i32(seg_slot), i32(tok_seg), len(toks), len(segments), max_ctx)
+                     i32(seg_start), i32(seg_slot), i32(tok_seg), len(toks), len(segments), max_ctx,
+                     [(s, p0, len(ids)) for (s, p0, ids) in segments])
 
 
 class _Scratch:
@@ -122,6 +124,12 @@ class HybridExecutor:
             self.dw[name] = K.to_device_weight(raw, t.ggml_type, t.n_rows, t.n_cols)
         if "output.weight" not in self.dw:
             self.dw["output.weight"] = self.dw["token_embd.weight"]
+        # prefill path: the two small F32 gate projections of a linear layer run as one bf16 tensor-core GEMM
+        self.ab_bf16: Dict[int, torch.Tensor] = {}
+        for i in range(self.cfg.n_layers):
+            a_name, b_name = f"blk.{i}.ssm_alpha.weight", f"blk.{i}.ssm_beta.weight"
+            if a_name in self.f32 and b_name in self.f32:
+                self.ab_bf16[i] = torch.cat([self.f32[a_name], self.f32[b_name]], 0).to(torch.bfloat16).contiguous()
 
     def W(self, i: int, slot: str) -> DeviceWeight:
         return self.dw[f"blk.{i}.{slot}"]
@@ -220,10 +228,14 @@ class HybridExecutor:
         cfg = self.cfg
         T = b.T
         H, Hkv, D = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
-        if T > GEMV_MAX_ROWS and b.n_seg == 1 and os.environ.get("HE_PREFILL_ATTN", "flash") == "flash":
+        if (T > GEMV_MAX_ROWS and b.segs_host is not None and os.environ.get("HE_PREFILL_ATTN", "flash") == "flash"):
             from ..ops import attention as A
             if A.flash_prefill_available(D):
-                A.flash_prefill(q_out, gate, self.kv[i], self.block_table, b, out, H, Hkv, D, PAGE, cfg.scale())
+                r0 = 0
+                for (slot, pos0, n) in b.segs_host:
+                    A.flash_prefill(q_out[r0:r0 + n], None if gate is None else gate[r0:r0 + n], self.kv[i],
+                                    self.block_table, slot, pos0, out[r0:r0 + n], H, Hkv, D, PAGE, cfg.scale())
+                    r0 += n
                 return
         split_len = 128 if b.max_ctx <= 8192 else 256
         max_splits = max(1, (b.max_ctx + split_len - 1) // split_len)
@@ -250,8 +262,14 @@ class HybridExecutor:
             K.rmsnorm_rows(h, self.F(i, "attn_norm.weight"), xn, cfg.rms_eps)
             qkv = self._gemm(xn, self.W(i, "attn_qkv.weight"), sc.get("qkv_bf", (T, C), torch.bfloat16), tag="q")
             z = self._gemm(xn, self.W(i, "attn_gate.weight"), sc.get("z_bf", (T, inner), torch.bfloat16), tag="q")
-            K.small_gemm_f32(xn, self.F(i, "ssm_alpha.weight"), a_p)
-            K.small_gemm_f32(xn, self.F(i, "ssm_beta.weight"), b_p)
+            if self.gemm_impl == "tcgen05" and (2 * Hv) % 8 == 0:
+                from ..ops import gemm as GM
+                ab = sc.get("ab_proj", (T, 2 * Hv), torch.float32)
+                GM.gemm_bf16(xn, self.ab_bf16[i], ab)
+                a_p, b_p = ab[:, :Hv], ab[:, Hv:]
+            else:
+                K.small_gemm_f32(xn, self.F(i, "ssm_alpha.weight"), a_p)
+                K.small_gemm_f32(xn, self.F(i, "ssm_beta.weight"), b_p)
         conv = sc.get("conv_out", (T, C), torch.float32)
         cj = journal["conv"][i] if journal is not None else None
         K.conv1d(qkv, self.F(i, "ssm_conv1d.weight"), self.conv_state[i], b.seg_start, b.seg_slot, b.tok_seg, conv, C,

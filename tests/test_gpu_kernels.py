@@ -286,3 +286,33 @@ def test_small_gemm_f32(K):
     out = torch.empty(70, 50, device="cuda")
     K.small_gemm_f32(x, w, out)
     assert torch.allclose(out, x.float() @ w.t(), atol=1e-3, rtol=1e-3)
+
+
+@pytest.mark.parametrize("D,H,Hkv,T,pos0", [(256, 6, 1, 200, 0), (256, 4, 2, 70, 37), (128, 8, 2, 129, 0), (64, 4, 4, 33, 5)])
+def test_flash_prefill_matches_reference(K, D, H, Hkv, T, pos0):
+    from hipengine_b200.ops import attention as A
+    S = pos0 + T
+    cache, bt = _paged_setup(S, Hkv, D, n_slots=2, max_ctx=320)
+    g = torch.Generator(device="cuda").manual_seed(1)
+    kf = torch.randn(S, Hkv * D, generator=g, device="cuda")
+    vf = torch.randn(S, Hkv * D, generator=g, device="cuda")
+    slot = torch.full((S,), 1, device="cuda", dtype=torch.int32)
+    pos = torch.arange(S, device="cuda", dtype=torch.int32)
+    dummy = torch.empty(S, H, D, device="cuda", dtype=torch.bfloat16)
+    K.qkv_post(torch.zeros(S, H * D, device="cuda"), kf, vf, None, None, dummy, None, cache, bt, slot, pos, H, Hkv, D,
+               16, False, 0, 1e6, 1e-6)
+    q = (torch.randn(T, H, D, generator=g, device="cuda") * 0.5).bfloat16()
+    gate = torch.randn(T, H, D, generator=g, device="cuda").bfloat16()
+    out = torch.empty(T, H * D, device="cuda", dtype=torch.bfloat16)
+    scale = D ** -0.5
+    A.flash_prefill(q, gate, cache, bt, 1, pos0, out, H, Hkv, D, 16, scale)
+    kb = kf.reshape(S, Hkv, D).bfloat16().float()
+    vb = vf.reshape(S, Hkv, D).bfloat16().float()
+    qpos = torch.arange(pos0, pos0 + T, device="cuda")
+    ref = R.causal_gqa_attention(q.float(), kb, vb, qpos, scale)
+    ref = R.bf16_round(ref) * torch.sigmoid(gate.float())
+    assert torch.allclose(out.float().reshape(T, H, D), ref, atol=2e-2, rtol=2e-2)
+    # sliding window, no gate
+    A.flash_prefill(q, None, cache, bt, 1, pos0, out, H, Hkv, D, 16, scale, window=48)
+    ref = R.causal_gqa_attention(q.float(), kb, vb, qpos, scale, window=48)
+    assert torch.allclose(out.float().reshape(T, H, D), ref, atol=2e-2, rtol=2e-2)
