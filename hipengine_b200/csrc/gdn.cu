@@ -116,24 +116,27 @@ __global__ void __launch_bounds__(128) gdn_scan_kernel(const GdnScanArgs p) {
         const float4 kv4 = *reinterpret_cast<const float4*>(&sk[tt][ks * 36 + i4 * 4]);
         kr[i4 * 4] = kv4.x; kr[i4 * 4 + 1] = kv4.y; kr[i4 * 4 + 2] = kv4.z; kr[i4 * 4 + 3] = kv4.w;
       }
-      float kv = 0.f;
+      // four independent partial sums per reduction keep the FMA pipe busy (the chains are otherwise serial)
+      float kv4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
         S[i] *= dec;
-        kv += kr[i] * S[i];
+        kv4[i & 3] += kr[i] * S[i];
       }
+      float kv = (kv4[0] + kv4[1]) + (kv4[2] + kv4[3]);
       kv += __shfl_xor_sync(0xffffffffu, kv, 1);
       kv += __shfl_xor_sync(0xffffffffu, kv, 2);
       const float delta = (sv[tt][cw] - kv) * bet;
-      float o = 0.f;
+      float o4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i4 = 0; i4 < 8; ++i4) {
         const float4 q4 = *reinterpret_cast<const float4*>(&sq[tt][ks * 36 + i4 * 4]);
-        S[i4 * 4] += kr[i4 * 4] * delta;         o += q4.x * S[i4 * 4];
-        S[i4 * 4 + 1] += kr[i4 * 4 + 1] * delta; o += q4.y * S[i4 * 4 + 1];
-        S[i4 * 4 + 2] += kr[i4 * 4 + 2] * delta; o += q4.z * S[i4 * 4 + 2];
-        S[i4 * 4 + 3] += kr[i4 * 4 + 3] * delta; o += q4.w * S[i4 * 4 + 3];
+        S[i4 * 4] += kr[i4 * 4] * delta;         o4[0] += q4.x * S[i4 * 4];
+        S[i4 * 4 + 1] += kr[i4 * 4 + 1] * delta; o4[1] += q4.y * S[i4 * 4 + 1];
+        S[i4 * 4 + 2] += kr[i4 * 4 + 2] * delta; o4[2] += q4.z * S[i4 * 4 + 2];
+        S[i4 * 4 + 3] += kr[i4 * 4 + 3] * delta; o4[3] += q4.w * S[i4 * 4 + 3];
       }
+      float o = (o4[0] + o4[1]) + (o4[2] + o4[3]);
       o += __shfl_xor_sync(0xffffffffu, o, 1);
       o += __shfl_xor_sync(0xffffffffu, o, 2);
       if (ks == 0) p.out[((size_t)(c0 + tt) * p.Hv + h) * DV + col] = o;

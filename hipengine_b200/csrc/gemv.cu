@@ -353,10 +353,34 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const __grid_constant_
       rr = row_of(a, L, t_row, rg);
 #pragma unroll
       for (int r = 0; r < R; ++r) acc[r] = 0.f;
+      const HeGemvSeg& fsg = a.seg[L.si];
+      if (fsg.qtype != HE_Q4_K && fsg.qtype != HE_Q6_K && fsg.qtype != HE_Q8_0 && fsg.epi < 3) {
+        // float-weight rows: the whole warp walks each row with coalesced loads (nothing was staged for them)
+        for (int t = 0; t < rg; ++t) {
+          const RowRef fr = row_of(a, L, t, rg);
+          if (!fr.valid) break;
+          float fa[R];
+#pragma unroll
+          for (int r = 0; r < R; ++r) fa[r] = 0.f;
+          hegemv::row_float_coop<R>(fr.w + (size_t)fr.n * (size_t)hegemv::row_bytes_dev(fr.qt, K), fr.qt, K, a.x,
+                                    a.x_dtype, a.x_stride, a.norm_w, s, lane, fa);
+#pragma unroll
+          for (int r = 0; r < R; ++r) {
+            const float v = warp_sum(fa[r]);
+            if (lane == 0) {
+              const size_t off = (size_t)r * fsg.out_stride + fr.n;
+              if (fsg.epi == 0) reinterpret_cast<float*>(fsg.out)[off] = v;
+              else if (fsg.epi == 1) reinterpret_cast<__nv_bfloat16*>(fsg.out)[off] = f32_to_bf16(v);
+              else reinterpret_cast<float*>(fsg.out)[off] += v;
+            }
+          }
+        }
+      }
     }
+    const bool float_item = !(rr.qt == HE_Q4_K || rr.qt == HE_Q6_K || rr.qt == HE_Q8_0) && a.seg[L.si].epi < 3;
     if (!sm100::mbar_wait(&bars[warp][cc.slot], cc.parity, &abort_flag, a.status, 201)) break;
     const int blk0 = cc.uk << bq_shift, nblk = min(BQ, nb - blk0);
-    if (bq < nblk) {
+    if (bq < nblk && !float_item) {
       const int b = blk0 + bq;
       const uint8_t* rowp = ring + (uint32_t)cc.slot * a.slot_bytes + (uint32_t)t_row * row_stride;
       if (rr.qt == HE_Q4_K) hegemv::block_q4k<R>(rowp + bq * 144, b, s, acc);
@@ -369,7 +393,7 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const __grid_constant_
       }
     }
     __syncwarp();   // every lane is done reading the slot before it may be refilled in the next iteration
-    if (cc.uk == upi - 1) {
+    if (cc.uk == upi - 1 && !float_item) {
       const HeGemvSeg& sg = a.seg[L.si];
 #pragma unroll
       for (int r = 0; r < R; ++r) {

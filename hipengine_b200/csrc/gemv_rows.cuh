@@ -209,4 +209,48 @@ __device__ __forceinline__ void block_float(const uint8_t* w, int qtype, int b, 
   }
 }
 
+// Whole-warp dot product of one float-weight row (coalesced loads), partial sums left in acc[] of every lane.
+template <int R>
+__device__ __forceinline__ void row_float_coop(const uint8_t* w, int qtype, int K, const void* x, int x_dtype,
+                                               long long x_stride, const float* norm_w, const SmemView& s, int lane,
+                                               float (&acc)[R]) {
+  for (int k = lane * 4; k < K; k += 128) {
+    float wv[4];
+    if (qtype == HE_F32) {
+      const float4 f = __ldg(reinterpret_cast<const float4*>(w + (size_t)k * 4));
+      wv[0] = f.x; wv[1] = f.y; wv[2] = f.z; wv[3] = f.w;
+    } else {
+      const uint2 u = __ldg(reinterpret_cast<const uint2*>(w + (size_t)k * 2));
+      if (qtype == HE_BF16) {
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+        const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+        wv[0] = a.x; wv[1] = a.y; wv[2] = c.x; wv[3] = c.y;
+      } else {
+        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&u.x));
+        const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
+        wv[0] = a.x; wv[1] = a.y; wv[2] = c.x; wv[3] = c.y;
+      }
+    }
+    float4 nw = make_float4(1.f, 1.f, 1.f, 1.f);
+    if (norm_w != nullptr) nw = __ldg(reinterpret_cast<const float4*>(norm_w + k));
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      float xv[4];
+      const size_t off = (size_t)r * x_stride + k;
+      if (x_dtype == 0) {
+        const float4 f = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(x) + off));
+        xv[0] = f.x; xv[1] = f.y; xv[2] = f.z; xv[3] = f.w;
+      } else {
+        const uint2 u = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(x) + off));
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+        const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+        xv[0] = a.x; xv[1] = a.y; xv[2] = c.x; xv[3] = c.y;
+      }
+      const float ir = s.inv_rms[r];
+      acc[r] += wv[0] * (xv[0] * ir * nw.x) + wv[1] * (xv[1] * ir * nw.y) + wv[2] * (xv[2] * ir * nw.z) +
+                wv[3] * (xv[3] * ir * nw.w);
+    }
+  }
+}
+
 }  // namespace hegemv

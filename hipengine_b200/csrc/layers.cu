@@ -171,7 +171,8 @@ struct ConvArgs {
   int C, KW, T, n_seg;
 };
 
-// one thread per (token, 8 channels)
+// one thread per (token, 8 channels); KWT > 0 fixes the kernel width at compile time (registers, no local memory)
+template <int KWT>
 __global__ void conv_fwd_kernel(const ConvArgs a) {
   const int C8 = a.C >> 3;
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -180,11 +181,17 @@ __global__ void conv_fwd_kernel(const ConvArgs a) {
   const int sg = a.tok_seg[t];
   const int s0 = a.seg_start[sg];
   const int local = t - s0;
-  const int KW = a.KW;
+  constexpr int KW = KWT;
   const float* st = a.state + ((size_t)a.seg_slot[sg] * a.C + c) * (KW - 1);
-  float acc[8], win[4][8];
+  float acc[8], win[KW][8];
 #pragma unroll
   for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+  float wreg[8][KW];
+#pragma unroll
+  for (int e = 0; e < 8; ++e)
+#pragma unroll
+    for (int k = 0; k < KW; ++k) wreg[e][k] = __ldg(a.w + (size_t)(c + e) * KW + k);
+#pragma unroll
   for (int k = 0; k < KW; ++k) {
     const int idx = local + k;  // index into [state(KW-1) ++ x_seg]
     if (idx < KW - 1) {
@@ -208,14 +215,16 @@ __global__ void conv_fwd_kernel(const ConvArgs a) {
       }
     }
 #pragma unroll
-    for (int e = 0; e < 8; ++e) acc[e] += win[k][e] * a.w[(size_t)(c + e) * KW + k];
+    for (int e = 0; e < 8; ++e) acc[e] += win[k][e] * wreg[e][k];
   }
   float* o = a.out + (size_t)t * a.C + c;
   *reinterpret_cast<float4*>(o) = make_float4(silu_f(acc[0]), silu_f(acc[1]), silu_f(acc[2]), silu_f(acc[3]));
   *reinterpret_cast<float4*>(o + 4) = make_float4(silu_f(acc[4]), silu_f(acc[5]), silu_f(acc[6]), silu_f(acc[7]));
   if (a.journal != nullptr) {
+#pragma unroll
     for (int e = 0; e < 8; ++e) {
       float* j = a.journal + ((size_t)t * a.C + c + e) * (KW - 1);
+#pragma unroll
       for (int k = 1; k < KW; ++k) j[k - 1] = win[k][e];
     }
   }
@@ -298,7 +307,10 @@ HE_API int he_conv1d(const ConvArgs* args, int update_state, cudaStream_t stream
   if (a.KW < 2 || a.KW > 4) return -HE_ERR_BAD_ARG;
   if (a.C % 8 != 0) return -HE_ERR_BAD_ARG;
   const long long n = (long long)a.T * (a.C / 8);
-  conv_fwd_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(a);
+  const unsigned nblk = (unsigned)((n + 255) / 256);
+  if (a.KW == 4) conv_fwd_kernel<4><<<nblk, 256, 0, stream>>>(a);
+  else if (a.KW == 3) conv_fwd_kernel<3><<<nblk, 256, 0, stream>>>(a);
+  else conv_fwd_kernel<2><<<nblk, 256, 0, stream>>>(a);
   HE_LAUNCH_CHECK();
   if (update_state) {
     const long long m = (long long)a.n_seg * a.C;

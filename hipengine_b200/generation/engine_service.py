@@ -1,0 +1,299 @@
+"""Engine service: one driver thread owns the model; front-end threads talk to it through a command queue.
+
+Same ownership rule as the reference (``hipengine/generation/engine_service.py:207-297,937-1025``): callers
+enqueue commands (submit / cancel / control) on a bounded queue and wait on per-request collectors; the
+driver loop drains commands, runs one engine tick, routes events and finishes requests.  A fatal failure
+records an ``unhealthy`` cause, fails every request and stops the loop (``:354-398``); a command that is not
+served within ``command_timeout_seconds`` raises ``EngineCommandTimeout`` (``:44,65-77``).
+"""
+from __future__ import annotations
+
+import queue
+import threading
+import time
+import traceback
+from dataclasses import dataclass, field
+from typing import Any, Callable, Dict, Iterator, List, Optional, Sequence, Tuple
+
+from ..config import EngineConfig
+from .engine_loop import EngineLoop
+from .scheduler import FINISHED, GenerationAdmissionRejected, RequestState
+from .types import FinishDetails, GenerationOutput, GenerationRequest, GenerationStreamChunk
+
+COMMAND_QUEUE_DEPTH = 1024
+
+
+class EngineCommandTimeout(TimeoutError):
+    pass
+
+
+class EngineUnavailable(RuntimeError):
+    """The service is closed or unhealthy (HTTP 503, retryable)."""
+
+
+class OutputCollector:
+    """Per-request mailbox: stream chunks (bounded) and the final output."""
+
+    def __init__(self, mailbox: int = 64, stream: bool = False):
+        self.stream = stream
+        self.chunks: "queue.Queue[GenerationStreamChunk]" = queue.Queue(maxsize=mailbox if stream else 0)
+        self.done = threading.Event()
+        self.output: Optional[GenerationOutput] = None
+        self.rid: Optional[int] = None
+
+    def put_chunk(self, ch: GenerationStreamChunk) -> None:
+        if self.stream:
+            try:
+                self.chunks.put(ch, timeout=30.0)
+            except queue.Full:
+                pass
+
+    def finish(self, out: GenerationOutput) -> None:
+        self.output = out
+        self.done.set()
+
+
+@dataclass
+class _Command:
+    kind: str
+    payload: Any = None
+    reply: "queue.Queue" = field(default_factory=lambda: queue.Queue(maxsize=1))
+
+
+class EngineService:
+    def __init__(self, loop: EngineLoop, config: EngineConfig, name: str = "he-engine-service"):
+        self.loop = loop
+        self.config = config
+        self.commands: "queue.Queue[_Command]" = queue.Queue(maxsize=COMMAND_QUEUE_DEPTH)
+        self.collectors: Dict[int, OutputCollector] = {}
+        self.unhealthy: Optional[Dict[str, Any]] = None
+        self.closed = False
+        self._wake = threading.Event()
+        self.loop.on_event = self._on_event
+        self.thread = threading.Thread(target=self._drive, name=name, daemon=True)
+        self.started_at = time.time()
+        self.thread.start()
+
+    # ------------------------------------------------------------------ front-end API (any thread)
+    def _call(self, kind: str, payload: Any = None, wait: bool = True) -> Any:
+        if self.closed:
+            raise EngineUnavailable("engine service is closed")
+        if self.unhealthy is not None:
+            raise EngineUnavailable(f"engine service is unhealthy: {self.unhealthy.get('exception_type')}: "
+                                    f"{self.unhealthy.get('message')}")
+        cmd = _Command(kind, payload)
+        try:
+            self.commands.put(cmd, timeout=self.config.command_timeout_seconds)
+        except queue.Full:
+            raise EngineCommandTimeout("engine command queue is full") from None
+        self._wake.set()
+        if not wait:
+            return None
+        try:
+            ok, val = cmd.reply.get(timeout=self.config.command_timeout_seconds)
+        except queue.Empty:
+            raise EngineCommandTimeout(f"engine did not serve {kind!r} within "
+                                       f"{self.config.command_timeout_seconds}s") from None
+        if not ok:
+            raise val
+        return val
+
+    def submit(self, req: GenerationRequest, stream: bool = False) -> OutputCollector:
+        col = OutputCollector(self.config.scheduler.stream_mailbox, stream)
+        col.rid = req.request_id
+        self._call("submit", (req, col))
+        return col
+
+    def generate(self, reqs: Sequence[GenerationRequest]) -> List[GenerationOutput]:
+        cols = [self.submit(r) for r in reqs]
+        outs = []
+        for c in cols:
+            self._wait(c)
+            outs.append(c.output)
+        return outs
+
+    def _wait(self, col: OutputCollector) -> None:
+        while not col.done.wait(timeout=0.5):
+            if self.unhealthy is not None or self.closed:
+                if not col.done.is_set():
+                    raise EngineUnavailable("engine stopped while the request was in flight")
+
+    def stream(self, req: GenerationRequest) -> Iterator[GenerationStreamChunk]:
+        col = self.submit(req, stream=True)
+        try:
+            while True:
+                try:
+                    ch = col.chunks.get(timeout=0.5)
+                except queue.Empty:
+                    if col.done.is_set() and col.chunks.empty():
+                        return
+                    if self.unhealthy is not None or self.closed:
+                        raise EngineUnavailable("engine stopped while streaming")
+                    continue
+                yield ch
+                if ch.finished:
+                    return
+        finally:
+            if not col.done.is_set():
+                self.cancel(req.request_id)
+
+    def stream_many(self, reqs: Sequence[GenerationRequest]) -> Iterator[Tuple[int, GenerationStreamChunk]]:
+        cols = [self.submit(r, stream=True) for r in reqs]
+        live = set(range(len(cols)))
+        while live:
+            progressed = False
+            for i in list(live):
+                try:
+                    ch = cols[i].chunks.get_nowait()
+                except queue.Empty:
+                    continue
+                progressed = True
+                yield i, ch
+                if ch.finished:
+                    live.discard(i)
+            if not progressed:
+                if self.unhealthy is not None or self.closed:
+                    raise EngineUnavailable("engine stopped while streaming")
+                time.sleep(0.001)
+
+    def cancel(self, rid: int, reason: str = "cancelled") -> bool:
+        try:
+            return bool(self._call("cancel", (rid, reason)))
+        except EngineUnavailable:
+            return False
+
+    def snapshot(self) -> Dict[str, Any]:
+        return self._call("snapshot")
+
+    def capacity(self) -> Dict[str, Any]:
+        return self._call("capacity")
+
+    def reset(self) -> None:
+        self._call("reset")
+
+    def health(self) -> Dict[str, Any]:
+        return {"healthy": self.unhealthy is None and not self.closed, "closed": self.closed,
+                "unhealthy": self.unhealthy, "uptime_seconds": time.time() - self.started_at,
+                "driver_alive": self.thread.is_alive(), "queued_commands": self.commands.qsize()}
+
+    def close(self) -> None:
+        if self.closed:
+            return
+        try:
+            self._call("close")
+        except Exception:
+            pass
+        self.closed = True
+        self._wake.set()
+        self.thread.join(timeout=10.0)
+
+    # ------------------------------------------------------------------ driver thread
+    def _on_event(self, rs: RequestState) -> None:
+        col = self.collectors.get(rs.rid)
+        if col is None:
+            return
+        toks = self.loop.sched.take_stream_tokens(rs)
+        finished = rs.status == FINISHED
+        if col.stream and (toks or finished):
+            lps = None
+            if rs.req.logprobs and rs.logprobs:
+                lps = rs.logprobs[rs.emitted - len(toks):rs.emitted]
+            col.put_chunk(GenerationStreamChunk(rs.rid, toks, None, finished, rs.finish if finished else None, lps,
+                                                rs.telemetry if finished else None, rs.error))
+        if finished:
+            col.finish(self.loop.sched.make_output(rs))
+            self.collectors.pop(rs.rid, None)
+            self.loop.sched.pop_finished(rs.rid)
+
+    def _serve(self, cmd: _Command) -> bool:
+        """Returns False when the loop should stop."""
+        try:
+            if cmd.kind == "submit":
+                req, col = cmd.payload
+                self.collectors[req.request_id] = col
+                try:
+                    self.loop.submit(req)
+                except GenerationAdmissionRejected as exc:
+                    self.collectors.pop(req.request_id, None)
+                    out = GenerationOutput(req.request_id, list(req.prompt_token_ids), [], None,
+                                           FinishDetails("error", message=str(exc)), None, error=str(exc))
+                    col.put_chunk(GenerationStreamChunk(req.request_id, [], None, True, out.finish, None, None,
+                                                        str(exc)))
+                    col.finish(out)
+                cmd.reply.put((True, None))
+            elif cmd.kind == "cancel":
+                rid, reason = cmd.payload
+                cmd.reply.put((True, self.loop.cancel(rid, reason)))
+            elif cmd.kind == "snapshot":
+                cmd.reply.put((True, self.loop.snapshot()))
+            elif cmd.kind == "capacity":
+                cmd.reply.put((True, self.loop.runner.capacity()))
+            elif cmd.kind == "reset":
+                self.loop.fail_all("engine reset")
+                self.loop.runner.reset()
+                cmd.reply.put((True, None))
+            elif cmd.kind == "close":
+                self.loop.fail_all("engine closed")
+                self.loop.runner.close()
+                cmd.reply.put((True, None))
+                return False
+            else:
+                cmd.reply.put((False, ValueError(f"unknown command {cmd.kind}")))
+        except Exception as exc:  # a failing control command must not kill the driver
+            try:
+                cmd.reply.put_nowait((False, exc))
+            except queue.Full:
+                pass
+        return True
+
+    def _drive(self) -> None:
+        try:
+            while True:
+                drained = 0
+                while drained < 64:
+                    try:
+                        cmd = self.commands.get_nowait()
+                    except queue.Empty:
+                        break
+                    drained += 1
+                    if not self._serve(cmd):
+                        return
+                if self.loop.idle():
+                    self._wake.wait(timeout=0.05)
+                    self._wake.clear()
+                    continue
+                self.loop.tick()
+        except BaseException as exc:  # fatal: record, fail everything, stop
+            tb = traceback.extract_tb(exc.__traceback__)
+            loc = f"{tb[-1].filename}:{tb[-1].lineno}" if tb else "?"
+            self.unhealthy = {"exception_type": type(exc).__name__, "message": str(exc), "location": loc,
+                              "cause_type": type(exc.__cause__).__name__ if exc.__cause__ else None,
+                              "request_ids": list(self.loop.sched.active), "at": time.time()}
+            try:
+                self.loop.fail_all(f"engine_unavailable: {type(exc).__name__}: {exc}")
+            except Exception:
+                pass
+            for col in list(self.collectors.values()):
+                if not col.done.is_set():
+                    out = GenerationOutput(col.rid or 0, [], [], None, FinishDetails("error", message=str(exc)),
+                                           None, error=f"engine_unavailable: {exc}")
+                    col.put_chunk(GenerationStreamChunk(col.rid or 0, [], None, True, out.finish, None, None,
+                                                        out.error))
+                    col.finish(out)
+            self.collectors.clear()
+
+
+def build_engine(weights, backend: str, config: EngineConfig, tokenizer=None) -> EngineService:
+    """weights + backend -> runner -> loop -> service."""
+    eos = getattr(tokenizer, "eos_token_id", None)
+    if backend == "cpu_reference":
+        from .runner import CpuReferenceRunner
+        runner = CpuReferenceRunner(weights, config, eos)
+    else:
+        from .gpu_runner import GpuRunner
+        runner = GpuRunner(weights, config, eos)
+    return EngineService(EngineLoop(runner, config, tokenizer), config)
+
+
+def engine_from_runner(runner, config: EngineConfig, tokenizer=None) -> EngineService:
+    return EngineService(EngineLoop(runner, config, tokenizer), config)

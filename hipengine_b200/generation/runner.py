@@ -1,0 +1,153 @@
+"""Model runners: the scheduler-facing adapters over a model executor.
+
+The engine loop talks to a runner through a small protocol (the role of the reference's
+``EngineLoopRunner``, ``hipengine/generation/engine_loop.py:420-488``, implemented there by
+``Qwen35GGUFResidentModelRunner``, ``hipengine/generation/qwen35_gguf.py:7133-13320``):
+``admit`` (slot + KV pages + prefix-cache match), ``prefill`` (chunked, packed), ``decode`` (one step for all
+resident rows), ``release``.  Two runners exist: ``CpuReferenceRunner`` (fp32 reference forward; the
+"cpu_reference backend" used for correctness runs and host-only tests) and ``GpuRunner`` (sm_100a executor,
+decode graphs, paged pool, radix prefix cache with recurrent-state snapshots).
+"""
+from __future__ import annotations
+
+import time
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..config import EngineConfig
+from ..kvcache.pool import PagePool, PoolExhausted
+from ..kvcache.radix import PrefixCompatibilityKey, RadixCache
+from . import sampling as S
+from .scheduler import GenerationAdmissionRejected, RequestState
+from .types import TokenLogprob
+
+
+class ExecutionFailure(RuntimeError):
+    """A contained failure: only ``request_ids`` are affected; the engine keeps serving the others.
+
+    ``mutation`` says how far device state for those requests got: none | partial | committed | unknown
+    (``hipengine/generation/engine_loop.py:301-340``).
+    """
+
+    def __init__(self, request_ids: Sequence[int], phase: str, message: str, mutation: str = "unknown"):
+        super().__init__(message)
+        self.request_ids = list(request_ids)
+        self.phase = phase
+        self.mutation = mutation
+
+
+class BaseRunner:
+    eos_token_id: Optional[int] = None
+    vocab: int = 0
+    max_slots: int = 1
+    max_context: int = 0
+    supports_mtp: bool = False
+
+    # -- sampling shared by both runners ------------------------------------------------------------
+    def _row_processors(self, rs: RequestState) -> Dict[str, Any]:
+        req = rs.req
+        suppress = list(req.suppress_token_ids)
+        eos = req.eos_token_id if req.eos_token_id is not None else self.eos_token_id
+        if eos is not None and (len(rs.generated) < req.min_tokens or (rs.thinking and rs.thinking.suppress_eos())
+                                or req.ignore_eos and False):
+            suppress.append(eos)
+        bias = list(req.logit_bias)
+        if rs.thinking is not None:
+            b = rs.thinking.close_bias()
+            if b > 0 and rs.thinking.close_ids:
+                bias.append((rs.thinking.close_ids[0], b))
+        return dict(logit_bias=bias, history=rs.generated, prompt=req.prompt_token_ids,
+                    repetition_penalty=req.repetition_penalty, presence_penalty=req.presence_penalty,
+                    frequency_penalty=req.frequency_penalty, suppress=suppress)
+
+    def _needs_processing(self, rs: RequestState) -> bool:
+        req = rs.req
+        return bool(req.logit_bias or req.suppress_token_ids or req.repetition_penalty != 1.0
+                    or req.presence_penalty != 0.0 or req.frequency_penalty != 0.0
+                    or len(rs.generated) < req.min_tokens
+                    or (rs.thinking is not None and (rs.thinking.suppress_eos() or rs.thinking.close_bias() > 0)))
+
+    def sample_host(self, rs: RequestState, logits: torch.Tensor) -> Tuple[int, Optional[TokenLogprob]]:
+        """Full host sampler law on one logits row (CPU tensor or CUDA tensor)."""
+        req = rs.req
+        if rs.forced:
+            tok = rs.forced.pop()
+            lp = None
+            if req.logprobs:
+                lp = TokenLogprob(tok, S.token_logprob(logits, tok, req.temperature or 1.0),
+                                  tuple(S.top_logprobs(logits, req.top_logprobs, req.temperature or 1.0)))
+            return tok, lp
+        lg = S.apply_processors(logits, **self._row_processors(rs)) if self._needs_processing(rs) else logits
+        tok, _ = S.sample_token(lg, req.temperature, req.top_k, req.top_p, req.min_p, rs.seed, rs.sample_counter)
+        lp = None
+        if req.logprobs:
+            t = req.temperature if req.temperature > 0 else 1.0
+            lp = TokenLogprob(tok, S.token_logprob(lg, tok, t), tuple(S.top_logprobs(lg, req.top_logprobs, t)))
+        return tok, lp
+
+    # -- protocol defaults ---------------------------------------------------------------------------
+    def capacity(self) -> Dict[str, Any]:
+        return {"max_slots": self.max_slots, "max_context": self.max_context}
+
+    def snapshot(self) -> Dict[str, Any]:
+        return {}
+
+    def reset(self) -> None:
+        pass
+
+    def close(self) -> None:
+        pass
+
+
+class CpuReferenceRunner(BaseRunner):
+    """fp32 reference forward on the host.  One ``RefState`` per admitted request."""
+
+    def __init__(self, weights, config: EngineConfig, eos_token_id: Optional[int] = None):
+        from ..ref.model import RefModel
+        self.model = RefModel(weights)
+        self.cfg = weights.config
+        self.vocab = self.cfg.vocab
+        self.eos_token_id = eos_token_id
+        self.max_slots = config.scheduler.max_active_requests
+        self.max_context = min(config.max_sequence_length, self.cfg.max_context)
+        self.states: Dict[int, Any] = {}
+        self.last_logits: Dict[int, torch.Tensor] = {}
+
+    def admit(self, rs: RequestState) -> bool:
+        if rs.total_budget_tokens > self.max_context:
+            raise GenerationAdmissionRejected(
+                f"context_overflow: prompt {rs.prompt_len} + max_tokens {rs.req.max_tokens} exceeds {self.max_context}")
+        if len(self.states) >= self.max_slots:
+            return False
+        self.states[rs.rid] = self.model.new_state()
+        rs.slot = len(self.states) - 1
+        return True
+
+    @torch.no_grad()
+    def prefill(self, work: List[Tuple[RequestState, int]]) -> Dict[int, Tuple[int, Optional[TokenLogprob]]]:
+        out: Dict[int, Tuple[int, Optional[TokenLogprob]]] = {}
+        for rs, n in work:
+            toks = rs.req.prompt_token_ids[rs.prefilled:rs.prefilled + n]
+            logits, _ = self.model.forward(torch.tensor(toks, dtype=torch.long), self.states[rs.rid])
+            if rs.prefilled + n >= rs.prompt_len:
+                out[rs.rid] = self.sample_host(rs, logits[-1])
+        return out
+
+    @torch.no_grad()
+    def decode(self, rows: List[RequestState]) -> List[Tuple[int, Optional[TokenLogprob]]]:
+        res = []
+        for rs in rows:
+            logits, _ = self.model.forward(torch.tensor([rs.last_token], dtype=torch.long), self.states[rs.rid])
+            res.append(self.sample_host(rs, logits[-1]))
+        return res
+
+    def release(self, rs: RequestState) -> None:
+        self.states.pop(rs.rid, None)
+
+    def reset(self) -> None:
+        self.states.clear()
+
+    def capacity(self) -> Dict[str, Any]:
+        return {"backend": "cpu_reference", "max_slots": self.max_slots, "max_context": self.max_context,
+                "active": len(self.states)}
