@@ -1,0 +1,296 @@
+"""GPU model runner: sm_100a executor + decode graphs + paged pool + radix prefix cache.
+
+Admission follows the reference's resident runner (``hipengine/generation/qwen35_gguf.py:7999-8060``):
+``positions = len(prompt) + max_tokens``, ``pages = ceil(positions / page)``, longest block-aligned radix
+match -> shared pages (+ recurrent-state snapshot restore for hybrid models), rest of the budget held as
+growth credit.  Prefill packs the chunks of several requests into one forward; decode replays a whole-step
+CUDA graph for the resident rows.  Prefix reuse for hybrid Gated-DeltaNet models is only possible at
+boundaries that carry a conv/GDN state snapshot (``hipengine/runtime/qwen35_gguf_prefix_state.py:1-60``), so
+prefill is split at ``snapshot_interval_tokens`` and the state is copied into a snapshot slot there.
+"""
+from __future__ import annotations
+
+import time
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..config import EngineConfig
+from ..kvcache.pool import KVLease, PagePool, PoolExhausted
+from ..kvcache.radix import PrefixCompatibilityKey, RadixCache
+from ..models.decode_graph import DecodeGraphRunner
+from ..models.executor import GEMV_MAX_ROWS, PAGE, HybridExecutor, make_batch
+from ..ops import kernels as K
+from .runner import BaseRunner, ExecutionFailure
+from .scheduler import GenerationAdmissionRejected, RequestState
+from .types import TokenLogprob
+
+
+class GpuRunner(BaseRunner):
+    def __init__(self, weights, config: EngineConfig, eos_token_id: Optional[int] = None,
+                 executor: Optional[HybridExecutor] = None):
+        self.config = config
+        self.cfg = weights.config if weights is not None else executor.cfg
+        self.vocab = self.cfg.vocab
+        self.eos_token_id = eos_token_id
+        self.max_slots = config.scheduler.max_active_requests
+        self.max_context = min(config.max_sequence_length, self.cfg.max_context)
+        self.page = config.kv.page_tokens
+        assert self.page == PAGE, "the attention kernels are built for 16-token pages"
+        self.use_prefix = config.kv.prefix_cache != "off"
+        self.n_snap = config.kv.max_snapshots if (self.use_prefix and self.cfg.is_hybrid) else 0
+        pages_per_slot = (self.max_context + self.page - 1) // self.page
+        n_pages = config.kv.pool_pages or (self.max_slots * pages_per_slot * (2 if self.use_prefix else 1) + 1)
+        if executor is not None:
+            self.ex = executor
+            self.max_slots = min(self.max_slots, executor.max_slots)
+            self.n_snap = min(self.n_snap, max(0, executor.max_slots - self.max_slots))
+            n_pages = executor.n_pages
+        else:
+            dev = "cuda"
+            self.ex = HybridExecutor(weights, device=dev, max_slots=self.max_slots + self.n_snap,
+                                     max_context=self.max_context, n_pages=n_pages)
+        self.device = self.ex.device
+        self.pool = PagePool(n_pages, self.page)
+        self.radix = RadixCache(self.page, PrefixCompatibilityKey(self.cfg.arch, kv_storage=config.kv.storage,
+                                                                  page_tokens=self.page,
+                                                                  rope=f"{self.cfg.rope_theta}:{self.cfg.rope_dim}"))
+        self.radix.on_retain = self.pool.retain_cache
+        self.radix.on_release = lambda pages: self.pool.release_cache(pages)
+        self.radix.page_refcount = lambda p: self.pool.refcount[p]
+        self.radix.on_snapshot_free = self._free_snapshot
+        self.pool.evict_hook = self.radix.evict
+        self.free_slots = list(range(self.max_slots - 1, -1, -1))
+        self.free_snaps = list(range(self.max_slots + self.n_snap - 1, self.max_slots - 1, -1))
+        self.graphs = DecodeGraphRunner(self.ex, max_rows=self.max_slots, use_graphs=config.use_cuda_graphs)
+        self.resident_key: Tuple[int, ...] = ()
+        self.pinned_ids = torch.zeros(max(self.max_slots, 8), dtype=torch.int64).pin_memory()
+        self.stats = {"prefix_hits": 0, "prefix_hit_tokens": 0, "snapshots_taken": 0, "h2d_bytes": 0, "d2h_bytes": 0}
+
+    # ------------------------------------------------------------------ snapshots
+    def _free_snapshot(self, sid: int) -> None:
+        if sid not in self.free_snaps:
+            self.free_snaps.append(sid)
+
+    def _alloc_snapshot(self) -> Optional[int]:
+        if self.free_snaps:
+            return self.free_snaps.pop()
+        sid = self.radix.evict_snapshot()
+        return sid
+
+    def _copy_state(self, src: int, dst: int) -> None:
+        for t in self.ex.conv_state.values():
+            t[dst].copy_(t[src])
+        for t in self.ex.gdn_state.values():
+            t[dst].copy_(t[src])
+
+    # ------------------------------------------------------------------ admission
+    def admit(self, rs: RequestState) -> bool:
+        total = rs.total_budget_tokens
+        if total > self.max_context:
+            raise GenerationAdmissionRejected(
+                f"context_overflow: prompt {rs.prompt_len} + max_tokens {rs.req.max_tokens} exceeds {self.max_context}")
+        if not self.free_slots:
+            return False
+        prompt = rs.req.prompt_token_ids
+        match = self.radix.match(prompt, require_snapshot=self.cfg.is_hybrid) if self.use_prefix else None
+        shared = match.pages if match and match.tokens else []
+        try:
+            lease = self.pool.admit(rs.rid, total, shared_prefix=shared, now_tokens=rs.prompt_len)
+        except PoolExhausted:
+            if self.pool.pages_for(total) > self.pool.n_pages - self.pool.reserved:
+                raise GenerationAdmissionRejected("context_overflow: request exceeds the whole KV pool") from None
+            return False
+        slot = self.free_slots.pop()
+        rs.slot = slot
+        rs.runner_data = lease
+        self.ex.reset_slot(slot)
+        if shared:
+            if self.cfg.is_hybrid and match.snapshot is not None:
+                self._copy_state(match.snapshot, slot)
+            rs.prefilled = rs.cached_tokens = match.tokens
+            self.stats["prefix_hits"] += 1
+            self.stats["prefix_hit_tokens"] += match.tokens
+        self._write_block_table(slot, lease)
+        return True
+
+    def _write_block_table(self, slot: int, lease: KVLease, start: int = 0) -> None:
+        pages = lease.pages[start:]
+        if pages:
+            t = torch.tensor(pages, dtype=torch.int32)
+            self.ex.block_table[slot, start:start + len(pages)].copy_(t, non_blocking=True)
+            self.stats["h2d_bytes"] += 4 * len(pages)
+
+    def _ensure_pages(self, rs: RequestState, upto_tokens: int) -> None:
+        lease: KVLease = rs.runner_data
+        before = len(lease.pages)
+        self.pool.append_pages(lease, upto_tokens)
+        if len(lease.pages) > before:
+            self._write_block_table(rs.slot, lease, before)
+
+    # ------------------------------------------------------------------ prefill
+    @torch.no_grad()
+    def prefill(self, work: List[Tuple[RequestState, int]]) -> Dict[int, Tuple[int, Optional[TokenLogprob]]]:
+        out: Dict[int, Tuple[int, Optional[TokenLogprob]]] = {}
+        interval = self.config.kv.snapshot_interval_tokens if self.n_snap else 0
+        # split every chunk at snapshot boundaries, then run the sub-chunks round by round as packed batches
+        plans: List[List[Tuple[int, int]]] = []
+        for rs, n in work:
+            cur, end, parts = rs.prefilled, rs.prefilled + n, []
+            while cur < end:
+                nxt = end
+                if interval:
+                    b = (cur // interval + 1) * interval
+                    nxt = min(end, b)
+                parts.append((cur, nxt))
+                cur = nxt
+            plans.append(parts)
+        rounds = max(len(p) for p in plans)
+        try:
+            for r in range(rounds):
+                segs, owners = [], []
+                for (rs, n), parts in zip(work, plans):
+                    if r < len(parts):
+                        a, b = parts[r]
+                        self._ensure_pages(rs, b)
+                        toks = rs.req.prompt_token_ids[a:b]
+                        segs.append((rs.slot, a, toks))
+                        owners.append((rs, a, b))
+                        rs.telemetry.h2d_bytes += 24 * (b - a)      # ids (int64) + slot / pos / segment (int32)
+                batch = make_batch(segs, self.device)
+                self.stats["h2d_bytes"] += 8 * batch.T + 16 * batch.T
+                h = self.ex.forward(batch)
+                row = 0
+                last_rows = []
+                for rs, a, b in owners:
+                    row += b - a
+                    if b >= rs.prompt_len:
+                        last_rows.append((rs, row - 1))
+                    if interval and b % interval == 0 and b < rs.prompt_len:
+                        self._snapshot(rs, b)
+                if last_rows:
+                    idx = torch.tensor([i for _, i in last_rows], device=self.device)
+                    logits = self.ex.logits(h.index_select(0, idx))
+                    toks = self._sample_rows([rs for rs, _ in last_rows], logits)
+                    for (rs, _), t in zip(last_rows, toks):
+                        out[rs.rid] = t
+        except torch.cuda.OutOfMemoryError as exc:
+            raise ExecutionFailure([rs.rid for rs, _ in work], "prefill", f"out of memory: {exc}", "partial") from exc
+        self.resident_key = ()
+        return out
+
+    def _snapshot(self, rs: RequestState, n_tokens: int) -> None:
+        """Copy the slot's recurrent state into a snapshot slot and publish the prefix [0, n_tokens)."""
+        sid = self._alloc_snapshot()
+        if sid is None:
+            return
+        self._copy_state(rs.slot, sid)
+        lease: KVLease = rs.runner_data
+        self.radix.insert(rs.req.prompt_token_ids[:n_tokens], lease.pages[:n_tokens // self.page], {n_tokens: sid})
+        self.stats["snapshots_taken"] += 1
+
+    # ------------------------------------------------------------------ sampling
+    def _sample_rows(self, rows: List[RequestState], logits: torch.Tensor) -> List[Tuple[int, Optional[TokenLogprob]]]:
+        """logits: fp32 [R, V] on the device.  Plain rows use the device sampler; processed rows the host law."""
+        R = len(rows)
+        res: List[Optional[Tuple[int, Optional[TokenLogprob]]]] = [None] * R
+        plain = [i for i, rs in enumerate(rows) if not rs.forced and not self._needs_processing(rs)]
+        if plain:
+            params = K.pack_sample_params([(rows[i].req.temperature, rows[i].req.top_k, rows[i].req.top_p,
+                                            rows[i].req.min_p, rows[i].seed, rows[i].sample_counter) for i in plain],
+                                          self.device)
+            sub = logits if len(plain) == R else logits.index_select(0, torch.tensor(plain, device=self.device))
+            ids = torch.empty(len(plain), dtype=torch.int64, device=self.device)
+            K.sample_rows(sub, params, ids)
+            host = self.pinned_ids[:len(plain)]
+            host.copy_(ids, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            self.stats["d2h_bytes"] += 8 * len(plain)
+            toks = host.tolist()
+            for i in plain:
+                rows[i].telemetry.d2h_bytes += 8
+            for j, i in enumerate(plain):
+                lp = None
+                if rows[i].req.logprobs:
+                    lp = self._device_logprobs(rows[i], sub[j:j + 1], toks[j])
+                res[i] = (int(toks[j]), lp)
+        for i, rs in enumerate(rows):
+            if res[i] is None:
+                res[i] = self.sample_host(rs, logits[i])
+                self.stats["d2h_bytes"] += 4 * self.vocab
+                rs.telemetry.d2h_bytes += 4 * self.vocab
+        return res  # type: ignore
+
+    def _device_logprobs(self, rs: RequestState, row: torch.Tensor, tok: int) -> TokenLogprob:
+        t = rs.req.temperature if rs.req.temperature > 0 else 1.0
+        chosen = torch.tensor([tok], dtype=torch.int64, device=self.device)
+        ids, lps, clp = K.topn_logprobs(row, rs.req.top_logprobs, t, chosen)
+        top = tuple((int(a), float(b)) for a, b in zip(ids[0].tolist(), lps[0].tolist()))
+        return TokenLogprob(tok, float(clp[0].item()), top)
+
+    # ------------------------------------------------------------------ decode
+    @torch.no_grad()
+    def decode(self, rows: List[RequestState]) -> List[Tuple[int, Optional[TokenLogprob]]]:
+        R = len(rows)
+        key = tuple(rs.rid for rs in rows)
+        for rs in rows:
+            self._ensure_pages(rs, rs.position)
+        if key != self.resident_key:
+            # the resident set changed (admission, finish, or a prefill ran): reinstall rows on the device
+            self.graphs.set_rows([rs.slot for rs in rows], [rs.last_token for rs in rows],
+                                 [rs.position - 1 for rs in rows])
+            self.stats["h2d_bytes"] += 24 * R
+            for rs in rows:
+                rs.telemetry.h2d_bytes += 24
+            self.resident_key = key
+        max_ctx = max(rs.position for rs in rows)
+        all_greedy = all(rs.req.temperature == 0.0 and not rs.forced and not self._needs_processing(rs)
+                         and not rs.req.logprobs for rs in rows)
+        if all_greedy:
+            self.graphs.step(R, max_ctx, greedy=True)
+            host = self.pinned_ids[:R]
+            host.copy_(self.graphs.next_ids[:R], non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            self.stats["d2h_bytes"] += 8 * R
+            for rs in rows:
+                rs.telemetry.d2h_bytes += 8
+            return [(int(t), None) for t in host.tolist()]
+        self.graphs.step(R, max_ctx, greedy=False)
+        res = self._sample_rows(rows, self.graphs.logits[:R])
+        self.graphs.next_ids[:R].copy_(torch.tensor([t for t, _ in res], dtype=torch.int64), non_blocking=True)
+        self.graphs.publish(R)
+        self.stats["h2d_bytes"] += 8 * R
+        return res
+
+    # ------------------------------------------------------------------ release / lifecycle
+    def release(self, rs: RequestState) -> None:
+        lease: Optional[KVLease] = rs.runner_data
+        if lease is not None:
+            if self.use_prefix and not self.cfg.is_hybrid and rs.prefilled >= self.page:
+                n = (min(rs.prefilled, rs.prompt_len) // self.page) * self.page
+                self.radix.insert(rs.req.prompt_token_ids[:n], lease.pages[:n // self.page])
+            self.pool.release(rs.rid)
+            rs.runner_data = None
+        if rs.slot is not None and rs.slot not in self.free_slots and rs.slot < self.max_slots:
+            self.free_slots.append(rs.slot)
+        if rs.rid in self.resident_key:
+            self.resident_key = ()
+
+    def reset(self) -> None:
+        for rid in list(self.pool.leases):
+            self.pool.release(rid)
+        self.radix.clear()
+        self.free_slots = list(range(self.max_slots - 1, -1, -1))
+        self.free_snaps = list(range(self.max_slots + self.n_snap - 1, self.max_slots - 1, -1))
+        self.resident_key = ()
+
+    def capacity(self) -> Dict[str, Any]:
+        return {"backend": "cuda_sm100a", "max_slots": self.max_slots, "max_context": self.max_context,
+                "free_slots": len(self.free_slots), "kv_pool": self.pool.snapshot(),
+                "prefix_cache": self.radix.snapshot_stats(), "state_bytes": self.ex.state_bytes(),
+                "kv_bytes_per_token": self.cfg.kv_bytes_per_token(),
+                "recurrent_state_bytes_per_request": self.cfg.recurrent_state_bytes()}
+
+    def snapshot(self) -> Dict[str, Any]:
+        return {"pool": self.pool.snapshot(), "prefix": self.radix.snapshot_stats(), "graphs": dict(self.graphs.stats, kernels_per_graph=None),
+                **self.stats}

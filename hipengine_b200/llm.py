@@ -139,6 +139,33 @@ class LLM:
         self._closed = False
         self._weights = None
 
+    @classmethod
+    def from_executor(cls, executor, tokenizer: Any = None, max_active_requests: Optional[int] = None,
+                      engine_config: Optional[EngineConfig] = None, **kw) -> "LLM":
+        """Wrap an already-resident GPU executor (weights stay where they are) in the public API."""
+        from .generation.engine_service import engine_from_runner
+        from .generation.gpu_runner import GpuRunner
+        from .tokenization.gguf_tokenizer import ByteTokenizer
+        self = cls.__new__(cls)
+        self.model = executor
+        self.backend = "cuda_sm100a"
+        self.profile = ExecutionProfile.PRODUCTION
+        base = engine_config or EngineConfig.from_env()
+        n = int(max_active_requests or executor.max_slots)
+        self.config = replace(base, max_sequence_length=executor.max_context,
+                              scheduler=replace(base.scheduler, max_active_requests=n),
+                              kv=replace(base.kv, prefix_cache=kw.get("prefix_cache", "off"),
+                                         pool_pages=executor.n_pages))
+        self._seed = 0
+        self._weights_recipe = "q4_k_m"
+        self._tokenizer = tokenizer or ByteTokenizer(executor.cfg.vocab)
+        self._lock = threading.Lock()
+        self._closed = False
+        self._weights = None
+        runner = GpuRunner(None, self.config, getattr(self._tokenizer, "eos_token_id", None), executor=executor)
+        self._engine = engine_from_runner(runner, self.config, self._tokenizer)
+        return self
+
     # ------------------------------------------------------------------ construction
     @staticmethod
     def _resolve_backend(backend: str, device: Optional[str]) -> str:

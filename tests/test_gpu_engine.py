@@ -1,0 +1,78 @@
+"""LLM API on the sm_100a backend: continuous batching, prefix-cache hits with recurrent-state snapshots,
+sampling modes, and agreement with the CPU reference engine."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def setup():
+    from dataclasses import replace
+    from hipengine_b200 import LLM
+    from hipengine_b200.config import EngineConfig, KVConfig
+    from hipengine_b200.loading.synth import build_random_model
+    from hipengine_b200.models.config import TINY_HYBRID
+    w = build_random_model(TINY_HYBRID, seed=2, std=0.05)
+    cfg = EngineConfig(kv=KVConfig(snapshot_interval_tokens=64, max_snapshots=4))
+    llm = LLM(w.to("cuda"), backend="cuda_sm100a", max_active_requests=4, max_sequence_length=512,
+              engine_config=cfg)
+    cpu = LLM(w, backend="cpu_reference", max_active_requests=4, max_sequence_length=512)
+    yield llm, cpu
+    llm.close()
+    cpu.close()
+
+
+def test_greedy_agrees_with_cpu_reference_engine(setup):
+    from hipengine_b200 import SamplingParams
+    llm, cpu = setup
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, 2048, (n,), generator=g).tolist() for n in (5, 40, 17)]
+    sp = SamplingParams(max_tokens=6, ignore_eos=True)
+    a = llm.generate_detailed(prompts, sp)
+    b = cpu.generate_detailed(prompts, sp)
+    agree = sum(x == y for oa, ob in zip(a, b) for x, y in zip(oa.token_ids, ob.token_ids))
+    assert agree >= 14, (agree, [o.token_ids for o in a], [o.token_ids for o in b])   # 18 tokens; near-ties may flip
+    assert all(o.finish.reason == "length" for o in a)
+
+
+def test_prefix_cache_hit_restores_recurrent_state(setup):
+    from hipengine_b200 import SamplingParams
+    llm, _ = setup
+    g = torch.Generator().manual_seed(6)
+    shared = torch.randint(0, 2048, (130,), generator=g).tolist()
+    sp = SamplingParams(max_tokens=8, ignore_eos=True)
+    first = llm.generate_detailed(shared + [11, 12, 13], sp)[0]
+    again = llm.generate_detailed(shared + [11, 12, 13], sp)[0]
+    other = llm.generate_detailed(shared + [99, 98], sp)[0]
+    assert first.telemetry.cached_prompt_tokens == 0
+    assert again.telemetry.cached_prompt_tokens == 128      # two 64-token snapshot boundaries
+    assert other.telemetry.cached_prompt_tokens == 128
+    assert again.token_ids == first.token_ids               # resumed from the snapshot: identical continuation
+    cap = llm.resident_capacity_estimate()
+    assert cap["prefix_cache"]["hits"] >= 2
+    assert cap["kv_pool"]["pages_cached"] >= 8
+
+
+def test_sampled_and_processed_rows_share_a_batch(setup):
+    from hipengine_b200 import SamplingParams
+    llm, _ = setup
+    sps = [SamplingParams(max_tokens=5, ignore_eos=True),
+           SamplingParams(max_tokens=5, temperature=0.8, top_k=20, seed=7, ignore_eos=True),
+           SamplingParams(max_tokens=5, logit_bias={33: 100.0}, ignore_eos=True),
+           SamplingParams(max_tokens=5, logprobs=True, top_logprobs=2, ignore_eos=True)]
+    outs = llm.generate_detailed([[1, 2, 3], [4, 5, 6], [7, 8, 9], [10, 11]], sps)
+    assert outs[2].token_ids == [33] * 5
+    assert len(outs[3].logprobs) == 5 and outs[3].logprobs[0].top[0][0] == outs[3].token_ids[0]
+    assert all(len(o.token_ids) == 5 for o in outs)
+    streamed = [t for c in llm.stream_detailed([1, 2, 3], sps[0]) for t in c.token_ids]
+    assert streamed == outs[0].token_ids
+
+
+def test_pool_is_conserved_after_traffic(setup):
+    llm, _ = setup
+    eng = llm._get_engine()
+    runner = eng.loop.runner
+    runner.pool.assert_conserved()
+    runner.radix.assert_consistent()
+    assert len(runner.free_slots) == runner.max_slots
