@@ -1,1 +1,1 @@
-"""server subpackage."""
+"""OpenAI-compatible server package."""

@@ -1,0 +1,113 @@
+"""``python -m hipengine_b200.server`` / ``hipengine-b200 serve``: start the OpenAI-compatible server.
+
+Flag surface follows the reference's server and engine-loop flags (``hipengine/server/__main__.py:139-490``,
+``hipengine/generation/engine_loop.py:2099-2215``), reduced to the knobs this engine has.
+"""
+from __future__ import annotations
+
+import argparse
+import logging
+import sys
+from dataclasses import replace
+from typing import List, Optional
+
+
+def build_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(prog="hipengine-b200 serve", description="OpenAI-compatible server on sm_100a")
+    ap.add_argument("--model", required=True, help="GGUF file / directory, or a built-in random-init geometry name")
+    ap.add_argument("--backend", default="auto", choices=["auto", "cuda_sm100a", "cpu_reference"])
+    ap.add_argument("--execution-profile", default="production", choices=["strict", "production", "batch_invariant", "fast"])
+    ap.add_argument("--served-model-name", default=None)
+    ap.add_argument("--api-key", default=None)
+    ap.add_argument("--host", default="127.0.0.1")
+    ap.add_argument("--port", type=int, default=8000)
+    ap.add_argument("--log-level", default="info")
+    ap.add_argument("--eager-load", action="store_true", help="load weights and reserve KV before accepting traffic")
+    ap.add_argument("--startup-chat-smoke", action="store_true", help="run one tiny chat request at startup")
+    ap.add_argument("--max-context-tokens", type=int, default=8192)
+    ap.add_argument("--max-active-requests", type=int, default=8)
+    ap.add_argument("--max-queued-requests", type=int, default=256)
+    ap.add_argument("--max-pending-requests", type=int, default=1024)
+    ap.add_argument("--max-chat-sessions", type=int, default=256)
+    ap.add_argument("--chat-default-max-tokens", type=int, default=4096)
+    ap.add_argument("--request-timeout-ms", type=int, default=None)
+    ap.add_argument("--stream-queue-max-chunks", type=int, default=16)
+    ap.add_argument("--shutdown-grace-seconds", type=float, default=5.0)
+    ap.add_argument("--kv-storage", default="bf16", choices=["bf16"])
+    ap.add_argument("--kv-pool-pages", type=int, default=None)
+    ap.add_argument("--prefix-cache", default="radix", choices=["off", "radix"])
+    ap.add_argument("--prefix-snapshot-interval", type=int, default=2048)
+    ap.add_argument("--prefix-max-snapshots", type=int, default=16)
+    ap.add_argument("--prefill-decode-policy", default="protect_decode",
+                    choices=["protect_decode", "protect_ttft", "fair", "token_budget"])
+    ap.add_argument("--max-prefill-chunk-tokens", type=int, default=4096)
+    ap.add_argument("--round-prefill-token-budget", type=int, default=4096)
+    ap.add_argument("--round-decode-row-budget", type=int, default=64)
+    ap.add_argument("--fair-prefill-burst-chunks", type=int, default=1)
+    ap.add_argument("--speculative-mtp-serving", default="off", choices=["off", "auto", "on"])
+    ap.add_argument("--speculative-candidate-budget", type=int, default=3)
+    ap.add_argument("--tensor-parallel", type=int, default=1)
+    ap.add_argument("--expert-parallel", type=int, default=1)
+    ap.add_argument("--no-cuda-graphs", action="store_true")
+    ap.add_argument("--metrics", default=None, choices=["prometheus"])
+    ap.add_argument("--info", action="store_true", help="print the resolved configuration and exit")
+    return ap
+
+
+def configs_from_args(a):
+    from ..config import EngineConfig, KVConfig, SchedulerConfig
+    from .api import ServerConfig
+    eng = EngineConfig(
+        max_sequence_length=a.max_context_tokens, use_cuda_graphs=not a.no_cuda_graphs,
+        scheduler=SchedulerConfig(policy=a.prefill_decode_policy, max_prefill_chunk_tokens=a.max_prefill_chunk_tokens,
+                                  round_prefill_token_budget=a.round_prefill_token_budget,
+                                  round_decode_row_budget=a.round_decode_row_budget,
+                                  fair_prefill_burst_chunks=a.fair_prefill_burst_chunks,
+                                  max_pending_requests=a.max_pending_requests,
+                                  max_active_requests=a.max_active_requests,
+                                  stream_mailbox=max(16, a.stream_queue_max_chunks * 4)),
+        kv=KVConfig(storage=a.kv_storage, pool_pages=a.kv_pool_pages, prefix_cache=a.prefix_cache,
+                    snapshot_interval_tokens=a.prefix_snapshot_interval, max_snapshots=a.prefix_max_snapshots))
+    srv = ServerConfig(served_model_name=a.served_model_name or str(a.model).rstrip("/").split("/")[-1],
+                       api_key=a.api_key, chat_default_max_tokens=a.chat_default_max_tokens,
+                       max_queued_requests=a.max_queued_requests, request_timeout_ms=a.request_timeout_ms,
+                       stream_queue_max_chunks=a.stream_queue_max_chunks, metrics=a.metrics,
+                       max_chat_sessions=a.max_chat_sessions, shutdown_grace_seconds=a.shutdown_grace_seconds)
+    srv.validate()
+    return eng, srv
+
+
+def main(argv: Optional[List[str]] = None) -> int:
+    a = build_parser().parse_args(argv)
+    eng, srv = configs_from_args(a)
+    if a.info:
+        import json
+        from dataclasses import asdict
+        print(json.dumps({"engine": asdict(eng), "server": asdict(srv)}, indent=1, default=str))
+        return 0
+    logging.basicConfig(level=a.log_level.upper(), format="%(asctime)s %(levelname)s %(name)s: %(message)s")
+    log = logging.getLogger("hipengine_b200.server")
+    from ..llm import LLM
+    from .api import create_app
+    import time
+    t0 = time.time()
+    llm = LLM(a.model, backend=a.backend, execution_profile=a.execution_profile,
+              max_active_requests=a.max_active_requests, max_sequence_length=a.max_context_tokens,
+              prefix_cache=a.prefix_cache, speculative_mtp_serving=a.speculative_mtp_serving,
+              speculative_candidate_budget=a.speculative_candidate_budget, tensor_parallel=a.tensor_parallel,
+              expert_parallel=a.expert_parallel, engine_config=eng)
+    if a.eager_load or a.startup_chat_smoke:
+        info = llm.prepare()
+        log.info("LOAD_TIMING prepare=%.2fs capacity=%s", time.time() - t0, info)
+    if a.startup_chat_smoke:
+        from ..llm import SamplingParams
+        out = llm.chat([{"role": "user", "content": "ping"}], SamplingParams(max_tokens=4))
+        log.info("startup chat smoke: %d tokens, finish=%s", len(out.token_ids), out.finish.reason)
+    app = create_app(llm, srv)
+    import uvicorn
+    uvicorn.run(app, host=a.host, port=a.port, log_level=a.log_level)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

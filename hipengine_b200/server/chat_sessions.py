@@ -59,6 +59,7 @@ class ChatSessionStore:
                 oldest = min(self.sessions.values(), key=lambda s: s.updated)
                 del self.sessions[oldest.id]
             s = ChatSession(sid or "sess_" + uuid.uuid4().hex[:20], copy.deepcopy(messages or []))
+            s.turns = sum(1 for m in s.messages if m.get("role") == "assistant")
             self.sessions[s.id] = s
             return s
 

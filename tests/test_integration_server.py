@@ -1,0 +1,148 @@
+"""FastAPI TestClient over the real engine on the CPU reference backend (tiny random-init model)."""
+import json
+
+import pytest
+
+fastapi = pytest.importorskip("fastapi")
+from fastapi.testclient import TestClient  # noqa: E402
+
+from hipengine_b200 import LLM  # noqa: E402
+from hipengine_b200.loading.synth import build_random_model  # noqa: E402
+from hipengine_b200.models.config import TINY_DENSE  # noqa: E402
+from hipengine_b200.server.api import ServerConfig, create_app  # noqa: E402
+
+
+@pytest.fixture(scope="module")
+def client():
+    w = build_random_model(TINY_DENSE, seed=0)
+    llm = LLM(w, backend="cpu_reference", max_active_requests=4, max_sequence_length=512)
+    app = create_app(llm, ServerConfig(served_model_name="tiny", api_key="k", metrics="prometheus",
+                                       chat_default_max_tokens=12))
+    with TestClient(app) as c:
+        c.headers.update({"Authorization": "Bearer k"})
+        yield c
+
+
+def _sse(resp):
+    out = []
+    for line in resp.iter_lines():
+        if line.startswith("data: "):
+            d = line[6:]
+            out.append(d if d == "[DONE]" else json.loads(d))
+    return out
+
+
+def test_health_ready_models_auth(client):
+    assert client.get("/health").json() == {"status": "ok"}
+    assert client.get("/ready").status_code == 200
+    assert client.get("/v1/models").json()["data"][0]["id"] == "tiny"
+    r = client.get("/v1/models", headers={"Authorization": "Bearer wrong"})
+    assert r.status_code == 401 and r.json()["error"]["code"] == "unauthorized"
+    r = client.post("/v1/completions", json={"model": "other", "prompt": "hi"})
+    assert r.status_code == 404 and r.json()["error"]["hipengine"]["code"] == "model_unavailable"
+
+
+def test_completions_shapes_and_logprobs(client):
+    r = client.post("/v1/completions", json={"prompt": "hello", "max_tokens": 5, "temperature": 0, "logprobs": 2,
+                                             "ignore_eos": True})
+    body = r.json()
+    assert r.status_code == 200 and body["object"] == "text_completion"
+    ch = body["choices"][0]
+    assert ch["finish_reason"] == "length" and len(ch["logprobs"]["tokens"]) == 5
+    assert body["usage"]["completion_tokens"] == 5 and body["usage"]["prompt_tokens"] == 5
+    r = client.post("/v1/completions", json={"prompt": ["a", "b"], "n": 2, "max_tokens": 2, "temperature": 0})
+    assert len(r.json()["choices"]) == 4
+    r = client.post("/v1/completions", json={"prompt": [1, 2, 3], "max_tokens": 2, "echo": True, "temperature": 0})
+    assert r.status_code == 200
+
+
+def test_completion_streaming_matches_blocking(client):
+    req = {"prompt": "stream me", "max_tokens": 6, "temperature": 0, "ignore_eos": True}
+    full = client.post("/v1/completions", json=req).json()["choices"][0]["text"]
+    with client.stream("POST", "/v1/completions", json=dict(req, stream=True,
+                                                            stream_options={"include_usage": True})) as r:
+        ev = _sse(r)
+    assert ev[-1] == "[DONE]"
+    text = "".join(e["choices"][0]["text"] for e in ev[:-1] if e.get("choices"))
+    assert text == full
+    assert ev[-2]["choices"] == [] and ev[-2]["usage"]["completion_tokens"] == 6
+
+
+def test_chat_completion_and_stream(client):
+    req = {"messages": [{"role": "system", "content": "s"}, {"role": "user", "content": "hi"}], "max_tokens": 8,
+           "temperature": 0, "enable_thinking": False, "ignore_eos": True}
+    r = client.post("/v1/chat/completions", json=req)
+    body = r.json()
+    assert r.status_code == 200 and body["choices"][0]["message"]["role"] == "assistant"
+    with client.stream("POST", "/v1/chat/completions", json=dict(req, stream=True,
+                       stream_options={"include_usage": True, "include_hipengine": True})) as r2:
+        ev = _sse(r2)
+    assert ev[0]["choices"][0]["delta"]["role"] == "assistant"
+    text = "".join(e["choices"][0]["delta"].get("content", "") for e in ev if isinstance(e, dict) and e.get("choices"))
+    assert text.strip() == (body["choices"][0]["message"]["content"] or "").strip()
+    finals = [e for e in ev if isinstance(e, dict) and e.get("choices") and e["choices"][0]["finish_reason"]]
+    assert finals and finals[-1]["choices"][0]["finish_reason"] == "length"
+    assert finals[-1]["hipengine"]["phase"] == "done"
+
+
+def test_chat_validation_errors(client):
+    r = client.post("/v1/chat/completions", json={"messages": []})
+    assert r.status_code == 400
+    r = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "x"}], "grammar": "root ::= x"})
+    assert r.status_code == 400 and r.json()["error"]["code"] == "unsupported_parameter"
+    r = client.post("/v1/chat/completions", json={"messages": [{"role": "tool", "content": "x"}]})
+    assert r.status_code == 400
+    r = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "x"}], "top_logprobs": 3})
+    assert r.status_code == 400
+    r = client.post("/v1/completions", json={"prompt": "x" * 600, "max_tokens": 50})
+    assert r.status_code == 400 and r.json()["error"]["code"] == "context_overflow"
+
+
+def test_structured_output_violation_is_reported(client):
+    r = client.post("/v1/chat/completions", json={
+        "messages": [{"role": "user", "content": "json please"}], "max_tokens": 6, "temperature": 0,
+        "enable_thinking": False,
+        "response_format": {"type": "json_schema", "json_schema": {"schema": {"type": "object", "required": ["a"]}}}})
+    ch = r.json()["choices"][0]
+    assert r.status_code == 200
+    # a random-init model does not emit valid JSON: the server must say so instead of returning garbage
+    assert ch["finish_details"]["reason"] == "schema_violation" and not ch["message"]["content"]
+
+
+def test_tools_required_not_satisfied(client):
+    tools = [{"type": "function", "function": {"name": "get_time", "parameters": {"type": "object"}}}]
+    r = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "time?"}], "tools": tools,
+                                                  "tool_choice": "required", "max_tokens": 4, "temperature": 0,
+                                                  "enable_thinking": False})
+    assert r.json()["choices"][0]["finish_details"]["reason"] == "tool_required_not_satisfied"
+    r = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "x"}], "tools": tools,
+                                                  "tool_choice": {"type": "function", "function": {"name": "nope"}}})
+    assert r.status_code == 400
+
+
+def test_sessions_and_tokenize_and_metrics(client):
+    r = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "a"}], "max_tokens": 3,
+                                                  "temperature": 0, "session": {"create": True},
+                                                  "enable_thinking": False})
+    sid = r.json()["session"]["id"]
+    r = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "b"}], "max_tokens": 3,
+                                                  "temperature": 0, "continuation_id": sid, "enable_thinking": False})
+    assert r.status_code == 200
+    lst = client.get("/v1/hipengine/sessions").json()["sessions"]
+    assert any(s["id"] == sid and s["turns"] == 2 for s in lst)
+    fork = client.post(f"/v1/hipengine/sessions/{sid}/fork").json()["id"]
+    rb = client.post(f"/v1/hipengine/sessions/{fork}/rollback", json={"turns": 1}).json()
+    assert rb["turns"] == 1
+    snap = client.get(f"/v1/hipengine/sessions/{sid}/snapshot").json()
+    assert snap["schema"].endswith("v1")
+    assert client.post("/v1/hipengine/sessions/restore", json=snap).status_code == 200
+    assert client.delete(f"/v1/hipengine/sessions/{sid}").json()["deleted"]
+    r = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "b"}], "continuation_id": sid})
+    assert r.status_code in (400, 410)
+    t = client.post("/v1/hipengine/tokenize", json={"text": "abc"}).json()
+    assert client.post("/v1/hipengine/detokenize", json={"tokens": t["tokens"]}).json()["text"] == "abc"
+    assert client.post("/v1/hipengine/fit_context", json={"text": "abc"}).json()["fits"]
+    m = client.get("/metrics").text
+    assert "he_engine_decode_tokens_total" in m and "he_http_requests_total" in m
+    caps = client.get("/v1/hipengine/capabilities").json()
+    assert caps["features"]["tools"] and caps["limits"]["top_logprobs"] == 20
