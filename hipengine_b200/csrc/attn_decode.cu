@@ -252,3 +252,44 @@ HE_API int he_attn_decode(const AttnDecArgs* args, cudaStream_t stream) {
   return 0;
 }
 HE_API int he_attn_dec_args_size() { return (int)sizeof(AttnDecArgs); }
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free variant (declared in attn_decode_noalloc.h; no counterpart in the reference engine).
+// The split-K partials go to a fixed array inside this module's device image instead of a caller
+// buffer, for callers that must not allocate: during or between stream captures, when the KV pool
+// owns all remaining device memory, or when calling the C symbols without a tensor framework.
+// One array per device, shared by all calls: calls that may overlap on the device race on it.
+#include "attn_decode_noalloc.h"
+
+static __device__ __align__(256) float g_noalloc_partial[HE_ATTN_NOALLOC_MAX_FLOATS];
+
+namespace {
+constexpr int NOALLOC_MAX_DEVICES = 64;
+float* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {};  // address of g_noalloc_partial on each device, once looked up
+}  // namespace
+
+HE_API long long he_attn_decode_noalloc_capacity(void) { return (long long)HE_ATTN_NOALLOC_MAX_FLOATS; }
+
+HE_API int he_attn_decode_noalloc(const AttnDecArgs* args, cudaStream_t stream) {
+  if (args == nullptr) return -HE_ERR_BAD_ARG;
+  if (args->R <= 0) return 0;
+  if (args->H <= 0 || args->max_splits <= 0 || args->D <= 0) return -HE_ERR_BAD_ARG;
+  const unsigned long long need =
+      (unsigned long long)args->R * args->H * (unsigned long long)args->max_splits * (unsigned long long)(args->D + 2);
+  if (need > (unsigned long long)HE_ATTN_NOALLOC_MAX_FLOATS) return -HE_ERR_BAD_ARG;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return -HE_ERR_BAD_ARG;
+  if (g_noalloc_ptr[dev] == nullptr) {
+    // Set-up, once per device with that device current.  Do this before any stream capture begins.
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress((void**)&ptr, g_noalloc_partial);
+    if (e != cudaSuccess) return (int)e;
+    if (ptr == nullptr) return (int)cudaErrorInvalidSymbol;
+    g_noalloc_ptr[dev] = ptr;
+  }
+  AttnDecArgs a = *args;
+  a.partial = g_noalloc_ptr[dev];
+  return he_attn_decode(&a, stream);
+}
