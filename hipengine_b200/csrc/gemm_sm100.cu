@@ -32,6 +32,9 @@ struct GemmArgs {
   int M, N, K;
   int epi;              // 0: bf16 store, 1: fp32 store, 2: fp32 += (C is fp32, in place)
   int* status;
+  // grouped mode (MoE experts): M-tile tm multiplies rows [tm*BM, +BM) of A with the weight block
+  // B[tile_group[tm] * N .. +N); a negative group marks an unused tile.  Null for a plain GEMM.
+  const int* tile_group;
 };
 
 struct __align__(8) Barriers {
@@ -85,6 +88,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t it = 0;
       for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
         const int tm = tile % tiles_m, tn = tile / tiles_m;
+        int b_row0 = tn * BN;
+        if (g.tile_group != nullptr) {
+          const int grp = __ldg(g.tile_group + tm);
+          if (grp < 0) continue;
+          b_row0 += grp * g.N;
+        }
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -92,7 +101,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           mbar_expect_tx(&bar->full[s], STAGE_BYTES);
           uint8_t* sa = smem + s * STAGE_BYTES;
           tma_load_2d(sa, &tmA, &bar->full[s], kb * BK, tm * BM);
-          tma_load_2d(sa + A_BYTES, &tmB, &bar->full[s], kb * BK, tn * BN);
+          tma_load_2d(sa + A_BYTES, &tmB, &bar->full[s], kb * BK, b_row0);
         }
         if (*abort_flag) break;
       }
@@ -102,7 +111,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (elect_one()) {
       constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
       uint32_t it = 0, tcount = 0;
-      for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tcount) {
+      for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+        if (g.tile_group != nullptr && __ldg(g.tile_group + tile % tiles_m) < 0) continue;
         const int acc = tcount & 1;
         const uint32_t acc_ph = (tcount >> 1) & 1;
         if (!mbar_wait(&bar->acc_empty[acc], acc_ph ^ 1, abort_flag, g.status, 102)) break;
@@ -125,14 +135,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         if (*abort_flag) break;
         umma_commit(&bar->acc_full[acc]);
+        ++tcount;
       }
     }
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5)
     const int q = warp & 3;              // TMEM lane quarter this warp may touch
     uint32_t tcount = 0;
-    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tcount) {
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
       const int tm = tile % tiles_m, tn = tile / tiles_m;
+      if (g.tile_group != nullptr && __ldg(g.tile_group + tm) < 0) continue;
       const int acc = tcount & 1;
       const uint32_t acc_ph = (tcount >> 1) & 1;
       if (!mbar_wait(&bar->acc_full[acc], acc_ph, abort_flag, g.status, 104)) break;
@@ -178,6 +190,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar->acc_empty[acc]);
+      ++tcount;
     }
   }
 
@@ -238,6 +251,7 @@ HE_API int he_gemm_bf16(const void* A, long long lda, const void* B, long long l
   if (rc != 0) return rc;
   GemmArgs g;
   g.C = C; g.ldc = ldc; g.resid = nullptr; g.M = M; g.N = N; g.K = K; g.epi = epi; g.status = (int*)status;
+  g.tile_group = nullptr;
   const size_t smem = STAGES * STAGE_BYTES + sizeof(Barriers) + 1024;
   static bool configured = false;
   if (!configured) {
@@ -245,6 +259,32 @@ HE_API int he_gemm_bf16(const void* A, long long lda, const void* B, long long l
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int grid = tiles < num_sms ? tiles : num_sms;
+  gemm_bf16_kernel<<<grid, NTHREADS, smem, stream>>>(tmA, tmB, g);
+  HE_LAUNCH_CHECK();
+  return 0;
+}
+
+// Grouped GEMM for MoE experts: rows [tm*128, +128) of A use weight block B[tile_group[tm]*N .. +N) of the
+// stacked matrix B[n_groups*N][K]; tile_group (device, ceil(M/128) ints) holds -1 for unused tiles, which are
+// skipped.  C[M][N] rows follow A.  M is the padded upper bound of sorted rows.
+HE_API int he_gemm_bf16_grouped(const void* A, long long lda, const void* B, long long ldb, void* C, long long ldc,
+                                int M, int N, int K, int n_groups, const int* tile_group, int epi, void* status,
+                                int num_sms, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || n_groups <= 0) return 0;
+  if (K % 8 != 0 || tile_group == nullptr) return -HE_ERR_BAD_ARG;
+  CUtensorMap tmA, tmB;
+  int rc = make_map(&tmA, A, M, K, lda, BM);
+  if (rc != 0) return rc;
+  rc = make_map(&tmB, B, (long long)n_groups * N, K, ldb, BN);
+  if (rc != 0) return rc;
+  GemmArgs g;
+  g.C = C; g.ldc = ldc; g.resid = nullptr; g.M = M; g.N = N; g.K = K; g.epi = epi; g.status = (int*)status;
+  g.tile_group = tile_group;
+  const size_t smem = STAGES * STAGE_BYTES + sizeof(Barriers) + 1024;
+  cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < num_sms ? tiles : num_sms;
   gemm_bf16_kernel<<<grid, NTHREADS, smem, stream>>>(tmA, tmB, g);

@@ -42,3 +42,21 @@ def gemm_quant(x: torch.Tensor, w: DeviceWeight, out: torch.Tensor, scratch, row
     wb = scratch.get("gemm_deq", (rows, w.n_cols), torch.bfloat16)
     dequant_bf16(w, wb, row0=row0, rows=rows)
     return gemm_bf16(x, wb, out, epi)
+
+
+def gemm_bf16_grouped(a_sorted: torch.Tensor, w_stacked: torch.Tensor, out: torch.Tensor, n_groups: int,
+                      tile_group: torch.Tensor, epi: Optional[int] = None) -> torch.Tensor:
+    """Grouped GEMM for MoE experts: 128-row tile ``tm`` of ``a_sorted`` multiplies expert ``tile_group[tm]``'s
+    block of ``w_stacked`` ([n_groups * N, K]); tiles marked -1 are skipped."""
+    M, K = a_sorted.shape
+    Nn = w_stacked.shape[0] // n_groups
+    assert w_stacked.shape[1] == K and tile_group.numel() >= (M + 127) // 128
+    if epi is None:
+        epi = 0 if out.dtype == torch.bfloat16 else 1
+    st = status_word(a_sorted.device)
+    N.check(N.lib().he_gemm_bf16_grouped(
+        C.c_void_p(a_sorted.data_ptr()), C.c_longlong(a_sorted.stride(0)), C.c_void_p(w_stacked.data_ptr()),
+        C.c_longlong(w_stacked.stride(0)), C.c_void_p(out.data_ptr()), C.c_longlong(out.stride(0)), C.c_int(M),
+        C.c_int(Nn), C.c_int(K), C.c_int(n_groups), C.c_void_p(tile_group.data_ptr()), C.c_int(epi),
+        C.c_void_p(st.data_ptr()), C.c_int(N.num_sms()), _stream()), "he_gemm_bf16_grouped")
+    return out

@@ -69,6 +69,13 @@ class _AttnDecArgs(C.Structure):
                 ("scale", C.c_float)]
 
 
+class _MoeSelArgs(C.Structure):
+    _fields_ = [("x", c_vp), ("ldx", c_ll), ("norm_w", c_vp), ("eps", C.c_float), ("ids", c_vp), ("wts", c_vp),
+                ("w1", c_vp), ("w2", c_vp), ("qtype1", C.c_int), ("qtype2", C.c_int),
+                ("T", C.c_int), ("k", C.c_int), ("K", C.c_int), ("N", C.c_int), ("act", C.c_int),
+                ("out", c_vp), ("ldo", c_ll), ("rows_per_cta", C.c_int)]
+
+
 _CHECKED = False
 
 
@@ -80,7 +87,7 @@ def _check_abi() -> None:
     L = N.lib()
     pairs = [("he_gemv_args_size", _GemvArgs), ("he_qkv_args_size", _QkvArgs), ("he_conv_args_size", _ConvArgs),
              ("he_gdn_prep_args_size", _GdnPrepArgs), ("he_gdn_scan_args_size", _GdnScanArgs),
-             ("he_attn_dec_args_size", _AttnDecArgs)]
+             ("he_attn_dec_args_size", _AttnDecArgs), ("he_moe_sel_args_size", _MoeSelArgs)]
     for fn, st in pairs:
         got = getattr(L, fn)()
         if got != C.sizeof(st):
@@ -369,6 +376,76 @@ def attn_decode(q: torch.Tensor, gate: Optional[torch.Tensor], kv_cache: torch.T
     a.split_len, a.max_splits, a.window, a.scale = split_len, max_splits, window, scale
     assert partial.numel() >= attn_decode_scratch_floats(a.R, H, max_splits, D)
     N.check(N.lib().he_attn_decode(C.byref(a), _stream()), "he_attn_decode")
+
+
+# ----------------------------------------------------------------------------- mixture of experts
+
+def moe_route(logits: torch.Tensor, k: int, ids: torch.Tensor, wts: torch.Tensor, n_experts: Optional[int] = None,
+              mode: int = 0, expert_scale: Optional[torch.Tensor] = None) -> None:
+    """logits fp32 [T, >=E] (row stride allowed) -> ids int32 [T, k], wts fp32 [T, k]."""
+    T = logits.shape[0]
+    E = logits.shape[1] if n_experts is None else n_experts
+    N.check(N.lib().he_moe_route(c_vp(logits.data_ptr()), c_ll(logits.stride(0)), C.c_int(T), C.c_int(E), C.c_int(k),
+                                 C.c_int(mode), c_vp(_p(expert_scale)), c_vp(ids.data_ptr()), c_vp(wts.data_ptr()),
+                                 _stream()), "he_moe_route")
+
+
+def moe_sorted_rows_bound(P: int, E: int) -> int:
+    return ((P + 127) // 128 + E) * 128
+
+
+def moe_group(ids: torch.Tensor, E: int, pos: torch.Tensor, tile_group: torch.Tensor, meta: torch.Tensor) -> None:
+    N.check(N.lib().he_moe_group(c_vp(ids.data_ptr()), C.c_int(ids.numel()), C.c_int(E), c_vp(pos.data_ptr()),
+                                 c_vp(tile_group.data_ptr()), C.c_int(tile_group.numel()), c_vp(meta.data_ptr()),
+                                 _stream()), "he_moe_group")
+
+
+def moe_gather(x: torch.Tensor, pos: torch.Tensor, k: int, sorted_rows: torch.Tensor) -> None:
+    N.check(N.lib().he_moe_gather(c_vp(x.data_ptr()), c_ll(x.stride(0)), c_vp(pos.data_ptr()), C.c_int(pos.numel()),
+                                  C.c_int(k), C.c_int(x.shape[1]), c_vp(sorted_rows.data_ptr()),
+                                  c_ll(sorted_rows.stride(0)), _stream()), "he_moe_gather")
+
+
+def moe_combine(h: torch.Tensor, y: torch.Tensor, pos: torch.Tensor, wts: torch.Tensor, k: int,
+                ysh: Optional[torch.Tensor] = None, sg: Optional[torch.Tensor] = None) -> None:
+    T, Nn = h.shape
+    N.check(N.lib().he_moe_combine(c_vp(h.data_ptr()), c_ll(h.stride(0)), c_vp(y.data_ptr()), c_ll(y.stride(0)),
+                                   c_vp(pos.data_ptr()), c_vp(wts.data_ptr()), C.c_int(T), C.c_int(k),
+                                   c_vp(_p(ysh)), c_ll(ysh.stride(0) if ysh is not None else 0), c_vp(_p(sg)),
+                                   c_ll(sg.stride(0) if sg is not None else 0), C.c_int(Nn), _stream()),
+            "he_moe_combine")
+
+
+def moe_scale_rows(act: torch.Tensor, sg: torch.Tensor) -> None:
+    T, Nn = act.shape
+    N.check(N.lib().he_moe_scale_rows(c_vp(act.data_ptr()), c_ll(act.stride(0)), C.c_int(T), C.c_int(Nn),
+                                      c_vp(sg.data_ptr()), c_ll(sg.stride(0)), _stream()), "he_moe_scale_rows")
+
+
+def _moe_sel(fn: str, x, norm_w, eps, ids, wts, w1: "DeviceWeight", w2, n_rows: int, out, act: str) -> None:
+    _check_abi()
+    a = _MoeSelArgs()
+    a.x, a.ldx, a.norm_w, a.eps = x.data_ptr(), x.stride(0), _p(norm_w), eps
+    a.ids, a.wts = ids.data_ptr(), wts.data_ptr()
+    a.w1, a.qtype1 = w1.ptr, w1.qtype
+    a.w2, a.qtype2 = (w2.ptr, w2.qtype) if w2 is not None else (None, w1.qtype)
+    a.T, a.k, a.K, a.N = ids.shape[0], ids.shape[1], w1.n_cols, n_rows
+    a.act = 0 if act == "silu" else 1
+    a.out, a.ldo = out.data_ptr(), out.stride(0)
+    N.check(getattr(N.lib(), fn)(C.byref(a), _stream()), fn)
+
+
+def moe_gateup_sel(h: torch.Tensor, norm_w: Optional[torch.Tensor], eps: float, ids: torch.Tensor,
+                   wts: torch.Tensor, w_gate: "DeviceWeight", w_up: "DeviceWeight", n_ff: int, out: torch.Tensor,
+                   act: str = "silu") -> None:
+    """out[t*k+j, :] = act(Wg[e] xn_t) * (Wu[e] xn_t) (bf16) for the selected experts e = ids[t, j]."""
+    _moe_sel("he_moe_gateup_sel", h, norm_w, eps, ids, wts, w_gate, w_up, n_ff, out, act)
+
+
+def moe_down_sel(act_rows: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_down: "DeviceWeight", n_out: int,
+                 h: torch.Tensor) -> None:
+    """h[t, :] += sum_j wts[t, j] * Wd[ids[t, j]] act_rows[t*k+j, :]  (fp32 residual, in place)."""
+    _moe_sel("he_moe_down_sel", act_rows, None, 0.0, ids, wts, w_down, None, n_out, h, "silu")
 
 
 # ----------------------------------------------------------------------------- sampling
