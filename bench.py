@@ -1,5 +1,6 @@
 """Headline benchmark: dense hybrid 27B decoder, GGUF Q4_K_M weights, bf16 KV, batch 1,
-4096-token prefill then 256 decode tokens, tensor-parallel over N GPUs of one node.
+4096-token prefill then 256 decode tokens.  With N GPUs: one replica and one request stream per GPU (the
+headline, weak scaling), plus the same request as a single stream sharded tensor-parallel over the N GPUs.
 
 One "step" is one complete request (prefill + decode).  `value` is decode tokens/s (whole job); prefill
 tokens/s, TTFT and ITL are reported beside it.  Weights are random N(0, 0.02) quantized on the device
@@ -100,6 +101,11 @@ def main() -> int:
     ap.add_argument("--model", default="qwen35-27b")
     ap.add_argument("--prompt-len", type=int, default=4096)
     ap.add_argument("--gen-len", type=int, default=256)
+    ap.add_argument("--parallelism", default="dp", choices=["dp", "tp"],
+                    help="N > 1: dp = one replica and one request stream per GPU (weak scaling, the headline); "
+                         "tp = one request stream sharded over the GPUs (strong scaling)")
+    ap.add_argument("--tp-comm", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--no-tp-extra", action="store_true", help="N > 1, dp: skip the extra tensor-parallel measurement")
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the layer stack (marks the run invalid)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graphs", action="store_true")
@@ -115,15 +121,10 @@ def main() -> int:
     from hipengine_b200.loading.synth import build_random_model
     from hipengine_b200.models.config import NAMED_CONFIGS
     from hipengine_b200.ops import kernels as K
+    from hipengine_b200.parallel.groups import init_distributed
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+    ctx = init_distributed()
+    world, rank, local_rank, dev = ctx.world, ctx.rank, ctx.local_rank, ctx.device
     if not native.lib_available():
         raise SystemExit("native library missing: run `python -c 'import __graft_entry__ as g; g.build()'` first")
 
@@ -131,102 +132,149 @@ def main() -> int:
     if args.layers:
         cfg = cfg.with_layers(args.layers)
     ctx_max = args.prompt_len + args.gen_len + 16
-    t_build0 = time.time()
-    if world > 1:
-        from hipengine_b200.parallel.tp import build_tp_executor
-        ex = build_tp_executor(cfg, seed=0, device=dev, max_slots=1, max_context=ctx_max)
-    else:
-        from hipengine_b200.models.executor import HybridExecutor
-        weights = build_random_model(cfg, seed=0, device=dev, recipe="q4_k_m")
-        ex = HybridExecutor(weights, device=dev, max_slots=1, max_context=ctx_max)
-        del weights
-    from hipengine_b200.models.decode_graph import DecodeGraphRunner
-    runner = DecodeGraphRunner(ex, max_rows=1, use_graphs=not args.no_graphs)
-    torch.cuda.synchronize()
-    build_s = time.time() - t_build0
-
-    gen = torch.Generator().manual_seed(1234)
+    mode = args.parallelism if world > 1 else "single"
+    gen = torch.Generator().manual_seed(1234 + (rank if mode == "dp" else 0))
     prompts = [torch.randint(0, cfg.vocab, (args.prompt_len,), generator=gen).tolist()
                for _ in range(args.steps + args.warmup)]
+    from hipengine_b200.models.decode_graph import DecodeGraphRunner
 
-    def one_request(prompt, ev):
-        ex.reset_slot(0)
-        ev[0].record()
-        logits = ex.prefill(0, prompt)
-        ex.greedy(logits, runner.next_ids[:1])
-        runner.slot[:1].zero_()
-        runner.pos[:1].fill_(len(prompt) - 1)
-        runner.ctx_len[:1].fill_(len(prompt))
-        runner.publish(1)                       # first token -> tokens[0], pos -> len(prompt)
-        ev[1].record()
-        for _ in range(args.gen_len - 1):
-            runner.step(1, ctx_max)
-        ev[2].record()
+    def build(tp: bool):
+        if tp:
+            from hipengine_b200.parallel.tp import build_tp_executor
+            e = build_tp_executor(cfg, seed=0, device=dev, ctx=ctx, comm=args.tp_comm, max_slots=1,
+                                  max_context=ctx_max)
+        else:
+            from hipengine_b200.models.executor import HybridExecutor
+            weights = build_random_model(cfg, seed=0, device=dev, recipe="q4_k_m")
+            e = HybridExecutor(weights, device=dev, max_slots=1, max_context=ctx_max)
+            del weights
+        return e, DecodeGraphRunner(e, max_rows=1, use_graphs=not args.no_graphs)
 
     def barrier():
-        if world > 1:
-            dist.barrier()
+        ctx.barrier()
         torch.cuda.synchronize()
 
-    mk = lambda: [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-    for i in range(args.warmup):
-        one_request(prompts[i], mk())
-    barrier()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    k0 = K.launch_count()
-    evs = [mk() for _ in range(args.steps)]
-    barrier()
-    t0 = time.time()
-    for i in range(args.steps):
-        one_request(prompts[args.warmup + i], evs[i])
-    barrier()
-    wall_s = time.time() - t0
-    launches = K.launch_count() - k0
-    clocks = sampler.stop() if rank == 0 else {}
+    def measure(ex, runner, n_warm, n_steps, sample_clocks):
+        """n_warm untimed requests, then n_steps timed ones; device times are max over ranks."""
+        def one_request(prompt, ev):
+            ex.reset_slot(0)
+            ev[0].record()
+            logits = ex.prefill(0, prompt)
+            ex.greedy(logits, runner.next_ids[:1])
+            runner.slot[:1].zero_()
+            runner.pos[:1].fill_(len(prompt) - 1)
+            runner.ctx_len[:1].fill_(len(prompt))
+            runner.publish(1)                       # first token -> tokens[0], pos -> len(prompt)
+            ev[1].record()
+            for _ in range(args.gen_len - 1):
+                runner.step(1, ctx_max)
+            ev[2].record()
 
-    prefill_ms = sum(e[0].elapsed_time(e[1]) for e in evs)
-    decode_ms = sum(e[1].elapsed_time(e[2]) for e in evs)
-    t = torch.tensor([prefill_ms, decode_ms], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    prefill_ms, decode_ms = t.tolist()
-    n_dec = (args.gen_len - 1) * args.steps
-    decode_tok_s = n_dec / (decode_ms / 1e3)
-    prefill_tok_s = args.prompt_len * args.steps / (prefill_ms / 1e3)
+        mk = lambda: [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        for i in range(n_warm):
+            one_request(prompts[i % len(prompts)], mk())
+        barrier()
+        sampler = ClockSampler(local_rank)
+        if rank == 0 and sample_clocks:
+            sampler.start()
+        k0 = K.launch_count()
+        evs = [mk() for _ in range(n_steps)]
+        barrier()
+        t0 = time.time()
+        for i in range(n_steps):
+            one_request(prompts[(n_warm + i) % len(prompts)], evs[i])
+        barrier()
+        wall_s = time.time() - t0
+        launches = K.launch_count() - k0
+        clocks = sampler.stop() if (rank == 0 and sample_clocks) else {}
+        K.check_status(dev)
+        t = torch.tensor([sum(e[0].elapsed_time(e[1]) for e in evs), sum(e[1].elapsed_time(e[2]) for e in evs)],
+                         dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        prefill_ms, decode_ms = t.tolist()
+        return {"prefill_ms": prefill_ms, "decode_ms": decode_ms, "wall_s": wall_s, "launches": launches,
+                "clocks": clocks}
+
+    t_build0 = time.time()
+    ex, runner = build(tp=(mode == "tp"))
+    torch.cuda.synchronize()
+    build_s = time.time() - t_build0
+    m = measure(ex, runner, args.warmup, args.steps, True)
+    streams = world if mode == "dp" else 1          # independent request streams in flight
+    n_dec = (args.gen_len - 1) * args.steps * streams
+    decode_tok_s = n_dec / (m["decode_ms"] / 1e3)
+    prefill_tok_s = args.prompt_len * args.steps * streams / (m["prefill_ms"] / 1e3)
 
     e2e = None
-    if not args.no_e2e and rank == 0 and world == 1:
+    if not args.no_e2e and mode != "tp":
         try:
-            e2e = run_e2e(args, cfg, ex, prompts)
+            mine = run_e2e(args, cfg, ex, prompts)
+            # replicas run side by side: tokens add up, the slowest replica sets the time
+            t = torch.tensor([mine["decode_s"], mine["prefill_s"]], dtype=torch.float64, device=dev)
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dec_s, pre_s = t.tolist()
+            e2e = {"value": round(n_dec / dec_s, 3), "unit": "tok/s",
+                   "prefill_tok_s": round(args.prompt_len * args.steps * streams / pre_s, 2),
+                   "h2d_bytes_per_step": mine["h2d_bytes_per_step"] * streams,
+                   "d2h_bytes_per_step": mine["d2h_bytes_per_step"] * streams}
         except Exception as exc:  # the device-timed line must still be printed
             e2e = {"error": f"{type(exc).__name__}: {exc}"}
+            if world > 1:
+                raise
+
+    tp_extra = None
+    if mode == "dp" and not args.no_tp_extra:
+        # the same request as ONE stream sharded over all GPUs (tensor parallel, fused peer-memory reductions)
+        runner.graphs.clear()
+        runner = ex = None
+        torch.cuda.empty_cache()
+        try:
+            ex, runner = build(tp=True)
+            mt = measure(ex, runner, 2, 1, False)
+            tp_extra = {"parallelism": f"tp{world}", "comm": args.tp_comm, "steps": 1, "warmup": 2,
+                        "decode_tok_s": round((args.gen_len - 1) / (mt["decode_ms"] / 1e3), 3),
+                        "prefill_tok_s": round(args.prompt_len / (mt["prefill_ms"] / 1e3), 2),
+                        "itl_ms": round(mt["decode_ms"] / (args.gen_len - 1), 4),
+                        "ttft_ms": round(mt["prefill_ms"], 3)}
+        except Exception as exc:
+            tp_extra = {"error": f"{type(exc).__name__}: {exc}"}
 
     if rank == 0:
+        par = {"single": "single", "dp": f"dp{world}", "tp": f"tp{world}"}[mode]
         line = {
-            "metric": "decode_tok_s (27B dense hybrid Q4_K_M, bf16 KV, batch 1, 4096 prefill + 256 decode)",
+            "metric": "decode_tok_s (27B dense hybrid Q4_K_M, bf16 KV, batch 1 per stream, 4096 prefill + 256 decode)",
             "value": round(decode_tok_s, 3), "unit": "tok/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": round((prefill_ms + decode_ms) / args.steps, 3),
-            "higher_is_better": True, "scaling": "strong",
+            "warmup": args.warmup, "ms_per_step": round((m["prefill_ms"] + m["decode_ms"]) / args.steps, 3),
+            "higher_is_better": True, "scaling": "strong" if mode == "tp" else "weak",
             "vs_baseline": round(decode_tok_s / BASELINE_DECODE_TOK_S, 3), "dtype": "bf16",
             "data": "synthetic (random-init N(0,0.02) weights quantized to Q4_K_M-style GGUF blocks, uniform random prompt ids)",
-            "config": {"model": args.model, "global_batch": 1, "seq_len": args.prompt_len, "gen_len": args.gen_len,
-                       "parallelism": f"tp{world}", "layers": cfg.n_layers, "l2": "inputs larger than L2 (weight stream ~15 GB/step)",
-                       "cuda_graphs": not args.no_graphs},
+            "config": {"model": args.model, "global_batch": streams, "seq_len": args.prompt_len,
+                       "gen_len": args.gen_len, "parallelism": par, "layers": cfg.n_layers,
+                       "l2": "inputs larger than L2 (weight stream ~15 GB/step)", "cuda_graphs": not args.no_graphs},
             "prefill_tok_s": round(prefill_tok_s, 2),
             "prefill_vs_baseline": round(prefill_tok_s / BASELINE_PREFILL_TOK_S, 3),
-            "ttft_ms": round(prefill_ms / args.steps, 3),
-            "itl_ms": round(decode_ms / n_dec, 4),
-            "wall_s": round(wall_s, 3), "build_s": round(build_s, 2),
-            "clocks": clocks, "gpu_launches": int(launches),
+            "ttft_ms": round(m["prefill_ms"] / args.steps, 3),
+            "itl_ms": round(m["decode_ms"] / ((args.gen_len - 1) * args.steps), 4),
+            "wall_s": round(m["wall_s"], 3), "build_s": round(build_s, 2),
+            "clocks": m["clocks"], "gpu_launches": int(m["launches"]) * (world if mode == "dp" else 1),
         }
         if e2e is not None:
             line["e2e"] = e2e
+        if tp_extra is not None:
+            line["tensor_parallel"] = tp_extra
         if args.layers:
             line["invalid"] = "truncated layer stack (debug run)"
         print(json.dumps(line))
     if world > 1:
+        # captured graphs hold library collectives: drop them before the process group goes away
+        import gc
+        if runner is not None:
+            runner.graphs.clear()
+        runner = ex = None
+        gc.collect()
+        barrier()
         dist.destroy_process_group()
     return 0
 
@@ -251,8 +299,7 @@ def run_e2e(args, cfg, ex, prompts):
         h2d += out.telemetry.h2d_bytes
         d2h += out.telemetry.d2h_bytes
     n_dec = (args.gen_len - 1) * args.steps
-    return {"value": round(n_dec / dec_s, 3), "unit": "tok/s",
-            "prefill_tok_s": round(args.prompt_len * args.steps / pre_s, 2),
+    return {"decode_s": dec_s, "prefill_s": pre_s,
             "h2d_bytes_per_step": h2d // args.steps, "d2h_bytes_per_step": d2h // args.steps}
 
 

@@ -223,6 +223,7 @@ int dispatch_g(const AttnDecArgs& a, cudaStream_t stream) {
   switch (a.H / a.Hkv) {
     case 1: return launch_split<D, 1>(a, stream);
     case 2: return launch_split<D, 2>(a, stream);
+    case 3: return launch_split<D, 3>(a, stream);
     case 4: return launch_split<D, 4>(a, stream);
     case 6: return launch_split<D, 6>(a, stream);
     case 8: return launch_split<D, 8>(a, stream);

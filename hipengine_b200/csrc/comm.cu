@@ -1,0 +1,149 @@
+// Peer-memory collectives for tensor-parallel decode: push all-reduce fused with the residual add.
+//
+// Every rank owns one "symmetric" region (same layout on all ranks, mapped into every peer through CUDA IPC):
+//     data  [2 phases][world][max_rows * width] fp32   -- slot (phase, src) is written only by rank `src`
+//     flags [2 phases][world][MAX_CTAS] uint32          -- epoch stamps, one per (phase, src rank, CTA)
+// One call = one kernel on every rank:
+//     1. CTA c copies its slice of the local partial rows into slot (phase, me) of EVERY rank (plain
+//        st.global over NVLink for peers), fences at system scope, then stamps flag (phase, me, c) on every rank;
+//     2. CTA c waits -- bounded -- until the stamps of all ranks for slice c show this call's epoch;
+//     3. CTA c sums the world slots of slice c in rank order (so all ranks compute bit-identical sums and the
+//        replicated residual stream cannot drift apart) and adds the sum to the fp32 residual rows.
+// The epoch lives in device memory and is advanced by the kernel itself, so a captured CUDA graph can be
+// replayed without any host-side argument patching.  Phases alternate per call: a rank can run at most one
+// call ahead of its slowest peer (it needs that peer's stamps to finish a call), so two phases are enough.
+// A wait that runs out records HE_ERR_WAIT_TIMEOUT in the status word and the CTA leaves without touching the
+// residual; the context stays usable and the host sees the failure on its next status check.
+// The reference engine is single-device: no counterpart there.
+#include "common.cuh"
+
+using namespace he;
+
+namespace {
+
+constexpr int COMM_MAX_CTAS = 64;
+constexpr int COMM_MAX_WORLD = 8;
+
+struct CommArgs {
+  float* data[COMM_MAX_WORLD];        // data region of every rank (peer-mapped), indexed by rank
+  uint32_t* flags[COMM_MAX_WORLD];    // flag region of every rank
+  uint32_t* epoch;                    // [COMM_MAX_CTAS] local per-CTA call counters
+  const float* partial;               // [rows][width] local partial products
+  float* resid;                       // [rows][ld_resid] residual stream, updated in place (may be null)
+  float* out;                         // optional: reduced rows stored here instead of / as well as resid
+  long long ld_resid, ld_out;
+  int rows, width, slot_floats;       // slot_floats = max_rows * width
+  int world, rank;
+  int* status;
+  unsigned wait_limit;                // polls before giving up
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float4 ld_cg4(const float* p) {
+  float4 v;
+  asm volatile("ld.global.cg.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+  return v;
+}
+
+__global__ void __launch_bounds__(256) comm_push_reduce_kernel(const CommArgs a) {
+  __shared__ int ok_s;
+  const int c = blockIdx.x, n_cta = gridDim.x;
+  const uint32_t epoch = a.epoch[c] + 1;
+  const int phase = epoch & 1;
+  const int total = a.rows * a.width;              // floats in flight this call (multiple of 4)
+  const int per = (((total + n_cta - 1) / n_cta) + 3) & ~3;
+  const int lo = min(total, c * per), hi = min(total, lo + per);
+  const size_t slot_me = ((size_t)phase * a.world + a.rank) * a.slot_floats;
+  // 1. push my slice to every rank
+  for (int i = lo + threadIdx.x * 4; i < hi; i += blockDim.x * 4) {
+    const float4 v = *reinterpret_cast<const float4*>(a.partial + i);
+    for (int r = 0; r < a.world; ++r) *reinterpret_cast<float4*>(a.data[r] + slot_me + i) = v;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < a.world)
+    st_release_sys(a.flags[threadIdx.x] + ((size_t)phase * a.world + a.rank) * COMM_MAX_CTAS + c, epoch);
+  // 2. bounded wait for every rank's stamp of this slice
+  if (threadIdx.x == 0) ok_s = 1;
+  __syncthreads();
+  if (threadIdx.x < a.world) {
+    const uint32_t* f = a.flags[a.rank] + ((size_t)phase * a.world + threadIdx.x) * COMM_MAX_CTAS + c;
+    unsigned polls = 0;
+    // stamps only grow; "epoch or later" also accepts a peer that is already one call ahead on this phase
+    while ((int)(ld_acquire_sys(f) - epoch) < 0) {
+      if (++polls > a.wait_limit) {
+        ok_s = 0;
+        if (a.status != nullptr) atomicCAS(a.status, 0, HE_ERR_WAIT_TIMEOUT);
+        break;
+      }
+      __nanosleep(64);
+    }
+  }
+  __syncthreads();
+  // 3. reduce in rank order + residual add
+  if (ok_s) {
+    const float* mine = a.data[a.rank] + (size_t)phase * a.world * a.slot_floats;
+    for (int i = lo + threadIdx.x * 4; i < hi; i += blockDim.x * 4) {
+      float4 s = ld_cg4(mine + i);
+      for (int r = 1; r < a.world; ++r) {
+        const float4 v = ld_cg4(mine + (size_t)r * a.slot_floats + i);
+        s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+      }
+      const int row = i / a.width, col = i % a.width;
+      if (a.out != nullptr) *reinterpret_cast<float4*>(a.out + (size_t)row * a.ld_out + col) = s;
+      if (a.resid != nullptr) {
+        float4* hp = reinterpret_cast<float4*>(a.resid + (size_t)row * a.ld_resid + col);
+        float4 h = *hp;
+        h.x += s.x; h.y += s.y; h.z += s.z; h.w += s.w;
+        *hp = h;
+      }
+    }
+  }
+  if (threadIdx.x == 0) a.epoch[c] = epoch;
+}
+
+}  // namespace
+
+// ---- symmetric region management (set-up time only)
+HE_API int he_comm_alloc(long long bytes, void** out) {
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, (size_t)bytes);
+  if (e != cudaSuccess) return (int)e;
+  e = cudaMemset(p, 0, (size_t)bytes);
+  if (e != cudaSuccess) return (int)e;
+  *out = p;
+  return 0;
+}
+HE_API int he_comm_free(void* p) { return (int)cudaFree(p); }
+HE_API int he_comm_ipc_handle_size() { return (int)sizeof(cudaIpcMemHandle_t); }
+HE_API int he_comm_ipc_get(void* p, void* handle_out) {
+  return (int)cudaIpcGetMemHandle(reinterpret_cast<cudaIpcMemHandle_t*>(handle_out), p);
+}
+HE_API int he_comm_ipc_open(const void* handle, void** out) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  return (int)cudaIpcOpenMemHandle(out, h, cudaIpcMemLazyEnablePeerAccess);
+}
+HE_API int he_comm_ipc_close(void* p) { return (int)cudaIpcCloseMemHandle(p); }
+
+HE_API int he_comm_max_ctas() { return COMM_MAX_CTAS; }
+HE_API int he_comm_args_size() { return (int)sizeof(CommArgs); }
+
+// All-reduce of `rows x width` fp32 partial rows over the ranks, fused with resid += sum (and/or out = sum).
+HE_API int he_comm_push_reduce(const CommArgs* args, int n_ctas, cudaStream_t stream) {
+  const CommArgs& a = *args;
+  if (a.rows <= 0) return 0;
+  if (a.world < 1 || a.world > COMM_MAX_WORLD || a.rank < 0 || a.rank >= a.world) return -HE_ERR_BAD_ARG;
+  if (a.width % 4 != 0 || (long long)a.rows * a.width > a.slot_floats) return -HE_ERR_BAD_ARG;
+  if (n_ctas < 1 || n_ctas > COMM_MAX_CTAS) return -HE_ERR_BAD_ARG;
+  comm_push_reduce_kernel<<<n_ctas, 256, 0, stream>>>(a);
+  HE_LAUNCH_CHECK();
+  return 0;
+}

@@ -290,6 +290,24 @@ HE_API int he_resid_add_bf16(void* h, const void* y, long long n, cudaStream_t s
   return 0;
 }
 
+__global__ void resid_add_f32_kernel(float* __restrict__ h, const float* __restrict__ y, long long n) {
+  const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i >= n) return;
+  float4 a = *reinterpret_cast<float4*>(h + i);
+  const float4 b = *reinterpret_cast<const float4*>(y + i);
+  a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+  *reinterpret_cast<float4*>(h + i) = a;
+}
+
+// h[i] += y[i] (fp32, contiguous, n % 4 == 0): residual add after a reduced row-parallel projection
+HE_API int he_resid_add_f32(void* h, const void* y, long long n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (n % 4 != 0) return -HE_ERR_BAD_ARG;
+  resid_add_f32_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, stream>>>((float*)h, (const float*)y, n);
+  HE_LAUNCH_CHECK();
+  return 0;
+}
+
 HE_API int he_qkv_post(const QkvArgs* args, int T, cudaStream_t stream) {
   const QkvArgs& a = *args;
   if (T <= 0) return 0;

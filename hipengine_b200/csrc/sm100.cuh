@@ -71,7 +71,7 @@ __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.p
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-// ---------------------------------------------------------------- TMA (tiled, no multicast)
+// ---------------------------------------------------------------- TMA (tiled, one destination CTA)
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* d) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(d)) : "memory");
 }

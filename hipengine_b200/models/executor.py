@@ -189,6 +189,15 @@ class HybridExecutor:
         torch.matmul(x, wb.t(), out=out)
         return out
 
+    # Row-parallel ("output") projections: h += x @ W^T.  A tensor-parallel executor overrides these two to
+    # reduce the partial products across ranks before the residual add.
+    def _out_small(self, x: torch.Tensor, w: DeviceWeight, h: torch.Tensor) -> None:
+        K.gemv(x, [GemvSegment(w, h, K.EPI_ADD_F32)])
+
+    def _out_big(self, x: torch.Tensor, w: DeviceWeight, h: torch.Tensor, tag: str) -> None:
+        y = self._gemm(x, w, self.scratch.get("y_bf", (x.shape[0], w.n_rows), torch.bfloat16), tag=tag)
+        K.resid_add_bf16(h, y)
+
     # ------------------------------------------------------------------ layers
     def _attention_full(self, i: int, h: torch.Tensor, b: BatchDesc, small: bool) -> None:
         cfg, sc = self.cfg, self.scratch
@@ -217,11 +226,9 @@ class HybridExecutor:
         attn = sc.get("attn_out", (T, H * D), torch.bfloat16)
         self._attend(i, q_out, gate, b, attn)
         if small:
-            K.gemv(attn, [GemvSegment(self.W(i, "attn_output.weight"), h, K.EPI_ADD_F32)])
+            self._out_small(attn, self.W(i, "attn_output.weight"), h)
         else:
-            y = self._gemm(attn, self.W(i, "attn_output.weight"), sc.get("y_bf", (T, cfg.hidden), torch.bfloat16),
-                           tag="o")
-            K.resid_add_bf16(h, y)
+            self._out_big(attn, self.W(i, "attn_output.weight"), h, "o")
 
     def _attend(self, i: int, q_out: torch.Tensor, gate: Optional[torch.Tensor], b: BatchDesc,
                 out: torch.Tensor) -> None:
@@ -285,10 +292,9 @@ class HybridExecutor:
         og = sc.get("gdn_og", (T, inner), torch.bfloat16)
         K.gdn_gated_norm(o, z, self.F(i, "ssm_norm.weight").reshape(-1), og, Hv, S, cfg.rms_eps)
         if small:
-            K.gemv(og, [GemvSegment(self.W(i, "ssm_out.weight"), h, K.EPI_ADD_F32)])
+            self._out_small(og, self.W(i, "ssm_out.weight"), h)
         else:
-            y = self._gemm(og, self.W(i, "ssm_out.weight"), sc.get("y_bf", (T, cfg.hidden), torch.bfloat16), tag="o")
-            K.resid_add_bf16(h, y)
+            self._out_big(og, self.W(i, "ssm_out.weight"), h, "o")
 
     def _ffn(self, i: int, h: torch.Tensor, b: BatchDesc, small: bool) -> None:
         cfg, sc = self.cfg, self.scratch
@@ -304,7 +310,7 @@ class HybridExecutor:
             act = sc.get("ffn_act", (T, Fd), torch.bfloat16)
             K.gemv(h, [GemvSegment(self.W(i, "ffn_gate.weight"), act, epi, self.W(i, "ffn_up.weight"))],
                    norm_w=norm_w, eps=cfg.rms_eps)
-            K.gemv(act, [GemvSegment(self.W(i, "ffn_down.weight"), h, K.EPI_ADD_F32)])
+            self._out_small(act, self.W(i, "ffn_down.weight"), h)
         else:
             xn = sc.get("xn", (T, cfg.hidden), torch.bfloat16)
             K.rmsnorm_rows(h, norm_w, xn, cfg.rms_eps)
@@ -313,8 +319,7 @@ class HybridExecutor:
             self._gemm(xn, self.W(i, "ffn_up.weight"), gu[:, Fd:], tag="g")
             act = sc.get("ffn_act", (T, Fd), torch.bfloat16)
             K.act_mul(gu, act, cfg.act)
-            y = self._gemm(act, self.W(i, "ffn_down.weight"), sc.get("y_bf", (T, cfg.hidden), torch.bfloat16), tag="d")
-            K.resid_add_bf16(h, y)
+            self._out_big(act, self.W(i, "ffn_down.weight"), h, "d")
 
     # ------------------------------------------------------------------ whole model
     def forward(self, b: BatchDesc, journal: Optional[dict] = None, h_out: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -378,6 +378,13 @@ def attn_decode(q: torch.Tensor, gate: Optional[torch.Tensor], kv_cache: torch.T
     N.check(N.lib().he_attn_decode(C.byref(a), _stream()), "he_attn_decode")
 
 
+def resid_add_f32(h: torch.Tensor, y: torch.Tensor) -> None:
+    assert h.dtype == torch.float32 and y.dtype == torch.float32 and h.numel() == y.numel()
+    assert h.is_contiguous() and y.is_contiguous()
+    N.check(N.lib().he_resid_add_f32(c_vp(h.data_ptr()), c_vp(y.data_ptr()), c_ll(h.numel()), _stream()),
+            "he_resid_add_f32")
+
+
 # ----------------------------------------------------------------------------- mixture of experts
 
 def moe_route(logits: torch.Tensor, k: int, ids: torch.Tensor, wts: torch.Tensor, n_experts: Optional[int] = None,
