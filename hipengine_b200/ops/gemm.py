@@ -12,7 +12,7 @@ from typing import Optional
 import torch
 
 from ..core import native as N
-from .kernels import DeviceWeight, _stream, dequant_bf16
+from .kernels import DeviceWeight, _check_device, _stream, dequant_bf16
 
 from .kernels import check_status, status_tensor as status_word  # noqa: E402,F401
 
@@ -20,6 +20,7 @@ from .kernels import check_status, status_tensor as status_word  # noqa: E402,F4
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: Optional[int] = None) -> torch.Tensor:
     """out[M, N] = x[M, K] @ w[N, K]^T.  x, w bf16 (row strides allowed); out bf16 or fp32."""
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    _check_device(x)
     M, K = x.shape
     Nn = w.shape[0]
     assert w.shape[1] == K and x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1

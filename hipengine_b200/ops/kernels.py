@@ -188,6 +188,7 @@ def gemv(x: torch.Tensor, segs: Sequence[GemvSegment], norm_w: Optional[torch.Te
          eps: float = 1e-6) -> None:
     """Fused [RMSNorm] + int8 activation quantize + quantized GEMV + epilogue for 1..8 rows."""
     _check_abi()
+    _check_device(x)
     R, K = x.shape
     a = _GemvArgs()
     for i, s in enumerate(segs):
@@ -254,7 +255,15 @@ def dequant_bf16(w: DeviceWeight, out: Optional[torch.Tensor] = None, row0: int 
     return out
 
 
+def _check_device(t: torch.Tensor) -> None:
+    """Launches go to the calling thread's current device: refuse tensors that live on another GPU."""
+    if t.device.index != torch.cuda.current_device():
+        raise RuntimeError(f"tensor on cuda:{t.device.index} but this thread's current device is "
+                           f"cuda:{torch.cuda.current_device()} (call torch.cuda.set_device in the launching thread)")
+
+
 def embed(w: DeviceWeight, ids: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    _check_device(out)
     assert ids.dtype == torch.int64 and out.dtype == torch.float32
     N.check(N.lib().he_embed(c_vp(w.ptr), C.c_int(w.qtype), c_ll(w.n_rows), C.c_int(w.n_cols), c_vp(ids.data_ptr()),
                              c_vp(out.data_ptr()), C.c_float(scale), C.c_int(ids.numel()), _stream()), "he_embed")
