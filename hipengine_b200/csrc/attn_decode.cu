@@ -54,6 +54,7 @@ __global__ void __launch_bounds__(256) attn_decode_split_kernel(const AttnDecArg
   // ---- phase 1: scores.  8 lanes per key; lane `sub` owns 16-byte chunks sub, sub+8, ...
   {
     const int sub = lane & 7, grp = lane >> 3;
+#pragma unroll 2
     for (int t0 = warp * 4; t0 < n; t0 += NWARP * 4) {
       const int tk = t0 + grp;
       float acc[G];
@@ -127,6 +128,7 @@ __global__ void __launch_bounds__(256) attn_decode_split_kernel(const AttnDecArg
     for (int e = 0; e < CPL * 8; ++e) acc[g][e] = 0.f;
   const int tgrp = NCH >= 32 ? 0 : lane / NCH;
   const int ch0 = NCH >= 32 ? lane : lane % NCH;
+#pragma unroll 2
   for (int t0 = warp * TPS; t0 < n; t0 += NWARP * TPS) {
     const int tk = t0 + tgrp;
     if (tk < n) {
@@ -178,8 +180,11 @@ __global__ void __launch_bounds__(256) attn_decode_split_kernel(const AttnDecArg
   }
 }
 
-// grid (H, R), block D
+// grid (H, R), block D.  Split statistics are staged in shared memory first, so the accumulation over splits
+// is a stream of independent loads instead of a chain of dependent ones.
 __global__ void attn_decode_reduce_kernel(const AttnDecArgs a) {
+  extern __shared__ float wsm[];     // [max_splits] softmax weights of the splits
+  __shared__ float red[33];
   const int h = blockIdx.x, r = blockIdx.y, d = threadIdx.x;
   const int D = a.D;
   const int ctx = a.ctx_len[r];
@@ -187,13 +192,27 @@ __global__ void attn_decode_reduce_kernel(const AttnDecArgs a) {
   const int ns = (ctx - start + a.split_len - 1) / a.split_len;
   const float* pb = a.partial + ((size_t)r * a.H + h) * a.max_splits * (D + 2);
   float m = -INFINITY;
-  for (int s = 0; s < ns; ++s) m = fmaxf(m, pb[(size_t)s * (D + 2) + D]);
-  float num = 0.f, den = 0.f;
-  for (int s = 0; s < ns; ++s) {
-    const float w = __expf(pb[(size_t)s * (D + 2) + D] - m);
-    num += w * pb[(size_t)s * (D + 2) + d];
+  for (int s = d; s < ns; s += blockDim.x) {
+    const float ms = pb[(size_t)s * (D + 2) + D];
+    wsm[s] = ms;
+    m = fmaxf(m, ms);
+  }
+  m = block_max(m, red);
+  float den = 0.f;
+  for (int s = d; s < ns; s += blockDim.x) {
+    const float w = __expf(wsm[s] - m);
+    wsm[s] = w;
     den += w * pb[(size_t)s * (D + 2) + D + 1];
   }
+  den = block_sum(den, red);      // barriers inside also publish wsm[]
+  float n4[4] = {0.f, 0.f, 0.f, 0.f};
+  int s = 0;
+  for (; s + 4 <= ns; s += 4) {
+#pragma unroll
+    for (int u = 0; u < 4; ++u) n4[u] += wsm[s + u] * pb[(size_t)(s + u) * (D + 2) + d];
+  }
+  for (; s < ns; ++s) n4[0] += wsm[s] * pb[(size_t)s * (D + 2) + d];
+  const float num = (n4[0] + n4[1]) + (n4[2] + n4[3]);
   float o = den > 0.f ? num / den : 0.f;
   if (a.gate != nullptr) {
     // the reference rounds the attention output to bf16 before the gate multiply (cpu_reference/ops.py:2250)
@@ -248,7 +267,7 @@ HE_API int he_attn_decode(const AttnDecArgs* args, cudaStream_t stream) {
   }
   if (rc != 0) return rc;
   dim3 grid(a.H, a.R);
-  attn_decode_reduce_kernel<<<grid, a.D, 0, stream>>>(a);
+  attn_decode_reduce_kernel<<<grid, a.D, (size_t)a.max_splits * sizeof(float), stream>>>(a);
   HE_LAUNCH_CHECK();
   return 0;
 }

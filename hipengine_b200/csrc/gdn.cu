@@ -189,6 +189,123 @@ __global__ void gdn_commit_kernel(float* __restrict__ state, const float* __rest
     dst[i] = src[i];
 }
 
+// ---------------------------------------------------------------------------------------------- decode fast path
+// For single-token segments (plain decode) the five kernels conv -> conv state -> prepare -> scan -> gated norm
+// collapse into two launches; a decode step is bound by launch latency, not by this arithmetic.
+struct GdnDecodeArgs {
+  const float* x;         // [R][x_stride] pre-conv projections q | k | v (fp32)
+  long long x_stride;
+  const float* conv_w;    // [C][4]
+  float* conv_state;      // [n_slots][C][3]
+  const float* a;         // [R][a_stride]
+  const float* b;         // [R][b_stride]
+  long long a_stride, b_stride;
+  const float* ssm_a;     // [Hv]
+  const float* dt_bias;   // [Hv]
+  const int* slot;        // [R]
+  float* qkv;             // [R][C] conv output (q, k normalised)
+  float* decay;           // [R][Hv]
+  float* beta;            // [R][Hv]
+  float* state;           // [n_slots][Hv][128][128]
+  const void* z;          // [R][z_stride] gate input
+  int z_dtype;
+  long long z_stride;
+  const float* norm_w;    // [128]
+  __nv_bfloat16* out;     // [R][out_stride]
+  long long out_stride;
+  float eps;
+  int C, G, Hv, R;
+};
+
+// grid (C/128, R), block 128: one channel per thread.  conv(k=4)+SiLU, rolling state shift, L2 norm of q/k heads,
+// and (block 0) the decay / beta gates of the row.
+__global__ void __launch_bounds__(128) gdn_decode_pre_kernel(const GdnDecodeArgs p) {
+  __shared__ float red[32];
+  const int r = blockIdx.y, blk = blockIdx.x, c = blk * 128 + threadIdx.x;
+  float* st = p.conv_state + ((size_t)p.slot[r] * p.C + c) * 3;
+  const float4 w = __ldg(reinterpret_cast<const float4*>(p.conv_w + (size_t)c * 4));
+  const float xv = p.x[(size_t)r * p.x_stride + c];
+  const float s0 = st[0], s1 = st[1], s2 = st[2];
+  float y = silu_f(w.x * s0 + w.y * s1 + w.z * s2 + w.w * xv);
+  st[0] = s1; st[1] = s2; st[2] = xv;
+  if (blk < 2 * p.G) {
+    const float ss = block_sum(y * y, red);
+    float inv = 1.f / fmaxf(sqrtf(ss), 1e-6f);
+    if (blk < p.G) inv *= rsqrtf(128.f);
+    y *= inv;
+  }
+  p.qkv[(size_t)r * p.C + c] = y;
+  if (blk == 0) {
+    for (int h = threadIdx.x; h < p.Hv; h += 128) {
+      const float av = p.a[(size_t)r * p.a_stride + h], bv = p.b[(size_t)r * p.b_stride + h];
+      p.beta[(size_t)r * p.Hv + h] = sigmoid_f(bv);
+      p.decay[(size_t)r * p.Hv + h] = __expf(p.ssm_a[h] * softplus20_f(av + p.dt_bias[h]));
+    }
+  }
+}
+
+// grid (Hv, R), block 512: thread (col = tid/4, ks = tid%4) owns rows ks*32..+31 of one column of S.
+// One recurrent step, then RMSNorm over the head's 128 outputs * w * SiLU(z) -> bf16.
+__global__ void __launch_bounds__(512) gdn_decode_step_kernel(const GdnDecodeArgs p) {
+  __shared__ __align__(16) float sq[KPAD];
+  __shared__ __align__(16) float sk[KPAD];
+  __shared__ float red[32];
+  const int h = blockIdx.x, r = blockIdx.y, tid = threadIdx.x;
+  const int col = tid >> 2, ks = tid & 3;
+  const int kh = h % p.G;
+  const float* row = p.qkv + (size_t)r * p.C;
+  if (tid < 128) {
+    const int dst = tid + (tid >> 5) * 4;
+    sq[dst] = row[(size_t)kh * DK + tid];
+    sk[dst] = row[(size_t)p.G * DK + (size_t)kh * DK + tid];
+  }
+  float* Sg = p.state + (((size_t)p.slot[r] * p.Hv + h) * DK) * DV;
+  float S[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) S[i] = Sg[(size_t)(ks * 32 + i) * DV + col];
+  const float v = row[(size_t)2 * p.G * DK + (size_t)h * DV + col];
+  const float dec = p.decay[(size_t)r * p.Hv + h], bet = p.beta[(size_t)r * p.Hv + h];
+  __syncthreads();
+  float kr[32];
+#pragma unroll
+  for (int i4 = 0; i4 < 8; ++i4) {
+    const float4 k4 = *reinterpret_cast<const float4*>(&sk[ks * 36 + i4 * 4]);
+    kr[i4 * 4] = k4.x; kr[i4 * 4 + 1] = k4.y; kr[i4 * 4 + 2] = k4.z; kr[i4 * 4 + 3] = k4.w;
+  }
+  float kv4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    S[i] *= dec;
+    kv4[i & 3] += kr[i] * S[i];
+  }
+  float kv = (kv4[0] + kv4[1]) + (kv4[2] + kv4[3]);
+  kv += __shfl_xor_sync(0xffffffffu, kv, 1);
+  kv += __shfl_xor_sync(0xffffffffu, kv, 2);
+  const float delta = (v - kv) * bet;
+  float o4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int i4 = 0; i4 < 8; ++i4) {
+    const float4 q4 = *reinterpret_cast<const float4*>(&sq[ks * 36 + i4 * 4]);
+    S[i4 * 4] += kr[i4 * 4] * delta;         o4[0] += q4.x * S[i4 * 4];
+    S[i4 * 4 + 1] += kr[i4 * 4 + 1] * delta; o4[1] += q4.y * S[i4 * 4 + 1];
+    S[i4 * 4 + 2] += kr[i4 * 4 + 2] * delta; o4[2] += q4.z * S[i4 * 4 + 2];
+    S[i4 * 4 + 3] += kr[i4 * 4 + 3] * delta; o4[3] += q4.w * S[i4 * 4 + 3];
+  }
+  float o = (o4[0] + o4[1]) + (o4[2] + o4[3]);
+  o += __shfl_xor_sync(0xffffffffu, o, 1);
+  o += __shfl_xor_sync(0xffffffffu, o, 2);
+#pragma unroll
+  for (int i = 0; i < 32; ++i) Sg[(size_t)(ks * 32 + i) * DV + col] = S[i];
+  const float ss = block_sum(ks == 0 ? o * o : 0.f, red);
+  if (ks == 0) {
+    const float inv = rsqrtf(ss / (float)DV + p.eps);
+    const size_t zi = (size_t)r * p.z_stride + (size_t)h * DV + col;
+    const float zv = p.z_dtype == 0 ? reinterpret_cast<const float*>(p.z)[zi]
+                                    : bf16_to_f32(reinterpret_cast<const __nv_bfloat16*>(p.z)[zi]);
+    p.out[(size_t)r * p.out_stride + (size_t)h * DV + col] = f32_to_bf16(o * inv * p.norm_w[col] * silu_f(zv));
+  }
+}
+
 }  // namespace
 
 HE_API int he_gdn_prepare(const GdnPrepArgs* args, cudaStream_t stream) {
@@ -230,3 +347,17 @@ HE_API int he_state_commit(void* state, const void* journal, const void* seg_slo
   HE_LAUNCH_CHECK();
   return 0;
 }
+
+// Decode fast path (every row is a single-token segment, no journal): conv + gates + one scan step + gated norm
+// in two launches.  Requires state size 128, conv kernel 4, C % 128 == 0.
+HE_API int he_gdn_decode(const GdnDecodeArgs* args, cudaStream_t stream) {
+  const GdnDecodeArgs& a = *args;
+  if (a.R <= 0) return 0;
+  if (a.C % 128 != 0 || a.C != 2 * a.G * 128 + a.Hv * 128 || a.Hv % a.G != 0) return -HE_ERR_BAD_ARG;
+  gdn_decode_pre_kernel<<<dim3(a.C / 128, a.R), 128, 0, stream>>>(a);
+  HE_LAUNCH_CHECK();
+  gdn_decode_step_kernel<<<dim3(a.Hv, a.R), 512, 0, stream>>>(a);
+  HE_LAUNCH_CHECK();
+  return 0;
+}
+HE_API int he_gdn_decode_args_size() { return (int)sizeof(GdnDecodeArgs); }

@@ -14,6 +14,7 @@
 //
 // Behavioural reference: the decode GEMV family in hipengine/kernels/hip_gfx1100/quant/gguf_q4_k_gemv.hip
 // (Q8_1 activation quantize + integer dot) and the oracle hipengine/kernels/cpu_reference/ops.py:466-537.
+#include <cstdlib>
 #include "common.cuh"
 #include "gemv_rows.cuh"
 #include "sm100.cuh"
@@ -337,7 +338,11 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const __grid_constant_
     advance(pc);
   };
 
+  // Programmatic dependent launch: let the next kernel of the stream start its own weight prefetch while this
+  // grid drains, start ours before the producer of the activations has finished, and only then wait for it.
+  asm volatile("griddepcontrol.launch_dependents;");
   for (int i = 0; i < a.n_slots - 1; ++i) issue();
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   prologue<R>(a, s, red);
 
@@ -435,8 +440,22 @@ int launch_nw(const HeGemvArgs& a, size_t smem, long long items, int num_sms, cu
   long long grid = (items + NW - 1) / NW;
   if (grid > num_sms) grid = num_sms;
   if (grid < 1) grid = 1;
-  gemv_kernel<R, NW><<<(unsigned)grid, NW * 32, smem, stream>>>(a);
-  HE_LAUNCH_CHECK();
+  static const bool pdl = []() {
+    const char* e = getenv("HE_PDL");
+    return !(e != nullptr && e[0] == '0');
+  }();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(NW * 32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_kernel<R, NW>, a);
+  if (e != cudaSuccess) return (int)e;
   return 0;
 }
 

@@ -249,11 +249,11 @@ class EngineService:
     def _drive(self) -> None:
         # The CUDA "current device" is per thread and starts at device 0: bind this thread to the runner's
         # device before it launches anything (on rank r > 0 the model lives on another GPU).
-        dev = getattr(self.loop.runner, "device", None)
-        if dev is not None and getattr(dev, "type", "cpu") == "cuda":
-            import torch
-            torch.cuda.set_device(dev)
         try:
+            dev = getattr(self.loop.runner, "device", None)
+            if dev is not None and getattr(dev, "type", "cpu") == "cuda" and dev.index is not None:
+                import torch
+                torch.cuda.set_device(dev)
             while True:
                 drained = 0
                 while drained < 64:

@@ -244,7 +244,7 @@ class HybridExecutor:
                                     self.block_table, slot, pos0, out[r0:r0 + n], H, Hkv, D, PAGE, cfg.scale())
                     r0 += n
                 return
-        split_len = 128 if b.max_ctx <= 8192 else 256
+        split_len = 64 if b.max_ctx <= 8192 else (128 if b.max_ctx <= 32768 else 256)
         max_splits = max(1, (b.max_ctx + split_len - 1) // split_len)
         part = self.scratch.get("attn_part", (K.attn_decode_scratch_floats(T, H, max_splits, D),), torch.float32)
         K.attn_decode(q_out, gate, self.kv[i], self.block_table, b.slot, b.ctx_len, part, out, H, Hkv, D, PAGE,
@@ -278,18 +278,27 @@ class HybridExecutor:
                 K.small_gemm_f32(xn, self.F(i, "ssm_alpha.weight"), a_p)
                 K.small_gemm_f32(xn, self.F(i, "ssm_beta.weight"), b_p)
         conv = sc.get("conv_out", (T, C), torch.float32)
+        decay = sc.get("decay", (T, Hv), torch.float32)
+        beta = sc.get("beta", (T, Hv), torch.float32)
+        og = sc.get("gdn_og", (T, inner), torch.bfloat16)
+        if (small and journal is None and b.n_seg == T and S == 128 and cfg.conv_kernel == 4
+                and os.environ.get("HE_GDN_FUSED", "1") != "0"):
+            # plain decode rows: two fused launches instead of five
+            K.gdn_decode(qkv, self.F(i, "ssm_conv1d.weight"), self.conv_state[i], a_p, b_p,
+                         self.F(i, "ssm_a").reshape(-1), self.F(i, "ssm_dt.bias").reshape(-1), b.seg_slot, conv,
+                         decay, beta, self.gdn_state[i], z, self.F(i, "ssm_norm.weight").reshape(-1), og, G, Hv,
+                         cfg.rms_eps)
+            self._out_small(og, self.W(i, "ssm_out.weight"), h)
+            return
         cj = journal["conv"][i] if journal is not None else None
         K.conv1d(qkv, self.F(i, "ssm_conv1d.weight"), self.conv_state[i], b.seg_start, b.seg_slot, b.tok_seg, conv, C,
                  update_state=journal is None, journal=cj)
-        decay = sc.get("decay", (T, Hv), torch.float32)
-        beta = sc.get("beta", (T, Hv), torch.float32)
         K.gdn_prepare(conv, a_p, b_p, self.F(i, "ssm_a").reshape(-1), self.F(i, "ssm_dt.bias").reshape(-1), decay, beta,
                       G, Hv, S)
         o = sc.get("gdn_o", (T, Hv, S), torch.float32)
         gj = journal["gdn"][i] if journal is not None else None
         K.gdn_scan(conv, decay, beta, self.gdn_state[i], b.seg_start, b.seg_slot, o, G, Hv,
                    write_state=journal is None, journal=gj)
-        og = sc.get("gdn_og", (T, inner), torch.bfloat16)
         K.gdn_gated_norm(o, z, self.F(i, "ssm_norm.weight").reshape(-1), og, Hv, S, cfg.rms_eps)
         if small:
             self._out_small(og, self.W(i, "ssm_out.weight"), h)

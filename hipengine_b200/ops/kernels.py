@@ -69,6 +69,14 @@ class _AttnDecArgs(C.Structure):
                 ("scale", C.c_float)]
 
 
+class _GdnDecodeArgs(C.Structure):
+    _fields_ = [("x", c_vp), ("x_stride", c_ll), ("conv_w", c_vp), ("conv_state", c_vp), ("a", c_vp), ("b", c_vp),
+                ("a_stride", c_ll), ("b_stride", c_ll), ("ssm_a", c_vp), ("dt_bias", c_vp), ("slot", c_vp),
+                ("qkv", c_vp), ("decay", c_vp), ("beta", c_vp), ("state", c_vp), ("z", c_vp), ("z_dtype", C.c_int),
+                ("z_stride", c_ll), ("norm_w", c_vp), ("out", c_vp), ("out_stride", c_ll), ("eps", C.c_float),
+                ("C", C.c_int), ("G", C.c_int), ("Hv", C.c_int), ("R", C.c_int)]
+
+
 class _MoeSelArgs(C.Structure):
     _fields_ = [("x", c_vp), ("ldx", c_ll), ("norm_w", c_vp), ("eps", C.c_float), ("ids", c_vp), ("wts", c_vp),
                 ("w1", c_vp), ("w2", c_vp), ("qtype1", C.c_int), ("qtype2", C.c_int),
@@ -87,7 +95,8 @@ def _check_abi() -> None:
     L = N.lib()
     pairs = [("he_gemv_args_size", _GemvArgs), ("he_qkv_args_size", _QkvArgs), ("he_conv_args_size", _ConvArgs),
              ("he_gdn_prep_args_size", _GdnPrepArgs), ("he_gdn_scan_args_size", _GdnScanArgs),
-             ("he_attn_dec_args_size", _AttnDecArgs), ("he_moe_sel_args_size", _MoeSelArgs)]
+             ("he_attn_dec_args_size", _AttnDecArgs), ("he_moe_sel_args_size", _MoeSelArgs),
+             ("he_gdn_decode_args_size", _GdnDecodeArgs)]
     for fn, st in pairs:
         got = getattr(L, fn)()
         if got != C.sizeof(st):
@@ -357,6 +366,25 @@ def gdn_gated_norm(o: torch.Tensor, z: torch.Tensor, w: torch.Tensor, out: torch
     N.check(N.lib().he_gdn_gated_norm(c_vp(o.data_ptr()), c_vp(z.data_ptr()), C.c_int(_dt(z)), c_ll(z.stride(0)),
                                       c_vp(w.data_ptr()), c_vp(out.data_ptr()), c_ll(out.stride(0)), C.c_int(T),
                                       C.c_int(Hv), C.c_int(Dv), C.c_float(eps), _stream()), "he_gdn_gated_norm")
+
+
+def gdn_decode(x: torch.Tensor, conv_w: torch.Tensor, conv_state: torch.Tensor, a: torch.Tensor, b: torch.Tensor,
+               ssm_a: torch.Tensor, dt_bias: torch.Tensor, slot: torch.Tensor, qkv: torch.Tensor,
+               decay: torch.Tensor, beta: torch.Tensor, state: torch.Tensor, z: torch.Tensor, norm_w: torch.Tensor,
+               out: torch.Tensor, G: int, Hv: int, eps: float) -> None:
+    """Decode fast path of a gated delta-net layer (single-token segments): conv + gates, then one recurrent
+    step with the gated RMSNorm, in two launches."""
+    _check_abi()
+    p = _GdnDecodeArgs()
+    p.x, p.x_stride, p.conv_w, p.conv_state = x.data_ptr(), x.stride(0), conv_w.data_ptr(), conv_state.data_ptr()
+    p.a, p.b, p.a_stride, p.b_stride = a.data_ptr(), b.data_ptr(), a.stride(0), b.stride(0)
+    p.ssm_a, p.dt_bias, p.slot = ssm_a.data_ptr(), dt_bias.data_ptr(), slot.data_ptr()
+    p.qkv, p.decay, p.beta, p.state = qkv.data_ptr(), decay.data_ptr(), beta.data_ptr(), state.data_ptr()
+    p.z, p.z_dtype, p.z_stride, p.norm_w = z.data_ptr(), _dt(z), z.stride(0), norm_w.data_ptr()
+    p.out, p.out_stride, p.eps = out.data_ptr(), out.stride(0), eps
+    p.C, p.G, p.Hv, p.R = qkv.shape[1], G, Hv, x.shape[0]
+    assert x.dtype == torch.float32
+    N.check(N.lib().he_gdn_decode(C.byref(p), _stream()), "he_gdn_decode")
 
 
 def state_commit(state: torch.Tensor, journal: torch.Tensor, seg_slot: torch.Tensor, commit_row: torch.Tensor,
