@@ -66,6 +66,13 @@ class GpuRunner(BaseRunner):
         self.resident_key: Tuple[int, ...] = ()
         self.pinned_ids = torch.zeros(max(self.max_slots, 8), dtype=torch.int64).pin_memory()
         self.stats = {"prefix_hits": 0, "prefix_hit_tokens": 0, "snapshots_taken": 0, "h2d_bytes": 0, "d2h_bytes": 0}
+        # MTP: the checkpoint's own NextN block drafts, the target verifies (``speculative/mtp.py``)
+        self.mtp = None
+        if config.speculative.mode == "mtp" and self.ex.has_nextn:
+            from ..speculative.mtp import MTPCycle
+            self.mtp = MTPCycle(self.ex, max_depth=max(1, config.speculative.draft_depth),
+                                max_requests=min(self.max_slots, 8))
+        self.supports_mtp = self.mtp is not None
 
     # ------------------------------------------------------------------ snapshots
     def _free_snapshot(self, sid: int) -> None:
@@ -105,6 +112,8 @@ class GpuRunner(BaseRunner):
         rs.slot = slot
         rs.runner_data = lease
         self.ex.reset_slot(slot)
+        if self.mtp is not None:
+            self.mtp.reset_slot(slot)
         if shared:
             if self.cfg.is_hybrid and match.snapshot is not None:
                 self._copy_state(match.snapshot, slot)
@@ -160,6 +169,8 @@ class GpuRunner(BaseRunner):
                 batch = make_batch(segs, self.device)
                 self.stats["h2d_bytes"] += 8 * batch.T + 16 * batch.T
                 h = self.ex.forward(batch)
+                if self.mtp is not None:
+                    self.mtp.after_prefill(batch, h)
                 row = 0
                 last_rows = []
                 for rs, a, b in owners:
@@ -260,6 +271,46 @@ class GpuRunner(BaseRunner):
         self.graphs.next_ids[:R].copy_(torch.tensor([t for t, _ in res], dtype=torch.int64), non_blocking=True)
         self.graphs.publish(R)
         self.stats["h2d_bytes"] += 8 * R
+        return res
+
+    # ------------------------------------------------------------------ speculative decoding (MTP)
+    def speculative_eligible(self, rs: RequestState) -> bool:
+        from ..speculative.serving import resolve_mtp_serving_plan
+        d = resolve_mtp_serving_plan(self.config.speculative.mode and "on", self.supports_mtp, rs.req.temperature,
+                                     self._needs_processing(rs), bool(rs.forced), bool(rs.req.logprobs),
+                                     depth=self.config.speculative.draft_depth,
+                                     requested=True)
+        return d.use_mtp
+
+    @torch.no_grad()
+    def speculative_cycle(self, rows: List[RequestState]):
+        from ..speculative.contracts import SpecCycleResult
+        from ..speculative.policy import plan_draft_depth
+        if len(rows) > self.mtp.max_requests:
+            return [SpecCycleResult([t], 0, 0) for t, _ in self.decode(rows)]
+        depth = self.mtp.max_depth
+        for rs in rows:
+            remaining = rs.remaining()
+            room = rs.total_budget_tokens - rs.position
+            depth = min(depth, plan_draft_depth(self.mtp.max_depth, remaining, room, rs.telemetry.speculative_drafted,
+                                                rs.telemetry.speculative_accepted))
+        if depth < 1:
+            return [SpecCycleResult([t], 0, 0) for t, _ in self.decode(rows)]
+        for rs in rows:
+            self._ensure_pages(rs, rs.position + depth)
+        try:
+            res, _txn = self.mtp.cycle([rs.slot for rs in rows], [rs.last_token for rs in rows],
+                                       [rs.position - 1 for rs in rows], depth,
+                                       [rs.req.temperature for rs in rows], [rs.seed for rs in rows],
+                                       [rs.sample_counter for rs in rows])
+        except torch.cuda.OutOfMemoryError as exc:
+            raise ExecutionFailure([rs.rid for rs in rows], "verify", f"out of memory: {exc}", "partial") from exc
+        for rs, c in zip(rows, res):
+            rs.sample_counter += 2 * (depth + 1)
+            rs.telemetry.d2h_bytes += 8 * (depth + 2)
+            rs.telemetry.h2d_bytes += 24 * (depth + 1)
+        self.stats["d2h_bytes"] += 8 * (depth + 2) * len(rows)
+        self.resident_key = ()          # the decode graph's resident rows no longer match the cursors
         return res
 
     # ------------------------------------------------------------------ release / lifecycle

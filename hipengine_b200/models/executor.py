@@ -367,6 +367,78 @@ class HybridExecutor:
             K.softcap_(out, cfg.final_softcap)
         return out
 
+    # ------------------------------------------------------------------ NextN / MTP draft block
+    @property
+    def has_nextn(self) -> bool:
+        return self.cfg.nextn_layers > 0 and f"blk.{self.cfg.n_layers}.nextn.eh_proj.weight" in self.dw
+
+    def nextn_forward(self, b: BatchDesc, hidden_prev: torch.Tensor) -> torch.Tensor:
+        """One pass of the trailing NextN block over the packed rows.
+
+        Row input = eh_proj([RMSNorm_e(embed(token)) | RMSNorm_h(hidden_prev)]) where ``hidden_prev`` [T, hidden]
+        is the post-norm hidden of the position before the row's token; then the block's own gated attention
+        (its own KV planes, layer index ``n_layers``) and FFN.  Returns the fp32 residual rows [T, hidden].
+        Contract: hipengine/kernels/cpu_reference/ops.py:840-955 (the reference's NextN oracle).
+        """
+        cfg, sc = self.cfg, self.scratch
+        i = cfg.n_layers
+        T, H = b.T, cfg.hidden
+        small = T <= GEMV_MAX_ROWS
+        table = self.dw.get(f"blk.{i}.nextn.embed_tokens.weight", self.dw["token_embd.weight"])
+        e = sc.get("nx_e", (T, H), torch.float32)
+        K.embed(table, b.tokens, e, cfg.embed_scale)
+        xcat = sc.get("nx_cat", (T, 2 * H), torch.float32)
+        K.rmsnorm_rows(e, self.F(i, "nextn.enorm.weight"), xcat[:, :H], cfg.rms_eps)
+        K.rmsnorm_rows(hidden_prev, self.F(i, "nextn.hnorm.weight"), xcat[:, H:], cfg.rms_eps)
+        h = sc.get("nx_h", (T, H), torch.float32)
+        w = self.W(i, "nextn.eh_proj.weight")
+        if small:
+            K.gemv(xcat, [GemvSegment(w, h, K.EPI_F32)])
+        else:
+            xb = sc.get("nx_cat_bf", (T, 2 * H), torch.bfloat16)
+            xb.copy_(xcat)
+            y = self._gemm(xb, w, sc.get("y_bf", (T, H), torch.bfloat16), tag="o")
+            h.copy_(y)
+        self._attention_full(i, h, b, small)
+        self._ffn(i, h, b, small)
+        return h
+
+    def nextn_logits(self, h_rows: torch.Tensor, out: Optional[torch.Tensor] = None,
+                     hidden_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Draft head: shared_head_norm (or output_norm) + shared head (or the model's head) over <= 8 rows."""
+        cfg = self.cfg
+        i = cfg.n_layers
+        R = h_rows.shape[0]
+        norm_w = self.f32.get(f"blk.{i}.nextn.shared_head_norm.weight", self.f32["output_norm.weight"])
+        head = self.dw.get(f"blk.{i}.nextn.shared_head_head.weight", self.dw["output.weight"])
+        if out is None:
+            out = self.scratch.get("nx_logits", (R, head.n_rows), torch.float32)
+        if hidden_out is not None:
+            K.rmsnorm_rows(h_rows, norm_w, hidden_out, cfg.rms_eps)
+        for r0 in range(0, R, GEMV_MAX_ROWS):
+            r1 = min(R, r0 + GEMV_MAX_ROWS)
+            K.gemv(h_rows[r0:r1], [GemvSegment(head, out[r0:r1])], norm_w=norm_w, eps=cfg.rms_eps)
+        return out
+
+    def alloc_journal(self, rows: int) -> dict:
+        """Per-verify-row recurrent state journals for every linear-attention layer."""
+        cfg = self.cfg
+        j = {"conv": {}, "gdn": {}}
+        for i in self.conv_state:
+            j["conv"][i] = torch.empty(rows, cfg.linear_qkv_width, cfg.conv_kernel - 1, dtype=torch.float32,
+                                       device=self.device)
+            j["gdn"][i] = torch.empty(rows, cfg.ssm_v_heads, cfg.ssm_state, cfg.ssm_state, dtype=torch.float32,
+                                      device=self.device)
+        return j
+
+    def commit_journal(self, journal: dict, seg_slot: torch.Tensor, commit_row: torch.Tensor) -> None:
+        """state[seg_slot[s]] = journal[commit_row[s]] for every linear layer (speculative commit)."""
+        cfg = self.cfg
+        for i, st in self.conv_state.items():
+            K.state_commit(st, journal["conv"][i], seg_slot, commit_row, cfg.linear_qkv_width * (cfg.conv_kernel - 1))
+            K.state_commit(self.gdn_state[i], journal["gdn"][i], seg_slot, commit_row,
+                           cfg.ssm_v_heads * cfg.ssm_state * cfg.ssm_state)
+
     def greedy(self, logits: torch.Tensor, out_ids: torch.Tensor) -> torch.Tensor:
         return K.argmax_rows(logits, self.am_v, self.am_i, out_ids)
 

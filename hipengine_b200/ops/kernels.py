@@ -492,6 +492,55 @@ def moe_down_sel(act_rows: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w
     _moe_sel("he_moe_down_sel", act_rows, None, 0.0, ids, wts, w_down, None, n_out, h, "silu")
 
 
+# ----------------------------------------------------------------------------- speculative decoding
+
+class _SpecSampledArgs(C.Structure):
+    _fields_ = [("p_logits", c_vp), ("q_logits", c_vp), ("draft", c_vp), ("temperature", c_vp), ("seed", c_vp),
+                ("counter", c_vp), ("n_accept", c_vp), ("out", c_vp), ("R", C.c_int), ("K", C.c_int), ("V", C.c_int)]
+
+
+def spec_accept_greedy(draft: torch.Tensor, target: torch.Tensor, n_accept: torch.Tensor, out: torch.Tensor,
+                       max_emit: Optional[torch.Tensor] = None) -> None:
+    """draft int64 [R, K], target int64 [R, K+1] -> n_accept int32 [R], out int64 [R, K+1] (-1 padded)."""
+    R, Kd = draft.shape
+    N.check(N.lib().he_spec_accept_greedy(c_vp(draft.data_ptr()), c_vp(target.data_ptr()), C.c_int(R), C.c_int(Kd),
+                                          c_vp(n_accept.data_ptr()), c_vp(out.data_ptr()), c_vp(_p(max_emit)),
+                                          _stream()), "he_spec_accept_greedy")
+
+
+def spec_accept_sampled(p_logits: torch.Tensor, q_logits: Optional[torch.Tensor], draft: torch.Tensor,
+                        temperature: torch.Tensor, seed: torch.Tensor, counter: torch.Tensor,
+                        n_accept: torch.Tensor, out: torch.Tensor) -> None:
+    """Exact speculative sampling on the device.  p_logits fp32 [R, K+1, V]; q_logits fp32 [R, K, V] or None when
+    the drafts were chosen greedily; seed / counter uint64 (as int64 tensors) per request."""
+    L = N.lib()
+    assert L.he_spec_sampled_args_size() == C.sizeof(_SpecSampledArgs)
+    R, Kd = draft.shape
+    a = _SpecSampledArgs()
+    a.p_logits, a.q_logits, a.draft = p_logits.data_ptr(), _p(q_logits), draft.data_ptr()
+    a.temperature, a.seed, a.counter = temperature.data_ptr(), seed.data_ptr(), counter.data_ptr()
+    a.n_accept, a.out = n_accept.data_ptr(), out.data_ptr()
+    a.R, a.K, a.V = R, Kd, p_logits.shape[-1]
+    assert p_logits.is_contiguous() and (q_logits is None or q_logits.is_contiguous())
+    N.check(L.he_spec_accept_sampled(C.byref(a), _stream()), "he_spec_accept_sampled")
+
+
+def spec_commit(n_accept: torch.Tensor, out: torch.Tensor, tokens: torch.Tensor, pos: torch.Tensor,
+                ctx_len: Optional[torch.Tensor], commit_row: Optional[torch.Tensor],
+                hidden_row: Optional[torch.Tensor]) -> None:
+    R, K1 = out.shape
+    N.check(N.lib().he_spec_commit(c_vp(n_accept.data_ptr()), c_vp(out.data_ptr()), C.c_int(R), C.c_int(K1 - 1),
+                                   c_vp(tokens.data_ptr()), c_vp(pos.data_ptr()), c_vp(_p(ctx_len)),
+                                   c_vp(_p(commit_row)), c_vp(_p(hidden_row)), _stream()), "he_spec_commit")
+
+
+def gather_rows_f32(src: torch.Tensor, rows: torch.Tensor, dst: torch.Tensor) -> None:
+    R, H = dst.shape
+    N.check(N.lib().he_gather_rows_f32(c_vp(src.data_ptr()), c_ll(src.stride(0)), c_vp(rows.data_ptr()),
+                                       c_vp(dst.data_ptr()), c_ll(dst.stride(0)), C.c_int(R), C.c_int(H), _stream()),
+            "he_gather_rows_f32")
+
+
 # ----------------------------------------------------------------------------- sampling
 
 class SampleParams(C.Structure):

@@ -1,0 +1,152 @@
+"""NextN / MTP chain speculation on the GPU executor: draft K tokens with the checkpoint's trailing NextN block,
+verify the chain with one target forward, accept on the device, commit by journal copy.
+
+Cycle for a request whose last committed token ``t0`` sits at position ``p`` (not yet fed to the target):
+  draft   d1 = argmax NextN(t0, h[p-1]) ... dK, each step feeding the block's own hidden forward;
+  verify  target forward over rows [t0, d1 .. dK] at positions p .. p+K; linear-attention layers journal their
+          conv / delta-net state after every row instead of updating the live state;
+  accept  greedy: longest prefix with d_{i+1} == argmax(row i); sampled: exact min(1, p/q) rule (``csrc/spec.cu``);
+  commit  live recurrent state <- journal row n, cursors += n + 1, h[p+n] kept for the next cycle.  KV rows past
+          the accepted prefix are simply overwritten by the next cycle (positions rewind, pages stay).
+Stages are recorded through ``SpecTransaction``.  Reference flow: ``hipengine/runtime/qwen35_gguf_mtp.py``
+(transactional proposal + verify) and ``hipengine/speculative/gguf_mtp.py`` (seed rows, draft proposals).
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from ..models.executor import GEMV_MAX_ROWS, BatchDesc, make_batch
+from ..ops import kernels as K
+from .contracts import SpecCycleResult
+from .transaction import SpecTransaction, Stage
+
+
+class MTPCycle:
+    def __init__(self, ex, max_depth: int = 3, max_requests: int = 8):
+        assert ex.has_nextn, "checkpoint has no NextN block"
+        self.ex = ex
+        self.max_depth = max_depth
+        self.max_requests = max_requests
+        dev, H = ex.device, ex.cfg.hidden
+        self.max_rows = max_requests * (max_depth + 1)
+        self.journal = None                       # allocated on first use (large)
+        self.h_prev = torch.zeros(ex.max_slots, H, dtype=torch.float32, device=dev)   # post-norm hidden per slot
+        self.n_accept = torch.zeros(max_requests, dtype=torch.int32, device=dev)
+        self.commit_row = torch.zeros(max_requests, dtype=torch.int32, device=dev)
+        self.hidden_row = torch.zeros(max_requests, dtype=torch.int32, device=dev)
+        self.am_ids = torch.zeros(self.max_rows, dtype=torch.int64, device=dev)
+        self.stats = {"cycles": 0, "drafted": 0, "accepted": 0}
+
+    # ------------------------------------------------------------------ prompt side
+    def reset_slot(self, slot: int) -> None:
+        self.h_prev[slot].zero_()
+
+    def after_prefill(self, batch: BatchDesc, h: torch.Tensor) -> None:
+        """Feed the prompt rows of ``batch`` through the NextN block so its KV covers the prompt, and keep the
+        last post-norm hidden of every segment.  ``h`` is the target's residual output for the batch rows."""
+        ex, cfg = self.ex, self.ex.cfg
+        T = batch.T
+        hid = ex.scratch.get("mtp_hid", (T, cfg.hidden), torch.float32)
+        K.rmsnorm_rows(h, ex.f32["output_norm.weight"], hid, cfg.rms_eps)
+        hprev = ex.scratch.get("mtp_hprev", (T, cfg.hidden), torch.float32)
+        r0 = 0
+        for (slot, pos0, n) in batch.segs_host:
+            hprev[r0].copy_(self.h_prev[slot])
+            if n > 1:
+                hprev[r0 + 1:r0 + n].copy_(hid[r0:r0 + n - 1])
+            self.h_prev[slot].copy_(hid[r0 + n - 1])
+            r0 += n
+        ex.nextn_forward(batch, hprev)
+
+    # ------------------------------------------------------------------ one cycle
+    @torch.no_grad()
+    def cycle(self, slots: Sequence[int], last_tokens: Sequence[int], positions: Sequence[int], depth: int,
+              temperature: Optional[Sequence[float]] = None, seeds: Optional[Sequence[int]] = None,
+              counters: Optional[Sequence[int]] = None, draft_override: Optional[torch.Tensor] = None
+              ) -> Tuple[List[SpecCycleResult], SpecTransaction]:
+        """positions[r] = position of last_tokens[r].  temperature None/0 -> greedy verification.
+        ``draft_override`` (int64 [R, depth]) replaces the NextN proposals after they are computed (the block
+        still runs, so its KV stays in step); used to test acceptance paths with known chains."""
+        ex, cfg, dev = self.ex, self.ex.cfg, self.ex.device
+        R, Kd = len(slots), depth
+        assert 1 <= Kd <= self.max_depth and R <= self.max_requests
+        txn = SpecTransaction(list(range(R)))
+        txn.advance(Stage.RESERVED)
+        if self.journal is None:
+            self.journal = ex.alloc_journal(self.max_rows)
+        sampled = temperature is not None and any(t > 0 for t in temperature)
+        slot_t = torch.tensor(list(slots), dtype=torch.int64, device=dev)
+        t0 = torch.tensor(list(last_tokens), dtype=torch.int64, device=dev)
+        drafts = torch.empty(R, Kd, dtype=torch.int64, device=dev)
+        txn.advance(Stage.TARGET_OPEN)
+        # ---- draft: K passes of the NextN block, R rows each
+        txn.advance(Stage.PROVIDER_OPEN)
+        cur = t0
+        hprev = self.h_prev.index_select(0, slot_t)
+        hid_next = ex.scratch.get("mtp_hid_next", (R, cfg.hidden), torch.float32)
+        ids = self.am_ids[:R]
+        for j in range(Kd):
+            b = make_batch([(s, p + j, [0]) for s, p in zip(slots, positions)], dev)
+            b.tokens = cur
+            h = ex.nextn_forward(b, hprev)
+            lg = ex.nextn_logits(h, hidden_out=hid_next)
+            for r0 in range(0, R, GEMV_MAX_ROWS):
+                r1 = min(R, r0 + GEMV_MAX_ROWS)
+                ex.greedy(lg[r0:r1], ids[r0:r1])
+            drafts[:, j].copy_(ids)
+            cur = drafts[:, j].contiguous()
+            hprev = hid_next.clone()
+        if draft_override is not None:
+            drafts.copy_(draft_override.to(dev))
+        txn.advance(Stage.DRAFTED)
+        # ---- verify: one target forward over R chains of K+1 rows, recurrent state journalled per row
+        T = R * (Kd + 1)
+        vb = make_batch([(s, p, [0] * (Kd + 1)) for s, p in zip(slots, positions)], dev)
+        vb.tokens = torch.cat([t0[:, None], drafts], 1).reshape(-1).contiguous()
+        journal = {"conv": {i: t[:T] for i, t in self.journal["conv"].items()},
+                   "gdn": {i: t[:T] for i, t in self.journal["gdn"].items()}}
+        h = ex.forward(vb, journal=journal)
+        logits = ex.scratch.get("mtp_logits", (T, cfg.vocab), torch.float32)
+        hid = ex.scratch.get("mtp_vhid", (T, cfg.hidden), torch.float32)
+        for r0 in range(0, T, GEMV_MAX_ROWS):
+            r1 = min(T, r0 + GEMV_MAX_ROWS)
+            ex.logits(h[r0:r1], out=logits[r0:r1], hidden_out=hid[r0:r1])
+        txn.advance(Stage.VERIFIED)
+        # ---- accept
+        out = torch.empty(R, Kd + 1, dtype=torch.int64, device=dev)
+        if not sampled:
+            tgt = self.am_ids[:T]
+            for r0 in range(0, T, GEMV_MAX_ROWS):
+                r1 = min(T, r0 + GEMV_MAX_ROWS)
+                ex.greedy(logits[r0:r1], tgt[r0:r1])
+            K.spec_accept_greedy(drafts, tgt.view(R, Kd + 1), self.n_accept[:R], out)
+        else:
+            temp = torch.tensor([max(float(t), 1e-6) for t in temperature], dtype=torch.float32, device=dev)
+            sd = torch.tensor([int(s) & (2 ** 63 - 1) for s in (seeds or [0] * R)], dtype=torch.int64, device=dev)
+            ct = torch.tensor([int(c) & (2 ** 63 - 1) for c in (counters or [0] * R)], dtype=torch.int64, device=dev)
+            K.spec_accept_sampled(logits.view(R, Kd + 1, cfg.vocab), None, drafts, temp, sd, ct, self.n_accept[:R], out)
+        txn.advance(Stage.ACCEPTED)
+        # ---- readback (the only host sync of the cycle)
+        n_host = self.n_accept[:R].tolist()
+        out_host = out.tolist()
+        txn.advance(Stage.READBACK)
+        # ---- commit: journal row n -> live state, hidden of row n -> next cycle's seed
+        txn.advance(Stage.COMMITTING)
+        pos_t = torch.tensor(list(positions), dtype=torch.int32, device=dev)
+        tok_t = torch.empty(R, dtype=torch.int64, device=dev)
+        K.spec_commit(self.n_accept[:R], out, tok_t, pos_t, None, self.commit_row[:R], self.hidden_row[:R])
+        ex.commit_journal(journal, vb.seg_slot, self.commit_row[:R])
+        picked = ex.scratch.get("mtp_pick", (R, cfg.hidden), torch.float32)
+        K.gather_rows_f32(hid, self.hidden_row[:R], picked)
+        self.h_prev.index_copy_(0, slot_t, picked)
+        txn.advance(Stage.COMMITTED)
+        res = []
+        for r in range(R):
+            n = int(n_host[r])
+            res.append(SpecCycleResult([int(x) for x in out_host[r][:n + 1]], Kd, n, list(txn.trace)))
+            self.stats["drafted"] += Kd
+            self.stats["accepted"] += n
+        self.stats["cycles"] += 1
+        return res, txn

@@ -76,3 +76,33 @@ def test_pool_is_conserved_after_traffic(setup):
     runner.pool.assert_conserved()
     runner.radix.assert_consistent()
     assert len(runner.free_slots) == runner.max_slots
+
+
+def test_mtp_serving_matches_plain_greedy_and_reports_cycles():
+    """Speculative MTP through the public API: same greedy tokens as the autoregressive engine, with cycles,
+    drafted and accepted counts in the telemetry."""
+    from dataclasses import replace
+    from hipengine_b200 import LLM, SamplingParams
+    from hipengine_b200.loading.synth import build_random_model
+    from hipengine_b200.models.config import TINY_HYBRID
+    w = build_random_model(replace(TINY_HYBRID, nextn_layers=1), seed=4, std=0.05).to("cuda")
+    plain = LLM(w, backend="cuda_sm100a", max_active_requests=2, max_sequence_length=256, prefix_cache="off")
+    spec = LLM(w, backend="cuda_sm100a", max_active_requests=2, max_sequence_length=256, prefix_cache="off",
+               speculative_mtp_serving="on", speculative_candidate_budget=3)
+    try:
+        g = torch.Generator().manual_seed(9)
+        prompts = [torch.randint(0, 2048, (n,), generator=g).tolist() for n in (12, 31)]
+        sp = SamplingParams(max_tokens=14, ignore_eos=True)
+        a = plain.generate_detailed(prompts, sp)
+        b = spec.generate_detailed(prompts, sp)
+        for x, y in zip(a, b):
+            assert x.token_ids == y.token_ids
+            assert len(y.token_ids) == 14 and y.finish.reason == "length"
+        assert all(o.telemetry.speculative_cycles >= 1 and o.telemetry.speculative_drafted >= 3 for o in b)
+        assert all(o.telemetry.speculative_cycles == 0 for o in a)
+        # sampled requests go through the exact accept kernel and still respect the length budget
+        s = spec.generate_detailed(prompts[:1], SamplingParams(max_tokens=9, temperature=0.8, seed=3, ignore_eos=True))[0]
+        assert len(s.token_ids) == 9 and all(0 <= t < 2048 for t in s.token_ids)
+    finally:
+        plain.close()
+        spec.close()
