@@ -101,11 +101,11 @@ def main() -> int:
     ap.add_argument("--model", default="qwen35-27b")
     ap.add_argument("--prompt-len", type=int, default=4096)
     ap.add_argument("--gen-len", type=int, default=256)
-    ap.add_argument("--parallelism", default="dp", choices=["dp", "tp"],
-                    help="N > 1: dp = one replica and one request stream per GPU (weak scaling, the headline); "
-                         "tp = one request stream sharded over the GPUs (strong scaling)")
+    ap.add_argument("--parallelism", default="tp", choices=["dp", "tp"],
+                    help="N > 1: tp = the one batch-1 request stream sharded tensor-parallel over the GPUs (the named "
+                         "config, strong scaling); dp = one replica and one request stream per GPU (weak scaling)")
     ap.add_argument("--tp-comm", default="fused", choices=["fused", "nccl"])
-    ap.add_argument("--no-tp-extra", action="store_true", help="N > 1, dp: skip the extra tensor-parallel measurement")
+    ap.add_argument("--no-extra", action="store_true", help="N > 1: skip the measurement of the other parallelism")
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the layer stack (marks the run invalid)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graphs", action="store_true")
@@ -207,7 +207,7 @@ def main() -> int:
     prefill_tok_s = args.prompt_len * args.steps * streams / (m["prefill_ms"] / 1e3)
 
     e2e = None
-    if not args.no_e2e and mode != "tp":
+    if not args.no_e2e:
         try:
             mine = run_e2e(args, cfg, ex, prompts)
             # replicas run side by side: tokens add up, the slowest replica sets the time
@@ -224,22 +224,26 @@ def main() -> int:
             if world > 1:
                 raise
 
-    tp_extra = None
-    if mode == "dp" and not args.no_tp_extra:
-        # the same request as ONE stream sharded over all GPUs (tensor parallel, fused peer-memory reductions)
+    extra = None
+    if world > 1 and not args.no_extra:
+        # the other way to use the N GPUs, measured briefly for context: tp -> N independent replicas (aggregate
+        # tokens/s, weak scaling); dp -> the single stream sharded over all GPUs
+        other_tp = mode == "dp"
         runner.graphs.clear()
         runner = ex = None
         torch.cuda.empty_cache()
         try:
-            ex, runner = build(tp=True)
+            ex, runner = build(tp=other_tp)
             mt = measure(ex, runner, 2, 1, False)
-            tp_extra = {"parallelism": f"tp{world}", "comm": args.tp_comm, "steps": 1, "warmup": 2,
-                        "decode_tok_s": round((args.gen_len - 1) / (mt["decode_ms"] / 1e3), 3),
-                        "prefill_tok_s": round(args.prompt_len / (mt["prefill_ms"] / 1e3), 2),
-                        "itl_ms": round(mt["decode_ms"] / (args.gen_len - 1), 4),
-                        "ttft_ms": round(mt["prefill_ms"], 3)}
+            k = 1 if other_tp else world
+            extra = {"parallelism": f"tp{world}" if other_tp else f"dp{world}", "steps": 1, "warmup": 2,
+                     "decode_tok_s": round(k * (args.gen_len - 1) / (mt["decode_ms"] / 1e3), 3),
+                     "prefill_tok_s": round(k * args.prompt_len / (mt["prefill_ms"] / 1e3), 2),
+                     "itl_ms": round(mt["decode_ms"] / (args.gen_len - 1), 4), "ttft_ms": round(mt["prefill_ms"], 3)}
+            if other_tp:
+                extra["comm"] = args.tp_comm
         except Exception as exc:
-            tp_extra = {"error": f"{type(exc).__name__}: {exc}"}
+            extra = {"error": f"{type(exc).__name__}: {exc}"}
 
     if rank == 0:
         par = {"single": "single", "dp": f"dp{world}", "tp": f"tp{world}"}[mode]
@@ -262,20 +266,28 @@ def main() -> int:
         }
         if e2e is not None:
             line["e2e"] = e2e
-        if tp_extra is not None:
-            line["tensor_parallel"] = tp_extra
+        if extra is not None:
+            line["other_parallelism"] = extra
+        if mode == "tp":
+            line["config"]["tp_comm"] = args.tp_comm
         if args.layers:
             line["invalid"] = "truncated layer stack (debug run)"
         print(json.dumps(line))
+    sys.stdout.flush()
     if world > 1:
-        # captured graphs hold library collectives: drop them before the process group goes away
+        # Captured graphs hold library collectives: drop them before the process group goes away.  The number is
+        # already printed; a watchdog ends the process if the library's teardown stalls anyway.
         import gc
+        dog = threading.Timer(45.0, lambda: os._exit(0))
+        dog.daemon = True
+        dog.start()
         if runner is not None:
             runner.graphs.clear()
         runner = ex = None
         gc.collect()
         barrier()
         dist.destroy_process_group()
+        dog.cancel()
     return 0
 
 
@@ -288,17 +300,24 @@ def run_e2e(args, cfg, ex, prompts):
         return {"error": "public API not wired"}
     sp = SamplingParams(max_tokens=args.gen_len, temperature=0.0, ignore_eos=True)
     pinned = [torch.tensor(p, dtype=torch.int64).pin_memory() for p in prompts]
-    for i in range(min(2, args.warmup)):
-        llm.generate_detailed(pinned[i].tolist(), sp)
-    dec_s = pre_s = 0.0
-    h2d = d2h = 0
-    for i in range(args.steps):
-        out = llm.generate_detailed(pinned[args.warmup + i].tolist(), sp)[0]
-        dec_s += out.telemetry.decode_seconds
-        pre_s += out.telemetry.prefill_seconds
-        h2d += out.telemetry.h2d_bytes
-        d2h += out.telemetry.d2h_bytes
-    n_dec = (args.gen_len - 1) * args.steps
+    try:
+        for i in range(min(2, args.warmup)):
+            llm.generate_detailed(pinned[i].tolist(), sp)
+        dec_s = pre_s = 0.0
+        h2d = d2h = 0
+        for i in range(args.steps):
+            out = llm.generate_detailed(pinned[args.warmup + i].tolist(), sp)[0]
+            dec_s += out.telemetry.decode_seconds
+            pre_s += out.telemetry.prefill_seconds
+            h2d += out.telemetry.h2d_bytes
+            d2h += out.telemetry.d2h_bytes
+    finally:
+        # the engine's decode graphs may hold library collectives: release them with the engine
+        try:
+            llm._engine.loop.runner.graphs.graphs.clear()
+        except Exception:
+            pass
+        llm.close()
     return {"decode_s": dec_s, "prefill_s": pre_s,
             "h2d_bytes_per_step": h2d // args.steps, "d2h_bytes_per_step": d2h // args.steps}
 
