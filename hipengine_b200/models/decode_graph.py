@@ -12,6 +12,7 @@ for the bucket's context ceiling; spans past a row's live context exit immediate
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
@@ -49,7 +50,11 @@ class DecodeGraphRunner:
         self.logits = torch.empty(R, ex.cfg.vocab, dtype=torch.float32, device=dev)
         self.hidden = torch.empty(R, ex.cfg.hidden, dtype=torch.float32, device=dev)
         self.graphs: Dict[Tuple[int, int, bool], torch.cuda.CUDAGraph] = {}
-        self.stats = {"hits": 0, "misses": 0, "captures": 0, "kernels_per_graph": {}}
+        self.stats = {"hits": 0, "misses": 0, "captures": 0, "kernels_per_graph": {}, "native_launches": 0}
+        # replay through the native launcher (validated control block + cudaGraphLaunch) when torch exposes the
+        # instantiated graph; otherwise through torch's own replay
+        self.native_launch = os.environ.get("HE_NATIVE_GRAPH_LAUNCH", "1") != "0"
+        self._execs: Dict[Tuple[int, int, bool], int] = {}
 
     def batch(self, rows: int, max_ctx: int) -> BatchDesc:
         return BatchDesc(self.tokens[:rows], self.slot[:rows], self.pos[:rows], self.ctx_len[:rows],
@@ -106,7 +111,19 @@ class DecodeGraphRunner:
             self.stats["captures"] += 1
         else:
             self.stats["hits"] += 1
-        g.replay()
+        exec_h = self._execs.get(key) if self.native_launch else None
+        if exec_h is None and self.native_launch and key not in self._execs:
+            from ..core import runtime as RT
+            exec_h = self._execs[key] = RT.graph_exec_handle(g)
+        if exec_h:
+            from ..core import runtime as RT
+            ctl = RT.make_control(RT.STAGE_DECODE_STEP, rows, 0)
+            res = RT.cycle_launch(ctl, exec_h, torch.cuda.current_stream().cuda_stream)
+            if res.rc != 0:
+                raise RuntimeError(f"native graph launch failed: rc={res.rc}")
+            self.stats["native_launches"] += 1
+        else:
+            g.replay()
         K.add_launches(self.stats["kernels_per_graph"][key])
 
     # -- warm-up isolation: a capture warm-up must not advance real request state

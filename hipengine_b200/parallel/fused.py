@@ -67,6 +67,30 @@ class FusedReducer:
         ctx.barrier()           # every rank has zeroed and mapped its region before the first kernel runs
         self.calls = 0
 
+    @classmethod
+    def loopback(cls, device, width: int, world: int = 2, rank: int = 0, max_rows: int = 8, n_ctas: int = 4,
+                 wait_limit: int = 2000) -> "FusedReducer":
+        """Single-process instance whose "peers" all alias this process's own region.  Only rank ``rank`` ever
+        runs, so the other ranks' stamps never arrive: used to exercise the bounded wait (it must give up after
+        ``wait_limit`` polls, record a status and leave the residual untouched) without any second GPU."""
+        L = N.lib()
+        self = cls.__new__(cls)
+        self.ctx = DistContext(rank, world, 0, torch.device(device), None, "loopback")
+        self.width, self.max_rows = width, max_rows
+        self.n_ctas, self.wait_limit = n_ctas, wait_limit
+        self.slot_floats = max_rows * width
+        self.data_bytes = 2 * world * self.slot_floats * 4
+        self.flag_bytes = 2 * world * L.he_comm_max_ctas() * 4
+        base = C.c_void_p()
+        N.check(L.he_comm_alloc(C.c_longlong(self.data_bytes + self.flag_bytes), C.byref(base)), "he_comm_alloc")
+        self._local = base.value
+        self._peer_ptrs = [self._local] * world
+        self._opened = []
+        self.epoch = torch.zeros(L.he_comm_max_ctas(), dtype=torch.int32, device=device)
+        self.partial = torch.zeros(max_rows, width, dtype=torch.float32, device=device)
+        self.calls = 0
+        return self
+
     def local_rows(self, rows: int) -> torch.Tensor:
         """Staging rows the producer kernel writes its partial products to."""
         return self.partial[:rows]
@@ -93,7 +117,8 @@ class FusedReducer:
     def close(self) -> None:
         L = N.lib()
         torch.cuda.synchronize()
-        self.ctx.barrier()
+        if self.ctx.backend != "loopback":
+            self.ctx.barrier()
         for p in self._opened:
             L.he_comm_ipc_close(C.c_void_p(p))
         self._opened = []

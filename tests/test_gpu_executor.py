@@ -67,3 +67,30 @@ def test_two_slots_are_isolated():
     h = ex.forward(batch)
     lab = ex.logits(h[:5]).clone()
     assert torch.allclose(la, lab, atol=2e-2, rtol=2e-2)
+
+
+def test_decode_graph_replays_through_native_launcher():
+    """Graph decode must equal eager decode, and the replay goes through the native control-block launcher."""
+    from hipengine_b200.models.decode_graph import DecodeGraphRunner
+    from hipengine_b200.models.executor import HybridExecutor
+    cfg = TINY_HYBRID
+    w = build_random_model(cfg, seed=5, std=0.05).to("cuda")
+    prompt = torch.randint(0, cfg.vocab, (20,), generator=torch.Generator().manual_seed(2)).tolist()
+
+    def run(use_graphs):
+        ex = HybridExecutor(w, max_slots=1, max_context=128)
+        r = DecodeGraphRunner(ex, max_rows=1, use_graphs=use_graphs)
+        first = int(ex.prefill(0, prompt).argmax(-1))
+        r.set_rows([0], [first], [len(prompt)])
+        out = [first]
+        for _ in range(6):
+            r.step(1, 128)
+            out.append(int(r.tokens[0]))
+        return out, r
+
+    eager, _ = run(False)
+    graph, r = run(True)
+    assert eager == graph
+    assert r.stats["captures"] == 1 and r.stats["hits"] == 5
+    if r.native_launch and any(r._execs.values()):
+        assert r.stats["native_launches"] == 6

@@ -1,0 +1,95 @@
+"""Failure detection and containment, injected on the host (no GPU is faulted, trapped or hung).
+
+* a runner failure naming some requests fails only those (containment);
+* a fatal error in the driver thread marks the service unhealthy and later calls are refused, not blocked;
+* a rank that never joins a collective is detected by the process-group timeout on the surviving rank (gloo).
+"""
+import os
+import time
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from hipengine_b200.config import EngineConfig, SchedulerConfig
+from hipengine_b200.generation.engine_service import EngineUnavailable, engine_from_runner
+from hipengine_b200.generation.simulator import SimulatedRunner
+from hipengine_b200.generation.types import GenerationRequest
+
+
+def _cfg():
+    return EngineConfig(max_sequence_length=1024, scheduler=SchedulerConfig(max_active_requests=4))
+
+
+def test_contained_failure_spares_other_requests():
+    cfg = _cfg()
+    runner = SimulatedRunner(cfg, fail_decode_admission=[1])
+    eng = engine_from_runner(runner, cfg, None)
+    try:
+        reqs = [GenerationRequest(prompt_token_ids=list(range(10 + i)), max_tokens=6, ignore_eos=True) for i in range(3)]
+        outs = eng.generate(reqs)
+        errs = [o for o in outs if o.error]
+        assert len(errs) == 1 and "execution_failed" in errs[0].error
+        assert all(len(o.token_ids) == 6 for o in outs if not o.error)
+        # the failed request's slot and pages were reclaimed: a new request still runs
+        again = eng.generate([GenerationRequest(prompt_token_ids=[1, 2, 3], max_tokens=3, ignore_eos=True)])
+        assert again[0].error is None and len(again[0].token_ids) == 3
+    finally:
+        eng.close()
+
+
+class _Exploding(SimulatedRunner):
+    def decode(self, rows):
+        raise ValueError("driver-thread bug")
+
+
+def test_fatal_error_marks_service_unhealthy():
+    cfg = _cfg()
+    eng = engine_from_runner(_Exploding(cfg), cfg, None)
+    try:
+        out = eng.generate([GenerationRequest(prompt_token_ids=[1, 2, 3], max_tokens=4, ignore_eos=True)])[0]
+        assert out.error and "engine_unavailable" in out.error
+        t0 = time.time()
+        with pytest.raises(EngineUnavailable):
+            eng.generate([GenerationRequest(prompt_token_ids=[1], max_tokens=1)])
+        assert time.time() - t0 < 5.0                      # refused at once, not after a timeout
+        assert eng.unhealthy["exception_type"] == "ValueError"
+    finally:
+        eng.close()
+
+
+def _rank(rank, world, port, q):
+    import datetime
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=3))
+    t = torch.ones(4)
+    dist.all_reduce(t)                                     # step 1: everyone present
+    if rank == 1:
+        q.put((rank, "left"))                              # leaves between steps, nothing in flight
+        q.close()
+        q.join_thread()
+        os._exit(0)
+    t0 = time.time()
+    try:
+        dist.all_reduce(t)                                 # step 2: the peer is gone
+        q.put((rank, "no error"))
+    except Exception as exc:
+        q.put((rank, f"detected after {time.time() - t0:.1f}s: {type(exc).__name__}"))
+    q.close()
+    q.join_thread()
+    os._exit(0)
+
+
+def test_missing_rank_is_detected_by_collective_timeout():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29800 + os.getpid() % 100
+    ps = [ctx.Process(target=_rank, args=(r, 2, port, q)) for r in range(2)]
+    for p in ps:
+        p.start()
+    res = dict(q.get(timeout=60) for _ in ps)
+    for p in ps:
+        p.join(timeout=30)
+    assert res[1] == "left"
+    assert res[0].startswith("detected"), res
