@@ -217,6 +217,11 @@ class LLM:
             self._tokenizer = tokenizer_from_metadata(w.metadata, w.config.vocab)
         return self._tokenizer
 
+    @property
+    def vocab_size(self) -> int:
+        cfg = getattr(self.model, "cfg", None)
+        return int(cfg.vocab) if cfg is not None else int(self._load_weights().config.vocab)
+
     def prepare(self) -> Dict[str, Any]:
         """Make the engine resident now (weights uploaded, KV pool and scratch reserved)."""
         t0 = time.time()
