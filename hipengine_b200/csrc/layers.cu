@@ -100,6 +100,7 @@ struct QkvArgs {
   float theta;
   float eps;
   float q_scale;           // multiplied into Q after norm/rope (1 = none)
+  int rope_denom;          // frequency spacing: inv_freq_i = theta^(-2i / rope_denom); 0 -> rope_dim
 };
 
 __device__ __forceinline__ float load_in(const void* p, int dtype, size_t i) {
@@ -135,7 +136,7 @@ __global__ void qkv_post_kernel(const QkvArgs a) {
     const int half = a.rope_dim >> 1;
     if (d < a.rope_dim) {
       const int i = d < half ? d : d - half;
-      const float inv_freq = powf(a.theta, -2.0f * (float)i / (float)a.rope_dim);
+      const float inv_freq = powf(a.theta, -2.0f * (float)i / (float)(a.rope_denom > 0 ? a.rope_denom : a.rope_dim));
       float sn, cs;
       sincosf((float)p * inv_freq, &sn, &cs);
       const float other = sh[d < half ? d + half : d - half];
@@ -304,6 +305,77 @@ HE_API int he_resid_add_f32(void* h, const void* y, long long n, cudaStream_t st
   if (n <= 0) return 0;
   if (n % 4 != 0) return -HE_ERR_BAD_ARG;
   resid_add_f32_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, stream>>>((float*)h, (const float*)y, n);
+  HE_LAUNCH_CHECK();
+  return 0;
+}
+
+// ---------------------------------------------------------------- sandwich-norm residual updates (Gemma)
+// h[t] += RMSNorm(y[t]) * w        (y fp32 or bf16; one CTA per row)
+__global__ void __launch_bounds__(256) norm_add_kernel(float* __restrict__ h, long long ldh, const void* __restrict__ y,
+                                                       int y_dtype, long long ldy, const float* __restrict__ w, int H,
+                                                       float eps) {
+  __shared__ float red[33];
+  const int t = blockIdx.x;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += 256) {
+    const float v = load_in(y, y_dtype, (size_t)t * ldy + i);
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float inv = rsqrtf(ss / (float)H + eps);
+  for (int i = threadIdx.x; i < H; i += 256)
+    h[(size_t)t * ldh + i] += load_in(y, y_dtype, (size_t)t * ldy + i) * inv * w[i];
+}
+
+// h[t] = (h[t] + RMSNorm(RMSNorm(d[t])*w1 + RMSNorm(e[t])*w2) * w3) * scalar[0]
+// d: dense-branch output, e: expert-branch output (either fp32 or bf16).
+__global__ void __launch_bounds__(256) ffn_combine_kernel(float* __restrict__ h, long long ldh,
+                                                          const void* __restrict__ d, int d_dtype, long long ldd,
+                                                          const void* __restrict__ e, int e_dtype, long long lde,
+                                                          const float* __restrict__ w1, const float* __restrict__ w2,
+                                                          const float* __restrict__ w3,
+                                                          const float* __restrict__ scalar, int H, float eps) {
+  extern __shared__ float buf[];   // [H]
+  __shared__ float red[33];
+  const int t = blockIdx.x;
+  float sd = 0.f, se = 0.f;
+  for (int i = threadIdx.x; i < H; i += 256) {
+    const float a = load_in(d, d_dtype, (size_t)t * ldd + i), b = load_in(e, e_dtype, (size_t)t * lde + i);
+    sd += a * a; se += b * b;
+  }
+  sd = block_sum(sd, red);
+  se = block_sum(se, red);
+  const float id = rsqrtf(sd / (float)H + eps), ie = rsqrtf(se / (float)H + eps);
+  float sc = 0.f;
+  for (int i = threadIdx.x; i < H; i += 256) {
+    const float c = load_in(d, d_dtype, (size_t)t * ldd + i) * id * w1[i] +
+                    load_in(e, e_dtype, (size_t)t * lde + i) * ie * w2[i];
+    buf[i] = c;
+    sc += c * c;
+  }
+  sc = block_sum(sc, red);
+  const float ic = rsqrtf(sc / (float)H + eps);
+  const float s = scalar != nullptr ? scalar[0] : 1.f;
+  for (int i = threadIdx.x; i < H; i += 256)
+    h[(size_t)t * ldh + i] = (h[(size_t)t * ldh + i] + buf[i] * ic * w3[i]) * s;
+}
+
+HE_API int he_norm_add(void* h, long long ldh, const void* y, int y_dtype, long long ldy, const void* w, int T, int H,
+                       float eps, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  norm_add_kernel<<<T, 256, 0, stream>>>((float*)h, ldh, y, y_dtype, ldy, (const float*)w, H, eps);
+  HE_LAUNCH_CHECK();
+  return 0;
+}
+
+HE_API int he_ffn_combine(void* h, long long ldh, const void* d, int d_dtype, long long ldd, const void* e, int e_dtype,
+                          long long lde, const void* w1, const void* w2, const void* w3, const void* scalar, int T,
+                          int H, float eps, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if ((size_t)H * sizeof(float) > 48 * 1024) return -HE_ERR_BAD_ARG;
+  ffn_combine_kernel<<<T, 256, (size_t)H * sizeof(float), stream>>>((float*)h, ldh, d, d_dtype, ldd, e, e_dtype, lde,
+                                                                    (const float*)w1, (const float*)w2,
+                                                                    (const float*)w3, (const float*)scalar, H, eps);
   HE_LAUNCH_CHECK();
   return 0;
 }

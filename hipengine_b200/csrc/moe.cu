@@ -236,6 +236,7 @@ struct MoeSelArgs {
   void* out;                // gate/up: bf16 [T*k][ldo]; down: fp32 residual [T][ldo], accumulated in place
   long long ldo;
   int rows_per_cta;
+  int expert_rows;          // rows between consecutive experts in w1 / w2 (0 -> N); 2N for a fused gate|up tensor
 };
 
 // grid (ceil(N / rows_per_cta), T*k), 256 threads
@@ -281,8 +282,9 @@ __global__ void __launch_bounds__(256) moe_gateup_sel_kernel(const MoeSelArgs a)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int sub = lane % lpr, rin = lane / lpr, rpp = 32 / lpr;
   const long long rb1 = hegemv::row_bytes_dev(a.qtype1, a.K), rb2 = hegemv::row_bytes_dev(a.qtype2, a.K);
-  const uint8_t* w1e = a.w1 + (size_t)e * a.N * rb1;
-  const uint8_t* w2e = a.w2 + (size_t)e * a.N * rb2;
+  const int erows = a.expert_rows > 0 ? a.expert_rows : a.N;
+  const uint8_t* w1e = a.w1 + (size_t)e * erows * rb1;
+  const uint8_t* w2e = a.w2 + (size_t)e * erows * rb2;
   const int row_end = min(a.N, (int)(blockIdx.x + 1) * a.rows_per_cta);
   for (int n0 = blockIdx.x * a.rows_per_cta + warp * rpp; n0 < row_end; n0 += 8 * rpp) {
     const int n = n0 + rin;
@@ -351,7 +353,7 @@ __global__ void __launch_bounds__(256) moe_down_sel_kernel(const MoeSelArgs a) {
     if (n < row_end) {
       for (int it = sub; it < items; it += lpr) {
         const int j = it / nblk, b = it % nblk;
-        const uint8_t* row = a.w1 + ((size_t)e_s[j] * a.N + n) * rb;
+        const uint8_t* row = a.w1 + ((size_t)e_s[j] * (a.expert_rows > 0 ? a.expert_rows : a.N) + n) * rb;
         acc += w_s[j] * dot_block(row, a.qtype1, a.K, b, s, j);
       }
     }

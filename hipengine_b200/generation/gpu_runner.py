@@ -48,8 +48,9 @@ class GpuRunner(BaseRunner):
             n_pages = executor.n_pages
         else:
             dev = "cuda"
-            self.ex = HybridExecutor(weights, device=dev, max_slots=self.max_slots + self.n_snap,
-                                     max_context=self.max_context, n_pages=n_pages)
+            from ..models import make_executor
+            self.ex = make_executor(weights, device=dev, max_slots=self.max_slots + self.n_snap,
+                                    max_context=self.max_context, n_pages=n_pages)
         self.device = self.ex.device
         self.pool = PagePool(n_pages, self.page)
         self.radix = RadixCache(self.page, PrefixCompatibilityKey(self.cfg.arch, kv_storage=config.kv.storage,

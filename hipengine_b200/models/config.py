@@ -55,7 +55,23 @@ class ModelConfig:
     nextn_layers: int = 0
     max_context: int = 8192
 
+    swa_rope_theta: float = 10000.0      # Gemma: sliding layers rotate the whole head with this base
+    global_rope_fraction: float = 0.25   # Gemma: global layers rotate this fraction of the head ("proportional")
+
     # ---- derived
+    def is_global_layer(self, i: int) -> bool:
+        """Gemma-style schedule: every ``swa_pattern``-th layer attends globally, the rest use a sliding window."""
+        return self.swa_pattern > 0 and (i + 1) % self.swa_pattern == 0
+
+    def layer_head_dim(self, i: int) -> int:
+        return self.global_head_dim if (self.is_global_layer(i) and self.global_head_dim) else self.head_dim
+
+    def layer_kv_heads(self, i: int) -> int:
+        return self.global_kv_heads if (self.is_global_layer(i) and self.global_kv_heads) else self.n_kv_heads
+
+    def layer_window(self, i: int) -> int:
+        return 0 if (self.swa_pattern == 0 or self.is_global_layer(i)) else self.sliding_window
+
     @property
     def is_hybrid(self) -> bool:
         return self.full_attention_interval > 0
@@ -161,7 +177,7 @@ GEMMA4_26B_A4B = ModelConfig(arch="gemma4", n_layers=30, hidden=2816, vocab=2621
                              act="gelu_tanh", tie_embeddings=True, max_context=262144)
 
 TINY_GEMMA4 = ModelConfig(arch="gemma4", n_layers=6, hidden=256, vocab=2048, n_heads=4, n_kv_heads=2,
-                          head_dim=64, ffn=512, rope_theta=1e6, rope_dim=64, qk_norm=True, attn_scale=1.0,
+                          head_dim=64, ffn=288, rope_theta=1e6, rope_dim=64, qk_norm=True, attn_scale=1.0,
                           sliding_window=32, swa_pattern=6, global_head_dim=128, global_kv_heads=1,
                           n_experts=8, n_experts_used=2, expert_ffn=128, final_softcap=30.0,
                           embed_scale=16.0, act="gelu_tanh", tie_embeddings=True, max_context=2048)

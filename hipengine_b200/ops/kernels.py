@@ -39,7 +39,8 @@ class _QkvArgs(C.Structure):
                 ("q_out", c_vp), ("gate_out", c_vp), ("kv_cache", c_vp), ("block_table", c_vp),
                 ("slot", c_vp), ("pos", c_vp), ("max_pages", C.c_int),
                 ("H", C.c_int), ("Hkv", C.c_int), ("D", C.c_int), ("page", C.c_int), ("gated", C.c_int),
-                ("rope_dim", C.c_int), ("theta", C.c_float), ("eps", C.c_float), ("q_scale", C.c_float)]
+                ("rope_dim", C.c_int), ("theta", C.c_float), ("eps", C.c_float), ("q_scale", C.c_float),
+                ("rope_denom", C.c_int)]
 
 
 class _ConvArgs(C.Structure):
@@ -81,7 +82,7 @@ class _MoeSelArgs(C.Structure):
     _fields_ = [("x", c_vp), ("ldx", c_ll), ("norm_w", c_vp), ("eps", C.c_float), ("ids", c_vp), ("wts", c_vp),
                 ("w1", c_vp), ("w2", c_vp), ("qtype1", C.c_int), ("qtype2", C.c_int),
                 ("T", C.c_int), ("k", C.c_int), ("K", C.c_int), ("N", C.c_int), ("act", C.c_int),
-                ("out", c_vp), ("ldo", c_ll), ("rows_per_cta", C.c_int)]
+                ("out", c_vp), ("ldo", c_ll), ("rows_per_cta", C.c_int), ("expert_rows", C.c_int)]
 
 
 _CHECKED = False
@@ -307,7 +308,8 @@ def resid_add_bf16(h: torch.Tensor, y: torch.Tensor) -> None:
 def qkv_post(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_norm, k_norm, q_out: torch.Tensor,
              gate_out: Optional[torch.Tensor], kv_cache: torch.Tensor, block_table: torch.Tensor,
              slot: torch.Tensor, pos: torch.Tensor, H: int, Hkv: int, D: int, page: int, gated: bool,
-             rope_dim: int, theta: float, eps: float, q_scale: float = 1.0, v_norm: bool = False) -> None:
+             rope_dim: int, theta: float, eps: float, q_scale: float = 1.0, v_norm: bool = False,
+             rope_denom: int = 0) -> None:
     _check_abi()
     T = q.shape[0]
     a = _QkvArgs()
@@ -321,6 +323,7 @@ def qkv_post(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_norm, k_norm, 
     a.max_pages = block_table.shape[1]
     a.H, a.Hkv, a.D, a.page, a.gated = H, Hkv, D, page, int(gated)
     a.rope_dim, a.theta, a.eps, a.q_scale = rope_dim, theta, eps, q_scale
+    a.rope_denom = rope_denom
     N.check(N.lib().he_qkv_post(C.byref(a), C.c_int(T), _stream()), "he_qkv_post")
 
 
@@ -422,6 +425,25 @@ def resid_add_f32(h: torch.Tensor, y: torch.Tensor) -> None:
             "he_resid_add_f32")
 
 
+def norm_add(h: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: float) -> None:
+    """h += RMSNorm(y) * w, row-wise (sandwich norm on a branch output)."""
+    T, H = h.shape
+    N.check(N.lib().he_norm_add(c_vp(h.data_ptr()), c_ll(h.stride(0)), c_vp(y.data_ptr()), C.c_int(_dt(y)),
+                                c_ll(y.stride(0)), c_vp(w.data_ptr()), C.c_int(T), C.c_int(H), C.c_float(eps),
+                                _stream()), "he_norm_add")
+
+
+def ffn_combine(h: torch.Tensor, dense: torch.Tensor, expert: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor,
+                w3: torch.Tensor, scalar: Optional[torch.Tensor], eps: float) -> None:
+    """h = (h + RMSNorm(RMSNorm(dense)*w1 + RMSNorm(expert)*w2) * w3) * scalar."""
+    T, H = h.shape
+    N.check(N.lib().he_ffn_combine(c_vp(h.data_ptr()), c_ll(h.stride(0)), c_vp(dense.data_ptr()),
+                                   C.c_int(_dt(dense)), c_ll(dense.stride(0)), c_vp(expert.data_ptr()),
+                                   C.c_int(_dt(expert)), c_ll(expert.stride(0)), c_vp(w1.data_ptr()),
+                                   c_vp(w2.data_ptr()), c_vp(w3.data_ptr()), c_vp(_p(scalar)), C.c_int(T),
+                                   C.c_int(H), C.c_float(eps), _stream()), "he_ffn_combine")
+
+
 # ----------------------------------------------------------------------------- mixture of experts
 
 def moe_route(logits: torch.Tensor, k: int, ids: torch.Tensor, wts: torch.Tensor, n_experts: Optional[int] = None,
@@ -466,13 +488,16 @@ def moe_scale_rows(act: torch.Tensor, sg: torch.Tensor) -> None:
                                       c_vp(sg.data_ptr()), c_ll(sg.stride(0)), _stream()), "he_moe_scale_rows")
 
 
-def _moe_sel(fn: str, x, norm_w, eps, ids, wts, w1: "DeviceWeight", w2, n_rows: int, out, act: str) -> None:
+def _moe_sel(fn: str, x, norm_w, eps, ids, wts, w1: "DeviceWeight", w2, n_rows: int, out, act: str,
+             expert_rows: int = 0, w2_row0: int = 0) -> None:
     _check_abi()
     a = _MoeSelArgs()
     a.x, a.ldx, a.norm_w, a.eps = x.data_ptr(), x.stride(0), _p(norm_w), eps
     a.ids, a.wts = ids.data_ptr(), wts.data_ptr()
     a.w1, a.qtype1 = w1.ptr, w1.qtype
-    a.w2, a.qtype2 = (w2.ptr, w2.qtype) if w2 is not None else (None, w1.qtype)
+    a.w2, a.qtype2 = (w2.ptr + w2_row0 * device_row_bytes(w2.qtype, w2.n_cols), w2.qtype) if w2 is not None \
+        else (None, w1.qtype)
+    a.expert_rows = expert_rows
     a.T, a.k, a.K, a.N = ids.shape[0], ids.shape[1], w1.n_cols, n_rows
     a.act = 0 if act == "silu" else 1
     a.out, a.ldo = out.data_ptr(), out.stride(0)
@@ -481,9 +506,14 @@ def _moe_sel(fn: str, x, norm_w, eps, ids, wts, w1: "DeviceWeight", w2, n_rows: 
 
 def moe_gateup_sel(h: torch.Tensor, norm_w: Optional[torch.Tensor], eps: float, ids: torch.Tensor,
                    wts: torch.Tensor, w_gate: "DeviceWeight", w_up: "DeviceWeight", n_ff: int, out: torch.Tensor,
-                   act: str = "silu") -> None:
-    """out[t*k+j, :] = act(Wg[e] xn_t) * (Wu[e] xn_t) (bf16) for the selected experts e = ids[t, j]."""
-    _moe_sel("he_moe_gateup_sel", h, norm_w, eps, ids, wts, w_gate, w_up, n_ff, out, act)
+                   act: str = "silu", fused_gate_up: bool = False) -> None:
+    """out[t*k+j, :] = act(Wg[e] xn_t) * (Wu[e] xn_t) (bf16) for the selected experts e = ids[t, j].
+    ``fused_gate_up``: ``w_gate`` holds, per expert, n_ff gate rows followed by n_ff up rows (``w_up`` ignored)."""
+    if fused_gate_up:
+        _moe_sel("he_moe_gateup_sel", h, norm_w, eps, ids, wts, w_gate, w_gate, n_ff, out, act,
+                 expert_rows=2 * n_ff, w2_row0=n_ff)
+    else:
+        _moe_sel("he_moe_gateup_sel", h, norm_w, eps, ids, wts, w_gate, w_up, n_ff, out, act)
 
 
 def moe_down_sel(act_rows: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_down: "DeviceWeight", n_out: int,
