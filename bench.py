@@ -251,7 +251,7 @@ def main() -> int:
             "metric": "decode_tok_s (27B dense hybrid Q4_K_M, bf16 KV, batch 1 per stream, 4096 prefill + 256 decode)",
             "value": round(decode_tok_s, 3), "unit": "tok/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round((m["prefill_ms"] + m["decode_ms"]) / args.steps, 3),
-            "higher_is_better": True, "scaling": "strong" if mode == "tp" else "weak",
+            "higher_is_better": True, "scaling": "weak" if mode == "dp" else "strong",
             "vs_baseline": round(decode_tok_s / BASELINE_DECODE_TOK_S, 3), "dtype": "bf16",
             "data": "synthetic (random-init N(0,0.02) weights quantized to Q4_K_M-style GGUF blocks, uniform random prompt ids)",
             "config": {"model": args.model, "global_batch": streams, "seq_len": args.prompt_len,

@@ -99,9 +99,74 @@ def bench_gemv(N, K, qtype="q4_k", rows=1):
             f"frac_of_{pk['src']}_hbm": round(gbs / pk["hbm_gbs"], 3)}
 
 
+def bench_gdn_scan(T, Hv=48, G=16, n_seg=1):
+    """Prefill scan of one gated delta-net layer: T tokens in n_seg segments (27B geometry by default)."""
+    from hipengine_b200.ops import kernels as Kn
+    pk = peaks()
+    S = 128
+    C = 2 * G * S + Hv * S
+    qkv = torch.randn(T, C, device="cuda") * 0.1
+    decay = torch.rand(T, Hv, device="cuda") * 0.2 + 0.8
+    beta = torch.rand(T, Hv, device="cuda")
+    state = torch.zeros(n_seg, Hv, S, S, device="cuda")
+    seg_start = torch.arange(0, T + 1, T // n_seg, device="cuda", dtype=torch.int32)[:n_seg + 1].contiguous()
+    seg_slot = torch.arange(n_seg, device="cuda", dtype=torch.int32)
+    out = torch.empty(T, Hv, S, device="cuda")
+    fn = lambda i: Kn.gdn_scan(qkv, decay, beta, state, seg_start, seg_slot, out, G, Hv)
+    ms = time_launches(fn, 1)
+    flops = 6.0 * T * Hv * S * S          # decay, k.S, rank-1 update, q.S: about 6 flop per state element per token
+    bytes_ = (qkv.numel() + out.numel()) * 4.0 + 2.0 * state.numel() * 4
+    return {"kernel": "gdn_scan", "T": T, "Hv": Hv, "n_seg": n_seg, "ms": round(ms, 4),
+            "tflops_fp32": round(flops / ms / 1e9, 2), "us_per_token": round(1e3 * ms / (T / n_seg), 3),
+            "GBps": round(bytes_ / ms / 1e6, 1), f"frac_of_{pk['src']}_hbm": round(bytes_ / ms / 1e6 / pk["hbm_gbs"], 3)}
+
+
+def bench_conv(T, C=10240):
+    from hipengine_b200.ops import kernels as Kn
+    pk = peaks()
+    x = (torch.randn(T, C, device="cuda") * 0.1).bfloat16()
+    w = torch.randn(C, 4, device="cuda")
+    state = torch.zeros(1, C, 3, device="cuda")
+    seg_start = torch.tensor([0, T], device="cuda", dtype=torch.int32)
+    seg_slot = torch.zeros(1, device="cuda", dtype=torch.int32)
+    tok_seg = torch.zeros(T, device="cuda", dtype=torch.int32)
+    out = torch.empty(T, C, device="cuda")
+    fn = lambda i: Kn.conv1d(x, w, state, seg_start, seg_slot, tok_seg, out, C)
+    ms = time_launches(fn, 1)
+    bytes_ = T * C * (2.0 + 4.0)
+    return {"kernel": "conv1d+state", "T": T, "C": C, "ms": round(ms, 4), "GBps": round(bytes_ / ms / 1e6, 1),
+            f"frac_of_{pk['src']}_hbm": round(bytes_ / ms / 1e6 / pk["hbm_gbs"], 3)}
+
+
+def bench_attn_decode(ctx, H=24, Hkv=4, D=256, rows=1):
+    from hipengine_b200.ops import kernels as Kn
+    pk = peaks()
+    page = 16
+    n_pages = (ctx + page - 1) // page
+    nvar = max(2, int(260e6 // (n_pages * 2 * Hkv * page * D * 2)) + 1)
+    caches = [(torch.randn(n_pages + 1, 2, Hkv, page, D, device="cuda") * 0.3).bfloat16() for _ in range(nvar)]
+    bt = (torch.arange(n_pages, device="cuda", dtype=torch.int32) + 1).reshape(1, -1).repeat(rows, 1).contiguous()
+    slot = torch.arange(rows, device="cuda", dtype=torch.int32)
+    ctx_len = torch.full((rows,), ctx, device="cuda", dtype=torch.int32)
+    q = torch.randn(rows, H, D, device="cuda").bfloat16()
+    gate = torch.randn(rows, H, D, device="cuda").bfloat16()
+    split_len = 64 if ctx <= 8192 else (128 if ctx <= 32768 else 256)
+    max_splits = (ctx + split_len - 1) // split_len
+    part = torch.empty(Kn.attn_decode_scratch_floats(rows, H, max_splits, D), device="cuda")
+    out = torch.empty(rows, H * D, device="cuda", dtype=torch.bfloat16)
+    fn = lambda i: Kn.attn_decode(q, gate, caches[i], bt, slot, ctx_len, part, out, H, Hkv, D, page, split_len,
+                                  max_splits, D ** -0.5)
+    ms = time_launches(fn, nvar)
+    bytes_ = ctx * 2.0 * Hkv * D * 2 * rows
+    return {"kernel": "attn_decode(split+reduce)", "ctx": ctx, "rows": rows, "ms": round(ms, 4),
+            "GBps": round(bytes_ / ms / 1e6, 1), f"frac_of_{pk['src']}_hbm": round(bytes_ / ms / 1e6 / pk["hbm_gbs"], 3)}
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "gemv", "all"])
+    ap.add_argument("what", choices=["gemm", "gemv", "gdn", "conv", "attn", "all"])
+    ap.add_argument("--t", type=int, default=4096)
+    ap.add_argument("--ctx", type=int, default=4096)
     ap.add_argument("--m", type=int, default=4096)
     ap.add_argument("--n", type=int, default=17408)
     ap.add_argument("--k", type=int, default=5120)
@@ -114,6 +179,12 @@ def main():
         out.append(bench_gemm(a.m, a.n, a.k, a.impl))
     elif a.what == "gemv":
         out.append(bench_gemv(a.n, a.k, a.qtype, a.rows))
+    elif a.what == "gdn":
+        out.append(bench_gdn_scan(a.t))
+    elif a.what == "conv":
+        out.append(bench_conv(a.t))
+    elif a.what == "attn":
+        out.append(bench_attn_decode(a.ctx, rows=a.rows))
     else:
         for (m, n, k) in [(4096, 10240, 5120), (4096, 34816, 5120), (4096, 5120, 17408), (4096, 5120, 6144)]:
             out.append(bench_gemm(m, n, k, "tcgen05"))
@@ -122,6 +193,10 @@ def main():
                           (5120, 6144, "q4_k"), (62080, 5120, "q6_k"), (8192, 5120, "q8_0")]:
             for r in (1, 4):
                 out.append(bench_gemv(n, k, q, r))
+        out.append(bench_gdn_scan(4096))
+        out.append(bench_conv(4096))
+        for c in (4096, 32768):
+            out.append(bench_attn_decode(c))
     for o in out:
         print(json.dumps(o))
 

@@ -34,6 +34,8 @@ template <int D, int G>
 __global__ void __launch_bounds__(256) attn_decode_split_kernel(const AttnDecArgs a) {
   extern __shared__ __align__(16) float smem[];
   const int sp = blockIdx.x, hk = blockIdx.y, r = blockIdx.z;
+  pdl_wait();
+  pdl_launch();
   const int ctx = a.ctx_len[r];
   const int start = (a.window > 0 && ctx > a.window) ? ctx - a.window : 0;
   const int k0 = start + sp * a.split_len;
@@ -187,6 +189,8 @@ __global__ void attn_decode_reduce_kernel(const AttnDecArgs a) {
   __shared__ float red[33];
   const int h = blockIdx.x, r = blockIdx.y, d = threadIdx.x;
   const int D = a.D;
+  pdl_wait();
+  pdl_launch();
   const int ctx = a.ctx_len[r];
   const int start = (a.window > 0 && ctx > a.window) ? ctx - a.window : 0;
   const int ns = (ctx - start + a.split_len - 1) / a.split_len;
@@ -232,8 +236,8 @@ int launch_split(const AttnDecArgs& a, cudaStream_t stream) {
     configured = smem;
   }
   dim3 grid(a.max_splits, a.Hkv, a.R);
-  attn_decode_split_kernel<D, G><<<grid, 256, smem, stream>>>(a);
-  HE_LAUNCH_CHECK();
+  cudaError_t le = launch_pdl(attn_decode_split_kernel<D, G>, grid, dim3(256), smem, stream, a);
+  if (le != cudaSuccess) return (int)le;
   return 0;
 }
 
@@ -267,8 +271,9 @@ HE_API int he_attn_decode(const AttnDecArgs* args, cudaStream_t stream) {
   }
   if (rc != 0) return rc;
   dim3 grid(a.H, a.R);
-  attn_decode_reduce_kernel<<<grid, a.D, (size_t)a.max_splits * sizeof(float), stream>>>(a);
-  HE_LAUNCH_CHECK();
+  cudaError_t le = launch_pdl(attn_decode_reduce_kernel, grid, dim3(a.D), (size_t)a.max_splits * sizeof(float),
+                              stream, a);
+  if (le != cudaSuccess) return (int)le;
   return 0;
 }
 HE_API int he_attn_dec_args_size() { return (int)sizeof(AttnDecArgs); }

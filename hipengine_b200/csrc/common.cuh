@@ -136,3 +136,39 @@ __device__ __forceinline__ int byte_of(const uint4& v, int i) {
 }
 
 }  // namespace he
+
+// ---------------------------------------------------------------- programmatic dependent launch
+// Kernels on the decode path are launched with the "programmatic stream serialization" attribute: the grid may be
+// scheduled while its predecessor in the stream is still draining, which hides the launch latency between the
+// many short kernels of a decode step.  Such a kernel must call pdl_wait() before it reads anything the predecessor
+// wrote (or writes anything the predecessor reads); pdl_launch() lets its own successor start being scheduled.
+// HE_PDL=0 in the environment turns the attribute off (plain stream order).
+#include <cstdlib>
+namespace he {
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;"); }
+
+inline bool pdl_enabled() {
+  static const bool on = []() {
+    const char* e = getenv("HE_PDL");
+    return !(e != nullptr && e[0] == '0');
+  }();
+  return on;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+}  // namespace he

@@ -68,23 +68,31 @@ constexpr int TCH = 16;       // tokens staged per shared-memory chunk
 
 constexpr int KPAD = DK + DK / 8;   // 4 pad floats per 32 so the 4 row groups of a column land in different banks
 
-// grid (n_seg, Hv, DV/SLICE), block 128.  Lane (col = lane/4, ks = lane%4) owns rows ks*32 .. ks*32+31 of one column.
-__global__ void __launch_bounds__(128) gdn_scan_kernel(const GdnScanArgs p) {
+// grid (n_seg, Hv, DV/SLICE), block 32*LPC.  A column of S is owned by LPC lanes of one warp; lane ks owns rows
+// ks*RPL .. ks*RPL+RPL-1 (RPL = 128/LPC).  LPC = 4 keeps more of the state per thread (fewer shuffles per token);
+// LPC = 8 doubles the warps when only a few (segment, head) pairs exist, which is what hides the issue latency of
+// this strictly sequential recurrence during a single-request prefill.
+template <int LPC>
+__global__ void __launch_bounds__(32 * LPC) gdn_scan_kernel(const GdnScanArgs p) {
+  constexpr int RPL = DK / LPC;            // rows per lane: 32 or 16
+  constexpr int NT = 32 * LPC;             // threads
+  constexpr int CPW = 32 / LPC;            // columns per warp
   __shared__ __align__(16) float sq[TCH][KPAD];
   __shared__ __align__(16) float sk[TCH][KPAD];
   __shared__ float sv[TCH][SLICE];
   __shared__ float sdec[TCH], sbeta[TCH];
   const int sg = blockIdx.x, h = blockIdx.y, sl = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int cw = warp * 8 + (lane >> 2);                // column inside the slice
-  const int col = sl * SLICE + cw;                      // column of S owned (with 3 other lanes)
-  const int ks = lane & 3;
+  const int cw = warp * CPW + lane / LPC;               // column inside the slice
+  const int col = sl * SLICE + cw;                      // column of S owned (with LPC-1 other lanes)
+  const int ks = lane % LPC;
   const int kh = h % p.G;
   const int s0 = p.seg_start[sg], s1 = p.seg_start[sg + 1];
   float* Sg = p.state + (((size_t)p.seg_slot[sg] * p.Hv + h) * DK) * DV;
-  float S[32];
+  float S[RPL];
 #pragma unroll
-  for (int i = 0; i < 32; ++i) S[i] = Sg[(size_t)(ks * 32 + i) * DV + col];
+  for (int i = 0; i < RPL; ++i) S[i] = Sg[(size_t)(ks * RPL + i) * DV + col];
+  const int koff = ks * RPL + ((ks * RPL) >> 5) * 4;    // padded offset of this lane's rows in sq / sk
 
   const size_t q_off = (size_t)kh * DK, k_off = (size_t)p.G * DK + (size_t)kh * DK;
   const size_t v_off = (size_t)2 * p.G * DK + (size_t)h * DV + sl * SLICE;
@@ -92,14 +100,14 @@ __global__ void __launch_bounds__(128) gdn_scan_kernel(const GdnScanArgs p) {
   for (int c0 = s0; c0 < s1; c0 += TCH) {
     const int n = min(TCH, s1 - c0);
     __syncthreads();
-    for (int i = tid; i < n * (DK / 4); i += 128) {
+    for (int i = tid; i < n * (DK / 4); i += NT) {
       const int tt = i / (DK / 4), d4 = (i % (DK / 4)) * 4;
       const float* row = p.qkv + (size_t)(c0 + tt) * p.C;
       const int dst = d4 + (d4 >> 5) * 4;
       *reinterpret_cast<float4*>(&sq[tt][dst]) = *reinterpret_cast<const float4*>(row + q_off + d4);
       *reinterpret_cast<float4*>(&sk[tt][dst]) = *reinterpret_cast<const float4*>(row + k_off + d4);
     }
-    for (int i = tid; i < n * SLICE; i += 128) {
+    for (int i = tid; i < n * SLICE; i += NT) {
       const int tt = i / SLICE, d = i % SLICE;
       sv[tt][d] = p.qkv[(size_t)(c0 + tt) * p.C + v_off + d];
     }
@@ -110,46 +118,46 @@ __global__ void __launch_bounds__(128) gdn_scan_kernel(const GdnScanArgs p) {
     __syncthreads();
     for (int tt = 0; tt < n; ++tt) {
       const float dec = sdec[tt], bet = sbeta[tt];
-      float kr[32];
+      float kr[RPL];
 #pragma unroll
-      for (int i4 = 0; i4 < 8; ++i4) {
-        const float4 kv4 = *reinterpret_cast<const float4*>(&sk[tt][ks * 36 + i4 * 4]);
+      for (int i4 = 0; i4 < RPL / 4; ++i4) {
+        const float4 kv4 = *reinterpret_cast<const float4*>(&sk[tt][koff + i4 * 4]);
         kr[i4 * 4] = kv4.x; kr[i4 * 4 + 1] = kv4.y; kr[i4 * 4 + 2] = kv4.z; kr[i4 * 4 + 3] = kv4.w;
       }
       // four independent partial sums per reduction keep the FMA pipe busy (the chains are otherwise serial)
       float kv4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
+      for (int i = 0; i < RPL; ++i) {
         S[i] *= dec;
         kv4[i & 3] += kr[i] * S[i];
       }
       float kv = (kv4[0] + kv4[1]) + (kv4[2] + kv4[3]);
-      kv += __shfl_xor_sync(0xffffffffu, kv, 1);
-      kv += __shfl_xor_sync(0xffffffffu, kv, 2);
+#pragma unroll
+      for (int o = 1; o < LPC; o <<= 1) kv += __shfl_xor_sync(0xffffffffu, kv, o);
       const float delta = (sv[tt][cw] - kv) * bet;
       float o4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int i4 = 0; i4 < 8; ++i4) {
-        const float4 q4 = *reinterpret_cast<const float4*>(&sq[tt][ks * 36 + i4 * 4]);
+      for (int i4 = 0; i4 < RPL / 4; ++i4) {
+        const float4 q4 = *reinterpret_cast<const float4*>(&sq[tt][koff + i4 * 4]);
         S[i4 * 4] += kr[i4 * 4] * delta;         o4[0] += q4.x * S[i4 * 4];
         S[i4 * 4 + 1] += kr[i4 * 4 + 1] * delta; o4[1] += q4.y * S[i4 * 4 + 1];
         S[i4 * 4 + 2] += kr[i4 * 4 + 2] * delta; o4[2] += q4.z * S[i4 * 4 + 2];
         S[i4 * 4 + 3] += kr[i4 * 4 + 3] * delta; o4[3] += q4.w * S[i4 * 4 + 3];
       }
       float o = (o4[0] + o4[1]) + (o4[2] + o4[3]);
-      o += __shfl_xor_sync(0xffffffffu, o, 1);
-      o += __shfl_xor_sync(0xffffffffu, o, 2);
+#pragma unroll
+      for (int of = 1; of < LPC; of <<= 1) o += __shfl_xor_sync(0xffffffffu, o, of);
       if (ks == 0) p.out[((size_t)(c0 + tt) * p.Hv + h) * DV + col] = o;
       if (p.journal != nullptr) {
         float* J = p.journal + (((size_t)(c0 + tt) * p.Hv + h) * DK) * DV;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) J[(size_t)(ks * 32 + i) * DV + col] = S[i];
+        for (int i = 0; i < RPL; ++i) J[(size_t)(ks * RPL + i) * DV + col] = S[i];
       }
     }
   }
   if (p.write_state) {
 #pragma unroll
-    for (int i = 0; i < 32; ++i) Sg[(size_t)(ks * 32 + i) * DV + col] = S[i];
+    for (int i = 0; i < RPL; ++i) Sg[(size_t)(ks * RPL + i) * DV + col] = S[i];
   }
 }
 
@@ -221,6 +229,8 @@ struct GdnDecodeArgs {
 // and (block 0) the decay / beta gates of the row.
 __global__ void __launch_bounds__(128) gdn_decode_pre_kernel(const GdnDecodeArgs p) {
   __shared__ float red[32];
+  pdl_wait();
+  pdl_launch();
   const int r = blockIdx.y, blk = blockIdx.x, c = blk * 128 + threadIdx.x;
   float* st = p.conv_state + ((size_t)p.slot[r] * p.C + c) * 3;
   const float4 w = __ldg(reinterpret_cast<const float4*>(p.conv_w + (size_t)c * 4));
@@ -254,6 +264,8 @@ __global__ void __launch_bounds__(512) gdn_decode_step_kernel(const GdnDecodeArg
   const int col = tid >> 2, ks = tid & 3;
   const int kh = h % p.G;
   const float* row = p.qkv + (size_t)r * p.C;
+  pdl_wait();
+  pdl_launch();
   if (tid < 128) {
     const int dst = tid + (tid >> 5) * 4;
     sq[dst] = row[(size_t)kh * DK + tid];
@@ -319,7 +331,10 @@ HE_API int he_gdn_prep_args_size() { return (int)sizeof(GdnPrepArgs); }
 HE_API int he_gdn_scan(const GdnScanArgs* args, cudaStream_t stream) {
   if (args->T <= 0 || args->n_seg <= 0) return 0;
   dim3 grid(args->n_seg, args->Hv, DV / SLICE);
-  gdn_scan_kernel<<<grid, 128, 0, stream>>>(*args);
+  // few (segment, head) pairs and long segments: spread every column over 8 lanes to double the resident warps
+  const bool wide = (long long)args->n_seg * args->Hv * (DV / SLICE) <= 1024 && args->T >= 64 * args->n_seg;
+  if (wide) gdn_scan_kernel<8><<<grid, 256, 0, stream>>>(*args);
+  else gdn_scan_kernel<4><<<grid, 128, 0, stream>>>(*args);
   HE_LAUNCH_CHECK();
   return 0;
 }
@@ -354,10 +369,10 @@ HE_API int he_gdn_decode(const GdnDecodeArgs* args, cudaStream_t stream) {
   const GdnDecodeArgs& a = *args;
   if (a.R <= 0) return 0;
   if (a.C % 128 != 0 || a.C != 2 * a.G * 128 + a.Hv * 128 || a.Hv % a.G != 0) return -HE_ERR_BAD_ARG;
-  gdn_decode_pre_kernel<<<dim3(a.C / 128, a.R), 128, 0, stream>>>(a);
-  HE_LAUNCH_CHECK();
-  gdn_decode_step_kernel<<<dim3(a.Hv, a.R), 512, 0, stream>>>(a);
-  HE_LAUNCH_CHECK();
+  cudaError_t e = launch_pdl(gdn_decode_pre_kernel, dim3(a.C / 128, a.R), dim3(128), 0, stream, a);
+  if (e != cudaSuccess) return (int)e;
+  e = launch_pdl(gdn_decode_step_kernel, dim3(a.Hv, a.R), dim3(512), 0, stream, a);
+  if (e != cudaSuccess) return (int)e;
   return 0;
 }
 HE_API int he_gdn_decode_args_size() { return (int)sizeof(GdnDecodeArgs); }

@@ -113,6 +113,8 @@ __global__ void qkv_post_kernel(const QkvArgs a) {
   __shared__ float red[33];
   const int t = blockIdx.x, hh = blockIdx.y, d = threadIdx.x;
   const int D = a.D;
+  pdl_wait();
+  pdl_launch();
   int kind, h;  // 0 q, 1 k, 2 v
   if (hh < a.H) { kind = 0; h = hh; }
   else if (hh < a.H + a.Hkv) { kind = 1; h = hh - a.H; }
@@ -172,61 +174,75 @@ struct ConvArgs {
   int C, KW, T, n_seg;
 };
 
-// one thread per (token, 8 channels); KWT > 0 fixes the kernel width at compile time (registers, no local memory)
+// one thread per (8 channels, CONV_TOK consecutive tokens); the 8 x KW filter taps are loaded once per thread
+// and reused for all its tokens (they used to dominate the load traffic at one token per thread).
+constexpr int CONV_TOK = 8;
 template <int KWT>
-__global__ void conv_fwd_kernel(const ConvArgs a) {
+__global__ void __launch_bounds__(256) conv_fwd_kernel(const ConvArgs a) {
   const int C8 = a.C >> 3;
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= (long long)a.T * C8) return;
-  const int t = (int)(i / C8), c = (int)(i % C8) * 8;
-  const int sg = a.tok_seg[t];
-  const int s0 = a.seg_start[sg];
-  const int local = t - s0;
+  const int n_tchunks = (a.T + CONV_TOK - 1) / CONV_TOK;
+  if (i >= (long long)n_tchunks * C8) return;
+  const int t_first = (int)(i / C8) * CONV_TOK, c = (int)(i % C8) * 8;
   constexpr int KW = KWT;
-  const float* st = a.state + ((size_t)a.seg_slot[sg] * a.C + c) * (KW - 1);
-  float acc[8], win[KW][8];
-#pragma unroll
-  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
   float wreg[8][KW];
-#pragma unroll
-  for (int e = 0; e < 8; ++e)
-#pragma unroll
-    for (int k = 0; k < KW; ++k) wreg[e][k] = __ldg(a.w + (size_t)(c + e) * KW + k);
-#pragma unroll
-  for (int k = 0; k < KW; ++k) {
-    const int idx = local + k;  // index into [state(KW-1) ++ x_seg]
-    if (idx < KW - 1) {
-#pragma unroll
-      for (int e = 0; e < 8; ++e) win[k][e] = st[(size_t)e * (KW - 1) + idx];
-    } else {
-      const size_t off = (size_t)(s0 + idx - (KW - 1)) * a.x_stride + c;
-      if (a.in_dtype == 0) {
-        const float4 v0 = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.x) + off);
-        const float4 v1 = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.x) + off + 4);
-        win[k][0] = v0.x; win[k][1] = v0.y; win[k][2] = v0.z; win[k][3] = v0.w;
-        win[k][4] = v1.x; win[k][5] = v1.y; win[k][6] = v1.z; win[k][7] = v1.w;
-      } else {
-        const uint4 u = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.x) + off);
-        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&u);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 f = __bfloat1622float2(h2[e]);
-          win[k][2 * e] = f.x; win[k][2 * e + 1] = f.y;
-        }
-      }
-    }
-#pragma unroll
-    for (int e = 0; e < 8; ++e) acc[e] += win[k][e] * wreg[e][k];
-  }
-  float* o = a.out + (size_t)t * a.C + c;
-  *reinterpret_cast<float4*>(o) = make_float4(silu_f(acc[0]), silu_f(acc[1]), silu_f(acc[2]), silu_f(acc[3]));
-  *reinterpret_cast<float4*>(o + 4) = make_float4(silu_f(acc[4]), silu_f(acc[5]), silu_f(acc[6]), silu_f(acc[7]));
-  if (a.journal != nullptr) {
+  if constexpr (KW == 4) {
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
-      float* j = a.journal + ((size_t)t * a.C + c + e) * (KW - 1);
+      const float4 w4 = __ldg(reinterpret_cast<const float4*>(a.w + (size_t)(c + e) * 4));
+      wreg[e][0] = w4.x; wreg[e][1] = w4.y; wreg[e][2] = w4.z; wreg[e][3] = w4.w;
+    }
+  } else {
 #pragma unroll
-      for (int k = 1; k < KW; ++k) j[k - 1] = win[k][e];
+    for (int e = 0; e < 8; ++e)
+#pragma unroll
+      for (int k = 0; k < KW; ++k) wreg[e][k] = __ldg(a.w + (size_t)(c + e) * KW + k);
+  }
+  const int t_last = min(a.T, t_first + CONV_TOK);
+  for (int t = t_first; t < t_last; ++t) {
+    const int sg = a.tok_seg[t];
+    const int s0 = a.seg_start[sg];
+    const int local = t - s0;
+    const float* st = a.state + ((size_t)a.seg_slot[sg] * a.C + c) * (KW - 1);
+    float acc[8], win[KW][8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+#pragma unroll
+    for (int k = 0; k < KW; ++k) {
+      const int idx = local + k;  // index into [state(KW-1) ++ x_seg]
+      if (idx < KW - 1) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) win[k][e] = st[(size_t)e * (KW - 1) + idx];
+      } else {
+        const size_t off = (size_t)(s0 + idx - (KW - 1)) * a.x_stride + c;
+        if (a.in_dtype == 0) {
+          const float4 v0 = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.x) + off);
+          const float4 v1 = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.x) + off + 4);
+          win[k][0] = v0.x; win[k][1] = v0.y; win[k][2] = v0.z; win[k][3] = v0.w;
+          win[k][4] = v1.x; win[k][5] = v1.y; win[k][6] = v1.z; win[k][7] = v1.w;
+        } else {
+          const uint4 u = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.x) + off);
+          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(h2[e]);
+            win[k][2 * e] = f.x; win[k][2 * e + 1] = f.y;
+          }
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += win[k][e] * wreg[e][k];
+    }
+    float* o = a.out + (size_t)t * a.C + c;
+    *reinterpret_cast<float4*>(o) = make_float4(silu_f(acc[0]), silu_f(acc[1]), silu_f(acc[2]), silu_f(acc[3]));
+    *reinterpret_cast<float4*>(o + 4) = make_float4(silu_f(acc[4]), silu_f(acc[5]), silu_f(acc[6]), silu_f(acc[7]));
+    if (a.journal != nullptr) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        float* j = a.journal + ((size_t)t * a.C + c + e) * (KW - 1);
+#pragma unroll
+        for (int k = 1; k < KW; ++k) j[k - 1] = win[k][e];
+      }
     }
   }
 }
@@ -385,8 +401,8 @@ HE_API int he_qkv_post(const QkvArgs* args, int T, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (a.D % 32 != 0 || a.D > 512) return -HE_ERR_BAD_ARG;
   dim3 grid(T, a.H + 2 * a.Hkv);
-  qkv_post_kernel<<<grid, a.D, a.D * sizeof(float), stream>>>(a);
-  HE_LAUNCH_CHECK();
+  cudaError_t le = launch_pdl(qkv_post_kernel, grid, dim3(a.D), a.D * sizeof(float), stream, a);
+  if (le != cudaSuccess) return (int)le;
   return 0;
 }
 HE_API int he_qkv_args_size() { return (int)sizeof(QkvArgs); }
@@ -396,7 +412,7 @@ HE_API int he_conv1d(const ConvArgs* args, int update_state, cudaStream_t stream
   if (a.T <= 0) return 0;
   if (a.KW < 2 || a.KW > 4) return -HE_ERR_BAD_ARG;
   if (a.C % 8 != 0) return -HE_ERR_BAD_ARG;
-  const long long n = (long long)a.T * (a.C / 8);
+  const long long n = (long long)((a.T + CONV_TOK - 1) / CONV_TOK) * (a.C / 8);
   const unsigned nblk = (unsigned)((n + 255) / 256);
   if (a.KW == 4) conv_fwd_kernel<4><<<nblk, 256, 0, stream>>>(a);
   else if (a.KW == 3) conv_fwd_kernel<3><<<nblk, 256, 0, stream>>>(a);

@@ -102,10 +102,12 @@ class HybridExecutor:
         self.n_pages = n_pages if n_pages is not None else max_slots * self.max_pages_per_slot + 1
         self.gemm_impl = gemm_impl or os.environ.get("HE_GEMM", "tcgen05")
         self.scratch = _Scratch(self.device)
+        self.shadow: Optional[dict] = None      # resident bf16 expansions for the tensor-core path (set below)
         self.dw: Dict[str, DeviceWeight] = {}
         self.f32: Dict[str, torch.Tensor] = {}
         self._load(weights)
         self._alloc_state()
+        self._init_shadow()
 
     # ------------------------------------------------------------------ weights
     def _load(self, weights: ModelWeights) -> None:
@@ -125,11 +127,31 @@ class HybridExecutor:
         if "output.weight" not in self.dw:
             self.dw["output.weight"] = self.dw["token_embd.weight"]
         # prefill path: the two small F32 gate projections of a linear layer run as one bf16 tensor-core GEMM
+        # ... and for decode they ride the int8 block path of the fused GEMV as one Q8_0 segment: as fp32 rows each
+        # was a 20 KB dot product walked by a single warp, a latency-bound tail twice as long as the rest of the launch
         self.ab_bf16: Dict[int, torch.Tensor] = {}
+        self.ab_q8: Dict[int, DeviceWeight] = {}
+        from ..quant.ggml import quantize
         for i in range(self.cfg.n_layers):
             a_name, b_name = f"blk.{i}.ssm_alpha.weight", f"blk.{i}.ssm_beta.weight"
             if a_name in self.f32 and b_name in self.f32:
-                self.ab_bf16[i] = torch.cat([self.f32[a_name], self.f32[b_name]], 0).to(torch.bfloat16).contiguous()
+                ab = torch.cat([self.f32[a_name], self.f32[b_name]], 0).contiguous()
+                self.ab_bf16[i] = ab.to(torch.bfloat16).contiguous()
+                if ab.shape[1] % 256 == 0 and os.environ.get("HE_AB_Q8", "1") != "0":
+                    raw = quantize(ab, GGMLType.Q8_0).reshape(ab.shape[0], -1).contiguous()
+                    self.ab_q8[i] = K.to_device_weight(raw, GGMLType.Q8_0, ab.shape[0], ab.shape[1])
+
+    def _init_shadow(self) -> None:
+        """B200 has HBM to spare: keep bf16 expansions of the projection weights resident for prefill / verify
+        GEMMs (decode still streams the 4-bit blocks).  ``HE_BF16_SHADOW`` = 0 | 1 | auto (default: on when at
+        least a third of the device memory is still free, using at most half of what is free)."""
+        mode = os.environ.get("HE_BF16_SHADOW", "auto")
+        if mode == "0" or self.device.type != "cuda":
+            return
+        free, total = torch.cuda.mem_get_info(self.device)
+        if mode == "auto" and free < total // 3:
+            return
+        self.shadow = {"_left": int(free * 0.5)}
 
     def W(self, i: int, slot: str) -> DeviceWeight:
         return self.dw[f"blk.{i}.{slot}"]
@@ -183,7 +205,7 @@ class HybridExecutor:
         rows = w.n_rows - row0 if rows is None else rows
         if self.gemm_impl == "tcgen05":
             from ..ops import gemm as G
-            return G.gemm_quant(x, w, out, self.scratch, row0=row0, rows=rows)
+            return G.gemm_quant(x, w, out, self.scratch, row0=row0, rows=rows, shadow=self.shadow)
         wb = self.scratch.get("deq_" + tag, (rows, w.n_cols), torch.bfloat16)
         K.dequant_bf16(w, wb, row0=row0, rows=rows)
         torch.matmul(x, wb.t(), out=out)
@@ -261,9 +283,17 @@ class HybridExecutor:
         if small:
             qkv = sc.get("qkv_f32", (T, C), torch.float32)
             z = sc.get("z_f32", (T, inner), torch.float32)
-            K.gemv(h, [GemvSegment(self.W(i, "attn_qkv.weight"), qkv), GemvSegment(self.W(i, "attn_gate.weight"), z),
-                       GemvSegment(self.W(i, "ssm_alpha.weight"), a_p), GemvSegment(self.W(i, "ssm_beta.weight"), b_p)],
-                   norm_w=self.F(i, "attn_norm.weight"), eps=cfg.rms_eps)
+            if i in self.ab_q8:
+                ab = sc.get("ab_proj", (T, 2 * Hv), torch.float32)
+                K.gemv(h, [GemvSegment(self.W(i, "attn_qkv.weight"), qkv), GemvSegment(self.W(i, "attn_gate.weight"), z),
+                           GemvSegment(self.ab_q8[i], ab)], norm_w=self.F(i, "attn_norm.weight"), eps=cfg.rms_eps)
+                a_p, b_p = ab[:, :Hv], ab[:, Hv:]
+            else:
+                K.gemv(h, [GemvSegment(self.W(i, "attn_qkv.weight"), qkv),
+                           GemvSegment(self.W(i, "attn_gate.weight"), z),
+                           GemvSegment(self.W(i, "ssm_alpha.weight"), a_p),
+                           GemvSegment(self.W(i, "ssm_beta.weight"), b_p)],
+                       norm_w=self.F(i, "attn_norm.weight"), eps=cfg.rms_eps)
         else:
             xn = sc.get("xn", (T, cfg.hidden), torch.bfloat16)
             K.rmsnorm_rows(h, self.F(i, "attn_norm.weight"), xn, cfg.rms_eps)

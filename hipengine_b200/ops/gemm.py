@@ -35,11 +35,28 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: Optional
 
 
 def gemm_quant(x: torch.Tensor, w: DeviceWeight, out: torch.Tensor, scratch, row0: int = 0,
-               rows: Optional[int] = None, epi: Optional[int] = None) -> torch.Tensor:
-    """out[M, rows] = x[M, K] @ W[row0:row0+rows]^T for a quantized device-layout weight."""
+               rows: Optional[int] = None, epi: Optional[int] = None, shadow: Optional[dict] = None) -> torch.Tensor:
+    """out[M, rows] = x[M, K] @ W[row0:row0+rows]^T for a quantized device-layout weight.
+
+    The weight is expanded to bf16 for the tensor cores.  With ``shadow`` (a dict owned by the executor, holding a
+    byte budget under the key ``"_left"``) the expansion is kept resident in HBM after its first use, so later
+    prefill chunks read bf16 tiles straight through TMA; without it the expansion goes to scratch every call.
+    """
     rows = w.n_rows - row0 if rows is None else rows
     if w.qtype == 30 and row0 == 0 and rows == w.n_rows:   # already bf16
         return gemm_bf16(x, w.data.view(torch.bfloat16).reshape(w.n_rows, w.n_cols), out, epi)
+    if shadow is not None:
+        key = (w.ptr, row0, rows)
+        wb = shadow.get(key)
+        if wb is None:
+            need = rows * w.n_cols * 2
+            if shadow.get("_left", 0) >= need:
+                wb = torch.empty(rows, w.n_cols, dtype=torch.bfloat16, device=x.device)
+                dequant_bf16(w, wb, row0=row0, rows=rows)
+                shadow[key] = wb
+                shadow["_left"] -= need
+        if wb is not None:
+            return gemm_bf16(x, wb, out, epi)
     wb = scratch.get("gemm_deq", (rows, w.n_cols), torch.bfloat16)
     dequant_bf16(w, wb, row0=row0, rows=rows)
     return gemm_bf16(x, wb, out, epi)
