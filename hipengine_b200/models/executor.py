@@ -74,11 +74,19 @@ def make_batch(segments: Sequence[Tuple[int, int, Sequence[int]]], device) -> Ba
 
 
 class _Scratch:
-    """Grow-only named scratch tensors (no allocation on the steady-state path)."""
+    """Grow-only named scratch tensors (no allocation on the steady-state path).
+
+    A buffer that has been handed out may be baked into a captured CUDA graph, so it must stay mapped for the
+    life of the executor: when a name outgrows its buffer the old tensor is *retired* (kept referenced), never
+    freed.  (Freed blocks go back to the caching allocator, which unmaps its cache at the next graph capture; an
+    older graph replaying into such a block is an illegal access.)  Capacity at least doubles on growth, which
+    bounds the retired bytes by the live bytes.
+    """
 
     def __init__(self, device):
         self.device = device
         self.bufs: Dict[str, torch.Tensor] = {}
+        self.retired: List[torch.Tensor] = []
 
     def get(self, name: str, shape, dtype) -> torch.Tensor:
         n = 1
@@ -86,9 +94,20 @@ class _Scratch:
             n *= s
         cur = self.bufs.get(name)
         if cur is None or cur.numel() < n or cur.dtype != dtype:
-            cur = torch.empty(max(n, 1), dtype=dtype, device=self.device)
+            if cur is not None:
+                self.retired.append(cur)
+                if cur.dtype == dtype:
+                    n_alloc = max(n, 2 * cur.numel())
+                else:
+                    n_alloc = n
+            else:
+                n_alloc = n
+            cur = torch.empty(max(n_alloc, 1), dtype=dtype, device=self.device)
             self.bufs[name] = cur
         return cur[:n].view(*shape)
+
+    def retired_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self.retired)
 
 
 class HybridExecutor:

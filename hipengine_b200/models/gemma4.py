@@ -188,8 +188,9 @@ class Gemma4Executor(HybridExecutor):
         wgu, wd = self.W(i, "ffn_gate_up_exps.weight"), self.W(i, "ffn_down_exps.weight")
         norm2 = self.F(i, "pre_ffw_norm_2.weight")
         if T <= SEL_MAX_ROWS:
-            if self._act_pad is None or self._act_pad.shape[0] < T * k:
-                self._act_pad = torch.zeros(max(T * k, GEMV_MAX_ROWS * k), Fp, dtype=torch.bfloat16, device=self.device)
+            if self._act_pad is None:
+                # sized once for the largest selected-expert batch: a buffer a captured graph may hold is never freed
+                self._act_pad = torch.zeros(SEL_MAX_ROWS * k, Fp, dtype=torch.bfloat16, device=self.device)
             act_rows = self._act_pad[:T * k]
             K.moe_gateup_sel(h, norm2, eps, ids, wts, wgu, None, F, act_rows, "gelu_tanh", fused_gate_up=True)
             K.moe_down_sel(act_rows, ids, wts, wd, H, eo)

@@ -94,3 +94,42 @@ def test_decode_graph_replays_through_native_launcher():
     assert r.stats["captures"] == 1 and r.stats["hits"] == 5
     if r.native_launch and any(r._execs.values()):
         assert r.stats["native_launches"] == 6
+
+
+def test_old_graph_survives_scratch_growth_and_later_captures():
+    """A graph captured while scratch buffers were small must stay valid after a long prefill has grown them and
+    after further captures (which empty the allocator cache): retired scratch buffers are kept mapped."""
+    from hipengine_b200.models.decode_graph import DecodeGraphRunner
+    from hipengine_b200.models.executor import HybridExecutor
+    cfg = TINY_HYBRID
+    w = build_random_model(cfg, seed=6, std=0.05).to("cuda")
+    g = torch.Generator().manual_seed(4)
+    short = torch.randint(0, cfg.vocab, (10,), generator=g).tolist()
+    long = torch.randint(0, cfg.vocab, (400,), generator=g).tolist()
+
+    def run(use_graphs):
+        ex = HybridExecutor(w, max_slots=3, max_context=512)
+        r = DecodeGraphRunner(ex, max_rows=2, use_graphs=use_graphs)
+        out = []
+        t0 = int(ex.prefill(0, short).argmax(-1))
+        r.set_rows([0], [t0], [len(short)])
+        for _ in range(3):
+            r.step(1, 512)                                  # graph for 1 row, captured with small scratch
+            out.append(int(r.tokens[0]))
+        t1 = int(ex.prefill(1, long).argmax(-1))            # grows every scratch buffer
+        r.set_rows([0, 1], [out[-1], t1], [len(short) + 3, len(long)])
+        for _ in range(2):
+            r.step(2, 512)                                  # second capture
+            out += [int(r.tokens[0]), int(r.tokens[1])]
+        last0 = int(r.tokens[0])
+        r.set_rows([0], [last0], [len(short) + 5])
+        for _ in range(3):
+            r.step(1, 512)                                  # replays the first graph
+            out.append(int(r.tokens[0]))
+        torch.cuda.synchronize()
+        return out, ex
+
+    eager, _ = run(False)
+    graph, ex = run(True)
+    assert graph == eager
+    assert ex.scratch.retired_bytes() > 0
