@@ -59,7 +59,7 @@ def ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
 
 
 # kernels launched per successful launcher call (used for launch accounting)
-KERNELS_PER_CALL = {"he_attn_decode": 2, "he_gdn_decode": 2, "he_argmax_rows": 2, "he_conv1d+state": 2, "he_gemm_quant": 2}
+KERNELS_PER_CALL = {"he_attn_decode": 2, "he_gemm_bf16_splitk_det": 2, "he_gdn_decode": 2, "he_argmax_rows": 2, "he_conv1d+state": 2, "he_gemm_quant": 2}
 _LAUNCHES = [0]
 
 

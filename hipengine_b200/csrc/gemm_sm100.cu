@@ -35,6 +35,10 @@ struct GemmArgs {
   // grouped mode (MoE experts): M-tile tm multiplies rows [tm*BM, +BM) of A with the weight block
   // B[tile_group[tm] * N .. +N); a negative group marks an unused tile.  Null for a plain GEMM.
   const int* tile_group;
+  // split-K (small M, few output tiles): the K range is cut into k_splits pieces handled by different CTAs, which
+  // add their partial tiles into the fp32 C with atomics (epi 3).  1 = off.
+  int k_splits;
+  long long split_stride;   // epi 4: split ks stores its fp32 partial tile at C + ks * split_stride (elements)
 };
 
 struct __align__(8) Barriers {
@@ -56,8 +60,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (g.M + BM - 1) / BM, tiles_n = (g.N + BN - 1) / BN;
-  const int n_tiles = tiles_m * tiles_n;
-  const int k_blocks = (g.K + BK - 1) / BK;
+  const int ksp = g.k_splits > 1 ? g.k_splits : 1;
+  const int n_tiles = tiles_m * tiles_n * ksp;
+  const int k_blocks_all = (g.K + BK - 1) / BK;
+  const int kb_per = (k_blocks_all + ksp - 1) / ksp;      // k-blocks per split (the last split may get fewer)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -87,14 +93,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tma_prefetch_desc(&tmB);
       uint32_t it = 0;
       for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-        const int tm = tile % tiles_m, tn = tile / tiles_m;
+        const int ks = tile % ksp, mn = tile / ksp;
+        const int tm = mn % tiles_m, tn = mn / tiles_m;
         int b_row0 = tn * BN;
         if (g.tile_group != nullptr) {
           const int grp = __ldg(g.tile_group + tm);
           if (grp < 0) continue;
           b_row0 += grp * g.N;
         }
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        const int kb0 = ks * kb_per, kb1 = min(k_blocks_all, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&bar->empty[s], ph ^ 1, abort_flag, g.status, 101)) break;
@@ -112,7 +120,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
       uint32_t it = 0, tcount = 0;
       for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-        if (g.tile_group != nullptr && __ldg(g.tile_group + tile % tiles_m) < 0) continue;
+        if (g.tile_group != nullptr && __ldg(g.tile_group + (tile / ksp) % tiles_m) < 0) continue;
+        const int kb0 = (tile % ksp) * kb_per, kb1 = min(k_blocks_all, kb0 + kb_per);
+        const int k_blocks = kb1 - kb0;
         const int acc = tcount & 1;
         const uint32_t acc_ph = (tcount >> 1) & 1;
         if (!mbar_wait(&bar->acc_empty[acc], acc_ph ^ 1, abort_flag, g.status, 102)) break;
@@ -143,8 +153,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int q = warp & 3;              // TMEM lane quarter this warp may touch
     uint32_t tcount = 0;
     for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-      const int tm = tile % tiles_m, tn = tile / tiles_m;
+      const int mn = tile / ksp;
+      const int tm = mn % tiles_m, tn = mn / tiles_m;
       if (g.tile_group != nullptr && __ldg(g.tile_group + tm) < 0) continue;
+      const int ks_e = tile % ksp;
+      const bool empty_split = ks_e * kb_per >= k_blocks_all;
       const int acc = tcount & 1;
       const uint32_t acc_ph = (tcount >> 1) & 1;
       if (!mbar_wait(&bar->acc_full[acc], acc_ph, abort_flag, g.status, 104)) break;
@@ -178,11 +191,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               for (int e = 0; e < ncols; ++e) dst[e] = __float2bfloat16_rn(__uint_as_float(r[e]));
             }
           } else {
-            float* dst = reinterpret_cast<float*>(g.C) + (size_t)row * g.ldc + col0;
-            if (g.epi == 1) {
+            float* dst = reinterpret_cast<float*>(g.C) + (size_t)row * g.ldc + col0 +
+                         (g.epi == 4 ? (size_t)ks_e * (size_t)g.split_stride : (size_t)0);
+            if (g.epi == 1 || g.epi == 4) {
               for (int e = 0; e < ncols; ++e) dst[e] = __uint_as_float(r[e]);
-            } else {
+            } else if (g.epi == 2) {
               for (int e = 0; e < ncols; ++e) dst[e] += __uint_as_float(r[e]);
+            } else if (!empty_split) {
+              for (int e = 0; e < ncols; ++e) atomicAdd(dst + e, __uint_as_float(r[e]));
             }
           }
         }
@@ -252,6 +268,8 @@ HE_API int he_gemm_bf16(const void* A, long long lda, const void* B, long long l
   GemmArgs g;
   g.C = C; g.ldc = ldc; g.resid = nullptr; g.M = M; g.N = N; g.K = K; g.epi = epi; g.status = (int*)status;
   g.tile_group = nullptr;
+  g.k_splits = 1;
+  g.split_stride = 0;
   const size_t smem = STAGES * STAGE_BYTES + sizeof(Barriers) + 1024;
   static bool configured = false;
   if (!configured) {
@@ -282,11 +300,112 @@ HE_API int he_gemm_bf16_grouped(const void* A, long long lda, const void* B, lon
   GemmArgs g;
   g.C = C; g.ldc = ldc; g.resid = nullptr; g.M = M; g.N = N; g.K = K; g.epi = epi; g.status = (int*)status;
   g.tile_group = tile_group;
+  g.k_splits = 1;
+  g.split_stride = 0;
   const size_t smem = STAGES * STAGE_BYTES + sizeof(Barriers) + 1024;
   cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < num_sms ? tiles : num_sms;
+  gemm_bf16_kernel<<<grid, NTHREADS, smem, stream>>>(tmA, tmB, g);
+  HE_LAUNCH_CHECK();
+  return 0;
+}
+
+// C[M][N] (fp32) += A[M][K] * B[N][K]^T with the K range split over CTAs and atomic accumulation: for small M and
+// few output tiles (decode batches of 9..128 rows against a 5120-wide output) this is what lets all SMs stream
+// the weight instead of one CTA per 256 output columns.  C must already hold the value to add to (e.g. the
+// residual stream).  k_splits <= 0 picks a split that gives about one tile per SM.
+namespace {
+// out[m][n] (+)= sum over splits, in split order (deterministic).  mode 0: fp32 store, 1: fp32 add in place.
+__global__ void splitk_reduce_kernel(const float* __restrict__ part, long long split_stride, int k_splits,
+                                     float* __restrict__ out, long long ldo, int M, int N, int mode) {
+  const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i >= (long long)M * N) return;
+  const int m = (int)(i / N), n = (int)(i % N);
+  float4 s = *reinterpret_cast<const float4*>(part + (size_t)m * N + n);
+  for (int k = 1; k < k_splits; ++k) {
+    const float4 v = *reinterpret_cast<const float4*>(part + (size_t)k * split_stride + (size_t)m * N + n);
+    s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+  }
+  float4* o = reinterpret_cast<float4*>(out + (size_t)m * ldo + n);
+  if (mode == 1) {
+    const float4 h = *o;
+    s.x += h.x; s.y += h.y; s.z += h.z; s.w += h.w;
+  }
+  *o = s;
+}
+}  // namespace
+
+// Deterministic split-K: partial tiles go to `partials` ([k_splits][M][N] fp32, caller scratch of at least
+// he_gemm_splitk_scratch_floats(M, N, K) floats), then one pass sums them in split order into `out`
+// (mode 0: store, 1: add in place -- the residual add).  Same use as he_gemm_bf16_splitk, bit-reproducible.
+HE_API long long he_gemm_splitk_plan(int M, int N, int K, int num_sms) {
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int k_blocks = (K + BK - 1) / BK;
+  int k_splits = (num_sms + tiles - 1) / tiles;
+  if (k_splits > k_blocks) k_splits = k_blocks;
+  if (k_splits < 1) k_splits = 1;
+  const int kb_per = (k_blocks + k_splits - 1) / k_splits;
+  return (k_blocks + kb_per - 1) / kb_per;
+}
+
+HE_API int he_gemm_bf16_splitk_det(const void* A, long long lda, const void* B, long long ldb, void* partials,
+                                   void* out, long long ldo, int M, int N, int K, int mode, void* status,
+                                   int num_sms, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (K % 8 != 0 || N % 4 != 0) return -HE_ERR_BAD_ARG;
+  CUtensorMap tmA, tmB;
+  int rc = make_map(&tmA, A, M, K, lda, BM);
+  if (rc != 0) return rc;
+  rc = make_map(&tmB, B, N, K, ldb, BN);
+  if (rc != 0) return rc;
+  const int k_splits = (int)he_gemm_splitk_plan(M, N, K, num_sms);
+  GemmArgs g;
+  g.C = partials; g.ldc = N; g.resid = nullptr; g.M = M; g.N = N; g.K = K; g.epi = 4; g.status = (int*)status;
+  g.tile_group = nullptr;
+  g.k_splits = k_splits;
+  g.split_stride = (long long)M * N;
+  const size_t smem = STAGES * STAGE_BYTES + sizeof(Barriers) + 1024;
+  cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int total = tiles * k_splits;
+  gemm_bf16_kernel<<<total < num_sms ? total : num_sms, NTHREADS, smem, stream>>>(tmA, tmB, g);
+  HE_LAUNCH_CHECK();
+  const long long n4 = ((long long)M * N + 3) / 4;
+  splitk_reduce_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>((const float*)partials, g.split_stride,
+                                                                        k_splits, (float*)out, ldo, M, N, mode);
+  HE_LAUNCH_CHECK();
+  return 0;
+}
+
+HE_API int he_gemm_bf16_splitk(const void* A, long long lda, const void* B, long long ldb, void* C, long long ldc,
+                               int M, int N, int K, int k_splits, void* status, int num_sms, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (K % 8 != 0) return -HE_ERR_BAD_ARG;
+  CUtensorMap tmA, tmB;
+  int rc = make_map(&tmA, A, M, K, lda, BM);
+  if (rc != 0) return rc;
+  rc = make_map(&tmB, B, N, K, ldb, BN);
+  if (rc != 0) return rc;
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int k_blocks = (K + BK - 1) / BK;
+  if (k_splits <= 0) k_splits = (num_sms + tiles - 1) / tiles;
+  if (k_splits > k_blocks) k_splits = k_blocks;
+  if (k_splits < 1) k_splits = 1;
+  const int kb_per = (k_blocks + k_splits - 1) / k_splits;
+  k_splits = (k_blocks + kb_per - 1) / kb_per;            // no empty split
+  GemmArgs g;
+  g.C = C; g.ldc = ldc; g.resid = nullptr; g.M = M; g.N = N; g.K = K; g.epi = 3; g.status = (int*)status;
+  g.tile_group = nullptr;
+  g.k_splits = k_splits;
+  g.split_stride = 0;
+  const size_t smem = STAGES * STAGE_BYTES + sizeof(Barriers) + 1024;
+  cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  const int total = tiles * k_splits;
+  const int grid = total < num_sms ? total : num_sms;
   gemm_bf16_kernel<<<grid, NTHREADS, smem, stream>>>(tmA, tmB, g);
   HE_LAUNCH_CHECK();
   return 0;

@@ -65,6 +65,26 @@ __global__ void act_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat
   *reinterpret_cast<uint4*>(out + i) = *reinterpret_cast<const uint4*>(o);
 }
 
+// same with the packed gate | up rows in fp32 (split-K accumulators of small batches)
+__global__ void act_mul_f32_kernel(const float* __restrict__ gu, __nv_bfloat16* __restrict__ out, long long T, int F,
+                                   int act) {
+  const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i >= T * F) return;
+  const long long t = i / F;
+  const int f = (int)(i % F);
+  const float4 g = *reinterpret_cast<const float4*>(gu + (size_t)t * 2 * F + f);
+  const float4 u = *reinterpret_cast<const float4*>(gu + (size_t)t * 2 * F + F + f);
+  const float gx[4] = {g.x, g.y, g.z, g.w}, ux[4] = {u.x, u.y, u.z, u.w};
+  __align__(8) __nv_bfloat162 o[2];
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    const float a0 = act == 0 ? silu_f(gx[2 * k]) : gelu_tanh_f(gx[2 * k]);
+    const float a1 = act == 0 ? silu_f(gx[2 * k + 1]) : gelu_tanh_f(gx[2 * k + 1]);
+    o[k] = __floats2bfloat162_rn(a0 * ux[2 * k], a1 * ux[2 * k + 1]);
+  }
+  *reinterpret_cast<uint2*>(out + i) = *reinterpret_cast<const uint2*>(o);
+}
+
 // ---------------------------------------------------------------- residual add: h (fp32) += y (bf16)
 __global__ void resid_add_bf16_kernel(float* __restrict__ h, const __nv_bfloat16* __restrict__ y, long long n) {
   const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
@@ -295,6 +315,15 @@ HE_API int he_act_mul(const void* gu, void* out, long long T, int F, int act, cu
   const long long n = T * F / 8;
   act_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, T, F,
                                                                    act);
+  HE_LAUNCH_CHECK();
+  return 0;
+}
+
+HE_API int he_act_mul_f32(const void* gu, void* out, long long T, int F, int act, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (F % 4 != 0) return -HE_ERR_BAD_ARG;
+  const long long n = T * F / 4;
+  act_mul_f32_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>((const float*)gu, (__nv_bfloat16*)out, T, F, act);
   HE_LAUNCH_CHECK();
   return 0;
 }

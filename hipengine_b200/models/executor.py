@@ -121,6 +121,10 @@ class HybridExecutor:
         self.n_pages = n_pages if n_pages is not None else max_slots * self.max_pages_per_slot + 1
         self.gemm_impl = gemm_impl or os.environ.get("HE_GEMM", "tcgen05")
         self.scratch = _Scratch(self.device)
+        # packed batches of up to small_rows rows take the quantised GEMV path, larger ones the tensor-core path
+        # (measured on the 27B geometry: the int8 GEMV costs ~3.4 ms per extra row, the split-K tensor-core path
+        # ~20 ms per step for any row count up to 16, so they cross between 5 and 6 rows)
+        self.small_rows = min(GEMV_MAX_ROWS, int(os.environ.get("HE_SMALL_ROWS", "6")))
         self.shadow: Optional[dict] = None      # resident bf16 expansions for the tensor-core path (set below)
         self.dw: Dict[str, DeviceWeight] = {}
         self.f32: Dict[str, torch.Tensor] = {}
@@ -230,13 +234,38 @@ class HybridExecutor:
         torch.matmul(x, wb.t(), out=out)
         return out
 
+    SPLITK_MAX_ROWS = 128
+
+    def _use_splitk(self, T: int) -> bool:
+        return (self.gemm_impl == "tcgen05" and T <= self.SPLITK_MAX_ROWS and os.environ.get("HE_SPLITK", "1") != "0")
+
+    def _proj(self, x: torch.Tensor, w: DeviceWeight, name: str, tag: str, out: Optional[torch.Tensor] = None
+              ) -> torch.Tensor:
+        """x[T, K] (bf16) @ W^T for the tensor-core path.  Large batches: bf16 result.  Batches of at most
+        SPLITK_MAX_ROWS rows: split-K into a zeroed fp32 buffer, so that all SMs stream the weight even when the
+        output is only a few tiles wide (the consumers take fp32 or bf16 rows)."""
+        T = x.shape[0]
+        if self._use_splitk(T):
+            from ..ops import gemm as GM
+            acc = out if out is not None else self.scratch.get(name + "_f32", (T, w.n_rows), torch.float32)
+            return GM.gemm_bf16_splitk_det(x, GM.bf16_weight(w, self.scratch, self.shadow), acc, self.scratch)
+        dst = out if out is not None else self.scratch.get(name + "_bf", (T, w.n_rows), torch.bfloat16)
+        return self._gemm(x, w, dst, tag=tag)
+
     # Row-parallel ("output") projections: h += x @ W^T.  A tensor-parallel executor overrides these two to
     # reduce the partial products across ranks before the residual add.
     def _out_small(self, x: torch.Tensor, w: DeviceWeight, h: torch.Tensor) -> None:
         K.gemv(x, [GemvSegment(w, h, K.EPI_ADD_F32)])
 
     def _out_big(self, x: torch.Tensor, w: DeviceWeight, h: torch.Tensor, tag: str) -> None:
-        y = self._gemm(x, w, self.scratch.get("y_bf", (x.shape[0], w.n_rows), torch.bfloat16), tag=tag)
+        T = x.shape[0]
+        if self._use_splitk(T) and h.is_contiguous():
+            # few rows against a hidden-wide output is only ~20 tiles: split K over the SMs and let the tiles add
+            # themselves into the fp32 residual (which is the residual add)
+            from ..ops import gemm as GM
+            GM.gemm_bf16_splitk_det(x, GM.bf16_weight(w, self.scratch, self.shadow), h, self.scratch, add=True)
+            return
+        y = self._gemm(x, w, self.scratch.get("y_bf", (T, w.n_rows), torch.bfloat16), tag=tag)
         K.resid_add_bf16(h, y)
 
     # ------------------------------------------------------------------ layers
@@ -255,9 +284,9 @@ class HybridExecutor:
         else:
             xn = sc.get("xn", (T, cfg.hidden), torch.bfloat16)
             K.rmsnorm_rows(h, self.F(i, "attn_norm.weight"), xn, cfg.rms_eps)
-            qf = self._gemm(xn, self.W(i, "attn_q.weight"), sc.get("q_bf", (T, qw), torch.bfloat16), tag="q")
-            kf = self._gemm(xn, self.W(i, "attn_k.weight"), sc.get("k_bf", (T, cfg.kv_width), torch.bfloat16), tag="k")
-            vf = self._gemm(xn, self.W(i, "attn_v.weight"), sc.get("v_bf", (T, cfg.kv_width), torch.bfloat16), tag="k")
+            qf = self._proj(xn, self.W(i, "attn_q.weight"), "q", "q")
+            kf = self._proj(xn, self.W(i, "attn_k.weight"), "k", "k")
+            vf = self._proj(xn, self.W(i, "attn_v.weight"), "v", "k")
         q_out = sc.get("q_out", (T, H, D), torch.bfloat16)
         gate = sc.get("gate_out", (T, H, D), torch.bfloat16) if cfg.gated_attention else None
         qn = self.f32.get(f"blk.{i}.attn_q_norm.weight") if cfg.qk_norm else None
@@ -316,8 +345,8 @@ class HybridExecutor:
         else:
             xn = sc.get("xn", (T, cfg.hidden), torch.bfloat16)
             K.rmsnorm_rows(h, self.F(i, "attn_norm.weight"), xn, cfg.rms_eps)
-            qkv = self._gemm(xn, self.W(i, "attn_qkv.weight"), sc.get("qkv_bf", (T, C), torch.bfloat16), tag="q")
-            z = self._gemm(xn, self.W(i, "attn_gate.weight"), sc.get("z_bf", (T, inner), torch.bfloat16), tag="q")
+            qkv = self._proj(xn, self.W(i, "attn_qkv.weight"), "qkv", "q")
+            z = self._proj(xn, self.W(i, "attn_gate.weight"), "z", "q")
             if self.gemm_impl == "tcgen05" and (2 * Hv) % 8 == 0:
                 from ..ops import gemm as GM
                 ab = sc.get("ab_proj", (T, 2 * Hv), torch.float32)
@@ -372,9 +401,15 @@ class HybridExecutor:
         else:
             xn = sc.get("xn", (T, cfg.hidden), torch.bfloat16)
             K.rmsnorm_rows(h, norm_w, xn, cfg.rms_eps)
-            gu = sc.get("ffn_gu", (T, 2 * Fd), torch.bfloat16)
-            self._gemm(xn, self.W(i, "ffn_gate.weight"), gu[:, :Fd], tag="g")
-            self._gemm(xn, self.W(i, "ffn_up.weight"), gu[:, Fd:], tag="g")
+            if self._use_splitk(T):
+                from ..ops import gemm as GM
+                gu = sc.get("ffn_gu_f32", (T, 2 * Fd), torch.float32)
+                GM.gemm_bf16_splitk_det(xn, GM.bf16_weight(self.W(i, "ffn_gate.weight"), sc, self.shadow), gu[:, :Fd], sc)
+                GM.gemm_bf16_splitk_det(xn, GM.bf16_weight(self.W(i, "ffn_up.weight"), sc, self.shadow), gu[:, Fd:], sc)
+            else:
+                gu = sc.get("ffn_gu", (T, 2 * Fd), torch.bfloat16)
+                self._gemm(xn, self.W(i, "ffn_gate.weight"), gu[:, :Fd], tag="g")
+                self._gemm(xn, self.W(i, "ffn_up.weight"), gu[:, Fd:], tag="g")
             act = sc.get("ffn_act", (T, Fd), torch.bfloat16)
             K.act_mul(gu, act, cfg.act)
             self._out_big(act, self.W(i, "ffn_down.weight"), h, "d")
@@ -384,7 +419,7 @@ class HybridExecutor:
         """Runs all layers over the packed rows; returns the fp32 residual stream [T, hidden] (pre output_norm)."""
         cfg = self.cfg
         T = b.T
-        small = T <= GEMV_MAX_ROWS
+        small = T <= self.small_rows
         h = h_out if h_out is not None else self.scratch.get("h", (T, cfg.hidden), torch.float32)
         K.embed(self.dw["token_embd.weight"], b.tokens, h, cfg.embed_scale)
         for i in range(cfg.n_layers):
@@ -432,7 +467,7 @@ class HybridExecutor:
         cfg, sc = self.cfg, self.scratch
         i = cfg.n_layers
         T, H = b.T, cfg.hidden
-        small = T <= GEMV_MAX_ROWS
+        small = T <= self.small_rows
         table = self.dw.get(f"blk.{i}.nextn.embed_tokens.weight", self.dw["token_embd.weight"])
         e = sc.get("nx_e", (T, H), torch.float32)
         K.embed(table, b.tokens, e, cfg.embed_scale)

@@ -224,7 +224,7 @@ class Gemma4Executor(HybridExecutor):
     def forward(self, b: BatchDesc, journal: Optional[dict] = None, h_out: Optional[torch.Tensor] = None) -> torch.Tensor:
         cfg = self.cfg
         T = b.T
-        small = T <= GEMV_MAX_ROWS
+        small = T <= self.small_rows
         h = h_out if h_out is not None else self.scratch.get("h", (T, cfg.hidden), torch.float32)
         K.embed(self.dw["token_embd.weight"], b.tokens, h, cfg.embed_scale)
         for i in range(cfg.n_layers):

@@ -78,3 +78,58 @@ def gemm_bf16_grouped(a_sorted: torch.Tensor, w_stacked: torch.Tensor, out: torc
         C.c_int(Nn), C.c_int(K), C.c_int(n_groups), C.c_void_p(tile_group.data_ptr()), C.c_int(epi),
         C.c_void_p(st.data_ptr()), C.c_int(N.num_sms()), _stream()), "he_gemm_bf16_grouped")
     return out
+
+
+def gemm_bf16_splitk_add(x: torch.Tensor, w: torch.Tensor, acc: torch.Tensor, k_splits: int = 0) -> torch.Tensor:
+    """acc[M, N] (fp32, in place) += x[M, K] @ w[N, K]^T with the K range split over CTAs (atomic accumulation).
+    For small M against a narrow output (decode batches on the tensor-core path)."""
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and acc.dtype == torch.float32
+    _check_device(x)
+    M, K = x.shape
+    st = status_word(x.device)
+    N.check(N.lib().he_gemm_bf16_splitk(C.c_void_p(x.data_ptr()), C.c_longlong(x.stride(0)), C.c_void_p(w.data_ptr()),
+                                        C.c_longlong(w.stride(0)), C.c_void_p(acc.data_ptr()),
+                                        C.c_longlong(acc.stride(0)), C.c_int(M), C.c_int(w.shape[0]), C.c_int(K),
+                                        C.c_int(k_splits), C.c_void_p(st.data_ptr()), C.c_int(N.num_sms()), _stream()),
+            "he_gemm_bf16_splitk")
+    return acc
+
+
+def gemm_bf16_splitk_det(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, scratch, add: bool = False
+                         ) -> torch.Tensor:
+    """out[M, N] (fp32) = (or +=) x[M, K] @ w[N, K]^T with K split over CTAs and the partial tiles summed in a
+    fixed order: the bit-reproducible form of ``gemm_bf16_splitk_add`` (``out`` may be a strided row view)."""
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.dtype == torch.float32
+    _check_device(x)
+    M, K = x.shape
+    Nn = w.shape[0]
+    L = N.lib()
+    L.he_gemm_splitk_plan.restype = C.c_longlong
+    ks = int(L.he_gemm_splitk_plan(C.c_int(M), C.c_int(Nn), C.c_int(K), C.c_int(N.num_sms())))
+    part = scratch.get("splitk_part", (ks * M * Nn,), torch.float32)
+    st = status_word(x.device)
+    N.check(L.he_gemm_bf16_splitk_det(C.c_void_p(x.data_ptr()), C.c_longlong(x.stride(0)), C.c_void_p(w.data_ptr()),
+                                      C.c_longlong(w.stride(0)), C.c_void_p(part.data_ptr()),
+                                      C.c_void_p(out.data_ptr()), C.c_longlong(out.stride(0)), C.c_int(M), C.c_int(Nn),
+                                      C.c_int(K), C.c_int(1 if add else 0), C.c_void_p(st.data_ptr()),
+                                      C.c_int(N.num_sms()), _stream()), "he_gemm_bf16_splitk_det")
+    return out
+
+
+def bf16_weight(w: DeviceWeight, scratch, shadow: Optional[dict] = None) -> torch.Tensor:
+    """The bf16 expansion of a quantised weight: the resident shadow copy when there is one, else scratch."""
+    if w.qtype == 30:
+        return w.data.view(torch.bfloat16).reshape(w.n_rows, w.n_cols)
+    if shadow is not None:
+        key = (w.ptr, 0, w.n_rows)
+        wb = shadow.get(key)
+        if wb is None and shadow.get("_left", 0) >= w.n_rows * w.n_cols * 2:
+            wb = torch.empty(w.n_rows, w.n_cols, dtype=torch.bfloat16, device=w.data.device)
+            dequant_bf16(w, wb)
+            shadow[key] = wb
+            shadow["_left"] -= w.n_rows * w.n_cols * 2
+        if wb is not None:
+            return wb
+    wb = scratch.get("gemm_deq", (w.n_rows, w.n_cols), torch.bfloat16)
+    dequant_bf16(w, wb)
+    return wb

@@ -294,6 +294,10 @@ def rmsnorm_rows(x: torch.Tensor, w: Optional[torch.Tensor], out: torch.Tensor, 
 
 def act_mul(gu: torch.Tensor, out: torch.Tensor, act: str = "silu") -> torch.Tensor:
     T, F2 = gu.shape
+    if gu.dtype == torch.float32:
+        N.check(N.lib().he_act_mul_f32(c_vp(gu.data_ptr()), c_vp(out.data_ptr()), c_ll(T), C.c_int(F2 // 2),
+                                       C.c_int(0 if act == "silu" else 1), _stream()), "he_act_mul")
+        return out
     N.check(N.lib().he_act_mul(c_vp(gu.data_ptr()), c_vp(out.data_ptr()), c_ll(T), C.c_int(F2 // 2),
                                C.c_int(0 if act == "silu" else 1), _stream()), "he_act_mul")
     return out

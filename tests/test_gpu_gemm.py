@@ -47,3 +47,32 @@ def test_gemm_strided_output_and_quant_weight():
     ref = x.float() @ deq.bfloat16().float().t()
     assert (big[:, :N] == 0).all()
     assert torch.allclose(big[:, N:].float(), ref, atol=0.02 * ref.abs().max().item(), rtol=2e-2)
+
+
+@pytest.mark.parametrize("M,N,K", [(16, 512, 2048), (100, 5120, 6144), (9, 768, 17408)])
+def test_splitk_accumulates_into_fp32(M, N, K):
+    from hipengine_b200.ops import gemm as G
+    g = torch.Generator(device="cuda").manual_seed(M)
+    x = (torch.randn(M, K, device="cuda", generator=g) * 0.5).bfloat16()
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.05).bfloat16()
+    acc = torch.randn(M, N, device="cuda", generator=g)
+    want = acc + x.float() @ w.float().t()
+    G.gemm_bf16_splitk_add(x, w, acc)
+    G.check_status()
+    torch.testing.assert_close(acc, want, atol=2e-2, rtol=2e-2)
+    acc2 = torch.zeros(M, N, device="cuda")
+    G.gemm_bf16_splitk_add(x, w, acc2, k_splits=3)
+    G.check_status()
+    torch.testing.assert_close(acc2, x.float() @ w.float().t(), atol=2e-2, rtol=2e-2)
+    # deterministic variant: same numbers, bit-identical across runs, strided output rows
+    from hipengine_b200.models.executor import _Scratch
+    sc = _Scratch(torch.device("cuda"))
+    wide = torch.zeros(M, 2 * N, device="cuda")
+    a = G.gemm_bf16_splitk_det(x, w, wide[:, N:], sc).clone()
+    b = G.gemm_bf16_splitk_det(x, w, wide[:, N:], sc).clone()
+    G.check_status()
+    assert torch.equal(a, b)
+    torch.testing.assert_close(a, x.float() @ w.float().t(), atol=2e-2, rtol=2e-2)
+    h = acc2.clone()
+    G.gemm_bf16_splitk_det(x, w, h, sc, add=True)
+    torch.testing.assert_close(h, 2 * (x.float() @ w.float().t()), atol=4e-2, rtol=2e-2)
