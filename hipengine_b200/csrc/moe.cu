@@ -87,7 +87,9 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, long long ld,
 // Single CTA: histogram of expert ids over the P = T*k pairs, prefix over experts with every expert's rows
 // padded to a multiple of 128, scatter.  pos[pair] = row in the sorted matrix, tile_group[tile] = expert of
 // that 128-row tile or -1.  meta[0] = padded row count in use.
-__global__ void __launch_bounds__(1024) moe_group_kernel(const int* __restrict__ ids, int P, int E,
+// Expert parallelism: only experts [e_lo, e_lo + E) are local; pairs routed elsewhere get pos = -1 and are skipped by
+// the gather and the combine (their owners add them in through the cross-rank reduction of the partial outputs).
+__global__ void __launch_bounds__(1024) moe_group_kernel(const int* __restrict__ ids, int P, int E, int e_lo,
                                                          int* __restrict__ pos, int* __restrict__ tile_group,
                                                          int max_tiles, int* __restrict__ meta) {
   extern __shared__ int sm[];
@@ -95,7 +97,10 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const int* __restrict__
   int* off = sm + E;        // [E + 1]
   for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
   __syncthreads();
-  for (int p = threadIdx.x; p < P; p += blockDim.x) atomicAdd(&cnt[ids[p]], 1);
+  for (int p = threadIdx.x; p < P; p += blockDim.x) {
+    const int e = ids[p] - e_lo;
+    if (e >= 0 && e < E) atomicAdd(&cnt[e], 1);
+  }
   __syncthreads();
   if (threadIdx.x == 0) {
     int run = 0;
@@ -115,8 +120,8 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const int* __restrict__
   }
   __syncthreads();
   for (int p = threadIdx.x; p < P; p += blockDim.x) {
-    const int e = ids[p];
-    pos[p] = off[e] + atomicAdd(&cnt[e], 1);
+    const int e = ids[p] - e_lo;
+    pos[p] = (e >= 0 && e < E) ? off[e] + atomicAdd(&cnt[e], 1) : -1;
   }
 }
 
@@ -124,7 +129,7 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const int* __restrict__
 __global__ void moe_gather_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const int* __restrict__ pos,
                                   int P, int k, int K, __nv_bfloat16* __restrict__ sorted, long long lds) {
   const int p = blockIdx.x;
-  if (p >= P) return;
+  if (p >= P || pos[p] < 0) return;
   const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)(p / k) * ldx);
   uint4* dst = reinterpret_cast<uint4*>(sorted + (size_t)pos[p] * lds);
   for (int i = threadIdx.x; i < K / 8; i += blockDim.x) dst[i] = __ldg(src + i);
@@ -139,9 +144,10 @@ __global__ void moe_combine_kernel(float* __restrict__ h, long long ldh, const _
   for (int n = threadIdx.x * 2; n < N; n += blockDim.x * 2) {
     float a0 = 0.f, a1 = 0.f;
     for (int j = 0; j < k; ++j) {
+      const int pj = pos[(size_t)t * k + j];
+      if (pj < 0) continue;     // expert lives on another rank
       const float w = wts[(size_t)t * k + j];
-      const float2 f = __bfloat1622float2(
-          *reinterpret_cast<const __nv_bfloat162*>(y + (size_t)pos[(size_t)t * k + j] * ldy + n));
+      const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(y + (size_t)pj * ldy + n));
       a0 += w * f.x; a1 += w * f.y;
     }
     if (ysh != nullptr) {
@@ -237,6 +243,7 @@ struct MoeSelArgs {
   long long ldo;
   int rows_per_cta;
   int expert_rows;          // rows between consecutive experts in w1 / w2 (0 -> N); 2N for a fused gate|up tensor
+  int expert_lo, expert_n;  // local expert range [lo, lo + n) (expert parallelism); n <= 0 -> all experts local
 };
 
 // grid (ceil(N / rows_per_cta), T*k), 256 threads
@@ -245,7 +252,8 @@ __global__ void __launch_bounds__(256) moe_gateup_sel_kernel(const MoeSelArgs a)
   __shared__ float red[32];
   const SmemView s = carve(smem_moe, 1, a.K);
   const int pair = blockIdx.y, t = pair / a.k;
-  const int e = a.ids[pair];
+  const int e = a.ids[pair] - a.expert_lo;
+  if (a.expert_n > 0 && (e < 0 || e >= a.expert_n)) return;     // not a local expert (uniform for the CTA)
   const float* xr = reinterpret_cast<const float*>(a.x) + (size_t)t * a.ldx;
   // RMSNorm + int8 quantisation of the token's row
   float ss = 0.f;
@@ -315,8 +323,10 @@ __global__ void __launch_bounds__(256) moe_down_sel_kernel(const MoeSelArgs a) {
   const SmemView s = carve(smem_moe, a.k, a.K);
   const int t = blockIdx.y;
   if (threadIdx.x < a.k) {
-    e_s[threadIdx.x] = a.ids[(size_t)t * a.k + threadIdx.x];
-    w_s[threadIdx.x] = a.wts[(size_t)t * a.k + threadIdx.x];
+    const int e = a.ids[(size_t)t * a.k + threadIdx.x] - a.expert_lo;
+    const bool local = a.expert_n <= 0 || (e >= 0 && e < a.expert_n);
+    e_s[threadIdx.x] = local ? e : -1;                                        // -1: expert lives on another rank
+    w_s[threadIdx.x] = local ? a.wts[(size_t)t * a.k + threadIdx.x] : 0.f;
   }
   const int gpr = a.K / 8;   // 8-element groups per row
   const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(a.x) + (size_t)t * a.k * a.ldx;
@@ -353,6 +363,7 @@ __global__ void __launch_bounds__(256) moe_down_sel_kernel(const MoeSelArgs a) {
     if (n < row_end) {
       for (int it = sub; it < items; it += lpr) {
         const int j = it / nblk, b = it % nblk;
+        if (e_s[j] < 0) continue;      // its activation row was never written on this rank
         const uint8_t* row = a.w1 + ((size_t)e_s[j] * (a.expert_rows > 0 ? a.expert_rows : a.N) + n) * rb;
         acc += w_s[j] * dot_block(row, a.qtype1, a.K, b, s, j);
       }
@@ -392,10 +403,10 @@ HE_API long long he_moe_sorted_rows_bound(long long P, int E) {
   return tiles * 128;
 }
 
-HE_API int he_moe_group(const int* ids, int P, int E, int* pos, int* tile_group, int max_tiles, int* meta,
+HE_API int he_moe_group(const int* ids, int P, int E, int e_lo, int* pos, int* tile_group, int max_tiles, int* meta,
                         cudaStream_t stream) {
   if (P <= 0) return 0;
-  moe_group_kernel<<<1, 1024, (2 * E + 1) * sizeof(int), stream>>>(ids, P, E, pos, tile_group, max_tiles, meta);
+  moe_group_kernel<<<1, 1024, (2 * E + 1) * sizeof(int), stream>>>(ids, P, E, e_lo, pos, tile_group, max_tiles, meta);
   HE_LAUNCH_CHECK();
   return 0;
 }

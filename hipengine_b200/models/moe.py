@@ -62,16 +62,31 @@ def _layer(ex, i: int) -> _MoeLayer:
 
 
 def moe_ffn(ex, i: int, h: torch.Tensor, T: int, norm_w: torch.Tensor, small: bool) -> None:
-    """h[T, hidden] (fp32 residual) += MoE(RMSNorm(h)) for layer ``i`` of executor ``ex``."""
+    """h[T, hidden] (fp32 residual) += MoE(RMSNorm(h)) for layer ``i`` of executor ``ex``.
+
+    Expert parallelism: an executor that owns only experts ``ex.expert_range = (lo, hi)`` (weights already sliced)
+    computes the contributions of its own experts for every token -- the activations are replicated across ranks
+    -- into a zeroed partial buffer that ``ex._moe_reduce`` sums over the ranks and adds to the residual.  The
+    shared expert runs on the one rank with ``ex.owns_shared_expert``.
+    """
+    rng = getattr(ex, "expert_range", None)
+    target = h
+    if rng is not None:
+        target = ex.scratch.get("moe_partial", (T, h.shape[1]), torch.float32)
+        target.zero_()
     if T <= SEL_MAX_ROWS:
-        _moe_selected(ex, i, h, T, norm_w)
+        _moe_selected(ex, i, h, target, T, norm_w, rng)
     else:
-        _moe_grouped(ex, i, h, T, norm_w)
+        _moe_grouped(ex, i, h, target, T, norm_w, rng)
+    if rng is not None:
+        ex._moe_reduce(h, target)
 
 
-def _moe_selected(ex, i: int, h: torch.Tensor, T: int, norm_w: torch.Tensor) -> None:
+def _moe_selected(ex, i: int, h: torch.Tensor, target: torch.Tensor, T: int, norm_w: torch.Tensor, rng) -> None:
     cfg, sc = ex.cfg, ex.scratch
     L = _layer(ex, i)
+    er = rng or (0, 0)
+    shared_here = L.has_shared and getattr(ex, "owns_shared_expert", True)
     E, k, F = cfg.n_experts, cfg.n_experts_used, cfg.expert_ffn
     logits = sc.get("moe_logits", (T, L.n_logits_pad), torch.float32)
     ids = sc.get("moe_ids", (T, k), torch.int32)
@@ -86,25 +101,28 @@ def _moe_selected(ex, i: int, h: torch.Tensor, T: int, norm_w: torch.Tensor) -> 
         if L.has_shared:
             segs.append(GemvSegment(L.shexp_gate, logits[r0:r1, E:E + 1]))
         K.gemv(h[r0:r1], segs, norm_w=norm_w, eps=cfg.rms_eps)
-        if L.has_shared:
+        if shared_here:
             K.gemv(h[r0:r1], [GemvSegment(ex.W(i, "ffn_gate_shexp.weight"), act_sh[r0:r1], epi,
                                           ex.W(i, "ffn_up_shexp.weight"))], norm_w=norm_w, eps=cfg.rms_eps)
     K.moe_route(logits, k, ids, wts, n_experts=E)
     K.moe_gateup_sel(h, norm_w, cfg.rms_eps, ids, wts, ex.W(i, "ffn_gate_exps.weight"),
-                     ex.W(i, "ffn_up_exps.weight"), F, act_rows, cfg.act)
-    K.moe_down_sel(act_rows, ids, wts, ex.W(i, "ffn_down_exps.weight"), cfg.hidden, h)
-    if L.has_shared:
+                     ex.W(i, "ffn_up_exps.weight"), F, act_rows, cfg.act, expert_range=er)
+    K.moe_down_sel(act_rows, ids, wts, ex.W(i, "ffn_down_exps.weight"), cfg.hidden, target, expert_range=er)
+    if shared_here:
         K.moe_scale_rows(act_sh, logits[:, E:E + 1])
         for r0 in range(0, T, 8):
             r1 = min(T, r0 + 8)
-            K.gemv(act_sh[r0:r1], [GemvSegment(ex.W(i, "ffn_down_shexp.weight"), h[r0:r1], K.EPI_ADD_F32)])
+            K.gemv(act_sh[r0:r1], [GemvSegment(ex.W(i, "ffn_down_shexp.weight"), target[r0:r1], K.EPI_ADD_F32)])
 
 
-def _moe_grouped(ex, i: int, h: torch.Tensor, T: int, norm_w: torch.Tensor) -> None:
+def _moe_grouped(ex, i: int, h: torch.Tensor, target: torch.Tensor, T: int, norm_w: torch.Tensor, rng) -> None:
     from ..ops import gemm as GM
     cfg, sc = ex.cfg, ex.scratch
     L = _layer(ex, i)
     E, k, F, H = cfg.n_experts, cfg.n_experts_used, cfg.expert_ffn, cfg.hidden
+    e_lo, e_hi = rng or (0, E)
+    El = e_hi - e_lo                      # local experts (all of them without expert parallelism)
+    shared_here = L.has_shared and getattr(ex, "owns_shared_expert", True)
     xn = sc.get("xn", (T, H), torch.bfloat16)
     K.rmsnorm_rows(h, norm_w, xn, cfg.rms_eps)
     logits = sc.get("moe_logits", (T, L.n_logits_pad), torch.float32)
@@ -114,29 +132,29 @@ def _moe_grouped(ex, i: int, h: torch.Tensor, T: int, norm_w: torch.Tensor) -> N
     wts = sc.get("moe_wts", (T, k), torch.float32)
     K.moe_route(logits, k, ids, wts, n_experts=E)
     P = T * k
-    bound = K.moe_sorted_rows_bound(P, E)
+    bound = K.moe_sorted_rows_bound(P, El)
     pos = sc.get("moe_pos", (P,), torch.int32)
     tile_group = sc.get("moe_tiles", (bound // 128,), torch.int32)
     meta = sc.get("moe_meta", (4,), torch.int32)
-    K.moe_group(ids, E, pos, tile_group, meta)
+    K.moe_group(ids, El, pos, tile_group, meta, expert_lo=e_lo)
     xs = sc.get("moe_xs", (bound, H), torch.bfloat16)
     K.moe_gather(xn, pos, k, xs)
     gu = sc.get("moe_gu", (bound, 2 * F), torch.bfloat16)
     wg, wu, wd = (ex.W(i, "ffn_gate_exps.weight"), ex.W(i, "ffn_up_exps.weight"), ex.W(i, "ffn_down_exps.weight"))
-    wb = sc.get("moe_deq", (E * max(F * H, H * F),), torch.bfloat16)
-    w_gu = wb[:E * F * H].view(E * F, H)
+    wb = sc.get("moe_deq", (El * max(F * H, H * F),), torch.bfloat16)
+    w_gu = wb[:El * F * H].view(El * F, H)
     K.dequant_bf16(wg, w_gu)
-    GM.gemm_bf16_grouped(xs, w_gu, gu[:, :F], E, tile_group)
+    GM.gemm_bf16_grouped(xs, w_gu, gu[:, :F], El, tile_group)
     K.dequant_bf16(wu, w_gu)
-    GM.gemm_bf16_grouped(xs, w_gu, gu[:, F:], E, tile_group)
+    GM.gemm_bf16_grouped(xs, w_gu, gu[:, F:], El, tile_group)
     act = sc.get("moe_act_g", (bound, F), torch.bfloat16)
     K.act_mul(gu, act, cfg.act)
-    w_d = wb[:E * H * F].view(E * H, F)
+    w_d = wb[:El * H * F].view(El * H, F)
     K.dequant_bf16(wd, w_d)
     ys = sc.get("moe_ys", (bound, H), torch.bfloat16)
-    GM.gemm_bf16_grouped(act, w_d, ys, E, tile_group)
+    GM.gemm_bf16_grouped(act, w_d, ys, El, tile_group)
     ysh = None
-    if L.has_shared:
+    if shared_here:
         Fs = cfg.shared_ffn
         gus = sc.get("moe_gus", (T, 2 * Fs), torch.bfloat16)
         ex._gemm(xn, ex.W(i, "ffn_gate_shexp.weight"), gus[:, :Fs], tag="g")
@@ -144,4 +162,4 @@ def _moe_grouped(ex, i: int, h: torch.Tensor, T: int, norm_w: torch.Tensor) -> N
         acts = sc.get("moe_acts", (T, Fs), torch.bfloat16)
         K.act_mul(gus, acts, cfg.act)
         ysh = ex._gemm(acts, ex.W(i, "ffn_down_shexp.weight"), sc.get("y_bf", (T, H), torch.bfloat16), tag="d")
-    K.moe_combine(h, ys, pos, wts, k, ysh, logits[:, E:E + 1] if L.has_shared else None)
+    K.moe_combine(target, ys, pos, wts, k, ysh, logits[:, E:E + 1] if shared_here else None)

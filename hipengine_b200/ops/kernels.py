@@ -82,7 +82,8 @@ class _MoeSelArgs(C.Structure):
     _fields_ = [("x", c_vp), ("ldx", c_ll), ("norm_w", c_vp), ("eps", C.c_float), ("ids", c_vp), ("wts", c_vp),
                 ("w1", c_vp), ("w2", c_vp), ("qtype1", C.c_int), ("qtype2", C.c_int),
                 ("T", C.c_int), ("k", C.c_int), ("K", C.c_int), ("N", C.c_int), ("act", C.c_int),
-                ("out", c_vp), ("ldo", c_ll), ("rows_per_cta", C.c_int), ("expert_rows", C.c_int)]
+                ("out", c_vp), ("ldo", c_ll), ("rows_per_cta", C.c_int), ("expert_rows", C.c_int),
+                ("expert_lo", C.c_int), ("expert_n", C.c_int)]
 
 
 _CHECKED = False
@@ -464,8 +465,12 @@ def moe_sorted_rows_bound(P: int, E: int) -> int:
     return ((P + 127) // 128 + E) * 128
 
 
-def moe_group(ids: torch.Tensor, E: int, pos: torch.Tensor, tile_group: torch.Tensor, meta: torch.Tensor) -> None:
-    N.check(N.lib().he_moe_group(c_vp(ids.data_ptr()), C.c_int(ids.numel()), C.c_int(E), c_vp(pos.data_ptr()),
+def moe_group(ids: torch.Tensor, E: int, pos: torch.Tensor, tile_group: torch.Tensor, meta: torch.Tensor,
+              expert_lo: int = 0) -> None:
+    """Bucket the (token, expert) pairs by expert.  ``E`` local experts starting at ``expert_lo``; pairs routed to
+    other experts get pos = -1."""
+    N.check(N.lib().he_moe_group(c_vp(ids.data_ptr()), C.c_int(ids.numel()), C.c_int(E), C.c_int(expert_lo),
+                                 c_vp(pos.data_ptr()),
                                  c_vp(tile_group.data_ptr()), C.c_int(tile_group.numel()), c_vp(meta.data_ptr()),
                                  _stream()), "he_moe_group")
 
@@ -493,7 +498,7 @@ def moe_scale_rows(act: torch.Tensor, sg: torch.Tensor) -> None:
 
 
 def _moe_sel(fn: str, x, norm_w, eps, ids, wts, w1: "DeviceWeight", w2, n_rows: int, out, act: str,
-             expert_rows: int = 0, w2_row0: int = 0) -> None:
+             expert_rows: int = 0, w2_row0: int = 0, expert_range: Tuple[int, int] = (0, 0)) -> None:
     _check_abi()
     a = _MoeSelArgs()
     a.x, a.ldx, a.norm_w, a.eps = x.data_ptr(), x.stride(0), _p(norm_w), eps
@@ -502,6 +507,7 @@ def _moe_sel(fn: str, x, norm_w, eps, ids, wts, w1: "DeviceWeight", w2, n_rows: 
     a.w2, a.qtype2 = (w2.ptr + w2_row0 * device_row_bytes(w2.qtype, w2.n_cols), w2.qtype) if w2 is not None \
         else (None, w1.qtype)
     a.expert_rows = expert_rows
+    a.expert_lo, a.expert_n = expert_range[0], max(0, expert_range[1] - expert_range[0])
     a.T, a.k, a.K, a.N = ids.shape[0], ids.shape[1], w1.n_cols, n_rows
     a.act = 0 if act == "silu" else 1
     a.out, a.ldo = out.data_ptr(), out.stride(0)
@@ -510,20 +516,23 @@ def _moe_sel(fn: str, x, norm_w, eps, ids, wts, w1: "DeviceWeight", w2, n_rows: 
 
 def moe_gateup_sel(h: torch.Tensor, norm_w: Optional[torch.Tensor], eps: float, ids: torch.Tensor,
                    wts: torch.Tensor, w_gate: "DeviceWeight", w_up: "DeviceWeight", n_ff: int, out: torch.Tensor,
-                   act: str = "silu", fused_gate_up: bool = False) -> None:
+                   act: str = "silu", fused_gate_up: bool = False, expert_range: Tuple[int, int] = (0, 0)) -> None:
     """out[t*k+j, :] = act(Wg[e] xn_t) * (Wu[e] xn_t) (bf16) for the selected experts e = ids[t, j].
     ``fused_gate_up``: ``w_gate`` holds, per expert, n_ff gate rows followed by n_ff up rows (``w_up`` ignored)."""
     if fused_gate_up:
         _moe_sel("he_moe_gateup_sel", h, norm_w, eps, ids, wts, w_gate, w_gate, n_ff, out, act,
-                 expert_rows=2 * n_ff, w2_row0=n_ff)
+                 expert_rows=2 * n_ff, w2_row0=n_ff, expert_range=expert_range)
     else:
-        _moe_sel("he_moe_gateup_sel", h, norm_w, eps, ids, wts, w_gate, w_up, n_ff, out, act)
+        _moe_sel("he_moe_gateup_sel", h, norm_w, eps, ids, wts, w_gate, w_up, n_ff, out, act,
+                 expert_range=expert_range)
 
 
 def moe_down_sel(act_rows: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_down: "DeviceWeight", n_out: int,
-                 h: torch.Tensor) -> None:
-    """h[t, :] += sum_j wts[t, j] * Wd[ids[t, j]] act_rows[t*k+j, :]  (fp32 residual, in place)."""
-    _moe_sel("he_moe_down_sel", act_rows, None, 0.0, ids, wts, w_down, None, n_out, h, "silu")
+                 h: torch.Tensor, expert_range: Tuple[int, int] = (0, 0)) -> None:
+    """h[t, :] += sum_j wts[t, j] * Wd[ids[t, j]] act_rows[t*k+j, :]  (fp32 residual, in place).
+    ``expert_range`` = (lo, hi) restricts the sum to the local experts of an expert-parallel rank."""
+    _moe_sel("he_moe_down_sel", act_rows, None, 0.0, ids, wts, w_down, None, n_out, h, "silu",
+             expert_range=expert_range)
 
 
 # ----------------------------------------------------------------------------- speculative decoding

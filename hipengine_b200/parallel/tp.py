@@ -37,6 +37,10 @@ class TPHybridExecutor(HybridExecutor):
         shard, self.plan = shard_weights(full_weights, ctx.world, ctx.rank)
         self.comm = comm or os.environ.get("HE_TP_COMM", "nccl")
         super().__init__(shard, device=ctx.device, **kw)
+        if self.full_cfg.is_moe and ctx.world > 1:
+            # expert parallelism over the replicated activations: this rank computes only its experts' share
+            self.expert_range = self.plan.experts
+            self.owns_shared_expert = self.plan.owns_shared_expert
         self.fused = None
         if self.comm == "fused" and ctx.world > 1:
             from .fused import FusedReducer
@@ -54,6 +58,16 @@ class TPHybridExecutor(HybridExecutor):
             return
         part = self.scratch.get("tp_part", (T, w.n_rows), torch.float32)
         K.gemv(x, [GemvSegment(w, part, K.EPI_F32)])
+        self.ctx.all_reduce_(part)
+        K.resid_add_f32(h, part)
+
+    def _moe_reduce(self, h: torch.Tensor, part: torch.Tensor) -> None:
+        """h += sum over ranks of the per-rank expert contributions ``part`` [T, hidden] fp32."""
+        T = part.shape[0]
+        if self.fused is not None and T <= self.fused.max_rows:
+            self.fused.local_rows(T).copy_(part)
+            self.fused.reduce_add(h, T)
+            return
         self.ctx.all_reduce_(part)
         K.resid_add_f32(h, part)
 

@@ -68,3 +68,23 @@ def test_tiny_dense_greedy_generation_config1():
     out2, lg2 = m.generate(prompt, 16)
     assert out1 == out2 and len(out1) == 16 and lg1.shape == (16, 4096)
     assert torch.equal(lg1, lg2)
+
+
+def test_gemma4_reference_incremental_equals_batch():
+    """Gemma 4 oracle: feeding a prompt in two pieces (KV carried over, sliding window exceeded) gives the same
+    logits as one pass, and the logits respect the soft-cap."""
+    import torch
+    from hipengine_b200.loading.synth import build_random_model
+    from hipengine_b200.models.config import TINY_GEMMA4
+    from hipengine_b200.ref.model import RefModel
+    w = build_random_model(TINY_GEMMA4, seed=0, std=0.05)
+    m = RefModel(w)
+    toks = torch.randint(0, TINY_GEMMA4.vocab, (48,), generator=torch.Generator().manual_seed(0))
+    full, _ = m.forward(toks)
+    a, st = m.forward(toks[:37])
+    b, _ = m.forward(toks[37:], st)
+    torch.testing.assert_close(torch.cat([a, b]), full, atol=2e-4, rtol=2e-4)
+    assert float(full.abs().max()) <= TINY_GEMMA4.final_softcap
+    # global layers have no attn_v tensor (V = K) and a wider head
+    assert "blk.5.attn_v.weight" not in w.tensors and "blk.0.attn_v.weight" in w.tensors
+    assert w["blk.5.attn_k.weight"].shape[0] == TINY_GEMMA4.global_kv_heads * TINY_GEMMA4.global_head_dim
