@@ -151,7 +151,140 @@ class GGUFBPETokenizer(BaseTokenizer):
         return self._tk.token_to_id(tok)
 
 
+class GGUFSPMTokenizer(BaseTokenizer):
+    """SentencePiece-style tokenizer rebuilt from GGUF metadata (``tokenizer.ggml.model = llama``; Gemma files).
+
+    Text is split on special tokens, spaces become U+2581, then adjacent symbols are merged greedily by the score
+    of the merged piece (highest first, leftmost on ties) -- the bigram-queue procedure llama.cpp uses for SPM
+    vocabularies; characters without a piece fall back to ``<0xNN>`` byte tokens.  Counterpart of the reference's
+    Gemma tokenizer (``hipengine/tokenization/``, "Gemma 4 SPM-style").
+    """
+
+    def __init__(self, tokens: Sequence[str], scores: Sequence[float], token_types: Optional[Sequence[int]] = None,
+                 eos_id: Optional[int] = None, bos_id: Optional[int] = None, add_space_prefix: bool = False):
+        self.tokens = list(tokens)
+        self.scores = list(scores) if scores else [0.0] * len(tokens)
+        self.vocab = {t: i for i, t in enumerate(self.tokens)}
+        self.vocab_size = len(self.tokens)
+        self.eos_token_id, self.bos_token_id = eos_id, bos_id
+        self.add_space_prefix = add_space_prefix
+        tt = list(token_types) if token_types is not None else [1] * len(tokens)
+        self.special = {t: i for i, t in enumerate(self.tokens) if tt[i] in (3, 4)}
+        self.byte_ids = {}
+        for i, t in enumerate(self.tokens):
+            if tt[i] == 6 or (len(t) == 6 and t.startswith("<0x") and t.endswith(">")):
+                try:
+                    self.byte_ids[int(t[3:5], 16)] = i
+                except ValueError:
+                    pass
+        self._special_re = (re.compile("|".join(re.escape(x) for x in sorted(self.special, key=len, reverse=True)))
+                            if self.special else None)
+        self.unk_id = self.vocab.get("<unk>", 0)
+
+    def _encode_piece(self, text: str) -> List[int]:
+        import heapq
+        if not text:
+            return []
+        syms = list(text)
+        n = len(syms)
+        prev = list(range(-1, n - 1))
+        nxt = list(range(1, n + 1))
+        nxt[-1] = -1
+        alive = [True] * n
+        heap = []
+
+        def push(i):
+            j = nxt[i]
+            if i < 0 or j < 0:
+                return
+            merged = syms[i] + syms[j]
+            tid = self.vocab.get(merged)
+            if tid is not None:
+                heapq.heappush(heap, (-self.scores[tid], i, merged))
+
+        for i in range(n - 1):
+            push(i)
+        while heap:
+            _, i, merged = heapq.heappop(heap)
+            j = nxt[i] if alive[i] else -1
+            if j < 0 or not alive[j] or syms[i] + syms[j] != merged:
+                continue
+            syms[i] = merged
+            alive[j] = False
+            nxt[i] = nxt[j]
+            if nxt[j] >= 0:
+                prev[nxt[j]] = i
+            if prev[i] >= 0:
+                push(prev[i])
+            push(i)
+        out: List[int] = []
+        i = 0
+        while i >= 0:
+            if alive[i]:
+                tid = self.vocab.get(syms[i])
+                if tid is not None:
+                    out.append(tid)
+                else:
+                    for b in syms[i].encode("utf-8"):
+                        out.append(self.byte_ids.get(b, self.unk_id))
+            i = nxt[i]
+        return out
+
+    def encode(self, text: str) -> List[int]:
+        out: List[int] = []
+        pos = 0
+        first = True
+
+        def plain(chunk: str) -> None:
+            nonlocal first
+            if not chunk:
+                return
+            t = chunk.replace(" ", "\u2581")
+            if first and self.add_space_prefix and not t.startswith("\u2581"):
+                t = "\u2581" + t
+            first = False
+            out.extend(self._encode_piece(t))
+
+        if self._special_re is not None:
+            for m in self._special_re.finditer(text):
+                plain(text[pos:m.start()])
+                out.append(self.special[m.group(0)])
+                first = False
+                pos = m.end()
+        plain(text[pos:])
+        return out
+
+    def decode(self, ids: Sequence[int]) -> str:
+        parts: List[str] = []
+        buf = bytearray()
+        inv_bytes = {v: k for k, v in self.byte_ids.items()}
+        for i in ids:
+            i = int(i)
+            if i in inv_bytes:
+                buf.append(inv_bytes[i])
+                continue
+            if buf:
+                parts.append(buf.decode("utf-8", errors="replace"))
+                buf = bytearray()
+            if 0 <= i < self.vocab_size:
+                parts.append(self.tokens[i])
+        if buf:
+            parts.append(buf.decode("utf-8", errors="replace"))
+        return "".join(parts).replace("\u2581", " ")
+
+    def token_to_id(self, tok: str) -> Optional[int]:
+        return self.vocab.get(tok)
+
+
 def tokenizer_from_metadata(meta: Mapping[str, Any], vocab_size: int) -> BaseTokenizer:
+    if meta.get("tokenizer.ggml.model") == "llama" and meta.get("tokenizer.ggml.tokens"):
+        try:
+            return GGUFSPMTokenizer(meta["tokenizer.ggml.tokens"], meta.get("tokenizer.ggml.scores") or [],
+                                    meta.get("tokenizer.ggml.token_type"), meta.get("tokenizer.ggml.eos_token_id"),
+                                    meta.get("tokenizer.ggml.bos_token_id"),
+                                    bool(meta.get("tokenizer.ggml.add_space_prefix", False)))
+        except Exception:
+            pass
     tokens = meta.get("tokenizer.ggml.tokens")
     merges = meta.get("tokenizer.ggml.merges")
     if tokens and merges and meta.get("tokenizer.ggml.model", "gpt2") == "gpt2":

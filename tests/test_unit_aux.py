@@ -97,3 +97,26 @@ def test_injected_decode_failure_is_contained():
     runner = SimulatedRunner(cfg, fail_decode_admission=[2])
     res = run_load_scenario(cfg, reqs, [0.0] * 4, max_concurrent=4, runner=runner)
     assert res.failed == 1 and res.completed == 3           # only the named request fails; the rest finish
+
+
+def test_tool_call_grammar_generator():
+    from hipengine_b200.generation.grammar import grammar_available, tool_call_grammar
+    tools = [{"type": "function", "function": {"name": "get_weather", "parameters": {
+        "type": "object", "properties": {"city": {"type": "string"}, "unit": {"enum": ["c", "f"]},
+                                         "days": {"type": "integer"}, "opts": {"type": "object"}},
+        "required": ["city", "days"]}}},
+        {"type": "function", "function": {"name": "noop", "parameters": {"type": "object", "properties": {}}}}]
+    g = tool_call_grammar(tools)
+    assert 'start: [text] call (ws call)*' in g
+    assert '"<function=get_weather>"' in g and '"<function=noop>"' in g
+    assert '"<parameter=city>"' in g and '[p_0_1]' in g            # optional parameter is bracketed
+    assert 'p_0_0 [p_0_1] p_0_2 [p_0_3]' in g                       # schema order, required ones mandatory
+    assert "json_value" in g and '"c" | "f"' in g
+    single = tool_call_grammar(tools, allow_text_before=False, parallel=False, only="noop")
+    assert "get_weather" not in single and single.startswith("start: call\n")
+    import pytest
+    with pytest.raises(ValueError):
+        tool_call_grammar([{"function": {"name": "bad name"}}])
+    with pytest.raises(ValueError):
+        tool_call_grammar(tools, only="missing")
+    assert isinstance(grammar_available(), bool)

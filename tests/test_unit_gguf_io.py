@@ -50,3 +50,42 @@ def test_fingerprint_ignores_tokenizer_and_general(tmp_path):
     w.metadata["qwen3.rope.freq_base"] = 12345.0
     c = write_gguf(w, tmp_path / "c.gguf")
     assert execution_fingerprint(scan_gguf(a)) != execution_fingerprint(scan_gguf(c))
+
+
+def test_spm_tokenizer_round_trip_and_scores():
+    from hipengine_b200.tokenization.gguf_tokenizer import GGUFSPMTokenizer, tokenizer_from_metadata
+    toks = ["<unk>", "<s>", "</s>"] + [f"<0x{b:02X}>" for b in range(256)] + \
+           ["\u2581", "h", "e", "l", "o", "w", "r", "d", "he", "ll", "llo", "hello", "\u2581hello", "\u2581w", "or", "ld",
+            "\u2581world", "<start_of_turn>"]
+    scores = [0.0] * 259 + [-1, -2, -2, -2, -2, -2, -2, -2, -3, -3, -4, -5, -6, -4, -4, -4, -7, 0]
+    types = [2, 3, 3] + [6] * 256 + [1] * 17 + [4]
+    tk = GGUFSPMTokenizer(toks, scores, types, eos_id=2, bos_id=1)
+    ids = tk.encode("hello world")
+    assert [toks[i] for i in ids] == ["hello", "\u2581w", "or", "ld"]      # best-scored merges win step by step
+    assert tk.decode(ids) == "hello world"
+    ids = tk.encode("<start_of_turn>hé")                                    # special token + byte fallback for é
+    assert ids[0] == tk.special["<start_of_turn>"] and toks[ids[1]] == "h"
+    assert [toks[i] for i in ids[2:]] == ["<0xC3>", "<0xA9>"] and tk.decode(ids) == "<start_of_turn>hé"
+    meta = {"tokenizer.ggml.model": "llama", "tokenizer.ggml.tokens": toks, "tokenizer.ggml.scores": scores,
+            "tokenizer.ggml.token_type": types, "tokenizer.ggml.eos_token_id": 2}
+    assert isinstance(tokenizer_from_metadata(meta, len(toks)), GGUFSPMTokenizer)
+
+
+def test_local_only_model_resolution(tmp_path, monkeypatch):
+    from hipengine_b200.loading.hf_cache import ModelNotFound, resolve_model_path
+    hub = tmp_path / "hub"
+    snap = hub / "models--org--m" / "snapshots" / "abc"
+    snap.mkdir(parents=True)
+    (hub / "models--org--m" / "refs").mkdir()
+    (hub / "models--org--m" / "refs" / "main").write_text("abc")
+    for n in ("m-Q4_K_M-00001-of-00002.gguf", "m-Q4_K_M-00002-of-00002.gguf", "m-Q8_0.gguf", "mmproj-m.gguf"):
+        (snap / n).write_bytes(b"GGUF")
+    monkeypatch.setenv("HF_HUB_CACHE", str(hub))
+    monkeypatch.delenv("HE_MODEL_DIR", raising=False)
+    got = resolve_model_path("org/m", quant_hint="q4_k_m")
+    assert [p.name for p in got] == ["m-Q4_K_M-00001-of-00002.gguf", "m-Q4_K_M-00002-of-00002.gguf"]
+    assert [p.name for p in resolve_model_path("org/m", quant_hint="q8_0")] == ["m-Q8_0.gguf"]
+    assert resolve_model_path(str(snap / "m-Q8_0.gguf"))[0].name == "m-Q8_0.gguf"
+    import pytest
+    with pytest.raises(ModelNotFound, match="never downloaded"):
+        resolve_model_path("org/absent")
