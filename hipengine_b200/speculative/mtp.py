@@ -107,7 +107,15 @@ class MTPCycle:
         vb.tokens = torch.cat([t0[:, None], drafts], 1).reshape(-1).contiguous()
         journal = {"conv": {i: t[:T] for i, t in self.journal["conv"].items()},
                    "gdn": {i: t[:T] for i, t in self.journal["gdn"].items()}}
-        h = ex.forward(vb, journal=journal)
+        # a verify chain must see the numerics of plain decode (the int8 GEMV path), or a near-tie could make the
+        # verifier disagree with what autoregressive decoding would have produced: keep chains of up to 8 rows there
+        saved_small = ex.small_rows
+        if T <= GEMV_MAX_ROWS:
+            ex.small_rows = GEMV_MAX_ROWS
+        try:
+            h = ex.forward(vb, journal=journal)
+        finally:
+            ex.small_rows = saved_small
         logits = ex.scratch.get("mtp_logits", (T, cfg.vocab), torch.float32)
         hid = ex.scratch.get("mtp_vhid", (T, cfg.hidden), torch.float32)
         for r0 in range(0, T, GEMV_MAX_ROWS):
