@@ -479,6 +479,8 @@ int launch_gemv(HeGemvArgs a, int num_sms, cudaStream_t stream) {
   // 16 warps per CTA when two ring slots each still fit beside the activations, else 8
   int nw = 16;
   if (x_bytes + (size_t)2 * 16 * a.slot_bytes > budget) nw = 8;
+  static const int nw_env = []() { const char* e = getenv("HE_GEMV_NW"); return e ? atoi(e) : 0; }();
+  if (nw_env == 8) nw = 8;
   int n_slots = MAX_SLOTS;
   while (n_slots > 2 && x_bytes + (size_t)n_slots * nw * a.slot_bytes > budget) --n_slots;
   if (x_bytes + (size_t)n_slots * nw * a.slot_bytes > budget) return -HE_ERR_BAD_ARG;
@@ -486,7 +488,23 @@ int launch_gemv(HeGemvArgs a, int num_sms, cudaStream_t stream) {
   // rows per item: as many as keeps every warp of the grid busy for at least two items
   const long long warps = (long long)num_sms * nw;
   int rg = 8;
-  while (rg > 2 && rows / rg < 2 * warps) rg >>= 1;
+  if (per_block == 144) {
+    // all-Q4_K launch (measured on B200): what matters is (a) lanes not idling in the last unit of a row --
+    // a unit is 32/rg blocks wide, so K = 5120 (20 blocks) wants rg = 8, K = 6144 (24 blocks) rg = 4 -- and
+    // (b) at least about half as many work items as warps; pick the rg with the best product of the two
+    double best = -1.0;
+    for (int cand = 8; cand >= 2; cand >>= 1) {
+      const int bq = 32 / cand;
+      const double eff = (double)nb / (double)(((nb + bq - 1) / bq) * bq);
+      const double fill = (double)(rows / cand) / (0.5 * (double)warps);
+      const double score = eff * (fill < 1.0 ? fill : 1.0);
+      if (score > best + 1e-9) { best = score; rg = cand; }
+    }
+  } else {
+    while (rg > 2 && rows / rg < 2 * warps) rg >>= 1;
+  }
+  static const int rg_env = []() { const char* e = getenv("HE_GEMV_RG"); return e ? atoi(e) : 0; }();
+  if (rg_env == 2 || rg_env == 4 || rg_env == 8) rg = rg_env;
   a.rg = rg;
   long long items = 0;
   for (int i = 0; i < a.n_seg; ++i) {

@@ -333,8 +333,17 @@ class HybridExecutor:
             z = sc.get("z_f32", (T, inner), torch.float32)
             if i in self.ab_q8:
                 ab = sc.get("ab_proj", (T, 2 * Hv), torch.float32)
-                K.gemv(h, [GemvSegment(self.W(i, "attn_qkv.weight"), qkv), GemvSegment(self.W(i, "attn_gate.weight"), z),
-                           GemvSegment(self.ab_q8[i], ab)], norm_w=self.F(i, "attn_norm.weight"), eps=cfg.rms_eps)
+                if os.environ.get("HE_AB_SPLIT", "1") != "0":
+                    # the 2*Hv Q8_0 rows get their own (tiny) launch: in the same launch their 272-byte blocks
+                    # would size every ring slot and halve the warps of the two big Q4_K projections
+                    K.gemv(h, [GemvSegment(self.W(i, "attn_qkv.weight"), qkv),
+                               GemvSegment(self.W(i, "attn_gate.weight"), z)],
+                           norm_w=self.F(i, "attn_norm.weight"), eps=cfg.rms_eps)
+                    K.gemv(h, [GemvSegment(self.ab_q8[i], ab)], norm_w=self.F(i, "attn_norm.weight"), eps=cfg.rms_eps)
+                else:
+                    K.gemv(h, [GemvSegment(self.W(i, "attn_qkv.weight"), qkv),
+                               GemvSegment(self.W(i, "attn_gate.weight"), z), GemvSegment(self.ab_q8[i], ab)],
+                           norm_w=self.F(i, "attn_norm.weight"), eps=cfg.rms_eps)
                 a_p, b_p = ab[:, :Hv], ab[:, Hv:]
             else:
                 K.gemv(h, [GemvSegment(self.W(i, "attn_qkv.weight"), qkv),
