@@ -99,7 +99,7 @@ def bench_gemv(N, K, qtype="q4_k", rows=1):
             f"frac_of_{pk['src']}_hbm": round(gbs / pk["hbm_gbs"], 3)}
 
 
-def bench_gdn_scan(T, Hv=48, G=16, n_seg=1):
+def bench_gdn_scan(T, Hv=48, G=16, n_seg=1, chunked=False):
     """Prefill scan of one gated delta-net layer: T tokens in n_seg segments (27B geometry by default)."""
     from hipengine_b200.ops import kernels as Kn
     pk = peaks()
@@ -112,11 +112,14 @@ def bench_gdn_scan(T, Hv=48, G=16, n_seg=1):
     seg_start = torch.arange(0, T + 1, T // n_seg, device="cuda", dtype=torch.int32)[:n_seg + 1].contiguous()
     seg_slot = torch.arange(n_seg, device="cuda", dtype=torch.int32)
     out = torch.empty(T, Hv, S, device="cuda")
-    fn = lambda i: Kn.gdn_scan(qkv, decay, beta, state, seg_start, seg_slot, out, G, Hv)
+    if chunked:
+        fn = lambda i: Kn.gdn_scan_chunked(qkv, decay, beta, state, seg_start, seg_slot, out, G, Hv)
+    else:
+        fn = lambda i: Kn.gdn_scan(qkv, decay, beta, state, seg_start, seg_slot, out, G, Hv)
     ms = time_launches(fn, 1)
     flops = 6.0 * T * Hv * S * S          # decay, k.S, rank-1 update, q.S: about 6 flop per state element per token
     bytes_ = (qkv.numel() + out.numel()) * 4.0 + 2.0 * state.numel() * 4
-    return {"kernel": "gdn_scan", "T": T, "Hv": Hv, "n_seg": n_seg, "ms": round(ms, 4),
+    return {"kernel": "gdn_scan_chunked" if chunked else "gdn_scan", "T": T, "Hv": Hv, "n_seg": n_seg, "ms": round(ms, 4),
             "tflops_fp32": round(flops / ms / 1e9, 2), "us_per_token": round(1e3 * ms / (T / n_seg), 3),
             "GBps": round(bytes_ / ms / 1e6, 1), f"frac_of_{pk['src']}_hbm": round(bytes_ / ms / 1e6 / pk["hbm_gbs"], 3)}
 
@@ -181,6 +184,7 @@ def main():
         out.append(bench_gemv(a.n, a.k, a.qtype, a.rows))
     elif a.what == "gdn":
         out.append(bench_gdn_scan(a.t))
+        out.append(bench_gdn_scan(a.t, chunked=True))
     elif a.what == "conv":
         out.append(bench_conv(a.t))
     elif a.what == "attn":
@@ -194,6 +198,7 @@ def main():
             for r in (1, 4):
                 out.append(bench_gemv(n, k, q, r))
         out.append(bench_gdn_scan(4096))
+        out.append(bench_gdn_scan(4096, chunked=True))
         out.append(bench_conv(4096))
         for c in (4096, 32768):
             out.append(bench_attn_decode(c))

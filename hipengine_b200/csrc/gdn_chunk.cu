@@ -1,0 +1,292 @@
+// Gated DeltaNet prefill scan in chunked (WY) form on the tensor cores.
+//
+// The recurrence  S_t = g_t S_{t-1} + k_t d_t^T,  d_t = beta_t (v_t - (g_t S_{t-1})^T k_t),  o_t = S_t^T q_t
+// (hipengine/kernels/cpu_reference/ops.py:1967-2012; chunked algebra oracle :2015-2141) is evaluated 16 tokens at
+// a time.  With G_t = prod_{s<=t} g_s inside the chunk (kept as log-sums, ratios G_t/G_j <= 1 for j <= t):
+//     A_tj = beta_t (G_t/G_j)(k_t.k_j), j < t          (strictly lower 16x16)
+//     (I + A) [U | W] = [beta*V | beta*G*K]             (forward substitution, one thread per column)
+//     D = U - W S_0                                     (the 16 delta rows)
+//     O = (G*Q) S_0 + P D,  P_tj = (G_t/G_j)(q_t.k_j), j <= t
+//     S_16 = G_16 S_0 + Kt^T D,  Kt_j = (G_16/G_j) k_j
+// All matrix products run as mma.sync m16n8k8 TF32 (fp32 accumulate) from shared memory; the state slice stays in
+// shared memory for the whole segment.  One CTA = (segment, V head, 32-column slice of the state), 4 warps; the
+// next chunk's K / Q / V rows are fetched with cp.async while the current chunk computes.
+// Used for prefill segments without a state journal; decode rows, verify chains and short segments keep the
+// serial kernel in gdn.cu.  V head h reads K head h % G (GGUF order).
+#include "common.cuh"
+
+using namespace he;
+
+namespace {
+
+constexpr int CK = 16;          // tokens per chunk
+constexpr int DK = 128;         // state rows (key dim)
+constexpr int NV = 32;          // state columns per CTA
+constexpr int LDK = DK + 4;     // sK / sQ / sW row stride (floats): conflict-free A-fragment reads
+constexpr int LDS_ = NV + 8;    // sS / sVn / sU row stride: conflict-free B-fragment reads
+constexpr int LDA = CK + 1;
+
+struct GdnChunkArgs {
+  const float* qkv;       // [T][C] prepared conv output: q | k | v (q, k normalised)
+  const float* decay;     // [T][Hv]
+  const float* beta;      // [T][Hv]
+  float* state;           // [n_slots][Hv][128][128]
+  const int* seg_start;   // [n_seg+1]
+  const int* seg_slot;    // [n_seg]
+  float* out;             // [T][Hv][128]
+  int C, G, Hv, T, n_seg;
+  int write_state;
+};
+
+__device__ __forceinline__ uint32_t tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ void mma_tf32(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, int src_bytes) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+struct Smem {
+  float K[2][CK][LDK];
+  float Q[2][CK][LDK];
+  float V[2][CK][LDS_];
+  float S[DK][LDS_];       // state slice [k][n]
+  float W[CK][LDK];
+  float U[CK][LDS_];
+  float D[CK][LDS_];       // delta rows
+  float A[CK][LDA];
+  float P[CK][LDA];
+  float b[2][CK];          // inclusive log-decay sums of the chunk
+  float bt[2][CK];         // beta
+};
+
+// grid (n_seg, Hv, DV/NV), block 128
+__global__ void __launch_bounds__(128) gdn_chunk_kernel(const GdnChunkArgs p) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
+  const int sg = blockIdx.x, h = blockIdx.y, sl = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int kh = h % p.G;
+  const int s0 = p.seg_start[sg], s1 = p.seg_start[sg + 1];
+  const int n_chunks = (s1 - s0 + CK - 1) / CK;
+  float* Sg = p.state + (((size_t)p.seg_slot[sg] * p.Hv + h) * DK) * 128 + sl * NV;
+  const size_t q_off = (size_t)kh * DK, k_off = (size_t)p.G * DK + (size_t)kh * DK;
+  const size_t v_off = (size_t)2 * p.G * DK + (size_t)h * 128 + sl * NV;
+
+  for (int i = tid; i < DK * (NV / 4); i += 128) {
+    const int r = i / (NV / 4), c4 = (i % (NV / 4)) * 4;
+    *reinterpret_cast<float4*>(&sm.S[r][c4]) = *reinterpret_cast<const float4*>(Sg + (size_t)r * 128 + c4);
+  }
+
+  auto prefetch = [&](int chunk, int buf) {
+    const int c0 = s0 + chunk * CK;
+    for (int i = tid; i < CK * (DK / 4); i += 128) {
+      const int tt = i / (DK / 4), d4 = (i % (DK / 4)) * 4;
+      const int tok = c0 + tt;
+      const bool ok = tok < s1;
+      const float* row = p.qkv + (size_t)(ok ? tok : s0) * p.C;
+      cp_async16(&sm.K[buf][tt][d4], row + k_off + d4, ok ? 16 : 0);
+      cp_async16(&sm.Q[buf][tt][d4], row + q_off + d4, ok ? 16 : 0);
+    }
+    for (int i = tid; i < CK * (NV / 4); i += 128) {
+      const int tt = i / (NV / 4), d4 = (i % (NV / 4)) * 4;
+      const int tok = c0 + tt;
+      const bool ok = tok < s1;
+      cp_async16(&sm.V[buf][tt][d4], p.qkv + (size_t)(ok ? tok : s0) * p.C + v_off + d4, ok ? 16 : 0);
+    }
+    cp_async_commit();
+    if (tid < CK) {
+      // inclusive prefix of log(decay) over the chunk; tokens past the segment end act as identity steps
+      const int tok = c0 + tid;
+      const bool ok = tok < s1;
+      float lg = ok ? __logf(fmaxf(p.decay[(size_t)tok * p.Hv + h], 1e-37f)) : 0.f;
+#pragma unroll
+      for (int o = 1; o < CK; o <<= 1) {
+        const float v = __shfl_up_sync(0x0000ffffu, lg, o, CK);
+        if (tid >= o) lg += v;
+      }
+      sm.b[buf][tid] = lg;
+      sm.bt[buf][tid] = ok ? p.beta[(size_t)tok * p.Hv + h] : 0.f;
+    }
+  };
+
+  if (n_chunks > 0) prefetch(0, 0);
+  float qs[4];
+  for (int ch = 0; ch < n_chunks; ++ch) {
+    const int buf = ch & 1;
+    cp_async_wait_all();
+    __syncthreads();                       // chunk data + previous state update visible to everyone
+    if (ch + 1 < n_chunks) prefetch(ch + 1, buf ^ 1);
+    float (*K_)[LDK] = sm.K[buf];
+    float (*Q_)[LDK] = sm.Q[buf];
+    const float* b = sm.b[buf];
+    const float* bt = sm.bt[buf];
+
+    // ---- phase 1: K K^T (warps 0,1), Q K^T (warps 2,3), and every warp's n-tile of Q S_0
+    {
+      const int nt = warp & 1;
+      float (*X_)[LDK] = warp < 2 ? K_ : Q_;
+      float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+      for (int ks = 0; ks < DK / 8; ++ks) {
+        const int k0 = ks * 8;
+        mma_tf32(c, tf32(X_[g][k0 + t]), tf32(X_[g + 8][k0 + t]), tf32(X_[g][k0 + t + 4]), tf32(X_[g + 8][k0 + t + 4]),
+                 tf32(K_[nt * 8 + g][k0 + t]), tf32(K_[nt * 8 + g][k0 + t + 4]));
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = g + (e >> 1) * 8, j = nt * 8 + 2 * t + (e & 1);
+        const float ratio = __expf(b[i] - b[j]);
+        if (warp < 2) sm.A[i][j] = j < i ? bt[i] * ratio * c[e] : 0.f;
+        else sm.P[i][j] = j <= i ? ratio * c[e] : 0.f;
+      }
+      qs[0] = qs[1] = qs[2] = qs[3] = 0.f;
+      const int n0 = warp * 8;
+#pragma unroll 4
+      for (int ks = 0; ks < DK / 8; ++ks) {
+        const int k0 = ks * 8;
+        mma_tf32(qs, tf32(Q_[g][k0 + t]), tf32(Q_[g + 8][k0 + t]), tf32(Q_[g][k0 + t + 4]), tf32(Q_[g + 8][k0 + t + 4]),
+                 tf32(sm.S[k0 + t][n0 + g]), tf32(sm.S[k0 + t + 4][n0 + g]));
+      }
+    }
+    __syncthreads();
+
+    // ---- phase 2: (I + A) [U | W] = [beta V | beta G K], one column per thread (W: 128 columns, U: 32)
+    {
+      float x[CK];
+#pragma unroll
+      for (int i = 0; i < CK; ++i) {
+        float r = bt[i] * __expf(b[i]) * K_[i][tid];
+#pragma unroll
+        for (int j = 0; j < i; ++j) r -= sm.A[i][j] * x[j];
+        x[i] = r;
+        sm.W[i][tid] = r;
+      }
+      if (tid < NV) {
+#pragma unroll
+        for (int i = 0; i < CK; ++i) {
+          float r = bt[i] * sm.V[buf][i][tid];
+#pragma unroll
+          for (int j = 0; j < i; ++j) r -= sm.A[i][j] * x[j];
+          x[i] = r;
+          sm.U[i][tid] = r;
+        }
+      }
+    }
+    __syncthreads();
+
+    // ---- phase 3: D = U - W S_0   (warp w -> columns [8w, 8w+8))
+    {
+      const int n0 = warp * 8;
+      float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+      for (int ks = 0; ks < DK / 8; ++ks) {
+        const int k0 = ks * 8;
+        mma_tf32(c, tf32(sm.W[g][k0 + t]), tf32(sm.W[g + 8][k0 + t]), tf32(sm.W[g][k0 + t + 4]),
+                 tf32(sm.W[g + 8][k0 + t + 4]), tf32(sm.S[k0 + t][n0 + g]), tf32(sm.S[k0 + t + 4][n0 + g]));
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = g + (e >> 1) * 8, j = n0 + 2 * t + (e & 1);
+        sm.D[i][j] = sm.U[i][j] - c[e];
+      }
+    }
+    __syncthreads();
+
+    // ---- phase 4a: O = G*(Q S_0) + P D
+    {
+      const int n0 = warp * 8;
+      float c[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) c[e] = qs[e] * __expf(b[g + (e >> 1) * 8]);
+#pragma unroll
+      for (int ks = 0; ks < CK / 8; ++ks) {
+        const int k0 = ks * 8;
+        mma_tf32(c, tf32(sm.P[g][k0 + t]), tf32(sm.P[g + 8][k0 + t]), tf32(sm.P[g][k0 + t + 4]),
+                 tf32(sm.P[g + 8][k0 + t + 4]), tf32(sm.D[k0 + t][n0 + g]), tf32(sm.D[k0 + t + 4][n0 + g]));
+      }
+      const int c0 = s0 + ch * CK;
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        const int tok = c0 + g + hh * 8;
+        if (tok < s1)
+          *reinterpret_cast<float2*>(p.out + ((size_t)tok * p.Hv + h) * 128 + sl * NV + n0 + 2 * t) =
+              make_float2(c[hh * 2], c[hh * 2 + 1]);
+      }
+    }
+    // ---- phase 4b: S <- G_16 S_0 + Kt^T D   (warp w owns state rows [32w, 32w+32))
+    {
+      const float bl = b[CK - 1];
+      const float gall = __expf(bl);
+      float e_lo[2], e_hi[2];          // exp(b_16 - b_j) for the token columns this lane feeds: j = ks*8 + t, +4
+#pragma unroll
+      for (int ks = 0; ks < 2; ++ks) {
+        e_lo[ks] = __expf(bl - b[ks * 8 + t]);
+        e_hi[ks] = __expf(bl - b[ks * 8 + t + 4]);
+      }
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) {
+        const int m0 = warp * 32 + mt * 16;
+#pragma unroll
+        for (int nt = 0; nt < NV / 8; ++nt) {
+          const int n0 = nt * 8;
+          float c[4];
+          c[0] = gall * sm.S[m0 + g][n0 + 2 * t];
+          c[1] = gall * sm.S[m0 + g][n0 + 2 * t + 1];
+          c[2] = gall * sm.S[m0 + g + 8][n0 + 2 * t];
+          c[3] = gall * sm.S[m0 + g + 8][n0 + 2 * t + 1];
+#pragma unroll
+          for (int ks = 0; ks < 2; ++ks) {
+            const int j0 = ks * 8;
+            mma_tf32(c, tf32(K_[j0 + t][m0 + g] * e_lo[ks]), tf32(K_[j0 + t][m0 + g + 8] * e_lo[ks]),
+                     tf32(K_[j0 + t + 4][m0 + g] * e_hi[ks]), tf32(K_[j0 + t + 4][m0 + g + 8] * e_hi[ks]),
+                     tf32(sm.D[j0 + t][n0 + g]), tf32(sm.D[j0 + t + 4][n0 + g]));
+          }
+          // a warp reads and writes only its own 32 rows of S here, and its lanes touch disjoint elements
+          sm.S[m0 + g][n0 + 2 * t] = c[0];
+          sm.S[m0 + g][n0 + 2 * t + 1] = c[1];
+          sm.S[m0 + g + 8][n0 + 2 * t] = c[2];
+          sm.S[m0 + g + 8][n0 + 2 * t + 1] = c[3];
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (p.write_state) {
+    for (int i = tid; i < DK * (NV / 4); i += 128) {
+      const int r = i / (NV / 4), c4 = (i % (NV / 4)) * 4;
+      *reinterpret_cast<float4*>(Sg + (size_t)r * 128 + c4) = *reinterpret_cast<const float4*>(&sm.S[r][c4]);
+    }
+  }
+}
+
+}  // namespace
+
+// Chunked tensor-core scan.  Same arguments as he_gdn_scan minus the journal; state size must be 128.
+HE_API int he_gdn_scan_chunked(const GdnChunkArgs* args, cudaStream_t stream) {
+  if (args->T <= 0 || args->n_seg <= 0) return 0;
+  if (args->C != 2 * args->G * 128 + args->Hv * 128) return -HE_ERR_BAD_ARG;
+  const size_t smem = sizeof(Smem);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gdn_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid(args->n_seg, args->Hv, 128 / NV);
+  gdn_chunk_kernel<<<grid, 128, smem, stream>>>(*args);
+  HE_LAUNCH_CHECK();
+  return 0;
+}
+HE_API int he_gdn_chunk_args_size() { return (int)sizeof(GdnChunkArgs); }

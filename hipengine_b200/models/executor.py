@@ -384,8 +384,12 @@ class HybridExecutor:
                       G, Hv, S)
         o = sc.get("gdn_o", (T, Hv, S), torch.float32)
         gj = journal["gdn"][i] if journal is not None else None
-        K.gdn_scan(conv, decay, beta, self.gdn_state[i], b.seg_start, b.seg_slot, o, G, Hv,
-                   write_state=journal is None, journal=gj)
+        if (journal is None and S == 128 and T >= 64 * b.n_seg and os.environ.get("HE_GDN_CHUNKED", "1") != "0"):
+            # long prefill segments: 16-token chunks on the tensor cores instead of the token-serial recurrence
+            K.gdn_scan_chunked(conv, decay, beta, self.gdn_state[i], b.seg_start, b.seg_slot, o, G, Hv)
+        else:
+            K.gdn_scan(conv, decay, beta, self.gdn_state[i], b.seg_start, b.seg_slot, o, G, Hv,
+                       write_state=journal is None, journal=gj)
         K.gdn_gated_norm(o, z, self.F(i, "ssm_norm.weight").reshape(-1), og, Hv, S, cfg.rms_eps)
         if small:
             self._out_small(og, self.W(i, "ssm_out.weight"), h)

@@ -78,6 +78,12 @@ class _GdnDecodeArgs(C.Structure):
                 ("C", C.c_int), ("G", C.c_int), ("Hv", C.c_int), ("R", C.c_int)]
 
 
+class _GdnChunkArgs(C.Structure):
+    _fields_ = [("qkv", c_vp), ("decay", c_vp), ("beta", c_vp), ("state", c_vp), ("seg_start", c_vp),
+                ("seg_slot", c_vp), ("out", c_vp), ("C", C.c_int), ("G", C.c_int), ("Hv", C.c_int), ("T", C.c_int),
+                ("n_seg", C.c_int), ("write_state", C.c_int)]
+
+
 class _MoeSelArgs(C.Structure):
     _fields_ = [("x", c_vp), ("ldx", c_ll), ("norm_w", c_vp), ("eps", C.c_float), ("ids", c_vp), ("wts", c_vp),
                 ("w1", c_vp), ("w2", c_vp), ("qtype1", C.c_int), ("qtype2", C.c_int),
@@ -98,7 +104,7 @@ def _check_abi() -> None:
     pairs = [("he_gemv_args_size", _GemvArgs), ("he_qkv_args_size", _QkvArgs), ("he_conv_args_size", _ConvArgs),
              ("he_gdn_prep_args_size", _GdnPrepArgs), ("he_gdn_scan_args_size", _GdnScanArgs),
              ("he_attn_dec_args_size", _AttnDecArgs), ("he_moe_sel_args_size", _MoeSelArgs),
-             ("he_gdn_decode_args_size", _GdnDecodeArgs)]
+             ("he_gdn_decode_args_size", _GdnDecodeArgs), ("he_gdn_chunk_args_size", _GdnChunkArgs)]
     for fn, st in pairs:
         got = getattr(L, fn)()
         if got != C.sizeof(st):
@@ -366,6 +372,20 @@ def gdn_scan(qkv: torch.Tensor, decay: torch.Tensor, beta: torch.Tensor, state: 
     p.seg_start, p.seg_slot, p.out, p.journal = seg_start.data_ptr(), seg_slot.data_ptr(), out.data_ptr(), _p(journal)
     p.C, p.G, p.Hv, p.T, p.n_seg, p.write_state = qkv.shape[1], G, Hv, qkv.shape[0], seg_slot.numel(), int(write_state)
     N.check(N.lib().he_gdn_scan(C.byref(p), _stream()), "he_gdn_scan")
+
+
+def gdn_scan_chunked(qkv: torch.Tensor, decay: torch.Tensor, beta: torch.Tensor, state: torch.Tensor,
+                     seg_start: torch.Tensor, seg_slot: torch.Tensor, out: torch.Tensor, G: int, Hv: int,
+                     write_state: bool = True) -> None:
+    """Chunked (16-token, WY form) tensor-core scan for prefill segments; same contract as ``gdn_scan`` without the
+    journal.  Products run in TF32 with fp32 accumulation."""
+    _check_abi()
+    p = _GdnChunkArgs()
+    p.qkv, p.decay, p.beta, p.state = qkv.data_ptr(), decay.data_ptr(), beta.data_ptr(), state.data_ptr()
+    p.seg_start, p.seg_slot, p.out = seg_start.data_ptr(), seg_slot.data_ptr(), out.data_ptr()
+    p.C, p.G, p.Hv, p.T, p.n_seg, p.write_state = qkv.shape[1], G, Hv, qkv.shape[0], seg_slot.numel(), int(write_state)
+    assert qkv.dtype == torch.float32 and qkv.is_contiguous()
+    N.check(N.lib().he_gdn_scan_chunked(C.byref(p), _stream()), "he_gdn_scan_chunked")
 
 
 def gdn_gated_norm(o: torch.Tensor, z: torch.Tensor, w: torch.Tensor, out: torch.Tensor, Hv: int, Dv: int,

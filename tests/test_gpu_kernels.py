@@ -316,3 +316,42 @@ def test_flash_prefill_matches_reference(K, D, H, Hkv, T, pos0):
     A.flash_prefill(q, None, cache, bt, 1, pos0, out, H, Hkv, D, 16, scale, window=48)
     ref = R.causal_gqa_attention(q.float(), kb, vb, qpos, scale, window=48)
     assert torch.allclose(out.float().reshape(T, H, D), ref, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("lens", [[64], [200], [37, 150, 16]], ids=["one_chunked", "ragged_tail", "three_segments"])
+def test_gdn_chunked_scan_matches_reference(lens):
+    """Chunked (WY, TF32 tensor-core) scan against the fp32 recurrence: outputs and final states."""
+    from hipengine_b200.ops import kernels as K
+    from hipengine_b200.ref import ops as R
+    G, Hv, S = 2, 4, 128
+    C = 2 * G * S + Hv * S
+    T = sum(lens)
+    g = torch.Generator().manual_seed(T)
+    q = R.l2norm(torch.randn(T, G, S, generator=g)) * S ** -0.5
+    k = R.l2norm(torch.randn(T, G, S, generator=g))
+    v = torch.randn(T, Hv, S, generator=g) * 0.5
+    decay = torch.rand(T, Hv, generator=g) * 0.5 + 0.5
+    decay[3] = 1e-9                                        # a near-total reset must not produce inf / nan
+    beta = torch.rand(T, Hv, generator=g)
+    state0 = torch.randn(len(lens), Hv, S, S, generator=g) * 0.1
+    qkv = torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)], 1).contiguous()
+    idx = torch.arange(Hv) % G
+    want_o, want_s = [], []
+    t0 = 0
+    for si, n in enumerate(lens):
+        o, s = R.gdn_recurrent(q[t0:t0 + n][:, idx], k[t0:t0 + n][:, idx], v[t0:t0 + n], decay[t0:t0 + n],
+                               beta[t0:t0 + n], state0[si].clone())
+        want_o.append(o)
+        want_s.append(s)
+        t0 += n
+    want_o, want_s = torch.cat(want_o), torch.stack(want_s)
+    seg_start = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device="cuda")
+    seg_slot = torch.arange(len(lens), dtype=torch.int32, device="cuda")
+    state = state0.cuda().clone()
+    out = torch.zeros(T, Hv, S, device="cuda")
+    K.gdn_scan_chunked(qkv.cuda(), decay.cuda(), beta.cuda(), state, seg_start, seg_slot, out, G, Hv)
+    torch.cuda.synchronize()
+    assert torch.isfinite(out).all() and torch.isfinite(state).all()
+    scale_o, scale_s = want_o.abs().max(), want_s.abs().max()
+    assert (out.cpu() - want_o).abs().max() / scale_o < 2e-2
+    assert (state.cpu() - want_s).abs().max() / scale_s < 2e-2
