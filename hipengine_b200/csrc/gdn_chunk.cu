@@ -62,10 +62,10 @@ struct Smem {
   float V[2][CK][LDS_];
   float S[DK][LDS_];       // state slice [k][n]
   float W[CK][LDK];
-  float U[CK][LDS_];
   float D[CK][LDS_];       // delta rows
   float A[CK][LDA];
   float P[CK][LDA];
+  float Tm[CK][LDA];       // (I + A)^-1
   float b[2][CK];          // inclusive log-decay sums of the chunk
   float bt[2][CK];         // beta
 };
@@ -106,123 +106,190 @@ __global__ void __launch_bounds__(128) gdn_chunk_kernel(const GdnChunkArgs p) {
       cp_async16(&sm.V[buf][tt][d4], p.qkv + (size_t)(ok ? tok : s0) * p.C + v_off + d4, ok ? 16 : 0);
     }
     cp_async_commit();
+  };
+  // The per-token decay / beta of a chunk are loaded one chunk ahead into registers (lanes 0..15 of warp 0) and
+  // turned into the inclusive log-decay prefix at the end of the previous iteration, so that their global-load
+  // latency is off the critical path.  Tokens past the segment end act as identity steps (decay 1, beta 0).
+  float nd = 1.f, nbeta = 0.f;
+  auto load_scalars = [&](int chunk) {
     if (tid < CK) {
-      // inclusive prefix of log(decay) over the chunk; tokens past the segment end act as identity steps
-      const int tok = c0 + tid;
+      const int tok = s0 + chunk * CK + tid;
       const bool ok = tok < s1;
-      float lg = ok ? __logf(fmaxf(p.decay[(size_t)tok * p.Hv + h], 1e-37f)) : 0.f;
+      nd = ok ? p.decay[(size_t)tok * p.Hv + h] : 1.f;
+      nbeta = ok ? p.beta[(size_t)tok * p.Hv + h] : 0.f;
+    }
+  };
+  auto store_scalars = [&](int buf) {
+    if (tid < CK) {
+      float lg = __logf(fmaxf(nd, 1e-37f));
 #pragma unroll
       for (int o = 1; o < CK; o <<= 1) {
         const float v = __shfl_up_sync(0x0000ffffu, lg, o, CK);
         if (tid >= o) lg += v;
       }
       sm.b[buf][tid] = lg;
-      sm.bt[buf][tid] = ok ? p.beta[(size_t)tok * p.Hv + h] : 0.f;
+      sm.bt[buf][tid] = nbeta;
     }
   };
 
-  if (n_chunks > 0) prefetch(0, 0);
-  float qs[4];
+  if (n_chunks > 0) {
+    prefetch(0, 0);
+    load_scalars(0);
+    store_scalars(0);
+  }
+  float qs[2][4];                          // warps 2,3: Q S_0 for their two n-tiles
   for (int ch = 0; ch < n_chunks; ++ch) {
     const int buf = ch & 1;
     cp_async_wait_all();
     __syncthreads();                       // chunk data + previous state update visible to everyone
-    if (ch + 1 < n_chunks) prefetch(ch + 1, buf ^ 1);
+    if (ch + 1 < n_chunks) {
+      prefetch(ch + 1, buf ^ 1);
+      load_scalars(ch + 1);
+    }
     float (*K_)[LDK] = sm.K[buf];
     float (*Q_)[LDK] = sm.Q[buf];
     const float* b = sm.b[buf];
     const float* bt = sm.bt[buf];
 
-    // ---- phase 1: K K^T (warps 0,1), Q K^T (warps 2,3), and every warp's n-tile of Q S_0
-    {
-      const int nt = warp & 1;
-      float (*X_)[LDK] = warp < 2 ? K_ : Q_;
-      float c[4] = {0.f, 0.f, 0.f, 0.f};
+    // ---- phase 1: warps 0,1: A = tril(beta G-ratio K K^T, -1), then warp 0 inverts (I + A);
+    //               warps 2,3: P = tril(G-ratio Q K^T) and Q S_0 for two n-tiles each (shared Q fragments)
+    if (warp < 2) {
+      const int nt = warp;
+      float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 4
-      for (int ks = 0; ks < DK / 8; ++ks) {
-        const int k0 = ks * 8;
-        mma_tf32(c, tf32(X_[g][k0 + t]), tf32(X_[g + 8][k0 + t]), tf32(X_[g][k0 + t + 4]), tf32(X_[g + 8][k0 + t + 4]),
+      for (int ks = 0; ks < DK / 8; ks += 2) {
+        const int k0 = ks * 8, k1 = k0 + 8;
+        mma_tf32(c0, tf32(K_[g][k0 + t]), tf32(K_[g + 8][k0 + t]), tf32(K_[g][k0 + t + 4]), tf32(K_[g + 8][k0 + t + 4]),
                  tf32(K_[nt * 8 + g][k0 + t]), tf32(K_[nt * 8 + g][k0 + t + 4]));
+        mma_tf32(c1, tf32(K_[g][k1 + t]), tf32(K_[g + 8][k1 + t]), tf32(K_[g][k1 + t + 4]), tf32(K_[g + 8][k1 + t + 4]),
+                 tf32(K_[nt * 8 + g][k1 + t]), tf32(K_[nt * 8 + g][k1 + t + 4]));
       }
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int i = g + (e >> 1) * 8, j = nt * 8 + 2 * t + (e & 1);
-        const float ratio = __expf(b[i] - b[j]);
-        if (warp < 2) sm.A[i][j] = j < i ? bt[i] * ratio * c[e] : 0.f;
-        else sm.P[i][j] = j <= i ? ratio * c[e] : 0.f;
+        sm.A[i][j] = j < i ? bt[i] * __expf(b[i] - b[j]) * (c0[e] + c1[e]) : 0.f;
       }
-      qs[0] = qs[1] = qs[2] = qs[3] = 0.f;
-      const int n0 = warp * 8;
-#pragma unroll 4
-      for (int ks = 0; ks < DK / 8; ++ks) {
-        const int k0 = ks * 8;
-        mma_tf32(qs, tf32(Q_[g][k0 + t]), tf32(Q_[g + 8][k0 + t]), tf32(Q_[g][k0 + t + 4]), tf32(Q_[g + 8][k0 + t + 4]),
-                 tf32(sm.S[k0 + t][n0 + g]), tf32(sm.S[k0 + t + 4][n0 + g]));
-      }
-    }
-    __syncthreads();
-
-    // ---- phase 2: (I + A) [U | W] = [beta V | beta G K], one column per thread (W: 128 columns, U: 32)
-    {
-      float x[CK];
-#pragma unroll
-      for (int i = 0; i < CK; ++i) {
-        float r = bt[i] * __expf(b[i]) * K_[i][tid];
-#pragma unroll
-        for (int j = 0; j < i; ++j) r -= sm.A[i][j] * x[j];
-        x[i] = r;
-        sm.W[i][tid] = r;
-      }
-      if (tid < NV) {
+      asm volatile("bar.sync 1, 64;" ::: "memory");       // A complete (warps 0 and 1 only)
+      if (warp == 0 && lane < CK) {
+        // column `lane` of Tm = (I + A)^-1 by forward substitution; stored in P's sibling array sm.Tm
+        float x[CK];
 #pragma unroll
         for (int i = 0; i < CK; ++i) {
-          float r = bt[i] * sm.V[buf][i][tid];
+          float r = i == lane ? 1.f : 0.f;
 #pragma unroll
-          for (int j = 0; j < i; ++j) r -= sm.A[i][j] * x[j];
+          for (int m = 0; m < i; ++m) r -= sm.A[i][m] * x[m];
           x[i] = r;
-          sm.U[i][tid] = r;
+          sm.Tm[i][lane] = r;
         }
+      }
+    } else {
+      const int nt = warp - 2;
+      float c0[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) qs[0][e] = qs[1][e] = 0.f;
+      const int n0 = nt * 16;
+#pragma unroll 4
+      for (int ks = 0; ks < DK / 8; ++ks) {
+        const int k0 = ks * 8;
+        const uint32_t a0 = tf32(Q_[g][k0 + t]), a1 = tf32(Q_[g + 8][k0 + t]), a2 = tf32(Q_[g][k0 + t + 4]),
+                       a3 = tf32(Q_[g + 8][k0 + t + 4]);
+        mma_tf32(c0, a0, a1, a2, a3, tf32(K_[nt * 8 + g][k0 + t]), tf32(K_[nt * 8 + g][k0 + t + 4]));
+        mma_tf32(qs[0], a0, a1, a2, a3, tf32(sm.S[k0 + t][n0 + g]), tf32(sm.S[k0 + t + 4][n0 + g]));
+        mma_tf32(qs[1], a0, a1, a2, a3, tf32(sm.S[k0 + t][n0 + 8 + g]), tf32(sm.S[k0 + t + 4][n0 + 8 + g]));
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = g + (e >> 1) * 8, j = nt * 8 + 2 * t + (e & 1);
+        sm.P[i][j] = j <= i ? __expf(b[i] - b[j]) * c0[e] : 0.f;
       }
     }
     __syncthreads();
 
-    // ---- phase 3: D = U - W S_0   (warp w -> columns [8w, 8w+8))
+    // ---- phase 2: [U | W] = Tm [beta V | beta G K]: warp w -> W n-tiles 4w..4w+3 (to shared) and U n-tile w (regs)
+    float u[4] = {0.f, 0.f, 0.f, 0.f};
+    {
+      uint32_t ta[2][4];
+#pragma unroll
+      for (int ks = 0; ks < 2; ++ks) {
+        ta[ks][0] = tf32(sm.Tm[g][ks * 8 + t]);
+        ta[ks][1] = tf32(sm.Tm[g + 8][ks * 8 + t]);
+        ta[ks][2] = tf32(sm.Tm[g][ks * 8 + t + 4]);
+        ta[ks][3] = tf32(sm.Tm[g + 8][ks * 8 + t + 4]);
+      }
+      float sc_lo[2], sc_hi[2], bt_lo[2], bt_hi[2];     // row scales of the right-hand sides for tokens ks*8+t, +4
+#pragma unroll
+      for (int ks = 0; ks < 2; ++ks) {
+        bt_lo[ks] = bt[ks * 8 + t];
+        bt_hi[ks] = bt[ks * 8 + t + 4];
+        sc_lo[ks] = bt_lo[ks] * __expf(b[ks * 8 + t]);
+        sc_hi[ks] = bt_hi[ks] * __expf(b[ks * 8 + t + 4]);
+      }
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        const int n0 = (warp * 4 + q4) * 8;
+        float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks)
+          mma_tf32(c, ta[ks][0], ta[ks][1], ta[ks][2], ta[ks][3], tf32(K_[ks * 8 + t][n0 + g] * sc_lo[ks]),
+                   tf32(K_[ks * 8 + t + 4][n0 + g] * sc_hi[ks]));
+        *reinterpret_cast<float2*>(&sm.W[g][n0 + 2 * t]) = make_float2(c[0], c[1]);
+        *reinterpret_cast<float2*>(&sm.W[g + 8][n0 + 2 * t]) = make_float2(c[2], c[3]);
+      }
+      const int n0 = warp * 8;
+#pragma unroll
+      for (int ks = 0; ks < 2; ++ks)
+        mma_tf32(u, ta[ks][0], ta[ks][1], ta[ks][2], ta[ks][3], tf32(sm.V[buf][ks * 8 + t][n0 + g] * bt_lo[ks]),
+                 tf32(sm.V[buf][ks * 8 + t + 4][n0 + g] * bt_hi[ks]));
+    }
+    __syncthreads();
+
+    // ---- phase 3: D = U - W S_0   (warp w -> columns [8w, 8w+8)), two accumulation chains
     {
       const int n0 = warp * 8;
-      float c[4] = {0.f, 0.f, 0.f, 0.f};
+      float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 4
-      for (int ks = 0; ks < DK / 8; ++ks) {
-        const int k0 = ks * 8;
-        mma_tf32(c, tf32(sm.W[g][k0 + t]), tf32(sm.W[g + 8][k0 + t]), tf32(sm.W[g][k0 + t + 4]),
+      for (int ks = 0; ks < DK / 8; ks += 2) {
+        const int k0 = ks * 8, k1 = k0 + 8;
+        mma_tf32(c0, tf32(sm.W[g][k0 + t]), tf32(sm.W[g + 8][k0 + t]), tf32(sm.W[g][k0 + t + 4]),
                  tf32(sm.W[g + 8][k0 + t + 4]), tf32(sm.S[k0 + t][n0 + g]), tf32(sm.S[k0 + t + 4][n0 + g]));
+        mma_tf32(c1, tf32(sm.W[g][k1 + t]), tf32(sm.W[g + 8][k1 + t]), tf32(sm.W[g][k1 + t + 4]),
+                 tf32(sm.W[g + 8][k1 + t + 4]), tf32(sm.S[k1 + t][n0 + g]), tf32(sm.S[k1 + t + 4][n0 + g]));
       }
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int i = g + (e >> 1) * 8, j = n0 + 2 * t + (e & 1);
-        sm.D[i][j] = sm.U[i][j] - c[e];
+        sm.D[i][j] = u[e] - (c0[e] + c1[e]);
       }
     }
     __syncthreads();
 
-    // ---- phase 4a: O = G*(Q S_0) + P D
-    {
-      const int n0 = warp * 8;
-      float c[4];
+    // ---- phase 4a (warps 2,3): O = G*(Q S_0) + P D for their two n-tiles
+    if (warp >= 2) {
+      const int c0t = s0 + ch * CK;
+      uint32_t pa[2][4];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) c[e] = qs[e] * __expf(b[g + (e >> 1) * 8]);
-#pragma unroll
-      for (int ks = 0; ks < CK / 8; ++ks) {
-        const int k0 = ks * 8;
-        mma_tf32(c, tf32(sm.P[g][k0 + t]), tf32(sm.P[g + 8][k0 + t]), tf32(sm.P[g][k0 + t + 4]),
-                 tf32(sm.P[g + 8][k0 + t + 4]), tf32(sm.D[k0 + t][n0 + g]), tf32(sm.D[k0 + t + 4][n0 + g]));
+      for (int ks = 0; ks < 2; ++ks) {
+        pa[ks][0] = tf32(sm.P[g][ks * 8 + t]);
+        pa[ks][1] = tf32(sm.P[g + 8][ks * 8 + t]);
+        pa[ks][2] = tf32(sm.P[g][ks * 8 + t + 4]);
+        pa[ks][3] = tf32(sm.P[g + 8][ks * 8 + t + 4]);
       }
-      const int c0 = s0 + ch * CK;
+      const float g_lo = __expf(b[g]), g_hi = __expf(b[g + 8]);
 #pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
-        const int tok = c0 + g + hh * 8;
-        if (tok < s1)
-          *reinterpret_cast<float2*>(p.out + ((size_t)tok * p.Hv + h) * 128 + sl * NV + n0 + 2 * t) =
-              make_float2(c[hh * 2], c[hh * 2 + 1]);
+      for (int q2 = 0; q2 < 2; ++q2) {
+        const int n0 = (warp - 2) * 16 + q2 * 8;
+        float c[4] = {qs[q2][0] * g_lo, qs[q2][1] * g_lo, qs[q2][2] * g_hi, qs[q2][3] * g_hi};
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks)
+          mma_tf32(c, pa[ks][0], pa[ks][1], pa[ks][2], pa[ks][3], tf32(sm.D[ks * 8 + t][n0 + g]),
+                   tf32(sm.D[ks * 8 + t + 4][n0 + g]));
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          const int tok = c0t + g + hh * 8;
+          if (tok < s1)
+            *reinterpret_cast<float2*>(p.out + ((size_t)tok * p.Hv + h) * 128 + sl * NV + n0 + 2 * t) =
+                make_float2(c[hh * 2], c[hh * 2 + 1]);
+        }
       }
     }
     // ---- phase 4b: S <- G_16 S_0 + Kt^T D   (warp w owns state rows [32w, 32w+32))
@@ -238,29 +305,32 @@ __global__ void __launch_bounds__(128) gdn_chunk_kernel(const GdnChunkArgs p) {
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt) {
         const int m0 = warp * 32 + mt * 16;
+        uint32_t ka[2][4];
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks) {
+          const int j0 = ks * 8;
+          ka[ks][0] = tf32(K_[j0 + t][m0 + g] * e_lo[ks]);
+          ka[ks][1] = tf32(K_[j0 + t][m0 + g + 8] * e_lo[ks]);
+          ka[ks][2] = tf32(K_[j0 + t + 4][m0 + g] * e_hi[ks]);
+          ka[ks][3] = tf32(K_[j0 + t + 4][m0 + g + 8] * e_hi[ks]);
+        }
 #pragma unroll
         for (int nt = 0; nt < NV / 8; ++nt) {
           const int n0 = nt * 8;
-          float c[4];
-          c[0] = gall * sm.S[m0 + g][n0 + 2 * t];
-          c[1] = gall * sm.S[m0 + g][n0 + 2 * t + 1];
-          c[2] = gall * sm.S[m0 + g + 8][n0 + 2 * t];
-          c[3] = gall * sm.S[m0 + g + 8][n0 + 2 * t + 1];
+          const float2 s_lo = *reinterpret_cast<const float2*>(&sm.S[m0 + g][n0 + 2 * t]);
+          const float2 s_hi = *reinterpret_cast<const float2*>(&sm.S[m0 + g + 8][n0 + 2 * t]);
+          float c[4] = {gall * s_lo.x, gall * s_lo.y, gall * s_hi.x, gall * s_hi.y};
 #pragma unroll
-          for (int ks = 0; ks < 2; ++ks) {
-            const int j0 = ks * 8;
-            mma_tf32(c, tf32(K_[j0 + t][m0 + g] * e_lo[ks]), tf32(K_[j0 + t][m0 + g + 8] * e_lo[ks]),
-                     tf32(K_[j0 + t + 4][m0 + g] * e_hi[ks]), tf32(K_[j0 + t + 4][m0 + g + 8] * e_hi[ks]),
-                     tf32(sm.D[j0 + t][n0 + g]), tf32(sm.D[j0 + t + 4][n0 + g]));
-          }
+          for (int ks = 0; ks < 2; ++ks)
+            mma_tf32(c, ka[ks][0], ka[ks][1], ka[ks][2], ka[ks][3], tf32(sm.D[ks * 8 + t][n0 + g]),
+                     tf32(sm.D[ks * 8 + t + 4][n0 + g]));
           // a warp reads and writes only its own 32 rows of S here, and its lanes touch disjoint elements
-          sm.S[m0 + g][n0 + 2 * t] = c[0];
-          sm.S[m0 + g][n0 + 2 * t + 1] = c[1];
-          sm.S[m0 + g + 8][n0 + 2 * t] = c[2];
-          sm.S[m0 + g + 8][n0 + 2 * t + 1] = c[3];
+          *reinterpret_cast<float2*>(&sm.S[m0 + g][n0 + 2 * t]) = make_float2(c[0], c[1]);
+          *reinterpret_cast<float2*>(&sm.S[m0 + g + 8][n0 + 2 * t]) = make_float2(c[2], c[3]);
         }
       }
     }
+    if (ch + 1 < n_chunks) store_scalars(buf ^ 1);
   }
   __syncthreads();
   if (p.write_state) {
