@@ -193,7 +193,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           } else {
             float* dst = reinterpret_cast<float*>(g.C) + (size_t)row * g.ldc + col0 +
                          (g.epi == 4 ? (size_t)ks_e * (size_t)g.split_stride : (size_t)0);
-            if (g.epi == 1 || g.epi == 4) {
+            const bool vec = ncols == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
+            if ((g.epi == 1 || g.epi == 4) && vec) {
+#pragma unroll
+              for (int v = 0; v < 8; ++v)
+                reinterpret_cast<float4*>(dst)[v] =
+                    make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]), __uint_as_float(r[4 * v + 2]),
+                                __uint_as_float(r[4 * v + 3]));
+            } else if (g.epi == 2 && vec) {
+#pragma unroll
+              for (int v = 0; v < 8; ++v) {
+                float4 o = reinterpret_cast<float4*>(dst)[v];
+                o.x += __uint_as_float(r[4 * v]); o.y += __uint_as_float(r[4 * v + 1]);
+                o.z += __uint_as_float(r[4 * v + 2]); o.w += __uint_as_float(r[4 * v + 3]);
+                reinterpret_cast<float4*>(dst)[v] = o;
+              }
+            } else if (g.epi == 1 || g.epi == 4) {
               for (int e = 0; e < ncols; ++e) dst[e] = __uint_as_float(r[e]);
             } else if (g.epi == 2) {
               for (int e = 0; e < ncols; ++e) dst[e] += __uint_as_float(r[e]);

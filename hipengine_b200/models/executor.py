@@ -265,6 +265,11 @@ class HybridExecutor:
             from ..ops import gemm as GM
             GM.gemm_bf16_splitk_det(x, GM.bf16_weight(w, self.scratch, self.shadow), h, self.scratch, add=True)
             return
+        if self.gemm_impl == "tcgen05" and h.is_contiguous():
+            # accumulate straight into the fp32 residual in the GEMM epilogue (one CTA per tile: plain +=)
+            from ..ops import gemm as GM
+            GM.gemm_quant(x, w, h, self.scratch, epi=2, shadow=self.shadow)
+            return
         y = self._gemm(x, w, self.scratch.get("y_bf", (T, w.n_rows), torch.bfloat16), tag=tag)
         K.resid_add_bf16(h, y)
 
