@@ -20,11 +20,16 @@ using namespace he;
 namespace {
 
 constexpr int CK = 16;          // tokens per chunk
+constexpr int NST = 2;          // chunk buffers: the next chunk's rows are in flight while one computes (a third stage measured no gain)
 constexpr int DK = 128;         // state rows (key dim)
-constexpr int NV = 32;          // state columns per CTA
-constexpr int LDK = DK + 4;     // sK / sQ / sW row stride (floats): conflict-free A-fragment reads
-constexpr int LDS_ = NV + 8;    // sS / sVn / sU row stride: conflict-free B-fragment reads
+constexpr int LDK = DK + 16;    // row stride (floats) of K / Q / W / transposed S: conflict-free 128-bit fragment reads
 constexpr int LDA = CK + 1;
+
+// Fragment convention for the 128-deep products (K K^T, Q K^T, Q S_0, W S_0): the k index is relabelled so that the
+// four k values a lane feeds into two consecutive m16n8k8 steps are contiguous in memory (k0 + 4t .. k0 + 4t + 3,
+// one 128-bit load); A and B use the same relabelling, so the product is unchanged.  Operands go in as raw fp32 bit
+// patterns (the tensor core drops the low mantissa bits).
+__device__ __forceinline__ uint4 ld4(const float* p) { return *reinterpret_cast<const uint4*>(p); }
 
 struct GdnChunkArgs {
   const float* qkv;       // [T][C] prepared conv output: q | k | v (q, k normalised)
@@ -55,25 +60,32 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src, int src_b
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_1() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
 
+template <int NV>
 struct Smem {
-  float K[2][CK][LDK];
-  float Q[2][CK][LDK];
-  float V[2][CK][LDS_];
-  float S[DK][LDS_];       // state slice [k][n]
+  static constexpr int LDS_ = NV + 8;   // row stride of S / V / D: conflict-free B-fragment reads
+  float K[NST][CK][LDK];
+  float Q[NST][CK][LDK];
+  float V[NST][CK][LDS_];
+  float St[NV][LDK];       // state slice, transposed: St[n][k]
   float W[CK][LDK];
   float D[CK][LDS_];       // delta rows
   float A[CK][LDA];
   float P[CK][LDA];
   float Tm[CK][LDA];       // (I + A)^-1
-  float b[2][CK];          // inclusive log-decay sums of the chunk
-  float bt[2][CK];         // beta
+  float b[NST][CK];        // inclusive log-decay sums of the chunk
+  float bt[NST][CK];       // beta
 };
 
-// grid (n_seg, Hv, DV/NV), block 128
+// grid (n_seg, Hv, DV/NV), block 128.  NV = 32 or 16 state columns per CTA: the narrower slice doubles the CTAs
+// (and repeats the K K^T / Q K^T / inverse work per slice), which pays when one sequence is all there is.
+template <int NV>
 __global__ void __launch_bounds__(128) gdn_chunk_kernel(const GdnChunkArgs p) {
+  constexpr int NT = NV / 8;              // n-tiles of the state slice
+  constexpr int QT = NT / 2;              // n-tiles of Q S_0 per warp (warps 2 and 3)
   extern __shared__ __align__(16) uint8_t smem_raw[];
-  Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
+  Smem<NV>& sm = *reinterpret_cast<Smem<NV>*>(smem_raw);
   const int sg = blockIdx.x, h = blockIdx.y, sl = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
@@ -86,7 +98,8 @@ __global__ void __launch_bounds__(128) gdn_chunk_kernel(const GdnChunkArgs p) {
 
   for (int i = tid; i < DK * (NV / 4); i += 128) {
     const int r = i / (NV / 4), c4 = (i % (NV / 4)) * 4;
-    *reinterpret_cast<float4*>(&sm.S[r][c4]) = *reinterpret_cast<const float4*>(Sg + (size_t)r * 128 + c4);
+    const float4 v = *reinterpret_cast<const float4*>(Sg + (size_t)r * 128 + c4);
+    sm.St[c4][r] = v.x; sm.St[c4 + 1][r] = v.y; sm.St[c4 + 2][r] = v.z; sm.St[c4 + 3][r] = v.w;
   }
 
   auto prefetch = [&](int chunk, int buf) {
@@ -132,20 +145,33 @@ __global__ void __launch_bounds__(128) gdn_chunk_kernel(const GdnChunkArgs p) {
     }
   };
 
+  // every warp keeps its 32 rows of the state slice in registers, in accumulator-fragment layout, for the whole
+  // segment; shared memory only holds the copy the other warps read as a B operand
+  float sreg[2][NT][4];
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const int m0 = warp * 32 + mt * 16, n0 = nt * 8;
+      sreg[mt][nt][0] = Sg[(size_t)(m0 + g) * 128 + n0 + 2 * t];
+      sreg[mt][nt][1] = Sg[(size_t)(m0 + g) * 128 + n0 + 2 * t + 1];
+      sreg[mt][nt][2] = Sg[(size_t)(m0 + g + 8) * 128 + n0 + 2 * t];
+      sreg[mt][nt][3] = Sg[(size_t)(m0 + g + 8) * 128 + n0 + 2 * t + 1];
+    }
   if (n_chunks > 0) {
     prefetch(0, 0);
     load_scalars(0);
     store_scalars(0);
   }
-  float qs[2][4];                          // warps 2,3: Q S_0 for their two n-tiles
+  if (NST > 2 && n_chunks > 1) prefetch(1, 1);
+  float qs[QT][4];                         // warps 2,3: Q S_0 for their n-tiles
   for (int ch = 0; ch < n_chunks; ++ch) {
-    const int buf = ch & 1;
-    cp_async_wait_all();
+    const int buf = ch % NST;
+    if (NST > 2 && ch + 1 < n_chunks) cp_async_wait_1();   // all but the newest group (chunk ch+1) has landed
+    else cp_async_wait_all();
     __syncthreads();                       // chunk data + previous state update visible to everyone
-    if (ch + 1 < n_chunks) {
-      prefetch(ch + 1, buf ^ 1);
-      load_scalars(ch + 1);
-    }
+    if (ch + NST - 1 < n_chunks) prefetch(ch + NST - 1, (ch + NST - 1) % NST);
+    if (ch + 1 < n_chunks) load_scalars(ch + 1);
     float (*K_)[LDK] = sm.K[buf];
     float (*Q_)[LDK] = sm.Q[buf];
     const float* b = sm.b[buf];
@@ -155,14 +181,24 @@ __global__ void __launch_bounds__(128) gdn_chunk_kernel(const GdnChunkArgs p) {
     //               warps 2,3: P = tril(G-ratio Q K^T) and Q S_0 for two n-tiles each (shared Q fragments)
     if (warp < 2) {
       const int nt = warp;
-      float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
-      for (int ks = 0; ks < DK / 8; ks += 2) {
-        const int k0 = ks * 8, k1 = k0 + 8;
-        mma_tf32(c0, tf32(K_[g][k0 + t]), tf32(K_[g + 8][k0 + t]), tf32(K_[g][k0 + t + 4]), tf32(K_[g + 8][k0 + t + 4]),
-                 tf32(K_[nt * 8 + g][k0 + t]), tf32(K_[nt * 8 + g][k0 + t + 4]));
-        mma_tf32(c1, tf32(K_[g][k1 + t]), tf32(K_[g + 8][k1 + t]), tf32(K_[g][k1 + t + 4]), tf32(K_[g + 8][k1 + t + 4]),
-                 tf32(K_[nt * 8 + g][k1 + t]), tf32(K_[nt * 8 + g][k1 + t + 4]));
+      // legacy mma.sync has a long result latency on this part: four independent accumulation chains per tile
+      float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f}, c2[4] = {0.f, 0.f, 0.f, 0.f},
+            c3[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int kk = 0; kk < DK; kk += 32) {
+        const uint4 alo = ld4(&K_[g][kk + 4 * t]), ahi = ld4(&K_[g + 8][kk + 4 * t]);
+        const uint4 bb = ld4(&K_[nt * 8 + g][kk + 4 * t]);
+        const uint4 alo2 = ld4(&K_[g][kk + 16 + 4 * t]), ahi2 = ld4(&K_[g + 8][kk + 16 + 4 * t]);
+        const uint4 bb2 = ld4(&K_[nt * 8 + g][kk + 16 + 4 * t]);
+        mma_tf32(c0, alo.x, ahi.x, alo.y, ahi.y, bb.x, bb.y);
+        mma_tf32(c1, alo.z, ahi.z, alo.w, ahi.w, bb.z, bb.w);
+        mma_tf32(c2, alo2.x, ahi2.x, alo2.y, ahi2.y, bb2.x, bb2.y);
+        mma_tf32(c3, alo2.z, ahi2.z, alo2.w, ahi2.w, bb2.z, bb2.w);
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        c0[e] += c2[e];
+        c1[e] += c3[e];
       }
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
@@ -186,17 +222,42 @@ __global__ void __launch_bounds__(128) gdn_chunk_kernel(const GdnChunkArgs p) {
       const int nt = warp - 2;
       float c0[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int e = 0; e < 4; ++e) qs[0][e] = qs[1][e] = 0.f;
-      const int n0 = nt * 16;
-#pragma unroll 4
-      for (int ks = 0; ks < DK / 8; ++ks) {
-        const int k0 = ks * 8;
-        const uint32_t a0 = tf32(Q_[g][k0 + t]), a1 = tf32(Q_[g + 8][k0 + t]), a2 = tf32(Q_[g][k0 + t + 4]),
-                       a3 = tf32(Q_[g + 8][k0 + t + 4]);
-        mma_tf32(c0, a0, a1, a2, a3, tf32(K_[nt * 8 + g][k0 + t]), tf32(K_[nt * 8 + g][k0 + t + 4]));
-        mma_tf32(qs[0], a0, a1, a2, a3, tf32(sm.S[k0 + t][n0 + g]), tf32(sm.S[k0 + t + 4][n0 + g]));
-        mma_tf32(qs[1], a0, a1, a2, a3, tf32(sm.S[k0 + t][n0 + 8 + g]), tf32(sm.S[k0 + t + 4][n0 + 8 + g]));
+      for (int q2 = 0; q2 < QT; ++q2)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) qs[q2][e] = 0.f;
+      const int n0 = nt * QT * 8;
+      float c1[4] = {0.f, 0.f, 0.f, 0.f};
+      float qs2[QT][4], qs3[QT][4], qs4[QT][4];     // extra chains of Q S_0, folded into qs[] after the loop
+#pragma unroll
+      for (int q2 = 0; q2 < QT; ++q2)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) qs2[q2][e] = qs3[q2][e] = qs4[q2][e] = 0.f;
+#pragma unroll
+      for (int kk = 0; kk < DK; kk += 32) {
+        const uint4 alo = ld4(&Q_[g][kk + 4 * t]), ahi = ld4(&Q_[g + 8][kk + 4 * t]);
+        const uint4 bk = ld4(&K_[nt * 8 + g][kk + 4 * t]);
+        const uint4 alo2 = ld4(&Q_[g][kk + 16 + 4 * t]), ahi2 = ld4(&Q_[g + 8][kk + 16 + 4 * t]);
+        const uint4 bk2 = ld4(&K_[nt * 8 + g][kk + 16 + 4 * t]);
+        mma_tf32(c0, alo.x, ahi.x, alo.y, ahi.y, bk.x, bk.y);
+        mma_tf32(c1, alo.z, ahi.z, alo.w, ahi.w, bk.z, bk.w);
+        mma_tf32(c0, alo2.x, ahi2.x, alo2.y, ahi2.y, bk2.x, bk2.y);
+        mma_tf32(c1, alo2.z, ahi2.z, alo2.w, ahi2.w, bk2.z, bk2.w);
+#pragma unroll
+        for (int q2 = 0; q2 < QT; ++q2) {
+          const uint4 bs = ld4(&sm.St[n0 + q2 * 8 + g][kk + 4 * t]);
+          const uint4 bs2 = ld4(&sm.St[n0 + q2 * 8 + g][kk + 16 + 4 * t]);
+          mma_tf32(qs[q2], alo.x, ahi.x, alo.y, ahi.y, bs.x, bs.y);
+          mma_tf32(qs2[q2], alo.z, ahi.z, alo.w, ahi.w, bs.z, bs.w);
+          mma_tf32(qs3[q2], alo2.x, ahi2.x, alo2.y, ahi2.y, bs2.x, bs2.y);
+          mma_tf32(qs4[q2], alo2.z, ahi2.z, alo2.w, ahi2.w, bs2.z, bs2.w);
+        }
       }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) c0[e] += c1[e];
+#pragma unroll
+      for (int q2 = 0; q2 < QT; ++q2)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) qs[q2][e] += qs2[q2][e] + (qs3[q2][e] + qs4[q2][e]);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int i = g + (e >> 1) * 8, j = nt * 8 + 2 * t + (e & 1);
@@ -235,25 +296,36 @@ __global__ void __launch_bounds__(128) gdn_chunk_kernel(const GdnChunkArgs p) {
         *reinterpret_cast<float2*>(&sm.W[g][n0 + 2 * t]) = make_float2(c[0], c[1]);
         *reinterpret_cast<float2*>(&sm.W[g + 8][n0 + 2 * t]) = make_float2(c[2], c[3]);
       }
-      const int n0 = warp * 8;
+      if (warp < NT) {
+        const int n0 = warp * 8;
 #pragma unroll
-      for (int ks = 0; ks < 2; ++ks)
-        mma_tf32(u, ta[ks][0], ta[ks][1], ta[ks][2], ta[ks][3], tf32(sm.V[buf][ks * 8 + t][n0 + g] * bt_lo[ks]),
-                 tf32(sm.V[buf][ks * 8 + t + 4][n0 + g] * bt_hi[ks]));
+        for (int ks = 0; ks < 2; ++ks)
+          mma_tf32(u, ta[ks][0], ta[ks][1], ta[ks][2], ta[ks][3], tf32(sm.V[buf][ks * 8 + t][n0 + g] * bt_lo[ks]),
+                   tf32(sm.V[buf][ks * 8 + t + 4][n0 + g] * bt_hi[ks]));
+      }
     }
     __syncthreads();
 
     // ---- phase 3: D = U - W S_0   (warp w -> columns [8w, 8w+8)), two accumulation chains
-    {
+    if (warp < NT) {
       const int n0 = warp * 8;
       float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
-      for (int ks = 0; ks < DK / 8; ks += 2) {
-        const int k0 = ks * 8, k1 = k0 + 8;
-        mma_tf32(c0, tf32(sm.W[g][k0 + t]), tf32(sm.W[g + 8][k0 + t]), tf32(sm.W[g][k0 + t + 4]),
-                 tf32(sm.W[g + 8][k0 + t + 4]), tf32(sm.S[k0 + t][n0 + g]), tf32(sm.S[k0 + t + 4][n0 + g]));
-        mma_tf32(c1, tf32(sm.W[g][k1 + t]), tf32(sm.W[g + 8][k1 + t]), tf32(sm.W[g][k1 + t + 4]),
-                 tf32(sm.W[g + 8][k1 + t + 4]), tf32(sm.S[k1 + t][n0 + g]), tf32(sm.S[k1 + t + 4][n0 + g]));
+      float c2[4] = {0.f, 0.f, 0.f, 0.f}, c3[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int kk = 0; kk < DK; kk += 32) {
+        const uint4 alo = ld4(&sm.W[g][kk + 4 * t]), ahi = ld4(&sm.W[g + 8][kk + 4 * t]);
+        const uint4 bs = ld4(&sm.St[n0 + g][kk + 4 * t]);
+        const uint4 alo2 = ld4(&sm.W[g][kk + 16 + 4 * t]), ahi2 = ld4(&sm.W[g + 8][kk + 16 + 4 * t]);
+        const uint4 bs2 = ld4(&sm.St[n0 + g][kk + 16 + 4 * t]);
+        mma_tf32(c0, alo.x, ahi.x, alo.y, ahi.y, bs.x, bs.y);
+        mma_tf32(c1, alo.z, ahi.z, alo.w, ahi.w, bs.z, bs.w);
+        mma_tf32(c2, alo2.x, ahi2.x, alo2.y, ahi2.y, bs2.x, bs2.y);
+        mma_tf32(c3, alo2.z, ahi2.z, alo2.w, ahi2.w, bs2.z, bs2.w);
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        c0[e] += c2[e];
+        c1[e] += c3[e];
       }
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
@@ -276,8 +348,8 @@ __global__ void __launch_bounds__(128) gdn_chunk_kernel(const GdnChunkArgs p) {
       }
       const float g_lo = __expf(b[g]), g_hi = __expf(b[g + 8]);
 #pragma unroll
-      for (int q2 = 0; q2 < 2; ++q2) {
-        const int n0 = (warp - 2) * 16 + q2 * 8;
+      for (int q2 = 0; q2 < QT; ++q2) {
+        const int n0 = ((warp - 2) * QT + q2) * 8;
         float c[4] = {qs[q2][0] * g_lo, qs[q2][1] * g_lo, qs[q2][2] * g_hi, qs[q2][3] * g_hi};
 #pragma unroll
         for (int ks = 0; ks < 2; ++ks)
@@ -302,43 +374,73 @@ __global__ void __launch_bounds__(128) gdn_chunk_kernel(const GdnChunkArgs p) {
         e_lo[ks] = __expf(bl - b[ks * 8 + t]);
         e_hi[ks] = __expf(bl - b[ks * 8 + t + 4]);
       }
+      uint32_t ka[2][2][4];          // [mt][ks]: scaled K^T fragments of this warp's two 16-row tiles
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt) {
         const int m0 = warp * 32 + mt * 16;
-        uint32_t ka[2][4];
 #pragma unroll
         for (int ks = 0; ks < 2; ++ks) {
           const int j0 = ks * 8;
-          ka[ks][0] = tf32(K_[j0 + t][m0 + g] * e_lo[ks]);
-          ka[ks][1] = tf32(K_[j0 + t][m0 + g + 8] * e_lo[ks]);
-          ka[ks][2] = tf32(K_[j0 + t + 4][m0 + g] * e_hi[ks]);
-          ka[ks][3] = tf32(K_[j0 + t + 4][m0 + g + 8] * e_hi[ks]);
+          ka[mt][ks][0] = tf32(K_[j0 + t][m0 + g] * e_lo[ks]);
+          ka[mt][ks][1] = tf32(K_[j0 + t][m0 + g + 8] * e_lo[ks]);
+          ka[mt][ks][2] = tf32(K_[j0 + t + 4][m0 + g] * e_hi[ks]);
+          ka[mt][ks][3] = tf32(K_[j0 + t + 4][m0 + g + 8] * e_hi[ks]);
+        }
+      }
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const int n0 = nt * 8;
+        uint32_t db[2][2];
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks) {
+          db[ks][0] = tf32(sm.D[ks * 8 + t][n0 + g]);
+          db[ks][1] = tf32(sm.D[ks * 8 + t + 4][n0 + g]);
         }
 #pragma unroll
-        for (int nt = 0; nt < NV / 8; ++nt) {
-          const int n0 = nt * 8;
-          const float2 s_lo = *reinterpret_cast<const float2*>(&sm.S[m0 + g][n0 + 2 * t]);
-          const float2 s_hi = *reinterpret_cast<const float2*>(&sm.S[m0 + g + 8][n0 + 2 * t]);
-          float c[4] = {gall * s_lo.x, gall * s_lo.y, gall * s_hi.x, gall * s_hi.y};
+        for (int mt = 0; mt < 2; ++mt) {
+          const int m0 = warp * 32 + mt * 16;
+          float (&c)[4] = sreg[mt][nt];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) c[e] *= gall;
 #pragma unroll
           for (int ks = 0; ks < 2; ++ks)
-            mma_tf32(c, ka[ks][0], ka[ks][1], ka[ks][2], ka[ks][3], tf32(sm.D[ks * 8 + t][n0 + g]),
-                     tf32(sm.D[ks * 8 + t + 4][n0 + g]));
-          // a warp reads and writes only its own 32 rows of S here, and its lanes touch disjoint elements
-          *reinterpret_cast<float2*>(&sm.S[m0 + g][n0 + 2 * t]) = make_float2(c[0], c[1]);
-          *reinterpret_cast<float2*>(&sm.S[m0 + g + 8][n0 + 2 * t]) = make_float2(c[2], c[3]);
+            mma_tf32(c, ka[mt][ks][0], ka[mt][ks][1], ka[mt][ks][2], ka[mt][ks][3], db[ks][0], db[ks][1]);
+          // publish the rows this warp owns for the next chunk's B-operand reads
+          sm.St[n0 + 2 * t][m0 + g] = c[0];
+          sm.St[n0 + 2 * t + 1][m0 + g] = c[1];
+          sm.St[n0 + 2 * t][m0 + g + 8] = c[2];
+          sm.St[n0 + 2 * t + 1][m0 + g + 8] = c[3];
         }
       }
     }
-    if (ch + 1 < n_chunks) store_scalars(buf ^ 1);
+    if (ch + 1 < n_chunks) store_scalars((ch + 1) % NST);
   }
   __syncthreads();
   if (p.write_state) {
     for (int i = tid; i < DK * (NV / 4); i += 128) {
       const int r = i / (NV / 4), c4 = (i % (NV / 4)) * 4;
-      *reinterpret_cast<float4*>(Sg + (size_t)r * 128 + c4) = *reinterpret_cast<const float4*>(&sm.S[r][c4]);
+      *reinterpret_cast<float4*>(Sg + (size_t)r * 128 + c4) =
+          make_float4(sm.St[c4][r], sm.St[c4 + 1][r], sm.St[c4 + 2][r], sm.St[c4 + 3][r]);
     }
   }
+}
+
+
+
+// Chunked tensor-core scan.  Same arguments as he_gdn_scan minus the journal; state size must be 128.
+template <int NV>
+int launch_chunk(const GdnChunkArgs& a, cudaStream_t stream) {
+  const size_t smem = sizeof(Smem<NV>);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gdn_chunk_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid(a.n_seg, a.Hv, 128 / NV);
+  gdn_chunk_kernel<NV><<<grid, 128, smem, stream>>>(a);
+  HE_LAUNCH_CHECK();
+  return 0;
 }
 
 }  // namespace
@@ -347,16 +449,10 @@ __global__ void __launch_bounds__(128) gdn_chunk_kernel(const GdnChunkArgs p) {
 HE_API int he_gdn_scan_chunked(const GdnChunkArgs* args, cudaStream_t stream) {
   if (args->T <= 0 || args->n_seg <= 0) return 0;
   if (args->C != 2 * args->G * 128 + args->Hv * 128) return -HE_ERR_BAD_ARG;
-  const size_t smem = sizeof(Smem);
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gdn_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
-  dim3 grid(args->n_seg, args->Hv, 128 / NV);
-  gdn_chunk_kernel<<<grid, 128, smem, stream>>>(*args);
-  HE_LAUNCH_CHECK();
-  return 0;
+  static const int nv_env = []() { const char* e = getenv("HE_GDN_NV"); return e ? atoi(e) : 0; }();
+  // 16-column slices double the CTAs but repeat the per-chunk K K^T / inverse work; measured equal to 32 columns on a
+  // single 4096-token sequence, so the wider slice is the default (HE_GDN_NV=16 selects the narrow one)
+  const bool narrow = nv_env == 16;
+  return narrow ? launch_chunk<16>(*args, stream) : launch_chunk<32>(*args, stream);
 }
 HE_API int he_gdn_chunk_args_size() { return (int)sizeof(GdnChunkArgs); }
