@@ -186,6 +186,10 @@ class EngineService:
         self.closed = True
         self._wake.set()
         self.thread.join(timeout=10.0)
+        try:
+            self.loop.runner.close()      # drops captured graphs (they may hold library collectives)
+        except Exception:
+            pass
 
     # ------------------------------------------------------------------ driver thread
     def _on_event(self, rs: RequestState) -> None:
@@ -295,6 +299,27 @@ def build_engine(weights, backend: str, config: EngineConfig, tokenizer=None) ->
     if backend == "cpu_reference":
         from .runner import CpuReferenceRunner
         runner = CpuReferenceRunner(weights, config, eos)
+    elif config.parallel.tp > 1 or config.parallel.ep > 1:
+        # SPMD serving: this process is one rank of a torchrun job; every rank builds the same engine over its own
+        # weight shard and must be driven with identical requests (the collectives inside the executor keep the
+        # ranks in step).  Prefix caching is per rank and deterministic, so the ranks make the same decisions.
+        from ..parallel.groups import init_distributed
+        from ..parallel.tp import TPHybridExecutor
+        from .gpu_runner import GpuRunner
+        ctx = init_distributed()
+        want = max(config.parallel.tp, config.parallel.ep)
+        if ctx.world != want:
+            raise RuntimeError(f"tensor/expert parallel size {want} needs a {want}-process job "
+                               f"(python -m torch.distributed.run --nproc-per-node {want} ...); this job has "
+                               f"{ctx.world} process(es)")
+        n_snap = config.kv.max_snapshots if (config.kv.prefix_cache != "off" and weights.config.is_hybrid) else 0
+        max_ctx = min(config.max_sequence_length, weights.config.max_context)
+        pages_per_slot = (max_ctx + config.kv.page_tokens - 1) // config.kv.page_tokens
+        n_slots = config.scheduler.max_active_requests
+        n_pages = config.kv.pool_pages or (n_slots * pages_per_slot * (2 if config.kv.prefix_cache != "off" else 1) + 1)
+        ex = TPHybridExecutor(weights.to(ctx.device), ctx, max_slots=n_slots + n_snap, max_context=max_ctx,
+                              n_pages=n_pages)
+        runner = GpuRunner(None, config, eos, executor=ex)
     else:
         from .gpu_runner import GpuRunner
         runner = GpuRunner(weights, config, eos)

@@ -328,6 +328,12 @@ class GpuRunner(BaseRunner):
         if rs.rid in self.resident_key:
             self.resident_key = ()
 
+    def close(self) -> None:
+        """Drop the captured decode graphs: in a multi-rank job they hold library collectives, which must be gone
+        before the process group is destroyed."""
+        self.graphs.graphs.clear()
+        self.graphs._execs.clear()
+
     def reset(self) -> None:
         for rid in list(self.pool.leases):
             self.pool.release(rid)

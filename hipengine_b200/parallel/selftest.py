@@ -80,6 +80,23 @@ def main() -> int:
                 ex.fused.close()
         del ex
 
+    # the public API as an SPMD job: every rank issues the same call; tokens must match a single-GPU engine
+    if ctx.world > 1:
+        from ..llm import LLM, SamplingParams
+        sp = SamplingParams(max_tokens=6, ignore_eos=True)
+        tp_llm = LLM(w, backend="cuda_sm100a", tensor_parallel=ctx.world, max_active_requests=2,
+                     max_sequence_length=256, prefix_cache="off")
+        got_ids = tp_llm.generate_token_ids([toks[:24]], sp)[0]
+        tp_llm.close()
+        one = LLM(w, backend="cuda_sm100a", max_active_requests=2, max_sequence_length=256, prefix_cache="off")
+        want_ids = one.generate_token_ids([toks[:24]], sp)[0]
+        one.close()
+        same = sum(int(a == b) for a, b in zip(got_ids, want_ids))
+        all_ids = ctx.all_gather(torch.tensor(got_ids, device=dev))
+        report["api_tokens_match"] = same
+        report["api_ranks_agree"] = bool((all_ids == all_ids[0]).all())
+        ok = ok and report["api_ranks_agree"] and same >= (3 if cfg.is_moe else 5)
+
     # device-timed reduction latency: 1 row of the 27B hidden width
     if ctx.world > 1:
         width = args.bench_width
