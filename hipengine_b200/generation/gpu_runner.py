@@ -47,7 +47,9 @@ class GpuRunner(BaseRunner):
             self.n_snap = min(self.n_snap, max(0, executor.max_slots - self.max_slots))
             n_pages = executor.n_pages
         else:
-            dev = "cuda"
+            # an explicit index: "cuda" alone means "this thread's current device", which differs between the
+            # constructing thread and the engine's driver thread on every rank but the first
+            dev = torch.device("cuda", torch.cuda.current_device())
             from ..models import make_executor
             self.ex = make_executor(weights, device=dev, max_slots=self.max_slots + self.n_snap,
                                     max_context=self.max_context, n_pages=n_pages)

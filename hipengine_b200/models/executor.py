@@ -115,6 +115,8 @@ class HybridExecutor:
                  n_pages: Optional[int] = None, gemm_impl: Optional[str] = None):
         self.cfg = cfg = weights.config
         self.device = torch.device(device)
+        if self.device.type == "cuda" and self.device.index is None:
+            self.device = torch.device("cuda", torch.cuda.current_device())
         self.max_slots = max_slots
         self.max_context = max_context
         self.max_pages_per_slot = (max_context + PAGE - 1) // PAGE
