@@ -41,6 +41,68 @@ struct GemmArgs {
   long long split_stride;   // epi 4: split ks stores its fp32 partial tile at C + ks * split_stride (elements)
 };
 
+// Fused GEMM -> all-reduce -> residual add over peer memory (tensor-parallel row-parallel projections).
+// Every rank owns one symmetric region, mapped into all peers:
+//     stage  [world src][owned_cap][BM*BN] bf16 : partial tiles pushed by rank `src` for the tiles this rank owns
+//     result [max_tiles][BM*BN] bf16            : reduced tiles, written by each tile's owner into every rank
+//     flags  arrive[max_tiles][world][4] u32, then done[max_tiles][4] u32 : epoch stamps per 32-row tile quarter
+// Tile t (M-fastest index) is owned by rank t % world.  One kernel per rank runs three phases; all
+// synchronisation is per warp (one epilogue warp handles one 32-row quarter of a tile in every phase):
+//   1. the GEMM epilogue stores its partial quarter straight into the owner's stage slot (peer stores for remote
+//      owners), fences at system scope and stamps arrive[t][me][q] on the owner;
+//   2. for each owned tile, wait (bounded) for the world stamps of the quarter, sum the slots in rank order in
+//      fp32, store the bf16 result into every rank's result region and stamp done[t][q] there;
+//   3. for each tile, wait (bounded) for done[t][q] locally and add the result rows into the fp32 residual.
+// The transfers of phase 1 overlap the MMAs of later tiles.  The epoch lives in device memory and is advanced by the
+// last CTA to leave, so the kernel can be replayed from a CUDA graph.  `phases` (bit 0/1/2) selects which phases a
+// launch runs: 7 in production; a single-GPU test runs the phases of several emulated ranks as separate launches
+// (1,1,..,2,2,..,4,4,..) so that no launch ever waits for a later one.
+constexpr int FUSE_MAX_WORLD = 8;
+constexpr int TILE_ELEMS = 128 * 256;
+
+struct FuseArgs {
+  __nv_bfloat16* stage[FUSE_MAX_WORLD];
+  __nv_bfloat16* result[FUSE_MAX_WORLD];
+  uint32_t* flags[FUSE_MAX_WORLD];
+  uint32_t* sync;         // local [2]: epoch of the last finished call, CTAs that have left the current call
+  float* resid;           // local fp32 [M][ld_resid]: resid += all-reduced product
+  long long ld_resid;
+  int world, rank, max_tiles, owned_cap, phases;
+  unsigned wait_limit;
+};
+
+__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_cg_u4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+// Whole-warp bounded wait until *p has reached `epoch` (stamps only grow); lanes < n poll p[lane * stride].
+__device__ __forceinline__ bool warp_wait_stamps(const uint32_t* p, int n, int stride, uint32_t epoch, unsigned limit,
+                                                 int* status) {
+  const int lane = threadIdx.x & 31;
+  bool ok = true;
+  if (lane < n) {
+    unsigned polls = 0;
+    while ((int)(ld_acquire_sys_u32(p + (size_t)lane * stride) - epoch) < 0) {
+      if (++polls > limit) {
+        ok = false;
+        if (status != nullptr) atomicCAS(status, 0, HE_ERR_WAIT_TIMEOUT);
+        break;
+      }
+      __nanosleep(64);
+    }
+  }
+  return __all_sync(0xffffffffu, ok);
+}
+
 struct __align__(8) Barriers {
   uint64_t full[STAGES];
   uint64_t empty[STAGES];
@@ -50,8 +112,9 @@ struct __align__(8) Barriers {
   int abort_flag;
 };
 
-__global__ void __launch_bounds__(NTHREADS, 1)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmArgs g) {
+template <bool FUSE>
+__device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& g,
+                                          const FuseArgs* f) {
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment for the swizzled tiles
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -61,7 +124,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (g.M + BM - 1) / BM, tiles_n = (g.N + BN - 1) / BN;
   const int ksp = g.k_splits > 1 ? g.k_splits : 1;
-  const int n_tiles = tiles_m * tiles_n * ksp;
+  const int n_tiles = (FUSE && !(f->phases & 1)) ? 0 : tiles_m * tiles_n * ksp;
   const int k_blocks_all = (g.K + BK - 1) / BK;
   const int kb_per = (k_blocks_all + ksp - 1) / ksp;      // k-blocks per split (the last split may get fewer)
 
@@ -85,6 +148,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = bar->tmem_base;
+  uint32_t fuse_epoch = 0;
+  if constexpr (FUSE) fuse_epoch = *reinterpret_cast<volatile uint32_t*>(f->sync) + 1;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -170,6 +235,25 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tmem_ld_32x32(t_row + c * 32, r);
         tmem_ld_wait();
         const int col0 = tn * BN + c * 32;
+        if constexpr (FUSE) {
+          // partial quarter -> the owner's stage slot; rows and columns past M / N are zeros (zero-filled operand
+          // tiles), so the whole tile is stored and no bound is needed
+          const int owner = mn % f->world, oi = mn / f->world;
+          __nv_bfloat16* dst = f->stage[owner] + ((size_t)f->rank * f->owned_cap + oi) * TILE_ELEMS +
+                               (size_t)(q * 32 + lane) * BN + c * 32;
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 pk;
+            uint32_t* pw = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * e]),
+                                                        __uint_as_float(r[v * 8 + 2 * e + 1]));
+              pw[e] = *reinterpret_cast<uint32_t*>(&h2);
+            }
+            *reinterpret_cast<uint4*>(dst + v * 8) = pk;
+          }
+        } else
         if (row < g.M && col0 < g.N) {
           const int ncols = min(32, g.N - col0);
           if (g.epi == 0) {
@@ -221,7 +305,85 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar->acc_empty[acc]);
+      if constexpr (FUSE) {
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0)
+          st_release_sys_u32(f->flags[mn % f->world] + ((size_t)mn * f->world + f->rank) * 4 + q, fuse_epoch);
+      }
       ++tcount;
+    }
+    if constexpr (FUSE) {
+      const int tiles_mn = tiles_m * tiles_n;
+      const int W = f->world;
+      bool alive = *abort_flag == 0;
+      uint32_t* my_flags = f->flags[f->rank];
+      const size_t done_off = (size_t)f->max_tiles * W * 4;
+      // ---- phase 2: reduce the tiles this rank owns (quarter q of each), broadcast the result
+      if (f->phases & 2) {
+        for (int mn = f->rank + blockIdx.x * W; mn < tiles_mn && alive; mn += gridDim.x * W) {
+          alive = warp_wait_stamps(my_flags + (size_t)mn * W * 4 + q, W, 4, fuse_epoch, f->wait_limit, g.status);
+          if (!alive) break;
+          const size_t q_off = (size_t)q * 32 * BN;                    // this warp's 32 rows of the tile
+          const __nv_bfloat16* src0 = f->stage[f->rank] + (size_t)(mn / W) * TILE_ELEMS + q_off;
+          const size_t src_stride = (size_t)f->owned_cap * TILE_ELEMS;
+#pragma unroll 2
+          for (int it = 0; it < 32; ++it) {
+            const size_t e0 = (size_t)(it * 32 + lane) * 8;
+            float acc8[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc8[e] = 0.f;
+            for (int r = 0; r < W; ++r) {
+              const uint4 v = ld_cg_u4(src0 + (size_t)r * src_stride + e0);
+              const __nv_bfloat162* hv = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 t2 = __bfloat1622float2(hv[e]);
+                acc8[2 * e] += t2.x;
+                acc8[2 * e + 1] += t2.y;
+              }
+            }
+            uint4 pk;
+            uint32_t* pw = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              __nv_bfloat162 h2 = __floats2bfloat162_rn(acc8[2 * e], acc8[2 * e + 1]);
+              pw[e] = *reinterpret_cast<uint32_t*>(&h2);
+            }
+            for (int r = 0; r < W; ++r)
+              *reinterpret_cast<uint4*>(f->result[r] + (size_t)mn * TILE_ELEMS + q_off + e0) = pk;
+          }
+          __threadfence_system();
+          __syncwarp();
+          if (lane < W) st_release_sys_u32(f->flags[lane] + done_off + (size_t)mn * 4 + q, fuse_epoch);
+        }
+      }
+      // ---- phase 3: resid += reduced tile (quarter q of every tile this CTA walks)
+      if (f->phases & 4) {
+        for (int mn = blockIdx.x; mn < tiles_mn && alive; mn += gridDim.x) {
+          alive = warp_wait_stamps(my_flags + done_off + (size_t)mn * 4 + q, 1, 1, fuse_epoch, f->wait_limit, g.status);
+          if (!alive) break;
+          const int tm = mn % tiles_m, tn = mn / tiles_m;
+          const __nv_bfloat16* res = f->result[f->rank] + (size_t)mn * TILE_ELEMS + (size_t)q * 32 * BN;
+          const int col = tn * BN + lane * 8;
+          if (col < g.N) {
+            for (int rr = 0; rr < 32; ++rr) {
+              const int row = tm * BM + q * 32 + rr;
+              if (row >= g.M) break;
+              const uint4 v = ld_cg_u4(res + (size_t)rr * BN + lane * 8);
+              const __nv_bfloat162* hv = reinterpret_cast<const __nv_bfloat162*>(&v);
+              float4* hp = reinterpret_cast<float4*>(f->resid + (size_t)row * f->ld_resid + col);
+              float4 h0 = hp[0], h1 = hp[1];
+              const float2 a0 = __bfloat1622float2(hv[0]), a1 = __bfloat1622float2(hv[1]);
+              const float2 a2 = __bfloat1622float2(hv[2]), a3 = __bfloat1622float2(hv[3]);
+              h0.x += a0.x; h0.y += a0.y; h0.z += a1.x; h0.w += a1.y;
+              h1.x += a2.x; h1.y += a2.y; h1.z += a3.x; h1.w += a3.y;
+              hp[0] = h0;
+              hp[1] = h1;
+            }
+          }
+        }
+      }
     }
   }
 
@@ -232,6 +394,29 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+  if constexpr (FUSE) {
+    // the last CTA to leave a launch that ran the final phase publishes the new epoch for the next launch
+    if (threadIdx.x == 0 && (f->phases & 4)) {
+      __threadfence();
+      const unsigned prev = atomicAdd(f->sync + 1, 1u);
+      if (prev == gridDim.x - 1) {
+        f->sync[1] = 0;
+        f->sync[0] = fuse_epoch;
+        __threadfence();
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(NTHREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmArgs g) {
+  gemm_body<false>(tmA, tmB, g, nullptr);
+}
+
+__global__ void __launch_bounds__(NTHREADS, 1)
+gemm_bf16_allreduce_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                           const GemmArgs g, const __grid_constant__ FuseArgs f) {
+  gemm_body<true>(tmA, tmB, g, &f);
 }
 
 // ---------------------------------------------------------------- host side: tensor maps
@@ -295,6 +480,47 @@ HE_API int he_gemm_bf16(const void* A, long long lda, const void* B, long long l
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < num_sms ? tiles : num_sms;
   gemm_bf16_kernel<<<grid, NTHREADS, smem, stream>>>(tmA, tmB, g);
+  HE_LAUNCH_CHECK();
+  return 0;
+}
+
+// resid[M][N] (fp32) += sum over ranks of A_rank[M][K] * B_rank[N][K]^T: the GEMM, the all-reduce over peer memory
+// and the residual add in one kernel per rank (see FuseArgs).  Every rank of the group must issue the same sequence
+// of calls with the same M and N.  `fuse` is a host copy of FuseArgs.
+HE_API int he_gemm_fuse_args_size() { return (int)sizeof(FuseArgs); }
+HE_API int he_gemm_fuse_tile_elems() { return TILE_ELEMS; }
+HE_API int he_gemm_fuse_tiles(int M, int N) { return ((M + BM - 1) / BM) * ((N + BN - 1) / BN); }
+
+HE_API int he_gemm_bf16_allreduce(const void* A, long long lda, const void* B, long long ldb, int M, int N, int K,
+                                  const FuseArgs* fuse, void* status, int num_sms, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  const FuseArgs& f = *fuse;
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  if (K % 8 != 0 || N % 8 != 0) return -HE_ERR_BAD_ARG;
+  if (f.world < 1 || f.world > FUSE_MAX_WORLD || f.rank < 0 || f.rank >= f.world) return -HE_ERR_BAD_ARG;
+  if (tiles > f.max_tiles || (tiles + f.world - 1) / f.world > f.owned_cap) return -HE_ERR_BAD_ARG;
+  if (f.resid == nullptr || (reinterpret_cast<uintptr_t>(f.resid) & 15) != 0 || f.ld_resid % 4 != 0 || f.ld_resid < N)
+    return -HE_ERR_BAD_ARG;
+  if ((f.phases & 7) == 0 || f.sync == nullptr) return -HE_ERR_BAD_ARG;
+  for (int r = 0; r < f.world; ++r)
+    if (f.stage[r] == nullptr || f.result[r] == nullptr || f.flags[r] == nullptr) return -HE_ERR_BAD_ARG;
+  CUtensorMap tmA, tmB;
+  int rc = make_map(&tmA, A, M, K, lda, BM);
+  if (rc != 0) return rc;
+  rc = make_map(&tmB, B, N, K, ldb, BN);
+  if (rc != 0) return rc;
+  GemmArgs g;
+  g.C = nullptr; g.ldc = 0; g.resid = nullptr; g.M = M; g.N = N; g.K = K; g.epi = 5; g.status = (int*)status;
+  g.tile_group = nullptr;
+  g.k_splits = 1;
+  g.split_stride = 0;
+  const size_t smem = STAGES * STAGE_BYTES + sizeof(Barriers) + 1024;
+  cudaError_t e = cudaFuncSetAttribute(gemm_bf16_allreduce_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  // every CTA must be resident at once (CTAs of one rank wait for tiles of CTAs on other ranks): one CTA per SM
+  const int grid = tiles < num_sms ? tiles : num_sms;
+  gemm_bf16_allreduce_kernel<<<grid, NTHREADS, smem, stream>>>(tmA, tmB, g, f);
   HE_LAUNCH_CHECK();
   return 0;
 }

@@ -125,3 +125,124 @@ class FusedReducer:
         if self._local:
             L.he_comm_free(C.c_void_p(self._local))
             self._local = 0
+
+
+class _FuseArgs(C.Structure):
+    _fields_ = [("stage", C.c_void_p * _MAX_WORLD), ("result", C.c_void_p * _MAX_WORLD),
+                ("flags", C.c_void_p * _MAX_WORLD), ("sync", C.c_void_p), ("resid", C.c_void_p),
+                ("ld_resid", C.c_longlong), ("world", C.c_int), ("rank", C.c_int), ("max_tiles", C.c_int),
+                ("owned_cap", C.c_int), ("phases", C.c_int), ("wait_limit", C.c_uint)]
+
+
+class FusedGemmAllReduce:
+    """Row-parallel projection for many rows: ``resid += all_reduce(x_rank @ W_rank^T)`` as ONE tcgen05 kernel per
+    rank (``csrc/gemm_sm100.cu::gemm_bf16_allreduce_kernel``).
+
+    The GEMM epilogue stores each partial tile into the stage buffer of the tile's owner rank through peer memory
+    while later tiles are still in the tensor cores; owners sum in rank order and write the bf16 result into every
+    rank, and each rank adds it into its fp32 residual -- all behind bounded per-warp flag waits.  Regions are plain
+    device allocations shared through CUDA IPC (single node).  The reference engine is single-device: no counterpart.
+    """
+
+    def __init__(self, ctx: DistContext, width: int, max_rows: int = 4096, wait_limit: int = 1 << 22,
+                 _regions: List[int] = None):
+        L = N.lib()
+        assert L.he_gemm_fuse_args_size() == C.sizeof(_FuseArgs), "ABI mismatch for FuseArgs"
+        assert ctx.world <= _MAX_WORLD and width % 8 == 0
+        self.ctx, self.width, self.max_rows, self.wait_limit = ctx, width, max_rows, wait_limit
+        self.tile_elems = L.he_gemm_fuse_tile_elems()
+        self.max_tiles = L.he_gemm_fuse_tiles(C.c_int(max_rows), C.c_int(width))
+        self.owned_cap = (self.max_tiles + ctx.world - 1) // ctx.world
+        self.stage_bytes = ctx.world * self.owned_cap * self.tile_elems * 2
+        self.result_bytes = self.max_tiles * self.tile_elems * 2
+        self.flag_bytes = (self.max_tiles * ctx.world * 4 + self.max_tiles * 4) * 4
+        self.total_bytes = self.stage_bytes + self.result_bytes + self.flag_bytes
+        self._opened: List[int] = []
+        self._local = 0
+        if _regions is not None:                      # emulated ranks of one process share plain pointers
+            self._peer_ptrs = list(_regions)
+        else:
+            base = C.c_void_p()
+            N.check(L.he_comm_alloc(C.c_longlong(self.total_bytes), C.byref(base)), "he_comm_alloc")
+            self._local = base.value
+            self._peer_ptrs = [self._local] * ctx.world
+            if ctx.world > 1:
+                hsz = L.he_comm_ipc_handle_size()
+                handle = (C.c_char * hsz)()
+                N.check(L.he_comm_ipc_get(C.c_void_p(self._local), handle), "he_comm_ipc_get")
+                handles: List[bytes] = [b""] * ctx.world
+                dist.all_gather_object(handles, bytes(handle.raw), group=ctx.group)
+                for r in range(ctx.world):
+                    if r == ctx.rank:
+                        continue
+                    p = C.c_void_p()
+                    buf = (C.c_char * hsz).from_buffer_copy(handles[r])
+                    N.check(L.he_comm_ipc_open(buf, C.byref(p)), "he_comm_ipc_open")
+                    self._peer_ptrs[r] = p.value
+                    self._opened.append(p.value)
+        self.sync = torch.zeros(2, dtype=torch.int32, device=ctx.device)
+        if _regions is None and ctx.world > 1:
+            ctx.barrier()       # every region is zeroed and mapped before the first kernel runs
+        self.calls = 0
+
+    @classmethod
+    def emulated_group(cls, device, width: int, world: int, max_rows: int = 512) -> List["FusedGemmAllReduce"]:
+        """``world`` instances in ONE process on one GPU, wired to each other's regions.  Their kernels must be run
+        phase by phase (all ranks' phase 1, then all phase 2, then all phase 3) so that no launch waits for a later
+        launch; see ``gemm_add(..., phases=...)``."""
+        L = N.lib()
+        regions: List[int] = []
+        out: List[FusedGemmAllReduce] = []
+        for r in range(world):
+            ctx = DistContext(r, world, 0, torch.device(device), None, "loopback")
+            inst = cls(ctx, width, max_rows, wait_limit=20000, _regions=[0] * world)
+            base = C.c_void_p()
+            N.check(L.he_comm_alloc(C.c_longlong(inst.total_bytes), C.byref(base)), "he_comm_alloc")
+            regions.append(base.value)
+            out.append(inst)
+        for inst in out:
+            inst._peer_ptrs = list(regions)
+        out[0]._owned_regions = regions
+        return out
+
+    def supports(self, rows: int, resid: torch.Tensor) -> bool:
+        return (rows <= self.max_rows and resid.dtype == torch.float32 and resid.stride(1) == 1
+                and resid.stride(0) % 4 == 0 and resid.data_ptr() % 16 == 0)
+
+    def gemm_add(self, x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor, phases: int = 7) -> None:
+        """resid[M, N] += sum over ranks of (x[M, K] @ w[N, K]^T); x, w bf16 (this rank's K shard), resid fp32."""
+        assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and resid.dtype == torch.float32
+        K._check_device(x)
+        M, Kd = x.shape
+        Nn = w.shape[0]
+        assert Nn == self.width and w.shape[1] == Kd and x.stride(1) == 1 and w.stride(1) == 1
+        assert self.supports(M, resid) and resid.shape[1] >= Nn
+        a = _FuseArgs()
+        off_res, off_flag = self.stage_bytes, self.stage_bytes + self.result_bytes
+        for r, p in enumerate(self._peer_ptrs):
+            a.stage[r], a.result[r], a.flags[r] = p, p + off_res, p + off_flag
+        a.sync = self.sync.data_ptr()
+        a.resid, a.ld_resid = resid.data_ptr(), resid.stride(0)
+        a.world, a.rank = self.ctx.world, self.ctx.rank
+        a.max_tiles, a.owned_cap, a.phases, a.wait_limit = self.max_tiles, self.owned_cap, phases, self.wait_limit
+        st = K.status_tensor(x.device)
+        N.check(N.lib().he_gemm_bf16_allreduce(
+            C.c_void_p(x.data_ptr()), C.c_longlong(x.stride(0)), C.c_void_p(w.data_ptr()), C.c_longlong(w.stride(0)),
+            C.c_int(M), C.c_int(Nn), C.c_int(Kd), C.byref(a), C.c_void_p(st.data_ptr()), C.c_int(N.num_sms()),
+            K._stream()), "he_gemm_bf16_allreduce")
+        self.calls += 1
+
+    def close(self) -> None:
+        L = N.lib()
+        torch.cuda.synchronize()
+        if self.ctx.backend not in ("loopback", "none") and self.ctx.world > 1:
+            self.ctx.barrier()
+        for p in self._opened:
+            L.he_comm_ipc_close(C.c_void_p(p))
+        self._opened = []
+        if self._local:
+            L.he_comm_free(C.c_void_p(self._local))
+            self._local = 0
+        for p in getattr(self, "_owned_regions", []):
+            L.he_comm_free(C.c_void_p(p))
+        self._owned_regions = []

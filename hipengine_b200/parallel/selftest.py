@@ -20,6 +20,7 @@ def main() -> int:
     ap.add_argument("--prompt", type=int, default=40)
     ap.add_argument("--decode", type=int, default=6)
     ap.add_argument("--bench-width", type=int, default=5120)
+    ap.add_argument("--bench-rows", type=int, default=4096)
     args = ap.parse_args()
     from ..loading.synth import build_random_model
     from ..models.config import NAMED_CONFIGS
@@ -78,6 +79,10 @@ def main() -> int:
             del r
             if ex.fused is not None:
                 ex.fused.close()
+            if ex.fgemm is not None:
+                report["fused_gemm_calls"] = ex.fgemm.calls
+                ok = ok and ex.fgemm.calls > 0
+                ex.fgemm.close()
         del ex
 
     # the public API as an SPMD job: every rank issues the same call; tokens must match a single-GPU engine
@@ -125,6 +130,36 @@ def main() -> int:
         ok = ok and report["fused_sum_ok"]
         report["nccl_allreduce_us"] = round(time_it(lambda: ctx.all_reduce_(part)), 2)
         red.close()
+        # row-parallel prefill projection, 27B FFN-down shape split over the ranks: one fused kernel against
+        # GEMM + library all-reduce + residual add
+        from ..ops import gemm as GM
+        from .fused import FusedGemmAllReduce
+        M, Nn, Kd = args.bench_rows, width, (17408 // ctx.world) // 64 * 64
+        g = torch.Generator(device=dev).manual_seed(11 + ctx.rank)
+        x = torch.randn(M, Kd, device=dev, generator=g).bfloat16()
+        wt = (torch.randn(Nn, Kd, device=dev, generator=g) * 0.02).bfloat16()
+        hf = torch.zeros(M, Nn, device=dev)
+        hn = torch.zeros(M, Nn, device=dev)
+        y = torch.empty(M, Nn, device=dev, dtype=torch.bfloat16)
+        fg = FusedGemmAllReduce(ctx, Nn, max_rows=M)
+
+        def baseline():
+            GM.gemm_bf16(x, wt, y)
+            ctx.all_reduce_(y)
+            K.resid_add_bf16(hn, y)
+
+        fg.gemm_add(x, wt, hf)
+        baseline()
+        torch.cuda.synchronize()
+        K.check_status(dev)
+        rel = ((hf - hn).abs().max() / hn.std().clamp_min(1e-6)).item()
+        report["fused_gemm_vs_nccl_rel_err"] = round(rel, 5)
+        ok = ok and rel < 0.1
+        report["fused_gemm_allreduce_us"] = round(time_it(lambda: fg.gemm_add(x, wt, hf), iters=20), 1)
+        K.check_status(dev)
+        report["gemm_nccl_allreduce_us"] = round(time_it(baseline, iters=20), 1)
+        report["fused_gemm_shape"] = [M, Nn, Kd]
+        fg.close()
     if ctx.rank == 0:
         report["ok"] = ok
         print(json.dumps(report))

@@ -6,9 +6,11 @@ holds the replicated fp32 residual stream and produces its own heads / FFN colum
 the ranks and added to the residual.  Two reduction back-ends:
 
 * ``comm="nccl"``  : ``torch.distributed.all_reduce`` (captured inside the decode CUDA graphs) -- the baseline;
-* ``comm="fused"`` : own kernels over peer memory (``csrc/comm.cu``): every rank pushes its partial rows into
-  all peers' symmetric buffers and the reduction is folded into one small kernel that also applies the
-  residual add, so a decode step has no library collective at all.
+* ``comm="fused"`` : own kernels over peer memory.  Few rows (``csrc/comm.cu``): every rank pushes its partial
+  rows into all peers' symmetric buffers and the reduction is folded into one small kernel that also applies
+  the residual add, so a decode step has no library collective at all.  Many rows
+  (``csrc/gemm_sm100.cu::gemm_bf16_allreduce_kernel``): the tcgen05 GEMM pushes its partial tiles to their owner
+  ranks from the epilogue, owners reduce and broadcast, every rank adds into its residual -- one kernel.
 
 The output head is vocab-parallel; logits are all-gathered (greedy decode merges per-shard (max, id) pairs
 instead).  The reference engine is single-device (its ``docs/ARCHITECTURE.md`` lists multi-GPU as future work),
@@ -42,9 +44,15 @@ class TPHybridExecutor(HybridExecutor):
             self.expert_range = self.plan.experts
             self.owns_shared_expert = self.plan.owns_shared_expert
         self.fused = None
+        self.fgemm = None
         if self.comm == "fused" and ctx.world > 1:
             from .fused import FusedReducer
             self.fused = FusedReducer(ctx, self.full_cfg.hidden, max_rows=GEMV_MAX_ROWS)
+            if self.gemm_impl == "tcgen05" and self.full_cfg.hidden % 8 == 0 and \
+                    os.environ.get("HE_TP_FUSED_GEMM", "1") != "0":
+                from .fused import FusedGemmAllReduce
+                rows = min(8192, (self.max_context + 127) // 128 * 128)
+                self.fgemm = FusedGemmAllReduce(ctx, self.full_cfg.hidden, max_rows=rows)
 
     # ------------------------------------------------------------------ reductions
     def _out_small(self, x: torch.Tensor, w: DeviceWeight, h: torch.Tensor) -> None:
@@ -74,6 +82,11 @@ class TPHybridExecutor(HybridExecutor):
     def _out_big(self, x: torch.Tensor, w: DeviceWeight, h: torch.Tensor, tag: str) -> None:
         if self.ctx.world == 1:
             return super()._out_big(x, w, h, tag)
+        if self.fgemm is not None and self.fgemm.supports(x.shape[0], h):
+            # GEMM, all-reduce over peer memory and residual add as one tcgen05 kernel per rank
+            from ..ops import gemm as GM
+            self.fgemm.gemm_add(x, GM.bf16_weight(w, self.scratch, self.shadow), h)
+            return
         y = self._gemm(x, w, self.scratch.get("y_bf", (x.shape[0], w.n_rows), torch.bfloat16), tag=tag)
         self.ctx.all_reduce_(y)
         K.resid_add_bf16(h, y)
