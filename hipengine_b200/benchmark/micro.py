@@ -165,9 +165,38 @@ def bench_attn_decode(ctx, H=24, Hkv=4, D=256, rows=1):
             "GBps": round(bytes_ / ms / 1e6, 1), f"frac_of_{pk['src']}_hbm": round(bytes_ / ms / 1e6 / pk["hbm_gbs"], 3)}
 
 
+def bench_fused_allreduce_gemm(M, N, K, phases=7):
+    """Single-rank run of the fused GEMM -> all-reduce -> residual-add kernel (every tile goes through the stage,
+    reduce and add phases in local memory) against the plain GEMM followed by the residual add: the difference is
+    what the collective phases cost on top of the tensor-core work when no link is involved."""
+    from hipengine_b200.ops import gemm as G
+    from hipengine_b200.ops import kernels as K_
+    from hipengine_b200.parallel.fused import FusedGemmAllReduce
+    from hipengine_b200.parallel.groups import DistContext
+    nvar = max(2, int(200e6 // (N * K * 2)) + 1)
+    ws = [(torch.randn(N, K, device="cuda") * 0.02).bfloat16() for _ in range(nvar)]
+    x = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+    h = torch.zeros(M, N, device="cuda")
+    y = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    ctx = DistContext(0, 1, 0, torch.device("cuda", torch.cuda.current_device()), None, "none")
+    fg = FusedGemmAllReduce(ctx, N, max_rows=M)
+
+    def plain(i):
+        G.gemm_bf16(x, ws[i], y)
+        K_.resid_add_bf16(h, y)
+
+    ms_f = time_launches(lambda i: fg.gemm_add(x, ws[i], h, phases=phases), nvar)
+    G.check_status()
+    ms_p = time_launches(plain, nvar)
+    fg.close()
+    tf = 2.0 * M * N * K / 1e9
+    return {"kernel": "gemm_bf16_allreduce[world=1]", "M": M, "N": N, "K": K, "phases": phases,
+            "fused_ms": round(ms_f, 4), "gemm_plus_add_ms": round(ms_p, 4), "fused_tflops": round(tf / ms_f, 1)}
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "gemv", "gdn", "conv", "attn", "all"])
+    ap.add_argument("what", choices=["gemm", "gemv", "gdn", "conv", "attn", "fusedar", "all"])
     ap.add_argument("--t", type=int, default=4096)
     ap.add_argument("--ctx", type=int, default=4096)
     ap.add_argument("--m", type=int, default=4096)
@@ -176,6 +205,7 @@ def main():
     ap.add_argument("--rows", type=int, default=1)
     ap.add_argument("--qtype", default="q4_k")
     ap.add_argument("--impl", default="tcgen05")
+    ap.add_argument("--phases", type=int, default=0, help="fusedar: phase mask to time (0 = 1, 3 and 7 in turn)")
     a = ap.parse_args()
     out = []
     if a.what == "gemm":
@@ -189,6 +219,9 @@ def main():
         out.append(bench_conv(a.t))
     elif a.what == "attn":
         out.append(bench_attn_decode(a.ctx, rows=a.rows))
+    elif a.what == "fusedar":
+        for ph in ([1, 3, 7] if a.phases == 0 else [a.phases]):
+            out.append(bench_fused_allreduce_gemm(a.m, a.n, a.k, ph))
     else:
         for (m, n, k) in [(4096, 10240, 5120), (4096, 34816, 5120), (4096, 5120, 17408), (4096, 5120, 6144)]:
             out.append(bench_gemm(m, n, k, "tcgen05"))

@@ -24,6 +24,7 @@ constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int ACC_COLS = BN;           // fp32 columns per accumulator
 constexpr int TMEM_COLS = 512;
 constexpr int NTHREADS = 192;
+constexpr int NTHREADS_FUSED = 320;    // + 4 collective warps (fused GEMM -> all-reduce kernel)
 
 struct GemmArgs {
   void* C;
@@ -47,7 +48,8 @@ struct GemmArgs {
 //     result [max_tiles][BM*BN] bf16            : reduced tiles, written by each tile's owner into every rank
 //     flags  arrive[max_tiles][world][4] u32, then done[max_tiles][4] u32 : epoch stamps per 32-row tile quarter
 // Tile t (M-fastest index) is owned by rank t % world.  One kernel per rank runs three phases; all
-// synchronisation is per warp (one epilogue warp handles one 32-row quarter of a tile in every phase):
+// synchronisation is per warp (phase 1: the four epilogue warps; phases 2 and 3: four extra "collective" warps that
+// run beside the GEMM pipeline for the whole kernel; each warp handles one 32-row quarter of a tile):
 //   1. the GEMM epilogue stores its partial quarter straight into the owner's stage slot (peer stores for remote
 //      owners), fences at system scope and stamps arrive[t][me][q] on the owner;
 //   2. for each owned tile, wait (bounded) for the world stamps of the quarter, sum the slots in rank order in
@@ -84,23 +86,114 @@ __device__ __forceinline__ uint4 ld_cg_u4(const void* p) {
   asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
   return v;
 }
-// Whole-warp bounded wait until *p has reached `epoch` (stamps only grow); lanes < n poll p[lane * stride].
-__device__ __forceinline__ bool warp_wait_stamps(const uint32_t* p, int n, int stride, uint32_t epoch, unsigned limit,
-                                                 int* status) {
+// Whole-warp probe: true when the n stamps p[lane * stride] (lanes < n) have all reached `epoch` (stamps only grow).
+__device__ __forceinline__ bool warp_stamps_ready(const uint32_t* p, int n, int stride, uint32_t epoch) {
   const int lane = threadIdx.x & 31;
   bool ok = true;
-  if (lane < n) {
-    unsigned polls = 0;
-    while ((int)(ld_acquire_sys_u32(p + (size_t)lane * stride) - epoch) < 0) {
-      if (++polls > limit) {
-        ok = false;
-        if (status != nullptr) atomicCAS(status, 0, HE_ERR_WAIT_TIMEOUT);
-        break;
+  if (lane < n) ok = (int)(ld_acquire_sys_u32(p + (size_t)lane * stride) - epoch) >= 0;
+  return __all_sync(0xffffffffu, ok);
+}
+
+// Phase 2 for one warp: quarter q of owned tile mn -- sum the world stage slots in rank order, store the bf16 result
+// into every rank, stamp done[mn][q] everywhere.  The quarter is 32 rows x 256 columns = 1024 16-byte groups.
+__device__ __forceinline__ void fuse_reduce_quarter(const FuseArgs* f, int mn, int q, uint32_t epoch) {
+  const int lane = threadIdx.x & 31, W = f->world;
+  const size_t q_off = (size_t)q * 32 * 256;
+  const __nv_bfloat16* src0 = f->stage[f->rank] + (size_t)(mn / W) * TILE_ELEMS + q_off;
+  const size_t src_stride = (size_t)f->owned_cap * TILE_ELEMS;
+  const size_t dst_off = (size_t)mn * TILE_ELEMS + q_off;
+#pragma unroll 1
+  for (int it0 = 0; it0 < 32; it0 += 4) {
+    float acc[4][8];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[u][e] = 0.f;
+    // two ranks' slots in flight at a time (8 independent 16-byte loads per lane); the sums stay in rank order
+    for (int r = 0; r < W; r += 2) {
+      const bool two = r + 1 < W;
+      uint4 v[4], v2[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const size_t o = (size_t)((it0 + u) * 32 + lane) * 8;
+        v[u] = ld_cg_u4(src0 + (size_t)r * src_stride + o);
+        v2[u] = two ? ld_cg_u4(src0 + (size_t)(r + 1) * src_stride + o) : make_uint4(0u, 0u, 0u, 0u);
       }
-      __nanosleep(64);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const __nv_bfloat162* hv = reinterpret_cast<const __nv_bfloat162*>(&v[u]);
+        const __nv_bfloat162* hw = reinterpret_cast<const __nv_bfloat162*>(&v2[u]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 t2 = __bfloat1622float2(hv[e]);
+          acc[u][2 * e] += t2.x;
+          acc[u][2 * e + 1] += t2.y;
+        }
+        if (two) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 t2 = __bfloat1622float2(hw[e]);
+            acc[u][2 * e] += t2.x;
+            acc[u][2 * e + 1] += t2.y;
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      uint4 pk;
+      uint32_t* pw = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        __nv_bfloat162 h2 = __floats2bfloat162_rn(acc[u][2 * e], acc[u][2 * e + 1]);
+        pw[e] = *reinterpret_cast<uint32_t*>(&h2);
+      }
+      const size_t e0 = (size_t)((it0 + u) * 32 + lane) * 8;
+      for (int r = 0; r < W; ++r) *reinterpret_cast<uint4*>(f->result[r] + dst_off + e0) = pk;
     }
   }
-  return __all_sync(0xffffffffu, ok);
+  __threadfence_system();
+  __syncwarp();
+  if (lane < W) st_release_sys_u32(f->flags[lane] + (size_t)f->max_tiles * W * 4 + (size_t)mn * 4 + q, epoch);
+}
+
+// Phase 3 for one warp: resid rows of quarter q of tile mn += reduced tile (lane = 8-column group, 4 rows in flight).
+__device__ __forceinline__ void fuse_add_quarter(const FuseArgs* f, int mn, int q, int tiles_m, int M, int N) {
+  const int lane = threadIdx.x & 31;
+  const int tm = mn % tiles_m, tn = mn / tiles_m;
+  const __nv_bfloat16* res = f->result[f->rank] + (size_t)mn * TILE_ELEMS + (size_t)q * 32 * 256 + lane * 8;
+  const int col = tn * 256 + lane * 8;
+  const int row0 = tm * 128 + q * 32;
+  if (col >= N) return;
+  float* hbase = f->resid + (size_t)row0 * f->ld_resid + col;
+#pragma unroll 1
+  for (int rr = 0; rr < 32; rr += 8) {
+    if (row0 + rr >= M) break;
+    uint4 v[8];
+    float4 h0[8], h1[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      if (row0 + rr + u < M) {
+        v[u] = ld_cg_u4(res + (size_t)(rr + u) * 256);
+        const float4* hp = reinterpret_cast<const float4*>(hbase + (size_t)(rr + u) * f->ld_resid);
+        h0[u] = hp[0];
+        h1[u] = hp[1];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      if (row0 + rr + u < M) {
+        const __nv_bfloat162* hv = reinterpret_cast<const __nv_bfloat162*>(&v[u]);
+        const float2 a0 = __bfloat1622float2(hv[0]), a1 = __bfloat1622float2(hv[1]);
+        const float2 a2 = __bfloat1622float2(hv[2]), a3 = __bfloat1622float2(hv[3]);
+        h0[u].x += a0.x; h0[u].y += a0.y; h0[u].z += a1.x; h0[u].w += a1.y;
+        h1[u].x += a2.x; h1[u].y += a2.y; h1[u].z += a3.x; h1[u].w += a3.y;
+        float4* hp = reinterpret_cast<float4*>(hbase + (size_t)(rr + u) * f->ld_resid);
+        hp[0] = h0[u];
+        hp[1] = h1[u];
+      }
+    }
+  }
 }
 
 struct __align__(8) Barriers {
@@ -213,7 +306,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
         ++tcount;
       }
     }
-  } else {
+  } else if (warp < 6) {
     // ------------------------------------------------------------ epilogue (warps 2..5)
     const int q = warp & 3;              // TMEM lane quarter this warp may touch
     uint32_t tcount = 0;
@@ -313,75 +406,35 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
       }
       ++tcount;
     }
+  } else {
+    // ------------------------------------------------------------ collective warps 6..9 (fused kernel only)
+    // Warp 6+q reduces quarter q of the tiles this rank owns (phase 2) and adds quarter q of this CTA's share of
+    // all tiles into the residual (phase 3) while the other warps keep the tensor cores busy.  It takes whichever
+    // unit has its stamps, and gives up after wait_limit polls without progress.
     if constexpr (FUSE) {
+      const int q = warp - 6;
       const int tiles_mn = tiles_m * tiles_n;
       const int W = f->world;
-      bool alive = *abort_flag == 0;
+      int p2_next = (f->phases & 2) ? f->rank + (int)blockIdx.x * W : tiles_mn;
+      int p3_next = (f->phases & 4) ? (int)blockIdx.x : tiles_mn;
       uint32_t* my_flags = f->flags[f->rank];
       const size_t done_off = (size_t)f->max_tiles * W * 4;
-      // ---- phase 2: reduce the tiles this rank owns (quarter q of each), broadcast the result
-      if (f->phases & 2) {
-        for (int mn = f->rank + blockIdx.x * W; mn < tiles_mn && alive; mn += gridDim.x * W) {
-          alive = warp_wait_stamps(my_flags + (size_t)mn * W * 4 + q, W, 4, fuse_epoch, f->wait_limit, g.status);
-          if (!alive) break;
-          const size_t q_off = (size_t)q * 32 * BN;                    // this warp's 32 rows of the tile
-          const __nv_bfloat16* src0 = f->stage[f->rank] + (size_t)(mn / W) * TILE_ELEMS + q_off;
-          const size_t src_stride = (size_t)f->owned_cap * TILE_ELEMS;
-#pragma unroll 2
-          for (int it = 0; it < 32; ++it) {
-            const size_t e0 = (size_t)(it * 32 + lane) * 8;
-            float acc8[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) acc8[e] = 0.f;
-            for (int r = 0; r < W; ++r) {
-              const uint4 v = ld_cg_u4(src0 + (size_t)r * src_stride + e0);
-              const __nv_bfloat162* hv = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float2 t2 = __bfloat1622float2(hv[e]);
-                acc8[2 * e] += t2.x;
-                acc8[2 * e + 1] += t2.y;
-              }
-            }
-            uint4 pk;
-            uint32_t* pw = reinterpret_cast<uint32_t*>(&pk);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              __nv_bfloat162 h2 = __floats2bfloat162_rn(acc8[2 * e], acc8[2 * e + 1]);
-              pw[e] = *reinterpret_cast<uint32_t*>(&h2);
-            }
-            for (int r = 0; r < W; ++r)
-              *reinterpret_cast<uint4*>(f->result[r] + (size_t)mn * TILE_ELEMS + q_off + e0) = pk;
+      unsigned stall = 0;
+      while (p2_next < tiles_mn || p3_next < tiles_mn) {
+        if (p2_next < tiles_mn && warp_stamps_ready(my_flags + (size_t)p2_next * W * 4 + q, W, 4, fuse_epoch)) {
+          fuse_reduce_quarter(f, p2_next, q, fuse_epoch);
+          p2_next += gridDim.x * W;
+          stall = 0;
+        } else if (p3_next < tiles_mn && warp_stamps_ready(my_flags + done_off + (size_t)p3_next * 4 + q, 1, 1, fuse_epoch)) {
+          fuse_add_quarter(f, p3_next, q, tiles_m, g.M, g.N);
+          p3_next += gridDim.x;
+          stall = 0;
+        } else {
+          if (++stall > f->wait_limit || *abort_flag) {
+            if (lane == 0 && g.status != nullptr) atomicCAS(g.status, 0, HE_ERR_WAIT_TIMEOUT);
+            break;
           }
-          __threadfence_system();
-          __syncwarp();
-          if (lane < W) st_release_sys_u32(f->flags[lane] + done_off + (size_t)mn * 4 + q, fuse_epoch);
-        }
-      }
-      // ---- phase 3: resid += reduced tile (quarter q of every tile this CTA walks)
-      if (f->phases & 4) {
-        for (int mn = blockIdx.x; mn < tiles_mn && alive; mn += gridDim.x) {
-          alive = warp_wait_stamps(my_flags + done_off + (size_t)mn * 4 + q, 1, 1, fuse_epoch, f->wait_limit, g.status);
-          if (!alive) break;
-          const int tm = mn % tiles_m, tn = mn / tiles_m;
-          const __nv_bfloat16* res = f->result[f->rank] + (size_t)mn * TILE_ELEMS + (size_t)q * 32 * BN;
-          const int col = tn * BN + lane * 8;
-          if (col < g.N) {
-            for (int rr = 0; rr < 32; ++rr) {
-              const int row = tm * BM + q * 32 + rr;
-              if (row >= g.M) break;
-              const uint4 v = ld_cg_u4(res + (size_t)rr * BN + lane * 8);
-              const __nv_bfloat162* hv = reinterpret_cast<const __nv_bfloat162*>(&v);
-              float4* hp = reinterpret_cast<float4*>(f->resid + (size_t)row * f->ld_resid + col);
-              float4 h0 = hp[0], h1 = hp[1];
-              const float2 a0 = __bfloat1622float2(hv[0]), a1 = __bfloat1622float2(hv[1]);
-              const float2 a2 = __bfloat1622float2(hv[2]), a3 = __bfloat1622float2(hv[3]);
-              h0.x += a0.x; h0.y += a0.y; h0.z += a1.x; h0.w += a1.y;
-              h1.x += a2.x; h1.y += a2.y; h1.z += a3.x; h1.w += a3.y;
-              hp[0] = h0;
-              hp[1] = h1;
-            }
-          }
+          __nanosleep(128);
         }
       }
     }
@@ -413,7 +466,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   gemm_body<false>(tmA, tmB, g, nullptr);
 }
 
-__global__ void __launch_bounds__(NTHREADS, 1)
+__global__ void __launch_bounds__(NTHREADS_FUSED, 1)
 gemm_bf16_allreduce_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                            const GemmArgs g, const __grid_constant__ FuseArgs f) {
   gemm_body<true>(tmA, tmB, g, &f);
@@ -520,7 +573,7 @@ HE_API int he_gemm_bf16_allreduce(const void* A, long long lda, const void* B, l
   if (e != cudaSuccess) return (int)e;
   // every CTA must be resident at once (CTAs of one rank wait for tiles of CTAs on other ranks): one CTA per SM
   const int grid = tiles < num_sms ? tiles : num_sms;
-  gemm_bf16_allreduce_kernel<<<grid, NTHREADS, smem, stream>>>(tmA, tmB, g, f);
+  gemm_bf16_allreduce_kernel<<<grid, NTHREADS_FUSED, smem, stream>>>(tmA, tmB, g, f);
   HE_LAUNCH_CHECK();
   return 0;
 }

@@ -21,6 +21,8 @@ def main() -> int:
     ap.add_argument("--decode", type=int, default=6)
     ap.add_argument("--bench-width", type=int, default=5120)
     ap.add_argument("--bench-rows", type=int, default=4096)
+    ap.add_argument("--phase-breakdown", action="store_true",
+                    help="also time the fused GEMM kernel with only its first one / two phases enabled")
     args = ap.parse_args()
     from ..loading.synth import build_random_model
     from ..models.config import NAMED_CONFIGS
@@ -159,6 +161,15 @@ def main() -> int:
         K.check_status(dev)
         report["gemm_nccl_allreduce_us"] = round(time_it(baseline, iters=20), 1)
         report["fused_gemm_shape"] = [M, Nn, Kd]
+        if args.phase_breakdown:
+            # timing only (the epoch does not advance without the last phase, so later launches find the stamps of
+            # the first one and never wait; the sums they produce are not meaningful): GEMM + push, + reduce, all
+            scratch_h = torch.zeros(M, Nn, device=dev)
+            report["fused_gemm_phase_us"] = {
+                str(ph): round(time_it(lambda ph=ph: fg.gemm_add(x, wt, scratch_h, phases=ph), iters=20), 1)
+                for ph in (1, 3, 7)}
+            report["gemm_only_us"] = round(time_it(lambda: GM.gemm_bf16(x, wt, y), iters=20), 1)
+            K.check_status(dev)
         fg.close()
     if ctx.rank == 0:
         report["ok"] = ok
