@@ -76,27 +76,29 @@ def test_fused_gemm_allreduce_world_of_one(n):
         fg.close()
 
 
-def test_fused_gemm_allreduce_two_emulated_ranks():
-    """Two ranks emulated on one GPU: the phases of both ranks run as separate launches in an order in which no
-    launch waits for a later one (all phase 1, all phase 2, all phase 3); each rank holds half of K."""
+@pytest.mark.parametrize("world", [2, 4])
+def test_fused_gemm_allreduce_emulated_ranks(world):
+    """Several ranks emulated on one GPU: the phases of both ranks run as separate launches in an order in which no
+    launch waits for a later one (all phase 1, all phase 2, all phase 3); each rank holds a slice of K."""
     from hipengine_b200.ops import kernels as K
     from hipengine_b200.parallel.fused import FusedGemmAllReduce
-    ranks = FusedGemmAllReduce.emulated_group("cuda", width=768, world=2, max_rows=512)
+    ranks = FusedGemmAllReduce.emulated_group("cuda", width=768, world=world, max_rows=512)
     try:
         g = torch.Generator(device="cuda").manual_seed(5)
-        ws = [(torch.randn(768, 256, device="cuda", generator=g) * 0.05).bfloat16() for _ in range(2)]
+        ws = [(torch.randn(768, 256, device="cuda", generator=g) * 0.05).bfloat16() for _ in range(world)]
         for rows in (200, 512):
-            xs = [torch.randn(rows, 256, device="cuda", generator=g).bfloat16() for _ in range(2)]
+            xs = [torch.randn(rows, 256, device="cuda", generator=g).bfloat16() for _ in range(world)]
             h0 = torch.randn(rows, 768, device="cuda", generator=g)
-            hs = [h0.clone(), h0.clone()]
+            hs = [h0.clone() for _ in range(world)]
             want = _ref_add(h0, xs, ws)
             for phase in (1, 2, 4):
-                for r in range(2):
+                for r in range(world):
                     ranks[r].gemm_add(xs[r], ws[r], hs[r], phases=phase)
             torch.cuda.synchronize()
             K.check_status("cuda")
-            torch.testing.assert_close(hs[0], want, rtol=2e-2, atol=2e-2)
-            assert torch.equal(hs[0], hs[1])               # replicated residual streams stay bit-identical
+            torch.testing.assert_close(hs[0], want, rtol=2e-2, atol=3e-2)
+            for r in range(1, world):                      # replicated residual streams stay bit-identical
+                assert torch.equal(hs[0], hs[r])
     finally:
         for r in ranks[1:]:
             r.close()
