@@ -340,9 +340,11 @@ class HybridExecutor:
             z = sc.get("z_f32", (T, inner), torch.float32)
             if i in self.ab_q8:
                 ab = sc.get("ab_proj", (T, 2 * Hv), torch.float32)
-                if os.environ.get("HE_AB_SPLIT", "1") != "0":
+                ab_split = os.environ.get("HE_AB_SPLIT", "1" if cfg.hidden >= 4096 else "0")
+                if ab_split != "0":
                     # the 2*Hv Q8_0 rows get their own (tiny) launch: in the same launch their 272-byte blocks
-                    # would size every ring slot and halve the warps of the two big Q4_K projections
+                    # would size every ring slot and halve the warps of the two big Q4_K projections (for narrow
+                    # models the projections are so short that the extra launch costs more than it saves)
                     K.gemv(h, [GemvSegment(self.W(i, "attn_qkv.weight"), qkv),
                                GemvSegment(self.W(i, "attn_gate.weight"), z)],
                            norm_w=self.F(i, "attn_norm.weight"), eps=cfg.rms_eps)
