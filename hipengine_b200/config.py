@@ -56,7 +56,7 @@ class KVConfig:
 
 @dataclass(frozen=True)
 class SpeculativeConfig:
-    mode: str = "off"                       # off | mtp
+    mode: str = "off"                       # off | mtp | prompt_lookup | ngram (``speculative/providers.py``)
     draft_depth: int = 3
     adaptive_depth: bool = False
 

@@ -127,7 +127,7 @@ class EngineLoop:
         rows = self.sched.next_decode_work(self.config.scheduler.round_decode_row_budget)
         if not rows:
             return 0
-        if (self.config.speculative.mode == "mtp" and self.runner.supports_mtp
+        if (self.config.speculative.mode not in ("off", "", None) and self.runner.supports_mtp
                 and hasattr(self.runner, "speculative_cycle")):
             spec_rows = [rs for rs in rows if self.runner.speculative_eligible(rs)]
             if spec_rows and len(spec_rows) == len(rows):

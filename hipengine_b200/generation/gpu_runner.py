@@ -69,13 +69,17 @@ class GpuRunner(BaseRunner):
         self.resident_key: Tuple[int, ...] = ()
         self.pinned_ids = torch.zeros(max(self.max_slots, 8), dtype=torch.int64).pin_memory()
         self.stats = {"prefix_hits": 0, "prefix_hit_tokens": 0, "snapshots_taken": 0, "h2d_bytes": 0, "d2h_bytes": 0}
-        # MTP: the checkpoint's own NextN block drafts, the target verifies (``speculative/mtp.py``)
+        # Speculative decoding: a provider drafts (the checkpoint's own NextN block, ``speculative/mtp.py``, or a
+        # host drafter over the token history, ``speculative/providers.py``), the target verifies the chain
         self.mtp = None
-        if config.speculative.mode == "mtp" and self.ex.has_nextn:
-            from ..speculative.mtp import MTPCycle
-            self.mtp = MTPCycle(self.ex, max_depth=max(1, config.speculative.draft_depth),
-                                max_requests=min(self.max_slots, 8))
+        if config.speculative.mode not in ("off", "", None):
+            from ..speculative.providers import SpeculativeProviderConfig, build_speculative_provider
+            self.mtp = build_speculative_provider(
+                self.ex, SpeculativeProviderConfig(name=config.speculative.mode,
+                                                   max_depth=max(1, config.speculative.draft_depth)),
+                max_requests=min(self.max_slots, 8))
         self.supports_mtp = self.mtp is not None
+        self.spec_uses_history = self.mtp is not None and hasattr(self.mtp, "drafter")
 
     # ------------------------------------------------------------------ snapshots
     def _free_snapshot(self, sid: int) -> None:
@@ -301,13 +305,23 @@ class GpuRunner(BaseRunner):
             return [SpecCycleResult([t], 0, 0) for t, _ in self.decode(rows)]
         for rs in rows:
             self._ensure_pages(rs, rs.position + depth)
+        kw = {}
+        if self.spec_uses_history:
+            kw["histories"] = [list(rs.req.prompt_token_ids) + rs.generated for rs in rows]
         try:
-            res, _txn = self.mtp.cycle([rs.slot for rs in rows], [rs.last_token for rs in rows],
-                                       [rs.position - 1 for rs in rows], depth,
-                                       [rs.req.temperature for rs in rows], [rs.seed for rs in rows],
-                                       [rs.sample_counter for rs in rows])
+            got = self.mtp.cycle([rs.slot for rs in rows], [rs.last_token for rs in rows],
+                                 [rs.position - 1 for rs in rows], depth,
+                                 [rs.req.temperature for rs in rows], [rs.seed for rs in rows],
+                                 [rs.sample_counter for rs in rows], **kw)
         except torch.cuda.OutOfMemoryError as exc:
             raise ExecutionFailure([rs.rid for rs in rows], "verify", f"out of memory: {exc}", "partial") from exc
+        if got is None:                 # the drafter had nothing to propose: plain decode step
+            return [SpecCycleResult([t], 0, 0) for t, _ in self.decode(rows)]
+        res, _txn = got
+        if self.spec_uses_history:
+            depth = res[0].drafted
+            for rs, c in zip(rows, res):
+                self.mtp.drafter.observe(list(rs.req.prompt_token_ids) + rs.generated + list(c.tokens))
         for rs, c in zip(rows, res):
             rs.sample_counter += 2 * (depth + 1)
             rs.telemetry.d2h_bytes += 8 * (depth + 2)

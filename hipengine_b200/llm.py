@@ -112,6 +112,7 @@ class LLM:
                  execution_profile: Any = None, max_active_requests: int = 8,
                  max_sequence_length: Optional[int] = None, prefix_cache: str = "radix",
                  speculative_mtp_serving: str = "off", speculative_candidate_budget: int = 3,
+                 speculative_provider: str = "mtp",
                  kv_storage: str = "bf16", tensor_parallel: int = 1, expert_parallel: int = 1,
                  engine_command_timeout_seconds: float = 300.0, seed: int = 0, tokenizer: Any = None,
                  engine_config: Optional[EngineConfig] = None, device: Optional[str] = None,
@@ -126,7 +127,8 @@ class LLM:
             profile=self.profile,
             scheduler=replace(base.scheduler, max_active_requests=int(max_active_requests)),
             kv=replace(base.kv, storage=kv_storage, prefix_cache=prefix_cache),
-            speculative=replace(base.speculative, mode="mtp" if speculative_mtp_serving not in ("off", None) else "off",
+            speculative=replace(base.speculative,
+                                mode=speculative_provider if speculative_mtp_serving not in ("off", None) else "off",
                                 draft_depth=int(speculative_candidate_budget)),
             parallel=replace(base.parallel, tp=int(tensor_parallel), ep=int(expert_parallel)),
             command_timeout_seconds=float(engine_command_timeout_seconds),

@@ -23,85 +23,44 @@ from .contracts import SpecCycleResult
 from .transaction import SpecTransaction, Stage
 
 
-class MTPCycle:
+class ChainVerifyCycle:
+    """Verify / accept / commit for chains of drafted tokens, whatever proposed them (the NextN block below, or a
+    host-side drafter such as prompt lookup, ``speculative/providers.py``).  Holds the journal and the small device
+    buffers of the accept and commit kernels."""
+
     def __init__(self, ex, max_depth: int = 3, max_requests: int = 8):
-        assert ex.has_nextn, "checkpoint has no NextN block"
         self.ex = ex
         self.max_depth = max_depth
         self.max_requests = max_requests
-        dev, H = ex.device, ex.cfg.hidden
+        dev = ex.device
         self.max_rows = max_requests * (max_depth + 1)
         self.journal = None                       # allocated on first use (large)
-        self.h_prev = torch.zeros(ex.max_slots, H, dtype=torch.float32, device=dev)   # post-norm hidden per slot
         self.n_accept = torch.zeros(max_requests, dtype=torch.int32, device=dev)
         self.commit_row = torch.zeros(max_requests, dtype=torch.int32, device=dev)
         self.hidden_row = torch.zeros(max_requests, dtype=torch.int32, device=dev)
         self.am_ids = torch.zeros(self.max_rows, dtype=torch.int64, device=dev)
         self.stats = {"cycles": 0, "drafted": 0, "accepted": 0}
 
-    # ------------------------------------------------------------------ prompt side
+    # hooks of drafters that keep device state per slot (the NextN block does)
     def reset_slot(self, slot: int) -> None:
-        self.h_prev[slot].zero_()
+        pass
 
     def after_prefill(self, batch: BatchDesc, h: torch.Tensor) -> None:
-        """Feed the prompt rows of ``batch`` through the NextN block so its KV covers the prompt, and keep the
-        last post-norm hidden of every segment.  ``h`` is the target's residual output for the batch rows."""
-        ex, cfg = self.ex, self.ex.cfg
-        T = batch.T
-        hid = ex.scratch.get("mtp_hid", (T, cfg.hidden), torch.float32)
-        K.rmsnorm_rows(h, ex.f32["output_norm.weight"], hid, cfg.rms_eps)
-        hprev = ex.scratch.get("mtp_hprev", (T, cfg.hidden), torch.float32)
-        r0 = 0
-        for (slot, pos0, n) in batch.segs_host:
-            hprev[r0].copy_(self.h_prev[slot])
-            if n > 1:
-                hprev[r0 + 1:r0 + n].copy_(hid[r0:r0 + n - 1])
-            self.h_prev[slot].copy_(hid[r0 + n - 1])
-            r0 += n
-        ex.nextn_forward(batch, hprev)
+        pass
 
-    # ------------------------------------------------------------------ one cycle
-    @torch.no_grad()
-    def cycle(self, slots: Sequence[int], last_tokens: Sequence[int], positions: Sequence[int], depth: int,
-              temperature: Optional[Sequence[float]] = None, seeds: Optional[Sequence[int]] = None,
-              counters: Optional[Sequence[int]] = None, draft_override: Optional[torch.Tensor] = None
-              ) -> Tuple[List[SpecCycleResult], SpecTransaction]:
-        """positions[r] = position of last_tokens[r].  temperature None/0 -> greedy verification.
-        ``draft_override`` (int64 [R, depth]) replaces the NextN proposals after they are computed (the block
-        still runs, so its KV stays in step); used to test acceptance paths with known chains."""
+    def _after_commit(self, slot_t: torch.Tensor, hid: torch.Tensor, R: int) -> None:
+        pass
+
+    def _verify_accept_commit(self, txn: SpecTransaction, slots, positions, t0: torch.Tensor, drafts: torch.Tensor,
+                              temperature, seeds, counters) -> List[SpecCycleResult]:
+        """Target forward over R chains [t0, d1..dK] with journalled recurrent state, device accept, one host
+        read-back, commit by journal copy.  ``txn`` must be in stage DRAFTED."""
         ex, cfg, dev = self.ex, self.ex.cfg, self.ex.device
-        R, Kd = len(slots), depth
-        assert 1 <= Kd <= self.max_depth and R <= self.max_requests
-        txn = SpecTransaction(list(range(R)))
-        txn.advance(Stage.RESERVED)
+        R, Kd = drafts.shape
         if self.journal is None:
             self.journal = ex.alloc_journal(self.max_rows)
         sampled = temperature is not None and any(t > 0 for t in temperature)
         slot_t = torch.tensor(list(slots), dtype=torch.int64, device=dev)
-        t0 = torch.tensor(list(last_tokens), dtype=torch.int64, device=dev)
-        drafts = torch.empty(R, Kd, dtype=torch.int64, device=dev)
-        txn.advance(Stage.TARGET_OPEN)
-        # ---- draft: K passes of the NextN block, R rows each
-        txn.advance(Stage.PROVIDER_OPEN)
-        cur = t0
-        hprev = self.h_prev.index_select(0, slot_t)
-        hid_next = ex.scratch.get("mtp_hid_next", (R, cfg.hidden), torch.float32)
-        ids = self.am_ids[:R]
-        for j in range(Kd):
-            b = make_batch([(s, p + j, [0]) for s, p in zip(slots, positions)], dev)
-            b.tokens = cur
-            h = ex.nextn_forward(b, hprev)
-            lg = ex.nextn_logits(h, hidden_out=hid_next)
-            for r0 in range(0, R, GEMV_MAX_ROWS):
-                r1 = min(R, r0 + GEMV_MAX_ROWS)
-                ex.greedy(lg[r0:r1], ids[r0:r1])
-            drafts[:, j].copy_(ids)
-            cur = drafts[:, j].contiguous()
-            hprev = hid_next.clone()
-        if draft_override is not None:
-            drafts.copy_(draft_override.to(dev))
-        txn.advance(Stage.DRAFTED)
-        # ---- verify: one target forward over R chains of K+1 rows, recurrent state journalled per row
         T = R * (Kd + 1)
         vb = make_batch([(s, p, [0] * (Kd + 1)) for s, p in zip(slots, positions)], dev)
         vb.tokens = torch.cat([t0[:, None], drafts], 1).reshape(-1).contiguous()
@@ -146,9 +105,7 @@ class MTPCycle:
         tok_t = torch.empty(R, dtype=torch.int64, device=dev)
         K.spec_commit(self.n_accept[:R], out, tok_t, pos_t, None, self.commit_row[:R], self.hidden_row[:R])
         ex.commit_journal(journal, vb.seg_slot, self.commit_row[:R])
-        picked = ex.scratch.get("mtp_pick", (R, cfg.hidden), torch.float32)
-        K.gather_rows_f32(hid, self.hidden_row[:R], picked)
-        self.h_prev.index_copy_(0, slot_t, picked)
+        self._after_commit(slot_t, hid, R)
         txn.advance(Stage.COMMITTED)
         res = []
         for r in range(R):
@@ -157,4 +114,98 @@ class MTPCycle:
             self.stats["drafted"] += Kd
             self.stats["accepted"] += n
         self.stats["cycles"] += 1
+        return res
+
+    @torch.no_grad()
+    def cycle_with_drafts(self, slots: Sequence[int], last_tokens: Sequence[int], positions: Sequence[int],
+                          drafts: Sequence[Sequence[int]], temperature: Optional[Sequence[float]] = None,
+                          seeds: Optional[Sequence[int]] = None, counters: Optional[Sequence[int]] = None
+                          ) -> Tuple[List[SpecCycleResult], SpecTransaction]:
+        """One cycle whose chains come from the host: ``drafts[r]`` are the K tokens proposed after
+        ``last_tokens[r]`` (all rows the same K).  A deterministic drafter is a one-hot proposal distribution, so
+        the sampled rule accepts token d with probability p(d) and resamples from p with d removed."""
+        dev = self.ex.device
+        R, Kd = len(slots), len(drafts[0])
+        assert 1 <= Kd <= self.max_depth and R <= self.max_requests and all(len(d) == Kd for d in drafts)
+        txn = SpecTransaction(list(range(R)))
+        txn.advance(Stage.RESERVED)
+        txn.advance(Stage.TARGET_OPEN)
+        txn.advance(Stage.PROVIDER_OPEN)
+        t0 = torch.tensor(list(last_tokens), dtype=torch.int64, device=dev)
+        d = torch.tensor([list(x) for x in drafts], dtype=torch.int64, device=dev)
+        txn.advance(Stage.DRAFTED)
+        return self._verify_accept_commit(txn, slots, positions, t0, d, temperature, seeds, counters), txn
+
+
+class MTPCycle(ChainVerifyCycle):
+    def __init__(self, ex, max_depth: int = 3, max_requests: int = 8):
+        assert ex.has_nextn, "checkpoint has no NextN block"
+        super().__init__(ex, max_depth, max_requests)
+        self.h_prev = torch.zeros(ex.max_slots, ex.cfg.hidden, dtype=torch.float32, device=ex.device)  # per slot
+
+    def _after_commit(self, slot_t: torch.Tensor, hid: torch.Tensor, R: int) -> None:
+        picked = self.ex.scratch.get("mtp_pick", (R, self.ex.cfg.hidden), torch.float32)
+        K.gather_rows_f32(hid, self.hidden_row[:R], picked)
+        self.h_prev.index_copy_(0, slot_t, picked)
+
+    # ------------------------------------------------------------------ prompt side
+    def reset_slot(self, slot: int) -> None:
+        self.h_prev[slot].zero_()
+
+    def after_prefill(self, batch: BatchDesc, h: torch.Tensor) -> None:
+        """Feed the prompt rows of ``batch`` through the NextN block so its KV covers the prompt, and keep the
+        last post-norm hidden of every segment.  ``h`` is the target's residual output for the batch rows."""
+        ex, cfg = self.ex, self.ex.cfg
+        T = batch.T
+        hid = ex.scratch.get("mtp_hid", (T, cfg.hidden), torch.float32)
+        K.rmsnorm_rows(h, ex.f32["output_norm.weight"], hid, cfg.rms_eps)
+        hprev = ex.scratch.get("mtp_hprev", (T, cfg.hidden), torch.float32)
+        r0 = 0
+        for (slot, pos0, n) in batch.segs_host:
+            hprev[r0].copy_(self.h_prev[slot])
+            if n > 1:
+                hprev[r0 + 1:r0 + n].copy_(hid[r0:r0 + n - 1])
+            self.h_prev[slot].copy_(hid[r0 + n - 1])
+            r0 += n
+        ex.nextn_forward(batch, hprev)
+
+    # ------------------------------------------------------------------ one cycle
+    @torch.no_grad()
+    def cycle(self, slots: Sequence[int], last_tokens: Sequence[int], positions: Sequence[int], depth: int,
+              temperature: Optional[Sequence[float]] = None, seeds: Optional[Sequence[int]] = None,
+              counters: Optional[Sequence[int]] = None, draft_override: Optional[torch.Tensor] = None
+              ) -> Tuple[List[SpecCycleResult], SpecTransaction]:
+        """positions[r] = position of last_tokens[r].  temperature None/0 -> greedy verification.
+        ``draft_override`` (int64 [R, depth]) replaces the NextN proposals after they are computed (the block
+        still runs, so its KV stays in step); used to test acceptance paths with known chains."""
+        ex, cfg, dev = self.ex, self.ex.cfg, self.ex.device
+        R, Kd = len(slots), depth
+        assert 1 <= Kd <= self.max_depth and R <= self.max_requests
+        txn = SpecTransaction(list(range(R)))
+        txn.advance(Stage.RESERVED)
+        slot_t = torch.tensor(list(slots), dtype=torch.int64, device=dev)
+        t0 = torch.tensor(list(last_tokens), dtype=torch.int64, device=dev)
+        drafts = torch.empty(R, Kd, dtype=torch.int64, device=dev)
+        txn.advance(Stage.TARGET_OPEN)
+        # ---- draft: K passes of the NextN block, R rows each
+        txn.advance(Stage.PROVIDER_OPEN)
+        cur = t0
+        hprev = self.h_prev.index_select(0, slot_t)
+        hid_next = ex.scratch.get("mtp_hid_next", (R, cfg.hidden), torch.float32)
+        ids = self.am_ids[:R]
+        for j in range(Kd):
+            b = make_batch([(s, p + j, [0]) for s, p in zip(slots, positions)], dev)
+            b.tokens = cur
+            h = ex.nextn_forward(b, hprev)
+            lg = ex.nextn_logits(h, hidden_out=hid_next)
+            for r0 in range(0, R, GEMV_MAX_ROWS):
+                r1 = min(R, r0 + GEMV_MAX_ROWS)
+                ex.greedy(lg[r0:r1], ids[r0:r1])
+            drafts[:, j].copy_(ids)
+            cur = drafts[:, j].contiguous()
+            hprev = hid_next.clone()
+        if draft_override is not None:
+            drafts.copy_(draft_override.to(dev))
+        txn.advance(Stage.DRAFTED)
+        res = self._verify_accept_commit(txn, slots, positions, t0, drafts, temperature, seeds, counters)
         return res, txn

@@ -135,3 +135,60 @@ def test_mtp_cycle_reproduces_greedy_decode(mode):
     assert got[:n_new] == want, (got, want)
     if mode == "all_accepted":
         assert accepted_total >= 9
+
+
+def test_lookup_cycle_with_known_chains_needs_no_nextn_block():
+    """Chain verify with host-supplied drafts on a checkpoint WITHOUT a NextN block: the true greedy continuation is
+    accepted in full (plus the bonus token), a corrupted chain is cut at the first wrong token, and the committed
+    sequence equals plain greedy decode either way."""
+    from hipengine_b200.models.executor import HybridExecutor, make_batch
+    from hipengine_b200.speculative.mtp import ChainVerifyCycle
+    w = build_random_model(TINY_HYBRID, seed=0, std=0.05).to("cuda")
+    prompt = _prompt(24, seed=9)
+    n_new = 14
+    want = _greedy_reference_tokens(w, prompt, n_new)
+    ex = HybridExecutor(w, max_slots=1, max_context=256)
+    cyc = ChainVerifyCycle(ex, max_depth=3, max_requests=1)
+    b = make_batch([(0, 0, prompt)], "cuda")
+    h = ex.forward(b)
+    got = [int(ex.logits(h[b.T - 1:b.T]).argmax(-1))]
+    step = 0
+    while len(got) < n_new:
+        nxt = want[len(got):len(got) + 3]
+        nxt = nxt + [0] * (3 - len(nxt))
+        corrupt = step % 2 == 1
+        if corrupt:
+            nxt[0] = (nxt[0] + 1) % TINY_HYBRID.vocab
+        res, txn = cyc.cycle_with_drafts([0], [got[-1]], [len(prompt) + len(got) - 1], [nxt])
+        assert txn.trace[-1] == "committed"
+        if len(got) + 4 < n_new:
+            assert res[0].accepted == (0 if corrupt else 3)
+        got += res[0].tokens
+        step += 1
+    assert got[:n_new] == want
+
+
+@pytest.mark.parametrize("provider", ["prompt_lookup", "ngram"])
+def test_lookup_provider_serving_matches_plain_greedy(provider):
+    """The engine with a host drafter must emit exactly the tokens of the plain engine.  The n-gram provider is
+    seeded with the true continuation (as if another request had produced it), so its chains are accepted."""
+    from hipengine_b200 import LLM, SamplingParams
+    w = build_random_model(TINY_HYBRID, seed=0, std=0.05).to("cuda")
+    prompt = _prompt(12, seed=11) * 4
+    sp = SamplingParams(max_tokens=20, ignore_eos=True)
+    plain = LLM(w, backend="cuda_sm100a", max_active_requests=2, max_sequence_length=256, prefix_cache="off")
+    want = plain.generate_token_ids([prompt], sp)[0]
+    plain.close()
+    spec = LLM(w, backend="cuda_sm100a", max_active_requests=2, max_sequence_length=256, prefix_cache="off",
+               speculative_mtp_serving="on", speculative_provider=provider)
+    cyc = spec._get_engine().loop.runner.mtp
+    if provider == "ngram":
+        cyc.drafter.span = 32
+        cyc.drafter.observe(prompt + want)
+    got = spec.generate_token_ids([prompt], sp)[0]
+    stats = dict(cyc.stats)
+    spec.close()
+    assert got == want
+    assert stats["cycles"] + stats["skipped_cycles"] >= 1          # the drafter was consulted
+    if provider == "ngram":
+        assert stats["accepted"] >= 6, stats

@@ -78,3 +78,31 @@ def test_planner_and_serving_rules():
     assert resolve_mtp_serving_plan("on", False, 0.0, False, False, False).reason == "no_nextn_block"
     assert resolve_mtp_serving_plan("on", True, 0.0, True, False, False).reason == "sampler_not_reproducible"
     assert resolve_mtp_serving_plan("auto", True, 0.0, False, False, False, breaker_open=True).reason == "circuit_open"
+
+
+def test_prompt_lookup_and_ngram_drafters_and_registry():
+    from hipengine_b200.speculative.providers import (NGramCacheDrafter, PromptLookupDrafter,
+                                                      SpeculativeProviderConfig, build_speculative_provider,
+                                                      register_builtin_speculative_providers,
+                                                      speculative_provider_names)
+    d = PromptLookupDrafter(min_ngram=2, max_ngram=3)
+    hist = [5, 6, 7, 8, 9, 1, 2, 6, 7, 8]
+    assert d.propose(hist, 3) == [9, 1, 2]              # "6 7 8" seen before, followed by 9 1 2
+    assert d.propose([1, 2, 3, 4], 3) == []             # nothing repeats
+    assert d.propose([4, 4, 4, 4], 2) == [4]            # most recent earlier match, continuation clipped by the end
+    hist2 = [1, 2, 3, 9, 1, 2, 3, 7, 1, 2, 3]
+    assert d.propose(hist2, 1) == [7]                   # the latest occurrence wins over the first
+    g = NGramCacheDrafter(min_ngram=2, max_ngram=2, table_entries=4)
+    g.observe([10, 11, 12, 13, 14])
+    assert g.propose([99, 10, 11], 2) == [12, 13]       # learnt from another request
+    g.observe(list(range(100, 140)))
+    assert len(g.table) <= 4                            # bounded
+    assert register_builtin_speculative_providers() == ["mtp", "ngram", "prompt_lookup"]
+    assert "prompt_lookup" in speculative_provider_names()
+
+    class _NoNextN:
+        has_nextn = False
+    assert build_speculative_provider(_NoNextN(), SpeculativeProviderConfig(name="mtp")) is None
+    import pytest
+    with pytest.raises(ValueError):
+        build_speculative_provider(_NoNextN(), SpeculativeProviderConfig(name="eagle"))
