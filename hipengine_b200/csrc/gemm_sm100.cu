@@ -71,6 +71,13 @@ struct FuseArgs {
   long long ld_resid;
   int world, rank, max_tiles, owned_cap, phases;
   unsigned wait_limit;
+  // 1: one-hop form for small worlds.  Every rank stores its partial tiles into ALL ranks' stage buffers
+  // (stage [2 epoch parities][world src][max_tiles][BM*BN], owned_cap = max_tiles) and every rank reduces every tile
+  // itself, straight into its residual: (world-1) x the link traffic of the owner form at world > 2, the same at
+  // world = 2, but one flag hop instead of two and no result buffer.  Two parities because a rank may be one call
+  // ahead of a peer that still reads the previous call's tiles.
+  int direct;
+  int reserved;
 };
 
 __device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
@@ -86,6 +93,11 @@ __device__ __forceinline__ uint4 ld_cg_u4(const void* p) {
   asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
   return v;
 }
+// resid[0..3] += v, no return value: the add happens at the L2, so the adder never waits for the old value
+__device__ __forceinline__ void red_add_f32x4(float* p, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
 // Whole-warp probe: true when the n stamps p[lane * stride] (lanes < n) have all reached `epoch` (stamps only grow).
 __device__ __forceinline__ bool warp_stamps_ready(const uint32_t* p, int n, int stride, uint32_t epoch) {
   const int lane = threadIdx.x & 31;
@@ -157,7 +169,7 @@ __device__ __forceinline__ void fuse_reduce_quarter(const FuseArgs* f, int mn, i
   if (lane < W) st_release_sys_u32(f->flags[lane] + (size_t)f->max_tiles * W * 4 + (size_t)mn * 4 + q, epoch);
 }
 
-// Phase 3 for one warp: resid rows of quarter q of tile mn += reduced tile (lane = 8-column group, 4 rows in flight).
+// Phase 3 for one warp: resid rows of quarter q of tile mn += reduced tile (lane = 8-column group, 16 rows in flight, vector red.add).
 __device__ __forceinline__ void fuse_add_quarter(const FuseArgs* f, int mn, int q, int tiles_m, int M, int N) {
   const int lane = threadIdx.x & 31;
   const int tm = mn % tiles_m, tn = mn / tiles_m;
@@ -167,30 +179,74 @@ __device__ __forceinline__ void fuse_add_quarter(const FuseArgs* f, int mn, int 
   if (col >= N) return;
   float* hbase = f->resid + (size_t)row0 * f->ld_resid + col;
 #pragma unroll 1
+  for (int rr = 0; rr < 32; rr += 16) {
+    if (row0 + rr >= M) break;
+    uint4 v[16];
+#pragma unroll
+    for (int u = 0; u < 16; ++u)
+      v[u] = (row0 + rr + u < M) ? ld_cg_u4(res + (size_t)(rr + u) * 256) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+    for (int u = 0; u < 16; ++u) {
+      if (row0 + rr + u < M) {
+        const __nv_bfloat162* hv = reinterpret_cast<const __nv_bfloat162*>(&v[u]);
+        const float2 a0 = __bfloat1622float2(hv[0]), a1 = __bfloat1622float2(hv[1]);
+        const float2 a2 = __bfloat1622float2(hv[2]), a3 = __bfloat1622float2(hv[3]);
+        float* hp = hbase + (size_t)(rr + u) * f->ld_resid;
+        red_add_f32x4(hp, a0.x, a0.y, a1.x, a1.y);
+        red_add_f32x4(hp + 4, a2.x, a2.y, a3.x, a3.y);
+      }
+    }
+  }
+}
+
+// One-hop form, one warp: resid rows of quarter q of tile mn += bf16(sum over ranks of the stage slots), ranks in
+// order (lane = 8-column group, 16 rows in flight, vector red.add).
+__device__ __forceinline__ void fuse_direct_quarter(const FuseArgs* f, int mn, int q, int tiles_m, int M, int N,
+                                                    uint32_t epoch) {
+  const int lane = threadIdx.x & 31, W = f->world;
+  const int tm = mn % tiles_m, tn = mn / tiles_m;
+  const size_t slot_stride = (size_t)f->owned_cap * TILE_ELEMS;
+  const __nv_bfloat16* src = f->stage[f->rank] + (size_t)(epoch & 1u) * W * slot_stride + (size_t)mn * TILE_ELEMS +
+                             (size_t)q * 32 * 256 + lane * 8;
+  const int col = tn * 256 + lane * 8;
+  const int row0 = tm * 128 + q * 32;
+  if (col >= N) return;
+  float* hbase = f->resid + (size_t)row0 * f->ld_resid + col;
+#pragma unroll 1
   for (int rr = 0; rr < 32; rr += 8) {
     if (row0 + rr >= M) break;
-    uint4 v[8];
-    float4 h0[8], h1[8];
+    float acc[8][8];
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      if (row0 + rr + u < M) {
-        v[u] = ld_cg_u4(res + (size_t)(rr + u) * 256);
-        const float4* hp = reinterpret_cast<const float4*>(hbase + (size_t)(rr + u) * f->ld_resid);
-        h0[u] = hp[0];
-        h1[u] = hp[1];
+    for (int u = 0; u < 8; ++u)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[u][e] = 0.f;
+    for (int r = 0; r < W; ++r) {
+      uint4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        v[u] = (row0 + rr + u < M) ? ld_cg_u4(src + (size_t)r * slot_stride + (size_t)(rr + u) * 256)
+                                   : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const __nv_bfloat162* hv = reinterpret_cast<const __nv_bfloat162*>(&v[u]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 t2 = __bfloat1622float2(hv[e]);
+          acc[u][2 * e] += t2.x;
+          acc[u][2 * e + 1] += t2.y;
+        }
       }
     }
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
       if (row0 + rr + u < M) {
-        const __nv_bfloat162* hv = reinterpret_cast<const __nv_bfloat162*>(&v[u]);
-        const float2 a0 = __bfloat1622float2(hv[0]), a1 = __bfloat1622float2(hv[1]);
-        const float2 a2 = __bfloat1622float2(hv[2]), a3 = __bfloat1622float2(hv[3]);
-        h0[u].x += a0.x; h0[u].y += a0.y; h0[u].z += a1.x; h0[u].w += a1.y;
-        h1[u].x += a2.x; h1[u].y += a2.y; h1[u].z += a3.x; h1[u].w += a3.y;
-        float4* hp = reinterpret_cast<float4*>(hbase + (size_t)(rr + u) * f->ld_resid);
-        hp[0] = h0[u];
-        hp[1] = h1[u];
+        // round the sum to bf16 first: the same value the owner form broadcasts, so both forms agree bit for bit
+        float s8[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) s8[e] = __bfloat162float(__float2bfloat16_rn(acc[u][e]));
+        float* hp = hbase + (size_t)(rr + u) * f->ld_resid;
+        red_add_f32x4(hp, s8[0], s8[1], s8[2], s8[3]);
+        red_add_f32x4(hp + 4, s8[4], s8[5], s8[6], s8[7]);
       }
     }
   }
@@ -331,20 +387,31 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
         if constexpr (FUSE) {
           // partial quarter -> the owner's stage slot; rows and columns past M / N are zeros (zero-filled operand
           // tiles), so the whole tile is stored and no bound is needed
-          const int owner = mn % f->world, oi = mn / f->world;
-          __nv_bfloat16* dst = f->stage[owner] + ((size_t)f->rank * f->owned_cap + oi) * TILE_ELEMS +
-                               (size_t)(q * 32 + lane) * BN + c * 32;
+          uint4 pk[4];
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
-            uint4 pk;
-            uint32_t* pw = reinterpret_cast<uint32_t*>(&pk);
+            uint32_t* pw = reinterpret_cast<uint32_t*>(&pk[v]);
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * e]),
                                                         __uint_as_float(r[v * 8 + 2 * e + 1]));
               pw[e] = *reinterpret_cast<uint32_t*>(&h2);
             }
-            *reinterpret_cast<uint4*>(dst + v * 8) = pk;
+          }
+          const size_t in_tile = (size_t)(q * 32 + lane) * BN + c * 32;
+          if (f->direct) {
+            const size_t off = (((size_t)(fuse_epoch & 1u) * f->world + f->rank) * f->owned_cap + mn) * TILE_ELEMS +
+                               in_tile;
+            for (int pr = 0; pr < f->world; ++pr) {
+              __nv_bfloat16* dst = f->stage[pr] + off;
+#pragma unroll
+              for (int v = 0; v < 4; ++v) *reinterpret_cast<uint4*>(dst + v * 8) = pk[v];
+            }
+          } else {
+            const int owner = mn % f->world, oi = mn / f->world;
+            __nv_bfloat16* dst = f->stage[owner] + ((size_t)f->rank * f->owned_cap + oi) * TILE_ELEMS + in_tile;
+#pragma unroll
+            for (int v = 0; v < 4; ++v) *reinterpret_cast<uint4*>(dst + v * 8) = pk[v];
           }
         } else
         if (row < g.M && col0 < g.N) {
@@ -401,8 +468,12 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
       if constexpr (FUSE) {
         __threadfence_system();
         __syncwarp();
-        if (lane == 0)
+        if (f->direct) {
+          if (lane < f->world)
+            st_release_sys_u32(f->flags[lane] + ((size_t)mn * f->world + f->rank) * 4 + q, fuse_epoch);
+        } else if (lane == 0) {
           st_release_sys_u32(f->flags[mn % f->world] + ((size_t)mn * f->world + f->rank) * 4 + q, fuse_epoch);
+        }
       }
       ++tcount;
     }
@@ -415,7 +486,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
       const int q = warp - 6;
       const int tiles_mn = tiles_m * tiles_n;
       const int W = f->world;
-      int p2_next = (f->phases & 2) ? f->rank + (int)blockIdx.x * W : tiles_mn;
+      int p2_next = ((f->phases & 2) && !f->direct) ? f->rank + (int)blockIdx.x * W : tiles_mn;
       int p3_next = (f->phases & 4) ? (int)blockIdx.x : tiles_mn;
       uint32_t* my_flags = f->flags[f->rank];
       const size_t done_off = (size_t)f->max_tiles * W * 4;
@@ -425,7 +496,13 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
           fuse_reduce_quarter(f, p2_next, q, fuse_epoch);
           p2_next += gridDim.x * W;
           stall = 0;
-        } else if (p3_next < tiles_mn && warp_stamps_ready(my_flags + done_off + (size_t)p3_next * 4 + q, 1, 1, fuse_epoch)) {
+        } else if (p3_next < tiles_mn && f->direct &&
+                   warp_stamps_ready(my_flags + (size_t)p3_next * W * 4 + q, W, 4, fuse_epoch)) {
+          fuse_direct_quarter(f, p3_next, q, tiles_m, g.M, g.N, fuse_epoch);
+          p3_next += gridDim.x;
+          stall = 0;
+        } else if (p3_next < tiles_mn && !f->direct &&
+                   warp_stamps_ready(my_flags + done_off + (size_t)p3_next * 4 + q, 1, 1, fuse_epoch)) {
           fuse_add_quarter(f, p3_next, q, tiles_m, g.M, g.N);
           p3_next += gridDim.x;
           stall = 0;
@@ -551,7 +628,8 @@ HE_API int he_gemm_bf16_allreduce(const void* A, long long lda, const void* B, l
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   if (K % 8 != 0 || N % 8 != 0) return -HE_ERR_BAD_ARG;
   if (f.world < 1 || f.world > FUSE_MAX_WORLD || f.rank < 0 || f.rank >= f.world) return -HE_ERR_BAD_ARG;
-  if (tiles > f.max_tiles || (tiles + f.world - 1) / f.world > f.owned_cap) return -HE_ERR_BAD_ARG;
+  if (tiles > f.max_tiles || (f.direct ? tiles : (tiles + f.world - 1) / f.world) > f.owned_cap)
+    return -HE_ERR_BAD_ARG;
   if (f.resid == nullptr || (reinterpret_cast<uintptr_t>(f.resid) & 15) != 0 || f.ld_resid % 4 != 0 || f.ld_resid < N)
     return -HE_ERR_BAD_ARG;
   if ((f.phases & 7) == 0 || f.sync == nullptr) return -HE_ERR_BAD_ARG;

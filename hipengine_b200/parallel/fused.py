@@ -8,7 +8,8 @@ graph.  Single node only (IPC handles do not cross hosts).
 from __future__ import annotations
 
 import ctypes as C
-from typing import List
+import os
+from typing import List, Optional
 
 import torch
 import torch.distributed as dist
@@ -131,7 +132,8 @@ class _FuseArgs(C.Structure):
     _fields_ = [("stage", C.c_void_p * _MAX_WORLD), ("result", C.c_void_p * _MAX_WORLD),
                 ("flags", C.c_void_p * _MAX_WORLD), ("sync", C.c_void_p), ("resid", C.c_void_p),
                 ("ld_resid", C.c_longlong), ("world", C.c_int), ("rank", C.c_int), ("max_tiles", C.c_int),
-                ("owned_cap", C.c_int), ("phases", C.c_int), ("wait_limit", C.c_uint)]
+                ("owned_cap", C.c_int), ("phases", C.c_int), ("wait_limit", C.c_uint), ("direct", C.c_int),
+                ("reserved", C.c_int)]
 
 
 class FusedGemmAllReduce:
@@ -145,16 +147,25 @@ class FusedGemmAllReduce:
     """
 
     def __init__(self, ctx: DistContext, width: int, max_rows: int = 4096, wait_limit: int = 1 << 22,
-                 _regions: List[int] = None):
+                 _regions: List[int] = None, direct: Optional[bool] = None):
         L = N.lib()
         assert L.he_gemm_fuse_args_size() == C.sizeof(_FuseArgs), "ABI mismatch for FuseArgs"
         assert ctx.world <= _MAX_WORLD and width % 8 == 0
         self.ctx, self.width, self.max_rows, self.wait_limit = ctx, width, max_rows, wait_limit
         self.tile_elems = L.he_gemm_fuse_tile_elems()
         self.max_tiles = L.he_gemm_fuse_tiles(C.c_int(max_rows), C.c_int(width))
-        self.owned_cap = (self.max_tiles + ctx.world - 1) // ctx.world
-        self.stage_bytes = ctx.world * self.owned_cap * self.tile_elems * 2
-        self.result_bytes = self.max_tiles * self.tile_elems * 2
+        # one-hop ("direct") form up to this world size, owner (reduce-scatter + broadcast) form above it
+        if direct is None:
+            direct = ctx.world <= int(os.environ.get("HE_FUSED_GEMM_DIRECT_MAX_WORLD", "2"))
+        self.direct = bool(direct)
+        if self.direct:
+            self.owned_cap = self.max_tiles
+            self.stage_bytes = 2 * ctx.world * self.max_tiles * self.tile_elems * 2
+            self.result_bytes = 0
+        else:
+            self.owned_cap = (self.max_tiles + ctx.world - 1) // ctx.world
+            self.stage_bytes = ctx.world * self.owned_cap * self.tile_elems * 2
+            self.result_bytes = self.max_tiles * self.tile_elems * 2
         self.flag_bytes = (self.max_tiles * ctx.world * 4 + self.max_tiles * 4) * 4
         self.total_bytes = self.stage_bytes + self.result_bytes + self.flag_bytes
         self._opened: List[int] = []
@@ -186,7 +197,8 @@ class FusedGemmAllReduce:
         self.calls = 0
 
     @classmethod
-    def emulated_group(cls, device, width: int, world: int, max_rows: int = 512) -> List["FusedGemmAllReduce"]:
+    def emulated_group(cls, device, width: int, world: int, max_rows: int = 512,
+                       direct: Optional[bool] = None) -> List["FusedGemmAllReduce"]:
         """``world`` instances in ONE process on one GPU, wired to each other's regions.  Their kernels must be run
         phase by phase (all ranks' phase 1, then all phase 2, then all phase 3) so that no launch waits for a later
         launch; see ``gemm_add(..., phases=...)``."""
@@ -195,7 +207,7 @@ class FusedGemmAllReduce:
         out: List[FusedGemmAllReduce] = []
         for r in range(world):
             ctx = DistContext(r, world, 0, torch.device(device), None, "loopback")
-            inst = cls(ctx, width, max_rows, wait_limit=20000, _regions=[0] * world)
+            inst = cls(ctx, width, max_rows, wait_limit=20000, _regions=[0] * world, direct=direct)
             base = C.c_void_p()
             N.check(L.he_comm_alloc(C.c_longlong(inst.total_bytes), C.byref(base)), "he_comm_alloc")
             regions.append(base.value)
@@ -225,6 +237,7 @@ class FusedGemmAllReduce:
         a.resid, a.ld_resid = resid.data_ptr(), resid.stride(0)
         a.world, a.rank = self.ctx.world, self.ctx.rank
         a.max_tiles, a.owned_cap, a.phases, a.wait_limit = self.max_tiles, self.owned_cap, phases, self.wait_limit
+        a.direct = 1 if self.direct else 0
         st = K.status_tensor(x.device)
         N.check(N.lib().he_gemm_bf16_allreduce(
             C.c_void_p(x.data_ptr()), C.c_longlong(x.stride(0)), C.c_void_p(w.data_ptr()), C.c_longlong(w.stride(0)),

@@ -51,15 +51,16 @@ def _ref_add(h, xs, ws):
     return h + acc.float().bfloat16().float()
 
 
+@pytest.mark.parametrize("direct", [True, False], ids=["one_hop", "owner"])
 @pytest.mark.parametrize("n", [512, 640])
-def test_fused_gemm_allreduce_world_of_one(n):
+def test_fused_gemm_allreduce_world_of_one(n, direct):
     """One rank: the single kernel runs GEMM, stage, reduce and residual add with its own CTAs waiting on each
     other's stamps; several calls with different row counts advance the device-side epoch."""
     from hipengine_b200.ops import kernels as K
     from hipengine_b200.parallel.fused import FusedGemmAllReduce
     from hipengine_b200.parallel.groups import DistContext
     ctx = DistContext(0, 1, 0, torch.device("cuda", torch.cuda.current_device()), None, "none")
-    fg = FusedGemmAllReduce(ctx, width=n, max_rows=1024)
+    fg = FusedGemmAllReduce(ctx, width=n, max_rows=1024, direct=direct)
     try:
         g = torch.Generator(device="cuda").manual_seed(3)
         w = (torch.randn(n, 384, device="cuda", generator=g) * 0.05).bfloat16()
@@ -76,13 +77,13 @@ def test_fused_gemm_allreduce_world_of_one(n):
         fg.close()
 
 
-@pytest.mark.parametrize("world", [2, 4])
-def test_fused_gemm_allreduce_emulated_ranks(world):
+@pytest.mark.parametrize("world,direct", [(2, True), (2, False), (4, False), (4, True)])
+def test_fused_gemm_allreduce_emulated_ranks(world, direct):
     """Several ranks emulated on one GPU: the phases of both ranks run as separate launches in an order in which no
     launch waits for a later one (all phase 1, all phase 2, all phase 3); each rank holds a slice of K."""
     from hipengine_b200.ops import kernels as K
     from hipengine_b200.parallel.fused import FusedGemmAllReduce
-    ranks = FusedGemmAllReduce.emulated_group("cuda", width=768, world=world, max_rows=512)
+    ranks = FusedGemmAllReduce.emulated_group("cuda", width=768, world=world, max_rows=512, direct=direct)
     try:
         g = torch.Generator(device="cuda").manual_seed(5)
         ws = [(torch.randn(768, 256, device="cuda", generator=g) * 0.05).bfloat16() for _ in range(world)]
