@@ -169,29 +169,31 @@ __device__ __forceinline__ void fuse_reduce_quarter(const FuseArgs* f, int mn, i
   if (lane < W) st_release_sys_u32(f->flags[lane] + (size_t)f->max_tiles * W * 4 + (size_t)mn * 4 + q, epoch);
 }
 
-// Phase 3 for one warp: resid rows of quarter q of tile mn += reduced tile (lane = 8-column group, 16 rows in flight, vector red.add).
+// Phase 3 for one warp: resid rows of quarter q of tile mn += reduced tile.  Lane = row of the quarter (the tile is
+// fragment-major, so the 32 lanes read 512 contiguous bytes per column group); 16 column groups in flight; the adds
+// are vector red.add, each lane covering one full 32-byte sector of its row.
 __device__ __forceinline__ void fuse_add_quarter(const FuseArgs* f, int mn, int q, int tiles_m, int M, int N) {
   const int lane = threadIdx.x & 31;
   const int tm = mn % tiles_m, tn = mn / tiles_m;
-  const __nv_bfloat16* res = f->result[f->rank] + (size_t)mn * TILE_ELEMS + (size_t)q * 32 * 256 + lane * 8;
-  const int col = tn * 256 + lane * 8;
-  const int row0 = tm * 128 + q * 32;
-  if (col >= N) return;
-  float* hbase = f->resid + (size_t)row0 * f->ld_resid + col;
+  const __nv_bfloat16* res = f->result[f->rank] + (size_t)mn * TILE_ELEMS + (size_t)q * 8192 + lane * 8;
+  const int row = tm * 128 + q * 32 + lane;
+  const int col0 = tn * 256;
+  const bool live = row < M;
+  float* hrow = f->resid + (size_t)(live ? row : 0) * f->ld_resid + col0;
 #pragma unroll 1
-  for (int rr = 0; rr < 32; rr += 16) {
-    if (row0 + rr >= M) break;
+  for (int cg0 = 0; cg0 < 32; cg0 += 16) {
+    if (col0 + cg0 * 8 >= N) break;
     uint4 v[16];
 #pragma unroll
     for (int u = 0; u < 16; ++u)
-      v[u] = (row0 + rr + u < M) ? ld_cg_u4(res + (size_t)(rr + u) * 256) : make_uint4(0u, 0u, 0u, 0u);
+      v[u] = (live && col0 + (cg0 + u) * 8 < N) ? ld_cg_u4(res + (size_t)(cg0 + u) * 256) : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
     for (int u = 0; u < 16; ++u) {
-      if (row0 + rr + u < M) {
+      if (live && col0 + (cg0 + u) * 8 < N) {
         const __nv_bfloat162* hv = reinterpret_cast<const __nv_bfloat162*>(&v[u]);
         const float2 a0 = __bfloat1622float2(hv[0]), a1 = __bfloat1622float2(hv[1]);
         const float2 a2 = __bfloat1622float2(hv[2]), a3 = __bfloat1622float2(hv[3]);
-        float* hp = hbase + (size_t)(rr + u) * f->ld_resid;
+        float* hp = hrow + (cg0 + u) * 8;
         red_add_f32x4(hp, a0.x, a0.y, a1.x, a1.y);
         red_add_f32x4(hp + 4, a2.x, a2.y, a3.x, a3.y);
       }
@@ -200,21 +202,21 @@ __device__ __forceinline__ void fuse_add_quarter(const FuseArgs* f, int mn, int 
 }
 
 // One-hop form, one warp: resid rows of quarter q of tile mn += bf16(sum over ranks of the stage slots), ranks in
-// order (lane = 8-column group, 16 rows in flight, vector red.add).
+// order.  Lane = row of the quarter, 8 column groups in flight per rank slot, vector red.add into the residual.
 __device__ __forceinline__ void fuse_direct_quarter(const FuseArgs* f, int mn, int q, int tiles_m, int M, int N,
                                                     uint32_t epoch) {
   const int lane = threadIdx.x & 31, W = f->world;
   const int tm = mn % tiles_m, tn = mn / tiles_m;
   const size_t slot_stride = (size_t)f->owned_cap * TILE_ELEMS;
   const __nv_bfloat16* src = f->stage[f->rank] + (size_t)(epoch & 1u) * W * slot_stride + (size_t)mn * TILE_ELEMS +
-                             (size_t)q * 32 * 256 + lane * 8;
-  const int col = tn * 256 + lane * 8;
-  const int row0 = tm * 128 + q * 32;
-  if (col >= N) return;
-  float* hbase = f->resid + (size_t)row0 * f->ld_resid + col;
+                             (size_t)q * 8192 + lane * 8;
+  const int row = tm * 128 + q * 32 + lane;
+  const int col0 = tn * 256;
+  const bool live = row < M;
+  float* hrow = f->resid + (size_t)(live ? row : 0) * f->ld_resid + col0;
 #pragma unroll 1
-  for (int rr = 0; rr < 32; rr += 8) {
-    if (row0 + rr >= M) break;
+  for (int cg0 = 0; cg0 < 32; cg0 += 8) {
+    if (col0 + cg0 * 8 >= N) break;
     float acc[8][8];
 #pragma unroll
     for (int u = 0; u < 8; ++u)
@@ -224,8 +226,8 @@ __device__ __forceinline__ void fuse_direct_quarter(const FuseArgs* f, int mn, i
       uint4 v[8];
 #pragma unroll
       for (int u = 0; u < 8; ++u)
-        v[u] = (row0 + rr + u < M) ? ld_cg_u4(src + (size_t)r * slot_stride + (size_t)(rr + u) * 256)
-                                   : make_uint4(0u, 0u, 0u, 0u);
+        v[u] = (live && col0 + (cg0 + u) * 8 < N) ? ld_cg_u4(src + (size_t)r * slot_stride + (size_t)(cg0 + u) * 256)
+                                                  : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
         const __nv_bfloat162* hv = reinterpret_cast<const __nv_bfloat162*>(&v[u]);
@@ -239,12 +241,12 @@ __device__ __forceinline__ void fuse_direct_quarter(const FuseArgs* f, int mn, i
     }
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
-      if (row0 + rr + u < M) {
+      if (live && col0 + (cg0 + u) * 8 < N) {
         // round the sum to bf16 first: the same value the owner form broadcasts, so both forms agree bit for bit
         float s8[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) s8[e] = __bfloat162float(__float2bfloat16_rn(acc[u][e]));
-        float* hp = hbase + (size_t)(rr + u) * f->ld_resid;
+        float* hp = hrow + (cg0 + u) * 8;
         red_add_f32x4(hp, s8[0], s8[1], s8[2], s8[3]);
         red_add_f32x4(hp + 4, s8[4], s8[5], s8[6], s8[7]);
       }
@@ -398,20 +400,23 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
               pw[e] = *reinterpret_cast<uint32_t*>(&h2);
             }
           }
-          const size_t in_tile = (size_t)(q * 32 + lane) * BN + c * 32;
+          // fragment-major tile layout: 16-byte group (quarter q, column group cg = 4c + v, row lane) sits at
+          // q * 8192 + (cg * 32 + lane) * 8, so every store instruction of the warp covers 512 contiguous bytes
+          // (full lines on the link) instead of 32 pieces 512 bytes apart
+          const size_t in_tile = (size_t)q * 8192 + ((size_t)(c * 4) * 32 + lane) * 8;
           if (f->direct) {
             const size_t off = (((size_t)(fuse_epoch & 1u) * f->world + f->rank) * f->owned_cap + mn) * TILE_ELEMS +
                                in_tile;
             for (int pr = 0; pr < f->world; ++pr) {
               __nv_bfloat16* dst = f->stage[pr] + off;
 #pragma unroll
-              for (int v = 0; v < 4; ++v) *reinterpret_cast<uint4*>(dst + v * 8) = pk[v];
+              for (int v = 0; v < 4; ++v) *reinterpret_cast<uint4*>(dst + v * 256) = pk[v];
             }
           } else {
             const int owner = mn % f->world, oi = mn / f->world;
             __nv_bfloat16* dst = f->stage[owner] + ((size_t)f->rank * f->owned_cap + oi) * TILE_ELEMS + in_tile;
 #pragma unroll
-            for (int v = 0; v < 4; ++v) *reinterpret_cast<uint4*>(dst + v * 8) = pk[v];
+            for (int v = 0; v < 4; ++v) *reinterpret_cast<uint4*>(dst + v * 256) = pk[v];
           }
         } else
         if (row < g.M && col0 < g.N) {
