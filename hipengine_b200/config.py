@@ -52,6 +52,9 @@ class KVConfig:
     prefix_cache: str = "radix"             # off | radix
     snapshot_interval_tokens: int = 2048    # hybrid recurrent-state snapshot cadence for prefix reuse
     max_snapshots: int = 16
+    cold_tier_bytes: int = 0                # > 0: evicted prefix blocks go to a host / disk tier (``kvcache/tiering.py``)
+    cold_tier_dir: Optional[str] = None     # None: host memory; a path: one file per object
+    cold_restore_prefill_tok_s: float = 16000.0   # recompute rate the restore economics compare against
 
 
 @dataclass(frozen=True)

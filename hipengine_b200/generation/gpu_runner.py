@@ -59,6 +59,16 @@ class GpuRunner(BaseRunner):
                                                                   page_tokens=self.page,
                                                                   rope=f"{self.cfg.rope_theta}:{self.cfg.rope_dim}"))
         self.radix.on_retain = self.pool.retain_cache
+        # optional cold tier: blocks the radix cache evicts are kept, compressed, in host memory or on disk and are
+        # brought back at admission when that beats recomputing them (single-GPU engines only: the ranks of a
+        # tensor-parallel job would have to take identical restore decisions)
+        self.cold = None
+        self.cold_snap: Dict[str, bool] = {}
+        if config.kv.cold_tier_bytes > 0 and self.use_prefix and executor is None:
+            from ..kvcache.tiering import ColdTier
+            self.cold = ColdTier(config.kv.cold_tier_bytes, config.kv.cold_tier_dir)
+            self.radix.on_evict_node = self._offload_block
+            self.radix.on_evict_snapshot = self._offload_snapshot
         self.radix.on_release = lambda pages: self.pool.release_cache(pages)
         self.radix.page_refcount = lambda p: self.pool.refcount[p]
         self.radix.on_snapshot_free = self._free_snapshot
@@ -98,6 +108,110 @@ class GpuRunner(BaseRunner):
         for t in self.ex.gdn_state.values():
             t[dst].copy_(t[src])
 
+    # ------------------------------------------------------------------ cold tier
+    def _offload_block(self, tokens: List[int], page: int, snapshot: Optional[int]) -> None:
+        """Radix eviction hook: keep the block's KV rows (and the recurrent-state snapshot at its boundary)."""
+        from ..kvcache.tiering import prefix_key
+        arrays = {f"kv.{i}": t[page] for i, t in self.ex.kv.items()}
+        if snapshot is not None:
+            arrays.update(self._snapshot_arrays(snapshot))
+        key = prefix_key(self.radix.compat, tokens)
+        if self.cold.put(key, arrays, {"tokens": len(tokens), "snapshot": snapshot is not None}) is not None:
+            self.cold_snap[key] = snapshot is not None or (key + ".s") in self.cold
+            self.stats["cold_offloaded_blocks"] = self.stats.get("cold_offloaded_blocks", 0) + 1
+
+    def _snapshot_arrays(self, sid: int) -> Dict[str, torch.Tensor]:
+        out = {f"conv.{i}": t[sid] for i, t in self.ex.conv_state.items()}
+        out.update({f"gdn.{i}": t[sid] for i, t in self.ex.gdn_state.items()})
+        return out
+
+    def _offload_snapshot(self, tokens: List[int], sid: int) -> None:
+        """A snapshot slot is being recycled while its block stays cached: keep the state as its own object."""
+        from ..kvcache.tiering import prefix_key
+        key = prefix_key(self.radix.compat, tokens)
+        if self.cold.put(key + ".s", self._snapshot_arrays(sid), {"tokens": len(tokens)}) is not None:
+            self.cold_snap[key] = True
+
+    def _restore_from_cold(self, prompt: Sequence[int], matched_tokens: int) -> int:
+        """Extend the usable cached prefix of ``prompt`` (``matched_tokens`` so far) with content of the cold tier:
+        evicted blocks get fresh pages, and for hybrid models the recurrent state of the last restored boundary
+        gets a snapshot slot (its block may be cold too, or still cached with its snapshot slot recycled).
+        Returns the number of tokens by which the usable prefix grew."""
+        from ..kvcache.tiering import prefix_key, restore_is_worthwhile
+        page, hybrid = self.page, self.cfg.is_hybrid
+        limit = (len(prompt) - 1) // page
+        present = self.radix.match(prompt, require_snapshot=False)      # blocks whose pages are still in the pool
+        b0 = present.tokens // page
+        keys = [prefix_key(self.radix.compat, prompt[:(b + 1) * page]) for b in range(limit)]
+        run, stored, raw = [], 0, 0
+        for b in range(b0, limit):
+            info = self.cold.index.get(keys[b])
+            if info is None:
+                break
+            run.append(keys[b])
+            stored += info.stored_bytes
+            raw += max(info.raw_bytes, info.stored_bytes)
+        end = b0 + len(run)                          # blocks available in pool + cold
+        if hybrid:                                   # usable only up to a boundary whose state is available
+            while end * page > matched_tokens and not self.cold_snap.get(keys[end - 1], False):
+                end -= 1
+        if end * page <= matched_tokens:
+            return 0
+        n = max(0, end - b0)                         # cold blocks that need pages
+        run = run[:n]
+        if not restore_is_worthwhile(end * page - matched_tokens, stored, raw,
+                                     self.config.kv.cold_restore_prefill_tok_s):
+            self.stats["cold_declined"] = self.stats.get("cold_declined", 0) + 1
+            return 0
+        held = list(present.pages)
+        for pg in held:                              # the blocks still cached must survive the steps below
+            self.pool.refcount[pg] += 1
+        try:
+            short = n + 1 - (len(self.pool.free) - self.pool.credit_total)
+            if n and short > 0:
+                self.radix.evict(short)
+                if len(self.pool.free) - self.pool.credit_total < n + 1:
+                    return 0
+            loaded = []
+            for key in run:
+                got = self.cold.get(key)
+                if got is None:                      # dropped or corrupt
+                    return 0
+                loaded.append(got[0])
+            sid, state = None, None
+            if hybrid:
+                if loaded and end == b0 + n and any(k.startswith("conv.") for k in loaded[-1]):
+                    state = loaded[-1]
+                else:
+                    got = self.cold.get(keys[end - 1] + ".s")
+                    if got is None:
+                        return 0
+                    state = got[0]
+                sid = self._alloc_snapshot()
+                if sid is None:
+                    return 0
+            new_pages = self.pool._take(n) if n else []
+            for pg, arrays in zip(new_pages, loaded):
+                for i, t in self.ex.kv.items():
+                    t[pg].copy_(arrays[f"kv.{i}"])
+            if sid is not None:
+                for i, t in self.ex.conv_state.items():
+                    t[sid].copy_(state[f"conv.{i}"])
+                for i, t in self.ex.gdn_state.items():
+                    t[sid].copy_(state[f"gdn.{i}"])
+            pages = (held + new_pages)[:end]
+            self.radix.insert(prompt[:end * page], pages, {end * page: sid} if sid is not None else None)
+            for pg in new_pages:                     # a block the trie did not take (quota) goes back to the pool
+                if not self.pool.cached[pg]:
+                    self.pool.free.append(pg)
+        finally:
+            for pg in held:
+                self.pool.refcount[pg] -= 1
+        self.stats["cold_restored_blocks"] = self.stats.get("cold_restored_blocks", 0) + n
+        self.stats["cold_restored_tokens"] = self.stats.get("cold_restored_tokens", 0) + end * page - matched_tokens
+        self.stats["h2d_bytes"] += raw
+        return end * page - matched_tokens
+
     # ------------------------------------------------------------------ admission
     def admit(self, rs: RequestState) -> bool:
         total = rs.total_budget_tokens
@@ -108,6 +222,9 @@ class GpuRunner(BaseRunner):
             return False
         prompt = rs.req.prompt_token_ids
         match = self.radix.match(prompt, require_snapshot=self.cfg.is_hybrid) if self.use_prefix else None
+        if self.cold is not None and len(self.cold) and match is not None:
+            if self._restore_from_cold(prompt, match.tokens):
+                match = self.radix.match(prompt, require_snapshot=self.cfg.is_hybrid)
         shared = match.pages if match and match.tokens else []
         try:
             lease = self.pool.admit(rs.rid, total, shared_prefix=shared, now_tokens=rs.prompt_len)

@@ -63,6 +63,11 @@ class RadixCache:
         self.on_retain: Callable[[List[int]], None] = lambda pages: None
         self.on_release: Callable[[List[int]], None] = lambda pages: None
         self.on_snapshot_free: Callable[[int], None] = lambda sid: None
+        # called for every block that ``evict`` is about to drop, while its page and snapshot slot still hold their
+        # content: (token path from the root, page id, snapshot slot or None); a cold tier hooks in here
+        self.on_evict_node: Optional[Callable[[List[int], int, Optional[int]], None]] = None
+        # same for a snapshot slot that ``evict_snapshot`` takes away from a block that stays cached
+        self.on_evict_snapshot: Optional[Callable[[List[int], int], None]] = None
         self.page_refcount: Callable[[int], int] = lambda p: 0
 
     # -- lookup
@@ -153,12 +158,25 @@ class RadixCache:
             for leaf in leaves:
                 if len(freed) >= n_pages:
                     break
+                if self.on_evict_node is not None:
+                    self.on_evict_node(self.token_path(leaf), leaf.page, leaf.snapshot)
                 self._remove(leaf)
                 freed.append(leaf.page)
         if freed:
             self.on_release(freed)
             self.stats["evicted_pages"] += len(freed)
         return freed
+
+    @staticmethod
+    def token_path(node: _Node) -> List[int]:
+        keys = []
+        while node is not None and node.parent is not None:
+            keys.append(node.key)
+            node = node.parent
+        out: List[int] = []
+        for k in reversed(keys):
+            out.extend(k)
+        return out
 
     def evict_snapshot(self) -> Optional[int]:
         """Free the least-recently-used snapshot slot (its pages stay cached).  Returns the slot id."""
@@ -171,6 +189,8 @@ class RadixCache:
             stack.extend(n.children.values())
         if best is None:
             return None
+        if self.on_evict_snapshot is not None:
+            self.on_evict_snapshot(self.token_path(best), best.snapshot)
         sid, best.snapshot = best.snapshot, None
         return sid
 

@@ -112,7 +112,8 @@ class LLM:
                  execution_profile: Any = None, max_active_requests: int = 8,
                  max_sequence_length: Optional[int] = None, prefix_cache: str = "radix",
                  speculative_mtp_serving: str = "off", speculative_candidate_budget: int = 3,
-                 speculative_provider: str = "mtp",
+                 speculative_provider: str = "mtp", kv_cold_tier_bytes: int = 0,
+                 kv_cold_tier_dir: Optional[str] = None,
                  kv_storage: str = "bf16", tensor_parallel: int = 1, expert_parallel: int = 1,
                  engine_command_timeout_seconds: float = 300.0, seed: int = 0, tokenizer: Any = None,
                  engine_config: Optional[EngineConfig] = None, device: Optional[str] = None,
@@ -126,7 +127,9 @@ class LLM:
             max_sequence_length=int(max_sequence_length or base.max_sequence_length),
             profile=self.profile,
             scheduler=replace(base.scheduler, max_active_requests=int(max_active_requests)),
-            kv=replace(base.kv, storage=kv_storage, prefix_cache=prefix_cache),
+            kv=replace(base.kv, storage=kv_storage, prefix_cache=prefix_cache,
+                       cold_tier_bytes=int(kv_cold_tier_bytes or base.kv.cold_tier_bytes),
+                       cold_tier_dir=kv_cold_tier_dir or base.kv.cold_tier_dir),
             speculative=replace(base.speculative,
                                 mode=speculative_provider if speculative_mtp_serving not in ("off", None) else "off",
                                 draft_depth=int(speculative_candidate_budget)),

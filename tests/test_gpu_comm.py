@@ -77,7 +77,7 @@ def test_fused_gemm_allreduce_world_of_one(n, direct):
         fg.close()
 
 
-@pytest.mark.parametrize("world,direct", [(2, True), (2, False), (4, False), (4, True)])
+@pytest.mark.parametrize("world,direct", [(2, True), (2, False), (4, False), (4, True), (8, False)])
 def test_fused_gemm_allreduce_emulated_ranks(world, direct):
     """Several ranks emulated on one GPU: the phases of both ranks run as separate launches in an order in which no
     launch waits for a later one (all phase 1, all phase 2, all phase 3); each rank holds a slice of K."""

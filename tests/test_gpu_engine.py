@@ -106,3 +106,36 @@ def test_mtp_serving_matches_plain_greedy_and_reports_cycles():
     finally:
         plain.close()
         spec.close()
+
+
+def test_cold_tier_brings_an_evicted_prefix_back():
+    """A small pool forces the radix cache to evict the first prompt's blocks; with the cold tier on they are
+    offloaded (KV rows + recurrent-state snapshots) and restored at the next admission, and the continuation is the
+    one the first run produced."""
+    from hipengine_b200 import LLM, SamplingParams
+    from hipengine_b200.config import EngineConfig, KVConfig
+    from hipengine_b200.loading.synth import build_random_model
+    from hipengine_b200.models.config import TINY_HYBRID
+    w = build_random_model(TINY_HYBRID, seed=2, std=0.05).to("cuda")
+    cfg = EngineConfig(kv=KVConfig(snapshot_interval_tokens=64, max_snapshots=8, pool_pages=41,
+                                   cold_restore_prefill_tok_s=1.0))
+    llm = LLM(w, backend="cuda_sm100a", max_active_requests=1, max_sequence_length=256, engine_config=cfg,
+              kv_cold_tier_bytes=256 << 20)
+    try:
+        g = torch.Generator().manual_seed(16)
+        first_prompt = torch.randint(0, 2048, (140,), generator=g).tolist()
+        sp = SamplingParams(max_tokens=4, ignore_eos=True)
+        first = llm.generate_detailed(first_prompt, sp)[0]
+        runner = llm._get_engine().loop.runner
+        assert runner.cold is not None
+        for _ in range(6):                                   # other traffic: pushes the first prompt out of the pool
+            llm.generate_detailed(torch.randint(0, 2048, (200,), generator=g).tolist(), sp)
+        assert runner.stats.get("cold_offloaded_blocks", 0) >= 8
+        assert runner.radix.match(first_prompt, require_snapshot=True).tokens == 0     # really gone from the pool
+        again = llm.generate_detailed(first_prompt, sp)[0]
+        assert runner.stats.get("cold_restored_tokens", 0) >= 64
+        assert again.telemetry.cached_prompt_tokens in (64, 128)
+        assert again.token_ids == first.token_ids
+        runner.pool.assert_conserved()
+    finally:
+        llm.close()

@@ -120,3 +120,51 @@ def test_tool_call_grammar_generator():
     with pytest.raises(ValueError):
         tool_call_grammar(tools, only="missing")
     assert isinstance(grammar_available(), bool)
+
+
+def test_cold_tier_roundtrip_lru_and_corruption(tmp_path):
+    import numpy as np
+    import torch
+    from hipengine_b200.kvcache.tiering import (ColdTier, ColdTierCorruption, decode_object, encode_object,
+                                                prefix_key, restore_is_worthwhile)
+    kv = torch.randn(2, 4, 16, 32).bfloat16()
+    state = np.arange(24, dtype=np.float32).reshape(2, 3, 4)
+    blob, raw = encode_object({"kv": kv, "state": state}, {"tokens": 16})
+    arrays, meta = decode_object(blob)
+    assert meta == {"tokens": 16} and raw == kv.numel() * 2 + state.nbytes
+    assert arrays["kv"].dtype == torch.bfloat16 and torch.equal(arrays["kv"], kv)
+    assert np.array_equal(arrays["state"], state)
+    bad = bytearray(blob)
+    bad[-3] ^= 0x40
+    import pytest
+    with pytest.raises(ColdTierCorruption):
+        decode_object(bytes(bad))
+    with pytest.raises(ColdTierCorruption):
+        decode_object(blob[:-1])
+
+    k1, k2 = prefix_key("qwen/q4", [1, 2, 3]), prefix_key("qwen/q4", [1, 2, 4])
+    assert k1 != k2 and k1 == prefix_key("qwen/q4", (1, 2, 3)) and k1 != prefix_key("other", [1, 2, 3])
+
+    for directory in (None, str(tmp_path / "cold")):
+        zeros = {"kv": torch.zeros(64, 1024)}                       # compresses well
+        one = len(encode_object(zeros)[0])
+        tier = ColdTier(capacity_bytes=2 * one + 16, directory=directory)
+        assert tier.put("a", zeros, {"n": 1}) is not None
+        assert tier.put("b", zeros) is not None
+        assert tier.get("a")[1] == {"n": 1}                         # touch: "b" is now the oldest
+        tier.put("c", zeros)
+        assert "b" not in tier and "a" in tier and "c" in tier and tier.stats["evicted"] == 1
+        assert tier.compression_ratio() > 50
+        assert tier.put("huge", {"x": torch.randn(4096, 64)}) is None     # larger than the whole tier
+        assert tier.get("missing") is None and tier.stats["misses"] == 1
+        if directory:                                               # flip a byte on disk: dropped, not returned
+            p = tier._path("c")
+            raw_file = bytearray(open(p, "rb").read())
+            raw_file[-1] ^= 0xFF
+            open(p, "wb").write(bytes(raw_file))
+            assert tier.get("c") is None and tier.stats["corrupt"] == 1 and "c" not in tier
+            again = ColdTier(capacity_bytes=1 << 20, directory=directory)   # a new process adopts what is left
+            assert "a" in again and torch.equal(again.get("a")[0]["kv"], zeros["kv"])
+    # 4096 tokens at 16k tok/s = 256 ms of prefill against ~1 GB of state: restore loses; against 100 MB it wins
+    assert not restore_is_worthwhile(4096, 10 ** 9, 10 ** 9, 16000.0)
+    assert restore_is_worthwhile(4096, 2 * 10 ** 7, 4 * 10 ** 7, 16000.0)
