@@ -55,6 +55,12 @@ __device__ __forceinline__ float4 ld_cg4(const float* p) {
 __global__ void __launch_bounds__(256) comm_push_reduce_kernel(const CommArgs a) {
   __shared__ int ok_s;
   const int c = blockIdx.x, n_cta = gridDim.x;
+  // Programmatic dependent launch: this grid is already resident when the producer of `partial` drains, and the
+  // kernel after it (a GEMV) may start prefetching its weights while the CTAs below wait for the peers' stamps.
+  // Nothing -- not even the epoch -- is read before the wait: with chained early launches only the wait orders this
+  // grid after ALL earlier kernels of the stream.
+  pdl_launch();
+  pdl_wait();
   const uint32_t epoch = a.epoch[c] + 1;
   const int phase = epoch & 1;
   const int total = a.rows * a.width;              // floats in flight this call (multiple of 4)
@@ -143,7 +149,8 @@ HE_API int he_comm_push_reduce(const CommArgs* args, int n_ctas, cudaStream_t st
   if (a.world < 1 || a.world > COMM_MAX_WORLD || a.rank < 0 || a.rank >= a.world) return -HE_ERR_BAD_ARG;
   if (a.width % 4 != 0 || (long long)a.rows * a.width > a.slot_floats) return -HE_ERR_BAD_ARG;
   if (n_ctas < 1 || n_ctas > COMM_MAX_CTAS) return -HE_ERR_BAD_ARG;
-  comm_push_reduce_kernel<<<n_ctas, 256, 0, stream>>>(a);
+  cudaError_t e = launch_pdl(comm_push_reduce_kernel, dim3(n_ctas), dim3(256), 0, stream, a);
+  if (e != cudaSuccess) return (int)e;
   HE_LAUNCH_CHECK();
   return 0;
 }
