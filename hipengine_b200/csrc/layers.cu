@@ -16,6 +16,8 @@ template <typename OutT>
 __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                                            OutT* __restrict__ out, int H, float eps,
                                                            long long x_stride, long long out_stride) {
+  pdl_wait();      // launched with programmatic stream serialization: order after all earlier kernels
+  pdl_launch();
   __shared__ float red[33];
   const float* xr = x + (size_t)blockIdx.x * x_stride;
   float ss = 0.f;
@@ -46,6 +48,8 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restri
 // ---------------------------------------------------------------- act(gate) * up over packed [T][2F] bf16 -> [T][F] bf16
 __global__ void act_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, long long T,
                                int F, int act) {
+  pdl_wait();      // launched with programmatic stream serialization: order after all earlier kernels
+  pdl_launch();
   const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (i >= T * F) return;
   const long long t = i / F;
@@ -68,6 +72,8 @@ __global__ void act_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat
 // same with the packed gate | up rows in fp32 (split-K accumulators of small batches)
 __global__ void act_mul_f32_kernel(const float* __restrict__ gu, __nv_bfloat16* __restrict__ out, long long T, int F,
                                    int act) {
+  pdl_wait();      // launched with programmatic stream serialization: order after all earlier kernels
+  pdl_launch();
   const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
   if (i >= T * F) return;
   const long long t = i / F;
@@ -87,6 +93,8 @@ __global__ void act_mul_f32_kernel(const float* __restrict__ gu, __nv_bfloat16* 
 
 // ---------------------------------------------------------------- residual add: h (fp32) += y (bf16)
 __global__ void resid_add_bf16_kernel(float* __restrict__ h, const __nv_bfloat16* __restrict__ y, long long n) {
+  pdl_wait();      // launched with programmatic stream serialization: order after all earlier kernels
+  pdl_launch();
   const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
   if (i >= n) return;
   float4 hv = *reinterpret_cast<float4*>(h + i);
@@ -199,6 +207,8 @@ struct ConvArgs {
 constexpr int CONV_TOK = 8;
 template <int KWT>
 __global__ void __launch_bounds__(256) conv_fwd_kernel(const ConvArgs a) {
+  pdl_wait();      // launched with programmatic stream serialization: order after all earlier kernels
+  pdl_launch();
   const int C8 = a.C >> 3;
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const int n_tchunks = (a.T + CONV_TOK - 1) / CONV_TOK;
@@ -269,6 +279,8 @@ __global__ void __launch_bounds__(256) conv_fwd_kernel(const ConvArgs a) {
 
 // one thread per (segment, channel): new state = last KW-1 entries of [state ++ x_seg]
 __global__ void conv_state_kernel(const ConvArgs a) {
+  pdl_wait();      // launched with programmatic stream serialization: order after all earlier kernels
+  pdl_launch();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (long long)a.n_seg * a.C) return;
   const int sg = (int)(i / a.C), c = (int)(i % a.C);
@@ -285,6 +297,8 @@ __global__ void conv_state_kernel(const ConvArgs a) {
 
 // ---------------------------------------------------------------- bookkeeping
 __global__ void advance_positions_kernel(int* pos, int* ctx_len, const int* active, int n, int delta) {
+  pdl_wait();      // launched with programmatic stream serialization: order after all earlier kernels
+  pdl_launch();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   if (active == nullptr || active[i]) {
@@ -300,10 +314,10 @@ HE_API int he_rmsnorm_rows(const void* x, const void* w, void* out, int out_bf16
   if (T <= 0) return 0;
   if (H % 4 != 0) return -HE_ERR_BAD_ARG;
   if (out_bf16)
-    rmsnorm_rows_kernel<__nv_bfloat16><<<T, 256, 0, stream>>>((const float*)x, (const float*)w, (__nv_bfloat16*)out, H,
+    (void)launch_pdl(rmsnorm_rows_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, (const float*)x, (const float*)w, (__nv_bfloat16*)out, H,
                                                               eps, x_stride, out_stride);
   else
-    rmsnorm_rows_kernel<float><<<T, 256, 0, stream>>>((const float*)x, (const float*)w, (float*)out, H, eps, x_stride,
+    (void)launch_pdl(rmsnorm_rows_kernel<float>, dim3(T), dim3(256), 0, stream, (const float*)x, (const float*)w, (float*)out, H, eps, x_stride,
                                                       out_stride);
   HE_LAUNCH_CHECK();
   return 0;
@@ -313,7 +327,7 @@ HE_API int he_act_mul(const void* gu, void* out, long long T, int F, int act, cu
   if (T <= 0) return 0;
   if (F % 8 != 0) return -HE_ERR_BAD_ARG;
   const long long n = T * F / 8;
-  act_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, T, F,
+  (void)launch_pdl(act_mul_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, T, F,
                                                                    act);
   HE_LAUNCH_CHECK();
   return 0;
@@ -323,7 +337,7 @@ HE_API int he_act_mul_f32(const void* gu, void* out, long long T, int F, int act
   if (T <= 0) return 0;
   if (F % 4 != 0) return -HE_ERR_BAD_ARG;
   const long long n = T * F / 4;
-  act_mul_f32_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>((const float*)gu, (__nv_bfloat16*)out, T, F, act);
+  (void)launch_pdl(act_mul_f32_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, (const float*)gu, (__nv_bfloat16*)out, T, F, act);
   HE_LAUNCH_CHECK();
   return 0;
 }
@@ -331,12 +345,14 @@ HE_API int he_act_mul_f32(const void* gu, void* out, long long T, int F, int act
 HE_API int he_resid_add_bf16(void* h, const void* y, long long n, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (n % 4 != 0) return -HE_ERR_BAD_ARG;
-  resid_add_bf16_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, stream>>>((float*)h, (const __nv_bfloat16*)y, n);
+  (void)launch_pdl(resid_add_bf16_kernel, dim3((unsigned)((n / 4 + 255) / 256)), dim3(256), 0, stream, (float*)h, (const __nv_bfloat16*)y, n);
   HE_LAUNCH_CHECK();
   return 0;
 }
 
 __global__ void resid_add_f32_kernel(float* __restrict__ h, const float* __restrict__ y, long long n) {
+  pdl_wait();      // launched with programmatic stream serialization: order after all earlier kernels
+  pdl_launch();
   const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
   if (i >= n) return;
   float4 a = *reinterpret_cast<float4*>(h + i);
@@ -349,7 +365,7 @@ __global__ void resid_add_f32_kernel(float* __restrict__ h, const float* __restr
 HE_API int he_resid_add_f32(void* h, const void* y, long long n, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (n % 4 != 0) return -HE_ERR_BAD_ARG;
-  resid_add_f32_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, stream>>>((float*)h, (const float*)y, n);
+  (void)launch_pdl(resid_add_f32_kernel, dim3((unsigned)((n / 4 + 255) / 256)), dim3(256), 0, stream, (float*)h, (const float*)y, n);
   HE_LAUNCH_CHECK();
   return 0;
 }
@@ -359,6 +375,8 @@ HE_API int he_resid_add_f32(void* h, const void* y, long long n, cudaStream_t st
 __global__ void __launch_bounds__(256) norm_add_kernel(float* __restrict__ h, long long ldh, const void* __restrict__ y,
                                                        int y_dtype, long long ldy, const float* __restrict__ w, int H,
                                                        float eps) {
+  pdl_wait();      // launched with programmatic stream serialization: order after all earlier kernels
+  pdl_launch();
   __shared__ float red[33];
   const int t = blockIdx.x;
   float ss = 0.f;
@@ -380,6 +398,8 @@ __global__ void __launch_bounds__(256) ffn_combine_kernel(float* __restrict__ h,
                                                           const float* __restrict__ w1, const float* __restrict__ w2,
                                                           const float* __restrict__ w3,
                                                           const float* __restrict__ scalar, int H, float eps) {
+  pdl_wait();      // launched with programmatic stream serialization: order after all earlier kernels
+  pdl_launch();
   extern __shared__ float buf[];   // [H]
   __shared__ float red[33];
   const int t = blockIdx.x;
@@ -408,7 +428,7 @@ __global__ void __launch_bounds__(256) ffn_combine_kernel(float* __restrict__ h,
 HE_API int he_norm_add(void* h, long long ldh, const void* y, int y_dtype, long long ldy, const void* w, int T, int H,
                        float eps, cudaStream_t stream) {
   if (T <= 0) return 0;
-  norm_add_kernel<<<T, 256, 0, stream>>>((float*)h, ldh, y, y_dtype, ldy, (const float*)w, H, eps);
+  (void)launch_pdl(norm_add_kernel, dim3(T), dim3(256), 0, stream, (float*)h, ldh, y, y_dtype, ldy, (const float*)w, H, eps);
   HE_LAUNCH_CHECK();
   return 0;
 }
@@ -418,7 +438,7 @@ HE_API int he_ffn_combine(void* h, long long ldh, const void* d, int d_dtype, lo
                           int H, float eps, cudaStream_t stream) {
   if (T <= 0) return 0;
   if ((size_t)H * sizeof(float) > 48 * 1024) return -HE_ERR_BAD_ARG;
-  ffn_combine_kernel<<<T, 256, (size_t)H * sizeof(float), stream>>>((float*)h, ldh, d, d_dtype, ldd, e, e_dtype, lde,
+  (void)launch_pdl(ffn_combine_kernel, dim3(T), dim3(256), (size_t)H * sizeof(float), stream, (float*)h, ldh, d, d_dtype, ldd, e, e_dtype, lde,
                                                                     (const float*)w1, (const float*)w2,
                                                                     (const float*)w3, (const float*)scalar, H, eps);
   HE_LAUNCH_CHECK();
@@ -443,13 +463,13 @@ HE_API int he_conv1d(const ConvArgs* args, int update_state, cudaStream_t stream
   if (a.C % 8 != 0) return -HE_ERR_BAD_ARG;
   const long long n = (long long)((a.T + CONV_TOK - 1) / CONV_TOK) * (a.C / 8);
   const unsigned nblk = (unsigned)((n + 255) / 256);
-  if (a.KW == 4) conv_fwd_kernel<4><<<nblk, 256, 0, stream>>>(a);
-  else if (a.KW == 3) conv_fwd_kernel<3><<<nblk, 256, 0, stream>>>(a);
-  else conv_fwd_kernel<2><<<nblk, 256, 0, stream>>>(a);
+  if (a.KW == 4) (void)launch_pdl(conv_fwd_kernel<4>, dim3(nblk), dim3(256), 0, stream, a);
+  else if (a.KW == 3) (void)launch_pdl(conv_fwd_kernel<3>, dim3(nblk), dim3(256), 0, stream, a);
+  else (void)launch_pdl(conv_fwd_kernel<2>, dim3(nblk), dim3(256), 0, stream, a);
   HE_LAUNCH_CHECK();
   if (update_state) {
     const long long m = (long long)a.n_seg * a.C;
-    conv_state_kernel<<<(unsigned)((m + 255) / 256), 256, 0, stream>>>(a);
+    (void)launch_pdl(conv_state_kernel, dim3((unsigned)((m + 255) / 256)), dim3(256), 0, stream, a);
     HE_LAUNCH_CHECK();
   }
   return 0;
@@ -458,7 +478,7 @@ HE_API int he_conv_args_size() { return (int)sizeof(ConvArgs); }
 
 HE_API int he_advance_positions(void* pos, void* ctx_len, const void* active, int n, int delta, cudaStream_t stream) {
   if (n <= 0) return 0;
-  advance_positions_kernel<<<(n + 127) / 128, 128, 0, stream>>>((int*)pos, (int*)ctx_len, (const int*)active, n, delta);
+  (void)launch_pdl(advance_positions_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, (int*)pos, (int*)ctx_len, (const int*)active, n, delta);
   HE_LAUNCH_CHECK();
   return 0;
 }

@@ -26,6 +26,8 @@ template <int MAXPL>
 __global__ void moe_route_kernel(const float* __restrict__ logits, long long ld, int T, int E, int k, int mode,
                                  const float* __restrict__ expert_scale, int* __restrict__ ids,
                                  float* __restrict__ wts) {
+  pdl_wait();      // launched with programmatic stream serialization: order after all earlier kernels
+  pdl_launch();
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (t >= T) return;
@@ -166,6 +168,8 @@ __global__ void moe_combine_kernel(float* __restrict__ h, long long ldh, const _
 // projection is linear, so scaling its input scales its output)
 __global__ void moe_scale_rows_kernel(__nv_bfloat16* __restrict__ act, long long ld, int N,
                                       const float* __restrict__ sg, long long ldsg) {
+  pdl_wait();      // launched with programmatic stream serialization: order after all earlier kernels
+  pdl_launch();
   const int t = blockIdx.x;
   const float g = sigmoid_f(sg[(size_t)t * ldsg]);
   for (int n = threadIdx.x; n < N; n += blockDim.x)
@@ -248,6 +252,9 @@ struct MoeSelArgs {
 
 // grid (ceil(N / rows_per_cta), T*k), 256 threads
 __global__ void __launch_bounds__(256) moe_gateup_sel_kernel(const MoeSelArgs a) {
+  pdl_wait();      // launched with programmatic stream serialization: order after all earlier kernels
+  // no early pdl_launch(): the grid spans several waves, and a successor made resident early would only
+  // hold SM resources that the later waves of this grid need
   extern __shared__ __align__(16) uint8_t smem_moe[];
   __shared__ float red[32];
   const SmemView s = carve(smem_moe, 1, a.K);
@@ -317,6 +324,9 @@ __global__ void __launch_bounds__(256) moe_gateup_sel_kernel(const MoeSelArgs a)
 // grid (ceil(N / rows_per_cta), T), 256 threads.  K = expert FFN width; activations of the token's k experts
 // are quantised into k shared rows; an output row is owned by lpr lanes covering all (expert, block) items.
 __global__ void __launch_bounds__(256) moe_down_sel_kernel(const MoeSelArgs a) {
+  pdl_wait();      // launched with programmatic stream serialization: order after all earlier kernels
+  // no early pdl_launch(): the grid spans several waves, and a successor made resident early would only
+  // hold SM resources that the later waves of this grid need
   extern __shared__ __align__(16) uint8_t smem_moe[];
   __shared__ int e_s[32];
   __shared__ float w_s[32];
@@ -390,9 +400,9 @@ HE_API int he_moe_route(const float* logits, long long ld, int T, int E, int k, 
   if (k > 32 || k <= 0 || E > 512 || E < k) return -HE_ERR_BAD_ARG;
   const int wpb = 4;
   const dim3 grid((T + wpb - 1) / wpb);
-  if (E <= 128) moe_route_kernel<4><<<grid, wpb * 32, 0, stream>>>(logits, ld, T, E, k, mode, expert_scale, ids, wts);
-  else if (E <= 256) moe_route_kernel<8><<<grid, wpb * 32, 0, stream>>>(logits, ld, T, E, k, mode, expert_scale, ids, wts);
-  else moe_route_kernel<16><<<grid, wpb * 32, 0, stream>>>(logits, ld, T, E, k, mode, expert_scale, ids, wts);
+  if (E <= 128) (void)launch_pdl(moe_route_kernel<4>, dim3(grid), dim3(wpb * 32), 0, stream, logits, ld, T, E, k, mode, expert_scale, ids, wts);
+  else if (E <= 256) (void)launch_pdl(moe_route_kernel<8>, dim3(grid), dim3(wpb * 32), 0, stream, logits, ld, T, E, k, mode, expert_scale, ids, wts);
+  else (void)launch_pdl(moe_route_kernel<16>, dim3(grid), dim3(wpb * 32), 0, stream, logits, ld, T, E, k, mode, expert_scale, ids, wts);
   HE_LAUNCH_CHECK();
   return 0;
 }
@@ -435,7 +445,7 @@ HE_API int he_moe_combine(float* h, long long ldh, const void* y, long long ldy,
 HE_API int he_moe_scale_rows(void* act, long long ld, int T, int N, const float* sg, long long ldsg,
                              cudaStream_t stream) {
   if (T <= 0) return 0;
-  moe_scale_rows_kernel<<<T, 256, 0, stream>>>(reinterpret_cast<__nv_bfloat16*>(act), ld, N, sg, ldsg);
+  (void)launch_pdl(moe_scale_rows_kernel, dim3(T), dim3(256), 0, stream, reinterpret_cast<__nv_bfloat16*>(act), ld, N, sg, ldsg);
   HE_LAUNCH_CHECK();
   return 0;
 }
@@ -457,7 +467,7 @@ HE_API int he_moe_gateup_sel(const MoeSelArgs* args, cudaStream_t stream) {
   rc = set_smem(moe_gateup_sel_kernel, smem);
   if (rc != 0) return rc;
   const dim3 grid((a.N + a.rows_per_cta - 1) / a.rows_per_cta, a.T * a.k);
-  moe_gateup_sel_kernel<<<grid, 256, smem, stream>>>(a);
+  (void)launch_pdl(moe_gateup_sel_kernel, dim3(grid), dim3(256), smem, stream, a);
   HE_LAUNCH_CHECK();
   return 0;
 }
@@ -472,7 +482,7 @@ HE_API int he_moe_down_sel(const MoeSelArgs* args, cudaStream_t stream) {
   rc = set_smem(moe_down_sel_kernel, smem);
   if (rc != 0) return rc;
   const dim3 grid((a.N + a.rows_per_cta - 1) / a.rows_per_cta, a.T);
-  moe_down_sel_kernel<<<grid, 256, smem, stream>>>(a);
+  (void)launch_pdl(moe_down_sel_kernel, dim3(grid), dim3(256), smem, stream, a);
   HE_LAUNCH_CHECK();
   return 0;
 }

@@ -136,6 +136,8 @@ __global__ void dequant_bf16_kernel(const uint8_t* __restrict__ w, __nv_bfloat16
 
 __global__ void embed_kernel(const uint8_t* __restrict__ w, int qtype, long long vocab, int K,
                              const int64_t* __restrict__ ids, float* __restrict__ out, float scale, int n_tok) {
+  pdl_wait();      // launched with programmatic stream serialization: order after all earlier kernels
+  pdl_launch();
   const int t = blockIdx.x;
   if (t >= n_tok) return;
   long long id = ids[t];
@@ -162,7 +164,7 @@ HE_API int he_dequant_bf16(const void* w, void* out, int qtype, long long row0, 
 HE_API int he_embed(const void* w, int qtype, long long vocab, int K, const void* ids, void* out, float scale,
                     int n_tok, cudaStream_t stream) {
   if (n_tok <= 0) return 0;
-  embed_kernel<<<n_tok, 256, 0, stream>>>((const uint8_t*)w, qtype, vocab, K, (const int64_t*)ids, (float*)out, scale,
+  (void)launch_pdl(embed_kernel, dim3(n_tok), dim3(256), 0, stream, (const uint8_t*)w, qtype, vocab, K, (const int64_t*)ids, (float*)out, scale,
                                           n_tok);
   HE_LAUNCH_CHECK();
   return 0;

@@ -53,6 +53,8 @@ constexpr int AM_PARTS = 64;
 // grid (AM_PARTS, R)
 __global__ void __launch_bounds__(256) argmax_stage1(const float* __restrict__ logits, long long stride, int V,
                                                      float* __restrict__ pv, int* __restrict__ pi) {
+  pdl_wait();      // launched with programmatic stream serialization: order after all earlier kernels
+  pdl_launch();
   __shared__ MaxIdx sh[32];
   const int r = blockIdx.y;
   const float* row = logits + (size_t)r * stride;
@@ -77,6 +79,8 @@ __global__ void __launch_bounds__(256) argmax_stage1(const float* __restrict__ l
 // grid R, block 64
 __global__ void argmax_stage2(const float* __restrict__ pv, const int* __restrict__ pi, long long* __restrict__ out,
                               float* __restrict__ out_val) {
+  pdl_wait();      // launched with programmatic stream serialization: order after all earlier kernels
+  pdl_launch();
   __shared__ MaxIdx sh[32];
   const int r = blockIdx.x;
   MaxIdx m;
@@ -112,6 +116,8 @@ __global__ void __launch_bounds__(1024) sample_rows_kernel(const float* __restri
                                                            const SampleParams* __restrict__ params,
                                                            long long* __restrict__ out_id,
                                                            float* __restrict__ out_logprob) {
+  pdl_wait();      // launched with programmatic stream serialization: order after all earlier kernels
+  pdl_launch();
   __shared__ float red[33];
   __shared__ MaxIdx shm[32];
   __shared__ float scan[1024];
@@ -268,6 +274,8 @@ __global__ void __launch_bounds__(1024) topn_logprobs_kernel(const float* __rest
 
 // softcap in place: x = cap * tanh(x / cap)
 __global__ void softcap_kernel(float* x, long long n, float cap) {
+  pdl_wait();      // launched with programmatic stream serialization: order after all earlier kernels
+  pdl_launch();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) x[i] = cap * tanhf(x[i] / cap);
 }
@@ -279,9 +287,9 @@ HE_API int he_argmax_rows(const void* logits, long long stride, int R, int V, vo
                           void* out_val, cudaStream_t stream) {
   if (R <= 0) return 0;
   dim3 g1(AM_PARTS, R);
-  argmax_stage1<<<g1, 256, 0, stream>>>((const float*)logits, stride, V, (float*)pv, (int*)pi);
+  (void)launch_pdl(argmax_stage1, dim3(g1), dim3(256), 0, stream, (const float*)logits, stride, V, (float*)pv, (int*)pi);
   HE_LAUNCH_CHECK();
-  argmax_stage2<<<R, AM_PARTS, 0, stream>>>((const float*)pv, (const int*)pi, (long long*)out_ids, (float*)out_val);
+  (void)launch_pdl(argmax_stage2, dim3(R), dim3(AM_PARTS), 0, stream, (const float*)pv, (const int*)pi, (long long*)out_ids, (float*)out_val);
   HE_LAUNCH_CHECK();
   return 0;
 }
@@ -289,7 +297,7 @@ HE_API int he_argmax_rows(const void* logits, long long stride, int R, int V, vo
 HE_API int he_sample_rows(const void* logits, long long stride, int R, int V, const void* params, void* out_ids,
                           void* out_logprob, cudaStream_t stream) {
   if (R <= 0) return 0;
-  sample_rows_kernel<<<R, 1024, 0, stream>>>((const float*)logits, stride, V, (const SampleParams*)params,
+  (void)launch_pdl(sample_rows_kernel, dim3(R), dim3(1024), 0, stream, (const float*)logits, stride, V, (const SampleParams*)params,
                                              (long long*)out_ids, (float*)out_logprob);
   HE_LAUNCH_CHECK();
   return 0;
@@ -309,7 +317,7 @@ HE_API int he_topn_logprobs(const void* logits, long long stride, int R, int V, 
 
 HE_API int he_softcap(void* x, long long n, float cap, cudaStream_t stream) {
   if (n <= 0) return 0;
-  softcap_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>((float*)x, n, cap);
+  (void)launch_pdl(softcap_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, (float*)x, n, cap);
   HE_LAUNCH_CHECK();
   return 0;
 }

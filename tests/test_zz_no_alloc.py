@@ -2,6 +2,7 @@
 ordinary entry point (caller-supplied scratch) on two calls in a row.  Collected last on purpose: it must hold
 both in a fresh process and after every other GPU test has used the library."""
 import ctypes as C
+import gc
 
 import pytest
 import torch
@@ -52,10 +53,14 @@ def test_noalloc_matches_regular_entry_point_twice():
         a.partial, a.out = part.data_ptr(), ref.data_ptr()
         assert lib.he_attn_decode(C.byref(a), stream) == 0
         a.partial, a.out = None, out.data_ptr()
-        before = torch.cuda.memory_allocated()
+        # count allocator calls, not live bytes: objects of earlier tests may be garbage-collected (and their
+        # memory freed) at any moment, which says nothing about this call
+        gc.collect()
+        torch.cuda.synchronize()
+        before = torch.cuda.memory_stats().get("allocation.all.allocated", 0)
         assert fn(C.byref(a), stream) == 0, f"call {call}"
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == before
+        assert torch.cuda.memory_stats().get("allocation.all.allocated", 0) == before
         torch.testing.assert_close(out.float(), ref.float(), atol=2e-2, rtol=2e-2)
         assert out.float().abs().max() > 0
 
