@@ -291,7 +291,7 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const __grid_constant_
   int total_items = 0;
   for (int i = 0; i < a.n_seg; ++i) total_items += seg_items(a.seg[i], rg_shift);
   const int upi = (nb + BQ - 1) >> bq_shift;                 // staged units per item
-  const int gw = blockIdx.x * NW + warp;                    // global warp id
+  const int gw = warp * gridDim.x + blockIdx.x;             // global warp id, CTA-first: item i starts on CTA i % grid
   const int tw = gridDim.x * NW;                            // total warps
   const int my_items = gw < total_items ? (total_items - gw + tw - 1) / tw : 0;
   const int my_units = my_items * upi;
@@ -437,7 +437,9 @@ int launch_nw(const HeGemvArgs& a, size_t smem, long long items, int num_sms, cu
     if (e != cudaSuccess) return (int)e;
     configured = smem;
   }
-  long long grid = (items + NW - 1) / NW;
+  // one CTA per SM as soon as there is an item for each: with fewer items than warps the busy warps are spread over
+  // all SMs (the kernel deals items out CTA-first) instead of filling a few CTAs and leaving the other SMs idle
+  long long grid = items;
   if (grid > num_sms) grid = num_sms;
   if (grid < 1) grid = 1;
   static const bool pdl = []() {
