@@ -478,11 +478,12 @@ int launch_gemv(HeGemvArgs a, int num_sms, cudaStream_t stream) {
   a.slot_bytes = 32 * per_block;
   const size_t x_bytes = ((size_t)R * nb * hegemv::XQ_STRIDE + (size_t)R * nb * 8 * 8 + 64 + 127) & ~(size_t)127;
   const size_t budget = 224 * 1024;
-  // 16 warps per CTA when two ring slots each still fit beside the activations, else 8
+  // 16 warps per CTA when two ring slots each still fit beside the activations, else 12, else 8
   int nw = 16;
-  if (x_bytes + (size_t)2 * 16 * a.slot_bytes > budget) nw = 8;
+  if (x_bytes + (size_t)2 * 16 * a.slot_bytes > budget) nw = 12;   // Q6_K / Q8_0 slots: 12 warps x 2 slots still fit
+  if (x_bytes + (size_t)2 * nw * a.slot_bytes > budget) nw = 8;
   static const int nw_env = []() { const char* e = getenv("HE_GEMV_NW"); return e ? atoi(e) : 0; }();
-  if (nw_env == 8) nw = 8;
+  if (nw_env == 8 || (nw_env == 12 && nw == 16)) nw = nw_env;
   int n_slots = MAX_SLOTS;
   while (n_slots > 2 && x_bytes + (size_t)n_slots * nw * a.slot_bytes > budget) --n_slots;
   if (x_bytes + (size_t)n_slots * nw * a.slot_bytes > budget) return -HE_ERR_BAD_ARG;
@@ -515,7 +516,9 @@ int launch_gemv(HeGemvArgs a, int num_sms, cudaStream_t stream) {
     items += (a.seg[i].n_rows + per - 1) / per;
   }
   const size_t smem = x_bytes + (size_t)n_slots * nw * a.slot_bytes;
-  return nw == 16 ? launch_nw<R, 16>(a, smem, items, num_sms, stream) : launch_nw<R, 8>(a, smem, items, num_sms, stream);
+  if (nw == 16) return launch_nw<R, 16>(a, smem, items, num_sms, stream);
+  if (nw == 12) return launch_nw<R, 12>(a, smem, items, num_sms, stream);
+  return launch_nw<R, 8>(a, smem, items, num_sms, stream);
 }
 
 }  // namespace
