@@ -491,9 +491,9 @@ int launch_gemv(HeGemvArgs a, int num_sms, cudaStream_t stream) {
   // rows per item: as many as keeps every warp of the grid busy for at least two items
   const long long warps = (long long)num_sms * nw;
   int rg = 8;
-  if (per_block == 144 && nb >= 20) {
-    // all-Q4_K launch with K >= 5120 (measured on B200; narrower models measured faster with the plain rule
-    // below): what matters is (a) lanes not idling in the last unit of a row --
+  if (nb >= 20) {
+    // K >= 5120, any block type (measured on B200 for Q4_K, Q6_K and Q8_0; narrower models measured faster with the
+    // plain rule below): what matters is (a) lanes not idling in the last unit of a row --
     // a unit is 32/rg blocks wide, so K = 5120 (20 blocks) wants rg = 8, K = 6144 (24 blocks) rg = 4 -- and
     // (b) at least about half as many work items as warps; pick the rg with the best product of the two
     double best = -1.0;
