@@ -146,7 +146,7 @@ class FusedGemmAllReduce:
     device allocations shared through CUDA IPC (single node).  The reference engine is single-device: no counterpart.
     """
 
-    def __init__(self, ctx: DistContext, width: int, max_rows: int = 4096, wait_limit: int = 1 << 22,
+    def __init__(self, ctx: DistContext, width: int, max_rows: int = 4096, wait_limit: int = 1 << 24,
                  _regions: List[int] = None, direct: Optional[bool] = None):
         L = N.lib()
         assert L.he_gemm_fuse_args_size() == C.sizeof(_FuseArgs), "ABI mismatch for FuseArgs"
