@@ -1,6 +1,7 @@
 """Per-kernel micro-benchmarks with roofline fractions.
 
     python -m hipengine_b200.benchmark.micro gemm --m 4096 --n 17408 --k 5120
+    python -m hipengine_b200.benchmark.micro gemmq --m 4096 --n 17408 --k 5120 --qtype q4_k
     python -m hipengine_b200.benchmark.micro gemv --n 17408 --k 5120 --qtype q4_k --rows 1
     python -m hipengine_b200.benchmark.micro all
 
@@ -76,6 +77,38 @@ def bench_gemm(M, N, K, impl="tcgen05"):
     tf = 2.0 * M * N * K / ms / 1e9
     return {"kernel": f"gemm_bf16[{impl}]", "M": M, "N": N, "K": K, "ms": round(ms, 4), "tflops": round(tf, 1),
             f"frac_of_{pk['src']}_bf16": round(tf / pk["bf16_tflops"], 3)}
+
+
+def bench_gemm_quant(M, N, K, qtype="q4_k"):
+    """Tensor-core GEMM over a quantised weight read in its device layout (dequantised inside the pipeline).
+    M > 128: plain tiling, reported against the tensor-core peak; M <= 128: split-K, reported against HBM bandwidth
+    (the weight bytes are what has to move)."""
+    from hipengine_b200.models.executor import _Scratch
+    from hipengine_b200.ops import gemm as G
+    from hipengine_b200.ops import kernels as Kn
+    from hipengine_b200.quant import ggml as Q
+    pk = peaks()
+    t = {"q4_k": Q.GGMLType.Q4_K, "q6_k": Q.GGMLType.Q6_K, "q8_0": Q.GGMLType.Q8_0}[qtype]
+    wbytes = N * Q.row_bytes(t, K)
+    nvar = max(2, int(260e6 // wbytes) + 1)
+    w = torch.randn(N, K, device="cuda") * 0.02
+    raw = Q.quantize(w, t)
+    dws = [Kn.to_device_weight(raw.clone(), t, N, K) for _ in range(nvar)]
+    x = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+    sc = _Scratch(torch.device("cuda", torch.cuda.current_device()))
+    if M > 128:
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        fn = lambda i: G.gemm_quant(x, dws[i], out, sc)
+    else:
+        out = torch.empty(M, N, device="cuda")
+        fn = lambda i: G.gemm_quant_splitk(x, dws[i], out, sc)
+    ms = time_launches(fn, nvar)
+    G.check_status()
+    tf = 2.0 * M * N * K / ms / 1e9
+    gbs = wbytes / ms / 1e6
+    return {"kernel": f"gemm_quant[{qtype}]", "M": M, "N": N, "K": K, "ms": round(ms, 4), "tflops": round(tf, 1),
+            f"frac_of_{pk['src']}_bf16": round(tf / pk["bf16_tflops"], 3), "weight_GBps": round(gbs, 1),
+            f"frac_of_{pk['src']}_hbm": round(gbs / pk["hbm_gbs"], 3)}
 
 
 def bench_gemv(N, K, qtype="q4_k", rows=1):
@@ -196,7 +229,7 @@ def bench_fused_allreduce_gemm(M, N, K, phases=7):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "gemv", "gdn", "conv", "attn", "fusedar", "all"])
+    ap.add_argument("what", choices=["gemm", "gemmq", "gemv", "gdn", "conv", "attn", "fusedar", "all"])
     ap.add_argument("--t", type=int, default=4096)
     ap.add_argument("--ctx", type=int, default=4096)
     ap.add_argument("--m", type=int, default=4096)
@@ -210,6 +243,8 @@ def main():
     out = []
     if a.what == "gemm":
         out.append(bench_gemm(a.m, a.n, a.k, a.impl))
+    elif a.what == "gemmq":
+        out.append(bench_gemm_quant(a.m, a.n, a.k, a.qtype))
     elif a.what == "gemv":
         out.append(bench_gemv(a.n, a.k, a.qtype, a.rows))
     elif a.what == "gdn":
@@ -226,6 +261,12 @@ def main():
         for (m, n, k) in [(4096, 10240, 5120), (4096, 34816, 5120), (4096, 5120, 17408), (4096, 5120, 6144)]:
             out.append(bench_gemm(m, n, k, "tcgen05"))
             out.append(bench_gemm(m, n, k, "cublas"))
+            out.append(bench_gemm_quant(m, n, k, "q4_k"))
+        out.append(bench_gemm_quant(4096, 5120, 17408, "q6_k"))
+        out.append(bench_gemm_quant(4096, 5120, 5120, "q8_0"))
+        for m in (16, 64, 128):
+            for (n, k, q) in [(34816, 5120, "q4_k"), (5120, 17408, "q6_k"), (10240, 5120, "q4_k")]:
+                out.append(bench_gemm_quant(m, n, k, q))
         for (n, k, q) in [(34816, 5120, "q4_k"), (5120, 17408, "q4_k"), (5120, 17408, "q6_k"), (16384, 5120, "q4_k"),
                           (5120, 6144, "q4_k"), (62080, 5120, "q6_k"), (8192, 5120, "q8_0")]:
             for r in (1, 4):

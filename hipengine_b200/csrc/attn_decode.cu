@@ -193,7 +193,9 @@ __global__ void attn_decode_reduce_kernel(const AttnDecArgs a) {
   pdl_launch();
   const int ctx = a.ctx_len[r];
   const int start = (a.window > 0 && ctx > a.window) ? ctx - a.window : 0;
-  const int ns = (ctx - start + a.split_len - 1) / a.split_len;
+  // never past what the split kernel wrote (its grid is max_splits wide) nor past wsm[]: a context longer than
+  // split_len * max_splits is the caller's error and is reduced over the first max_splits splits only
+  const int ns = min((ctx - start + a.split_len - 1) / a.split_len, a.max_splits);
   const float* pb = a.partial + ((size_t)r * a.H + h) * a.max_splits * (D + 2);
   float m = -INFINITY;
   for (int s = d; s < ns; s += blockDim.x) {
@@ -228,12 +230,15 @@ __global__ void attn_decode_reduce_kernel(const AttnDecArgs a) {
 template <int D, int G>
 int launch_split(const AttnDecArgs& a, cudaStream_t stream) {
   const size_t smem = ((size_t)G * D + (size_t)G * a.split_len + (size_t)NWARP * G * D) * sizeof(float);
-  static size_t configured = 0;
-  if (smem > configured) {
+  // the attribute belongs to the (function, device) pair: remember the largest value set per device
+  static size_t configured[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+  if (smem > configured[dev]) {
     cudaError_t e = cudaFuncSetAttribute(attn_decode_split_kernel<D, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem);
     if (e != cudaSuccess) return (int)e;
-    configured = smem;
+    configured[dev] = smem;
   }
   dim3 grid(a.max_splits, a.Hkv, a.R);
   cudaError_t le = launch_pdl(attn_decode_split_kernel<D, G>, grid, dim3(256), smem, stream, a);

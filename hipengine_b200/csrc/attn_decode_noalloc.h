@@ -22,6 +22,10 @@
 //   * The first call on each device looks the array's address up (cudaGetSymbolAddress, with that
 //     device current) and remembers it.  Make that first call before starting any stream capture;
 //     later calls on the same device only launch kernels.
+//     Two first calls on the same device from different host threads only repeat the look-up (both
+//     store the same address), but do not rely on that: make the first call from one thread.
+//   * Every row's context must fit the split grid: ctx_len[r] (or the window, when one is set)
+//     <= split_len * max_splits.  A longer context is reduced over the first max_splits splits only.
 //   * Nothing in the scratch has to start at zero: every value the reduce kernel reads was written by
 //     the split kernel of the same call.
 //   * There is ONE array per device, shared by every call.  Two calls whose kernels can overlap

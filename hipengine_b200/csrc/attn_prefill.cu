@@ -232,12 +232,9 @@ __global__ void __launch_bounds__(NTHR) flash_prefill_kernel(const PrefillArgs a
 template <int D>
 int launch(const PrefillArgs& a, cudaStream_t stream) {
   const size_t smem = (size_t)(BM + 4 * BN) * (D + 8) * sizeof(__nv_bfloat16);
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(flash_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
+  // set per call (cheap): the attribute belongs to the (function, device) pair, not to the process
+  cudaError_t e = cudaFuncSetAttribute(flash_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
   dim3 grid((a.T + BM - 1) / BM, a.H);
   flash_prefill_kernel<D><<<grid, NTHR, smem, stream>>>(a);
   HE_LAUNCH_CHECK();

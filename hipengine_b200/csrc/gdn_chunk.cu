@@ -431,12 +431,9 @@ __global__ void __launch_bounds__(128) gdn_chunk_kernel(const GdnChunkArgs p) {
 template <int NV>
 int launch_chunk(const GdnChunkArgs& a, cudaStream_t stream) {
   const size_t smem = sizeof(Smem<NV>);
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gdn_chunk_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
+  // set per call (cheap): the attribute belongs to the (function, device) pair, not to the process
+  cudaError_t e = cudaFuncSetAttribute(gdn_chunk_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
   dim3 grid(a.n_seg, a.Hv, 128 / NV);
   gdn_chunk_kernel<NV><<<grid, 128, smem, stream>>>(a);
   HE_LAUNCH_CHECK();

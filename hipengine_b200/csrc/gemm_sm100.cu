@@ -26,6 +26,21 @@ constexpr int TMEM_COLS = 512;
 constexpr int NTHREADS = 192;
 constexpr int NTHREADS_FUSED = 320;    // + 4 collective warps (fused GEMM -> all-reduce kernel)
 
+// Quantised-B mode (QM): the weight stays in its GGUF-derived device layout (Q4_K 144-byte blocks, Q6_K 224-byte
+// blocks, Q8_0 int8 + scale planes) all the way into shared memory.  One extra warp streams raw block bytes with
+// 2-D byte-typed TMA boxes into a small ring ("q-stages"); eight unpack warps expand each 64-column slice to bf16
+// straight into the 128-byte-swizzled K-major operand stage that the MMA issuer reads, so DRAM and L2 only ever see
+// 4.5 / 6.6 / 8.5 bits per weight and no bf16 copy of the weight exists anywhere.
+//   Q4_K : q-stage = one 256-column super-block per row (144 B): 4 k-blocks per q-stage
+//   Q6_K : q-stage = one 128-column half block per row (ql 64 B + qh 32 B + scales/d 32 B): 2 k-blocks
+//   Q8_0 : q-stage = 128 columns per row (128 B int8 + the 16-byte scale group of the 256-aligned range): 2 k-blocks
+constexpr int STAGES_Q = 3;            // A / dequantised-B ring depth in QM
+constexpr int QSTAGES = 2;             // raw-block ring depth
+constexpr int Q_STAGE_BYTES = BN * 144;
+constexpr int N_UNPACK_WARPS = 8;
+constexpr int NTHREADS_Q = NTHREADS + 32 * (1 + N_UNPACK_WARPS);
+constexpr int NTHREADS_FUSED_Q = NTHREADS_FUSED + 32 * (1 + N_UNPACK_WARPS);
+
 struct GemmArgs {
   void* C;
   long long ldc;        // elements
@@ -40,6 +55,8 @@ struct GemmArgs {
   // add their partial tiles into the fp32 C with atomics (epi 3).  1 = off.
   int k_splits;
   long long split_stride;   // epi 4: split ks stores its fp32 partial tile at C + ks * split_stride (elements)
+  int qtype;                // QM kernels: HE_Q4_K / HE_Q6_K / HE_Q8_0
+  int kb_per;               // k-blocks per split when > 0 (set by the split-K launchers), else derived from k_splits
 };
 
 // Fused GEMM -> all-reduce -> residual add over peer memory (tensor-parallel row-parallel projections).
@@ -259,30 +276,160 @@ struct __align__(8) Barriers {
   uint64_t empty[STAGES];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
+  uint64_t bfull[STAGES];     // QM: dequantised B slice of the stage is in place (one arrive per unpack warp)
+  uint64_t qfull[QSTAGES];    // QM: raw blocks of the q-stage have landed (TMA bytes)
+  uint64_t qempty[QSTAGES];   // QM: every unpack warp is done with the q-stage
   uint32_t tmem_base;
   int abort_flag;
 };
 
-template <bool FUSE>
-__device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& g,
-                                          const FuseArgs* f) {
+// ---------------------------------------------------------------- in-pipeline dequantisation (QM)
+__device__ __forceinline__ uint32_t prmt_b32(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+  return r;
+}
+__device__ __forceinline__ __nv_bfloat162 bf162_bits(uint32_t v) { return *reinterpret_cast<__nv_bfloat162*>(&v); }
+__device__ __forceinline__ uint32_t bits_bf162(__nv_bfloat162 v) { return *reinterpret_cast<uint32_t*>(&v); }
+
+// Four small unsigned integers (< 128), one per byte of `b4`, become two bf16x2 registers holding
+// (q - sub) * s + add.  A byte q under the high byte 0x43 is the bf16 number 128 + q exactly, so the integer
+// reaches bf16 with one byte permute and one subtract; the scale and offset are applied by a single fused
+// multiply-add (one rounding).
+__device__ __forceinline__ void bytes4_to_bf16(uint32_t b4, __nv_bfloat162 sub, __nv_bfloat162 s, __nv_bfloat162 add,
+                                               uint32_t& o01, uint32_t& o23) {
+  const uint32_t MAGIC = 0x43434343u;
+  const __nv_bfloat162 v0 = __hsub2(bf162_bits(prmt_b32(b4, MAGIC, 0x5140u)), sub);
+  const __nv_bfloat162 v1 = __hsub2(bf162_bits(prmt_b32(b4, MAGIC, 0x7362u)), sub);
+  o01 = bits_bf162(__hfma2(v0, s, add));
+  o23 = bits_bf162(__hfma2(v1, s, add));
+}
+
+// 16-byte chunk `chunk` (0..7) of row `row` in a K-major operand tile with the 128-byte swizzle.
+__device__ __forceinline__ void st_b_chunk(uint8_t* bstage, int row, int chunk, uint4 v) {
+  *reinterpret_cast<uint4*>(bstage + (size_t)row * 128 + (size_t)((chunk ^ (row & 7)) << 4)) = v;
+}
+
+// Q4_K: thread `ut` (0..255) owns weight row `ut` of the tile; k-block c (0..3) of the staged super-block is the 32
+// nibble bytes [16 + 32c, +32) of the 144-byte block: low nibbles = columns 0..31, high nibbles = columns 32..63.
+__device__ __forceinline__ void unpack_q4k(const uint8_t* qst, uint8_t* bstage, int ut, int c) {
+  const uint8_t* blk = qst + (size_t)ut * 144;
+  const uint4 meta = *reinterpret_cast<const uint4*>(blk);
+  const float2 dd = __half22float2(*reinterpret_cast<const __half2*>(&meta.x));
+  uint32_t scw, mnw;   // bytes 0,1: 6-bit scale / min of sub-blocks 2c, 2c+1
+  if (c < 2) {
+    scw = (meta.y & 0x3F3F3F3Fu) >> (16 * c);
+    mnw = (meta.z & 0x3F3F3F3Fu) >> (16 * c);
+  } else {
+    scw = ((meta.w & 0x0F0F0F0Fu) | ((meta.y >> 2) & 0x30303030u)) >> (16 * (c - 2));
+    mnw = (((meta.w >> 4) & 0x0F0F0F0Fu) | ((meta.z >> 2) & 0x30303030u)) >> (16 * (c - 2));
+  }
+  const __nv_bfloat162 s_lo = __float2bfloat162_rn(dd.x * (float)(scw & 0xFFu));
+  const __nv_bfloat162 s_hi = __float2bfloat162_rn(dd.x * (float)((scw >> 8) & 0xFFu));
+  const __nv_bfloat162 m_lo = __float2bfloat162_rn(-dd.y * (float)(mnw & 0xFFu));
+  const __nv_bfloat162 m_hi = __float2bfloat162_rn(-dd.y * (float)((mnw >> 8) & 0xFFu));
+  const __nv_bfloat162 k128 = bf162_bits(0x43004300u);
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const uint4 qv = *reinterpret_cast<const uint4*>(blk + 16 + 32 * c + 16 * half);
+    const uint32_t w[4] = {qv.x, qv.y, qv.z, qv.w};
+    uint32_t lo[8], hi[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      bytes4_to_bf16(w[i] & 0x0F0F0F0Fu, k128, s_lo, m_lo, lo[2 * i], lo[2 * i + 1]);
+      bytes4_to_bf16((w[i] >> 4) & 0x0F0F0F0Fu, k128, s_hi, m_hi, hi[2 * i], hi[2 * i + 1]);
+    }
+    st_b_chunk(bstage, ut, 2 * half, make_uint4(lo[0], lo[1], lo[2], lo[3]));
+    st_b_chunk(bstage, ut, 2 * half + 1, make_uint4(lo[4], lo[5], lo[6], lo[7]));
+    st_b_chunk(bstage, ut, 4 + 2 * half, make_uint4(hi[0], hi[1], hi[2], hi[3]));
+    st_b_chunk(bstage, ut, 4 + 2 * half + 1, make_uint4(hi[4], hi[5], hi[6], hi[7]));
+  }
+}
+
+// Q6_K: the q-stage holds half `h` of each row's block as three dense regions: ql [BN][64], qh [BN][32],
+// tail [BN][32] (16 int8 scales, d).  k-block cb (0 / 1) of the half takes the low / high nibbles of the 64 ql bytes
+// and bit pairs 4cb.. of qh.  A task is (row, 16 ql bytes) = 16 consecutive columns; 4 tasks per thread.
+__device__ __forceinline__ void unpack_q6k(const uint8_t* qst, uint8_t* bstage, int ut, int cb, int h) {
+  const __nv_bfloat162 k160 = bf162_bits(0x43204320u);   // 128 + 32: the stored value is q + 32
+  const __nv_bfloat162 zero = bf162_bits(0u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int id = ut + 256 * i, row = id >> 2, j = id & 3;
+    const uint4 la = *reinterpret_cast<const uint4*>(qst + (size_t)row * 64 + j * 16);
+    const uint4 hq = *reinterpret_cast<const uint4*>(qst + BN * 64 + (size_t)row * 32 + (j & 1) * 16);
+    const uint8_t* tail = qst + BN * 96 + (size_t)row * 32;
+    const int qt = 2 * cb + (j >> 1);
+    const float d = __half2float(*reinterpret_cast<const __half*>(tail + 16));
+    const float sc = (float)reinterpret_cast<const int8_t*>(tail)[h * 8 + 2 * qt + (j & 1)];
+    const __nv_bfloat162 s = __float2bfloat162_rn(d * sc);
+    const uint32_t lw[4] = {la.x, la.y, la.z, la.w}, hw[4] = {hq.x, hq.y, hq.z, hq.w};
+    uint32_t o[8];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const uint32_t nib = (cb ? (lw[u] >> 4) : lw[u]) & 0x0F0F0F0Fu;
+      const uint32_t q4 = nib | (((hw[u] >> (2 * qt)) & 0x03030303u) << 4);
+      bytes4_to_bf16(q4, k160, s, zero, o[2 * u], o[2 * u + 1]);
+    }
+    st_b_chunk(bstage, row, 2 * j, make_uint4(o[0], o[1], o[2], o[3]));
+    st_b_chunk(bstage, row, 2 * j + 1, make_uint4(o[4], o[5], o[6], o[7]));
+  }
+}
+
+// Q8_0: the q-stage holds 128 int8 columns per row ([BN][128]) and the 16-byte group of eight fp16 scales of the
+// 256-aligned column range ([BN][16]); `par` = which half of that range this q-stage is.  A task is (row, 16 int8).
+__device__ __forceinline__ void unpack_q80(const uint8_t* qst, uint8_t* bstage, int ut, int cb, int par) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int id = ut + 256 * i, row = id >> 2, j = id & 3;
+    const uint4 qv = *reinterpret_cast<const uint4*>(qst + (size_t)row * 128 + cb * 64 + j * 16);
+    const float d =
+        __half2float(reinterpret_cast<const __half*>(qst + BN * 128 + (size_t)row * 16)[par * 4 + cb * 2 + (j >> 1)]);
+    const uint32_t w[4] = {qv.x, qv.y, qv.z, qv.w};
+    uint32_t o[8];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const float f0 = d * (float)(int8_t)(w[u] & 0xFFu), f1 = d * (float)(int8_t)((w[u] >> 8) & 0xFFu);
+      const float f2 = d * (float)(int8_t)((w[u] >> 16) & 0xFFu), f3 = d * (float)(int8_t)(w[u] >> 24);
+      o[2 * u] = bits_bf162(__floats2bfloat162_rn(f0, f1));
+      o[2 * u + 1] = bits_bf162(__floats2bfloat162_rn(f2, f3));
+    }
+    st_b_chunk(bstage, row, 2 * j, make_uint4(o[0], o[1], o[2], o[3]));
+    st_b_chunk(bstage, row, 2 * j + 1, make_uint4(o[4], o[5], o[6], o[7]));
+  }
+}
+
+__device__ __forceinline__ int q_kb_per_stage(int qtype) { return qtype == HE_Q4_K ? 4 : 2; }
+
+template <bool FUSE, bool QM>
+__device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmQ1,
+                                          const CUtensorMap& tmQ2, const GemmArgs& g, const FuseArgs* f) {
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment for the swizzled tiles
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  Barriers* bar = reinterpret_cast<Barriers*>(smem + STAGES * STAGE_BYTES);
+  constexpr int NST = QM ? STAGES_Q : STAGES;
+  uint8_t* qring = smem + NST * STAGE_BYTES;                     // QM only: QSTAGES x Q_STAGE_BYTES
+  Barriers* bar = reinterpret_cast<Barriers*>(smem + NST * STAGE_BYTES + (QM ? QSTAGES * Q_STAGE_BYTES : 0));
   volatile int* abort_flag = &bar->abort_flag;
+  constexpr int WARP_Q = FUSE ? 10 : 6;                          // QM: raw-block producer warp, then the unpack warps
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (g.M + BM - 1) / BM, tiles_n = (g.N + BN - 1) / BN;
   const int ksp = g.k_splits > 1 ? g.k_splits : 1;
   const int n_tiles = (FUSE && !(f->phases & 1)) ? 0 : tiles_m * tiles_n * ksp;
   const int k_blocks_all = (g.K + BK - 1) / BK;
-  const int kb_per = (k_blocks_all + ksp - 1) / ksp;      // k-blocks per split (the last split may get fewer)
+  // k-blocks per split (the last split may get fewer); in QM the launcher makes it a multiple of 4, so that every
+  // split starts on a 256-column boundary (whole q-stages)
+  const int kb_per = g.kb_per > 0 ? g.kb_per : (k_blocks_all + ksp - 1) / ksp;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
+    for (int s = 0; s < NST; ++s) {
       mbar_init(&bar->full[s], 1);
       mbar_init(&bar->empty[s], 1);
+      mbar_init(&bar->bfull[s], N_UNPACK_WARPS);
+    }
+    for (int s = 0; s < QSTAGES; ++s) {
+      mbar_init(&bar->qfull[s], 1);
+      mbar_init(&bar->qempty[s], N_UNPACK_WARPS);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&bar->acc_full[a], 1);
@@ -303,10 +450,10 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
   if constexpr (FUSE) fuse_epoch = *reinterpret_cast<volatile uint32_t*>(f->sync) + 1;
 
   if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------ TMA producer (A, and B when it is bf16)
     if (elect_one()) {
       tma_prefetch_desc(&tmA);
-      tma_prefetch_desc(&tmB);
+      if constexpr (!QM) tma_prefetch_desc(&tmB);
       uint32_t it = 0;
       for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
         const int ks = tile % ksp, mn = tile / ksp;
@@ -319,13 +466,13 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
         }
         const int kb0 = ks * kb_per, kb1 = min(k_blocks_all, kb0 + kb_per);
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
+          const int s = it % NST;
+          const uint32_t ph = (it / NST) & 1;
           if (!mbar_wait(&bar->empty[s], ph ^ 1, abort_flag, g.status, 101)) break;
-          mbar_expect_tx(&bar->full[s], STAGE_BYTES);
+          mbar_expect_tx(&bar->full[s], QM ? A_BYTES : STAGE_BYTES);
           uint8_t* sa = smem + s * STAGE_BYTES;
           tma_load_2d(sa, &tmA, &bar->full[s], kb * BK, tm * BM);
-          tma_load_2d(sa + A_BYTES, &tmB, &bar->full[s], kb * BK, b_row0);
+          if constexpr (!QM) tma_load_2d(sa + A_BYTES, &tmB, &bar->full[s], kb * BK, b_row0);
         }
         if (*abort_flag) break;
       }
@@ -345,9 +492,12 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * ACC_COLS;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
+          const int s = it % NST;
+          const uint32_t ph = (it / NST) & 1;
           if (!mbar_wait(&bar->full[s], ph, abort_flag, g.status, 103)) break;
+          if constexpr (QM) {
+            if (!mbar_wait(&bar->bfull[s], ph, abort_flag, g.status, 105)) break;
+          }
           tc_fence_after();
           const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
           const uint32_t b_addr = a_addr + A_BYTES;
@@ -363,6 +513,78 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
         umma_commit(&bar->acc_full[acc]);
         ++tcount;
       }
+    }
+  } else if (QM && warp == WARP_Q) {
+    // ------------------------------------------------------------ raw-block producer (QM)
+    if (elect_one()) {
+      tma_prefetch_desc(&tmB);
+      const int kbq = q_kb_per_stage(g.qtype);
+      uint32_t qit = 0;
+      for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+        const int ks = tile % ksp, mn = tile / ksp;
+        const int tm = mn % tiles_m, tn = mn / tiles_m;
+        int b_row0 = tn * BN;
+        if (g.tile_group != nullptr) {
+          const int grp = __ldg(g.tile_group + tm);
+          if (grp < 0) continue;
+          b_row0 += grp * g.N;
+        }
+        const int kb0 = ks * kb_per, kb1 = min(k_blocks_all, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; kb += kbq, ++qit) {
+          const int qs = qit % QSTAGES;
+          const uint32_t ph = (qit / QSTAGES) & 1;
+          if (!mbar_wait(&bar->qempty[qs], ph ^ 1, abort_flag, g.status, 106)) break;
+          uint8_t* dst = qring + qs * Q_STAGE_BYTES;
+          uint64_t* fb = &bar->qfull[qs];
+          const int qi = kb / kbq;                      // q-stage index along K
+          if (g.qtype == HE_Q4_K) {
+            mbar_expect_tx(fb, BN * 144);
+            tma_load_2d(dst, &tmB, fb, qi * 144, b_row0);
+          } else if (g.qtype == HE_Q6_K) {
+            const int sb = qi >> 1, h = qi & 1;
+            mbar_expect_tx(fb, BN * 128);
+            tma_load_2d(dst, &tmB, fb, sb * 224 + 64 * h, b_row0);
+            tma_load_2d(dst + BN * 64, &tmQ1, fb, sb * 224 + 128 + 32 * h, b_row0);
+            tma_load_2d(dst + BN * 96, &tmQ2, fb, sb * 224 + 192, b_row0);
+          } else {
+            mbar_expect_tx(fb, BN * 144);
+            tma_load_2d(dst, &tmB, fb, qi * 128, b_row0);
+            tma_load_2d(dst + BN * 128, &tmQ1, fb, g.K + 16 * (qi >> 1), b_row0);
+          }
+        }
+        if (*abort_flag) break;
+      }
+    }
+  } else if (QM && warp > WARP_Q) {
+    // ------------------------------------------------------------ unpack warps (QM): raw blocks -> bf16 operand stage
+    const int ut = (int)threadIdx.x - (WARP_Q + 1) * 32;
+    const int kbq = q_kb_per_stage(g.qtype);
+    uint32_t it = 0, qit = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+      if (g.tile_group != nullptr && __ldg(g.tile_group + (tile / ksp) % tiles_m) < 0) continue;
+      const int kb0 = (tile % ksp) * kb_per, kb1 = min(k_blocks_all, kb0 + kb_per);
+      bool ok = true;
+      for (int kb = kb0; kb < kb1 && ok; kb += kbq, ++qit) {
+        const int qs = qit % QSTAGES;
+        if (!mbar_wait(&bar->qfull[qs], (qit / QSTAGES) & 1, abort_flag, g.status, 107)) { ok = false; break; }
+        const uint8_t* qst = qring + qs * Q_STAGE_BYTES;
+        const int qi = kb / kbq;
+        for (int c = 0; c < kbq; ++c, ++it) {
+          const int s = it % NST;
+          if (!mbar_wait(&bar->empty[s], ((it / NST) & 1) ^ 1, abort_flag, g.status, 108)) { ok = false; break; }
+          uint8_t* bstage = smem + s * STAGE_BYTES + A_BYTES;
+          if (g.qtype == HE_Q4_K) unpack_q4k(qst, bstage, ut, c);
+          else if (g.qtype == HE_Q6_K) unpack_q6k(qst, bstage, ut, c, qi & 1);
+          else unpack_q80(qst, bstage, ut, c, qi & 1);
+          fence_proxy_async_smem();      // the tensor core reads the stage through the async proxy
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bar->bfull[s]);
+        }
+        if (!ok) break;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar->qempty[qs]);
+      }
+      if (!ok || *abort_flag) break;
     }
   } else if (warp < 6) {
     // ------------------------------------------------------------ epilogue (warps 2..5)
@@ -482,7 +704,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
       }
       ++tcount;
     }
-  } else {
+  } else if (warp < 10) {
     // ------------------------------------------------------------ collective warps 6..9 (fused kernel only)
     // Warp 6+q reduces quarter q of the tiles this rank owns (phase 2) and adds quarter q of this CTA's share of
     // all tiles into the residual (phase 3) while the other warps keep the tensor cores busy.  It takes whichever
@@ -545,13 +767,27 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
 
 __global__ void __launch_bounds__(NTHREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmArgs g) {
-  gemm_body<false>(tmA, tmB, g, nullptr);
+  gemm_body<false, false>(tmA, tmB, tmB, tmB, g, nullptr);
 }
 
 __global__ void __launch_bounds__(NTHREADS_FUSED, 1)
 gemm_bf16_allreduce_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                            const GemmArgs g, const __grid_constant__ FuseArgs f) {
-  gemm_body<true>(tmA, tmB, g, &f);
+  gemm_body<true, false>(tmA, tmB, tmB, tmB, g, &f);
+}
+
+// The same pipelines with the weight read in its quantised device layout (tmQ0..2: byte-typed maps over the rows).
+__global__ void __launch_bounds__(NTHREADS_Q, 1)
+gemm_q_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmQ0,
+              const __grid_constant__ CUtensorMap tmQ1, const __grid_constant__ CUtensorMap tmQ2, const GemmArgs g) {
+  gemm_body<false, true>(tmA, tmQ0, tmQ1, tmQ2, g, nullptr);
+}
+
+__global__ void __launch_bounds__(NTHREADS_FUSED_Q, 1)
+gemm_q_allreduce_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmQ0,
+                        const __grid_constant__ CUtensorMap tmQ1, const __grid_constant__ CUtensorMap tmQ2,
+                        const GemmArgs g, const __grid_constant__ FuseArgs f) {
+  gemm_body<true, true>(tmA, tmQ0, tmQ1, tmQ2, g, &f);
 }
 
 // ---------------------------------------------------------------- host side: tensor maps
@@ -586,6 +822,56 @@ int make_map(CUtensorMap* m, const void* ptr, long long rows, long long cols, lo
   return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
 }
 
+// Byte-typed 2-D map over quantised weight rows: [rows][row_bytes] uint8, box = {box_bytes, BN rows}, no swizzle.
+int make_byte_map(CUtensorMap* m, const void* ptr, long long rows, long long row_bytes, int box_bytes) {
+  EncodeTiledFn enc = get_encode();
+  if (enc == nullptr) return -HE_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0 || row_bytes % 16 != 0 || box_bytes % 16 != 0) return -HE_ERR_BAD_ARG;
+  cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
+  cuuint32_t box[2] = {(cuuint32_t)box_bytes, (cuuint32_t)BN};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
+}
+
+struct QMaps {
+  CUtensorMap m[3];
+};
+
+// Maps for the raw-block boxes of each type (see the q-stage table at the top of the file).
+int make_qmaps(QMaps* q, const void* B, int qtype, long long rows, int K) {
+  if (K % 256 != 0) return -HE_ERR_BAD_ARG;
+  int rc;
+  if (qtype == HE_Q4_K) {
+    const long long rb = (long long)(K >> 8) * 144;
+    rc = make_byte_map(&q->m[0], B, rows, rb, 144);
+    q->m[1] = q->m[0];
+    q->m[2] = q->m[0];
+    return rc;
+  }
+  if (qtype == HE_Q6_K) {
+    const long long rb = (long long)(K >> 8) * 224;
+    if ((rc = make_byte_map(&q->m[0], B, rows, rb, 64)) != 0) return rc;
+    if ((rc = make_byte_map(&q->m[1], B, rows, rb, 32)) != 0) return rc;
+    q->m[2] = q->m[1];
+    return 0;
+  }
+  if (qtype == HE_Q8_0) {
+    const long long rb = (long long)K + (((K >> 4) + 15) / 16) * 16;
+    if ((rc = make_byte_map(&q->m[0], B, rows, rb, 128)) != 0) return rc;
+    if ((rc = make_byte_map(&q->m[1], B, rows, rb, 16)) != 0) return rc;
+    q->m[2] = q->m[1];
+    return 0;
+  }
+  return -HE_ERR_BAD_ARG;
+}
+
+constexpr size_t SMEM_BF16 = STAGES * STAGE_BYTES + sizeof(Barriers) + 1024;
+constexpr size_t SMEM_Q = STAGES_Q * STAGE_BYTES + QSTAGES * Q_STAGE_BYTES + sizeof(Barriers) + 1024;
+
 }  // namespace
 
 // C[M][N] = A[M][K] (bf16, row stride lda) * B[N][K]^T (bf16, row stride ldb).
@@ -600,18 +886,17 @@ HE_API int he_gemm_bf16(const void* A, long long lda, const void* B, long long l
   if (rc != 0) return rc;
   rc = make_map(&tmB, B, N, K, ldb, BN);
   if (rc != 0) return rc;
-  GemmArgs g;
+  GemmArgs g = {};
   g.C = C; g.ldc = ldc; g.resid = nullptr; g.M = M; g.N = N; g.K = K; g.epi = epi; g.status = (int*)status;
   g.tile_group = nullptr;
   g.k_splits = 1;
   g.split_stride = 0;
+  g.qtype = 0;
+  g.kb_per = 0;
   const size_t smem = STAGES * STAGE_BYTES + sizeof(Barriers) + 1024;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
+  // the attribute is per device: set it on every call (cheap) rather than once per process
+  cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < num_sms ? tiles : num_sms;
   gemm_bf16_kernel<<<grid, NTHREADS, smem, stream>>>(tmA, tmB, g);
@@ -645,11 +930,13 @@ HE_API int he_gemm_bf16_allreduce(const void* A, long long lda, const void* B, l
   if (rc != 0) return rc;
   rc = make_map(&tmB, B, N, K, ldb, BN);
   if (rc != 0) return rc;
-  GemmArgs g;
+  GemmArgs g = {};
   g.C = nullptr; g.ldc = 0; g.resid = nullptr; g.M = M; g.N = N; g.K = K; g.epi = 5; g.status = (int*)status;
   g.tile_group = nullptr;
   g.k_splits = 1;
   g.split_stride = 0;
+  g.qtype = 0;
+  g.kb_per = 0;
   const size_t smem = STAGES * STAGE_BYTES + sizeof(Barriers) + 1024;
   cudaError_t e = cudaFuncSetAttribute(gemm_bf16_allreduce_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)smem);
@@ -674,11 +961,13 @@ HE_API int he_gemm_bf16_grouped(const void* A, long long lda, const void* B, lon
   if (rc != 0) return rc;
   rc = make_map(&tmB, B, (long long)n_groups * N, K, ldb, BN);
   if (rc != 0) return rc;
-  GemmArgs g;
+  GemmArgs g = {};
   g.C = C; g.ldc = ldc; g.resid = nullptr; g.M = M; g.N = N; g.K = K; g.epi = epi; g.status = (int*)status;
   g.tile_group = tile_group;
   g.k_splits = 1;
   g.split_stride = 0;
+  g.qtype = 0;
+  g.kb_per = 0;
   const size_t smem = STAGES * STAGE_BYTES + sizeof(Barriers) + 1024;
   cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
@@ -738,7 +1027,7 @@ HE_API int he_gemm_bf16_splitk_det(const void* A, long long lda, const void* B, 
   rc = make_map(&tmB, B, N, K, ldb, BN);
   if (rc != 0) return rc;
   const int k_splits = (int)he_gemm_splitk_plan(M, N, K, num_sms);
-  GemmArgs g;
+  GemmArgs g = {};
   g.C = partials; g.ldc = N; g.resid = nullptr; g.M = M; g.N = N; g.K = K; g.epi = 4; g.status = (int*)status;
   g.tile_group = nullptr;
   g.k_splits = k_splits;
@@ -773,7 +1062,7 @@ HE_API int he_gemm_bf16_splitk(const void* A, long long lda, const void* B, long
   if (k_splits < 1) k_splits = 1;
   const int kb_per = (k_blocks + k_splits - 1) / k_splits;
   k_splits = (k_blocks + kb_per - 1) / kb_per;            // no empty split
-  GemmArgs g;
+  GemmArgs g = {};
   g.C = C; g.ldc = ldc; g.resid = nullptr; g.M = M; g.N = N; g.K = K; g.epi = 3; g.status = (int*)status;
   g.tile_group = nullptr;
   g.k_splits = k_splits;
@@ -784,6 +1073,123 @@ HE_API int he_gemm_bf16_splitk(const void* A, long long lda, const void* B, long
   const int total = tiles * k_splits;
   const int grid = total < num_sms ? total : num_sms;
   gemm_bf16_kernel<<<grid, NTHREADS, smem, stream>>>(tmA, tmB, g);
+  HE_LAUNCH_CHECK();
+  return 0;
+}
+
+// ---------------------------------------------------------------- quantised-weight entry points
+// C[M][N] = A[M][K] (bf16) * W[N][K]^T where W is `b_rows` rows in the device layout of `qtype` (Q4_K / Q6_K / Q8_0),
+// dequantised inside the pipeline.  epi as he_gemm_bf16.  With `tile_group` (device, ceil(M/128) ints) the call is the
+// grouped form: M-tile tm uses weight rows [tile_group[tm] * N, +N); negative entries skip the tile.
+// `a_cols` (<= K, multiple of 8) is the number of columns A really has: columns up to K read as zeros (weights whose K
+// was padded to a whole number of 256-column blocks).
+HE_API int he_gemm_q(const void* A, long long lda, int a_cols, const void* B, int qtype, long long b_rows, void* C,
+                     long long ldc, int M, int N, int K, int epi, const int* tile_group, void* status, int num_sms,
+                     cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (a_cols <= 0 || a_cols > K || a_cols % 8 != 0) return -HE_ERR_BAD_ARG;
+  CUtensorMap tmA;
+  QMaps q;
+  int rc = make_map(&tmA, A, M, a_cols, lda, BM);
+  if (rc != 0) return rc;
+  rc = make_qmaps(&q, B, qtype, b_rows, K);
+  if (rc != 0) return rc;
+  GemmArgs g = {};
+  g.C = C; g.ldc = ldc; g.resid = nullptr; g.M = M; g.N = N; g.K = K; g.epi = epi; g.status = (int*)status;
+  g.tile_group = tile_group;
+  g.k_splits = 1;
+  g.split_stride = 0;
+  g.qtype = qtype;
+  g.kb_per = 0;
+  cudaError_t e = cudaFuncSetAttribute(gemm_q_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_Q);
+  if (e != cudaSuccess) return (int)e;
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  gemm_q_kernel<<<tiles < num_sms ? tiles : num_sms, NTHREADS_Q, SMEM_Q, stream>>>(tmA, q.m[0], q.m[1], q.m[2], g);
+  HE_LAUNCH_CHECK();
+  return 0;
+}
+
+// Split count of the deterministic split-K form for a quantised weight: about one tile per SM, every split a whole
+// number of 256-column blocks and none empty.  The low 32 bits are the split count, the high 32 bits the k-blocks
+// (of 64 columns) per split.
+HE_API long long he_gemm_q_splitk_plan(int M, int N, int K, int num_sms) {
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int k_blocks = (K + BK - 1) / BK;
+  int k_splits = (num_sms + tiles - 1) / tiles;
+  if (k_splits < 1) k_splits = 1;
+  int kb_per = (k_blocks + k_splits - 1) / k_splits;
+  kb_per = (kb_per + 3) & ~3;
+  k_splits = (k_blocks + kb_per - 1) / kb_per;
+  return ((long long)kb_per << 32) | (long long)k_splits;
+}
+
+// out[M][N] (fp32) = (mode 0) or += (mode 1) A * W^T, K split over CTAs so that every SM streams a share of the
+// quantised weight; partial tiles go to `partials` ([k_splits][M][N] fp32) and are summed in split order.
+HE_API int he_gemm_q_splitk_det(const void* A, long long lda, const void* B, int qtype, long long b_rows,
+                                void* partials, void* out, long long ldo, int M, int N, int K, int mode, void* status,
+                                int num_sms, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (N % 4 != 0) return -HE_ERR_BAD_ARG;
+  CUtensorMap tmA;
+  QMaps q;
+  int rc = make_map(&tmA, A, M, K, lda, BM);
+  if (rc != 0) return rc;
+  rc = make_qmaps(&q, B, qtype, b_rows, K);
+  if (rc != 0) return rc;
+  const long long plan = he_gemm_q_splitk_plan(M, N, K, num_sms);
+  const int k_splits = (int)(plan & 0xffffffffll);
+  GemmArgs g = {};
+  g.C = partials; g.ldc = N; g.resid = nullptr; g.M = M; g.N = N; g.K = K; g.epi = 4; g.status = (int*)status;
+  g.tile_group = nullptr;
+  g.k_splits = k_splits;
+  g.split_stride = (long long)M * N;
+  g.qtype = qtype;
+  g.kb_per = (int)(plan >> 32);
+  cudaError_t e = cudaFuncSetAttribute(gemm_q_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_Q);
+  if (e != cudaSuccess) return (int)e;
+  const int total = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * k_splits;
+  gemm_q_kernel<<<total < num_sms ? total : num_sms, NTHREADS_Q, SMEM_Q, stream>>>(tmA, q.m[0], q.m[1], q.m[2], g);
+  HE_LAUNCH_CHECK();
+  const long long n4 = ((long long)M * N + 3) / 4;
+  splitk_reduce_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>((const float*)partials, g.split_stride,
+                                                                        k_splits, (float*)out, ldo, M, N, mode);
+  HE_LAUNCH_CHECK();
+  return 0;
+}
+
+// The fused GEMM -> all-reduce -> residual add of he_gemm_bf16_allreduce with a quantised weight.
+HE_API int he_gemm_q_allreduce(const void* A, long long lda, const void* B, int qtype, long long b_rows, int M, int N,
+                               int K, const FuseArgs* fuse, void* status, int num_sms, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  const FuseArgs& f = *fuse;
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  if (N % 8 != 0) return -HE_ERR_BAD_ARG;
+  if (f.world < 1 || f.world > FUSE_MAX_WORLD || f.rank < 0 || f.rank >= f.world) return -HE_ERR_BAD_ARG;
+  if (tiles > f.max_tiles || (f.direct ? tiles : (tiles + f.world - 1) / f.world) > f.owned_cap)
+    return -HE_ERR_BAD_ARG;
+  if (f.resid == nullptr || (reinterpret_cast<uintptr_t>(f.resid) & 15) != 0 || f.ld_resid % 4 != 0 || f.ld_resid < N)
+    return -HE_ERR_BAD_ARG;
+  if ((f.phases & 7) == 0 || f.sync == nullptr) return -HE_ERR_BAD_ARG;
+  for (int r = 0; r < f.world; ++r)
+    if (f.stage[r] == nullptr || f.result[r] == nullptr || f.flags[r] == nullptr) return -HE_ERR_BAD_ARG;
+  CUtensorMap tmA;
+  QMaps q;
+  int rc = make_map(&tmA, A, M, K, lda, BM);
+  if (rc != 0) return rc;
+  rc = make_qmaps(&q, B, qtype, b_rows, K);
+  if (rc != 0) return rc;
+  GemmArgs g = {};
+  g.C = nullptr; g.ldc = 0; g.resid = nullptr; g.M = M; g.N = N; g.K = K; g.epi = 5; g.status = (int*)status;
+  g.tile_group = nullptr;
+  g.k_splits = 1;
+  g.split_stride = 0;
+  g.qtype = qtype;
+  g.kb_per = 0;
+  cudaError_t e = cudaFuncSetAttribute(gemm_q_allreduce_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)SMEM_Q);
+  if (e != cudaSuccess) return (int)e;
+  const int grid = tiles < num_sms ? tiles : num_sms;
+  gemm_q_allreduce_kernel<<<grid, NTHREADS_FUSED_Q, SMEM_Q, stream>>>(tmA, q.m[0], q.m[1], q.m[2], g, f);
   HE_LAUNCH_CHECK();
   return 0;
 }

@@ -431,11 +431,13 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const __grid_constant_
 
 template <int R, int NW>
 int launch_nw(const HeGemvArgs& a, size_t smem, long long items, int num_sms, cudaStream_t stream) {
-  static size_t configured = 0;
-  if (smem > configured) {
+  static size_t configured[64] = {};   // per device: the attribute belongs to the (function, device) pair
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+  if (smem > configured[dev]) {
     cudaError_t e = cudaFuncSetAttribute(gemv_kernel<R, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    configured = smem;
+    configured[dev] = smem;
   }
   // one CTA per SM as soon as there is an item for each: with fewer items than warps the busy warps are spread over
   // all SMs (the kernel deals items out CTA-first) instead of filling a few CTAs and leaving the other SMs idle

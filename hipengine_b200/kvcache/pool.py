@@ -112,11 +112,19 @@ class PagePool:
         n_sh = len(shared_prefix)
         need_now = max(self.pages_for(now_tokens), n_sh) - n_sh
         credit = max(0, need_total - n_sh - need_now)
-        if need_now + credit > self.n_available + self._reclaimable():
-            raise PoolExhausted(f"request needs {need_now + credit} pages; {self.n_available} available")
-        pages = self._take(need_now)
+        # Reference the shared prefix FIRST: from here on its pages are neither counted as reclaimable nor offered
+        # to the eviction hook, so making room for the private pages can never hand a matched prefix page back as
+        # one of this lease's own pages.
         for p in shared_prefix:
             self.refcount[p] += 1
+        try:
+            if need_now + credit > self.n_available + self._reclaimable():
+                raise PoolExhausted(f"request needs {need_now + credit} pages; {self.n_available} available")
+            pages = self._take(need_now)
+        except PoolExhausted:
+            for p in shared_prefix:
+                self._unref(p)
+            raise
         for p in pages:
             self.refcount[p] = 1
         lease = KVLease(owner, list(shared_prefix) + pages, n_sh, credit, 0)

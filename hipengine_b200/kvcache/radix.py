@@ -148,20 +148,25 @@ class RadixCache:
         return out
 
     def evict(self, n_pages: int) -> List[int]:
-        """Evict up to ``n_pages`` least-recently-used unreferenced leaf pages; returns the freed page ids."""
+        """Evict up to ``n_pages`` unreferenced leaf pages in strict least-recently-used order; returns the freed
+        page ids.  A parent that becomes a leaf when its last child goes joins the candidates at once (heap), so an
+        old interior node is taken before a recently used leaf."""
+        import heapq
         freed: List[int] = []
-        while len(freed) < n_pages:
-            leaves = [l for l in self._leaves() if self.page_refcount(l.page) == 0]
-            if not leaves:
-                break
-            leaves.sort(key=lambda l: l.last_used)
-            for leaf in leaves:
-                if len(freed) >= n_pages:
-                    break
-                if self.on_evict_node is not None:
-                    self.on_evict_node(self.token_path(leaf), leaf.page, leaf.snapshot)
-                self._remove(leaf)
-                freed.append(leaf.page)
+        heap = [(l.last_used, id(l), l) for l in self._leaves() if self.page_refcount(l.page) == 0]
+        heapq.heapify(heap)
+        while heap and len(freed) < n_pages:
+            _, _, leaf = heapq.heappop(heap)
+            if leaf.children or self.page_refcount(leaf.page) != 0:
+                continue
+            parent = leaf.parent
+            if self.on_evict_node is not None:
+                self.on_evict_node(self.token_path(leaf), leaf.page, leaf.snapshot)
+            self._remove(leaf)
+            freed.append(leaf.page)
+            if (parent is not None and parent is not self.root and not parent.children
+                    and self.page_refcount(parent.page) == 0):
+                heapq.heappush(heap, (parent.last_used, id(parent), parent))
         if freed:
             self.on_release(freed)
             self.stats["evicted_pages"] += len(freed)

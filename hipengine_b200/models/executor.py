@@ -124,15 +124,13 @@ class HybridExecutor:
         self.gemm_impl = gemm_impl or os.environ.get("HE_GEMM", "tcgen05")
         self.scratch = _Scratch(self.device)
         # packed batches of up to small_rows rows take the quantised GEMV path, larger ones the tensor-core path
-        # (measured on the 27B geometry: the int8 GEMV costs ~3.4 ms per extra row, the split-K tensor-core path
-        # ~20 ms per step for any row count up to 16, so they cross between 5 and 6 rows)
+        # (the int8 GEMV costs a few ms per extra row on the 27B geometry; the split-K tensor-core path streams the
+        # same quantised blocks once for any row count up to 128)
         self.small_rows = min(GEMV_MAX_ROWS, int(os.environ.get("HE_SMALL_ROWS", "6")))
-        self.shadow: Optional[dict] = None      # resident bf16 expansions for the tensor-core path (set below)
         self.dw: Dict[str, DeviceWeight] = {}
         self.f32: Dict[str, torch.Tensor] = {}
         self._load(weights)
         self._alloc_state()
-        self._init_shadow()
 
     # ------------------------------------------------------------------ weights
     def _load(self, weights: ModelWeights) -> None:
@@ -165,18 +163,6 @@ class HybridExecutor:
                 if ab.shape[1] % 256 == 0 and os.environ.get("HE_AB_Q8", "1") != "0":
                     raw = quantize(ab, GGMLType.Q8_0).reshape(ab.shape[0], -1).contiguous()
                     self.ab_q8[i] = K.to_device_weight(raw, GGMLType.Q8_0, ab.shape[0], ab.shape[1])
-
-    def _init_shadow(self) -> None:
-        """B200 has HBM to spare: keep bf16 expansions of the projection weights resident for prefill / verify
-        GEMMs (decode still streams the 4-bit blocks).  ``HE_BF16_SHADOW`` = 0 | 1 | auto (default: on when at
-        least a third of the device memory is still free, using at most half of what is free)."""
-        mode = os.environ.get("HE_BF16_SHADOW", "auto")
-        if mode == "0" or self.device.type != "cuda":
-            return
-        free, total = torch.cuda.mem_get_info(self.device)
-        if mode == "auto" and free < total // 3:
-            return
-        self.shadow = {"_left": int(free * 0.5)}
 
     def W(self, i: int, slot: str) -> DeviceWeight:
         return self.dw[f"blk.{i}.{slot}"]
@@ -230,7 +216,7 @@ class HybridExecutor:
         rows = w.n_rows - row0 if rows is None else rows
         if self.gemm_impl == "tcgen05":
             from ..ops import gemm as G
-            return G.gemm_quant(x, w, out, self.scratch, row0=row0, rows=rows, shadow=self.shadow)
+            return G.gemm_quant(x, w, out, self.scratch, row0=row0, rows=rows)
         wb = self.scratch.get("deq_" + tag, (rows, w.n_cols), torch.bfloat16)
         K.dequant_bf16(w, wb, row0=row0, rows=rows)
         torch.matmul(x, wb.t(), out=out)
@@ -250,7 +236,7 @@ class HybridExecutor:
         if self._use_splitk(T):
             from ..ops import gemm as GM
             acc = out if out is not None else self.scratch.get(name + "_f32", (T, w.n_rows), torch.float32)
-            return GM.gemm_bf16_splitk_det(x, GM.bf16_weight(w, self.scratch, self.shadow), acc, self.scratch)
+            return GM.gemm_quant_splitk(x, w, acc, self.scratch)
         dst = out if out is not None else self.scratch.get(name + "_bf", (T, w.n_rows), torch.bfloat16)
         return self._gemm(x, w, dst, tag=tag)
 
@@ -265,12 +251,12 @@ class HybridExecutor:
             # few rows against a hidden-wide output is only ~20 tiles: split K over the SMs and let the tiles add
             # themselves into the fp32 residual (which is the residual add)
             from ..ops import gemm as GM
-            GM.gemm_bf16_splitk_det(x, GM.bf16_weight(w, self.scratch, self.shadow), h, self.scratch, add=True)
+            GM.gemm_quant_splitk(x, w, h, self.scratch, add=True)
             return
         if self.gemm_impl == "tcgen05" and h.is_contiguous():
             # accumulate straight into the fp32 residual in the GEMM epilogue (one CTA per tile: plain +=)
             from ..ops import gemm as GM
-            GM.gemm_quant(x, w, h, self.scratch, epi=2, shadow=self.shadow)
+            GM.gemm_quant(x, w, h, self.scratch, epi=2)
             return
         y = self._gemm(x, w, self.scratch.get("y_bf", (T, w.n_rows), torch.bfloat16), tag=tag)
         K.resid_add_bf16(h, y)
@@ -426,8 +412,8 @@ class HybridExecutor:
             if self._use_splitk(T):
                 from ..ops import gemm as GM
                 gu = sc.get("ffn_gu_f32", (T, 2 * Fd), torch.float32)
-                GM.gemm_bf16_splitk_det(xn, GM.bf16_weight(self.W(i, "ffn_gate.weight"), sc, self.shadow), gu[:, :Fd], sc)
-                GM.gemm_bf16_splitk_det(xn, GM.bf16_weight(self.W(i, "ffn_up.weight"), sc, self.shadow), gu[:, Fd:], sc)
+                GM.gemm_quant_splitk(xn, self.W(i, "ffn_gate.weight"), gu[:, :Fd], sc)
+                GM.gemm_quant_splitk(xn, self.W(i, "ffn_up.weight"), gu[:, Fd:], sc)
             else:
                 gu = sc.get("ffn_gu", (T, 2 * Fd), torch.bfloat16)
                 self._gemm(xn, self.W(i, "ffn_gate.weight"), gu[:, :Fd], tag="g")

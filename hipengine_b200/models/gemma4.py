@@ -176,10 +176,8 @@ class Gemma4Executor(HybridExecutor):
             self._gemm(xn, self.W(i, "ffn_up.weight"), gu[:, Fd:], tag="g")
             act = sc.get("ffn_act", (T, Fd), torch.bfloat16)
             K.act_mul(gu, act, "gelu_tanh")
-            wdn = self.W(i, "ffn_down.weight")
-            wdb = sc.get("gemm_deq", (wdn.n_rows, wdn.n_cols), torch.bfloat16)
-            K.dequant_bf16(wdn, wdb)
-            d = GM.gemm_bf16(act, wdb[:, :Fd], sc.get("ffn_d_bf", (T, H), torch.bfloat16))
+            # the down weight's K is zero-padded to whole blocks; the GEMM reads the missing activation columns as 0
+            d = GM.gemm_quant(act, self.W(i, "ffn_down.weight"), sc.get("ffn_d_bf", (T, H), torch.bfloat16), sc)
             xr = sc.get("xn_router", (T, H), torch.bfloat16)
             K.rmsnorm_rows(h, self.router_norm[i], xr, eps)
             GM.gemm_bf16(xr, self.router_hi[i], logits, epi=1)
@@ -205,17 +203,13 @@ class Gemma4Executor(HybridExecutor):
             K.moe_group(ids, E, pos, tiles, meta)
             xs = sc.get("moe_xs", (bound, H), torch.bfloat16)
             K.moe_gather(x2, pos, k, xs)
-            wb = sc.get("moe_deq", (E * max(2 * F * H, H * Fp),), torch.bfloat16)
-            w_gu = wb[:E * 2 * F * H].view(E * 2 * F, H)
-            K.dequant_bf16(wgu, w_gu)
+            from .moe import _grouped
             gus = sc.get("moe_gu", (bound, 2 * F), torch.bfloat16)
-            GM.gemm_bf16_grouped(xs, w_gu, gus, E, tiles)
+            _grouped(sc, xs, wgu, gus, E, tiles)
             acts = sc.get("moe_act_g", (bound, F), torch.bfloat16)
             K.act_mul(gus, acts, "gelu_tanh")
-            w_d = wb[:E * H * Fp].view(E * H, Fp)
-            K.dequant_bf16(wd, w_d)
             ys = sc.get("moe_ys", (bound, H), torch.bfloat16)
-            GM.gemm_bf16_grouped(acts, w_d[:, :F], ys, E, tiles)
+            _grouped(sc, acts, wd, ys, E, tiles)
             K.moe_combine(eo, ys, pos, wts, k)
         K.ffn_combine(h, d, eo, self.F(i, "post_ffw_norm_1.weight"), self.F(i, "post_ffw_norm_2.weight"),
                       self.F(i, "post_ffw_norm.weight"), self.F(i, "layer_output_scale.weight"), eps)

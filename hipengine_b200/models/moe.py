@@ -7,8 +7,8 @@ Two routes, chosen by the number of packed rows:
   (token, expert) pairs reading the experts' quantised rows in place.  No expert id is ever read by the host,
   so the whole block is CUDA-graph capturable.
 * larger ``T``: *grouped tensor-core GEMM*.  Pairs are bucketed by expert (128-row padded segments), rows are
-  gathered, the experts are dequantised to bf16 scratch and the tcgen05 GEMM runs in grouped mode (each
-  128-row tile carries its expert id), followed by a combine kernel that applies the routing weights, the
+  gathered and the tcgen05 GEMM runs in grouped mode over the experts' quantised blocks (each 128-row tile
+  carries its expert id; the blocks are expanded to bf16 inside the GEMM pipeline), followed by a combine kernel that applies the routing weights, the
   sigmoid-gated shared expert and the residual add.
 
 Behaviour follows the reference MoE layer executor (``hipengine/runtime/qwen35_gguf_layer_ffn.py:719-1278``)
@@ -115,6 +115,17 @@ def _moe_selected(ex, i: int, h: torch.Tensor, target: torch.Tensor, T: int, nor
             K.gemv(act_sh[r0:r1], [GemvSegment(ex.W(i, "ffn_down_shexp.weight"), target[r0:r1], K.EPI_ADD_F32)])
 
 
+def _grouped(sc, a_sorted: torch.Tensor, w, out: torch.Tensor, n_groups: int, tile_group: torch.Tensor) -> None:
+    """Grouped expert GEMM: quantised experts in place; float-typed experts through a bf16 scratch expansion."""
+    from ..ops import gemm as GM
+    if GM.quant_gemm_ok(w):
+        GM.gemm_quant_grouped(a_sorted, w, out, n_groups, tile_group)
+        return
+    wb = sc.get("moe_deq", (w.n_rows, w.n_cols), torch.bfloat16)
+    K.dequant_bf16(w, wb)
+    GM.gemm_bf16_grouped(a_sorted, wb[:, :a_sorted.shape[1]], out, n_groups, tile_group)
+
+
 def _moe_grouped(ex, i: int, h: torch.Tensor, target: torch.Tensor, T: int, norm_w: torch.Tensor, rng) -> None:
     from ..ops import gemm as GM
     cfg, sc = ex.cfg, ex.scratch
@@ -141,18 +152,13 @@ def _moe_grouped(ex, i: int, h: torch.Tensor, target: torch.Tensor, T: int, norm
     K.moe_gather(xn, pos, k, xs)
     gu = sc.get("moe_gu", (bound, 2 * F), torch.bfloat16)
     wg, wu, wd = (ex.W(i, "ffn_gate_exps.weight"), ex.W(i, "ffn_up_exps.weight"), ex.W(i, "ffn_down_exps.weight"))
-    wb = sc.get("moe_deq", (El * max(F * H, H * F),), torch.bfloat16)
-    w_gu = wb[:El * F * H].view(El * F, H)
-    K.dequant_bf16(wg, w_gu)
-    GM.gemm_bf16_grouped(xs, w_gu, gu[:, :F], El, tile_group)
-    K.dequant_bf16(wu, w_gu)
-    GM.gemm_bf16_grouped(xs, w_gu, gu[:, F:], El, tile_group)
+    # the experts' quantised blocks are read in place by the grouped tensor-core GEMM (no bf16 expansion)
+    _grouped(sc, xs, wg, gu[:, :F], El, tile_group)
+    _grouped(sc, xs, wu, gu[:, F:], El, tile_group)
     act = sc.get("moe_act_g", (bound, F), torch.bfloat16)
     K.act_mul(gu, act, cfg.act)
-    w_d = wb[:El * H * F].view(El * H, F)
-    K.dequant_bf16(wd, w_d)
     ys = sc.get("moe_ys", (bound, H), torch.bfloat16)
-    GM.gemm_bf16_grouped(act, w_d, ys, El, tile_group)
+    _grouped(sc, act, wd, ys, El, tile_group)
     ysh = None
     if shared_here:
         Fs = cfg.shared_ffn

@@ -34,32 +34,97 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: Optional
     return out
 
 
-def gemm_quant(x: torch.Tensor, w: DeviceWeight, out: torch.Tensor, scratch, row0: int = 0,
-               rows: Optional[int] = None, epi: Optional[int] = None, shadow: Optional[dict] = None) -> torch.Tensor:
-    """out[M, rows] = x[M, K] @ W[row0:row0+rows]^T for a quantized device-layout weight.
+QUANT_GEMM_TYPES = (8, 12, 14)     # Q8_0, Q4_K, Q6_K: read in their device layout by the tensor-core pipeline
 
-    The weight is expanded to bf16 for the tensor cores.  With ``shadow`` (a dict owned by the executor, holding a
-    byte budget under the key ``"_left"``) the expansion is kept resident in HBM after its first use, so later
-    prefill chunks read bf16 tiles straight through TMA; without it the expansion goes to scratch every call.
+
+def quant_gemm_ok(w: DeviceWeight) -> bool:
+    return w.qtype in QUANT_GEMM_TYPES and w.n_cols % 256 == 0
+
+
+def _row_bytes(w: DeviceWeight) -> int:
+    return w.data.numel() * w.data.element_size() // w.n_rows
+
+
+def _float_weight_bf16(w: DeviceWeight, scratch) -> torch.Tensor:
+    """bf16 view of a weight that is stored as floats (bf16 as is; f32 / f16 widened once and kept: these are the
+    few small unquantised matrices of a checkpoint)."""
+    if w.qtype == 30:
+        return w.data.view(torch.bfloat16).reshape(w.n_rows, w.n_cols)
+    cache = scratch.__dict__.setdefault("_float_bf16", {})
+    wb = cache.get(w.ptr)
+    if wb is None:
+        wb = dequant_bf16(w)
+        cache[w.ptr] = wb
+    return wb
+
+
+def gemm_quant(x: torch.Tensor, w: DeviceWeight, out: torch.Tensor, scratch, row0: int = 0,
+               rows: Optional[int] = None, epi: Optional[int] = None) -> torch.Tensor:
+    """out[M, rows] = x[M, K] @ W[row0:row0+rows]^T for a device-layout weight.
+
+    Q4_K / Q6_K / Q8_0 weights are read as stored (raw blocks by TMA, expanded to bf16 operand tiles inside the
+    kernel's shared-memory pipeline): the only copy of the weight in HBM is the quantised one.  Counterpart of the
+    reference's quantised prefill GEMMs (``hipengine/kernels/hip_gfx1100/quant/gguf_q4_k_prefill.hip:170-296``,
+    ``gguf_q8_0_prefill.hip``).
     """
     rows = w.n_rows - row0 if rows is None else rows
-    if w.qtype == 30 and row0 == 0 and rows == w.n_rows:   # already bf16
-        return gemm_bf16(x, w.data.view(torch.bfloat16).reshape(w.n_rows, w.n_cols), out, epi)
-    if shadow is not None:
-        key = (w.ptr, row0, rows)
-        wb = shadow.get(key)
-        if wb is None:
-            need = rows * w.n_cols * 2
-            if shadow.get("_left", 0) >= need:
-                wb = torch.empty(rows, w.n_cols, dtype=torch.bfloat16, device=x.device)
-                dequant_bf16(w, wb, row0=row0, rows=rows)
-                shadow[key] = wb
-                shadow["_left"] -= need
-        if wb is not None:
-            return gemm_bf16(x, wb, out, epi)
-    wb = scratch.get("gemm_deq", (rows, w.n_cols), torch.bfloat16)
-    dequant_bf16(w, wb, row0=row0, rows=rows)
-    return gemm_bf16(x, wb, out, epi)
+    if not quant_gemm_ok(w):
+        wb = _float_weight_bf16(w, scratch)
+        return gemm_bf16(x, wb[row0:row0 + rows], out, epi)
+    assert x.dtype == torch.bfloat16 and x.stride(1) == 1 and out.stride(1) == 1 and x.shape[1] <= w.n_cols
+    _check_device(x)
+    if epi is None:
+        epi = 0 if out.dtype == torch.bfloat16 else 1
+    M, a_cols = x.shape        # fewer columns than the weight's (zero-padded) K read as zeros
+    st = status_word(x.device)
+    N.check(N.lib().he_gemm_q(C.c_void_p(x.data_ptr()), C.c_longlong(x.stride(0)), C.c_int(a_cols),
+                              C.c_void_p(w.ptr + row0 * _row_bytes(w)), C.c_int(w.qtype), C.c_longlong(rows),
+                              C.c_void_p(out.data_ptr()), C.c_longlong(out.stride(0)), C.c_int(M), C.c_int(rows),
+                              C.c_int(w.n_cols), C.c_int(epi), C.c_void_p(None), C.c_void_p(st.data_ptr()),
+                              C.c_int(N.num_sms()), _stream()), "he_gemm_q")
+    return out
+
+
+def gemm_quant_grouped(a_sorted: torch.Tensor, w: DeviceWeight, out: torch.Tensor, n_groups: int,
+                       tile_group: torch.Tensor, epi: Optional[int] = None) -> torch.Tensor:
+    """Grouped form of ``gemm_quant`` for MoE experts: ``w`` stacks ``n_groups`` expert matrices of
+    ``w.n_rows // n_groups`` rows; 128-row tile ``tm`` of ``a_sorted`` uses expert ``tile_group[tm]`` (-1: skip)."""
+    assert quant_gemm_ok(w) and a_sorted.dtype == torch.bfloat16
+    M, a_cols = a_sorted.shape
+    Nn = w.n_rows // n_groups
+    assert tile_group.numel() >= (M + 127) // 128 and a_cols <= w.n_cols
+    if epi is None:
+        epi = 0 if out.dtype == torch.bfloat16 else 1
+    st = status_word(a_sorted.device)
+    N.check(N.lib().he_gemm_q(C.c_void_p(a_sorted.data_ptr()), C.c_longlong(a_sorted.stride(0)), C.c_int(a_cols),
+                              C.c_void_p(w.ptr), C.c_int(w.qtype), C.c_longlong(w.n_rows), C.c_void_p(out.data_ptr()),
+                              C.c_longlong(out.stride(0)), C.c_int(M), C.c_int(Nn), C.c_int(w.n_cols), C.c_int(epi),
+                              C.c_void_p(tile_group.data_ptr()), C.c_void_p(st.data_ptr()), C.c_int(N.num_sms()),
+                              _stream()), "he_gemm_q(grouped)")
+    return out
+
+
+def gemm_quant_splitk(x: torch.Tensor, w: DeviceWeight, out: torch.Tensor, scratch, add: bool = False
+                      ) -> torch.Tensor:
+    """out[M, N] (fp32) = (or +=) x @ W^T for few rows (<= 128): the K range is split over the SMs so that all of
+    them stream a share of the quantised weight; partial tiles are summed in split order (bit-reproducible)."""
+    assert x.dtype == torch.bfloat16 and out.dtype == torch.float32
+    if not quant_gemm_ok(w):
+        return gemm_bf16_splitk_det(x, _float_weight_bf16(w, scratch), out, scratch, add=add)
+    _check_device(x)
+    M, K = x.shape
+    L = N.lib()
+    L.he_gemm_q_splitk_plan.restype = C.c_longlong
+    ks = int(L.he_gemm_q_splitk_plan(C.c_int(M), C.c_int(w.n_rows), C.c_int(K), C.c_int(N.num_sms()))) & 0xffffffff
+    part = scratch.get("splitk_part", (ks * M * w.n_rows,), torch.float32)
+    st = status_word(x.device)
+    N.check(L.he_gemm_q_splitk_det(C.c_void_p(x.data_ptr()), C.c_longlong(x.stride(0)), C.c_void_p(w.ptr),
+                                   C.c_int(w.qtype), C.c_longlong(w.n_rows), C.c_void_p(part.data_ptr()),
+                                   C.c_void_p(out.data_ptr()), C.c_longlong(out.stride(0)), C.c_int(M),
+                                   C.c_int(w.n_rows), C.c_int(K), C.c_int(1 if add else 0),
+                                   C.c_void_p(st.data_ptr()), C.c_int(N.num_sms()), _stream()),
+            "he_gemm_q_splitk_det")
+    return out
 
 
 def gemm_bf16_grouped(a_sorted: torch.Tensor, w_stacked: torch.Tensor, out: torch.Tensor, n_groups: int,
@@ -114,22 +179,3 @@ def gemm_bf16_splitk_det(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, sc
                                       C.c_int(K), C.c_int(1 if add else 0), C.c_void_p(st.data_ptr()),
                                       C.c_int(N.num_sms()), _stream()), "he_gemm_bf16_splitk_det")
     return out
-
-
-def bf16_weight(w: DeviceWeight, scratch, shadow: Optional[dict] = None) -> torch.Tensor:
-    """The bf16 expansion of a quantised weight: the resident shadow copy when there is one, else scratch."""
-    if w.qtype == 30:
-        return w.data.view(torch.bfloat16).reshape(w.n_rows, w.n_cols)
-    if shadow is not None:
-        key = (w.ptr, 0, w.n_rows)
-        wb = shadow.get(key)
-        if wb is None and shadow.get("_left", 0) >= w.n_rows * w.n_cols * 2:
-            wb = torch.empty(w.n_rows, w.n_cols, dtype=torch.bfloat16, device=w.data.device)
-            dequant_bf16(w, wb)
-            shadow[key] = wb
-            shadow["_left"] -= w.n_rows * w.n_cols * 2
-        if wb is not None:
-            return wb
-    wb = scratch.get("gemm_deq", (w.n_rows, w.n_cols), torch.bfloat16)
-    dequant_bf16(w, wb)
-    return wb

@@ -221,13 +221,20 @@ class FusedGemmAllReduce:
         return (rows <= self.max_rows and resid.dtype == torch.float32 and resid.stride(1) == 1
                 and resid.stride(0) % 4 == 0 and resid.data_ptr() % 16 == 0)
 
-    def gemm_add(self, x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor, phases: int = 7) -> None:
-        """resid[M, N] += sum over ranks of (x[M, K] @ w[N, K]^T); x, w bf16 (this rank's K shard), resid fp32."""
-        assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and resid.dtype == torch.float32
+    def gemm_add(self, x: torch.Tensor, w, resid: torch.Tensor, phases: int = 7) -> None:
+        """resid[M, N] += sum over ranks of (x[M, K] @ w[N, K]^T); x bf16 (this rank's K shard), resid fp32.
+        ``w`` is either a bf16 tensor or a quantised ``DeviceWeight`` (Q4_K / Q6_K / Q8_0), which the kernel reads in
+        its device layout and expands inside the pipeline."""
+        assert x.dtype == torch.bfloat16 and resid.dtype == torch.float32
         K._check_device(x)
         M, Kd = x.shape
-        Nn = w.shape[0]
-        assert Nn == self.width and w.shape[1] == Kd and x.stride(1) == 1 and w.stride(1) == 1
+        quant = isinstance(w, K.DeviceWeight)
+        Nn = w.n_rows if quant else w.shape[0]
+        if quant:
+            assert w.n_cols == Kd and Kd % 256 == 0 and w.qtype in (8, 12, 14)
+        else:
+            assert w.dtype == torch.bfloat16 and w.shape[1] == Kd and w.stride(1) == 1
+        assert Nn == self.width and x.stride(1) == 1
         assert self.supports(M, resid) and resid.shape[1] >= Nn
         a = _FuseArgs()
         off_res, off_flag = self.stage_bytes, self.stage_bytes + self.result_bytes
@@ -239,10 +246,16 @@ class FusedGemmAllReduce:
         a.max_tiles, a.owned_cap, a.phases, a.wait_limit = self.max_tiles, self.owned_cap, phases, self.wait_limit
         a.direct = 1 if self.direct else 0
         st = K.status_tensor(x.device)
-        N.check(N.lib().he_gemm_bf16_allreduce(
-            C.c_void_p(x.data_ptr()), C.c_longlong(x.stride(0)), C.c_void_p(w.data_ptr()), C.c_longlong(w.stride(0)),
-            C.c_int(M), C.c_int(Nn), C.c_int(Kd), C.byref(a), C.c_void_p(st.data_ptr()), C.c_int(N.num_sms()),
-            K._stream()), "he_gemm_bf16_allreduce")
+        if quant:
+            N.check(N.lib().he_gemm_q_allreduce(
+                C.c_void_p(x.data_ptr()), C.c_longlong(x.stride(0)), C.c_void_p(w.ptr), C.c_int(w.qtype),
+                C.c_longlong(w.n_rows), C.c_int(M), C.c_int(Nn), C.c_int(Kd), C.byref(a), C.c_void_p(st.data_ptr()),
+                C.c_int(N.num_sms()), K._stream()), "he_gemm_q_allreduce")
+        else:
+            N.check(N.lib().he_gemm_bf16_allreduce(
+                C.c_void_p(x.data_ptr()), C.c_longlong(x.stride(0)), C.c_void_p(w.data_ptr()),
+                C.c_longlong(w.stride(0)), C.c_int(M), C.c_int(Nn), C.c_int(Kd), C.byref(a),
+                C.c_void_p(st.data_ptr()), C.c_int(N.num_sms()), K._stream()), "he_gemm_bf16_allreduce")
         self.calls += 1
 
     def close(self) -> None:

@@ -85,7 +85,7 @@ class TPHybridExecutor(HybridExecutor):
         if self.fgemm is not None and self.fgemm.supports(x.shape[0], h):
             # GEMM, all-reduce over peer memory and residual add as one tcgen05 kernel per rank
             from ..ops import gemm as GM
-            self.fgemm.gemm_add(x, GM.bf16_weight(w, self.scratch, self.shadow), h)
+            self.fgemm.gemm_add(x, w if GM.quant_gemm_ok(w) else GM._float_weight_bf16(w, self.scratch), h)
             return
         y = self._gemm(x, w, self.scratch.get("y_bf", (x.shape[0], w.n_rows), torch.bfloat16), tag=tag)
         self.ctx.all_reduce_(y)

@@ -168,3 +168,78 @@ def test_cold_tier_roundtrip_lru_and_corruption(tmp_path):
     # 4096 tokens at 16k tok/s = 256 ms of prefill against ~1 GB of state: restore loses; against 100 MB it wins
     assert not restore_is_worthwhile(4096, 10 ** 9, 10 ** 9, 16000.0)
     assert restore_is_worthwhile(4096, 2 * 10 ** 7, 4 * 10 ** 7, 16000.0)
+
+
+def _wired_pool(n_pages):
+    """PagePool + RadixCache wired the way the GPU runner wires them."""
+    from hipengine_b200.kvcache.pool import PagePool
+    from hipengine_b200.kvcache.radix import RadixCache
+    pool = PagePool(n_pages, page_tokens=16)
+    t = [0.0]
+
+    def clock():
+        t[0] += 1.0
+        return t[0]
+
+    radix = RadixCache(16, clock=clock)
+    radix.on_retain = pool.retain_cache
+    radix.on_release = pool.release_cache
+    radix.page_refcount = lambda p: pool.refcount[p]
+    pool.evict_hook = radix.evict
+    return pool, radix
+
+
+def test_admit_with_shared_prefix_on_a_full_pool_never_reuses_the_prefix_pages():
+    """Seven usable pages, prefix A (4 pages) and prefix B (3 pages) cached, then a request that matches A and
+    needs three more pages: the three must come from B, never from A itself."""
+    from hipengine_b200.kvcache.pool import PoolExhausted
+    pool, radix = _wired_pool(8)
+    a_tok = list(range(64))
+    b_tok = list(range(1000, 1048))
+    la = pool.admit(1, 64, now_tokens=64)
+    radix.insert(a_tok, la.pages)
+    pool.release(1)
+    lb = pool.admit(2, 48, now_tokens=48)
+    radix.insert(b_tok, lb.pages)
+    pool.release(2)
+    assert pool.n_free == 0 and pool.n_evictable() == 7
+    m = radix.match(a_tok + list(range(5000, 5048)))
+    assert m.tokens == 64 and len(m.pages) == 4
+    lease = pool.admit(3, 64 + 48, shared_prefix=m.pages, now_tokens=64 + 48)
+    assert len(set(lease.pages)) == len(lease.pages) == 7
+    assert lease.pages[:4] == m.pages
+    assert not set(lease.pages[4:]) & set(m.pages)
+    pool.assert_conserved()
+    radix.assert_consistent()
+    assert radix.match(a_tok + [1]).tokens == 64          # the matched prefix is still published
+    # a request that cannot fit leaves the prefix refcounts as they were
+    pool.release(3)
+    m = radix.match(a_tok + list(range(5000, 5048)))
+    before = list(pool.refcount)
+    try:
+        pool.admit(4, 64 + 16 * 20, shared_prefix=m.pages, now_tokens=64)
+        raise AssertionError("expected PoolExhausted")
+    except PoolExhausted:
+        pass
+    assert pool.refcount == before
+    pool.assert_conserved()
+
+
+def test_radix_eviction_is_strict_lru_across_newly_exposed_leaves():
+    """A long stale chain must be evicted (leaf by leaf, parents as they become leaves) before a fresher leaf."""
+    pool, radix = _wired_pool(12)
+    old = list(range(48))
+    l1 = pool.admit(1, 48, now_tokens=48)
+    old_pages = list(l1.pages)
+    radix.insert(old, old_pages)
+    pool.release(1)
+    fresh = list(range(900, 916))
+    l2 = pool.admit(2, 16, now_tokens=16)
+    radix.insert(fresh, l2.pages)
+    pool.release(2)
+    radix.match(fresh + [1])                               # touch: fresh is now the most recent
+    freed = radix.evict(3)
+    assert sorted(freed) == sorted(old_pages)
+    assert radix.match(fresh + [1]).tokens == 16
+    assert radix.match(old + [1]).tokens == 0
+    pool.assert_conserved()
