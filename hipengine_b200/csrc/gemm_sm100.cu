@@ -38,7 +38,6 @@ constexpr int STAGES_Q = 3;            // A / dequantised-B ring depth in QM
 constexpr int QSTAGES = 2;             // raw-block ring depth
 constexpr int Q_STAGE_BYTES = BN * 144;
 constexpr int N_UNPACK_WARPS = 8;
-constexpr int NTHREADS_Q = NTHREADS + 32 * (1 + N_UNPACK_WARPS);
 constexpr int NTHREADS_FUSED_Q = NTHREADS_FUSED + 32 * (1 + N_UNPACK_WARPS);
 
 struct GemmArgs {
@@ -776,13 +775,8 @@ gemm_bf16_allreduce_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
   gemm_body<true, false>(tmA, tmB, tmB, tmB, g, &f);
 }
 
-// The same pipelines with the weight read in its quantised device layout (tmQ0..2: byte-typed maps over the rows).
-__global__ void __launch_bounds__(NTHREADS_Q, 1)
-gemm_q_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmQ0,
-              const __grid_constant__ CUtensorMap tmQ1, const __grid_constant__ CUtensorMap tmQ2, const GemmArgs g) {
-  gemm_body<false, true>(tmA, tmQ0, tmQ1, tmQ2, g, nullptr);
-}
-
+// The fused pipeline with the weight read in its quantised device layout (tmQ0..2: byte-typed maps over the rows;
+// the stand-alone quantised GEMM lives in gemm_wq_sm100.cu).
 __global__ void __launch_bounds__(NTHREADS_FUSED_Q, 1)
 gemm_q_allreduce_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmQ0,
                         const __grid_constant__ CUtensorMap tmQ1, const __grid_constant__ CUtensorMap tmQ2,
@@ -869,7 +863,6 @@ int make_qmaps(QMaps* q, const void* B, int qtype, long long rows, int K) {
   return -HE_ERR_BAD_ARG;
 }
 
-constexpr size_t SMEM_BF16 = STAGES * STAGE_BYTES + sizeof(Barriers) + 1024;
 constexpr size_t SMEM_Q = STAGES_Q * STAGE_BYTES + QSTAGES * Q_STAGE_BYTES + sizeof(Barriers) + 1024;
 
 }  // namespace
@@ -1078,85 +1071,6 @@ HE_API int he_gemm_bf16_splitk(const void* A, long long lda, const void* B, long
 }
 
 // ---------------------------------------------------------------- quantised-weight entry points
-// C[M][N] = A[M][K] (bf16) * W[N][K]^T where W is `b_rows` rows in the device layout of `qtype` (Q4_K / Q6_K / Q8_0),
-// dequantised inside the pipeline.  epi as he_gemm_bf16.  With `tile_group` (device, ceil(M/128) ints) the call is the
-// grouped form: M-tile tm uses weight rows [tile_group[tm] * N, +N); negative entries skip the tile.
-// `a_cols` (<= K, multiple of 8) is the number of columns A really has: columns up to K read as zeros (weights whose K
-// was padded to a whole number of 256-column blocks).
-HE_API int he_gemm_q(const void* A, long long lda, int a_cols, const void* B, int qtype, long long b_rows, void* C,
-                     long long ldc, int M, int N, int K, int epi, const int* tile_group, void* status, int num_sms,
-                     cudaStream_t stream) {
-  if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if (a_cols <= 0 || a_cols > K || a_cols % 8 != 0) return -HE_ERR_BAD_ARG;
-  CUtensorMap tmA;
-  QMaps q;
-  int rc = make_map(&tmA, A, M, a_cols, lda, BM);
-  if (rc != 0) return rc;
-  rc = make_qmaps(&q, B, qtype, b_rows, K);
-  if (rc != 0) return rc;
-  GemmArgs g = {};
-  g.C = C; g.ldc = ldc; g.resid = nullptr; g.M = M; g.N = N; g.K = K; g.epi = epi; g.status = (int*)status;
-  g.tile_group = tile_group;
-  g.k_splits = 1;
-  g.split_stride = 0;
-  g.qtype = qtype;
-  g.kb_per = 0;
-  cudaError_t e = cudaFuncSetAttribute(gemm_q_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_Q);
-  if (e != cudaSuccess) return (int)e;
-  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  gemm_q_kernel<<<tiles < num_sms ? tiles : num_sms, NTHREADS_Q, SMEM_Q, stream>>>(tmA, q.m[0], q.m[1], q.m[2], g);
-  HE_LAUNCH_CHECK();
-  return 0;
-}
-
-// Split count of the deterministic split-K form for a quantised weight: about one tile per SM, every split a whole
-// number of 256-column blocks and none empty.  The low 32 bits are the split count, the high 32 bits the k-blocks
-// (of 64 columns) per split.
-HE_API long long he_gemm_q_splitk_plan(int M, int N, int K, int num_sms) {
-  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  const int k_blocks = (K + BK - 1) / BK;
-  int k_splits = (num_sms + tiles - 1) / tiles;
-  if (k_splits < 1) k_splits = 1;
-  int kb_per = (k_blocks + k_splits - 1) / k_splits;
-  kb_per = (kb_per + 3) & ~3;
-  k_splits = (k_blocks + kb_per - 1) / kb_per;
-  return ((long long)kb_per << 32) | (long long)k_splits;
-}
-
-// out[M][N] (fp32) = (mode 0) or += (mode 1) A * W^T, K split over CTAs so that every SM streams a share of the
-// quantised weight; partial tiles go to `partials` ([k_splits][M][N] fp32) and are summed in split order.
-HE_API int he_gemm_q_splitk_det(const void* A, long long lda, const void* B, int qtype, long long b_rows,
-                                void* partials, void* out, long long ldo, int M, int N, int K, int mode, void* status,
-                                int num_sms, cudaStream_t stream) {
-  if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if (N % 4 != 0) return -HE_ERR_BAD_ARG;
-  CUtensorMap tmA;
-  QMaps q;
-  int rc = make_map(&tmA, A, M, K, lda, BM);
-  if (rc != 0) return rc;
-  rc = make_qmaps(&q, B, qtype, b_rows, K);
-  if (rc != 0) return rc;
-  const long long plan = he_gemm_q_splitk_plan(M, N, K, num_sms);
-  const int k_splits = (int)(plan & 0xffffffffll);
-  GemmArgs g = {};
-  g.C = partials; g.ldc = N; g.resid = nullptr; g.M = M; g.N = N; g.K = K; g.epi = 4; g.status = (int*)status;
-  g.tile_group = nullptr;
-  g.k_splits = k_splits;
-  g.split_stride = (long long)M * N;
-  g.qtype = qtype;
-  g.kb_per = (int)(plan >> 32);
-  cudaError_t e = cudaFuncSetAttribute(gemm_q_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_Q);
-  if (e != cudaSuccess) return (int)e;
-  const int total = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * k_splits;
-  gemm_q_kernel<<<total < num_sms ? total : num_sms, NTHREADS_Q, SMEM_Q, stream>>>(tmA, q.m[0], q.m[1], q.m[2], g);
-  HE_LAUNCH_CHECK();
-  const long long n4 = ((long long)M * N + 3) / 4;
-  splitk_reduce_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>((const float*)partials, g.split_stride,
-                                                                        k_splits, (float*)out, ldo, M, N, mode);
-  HE_LAUNCH_CHECK();
-  return 0;
-}
-
 // The fused GEMM -> all-reduce -> residual add of he_gemm_bf16_allreduce with a quantised weight.
 HE_API int he_gemm_q_allreduce(const void* A, long long lda, const void* B, int qtype, long long b_rows, int M, int N,
                                int K, const FuseArgs* fuse, void* status, int num_sms, cudaStream_t stream) {

@@ -1,0 +1,606 @@
+// Tensor-core GEMM over a QUANTISED weight for sm_100a: C[M][N] = X[M][K] * W[N][K]^T with W kept in its
+// GGUF-derived device layout (Q4_K 144-byte blocks, Q6_K 224-byte blocks, Q8_0 int8 + scale planes).
+//
+// The product is computed transposed, D^T[128 weight rows][mt activation rows], so that the WEIGHT is the MMA's
+// A operand -- and tcgen05.mma can take A from tensor memory.  Raw block bytes arrive in shared memory by
+// byte-typed TMA boxes; sixteen unpack warps turn each 64-column slice of a weight row into 32 packed bf16x2
+// registers and store them with tcgen05.st straight into a TMEM operand stage (row = TMEM lane).  The expanded
+// weight therefore never exists in shared or global memory: DRAM and L2 see 4.5 / 6.6 / 8.5 bits per weight, and
+// shared-memory bandwidth is left to the activation tiles.  Roles (24 warps):
+//   warp 0      : TMA producer of activation tiles X[mt][64] (128-byte swizzle, 5-stage ring)
+//   warp 1      : MMA issuer (tcgen05.mma 128 x mt x 16, A from TMEM, B from smem); owns the TMEM allocation
+//   warp 2      : TMA producer of raw weight blocks (one 256-column super-block of 128 rows per q-stage, 3 stages)
+//   warps 4..7  : epilogue (tcgen05.ld, transposed store: lane = weight row n, register = activation row m, so a
+//                 store instruction of a warp covers 32 consecutive n of one output row)
+//   warps 8..23 : unpack, four sets of four warps; set g expands k-block g of every super-block into TMEM
+//                 operand stage g (thread = weight row), so four k-blocks are in flight
+// TMEM (512 columns): two accumulators of 192 fp32 columns (epilogue of tile i overlaps the main loop of
+// tile i+1) + four operand stages of 32 columns.
+// Counterparts in the reference: hipengine/kernels/hip_gfx1100/quant/gguf_q4_k_prefill.hip:170-296 (raw 144-byte
+// blocks read inside the matrix-core loop), gguf_q8_0_prefill.hip, and the grouped expert form
+// quant/gguf_q4_k_selected_prefill.hip.
+#include "common.cuh"
+#include "sm100.cuh"
+
+using namespace sm100;
+
+namespace {
+
+constexpr int WN = 128;                  // weight rows per tile (the MMA's M)
+constexpr int MT_MAX = 192;              // activation rows per tile (the MMA's N), multiple of 16
+constexpr int BK = 64, UK = 16;
+constexpr int XSTAGES = 5;                          // activation ring depth (stage = mt x 64 bf16, <= 24 KB)
+constexpr int QSTAGES_MAX = 12;                     // raw-block ring: as many stages as shared memory holds, up to 12
+constexpr int SMEM_BUDGET = 224 * 1024;             // dynamic shared memory the rings may use
+constexpr int N_SETS = 4;                           // unpack sets == TMEM operand stages == k-blocks per q-stage
+constexpr int N_UNPACK_WARPS = 16;
+constexpr int WARP_UNPACK0 = 8;
+constexpr int NTHREADS_WQ = (WARP_UNPACK0 + N_UNPACK_WARPS) * 32;   // 768
+constexpr int TMEM_COLS = 512;
+constexpr int D_COLS = MT_MAX;                      // column stride between the two accumulators
+constexpr int A_COL0 = 2 * D_COLS;                  // first operand-stage column (384)
+constexpr int A_STAGE_COLS = 32;                    // 64 bf16 per lane
+
+struct WqArgs {
+  void* C;
+  long long ldc;            // elements
+  int M, N, K;
+  int epi;                  // 0: bf16 store, 1: fp32 store, 2: fp32 +=, 4: fp32 split-K partial store
+  int qtype;                // HE_Q4_K / HE_Q6_K / HE_Q8_0
+  int mt;                   // activation rows per tile: multiple of 16, <= MT_MAX (128 in grouped mode)
+  int k_splits;             // >= 1
+  int sb_per;               // super-blocks (256 columns) per split
+  long long split_stride;   // epi 4: split ks stores at C + ks * split_stride
+  const int* tile_group;    // grouped mode: M-tile tm uses weight rows [tile_group[tm] * N, +N); < 0 skips the tile
+  int* status;
+  // ring geometry, set by the launcher: few activation rows leave room for a deep raw-block ring, which is what
+  // hides DRAM latency when the weight is streamed once (decode batches)
+  int x_stage_bytes;        // mt * 128 rounded up to 1 KB
+  int q_stage_bytes;        // 128 rows x bytes per super-block row, rounded up to 1 KB
+  int q_stages;
+};
+
+struct __align__(8) WqBarriers {
+  uint64_t x_full[XSTAGES];
+  uint64_t x_empty[XSTAGES];
+  uint64_t q_full[QSTAGES_MAX];
+  uint64_t q_empty[QSTAGES_MAX];
+  uint64_t a_full[N_SETS];
+  uint64_t a_empty[N_SETS];
+  uint64_t d_full[2];
+  uint64_t d_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+// ---------------------------------------------------------------- register-level dequantisation
+__device__ __forceinline__ uint32_t prmt_b32(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+  return r;
+}
+__device__ __forceinline__ __nv_bfloat162 bf162_bits(uint32_t v) { return *reinterpret_cast<__nv_bfloat162*>(&v); }
+__device__ __forceinline__ uint32_t bits_bf162(__nv_bfloat162 v) { return *reinterpret_cast<uint32_t*>(&v); }
+
+// Four small unsigned integers (< 128), one per byte of `b4`, become two bf16x2 registers holding
+// bf16(q * s + off) with a single rounding.  A byte (0x80 | q) placed under the exponent byte 0x3F is the fp32 number
+// 1 + q / 128 exactly, so the integer reaches fp32 with one byte permute; then one fp32 FMA,
+//     (1 + q / 128) * (128 s) + (off - 128 s) = q * s + off,
+// and one packing conversion per pair.  `s128` = 128 * s and `c` = off - 128 * s are per sub-block constants.  The
+// result equals the reference dequantisation (fp32) rounded once to bf16.
+__device__ __forceinline__ void bytes4_to_bf16(uint32_t b4, float s128, float c, uint32_t& o01, uint32_t& o23) {
+  const uint32_t q8 = b4 | 0x80808080u;
+  const float f0 = fmaf(__uint_as_float(prmt_b32(q8, 0x3Fu, 0x4055u)), s128, c);
+  const float f1 = fmaf(__uint_as_float(prmt_b32(q8, 0x3Fu, 0x4155u)), s128, c);
+  const float f2 = fmaf(__uint_as_float(prmt_b32(q8, 0x3Fu, 0x4255u)), s128, c);
+  const float f3 = fmaf(__uint_as_float(prmt_b32(q8, 0x3Fu, 0x4355u)), s128, c);
+  o01 = bits_bf162(__floats2bfloat162_rn(f0, f1));
+  o23 = bits_bf162(__floats2bfloat162_rn(f2, f3));
+}
+
+// Q4_K, k-block c (0..3) of the super-block at `blk` (144 bytes): the 32 nibble bytes [16 + 32c, +32); low
+// nibbles are columns 0..31 (sub-block 2c), high nibbles columns 32..63 (sub-block 2c+1).  r[j] = columns 2j, 2j+1.
+__device__ __forceinline__ void unpack_q4k(const uint8_t* blk, int c, uint32_t (&r)[32]) {
+  const uint4 meta = *reinterpret_cast<const uint4*>(blk);
+  const float2 dd = __half22float2(*reinterpret_cast<const __half2*>(&meta.x));
+  uint32_t scw, mnw;   // bytes 0,1: 6-bit scale / min of sub-blocks 2c, 2c+1
+  if (c < 2) {
+    scw = (meta.y & 0x3F3F3F3Fu) >> (16 * c);
+    mnw = (meta.z & 0x3F3F3F3Fu) >> (16 * c);
+  } else {
+    scw = ((meta.w & 0x0F0F0F0Fu) | ((meta.y >> 2) & 0x30303030u)) >> (16 * (c - 2));
+    mnw = (((meta.w >> 4) & 0x0F0F0F0Fu) | ((meta.z >> 2) & 0x30303030u)) >> (16 * (c - 2));
+  }
+  const float s_lo = 128.f * dd.x * (float)(scw & 0xFFu), s_hi = 128.f * dd.x * (float)((scw >> 8) & 0xFFu);
+  const float c_lo = -dd.y * (float)(mnw & 0xFFu) - s_lo, c_hi = -dd.y * (float)((mnw >> 8) & 0xFFu) - s_hi;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const uint4 qv = *reinterpret_cast<const uint4*>(blk + 16 + 32 * c + 16 * half);
+    const uint32_t w[4] = {qv.x, qv.y, qv.z, qv.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      // word i of this half holds columns 16*half + 4i .. +3 (low nibbles) and 32 + the same (high nibbles)
+      bytes4_to_bf16(w[i] & 0x0F0F0F0Fu, s_lo, c_lo, r[8 * half + 2 * i], r[8 * half + 2 * i + 1]);
+      bytes4_to_bf16((w[i] >> 4) & 0x0F0F0F0Fu, s_hi, c_hi, r[16 + 8 * half + 2 * i], r[16 + 8 * half + 2 * i + 1]);
+    }
+  }
+}
+
+// Q6_K, k-block c of the 224-byte block [ql 128][qh 64][scales 16][d]: half = c >> 1, cb = c & 1.  Columns
+// 32t + l (t = 0, 1) of the k-block are element (half, qt = 2cb + t, l): ql byte half*64 + 32t + l (low nibble when
+// cb = 0, high when cb = 1), qh byte 128 + half*32 + l bits [2qt, 2qt+2), scale index half*8 + 2qt + (l >> 4).
+__device__ __forceinline__ void unpack_q6k(const uint8_t* blk, int c, uint32_t (&r)[32]) {
+  const int half = c >> 1, cb = c & 1;
+  const float d = __half2float(*reinterpret_cast<const __half*>(blk + 208));
+  const uint32_t scw = *reinterpret_cast<const uint32_t*>(blk + 192 + half * 8 + 4 * cb);   // 4 int8 scales
+  const uint4 h0 = *reinterpret_cast<const uint4*>(blk + 128 + half * 32);
+  const uint4 h1 = *reinterpret_cast<const uint4*>(blk + 128 + half * 32 + 16);
+  const uint32_t hw[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int sh = 4 * cb + 2 * t;   // = 2 * qt
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {    // l = 16u .. 16u+15 share one scale
+      const uint4 la = *reinterpret_cast<const uint4*>(blk + half * 64 + 32 * t + 16 * u);
+      const uint32_t lw[4] = {la.x, la.y, la.z, la.w};
+      const float sv = d * (float)(int8_t)(scw >> (8 * (2 * t + u)));   // weight = sv * (stored - 32)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t nib = (cb ? (lw[i] >> 4) : lw[i]) & 0x0F0F0F0Fu;
+        const uint32_t q4 = nib | (((hw[4 * u + i] >> sh) & 0x03030303u) << 4);
+        bytes4_to_bf16(q4, 128.f * sv, -160.f * sv, r[16 * t + 8 * u + 2 * i], r[16 * t + 8 * u + 2 * i + 1]);
+      }
+    }
+  }
+}
+
+// Q8_0, k-block c of a 256-column range staged as two 128-byte-swizzled planes [2][128 rows][128 int8] and one
+// plane [128 rows][8 fp16 scales]; `row` is the row inside the tile.
+__device__ __forceinline__ void unpack_q80(const uint8_t* qst, int row, int c, uint32_t (&r)[32]) {
+  const uint8_t* plane = qst + (size_t)(c >> 1) * (WN * 128) + (size_t)row * 128;
+  const uint32_t scw = *reinterpret_cast<const uint32_t*>(qst + 2 * WN * 128 + (size_t)row * 16 + 4 * c);
+  const __half2 sc2 = *reinterpret_cast<const __half2*>(&scw);
+  const float ds[2] = {__low2float(sc2), __high2float(sc2)};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {      // 16-byte chunk j of the k-block = chunk 4*(c&1) + j of the 128-byte row
+    const int chunk = 4 * (c & 1) + j;
+    const uint4 qv = *reinterpret_cast<const uint4*>(plane + ((chunk ^ (row & 7)) << 4));
+    const uint32_t w[4] = {qv.x, qv.y, qv.z, qv.w};
+    const float d = ds[j >> 1];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float f0 = d * (float)(int8_t)(w[i] & 0xFFu), f1 = d * (float)(int8_t)((w[i] >> 8) & 0xFFu);
+      const float f2 = d * (float)(int8_t)((w[i] >> 16) & 0xFFu), f3 = d * (float)(int8_t)(w[i] >> 24);
+      r[8 * j + 2 * i] = bits_bf162(__floats2bfloat162_rn(f0, f1));
+      r[8 * j + 2 * i + 1] = bits_bf162(__floats2bfloat162_rn(f2, f3));
+    }
+  }
+}
+
+__device__ __forceinline__ int q_row_bytes(int qtype) { return qtype == HE_Q4_K ? 144 : (qtype == HE_Q6_K ? 224 : 272); }
+
+// Tile walk shared by every role: tile index -> (split, m-tile, n-tile); M-fastest so that CTAs running at the
+// same time share the weight tile in L2.
+struct TileCoord {
+  int ks, tm, tn, b_row0, sb0, sb1;
+  bool skip;
+};
+
+__device__ __forceinline__ TileCoord tile_coord(const WqArgs& g, int tile, int tiles_m, int sb_all) {
+  TileCoord t;
+  const int ksp = g.k_splits;
+  t.ks = tile % ksp;
+  const int mn = tile / ksp;
+  t.tm = mn % tiles_m;
+  t.tn = mn / tiles_m;
+  t.b_row0 = t.tn * WN;
+  t.skip = false;
+  if (g.tile_group != nullptr) {
+    const int grp = __ldg(g.tile_group + t.tm);
+    t.skip = grp < 0;
+    t.b_row0 += (grp < 0 ? 0 : grp) * g.N;
+  }
+  t.sb0 = t.ks * g.sb_per;
+  t.sb1 = min(sb_all, t.sb0 + g.sb_per);
+  return t;
+}
+
+__global__ void __launch_bounds__(NTHREADS_WQ, 1)
+gemm_wq_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmQ0,
+               const __grid_constant__ CUtensorMap tmQ1, const WqArgs g) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* qring = smem + XSTAGES * g.x_stage_bytes;
+  WqBarriers* bar = reinterpret_cast<WqBarriers*>(qring + g.q_stages * g.q_stage_bytes);
+  const int QS = g.q_stages;
+  volatile int* abort_flag = &bar->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int mt = g.mt;
+  const int tiles_m = (g.M + mt - 1) / mt, tiles_n = (g.N + WN - 1) / WN;
+  const int n_tiles = tiles_m * tiles_n * g.k_splits;
+  const int sb_all = g.K >> 8;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < XSTAGES; ++s) {
+      mbar_init(&bar->x_full[s], 1);
+      mbar_init(&bar->x_empty[s], 1);
+    }
+    for (int s = 0; s < QS; ++s) {
+      mbar_init(&bar->q_full[s], 1);
+      mbar_init(&bar->q_empty[s], N_UNPACK_WARPS);
+    }
+    for (int s = 0; s < N_SETS; ++s) {
+      mbar_init(&bar->a_full[s], N_UNPACK_WARPS / N_SETS);
+      mbar_init(&bar->a_empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&bar->d_full[a], 1);
+      mbar_init(&bar->d_empty[a], 4);
+    }
+    bar->abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bar->tmem_base, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bar->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ activation tiles
+    if (elect_one()) {
+      tma_prefetch_desc(&tmX);
+      uint32_t it = 0;
+      for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+        const TileCoord t = tile_coord(g, tile, tiles_m, sb_all);
+        if (t.skip) continue;
+        for (int kb = 4 * t.sb0; kb < 4 * t.sb1; ++kb, ++it) {
+          const int s = it % XSTAGES;
+          if (!mbar_wait(&bar->x_empty[s], ((it / XSTAGES) & 1) ^ 1, abort_flag, g.status, 301)) break;
+          mbar_expect_tx(&bar->x_full[s], (uint32_t)mt * BK * 2);
+          tma_load_2d(smem + s * g.x_stage_bytes, &tmX, &bar->x_full[s], kb * BK, t.tm * mt);
+        }
+        if (*abort_flag) break;
+      }
+    }
+  } else if (warp == 2) {
+    // ------------------------------------------------------------ raw weight blocks
+    if (elect_one()) {
+      tma_prefetch_desc(&tmQ0);
+      const uint32_t rb = (uint32_t)q_row_bytes(g.qtype);
+      uint32_t qit = 0;
+      for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+        const TileCoord t = tile_coord(g, tile, tiles_m, sb_all);
+        if (t.skip) continue;
+        for (int sb = t.sb0; sb < t.sb1; ++sb, ++qit) {
+          const int qs = qit % QS;
+          if (!mbar_wait(&bar->q_empty[qs], ((qit / QS) & 1) ^ 1, abort_flag, g.status, 302)) break;
+          uint8_t* dst = qring + qs * g.q_stage_bytes;
+          uint64_t* fb = &bar->q_full[qs];
+          mbar_expect_tx(fb, WN * rb);
+          if (g.qtype == HE_Q8_0) {
+            tma_load_2d(dst, &tmQ0, fb, sb * 256, t.b_row0);
+            tma_load_2d(dst + WN * 128, &tmQ0, fb, sb * 256 + 128, t.b_row0);
+            tma_load_2d(dst + 2 * WN * 128, &tmQ1, fb, g.K + 16 * sb, t.b_row0);
+          } else {
+            tma_load_2d(dst, &tmQ0, fb, sb * (int)rb, t.b_row0);
+          }
+        }
+        if (*abort_flag) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      const uint32_t idesc = umma_idesc_bf16(WN, mt);
+      uint32_t it = 0, tcount = 0;
+      for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+        const TileCoord t = tile_coord(g, tile, tiles_m, sb_all);
+        if (t.skip) continue;
+        const int acc = tcount & 1;
+        if (!mbar_wait(&bar->d_empty[acc], ((tcount >> 1) & 1) ^ 1, abort_flag, g.status, 303)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * D_COLS;
+        const int n_kb = 4 * (t.sb1 - t.sb0);
+        for (int kb = 0; kb < n_kb; ++kb, ++it) {
+          const int s = it % XSTAGES, a = it % N_SETS;
+          if (!mbar_wait(&bar->x_full[s], (it / XSTAGES) & 1, abort_flag, g.status, 304)) break;
+          if (!mbar_wait(&bar->a_full[a], (it / N_SETS) & 1, abort_flag, g.status, 305)) break;
+          tc_fence_after();
+          const uint32_t x_addr = smem_u32(smem + s * g.x_stage_bytes);
+          const uint32_t a_tmem = tmem_base + A_COL0 + a * A_STAGE_COLS;
+#pragma unroll
+          for (int k = 0; k < BK / UK; ++k)
+            umma_f16_ts(d_tmem, a_tmem + k * (UK / 2), umma_desc_k_sw128(x_addr + k * UK * 2), idesc,
+                        (kb > 0 || k > 0) ? 1u : 0u);
+          umma_commit(&bar->x_empty[s]);    // the smem stage and ...
+          umma_commit(&bar->a_empty[a]);    // ... the TMEM operand stage are free once these MMAs have read them
+        }
+        if (*abort_flag) break;
+        umma_commit(&bar->d_full[acc]);
+        ++tcount;
+      }
+    }
+  } else if (warp >= WARP_UNPACK0) {
+    // ------------------------------------------------------------ unpack: raw blocks -> bf16 operand in TMEM
+    const int set = (warp - WARP_UNPACK0) >> 2;          // k-block of every super-block this warp expands
+    const int row = (warp & 3) * 32 + lane;              // weight row in the tile == TMEM lane
+    const uint32_t a_tmem = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + A_COL0 + set * A_STAGE_COLS;
+    const uint32_t rb = (uint32_t)q_row_bytes(g.qtype);
+    uint32_t qit = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+      const TileCoord t = tile_coord(g, tile, tiles_m, sb_all);
+      if (t.skip) continue;
+      for (int sb = t.sb0; sb < t.sb1; ++sb, ++qit) {
+        const int qs = qit % QS;
+        if (!mbar_wait(&bar->q_full[qs], (qit / QS) & 1, abort_flag, g.status, 306)) { ok = false; break; }
+        const uint8_t* qst = qring + qs * g.q_stage_bytes;
+        uint32_t r[32];
+        if (g.qtype == HE_Q4_K) unpack_q4k(qst + (size_t)row * 144, set, r);
+        else if (g.qtype == HE_Q6_K) unpack_q6k(qst + (size_t)row * 224, set, r);
+        else unpack_q80(qst, row, set, r);
+        // the operand stage is reused every super-block: wait until the MMAs of the previous one have read it
+        if (!mbar_wait(&bar->a_empty[set], (qit & 1) ^ 1, abort_flag, g.status, 307)) { ok = false; break; }
+        tc_fence_after();
+        tmem_st_32x32(a_tmem, r);
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&bar->a_full[set]);
+          mbar_arrive(&bar->q_empty[qs]);
+        }
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------ epilogue (warps 4..7): transposed store
+    const int q = warp & 3;
+    uint32_t tcount = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+      const TileCoord t = tile_coord(g, tile, tiles_m, sb_all);
+      if (t.skip) continue;
+      const int acc = tcount & 1;
+      if (!mbar_wait(&bar->d_full[acc], (tcount >> 1) & 1, abort_flag, g.status, 308)) break;
+      tc_fence_after();
+      const int n = t.tn * WN + q * 32 + lane;               // output column of this thread
+      const bool n_ok = n < g.N;
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * D_COLS;
+      const int m0 = t.tm * mt;
+      const int m_lim = min(mt, g.M - m0);                   // live activation rows of this tile
+#pragma unroll 1
+      for (int c = 0; c * 32 < m_lim; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c * 32, r);
+        tmem_ld_wait();
+        const int jn = min(32, m_lim - c * 32);
+        if (n_ok) {
+          if (g.epi == 0) {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(g.C) + (size_t)(m0 + c * 32) * g.ldc + n;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < jn) dst[(size_t)j * g.ldc] = __float2bfloat16_rn(__uint_as_float(r[j]));
+          } else {
+            float* dst = reinterpret_cast<float*>(g.C) + (size_t)(m0 + c * 32) * g.ldc + n +
+                         (g.epi == 4 ? (size_t)t.ks * (size_t)g.split_stride : (size_t)0);
+            if (g.epi == 2) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (j < jn) dst[(size_t)j * g.ldc] += __uint_as_float(r[j]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (j < jn) dst[(size_t)j * g.ldc] = __uint_as_float(r[j]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar->d_empty[acc]);
+      ++tcount;
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// out[m][n] (+)= sum over splits, in split order (deterministic).  mode 0: fp32 store, 1: fp32 add in place.
+__global__ void wq_splitk_reduce_kernel(const float* __restrict__ part, long long split_stride, int k_splits,
+                                        float* __restrict__ out, long long ldo, int M, int N, int mode) {
+  const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i >= (long long)M * N) return;
+  const int m = (int)(i / N), n = (int)(i % N);
+  float4 s = *reinterpret_cast<const float4*>(part + (size_t)m * N + n);
+  for (int k = 1; k < k_splits; ++k) {
+    const float4 v = *reinterpret_cast<const float4*>(part + (size_t)k * split_stride + (size_t)m * N + n);
+    s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+  }
+  float4* o = reinterpret_cast<float4*>(out + (size_t)m * ldo + n);
+  if (mode == 1) {
+    const float4 h = *o;
+    s.x += h.x; s.y += h.y; s.z += h.z; s.w += h.w;
+  }
+  *o = s;
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// Activations: bf16 row-major [rows][cols], row stride ld elements; box {64 columns, box_rows}, 128-byte swizzle.
+int make_x_map(CUtensorMap* m, const void* ptr, long long rows, long long cols, long long ld, int box_rows) {
+  EncodeTiledFn enc = get_encode();
+  if (enc == nullptr) return -HE_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0 || (ld * 2) % 16 != 0) return -HE_ERR_BAD_ARG;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
+}
+
+// Raw weight rows as bytes: [rows][row_bytes] uint8; box {box_bytes, 128 rows}.
+int make_q_map(CUtensorMap* m, const void* ptr, long long rows, long long row_bytes, int box_bytes, bool swizzle128) {
+  EncodeTiledFn enc = get_encode();
+  if (enc == nullptr) return -HE_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0 || row_bytes % 16 != 0 || box_bytes % 16 != 0) return -HE_ERR_BAD_ARG;
+  cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
+  cuuint32_t box[2] = {(cuuint32_t)box_bytes, (cuuint32_t)WN};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
+}
+
+int make_q_maps(CUtensorMap* q0, CUtensorMap* q1, const void* B, int qtype, long long rows, int K) {
+  int rc;
+  if (qtype == HE_Q4_K) {
+    rc = make_q_map(q0, B, rows, (long long)(K >> 8) * 144, 144, false);
+    *q1 = *q0;
+    return rc;
+  }
+  if (qtype == HE_Q6_K) {
+    rc = make_q_map(q0, B, rows, (long long)(K >> 8) * 224, 224, false);
+    *q1 = *q0;
+    return rc;
+  }
+  if (qtype == HE_Q8_0) {
+    const long long rb = (long long)K + (((K >> 4) + 15) / 16) * 16;
+    if ((rc = make_q_map(q0, B, rows, rb, 128, true)) != 0) return rc;
+    return make_q_map(q1, B, rows, rb, 16, false);
+  }
+  return -HE_ERR_BAD_ARG;
+}
+
+constexpr size_t SMEM_WQ = (size_t)SMEM_BUDGET + sizeof(WqBarriers) + 1024;
+
+int pick_mt(int M, bool grouped) {
+  if (grouped) return 128;
+  if (M >= MT_MAX) return MT_MAX;
+  return (M + 15) & ~15;
+}
+
+int launch_wq(const void* A, long long lda, int a_cols, const void* B, int qtype, long long b_rows, WqArgs g,
+              int num_sms, cudaStream_t stream) {
+  if (g.K % 256 != 0) return -HE_ERR_BAD_ARG;
+  if (a_cols <= 0 || a_cols > g.K || a_cols % 8 != 0) return -HE_ERR_BAD_ARG;
+  const int row_bytes = qtype == HE_Q4_K ? 144 : (qtype == HE_Q6_K ? 224 : 272);
+  g.x_stage_bytes = (g.mt * BK * 2 + 1023) & ~1023;
+  g.q_stage_bytes = (WN * row_bytes + 1023) & ~1023;
+  g.q_stages = (SMEM_BUDGET - XSTAGES * g.x_stage_bytes) / g.q_stage_bytes;
+  if (g.q_stages > QSTAGES_MAX) g.q_stages = QSTAGES_MAX;
+  if (g.q_stages < 2) return -HE_ERR_BAD_ARG;
+  CUtensorMap tmX, q0, q1;
+  int rc = make_x_map(&tmX, A, g.M, a_cols, lda, g.mt);
+  if (rc != 0) return rc;
+  rc = make_q_maps(&q0, &q1, B, qtype, b_rows, g.K);
+  if (rc != 0) return rc;
+  cudaError_t e = cudaFuncSetAttribute(gemm_wq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_WQ);
+  if (e != cudaSuccess) return (int)e;
+  const long long tiles = (long long)((g.M + g.mt - 1) / g.mt) * ((g.N + WN - 1) / WN) * g.k_splits;
+  const int grid = (int)(tiles < num_sms ? tiles : num_sms);
+  gemm_wq_kernel<<<grid, NTHREADS_WQ, SMEM_WQ, stream>>>(tmX, q0, q1, g);
+  HE_LAUNCH_CHECK();
+  return 0;
+}
+
+}  // namespace
+
+// C[M][N] = A[M][K] (bf16) * W[N][K]^T where W is `b_rows` rows in the device layout of `qtype` (Q4_K / Q6_K / Q8_0),
+// expanded to bf16 inside the pipeline.  epi: 0 bf16 store, 1 fp32 store, 2 fp32 accumulate into C.
+// `a_cols` (<= K, multiple of 8) is the number of columns A really has: columns up to K read as zeros (weights whose
+// K was padded to a whole number of 256-column blocks).  With `tile_group` (device, ceil(M/128) ints) the call is the
+// grouped form: 128-row M-tile tm uses weight rows [tile_group[tm] * N, +N); negative entries skip the tile.
+HE_API int he_gemm_q(const void* A, long long lda, int a_cols, const void* B, int qtype, long long b_rows, void* C,
+                     long long ldc, int M, int N, int K, int epi, const int* tile_group, void* status, int num_sms,
+                     cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  WqArgs g = {};
+  g.C = C; g.ldc = ldc; g.M = M; g.N = N; g.K = K; g.epi = epi; g.qtype = qtype;
+  g.mt = pick_mt(M, tile_group != nullptr);
+  g.k_splits = 1;
+  g.sb_per = K >> 8;
+  g.split_stride = 0;
+  g.tile_group = tile_group;
+  g.status = (int*)status;
+  return launch_wq(A, lda, a_cols, B, qtype, b_rows, g, num_sms, stream);
+}
+
+// Split plan of the deterministic split-K form: about one tile per SM, every split a whole number of 256-column
+// super-blocks and none empty.  Low 32 bits: split count; high 32 bits: super-blocks per split.
+HE_API long long he_gemm_q_splitk_plan(int M, int N, int K, int num_sms) {
+  const int mt = pick_mt(M, false);
+  const int tiles = ((M + mt - 1) / mt) * ((N + WN - 1) / WN);
+  const int sb_all = K >> 8;
+  // cost of a plan = rounds of work items per CTA x super-blocks per item (+1 per round for the tile change-over)
+  int k_splits = 1, sb_per = sb_all;
+  long long best = -1;
+  for (int ks = 1; ks <= sb_all && ks <= 32; ++ks) {
+    const int per = (sb_all + ks - 1) / ks;
+    const int ks_eff = (sb_all + per - 1) / per;
+    const long long items = (long long)tiles * ks_eff;
+    const long long rounds = (items + num_sms - 1) / num_sms;
+    const long long cost = rounds * (per + 1);
+    if (best < 0 || cost < best) {
+      best = cost;
+      k_splits = ks_eff;
+      sb_per = per;
+    }
+  }
+  return ((long long)sb_per << 32) | (long long)k_splits;
+}
+
+// out[M][N] (fp32) = (mode 0) or += (mode 1) A * W^T for few rows: the K range is split over CTAs so that every SM
+// streams a share of the quantised weight; partial tiles go to `partials` ([k_splits][M][N] fp32, caller scratch)
+// and are summed in split order (bit-reproducible).
+HE_API int he_gemm_q_splitk_det(const void* A, long long lda, const void* B, int qtype, long long b_rows,
+                                void* partials, void* out, long long ldo, int M, int N, int K, int mode, void* status,
+                                int num_sms, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (N % 4 != 0 || K % 256 != 0) return -HE_ERR_BAD_ARG;
+  const long long plan = he_gemm_q_splitk_plan(M, N, K, num_sms);
+  WqArgs g = {};
+  g.C = partials; g.ldc = N; g.M = M; g.N = N; g.K = K; g.epi = 4; g.qtype = qtype;
+  g.mt = pick_mt(M, false);
+  g.k_splits = (int)(plan & 0xffffffffll);
+  g.sb_per = (int)(plan >> 32);
+  g.split_stride = (long long)M * N;
+  g.tile_group = nullptr;
+  g.status = (int*)status;
+  const int rc = launch_wq(A, lda, K, B, qtype, b_rows, g, num_sms, stream);
+  if (rc != 0) return rc;
+  const long long n4 = ((long long)M * N + 3) / 4;
+  wq_splitk_reduce_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>((const float*)partials, g.split_stride,
+                                                                           g.k_splits, (float*)out, ldo, M, N, mode);
+  HE_LAUNCH_CHECK();
+  return 0;
+}

@@ -78,6 +78,9 @@ class GpuRunner(BaseRunner):
         self.graphs = DecodeGraphRunner(self.ex, max_rows=self.max_slots, use_graphs=config.use_cuda_graphs)
         self.resident_key: Tuple[int, ...] = ()
         self.pinned_ids = torch.zeros(max(self.max_slots, 8), dtype=torch.int64).pin_memory()
+        # the kernels' status word rides along with every per-step read-back (see _sync_checked)
+        self.pinned_status = torch.zeros(4, dtype=torch.int32).pin_memory()
+        self.status_word = K.status_tensor(self.device)
         self.stats = {"prefix_hits": 0, "prefix_hit_tokens": 0, "snapshots_taken": 0, "h2d_bytes": 0, "d2h_bytes": 0}
         # Speculative decoding: a provider drafts (the checkpoint's own NextN block, ``speculative/mtp.py``, or a
         # host drafter over the token history, ``speculative/providers.py``), the target verifies the chain
@@ -324,6 +327,23 @@ class GpuRunner(BaseRunner):
         self.radix.insert(rs.req.prompt_token_ids[:n_tokens], lease.pages[:n_tokens // self.page], {n_tokens: sid})
         self.stats["snapshots_taken"] += 1
 
+    # ------------------------------------------------------------------ device status
+    def _sync_checked(self, phase: str) -> None:
+        """The per-step stream synchronise, with the kernels' status word read back in the same breath.
+
+        A kernel whose bounded wait gave up (an mbarrier, or a peer rank's flag in the tensor-parallel collectives)
+        skips its update and records a code; tokens computed after that are wrong and, with several ranks, the
+        replicas no longer agree.  That is not containable per request: raise, so that the engine service records
+        itself unhealthy and fails what is in flight."""
+        self.pinned_status.copy_(self.status_word, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        self.stats["d2h_bytes"] += 16
+        code = int(self.pinned_status[0])
+        if code != 0:
+            self.status_word.zero_()
+            raise K.DeviceStatusError(f"{phase}: a kernel reported status {code} (a bounded wait gave up); "
+                                      "device state is incomplete")
+
     # ------------------------------------------------------------------ sampling
     def _sample_rows(self, rows: List[RequestState], logits: torch.Tensor) -> List[Tuple[int, Optional[TokenLogprob]]]:
         """logits: fp32 [R, V] on the device.  Plain rows use the device sampler; processed rows the host law."""
@@ -339,7 +359,7 @@ class GpuRunner(BaseRunner):
             K.sample_rows(sub, params, ids)
             host = self.pinned_ids[:len(plain)]
             host.copy_(ids, non_blocking=True)
-            torch.cuda.current_stream().synchronize()
+            self._sync_checked("sample")
             self.stats["d2h_bytes"] += 8 * len(plain)
             toks = host.tolist()
             for i in plain:
@@ -385,7 +405,7 @@ class GpuRunner(BaseRunner):
             self.graphs.step(R, max_ctx, greedy=True)
             host = self.pinned_ids[:R]
             host.copy_(self.graphs.next_ids[:R], non_blocking=True)
-            torch.cuda.current_stream().synchronize()
+            self._sync_checked("decode")
             self.stats["d2h_bytes"] += 8 * R
             for rs in rows:
                 rs.telemetry.d2h_bytes += 8

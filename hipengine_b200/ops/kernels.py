@@ -243,14 +243,20 @@ _STATUS_WORDS = {}
 
 def status_tensor(device) -> torch.Tensor:
     """Per-device int32[4] status word that kernels with bounded waits write on failure."""
-    key = torch.device(device).index or 0
+    dev = torch.device(device)
+    # "cuda" without an index means this thread's current device (rank r of a multi-GPU job runs on cuda:r)
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
     if key not in _STATUS_WORDS:
-        _STATUS_WORDS[key] = torch.zeros(4, dtype=torch.int32, device=device)
+        _STATUS_WORDS[key] = torch.zeros(4, dtype=torch.int32, device=torch.device("cuda", key))
     return _STATUS_WORDS[key]
 
 
 def _status_ptr(device) -> int:
     return status_tensor(device).data_ptr()
+
+
+class DeviceStatusError(RuntimeError):
+    """A kernel's bounded wait gave up (mbarrier, peer flag): what it was computing is incomplete."""
 
 
 def check_status(device="cuda") -> None:
@@ -259,7 +265,7 @@ def check_status(device="cuda") -> None:
     v = int(st[0].item())
     if v != 0:
         st.zero_()
-        raise RuntimeError(f"sm_100a kernel reported status {v} (a bounded wait gave up)")
+        raise DeviceStatusError(f"sm_100a kernel reported status {v} (a bounded wait gave up)")
 
 
 def dequant_bf16(w: DeviceWeight, out: Optional[torch.Tensor] = None, row0: int = 0,

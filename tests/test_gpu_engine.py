@@ -139,3 +139,29 @@ def test_cold_tier_brings_an_evicted_prefix_back():
         runner.pool.assert_conserved()
     finally:
         llm.close()
+
+
+def test_status_word_of_a_failed_device_wait_makes_the_engine_unhealthy():
+    """A kernel whose bounded wait gave up records a status code and skips its update.  The serving path reads that
+    word with every per-step read-back: the request fails, the service turns unhealthy and refuses new work (the
+    code is injected on the host here: nothing on the device waits or faults)."""
+    from hipengine_b200 import LLM, SamplingParams
+    from hipengine_b200.generation.engine_service import EngineUnavailable
+    from hipengine_b200.loading.synth import build_random_model
+    from hipengine_b200.models.config import TINY_HYBRID
+    from hipengine_b200.ops import kernels as K
+    w = build_random_model(TINY_HYBRID, seed=3, std=0.05)
+    llm = LLM(w.to("cuda"), backend="cuda_sm100a", max_active_requests=2, max_sequence_length=256)
+    try:
+        ok = llm.generate_detailed([1, 2, 3, 4], SamplingParams(max_tokens=3, ignore_eos=True))[0]
+        assert len(ok.token_ids) == 3
+        K.status_tensor("cuda")[0] = 1            # what comm_push_reduce / the GEMM pipelines write on a timeout
+        torch.cuda.synchronize()
+        bad = llm.generate_detailed([5, 6, 7, 8], SamplingParams(max_tokens=4, ignore_eos=True))[0]
+        assert bad.finish.reason == "error" and "status" in (bad.error or "").lower(), (bad.finish, bad.error)
+        assert int(K.status_tensor("cuda")[0].item()) == 0          # consumed
+        with pytest.raises(EngineUnavailable):
+            llm.generate_detailed([9, 10], SamplingParams(max_tokens=2))
+    finally:
+        K.status_tensor("cuda").zero_()
+        llm.close()
