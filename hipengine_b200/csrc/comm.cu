@@ -16,6 +16,7 @@
 // residual; the context stays usable and the host sees the failure on its next status check.
 // The reference engine is single-device: no counterpart there.
 #include "common.cuh"
+#include "peer_comm.cuh"
 
 using namespace he;
 
@@ -150,6 +151,162 @@ HE_API int he_comm_push_reduce(const CommArgs* args, int n_ctas, cudaStream_t st
   if (a.width % 4 != 0 || (long long)a.rows * a.width > a.slot_floats) return -HE_ERR_BAD_ARG;
   if (n_ctas < 1 || n_ctas > COMM_MAX_CTAS) return -HE_ERR_BAD_ARG;
   cudaError_t e = launch_pdl(comm_push_reduce_kernel, dim3(n_ctas), dim3(256), 0, stream, a);
+  if (e != cudaSuccess) return (int)e;
+  HE_LAUNCH_CHECK();
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Collectives over the same receive regions as the decode GEMV's push epilogue (peer_comm.cuh).
+namespace {
+
+// Stand-alone consumer of a push: resid rows += sum over ranks of the pushed partial rows (rank order).  Used where
+// the next reader of the residual is not a GEMV with a reduce prologue (MoE routing, tensor-core batches, NextN).
+__global__ void __launch_bounds__(256) comm_reduce_in_kernel(const HeGemvComm c, float* resid, long long ld_resid,
+                                                             int rows, int* status) {
+  pdl_launch();
+  pdl_wait();
+  const uint32_t tag = *reinterpret_cast<volatile uint32_t*>(c.state);
+  const int parity = (int)((tag - 1u) & 1u);
+  const uint2* mine = c.recv[c.rank] + (size_t)parity * c.world * c.slot_floats;
+  const int total = rows * c.width;
+  for (int i = (blockIdx.x * blockDim.x + threadIdx.x) * 8; i < total; i += gridDim.x * blockDim.x * 8) {
+    float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int q = 0; q < c.world; ++q) {
+      float v[8];
+      ll_load8(mine + (size_t)q * c.slot_floats + i, tag, c.wait_limit, status, v);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) s[e] = q == 0 ? v[e] : s[e] + v[e];
+    }
+    const int row = i / c.width, col = i % c.width;
+    float4* hp = reinterpret_cast<float4*>(resid + (size_t)row * ld_resid + col);
+    float4 h0 = hp[0], h1 = hp[1];
+    h0.x += s[0]; h0.y += s[1]; h0.z += s[2]; h0.w += s[3];
+    h1.x += s[4]; h1.y += s[5]; h1.z += s[6]; h1.w += s[7];
+    hp[0] = h0;
+    hp[1] = h1;
+  }
+}
+
+// Stand-alone producer: pushes `rows` fp32 rows (any producer's output, e.g. the MoE expert sum) to every rank.
+__global__ void __launch_bounds__(256) comm_push_rows_kernel(const HeGemvComm c, const float* partial, int rows) {
+  pdl_launch();
+  pdl_wait();
+  const uint32_t seq0 = *reinterpret_cast<volatile uint32_t*>(c.state);
+  const size_t off = ((size_t)(seq0 & 1u) * c.world + c.rank) * c.slot_floats;
+  const int total = rows * c.width;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    const float v = partial[i];
+    for (int q = 0; q < c.world; ++q) ll_store(c.recv[q] + off + i, v, seq0 + 1u);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned prev = atomicAdd(c.state + 1, 1u);
+    if (prev == gridDim.x - 1) {
+      c.state[1] = 0;
+      *reinterpret_cast<volatile uint32_t*>(c.state) = seq0 + 1u;
+    }
+  }
+}
+
+// Vocab-parallel greedy head: every rank has the (max, id) of its own vocabulary shard per row; one CTA pushes its
+// pairs to every rank, waits (bounded) for the others and keeps the best pair: larger value, lower token id on exact
+// ties -- what a single argmax over the concatenated logits returns.  A region word is one (value, id) pair; this
+// exchange is ordered by the region's stamps (fence + flag), not by tags.
+__global__ void __launch_bounds__(64) comm_argmax_merge_kernel(const HeGemvComm c, const float* loc_val,
+                                                               const long long* loc_idx, int vocab_off, int rows,
+                                                               long long* out_ids, int* status) {
+  __shared__ int ok_s;
+  pdl_launch();
+  pdl_wait();
+  const uint32_t seq0 = *reinterpret_cast<volatile uint32_t*>(c.state);
+  const int parity = (int)(seq0 & 1u);
+  const int t = threadIdx.x;
+  if (t < rows) {
+    const uint2 word = make_uint2(__float_as_uint(loc_val[t]), (uint32_t)((int)loc_idx[t] + vocab_off));
+    const size_t off = ((size_t)parity * c.world + c.rank) * c.slot_floats + (size_t)t;
+    for (int q = 0; q < c.world; ++q) c.recv[q][off] = word;
+  }
+  if (t == 0) ok_s = 1;
+  __threadfence_system();
+  __syncthreads();
+  if (t < c.world) st_release_sys_u32(c.flags[t] + parity * c.world + c.rank, seq0 + 1u);
+  if (t < c.world) {
+    const uint32_t* f = c.flags[c.rank] + parity * c.world + t;
+    unsigned polls = 0;
+    while ((int)(ld_acquire_sys_u32(f) - (seq0 + 1u)) < 0) {
+      if (++polls > c.wait_limit) {
+        ok_s = 0;
+        if (status != nullptr) atomicCAS(status, 0, HE_ERR_WAIT_TIMEOUT);
+        break;
+      }
+      __nanosleep(64);
+    }
+  }
+  __syncthreads();
+  if (t < rows && ok_s) {
+    const uint2* mine = c.recv[c.rank] + (size_t)parity * c.world * c.slot_floats + (size_t)t;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int q = 0; q < c.world; ++q) {
+      uint2 p;
+      asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(p.x), "=r"(p.y) : "l"(mine + (size_t)q * c.slot_floats));
+      const float pv = __uint_as_float(p.x);
+      const int id = (int)p.y;
+      if (pv > bv || (pv == bv && id < bi)) { bv = pv; bi = id; }
+    }
+    out_ids[t] = bi == 0x7fffffff ? 0 : bi;
+  }
+  if (t == 0) *reinterpret_cast<volatile uint32_t*>(c.state) = seq0 + 1u;
+}
+
+int comm_valid(const HeGemvComm& c, int rows) {
+  if (c.world < 2 || c.world > GEMV_MAX_WORLD || c.rank < 0 || c.rank >= c.world || c.state == nullptr) return 0;
+  if (c.width % 8 != 0 && c.width != 1) return 0;
+  if ((long long)rows * c.width > c.slot_floats) return 0;
+  for (int q = 0; q < c.world; ++q)
+    if (c.recv[q] == nullptr || c.flags[q] == nullptr) return 0;
+  return 1;
+}
+
+}  // namespace
+
+HE_API int he_gemv_comm_size() { return (int)sizeof(HeGemvComm); }
+
+HE_API int he_comm_reduce_in(const HeGemvComm* comm, void* resid, long long ld_resid, int rows, void* status,
+                             cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (!comm_valid(*comm, rows) || ld_resid % 4 != 0) return -HE_ERR_BAD_ARG;
+  const int n8 = rows * comm->width / 8;
+  int grid = (n8 + 255) / 256;
+  if (grid > 32) grid = 32;
+  if (grid < 1) grid = 1;
+  cudaError_t e = launch_pdl(comm_reduce_in_kernel, dim3(grid), dim3(256), 0, stream, *comm, (float*)resid, ld_resid,
+                             rows, (int*)status);
+  if (e != cudaSuccess) return (int)e;
+  HE_LAUNCH_CHECK();
+  return 0;
+}
+
+HE_API int he_comm_push_rows(const HeGemvComm* comm, const void* partial, int rows, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (!comm_valid(*comm, rows)) return -HE_ERR_BAD_ARG;
+  const int n1 = rows * comm->width;
+  int grid = (n1 + 255) / 256;
+  if (grid > 64) grid = 64;
+  cudaError_t e = launch_pdl(comm_push_rows_kernel, dim3(grid), dim3(256), 0, stream, *comm, (const float*)partial,
+                             rows);
+  if (e != cudaSuccess) return (int)e;
+  HE_LAUNCH_CHECK();
+  return 0;
+}
+
+HE_API int he_comm_argmax_merge(const HeGemvComm* comm, const void* loc_val, const void* loc_idx, int vocab_off,
+                                int rows, void* out_ids, void* status, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (rows > 64 || comm->width != 1 || !comm_valid(*comm, rows)) return -HE_ERR_BAD_ARG;
+  cudaError_t e = launch_pdl(comm_argmax_merge_kernel, dim3(1), dim3(64), 0, stream, *comm, (const float*)loc_val,
+                             (const long long*)loc_idx, vocab_off, rows, (long long*)out_ids, (int*)status);
   if (e != cudaSuccess) return (int)e;
   HE_LAUNCH_CHECK();
   return 0;

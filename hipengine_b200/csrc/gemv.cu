@@ -17,6 +17,7 @@
 #include <cstdlib>
 #include "common.cuh"
 #include "gemv_rows.cuh"
+#include "peer_comm.cuh"
 #include "sm100.cuh"
 
 using namespace he;
@@ -47,6 +48,7 @@ struct HeGemvArgs {
   int rg;           // weight rows per work item: 2, 4 or 8 (set by the launcher); 32/rg blocks per staged unit
   int slot_bytes;   // bytes of one ring slot = rg * row_stride
   int* status;      // device status word (may be null)
+  HeGemvComm comm;  // mode 0: unused
 };
 
 namespace {
@@ -108,6 +110,16 @@ __device__ void prologue(const HeGemvArgs& a, const SmemView& s, float* red) {
   constexpr int MAXG = 4;
   const int nthr = (int)blockDim.x;
   const bool one_pass = a.norm_w != nullptr && n_groups <= MAXG * nthr;
+  // reduce mode (the launcher admits it only with the one-pass prologue and fp32 rows): the rows are the residual
+  // stream, to which the partial rows pushed by every rank are added before anything else happens
+  const bool rin = (a.comm.mode & 2) != 0;
+  __shared__ int last_cta_s;
+  uint32_t rin_tag = 0;
+  int parity = 0;
+  if (rin) {
+    rin_tag = *reinterpret_cast<volatile uint32_t*>(a.comm.state);     // tag of the push being consumed
+    parity = (int)((rin_tag - 1u) & 1u);
+  }
   for (int r = 0; r < R; ++r) {
     const size_t base = (size_t)r * a.x_stride;
     if (one_pass) {
@@ -118,6 +130,16 @@ __device__ void prologue(const HeGemvArgs& a, const SmemView& s, float* red) {
         const int g = u * nthr + (int)threadIdx.x;
         if (g < n_groups) {
           load8(a.x, a.x_dtype, base + (size_t)g * 8, v[u]);
+          if (rin) {
+            const uint2* pp = a.comm.recv[a.comm.rank] + (size_t)parity * a.comm.world * a.comm.slot_floats +
+                              (size_t)r * a.comm.width + (size_t)g * 8;
+            for (int q = 0; q < a.comm.world; ++q, pp += a.comm.slot_floats) {   // rank order: replicas agree
+              float pv[8];
+              ll_load8(pp, rin_tag, a.comm.wait_limit, a.status, pv);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) v[u][i] += pv[i];
+            }
+          }
 #pragma unroll
           for (int i = 0; i < 8; ++i) ss += v[u][i] * v[u][i];
         } else {
@@ -128,6 +150,27 @@ __device__ void prologue(const HeGemvArgs& a, const SmemView& s, float* red) {
       ss = block_sum(ss, red);
       const float inv_rms = rsqrtf(ss / (float)K + a.eps);
       if (threadIdx.x == 0) s.inv_rms[r] = inv_rms;
+      if (rin) {
+        // every thread of this CTA has read row r (the barriers inside block_sum); the last CTA of the grid to get
+        // here is the only one that may overwrite the row with the reduced residual
+        if (threadIdx.x == 0) {
+          const unsigned prev = atomicAdd(a.comm.state + 2 + r, 1u);
+          last_cta_s = prev == gridDim.x - 1;
+          if (last_cta_s) a.comm.state[2 + r] = 0;
+        }
+        __syncthreads();
+        if (last_cta_s) {
+          float* xw = const_cast<float*>(reinterpret_cast<const float*>(a.x)) + base;
+#pragma unroll
+          for (int u = 0; u < MAXG; ++u) {
+            const int g = u * nthr + (int)threadIdx.x;
+            if (g < n_groups) {
+              reinterpret_cast<float4*>(xw + (size_t)g * 8)[0] = make_float4(v[u][0], v[u][1], v[u][2], v[u][3]);
+              reinterpret_cast<float4*>(xw + (size_t)g * 8)[1] = make_float4(v[u][4], v[u][5], v[u][6], v[u][7]);
+            }
+          }
+        }
+      }
 #pragma unroll
       for (int u = 0; u < MAXG; ++u) {
         const int g = u * nthr + (int)threadIdx.x;
@@ -344,6 +387,18 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const __grid_constant_
   for (int i = 0; i < a.n_slots - 1; ++i) issue();
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
+  const bool push = (a.comm.mode & 1) != 0;
+  uint32_t push_seq = 0;
+  size_t push_off = 0;                 // float offset of slot (parity, my rank) inside a receive region
+  if (push) {
+    push_seq = *reinterpret_cast<volatile uint32_t*>(a.comm.state);
+    push_off = ((size_t)(push_seq & 1u) * a.comm.world + a.comm.rank) * a.comm.slot_floats;
+  }
+  auto push_store = [&](int r, int n, float v) {
+    const size_t off = push_off + (size_t)r * a.comm.width + n;
+    for (int q = 0; q < a.comm.world; ++q) ll_store(a.comm.recv[q] + off, v, push_seq + 1u);
+  };
+
   prologue<R>(a, s, red);
 
   const int t_row = lane >> bq_shift, bq = lane & (BQ - 1);
@@ -374,7 +429,8 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const __grid_constant_
             const float v = warp_sum(fa[r]);
             if (lane == 0) {
               const size_t off = (size_t)r * fsg.out_stride + fr.n;
-              if (fsg.epi == 0) reinterpret_cast<float*>(fsg.out)[off] = v;
+              if (push) push_store(r, fr.n, v);
+              else if (fsg.epi == 0) reinterpret_cast<float*>(fsg.out)[off] = v;
               else if (fsg.epi == 1) reinterpret_cast<__nv_bfloat16*>(fsg.out)[off] = f32_to_bf16(v);
               else reinterpret_cast<float*>(fsg.out)[off] += v;
             }
@@ -419,13 +475,26 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const __grid_constant_
 #pragma unroll
         for (int r = 0; r < R; ++r) {
           const size_t off = (size_t)r * sg.out_stride + rr.n;
-          if (sg.epi == 0) reinterpret_cast<float*>(sg.out)[off] = acc[r];
+          if (push) push_store(r, rr.n, acc[r]);
+          else if (sg.epi == 0) reinterpret_cast<float*>(sg.out)[off] = acc[r];
           else if (sg.epi == 1) reinterpret_cast<__nv_bfloat16*>(sg.out)[off] = f32_to_bf16(acc[r]);
           else reinterpret_cast<float*>(sg.out)[off] += acc[r];
         }
       }
     }
     advance(cc);
+  }
+  if (push) {
+    // the words carry their own tag, so nothing has to be published: the last CTA of the grid only advances the
+    // local sequence number for the launches that follow in this stream
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const unsigned prev = atomicAdd(a.comm.state + 1, 1u);
+      if (prev == gridDim.x - 1) {
+        a.comm.state[1] = 0;
+        *reinterpret_cast<volatile uint32_t*>(a.comm.state) = push_seq + 1u;
+      }
+    }
   }
 }
 
@@ -531,6 +600,27 @@ int launch_gemv(HeGemvArgs a, int num_sms, cudaStream_t stream) {
 HE_API int he_gemv(const HeGemvArgs* args, int num_sms, cudaStream_t stream) {
   const HeGemvArgs& a = *args;
   if (a.K % 256 != 0 || a.n_seg < 1 || a.n_seg > 4 || a.R < 1 || a.R > 8) return -HE_ERR_BAD_ARG;
+  if (a.comm.mode != 0) {
+    const HeGemvComm& c = a.comm;
+    if (c.world < 2 || c.world > GEMV_MAX_WORLD || c.rank < 0 || c.rank >= c.world || c.state == nullptr ||
+        (long long)a.R * c.width > c.slot_floats)
+      return -HE_ERR_BAD_ARG;
+    for (int q = 0; q < c.world; ++q)
+      if (c.recv[q] == nullptr || c.flags[q] == nullptr) return -HE_ERR_BAD_ARG;
+    // push: one fp32-store segment as wide as the reduced tensor
+    if ((c.mode & 1) && (a.n_seg != 1 || a.seg[0].epi != 0 || a.seg[0].n_rows != c.width)) return -HE_ERR_BAD_ARG;
+    // reduce: fp32 residual rows of that width through the one-pass norm prologue (at most 8192 columns), and every
+    // segment quantised (float-typed weights read the activation rows from global memory, not the reduced values)
+    if (c.mode & 2) {
+      if (a.x_dtype != 0 || a.norm_w == nullptr || a.K != c.width || a.K > 8192 || c.width % 8 != 0)
+        return -HE_ERR_BAD_ARG;
+      for (int i = 0; i < a.n_seg; ++i) {
+        const int t[2] = {a.seg[i].qtype, a.seg[i].epi >= 3 ? a.seg[i].qtype2 : a.seg[i].qtype};
+        for (int j = 0; j < 2; ++j)
+          if (t[j] != HE_Q4_K && t[j] != HE_Q6_K && t[j] != HE_Q8_0) return -HE_ERR_BAD_ARG;
+      }
+    }
+  }
   switch (a.R) {
     case 1: return launch_gemv<1>(a, num_sms, stream);
     case 2: return launch_gemv<2>(a, num_sms, stream);

@@ -73,11 +73,12 @@ class DecodeGraphRunner:
     def _step_body(self, rows: int, max_ctx: int, greedy: bool) -> None:
         ex = self.ex
         b = self.batch(rows, max_ctx)
-        h = ex.forward(b)
-        ex.logits(h, out=self.logits[:rows], hidden_out=self.hidden[:rows])
+        h = ex.forward(b, defer_resid=True)
         if greedy:
-            ex.greedy(self.logits[:rows], self.next_ids[:rows])
+            ex.head_greedy(h, self.next_ids[:rows], logits_out=self.logits[:rows], hidden_out=self.hidden[:rows])
             self.publish(rows)
+        else:
+            ex.logits(h, out=self.logits[:rows], hidden_out=self.hidden[:rows])
 
     def publish(self, rows: int) -> None:
         """next_ids -> tokens, advance positions (device side)."""

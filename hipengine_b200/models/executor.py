@@ -240,6 +240,15 @@ class HybridExecutor:
         dst = out if out is not None else self.scratch.get(name + "_bf", (T, w.n_rows), torch.bfloat16)
         return self._gemm(x, w, dst, tag=tag)
 
+    # GEMVs whose activation rows ARE the residual stream go through this hook, and any other reader of the residual
+    # calls _sync_resid first: a tensor-parallel executor defers the cross-rank sum of a row-parallel projection to
+    # the next reader (folded into that GEMV's prologue, or a small stand-alone kernel).
+    def _gemv_resid(self, h: torch.Tensor, segs, norm_w: torch.Tensor, eps: float) -> None:
+        K.gemv(h, segs, norm_w=norm_w, eps=eps)
+
+    def _sync_resid(self, h: torch.Tensor) -> None:
+        return
+
     # Row-parallel ("output") projections: h += x @ W^T.  A tensor-parallel executor overrides these two to
     # reduce the partial products across ranks before the residual add.
     def _out_small(self, x: torch.Tensor, w: DeviceWeight, h: torch.Tensor) -> None:
@@ -271,10 +280,12 @@ class HybridExecutor:
             qf = sc.get("q_f32", (T, qw), torch.float32)
             kf = sc.get("k_f32", (T, cfg.kv_width), torch.float32)
             vf = sc.get("v_f32", (T, cfg.kv_width), torch.float32)
-            K.gemv(h, [GemvSegment(self.W(i, "attn_q.weight"), qf), GemvSegment(self.W(i, "attn_k.weight"), kf),
-                       GemvSegment(self.W(i, "attn_v.weight"), vf)], norm_w=self.F(i, "attn_norm.weight"),
-                   eps=cfg.rms_eps)
+            self._gemv_resid(h, [GemvSegment(self.W(i, "attn_q.weight"), qf),
+                                 GemvSegment(self.W(i, "attn_k.weight"), kf),
+                                 GemvSegment(self.W(i, "attn_v.weight"), vf)], self.F(i, "attn_norm.weight"),
+                             cfg.rms_eps)
         else:
+            self._sync_resid(h)
             xn = sc.get("xn", (T, cfg.hidden), torch.bfloat16)
             K.rmsnorm_rows(h, self.F(i, "attn_norm.weight"), xn, cfg.rms_eps)
             qf = self._proj(xn, self.W(i, "attn_q.weight"), "q", "q")
@@ -331,22 +342,24 @@ class HybridExecutor:
                     # the 2*Hv Q8_0 rows get their own (tiny) launch: in the same launch their 272-byte blocks
                     # would size every ring slot and halve the warps of the two big Q4_K projections (for narrow
                     # models the projections are so short that the extra launch costs more than it saves)
-                    K.gemv(h, [GemvSegment(self.W(i, "attn_qkv.weight"), qkv),
-                               GemvSegment(self.W(i, "attn_gate.weight"), z)],
-                           norm_w=self.F(i, "attn_norm.weight"), eps=cfg.rms_eps)
+                    self._gemv_resid(h, [GemvSegment(self.W(i, "attn_qkv.weight"), qkv),
+                                         GemvSegment(self.W(i, "attn_gate.weight"), z)],
+                                     self.F(i, "attn_norm.weight"), cfg.rms_eps)
                     K.gemv(h, [GemvSegment(self.ab_q8[i], ab)], norm_w=self.F(i, "attn_norm.weight"), eps=cfg.rms_eps)
                 else:
-                    K.gemv(h, [GemvSegment(self.W(i, "attn_qkv.weight"), qkv),
-                               GemvSegment(self.W(i, "attn_gate.weight"), z), GemvSegment(self.ab_q8[i], ab)],
-                           norm_w=self.F(i, "attn_norm.weight"), eps=cfg.rms_eps)
+                    self._gemv_resid(h, [GemvSegment(self.W(i, "attn_qkv.weight"), qkv),
+                                         GemvSegment(self.W(i, "attn_gate.weight"), z),
+                                         GemvSegment(self.ab_q8[i], ab)],
+                                     self.F(i, "attn_norm.weight"), cfg.rms_eps)
                 a_p, b_p = ab[:, :Hv], ab[:, Hv:]
             else:
-                K.gemv(h, [GemvSegment(self.W(i, "attn_qkv.weight"), qkv),
-                           GemvSegment(self.W(i, "attn_gate.weight"), z),
-                           GemvSegment(self.W(i, "ssm_alpha.weight"), a_p),
-                           GemvSegment(self.W(i, "ssm_beta.weight"), b_p)],
-                       norm_w=self.F(i, "attn_norm.weight"), eps=cfg.rms_eps)
+                self._gemv_resid(h, [GemvSegment(self.W(i, "attn_qkv.weight"), qkv),
+                                     GemvSegment(self.W(i, "attn_gate.weight"), z),
+                                     GemvSegment(self.W(i, "ssm_alpha.weight"), a_p),
+                                     GemvSegment(self.W(i, "ssm_beta.weight"), b_p)],
+                                 self.F(i, "attn_norm.weight"), cfg.rms_eps)
         else:
+            self._sync_resid(h)
             xn = sc.get("xn", (T, cfg.hidden), torch.bfloat16)
             K.rmsnorm_rows(h, self.F(i, "attn_norm.weight"), xn, cfg.rms_eps)
             qkv = self._proj(xn, self.W(i, "attn_qkv.weight"), "qkv", "q")
@@ -397,16 +410,18 @@ class HybridExecutor:
         norm_w = self.F(i, ffn_norm_slot(cfg))
         if cfg.is_moe:
             from . import moe as M
+            self._sync_resid(h)
             M.moe_ffn(self, i, h, T, norm_w, small)
             return
         Fd = cfg.ffn
         epi = K.EPI_SILU_MUL if cfg.act == "silu" else K.EPI_GELU_MUL
         if small:
             act = sc.get("ffn_act", (T, Fd), torch.bfloat16)
-            K.gemv(h, [GemvSegment(self.W(i, "ffn_gate.weight"), act, epi, self.W(i, "ffn_up.weight"))],
-                   norm_w=norm_w, eps=cfg.rms_eps)
+            self._gemv_resid(h, [GemvSegment(self.W(i, "ffn_gate.weight"), act, epi, self.W(i, "ffn_up.weight"))],
+                             norm_w, cfg.rms_eps)
             self._out_small(act, self.W(i, "ffn_down.weight"), h)
         else:
+            self._sync_resid(h)
             xn = sc.get("xn", (T, cfg.hidden), torch.bfloat16)
             K.rmsnorm_rows(h, norm_w, xn, cfg.rms_eps)
             if self._use_splitk(T):
@@ -423,8 +438,11 @@ class HybridExecutor:
             self._out_big(act, self.W(i, "ffn_down.weight"), h, "d")
 
     # ------------------------------------------------------------------ whole model
-    def forward(self, b: BatchDesc, journal: Optional[dict] = None, h_out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """Runs all layers over the packed rows; returns the fp32 residual stream [T, hidden] (pre output_norm)."""
+    def forward(self, b: BatchDesc, journal: Optional[dict] = None, h_out: Optional[torch.Tensor] = None,
+                defer_resid: bool = False) -> torch.Tensor:
+        """Runs all layers over the packed rows; returns the fp32 residual stream [T, hidden] (pre output_norm).
+        With ``defer_resid`` a tensor-parallel executor may leave the last cross-rank sum pending for ``logits`` /
+        ``head_greedy`` to fold in; otherwise the returned rows are complete."""
         cfg = self.cfg
         T = b.T
         small = T <= self.small_rows
@@ -436,6 +454,8 @@ class HybridExecutor:
             else:
                 self._attention_linear(i, h, b, small, journal)
             self._ffn(i, h, b, small)
+        if not defer_resid:
+            self._sync_resid(h)
         return h
 
     def logits(self, h_rows: torch.Tensor, out: Optional[torch.Tensor] = None,
@@ -446,18 +466,26 @@ class HybridExecutor:
         head = self.dw["output.weight"]
         if out is None:
             out = self.scratch.get("logits", (R, cfg.vocab), torch.float32)
-        if hidden_out is not None:
-            K.rmsnorm_rows(h_rows, self.f32["output_norm.weight"], hidden_out, cfg.rms_eps)
         if R <= GEMV_MAX_ROWS:
-            K.gemv(h_rows, [GemvSegment(head, out)], norm_w=self.f32["output_norm.weight"], eps=cfg.rms_eps)
+            self._gemv_resid(h_rows, [GemvSegment(head, out)], self.f32["output_norm.weight"], cfg.rms_eps)
         else:
+            self._sync_resid(h_rows)
             xn = self.scratch.get("xn_head", (R, cfg.hidden), torch.bfloat16)
             K.rmsnorm_rows(h_rows, self.f32["output_norm.weight"], xn, cfg.rms_eps)
             lb = self._gemm(xn, head, self.scratch.get("logits_bf", (R, cfg.vocab), torch.bfloat16), tag="head")
             out.copy_(lb)
+        if hidden_out is not None:
+            K.rmsnorm_rows(h_rows, self.f32["output_norm.weight"], hidden_out, cfg.rms_eps)
         if cfg.final_softcap > 0:
             K.softcap_(out, cfg.final_softcap)
         return out
+
+    def head_greedy(self, h_rows: torch.Tensor, out_ids: torch.Tensor, logits_out: Optional[torch.Tensor] = None,
+                    hidden_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Greedy decode head: output norm + lm_head + argmax over the rows -> ``out_ids`` (int64).  A vocab-parallel
+        executor overrides this to merge per-shard (max, id) pairs instead of gathering logits."""
+        lg = self.logits(h_rows, out=logits_out, hidden_out=hidden_out)
+        return self.greedy(lg, out_ids)
 
     # ------------------------------------------------------------------ NextN / MTP draft block
     @property

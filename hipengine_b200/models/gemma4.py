@@ -215,7 +215,8 @@ class Gemma4Executor(HybridExecutor):
                       self.F(i, "post_ffw_norm.weight"), self.F(i, "layer_output_scale.weight"), eps)
 
     # ------------------------------------------------------------------ whole model
-    def forward(self, b: BatchDesc, journal: Optional[dict] = None, h_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def forward(self, b: BatchDesc, journal: Optional[dict] = None, h_out: Optional[torch.Tensor] = None,
+                defer_resid: bool = False) -> torch.Tensor:
         cfg = self.cfg
         T = b.T
         small = T <= self.small_rows

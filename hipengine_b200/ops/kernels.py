@@ -26,10 +26,19 @@ class _GemvSeg(C.Structure):
                 ("qtype", C.c_int), ("qtype2", C.c_int), ("epi", C.c_int)]
 
 
+class GemvComm(C.Structure):
+    """Peer-memory description of a tensor-parallel group for the decode kernels (``csrc/peer_comm.cuh``)."""
+    _fields_ = [("recv", c_vp * 8), ("flags", c_vp * 8), ("state", c_vp), ("world", C.c_int), ("rank", C.c_int),
+                ("slot_floats", C.c_int), ("width", C.c_int), ("mode", C.c_int), ("wait_limit", C.c_uint)]
+
+
+COMM_PUSH, COMM_REDUCE = 1, 2
+
+
 class _GemvArgs(C.Structure):
     _fields_ = [("seg", _GemvSeg * 4), ("n_seg", C.c_int), ("K", C.c_int), ("R", C.c_int), ("x_dtype", C.c_int),
                 ("x", c_vp), ("x_stride", c_ll), ("norm_w", c_vp), ("eps", C.c_float), ("n_slots", C.c_int),
-                ("rg", C.c_int), ("slot_bytes", C.c_int), ("status", c_vp)]
+                ("rg", C.c_int), ("slot_bytes", C.c_int), ("status", c_vp), ("comm", GemvComm)]
 
 
 class _QkvArgs(C.Structure):
@@ -104,7 +113,8 @@ def _check_abi() -> None:
     pairs = [("he_gemv_args_size", _GemvArgs), ("he_qkv_args_size", _QkvArgs), ("he_conv_args_size", _ConvArgs),
              ("he_gdn_prep_args_size", _GdnPrepArgs), ("he_gdn_scan_args_size", _GdnScanArgs),
              ("he_attn_dec_args_size", _AttnDecArgs), ("he_moe_sel_args_size", _MoeSelArgs),
-             ("he_gdn_decode_args_size", _GdnDecodeArgs), ("he_gdn_chunk_args_size", _GdnChunkArgs)]
+             ("he_gdn_decode_args_size", _GdnDecodeArgs), ("he_gdn_chunk_args_size", _GdnChunkArgs),
+             ("he_gemv_comm_size", GemvComm)]
     for fn, st in pairs:
         got = getattr(L, fn)()
         if got != C.sizeof(st):
@@ -202,8 +212,12 @@ class GemvSegment:
 
 
 def gemv(x: torch.Tensor, segs: Sequence[GemvSegment], norm_w: Optional[torch.Tensor] = None,
-         eps: float = 1e-6) -> None:
-    """Fused [RMSNorm] + int8 activation quantize + quantized GEMV + epilogue for 1..8 rows."""
+         eps: float = 1e-6, comm: Optional[GemvComm] = None) -> None:
+    """Fused [RMSNorm] + int8 activation quantize + quantized GEMV + epilogue for 1..8 rows.
+
+    ``comm`` (tensor-parallel decode) with mode ``COMM_PUSH`` makes the epilogue store the outputs of the single
+    fp32 segment into every rank's receive region instead of ``out``; with ``COMM_REDUCE`` the prologue first adds
+    the partial rows every rank pushed to the fp32 rows ``x`` (and writes the sums back)."""
     _check_abi()
     _check_device(x)
     R, K = x.shape
@@ -228,8 +242,10 @@ def gemv(x: torch.Tensor, segs: Sequence[GemvSegment], norm_w: Optional[torch.Te
     a.norm_w = _p(norm_w)
     a.eps = eps
     a.status = _status_ptr(x.device)
+    if comm is not None:
+        a.comm = comm
     rc = N.lib().he_gemv(C.byref(a), C.c_int(N.num_sms()), _stream())
-    if rc == -3 and R > 1:
+    if rc == -3 and R > 1 and comm is None:
         # activation rows + staging rings do not fit shared memory: run the rows in two halves
         h = R // 2
         gemv(x[:h], [GemvSegment(s.w, s.out[:h], s.epi, s.w2) for s in segs], norm_w, eps)

@@ -272,3 +272,120 @@ class FusedGemmAllReduce:
         for p in getattr(self, "_owned_regions", []):
             L.he_comm_free(C.c_void_p(p))
         self._owned_regions = []
+
+
+class PeerResidual:
+    """Receive regions and device state for the all-reduce that tensor-parallel decode folds into its GEMVs.
+
+    A row-parallel projection *pushes* (its GEMV epilogue stores the partial rows into every rank's region and the last
+    CTA stamps a sequence number), the next reader of the residual *reduces* (a GEMV prologue, or ``reduce_in`` for
+    other readers, waits for all stamps and adds the rows in rank order).  Region per rank:
+    ``[2 parities][world][max_rows * width]`` 8-byte words ``{fp32 value, sequence tag}`` then ``[2][world]`` u32
+    stamps.  A ``width == 1`` region carries one (value, token id) pair per row for the vocab-parallel greedy head
+    (``argmax_merge``).  Everything is driven by device-side
+    counters, so captured CUDA graphs replay without host patching.  Single node (CUDA IPC)."""
+
+    def __init__(self, ctx: DistContext, width: int, max_rows: int = 8, wait_limit: int = 1 << 22,
+                 _regions: Optional[List[int]] = None):
+        L = N.lib()
+        assert ctx.world <= _MAX_WORLD
+        self.ctx, self.width, self.max_rows, self.wait_limit = ctx, width, max_rows, wait_limit
+        self.slot_floats = max_rows * width
+        self.data_bytes = 2 * ctx.world * self.slot_floats * 8      # one 8-byte {value, tag} word per element
+        self.total_bytes = (self.data_bytes + 2 * ctx.world * 4 + 255) // 256 * 256
+        self._opened: List[int] = []
+        self._local = 0
+        if _regions is not None:
+            self._peer_ptrs = list(_regions)
+        else:
+            base = C.c_void_p()
+            N.check(L.he_comm_alloc(C.c_longlong(self.total_bytes), C.byref(base)), "he_comm_alloc")
+            self._local = base.value
+            self._peer_ptrs = [self._local] * ctx.world
+            if ctx.world > 1:
+                hsz = L.he_comm_ipc_handle_size()
+                handle = (C.c_char * hsz)()
+                N.check(L.he_comm_ipc_get(C.c_void_p(self._local), handle), "he_comm_ipc_get")
+                handles: List[bytes] = [b""] * ctx.world
+                dist.all_gather_object(handles, bytes(handle.raw), group=ctx.group)
+                for r in range(ctx.world):
+                    if r == ctx.rank:
+                        continue
+                    p = C.c_void_p()
+                    buf = (C.c_char * hsz).from_buffer_copy(handles[r])
+                    N.check(L.he_comm_ipc_open(buf, C.byref(p)), "he_comm_ipc_open")
+                    self._peer_ptrs[r] = p.value
+                    self._opened.append(p.value)
+        self.state = torch.zeros(16, dtype=torch.int32, device=ctx.device)
+        if _regions is None and ctx.world > 1:
+            ctx.barrier()
+        self.pending_rows = 0        # rows pushed and not yet reduced into the residual
+
+    @classmethod
+    def emulated_group(cls, device, width: int, world: int, max_rows: int = 8,
+                       wait_limit: int = 2000) -> List["PeerResidual"]:
+        """``world`` instances in one process on one GPU wired to each other's regions.  All ranks' pushes must be
+        launched before any rank's reduce (no launch may wait for a later launch)."""
+        L = N.lib()
+        regions: List[int] = []
+        out: List[PeerResidual] = []
+        for r in range(world):
+            ctx = DistContext(r, world, 0, torch.device(device), None, "loopback")
+            inst = cls(ctx, width, max_rows, wait_limit, _regions=[0] * world)
+            base = C.c_void_p()
+            N.check(L.he_comm_alloc(C.c_longlong(inst.total_bytes), C.byref(base)), "he_comm_alloc")
+            regions.append(base.value)
+            out.append(inst)
+        for inst in out:
+            inst._peer_ptrs = list(regions)
+        out[0]._owned_regions = regions
+        return out
+
+    def comm(self, mode: int = 0) -> K.GemvComm:
+        c = K.GemvComm()
+        for r, p in enumerate(self._peer_ptrs):
+            c.recv[r] = p
+            c.flags[r] = p + self.data_bytes
+        c.state = self.state.data_ptr()
+        c.world, c.rank = self.ctx.world, self.ctx.rank
+        c.slot_floats, c.width, c.mode, c.wait_limit = self.slot_floats, self.width, mode, self.wait_limit
+        return c
+
+    def reduce_in(self, resid: torch.Tensor, rows: int) -> None:
+        """resid[:rows] += sum over ranks of the rows of the last push (stand-alone consumer)."""
+        st = K.status_tensor(self.ctx.device)
+        c = self.comm()
+        N.check(N.lib().he_comm_reduce_in(C.byref(c), C.c_void_p(resid.data_ptr()), C.c_longlong(resid.stride(0)),
+                                          C.c_int(rows), C.c_void_p(st.data_ptr()), K._stream()), "he_comm_reduce_in")
+
+    def push_rows(self, partial: torch.Tensor, rows: int) -> None:
+        """Push ``rows`` contiguous fp32 rows of this rank to every rank (stand-alone producer)."""
+        assert partial.dtype == torch.float32 and partial.is_contiguous() and partial.shape[1] == self.width
+        c = self.comm()
+        N.check(N.lib().he_comm_push_rows(C.byref(c), C.c_void_p(partial.data_ptr()), C.c_int(rows), K._stream()),
+                "he_comm_push_rows")
+
+    def argmax_merge(self, loc_val: torch.Tensor, loc_idx: torch.Tensor, vocab_off: int, rows: int,
+                     out_ids: torch.Tensor) -> None:
+        """Greedy vocab-parallel head: merge every rank's per-row (max, local id) into global token ids."""
+        assert self.width == 1 and loc_val.dtype == torch.float32 and loc_idx.dtype == torch.int64
+        st = K.status_tensor(self.ctx.device)
+        c = self.comm()
+        N.check(N.lib().he_comm_argmax_merge(C.byref(c), C.c_void_p(loc_val.data_ptr()), C.c_void_p(loc_idx.data_ptr()),
+                                             C.c_int(vocab_off), C.c_int(rows), C.c_void_p(out_ids.data_ptr()),
+                                             C.c_void_p(st.data_ptr()), K._stream()), "he_comm_argmax_merge")
+
+    def close(self) -> None:
+        L = N.lib()
+        torch.cuda.synchronize()
+        if self.ctx.backend not in ("loopback", "none") and self.ctx.world > 1:
+            self.ctx.barrier()
+        for p in self._opened:
+            L.he_comm_ipc_close(C.c_void_p(p))
+        self._opened = []
+        if self._local:
+            L.he_comm_free(C.c_void_p(self._local))
+            self._local = 0
+        for p in getattr(self, "_owned_regions", []):
+            L.he_comm_free(C.c_void_p(p))
+        self._owned_regions = []

@@ -45,9 +45,19 @@ class TPHybridExecutor(HybridExecutor):
             self.owns_shared_expert = self.plan.owns_shared_expert
         self.fused = None
         self.fgemm = None
+        self.peer = None
+        self.peer_head = None
+        self._pending = None
         if self.comm == "fused" and ctx.world > 1:
-            from .fused import FusedReducer
+            from .fused import FusedReducer, PeerResidual
             self.fused = FusedReducer(ctx, self.full_cfg.hidden, max_rows=GEMV_MAX_ROWS)
+            # decode: the all-reduce of a row-parallel projection is folded into the GEMVs around it (push from the
+            # epilogue, sum in the next prologue), and the greedy head merges (max, id) pairs over peer memory
+            if os.environ.get("HE_TP_FOLD", "1") != "0" and self.full_cfg.hidden % 8 == 0 \
+                    and self.full_cfg.hidden <= 8192:
+                self.peer = PeerResidual(ctx, self.full_cfg.hidden, max_rows=GEMV_MAX_ROWS)
+                self.peer_head = PeerResidual(ctx, 1, max_rows=64)
+                self._pending = None          # (residual tensor, rows) of a push not yet summed into the residual
             if self.gemm_impl == "tcgen05" and self.full_cfg.hidden % 8 == 0 and \
                     os.environ.get("HE_TP_FUSED_GEMM", "1") != "0":
                 from .fused import FusedGemmAllReduce
@@ -55,10 +65,35 @@ class TPHybridExecutor(HybridExecutor):
                 self.fgemm = FusedGemmAllReduce(ctx, self.full_cfg.hidden, max_rows=rows)
 
     # ------------------------------------------------------------------ reductions
+    def _sync_resid(self, h: torch.Tensor) -> None:
+        """Finish a pending push with the stand-alone reduce kernel (readers that are not a reduce-prologue GEMV)."""
+        if self._pending is not None:
+            ph, rows = self._pending
+            self._pending = None
+            self.peer.reduce_in(ph, rows)
+
+    def _gemv_resid(self, h: torch.Tensor, segs, norm_w: torch.Tensor, eps: float) -> None:
+        if self._pending is not None:
+            ph, rows = self._pending
+            fold = (ph.data_ptr() == h.data_ptr() and rows == h.shape[0] and h.dtype == torch.float32
+                    and norm_w is not None and h.shape[1] == self.peer.width
+                    and all(s.w.qtype in (8, 12, 14) and (s.w2 is None or s.w2.qtype in (8, 12, 14)) for s in segs))
+            if fold:
+                self._pending = None
+                K.gemv(h, segs, norm_w=norm_w, eps=eps, comm=self.peer.comm(K.COMM_REDUCE))
+                return
+            self._sync_resid(h)
+        K.gemv(h, segs, norm_w=norm_w, eps=eps)
+
     def _out_small(self, x: torch.Tensor, w: DeviceWeight, h: torch.Tensor) -> None:
         if self.ctx.world == 1:
             return super()._out_small(x, w, h)
         T = x.shape[0]
+        if self.peer is not None and w.n_rows == self.peer.width and w.qtype in (8, 12, 14):
+            self._sync_resid(h)                 # at most one push in flight per residual
+            K.gemv(x, [GemvSegment(w, h, K.EPI_F32)], comm=self.peer.comm(K.COMM_PUSH))
+            self._pending = (h, T)
+            return
         if self.fused is not None:
             part = self.fused.local_rows(T)
             K.gemv(x, [GemvSegment(w, part, K.EPI_F32)])
@@ -72,6 +107,11 @@ class TPHybridExecutor(HybridExecutor):
     def _moe_reduce(self, h: torch.Tensor, part: torch.Tensor) -> None:
         """h += sum over ranks of the per-rank expert contributions ``part`` [T, hidden] fp32."""
         T = part.shape[0]
+        if self.peer is not None and T <= self.peer.max_rows and part.is_contiguous():
+            self._sync_resid(h)
+            self.peer.push_rows(part, T)
+            self._pending = (h, T)
+            return
         if self.fused is not None and T <= self.fused.max_rows:
             self.fused.local_rows(T).copy_(part)
             self.fused.reduce_add(h, T)
@@ -103,15 +143,16 @@ class TPHybridExecutor(HybridExecutor):
         assert full.vocab % self.ctx.world == 0, "vocab-parallel head needs an even split"
         loc = self.scratch.get("logits_local", (R, Vl), torch.float32)
         head = self.dw["output.weight"]
-        if hidden_out is not None:
-            K.rmsnorm_rows(h_rows, self.f32["output_norm.weight"], hidden_out, cfg.rms_eps)
         if R <= GEMV_MAX_ROWS:
-            K.gemv(h_rows, [GemvSegment(head, loc)], norm_w=self.f32["output_norm.weight"], eps=cfg.rms_eps)
+            self._gemv_resid(h_rows, [GemvSegment(head, loc)], self.f32["output_norm.weight"], cfg.rms_eps)
         else:
+            self._sync_resid(h_rows)
             xn = self.scratch.get("xn_head", (R, cfg.hidden), torch.bfloat16)
             K.rmsnorm_rows(h_rows, self.f32["output_norm.weight"], xn, cfg.rms_eps)
             lb = self._gemm(xn, head, self.scratch.get("logits_bf", (R, Vl), torch.bfloat16), tag="head")
             loc.copy_(lb)
+        if hidden_out is not None:
+            K.rmsnorm_rows(h_rows, self.f32["output_norm.weight"], hidden_out, cfg.rms_eps)
         self._local_logits = loc
         gathered = self.ctx.all_gather(loc)                       # [world, R, Vl]
         if out is None:
@@ -120,6 +161,34 @@ class TPHybridExecutor(HybridExecutor):
         if cfg.final_softcap > 0:
             K.softcap_(out, cfg.final_softcap)
         return out
+
+
+    def head_greedy(self, h_rows: torch.Tensor, out_ids: torch.Tensor, logits_out: Optional[torch.Tensor] = None,
+                    hidden_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Vocab-parallel greedy head without a logits gather: argmax over this rank's vocabulary shard, then the
+        ranks' (max, id) pairs are exchanged over peer memory and merged (lower id wins exact ties, as one argmax
+        over the concatenated logits would)."""
+        R = h_rows.shape[0]
+        if self.ctx.world == 1 or self.peer_head is None or R > GEMV_MAX_ROWS or self.cfg.final_softcap > 0:
+            return super().head_greedy(h_rows, out_ids, logits_out, hidden_out)
+        cfg = self.cfg
+        v0, v1 = self.plan.vocab_rows
+        loc = self.scratch.get("logits_local", (R, v1 - v0), torch.float32)
+        self._gemv_resid(h_rows, [GemvSegment(self.dw["output.weight"], loc)], self.f32["output_norm.weight"],
+                         cfg.rms_eps)
+        if hidden_out is not None:
+            K.rmsnorm_rows(h_rows, self.f32["output_norm.weight"], hidden_out, cfg.rms_eps)
+        lv = self.scratch.get("head_val", (R,), torch.float32)
+        li = self.scratch.get("head_idx", (R,), torch.int64)
+        K.argmax_rows(loc, self.am_v, self.am_i, li, out_val=lv)
+        self.peer_head.argmax_merge(lv, li, v0, R, out_ids)
+        return out_ids
+
+    def close_comm(self) -> None:
+        for obj in (self.peer, self.peer_head):
+            if obj is not None:
+                obj.close()
+        self.peer = self.peer_head = None
 
 
 def build_tp_executor(cfg, seed: int, device, ctx: Optional[DistContext] = None, comm: Optional[str] = None,

@@ -127,3 +127,99 @@ def test_fused_gemm_allreduce_absent_peer_times_out():
         for r in ranks[1:]:
             r.close()
         ranks[0].close()
+
+
+def _q4k(n, k, seed):
+    from hipengine_b200.ops import kernels as K
+    from hipengine_b200.quant import ggml as Q
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    w = torch.randn(n, k, generator=g, device="cuda") * 0.05
+    raw = Q.quantize(w, Q.GGMLType.Q4_K)
+    return K.to_device_weight(raw, Q.GGMLType.Q4_K, n, k)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_folded_decode_allreduce_push_epilogue_and_reduce_prologue(world):
+    """Tensor-parallel decode without a stand-alone reduction: each emulated rank's row-parallel GEMV pushes its
+    partial rows from the epilogue, the next GEMV's prologue sums them into the residual.  All ranks' pushes are
+    launched before any reduce, so no launch waits for a later one.  Three rounds exercise both slot parities."""
+    from hipengine_b200.ops import kernels as K
+    from hipengine_b200.parallel.fused import PeerResidual
+    width, kq, n2, R = 1024, 512, 768, 3
+    group = PeerResidual.emulated_group("cuda", width, world)
+    w_out = [_q4k(width, kq, 10 + q) for q in range(world)]
+    w_next = _q4k(n2, width, 99)
+    nw = torch.rand(width, device="cuda") + 0.5
+    h_ref = torch.randn(R, width, device="cuda")
+    hs = [h_ref.clone() for _ in range(world)]
+    for rnd in range(3):
+        xs = [torch.randn(R, kq, device="cuda") for _ in range(world)]
+        parts = []
+        for q in range(world):
+            p = torch.zeros(R, width, device="cuda")
+            K.gemv(xs[q], [K.GemvSegment(w_out[q], p)])
+            parts.append(p)
+        for q in range(world):
+            K.gemv(xs[q], [K.GemvSegment(w_out[q], hs[q])], comm=group[q].comm(K.COMM_PUSH))
+        before = [h.clone() for h in hs]
+        for p in parts:                       # rank order, like the kernel
+            h_ref = h_ref + p
+        outs = []
+        for q in range(world):
+            o = torch.zeros(R, n2, device="cuda")
+            K.gemv(hs[q], [K.GemvSegment(w_next, o)], norm_w=nw, comm=group[q].comm(K.COMM_REDUCE))
+            outs.append(o)
+        torch.cuda.synchronize()
+        K.check_status()
+        want = torch.zeros(R, n2, device="cuda")
+        K.gemv(h_ref, [K.GemvSegment(w_next, want)], norm_w=nw)
+        for q in range(world):
+            assert not torch.equal(hs[q], before[q])
+            assert torch.equal(hs[q], h_ref), (rnd, q, (hs[q] - h_ref).abs().max())     # bit-identical replicas
+            assert torch.equal(outs[q], want), (rnd, q)
+    # stand-alone producer / consumer on the same regions
+    part = [torch.randn(2, width, device="cuda") for _ in range(world)]
+    for q in range(world):
+        group[q].push_rows(part[q], 2)
+    for q in range(world):
+        group[q].reduce_in(hs[q], 2)
+    torch.cuda.synchronize()
+    K.check_status()
+    want = h_ref.clone()
+    for p in part:
+        pass
+    acc = part[0].clone()
+    for p in part[1:]:
+        acc = acc + p
+    want[:2] += acc
+    for q in range(world):
+        assert torch.equal(hs[q], want)
+    for g in group:
+        g.close()
+
+
+def test_vocab_parallel_argmax_merge_and_bounded_wait():
+    from hipengine_b200.ops import kernels as K
+    from hipengine_b200.parallel.fused import PeerResidual
+    world, R, shard = 4, 5, 1000
+    vals = torch.randn(world, R, device="cuda")
+    vals[2, 1] = vals[0, 1] = vals[:, 1].max() + 1.0          # exact tie between ranks 0 and 2: lower id wins
+    idx = torch.randint(0, shard, (world, R), device="cuda", dtype=torch.int64)
+    # one CTA per rank pushes and then waits for the others: emulated ranks would wait for later launches, so the
+    # pairs of the other ranks are put in place by running every rank once (bounded waits run out, status is
+    # cleared), after which a second pass over the same sequence numbers' slots finds all stamps present
+    group = PeerResidual.emulated_group("cuda", 1, world, max_rows=64, wait_limit=200)
+    outs = [torch.zeros(R, dtype=torch.int64, device="cuda") for _ in range(world)]
+    for q in range(world):
+        group[q].argmax_merge(vals[q].contiguous(), idx[q].contiguous(), q * shard, R, outs[q])
+    torch.cuda.synchronize()
+    st = K.status_tensor("cuda")
+    assert int(st[0].item()) == 1                              # the first ranks gave up waiting, as designed
+    st.zero_()
+    # the last rank saw every stamp: its result is the true merge
+    gid = idx + torch.arange(world, device="cuda").view(-1, 1) * shard
+    best = vals.max(0).values
+    cand = torch.where(vals == best, gid, torch.full_like(gid, 1 << 40))
+    assert torch.equal(outs[world - 1], cand.min(0).values)
+    for g in group:
+        g.close()
