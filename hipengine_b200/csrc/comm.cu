@@ -311,3 +311,142 @@ HE_API int he_comm_argmax_merge(const HeGemvComm* comm, const void* loc_val, con
   HE_LAUNCH_CHECK();
   return 0;
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// Sequence-parallel prefill: the fp32 residual is sharded by M-tiles (tile tm of `mt` rows belongs to rank
+// tm % world).  After a reduce-scatter GEMM has completed a rank's rows, this kernel normalises them and writes the
+// bf16 result into EVERY rank's activation buffer (RMSNorm + all-gather as peer stores of whole rows), then stamps
+// its flag on every rank; the consumers (gemm_wq_sm100.cu, all-gather wait) read the rows from local memory once the
+// stamp of the rows' owner is there.  mode 1 copies the fp32 rows instead (gathering the residual itself at the end
+// of a forward pass).  The reference engine is single-device: no counterpart there.
+namespace {
+
+struct SpPushArgs {
+  void* dst[GEMV_MAX_WORLD];        // every rank's destination rows (bf16 [T][ld_dst] or fp32 for mode 1)
+  uint32_t* flags[GEMV_MAX_WORLD];  // every rank's stamp array [world]
+  uint32_t* state;                  // local: [0] epoch of the last completed push, [1] CTAs done
+  const float* h;
+  const float* norm_w;
+  long long ld_h, ld_dst;
+  float eps;
+  int T, H, mt, world, rank, mode;
+};
+
+constexpr int SP_MAXG = 4;   // 8-element groups per thread: rows of up to 256 * 4 * 8 = 8192 columns
+
+__global__ void __launch_bounds__(256) sp_norm_push_kernel(const SpPushArgs a) {
+  __shared__ float red[33];
+  const int W = a.world;
+  const int tiles_m = (a.T + a.mt - 1) / a.mt;
+  const int owned_tiles = tiles_m > a.rank ? (tiles_m - a.rank + W - 1) / W : 0;
+  const int n_groups = a.H / 8;
+  for (int j = blockIdx.x; j < owned_tiles * a.mt; j += gridDim.x) {
+    const int m = (a.rank + W * (j / a.mt)) * a.mt + j % a.mt;
+    if (m >= a.T) continue;                           // uniform across the CTA
+    const float* hr = a.h + (size_t)m * a.ld_h;
+    float v[SP_MAXG][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int u = 0; u < SP_MAXG; ++u) {
+      const int g = u * 256 + (int)threadIdx.x;
+      if (g < n_groups) {
+        const float4 x0 = *reinterpret_cast<const float4*>(hr + (size_t)g * 8);
+        const float4 x1 = *reinterpret_cast<const float4*>(hr + (size_t)g * 8 + 4);
+        v[u][0] = x0.x; v[u][1] = x0.y; v[u][2] = x0.z; v[u][3] = x0.w;
+        v[u][4] = x1.x; v[u][5] = x1.y; v[u][6] = x1.z; v[u][7] = x1.w;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss += v[u][e] * v[u][e];
+      }
+    }
+    float inv = 1.f;
+    if (a.mode == 0) {
+      ss = block_sum(ss, red);
+      inv = rsqrtf(ss / (float)a.H + a.eps);
+    }
+#pragma unroll
+    for (int u = 0; u < SP_MAXG; ++u) {
+      const int g = u * 256 + (int)threadIdx.x;
+      if (g < n_groups) {
+        if (a.mode == 0) {
+          const float4 w0 = __ldg(reinterpret_cast<const float4*>(a.norm_w + (size_t)g * 8));
+          const float4 w1 = __ldg(reinterpret_cast<const float4*>(a.norm_w + (size_t)g * 8 + 4));
+          const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+          uint4 pk;
+          uint32_t* pw = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[u][2 * e] * inv * wv[2 * e], v[u][2 * e + 1] * inv * wv[2 * e + 1]);
+            pw[e] = *reinterpret_cast<uint32_t*>(&h2);
+          }
+          for (int q = 0; q < W; ++q)
+            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.dst[q]) + (size_t)m * a.ld_dst + (size_t)g * 8) = pk;
+        } else {
+          for (int q = 0; q < W; ++q) {
+            if (q == a.rank) continue;                 // the local rows are the source
+            float* d = reinterpret_cast<float*>(a.dst[q]) + (size_t)m * a.ld_dst + (size_t)g * 8;
+            *reinterpret_cast<float4*>(d) = make_float4(v[u][0], v[u][1], v[u][2], v[u][3]);
+            *reinterpret_cast<float4*>(d + 4) = make_float4(v[u][4], v[u][5], v[u][6], v[u][7]);
+          }
+        }
+      }
+    }
+  }
+  // every row of this CTA is stored; the last CTA of the grid publishes the push on every rank
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const unsigned prev = atomicAdd(a.state + 1, 1u);
+    if (prev == gridDim.x - 1) {
+      a.state[1] = 0;
+      const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(a.state) + 1u;
+      __threadfence_system();
+      for (int q = 0; q < W; ++q) st_release_sys_u32(a.flags[q] + a.rank, epoch);
+      *reinterpret_cast<volatile uint32_t*>(a.state) = epoch;
+    }
+  }
+}
+
+// Stream-ordered wait for the stamps of all ranks (for consumers that are not the all-gather GEMM).
+__global__ void sp_wait_kernel(const uint32_t* flags, const uint32_t* state, int world, unsigned limit, int* status) {
+  const uint32_t want = *reinterpret_cast<const volatile uint32_t*>(state);
+  if ((int)threadIdx.x < world) {
+    unsigned polls = 0;
+    while ((int)(ld_acquire_sys_u32(flags + threadIdx.x) - want) < 0) {
+      if (++polls > limit) {
+        if (status != nullptr) atomicCAS(status, 0, HE_ERR_WAIT_TIMEOUT);
+        break;
+      }
+      __nanosleep(100);
+    }
+  }
+}
+
+}  // namespace
+
+HE_API int he_sp_push_args_size() { return (int)sizeof(SpPushArgs); }
+
+HE_API int he_sp_norm_push(const SpPushArgs* args, int num_sms, cudaStream_t stream) {
+  const SpPushArgs& a = *args;
+  if (a.T <= 0) return 0;
+  if (a.world < 1 || a.world > GEMV_MAX_WORLD || a.rank < 0 || a.rank >= a.world || a.mt <= 0) return -HE_ERR_BAD_ARG;
+  if (a.H % 8 != 0 || a.H > 256 * SP_MAXG * 8 || a.state == nullptr || a.h == nullptr) return -HE_ERR_BAD_ARG;
+  if (a.mode == 0 && a.norm_w == nullptr) return -HE_ERR_BAD_ARG;
+  for (int q = 0; q < a.world; ++q)
+    if (a.dst[q] == nullptr || a.flags[q] == nullptr) return -HE_ERR_BAD_ARG;
+  const int tiles_m = (a.T + a.mt - 1) / a.mt;
+  const int owned = tiles_m > a.rank ? (tiles_m - a.rank + a.world - 1) / a.world : 0;
+  int grid = owned * a.mt;
+  if (grid > 4 * num_sms) grid = 4 * num_sms;
+  if (grid < 1) grid = 1;
+  sp_norm_push_kernel<<<grid, 256, 0, stream>>>(a);
+  HE_LAUNCH_CHECK();
+  return 0;
+}
+
+HE_API int he_sp_wait(const void* flags, const void* state, int world, unsigned limit, void* status,
+                      cudaStream_t stream) {
+  if (world < 1 || world > GEMV_MAX_WORLD) return -HE_ERR_BAD_ARG;
+  sp_wait_kernel<<<1, 32, 0, stream>>>((const uint32_t*)flags, (const uint32_t*)state, world, limit, (int*)status);
+  HE_LAUNCH_CHECK();
+  return 0;
+}

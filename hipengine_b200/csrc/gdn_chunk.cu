@@ -449,7 +449,13 @@ HE_API int he_gdn_scan_chunked(const GdnChunkArgs* args, cudaStream_t stream) {
   static const int nv_env = []() { const char* e = getenv("HE_GDN_NV"); return e ? atoi(e) : 0; }();
   // 16-column slices double the CTAs but repeat the per-chunk K K^T / inverse work; measured equal to 32 columns on a
   // single 4096-token sequence, so the wider slice is the default (HE_GDN_NV=16 selects the narrow one)
-  const bool narrow = nv_env == 16;
+  // ... unless the grid would leave most SMs idle (few heads: a tensor-parallel shard), where more CTAs win
+  int sms = 148;
+  {
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const bool narrow = nv_env == 16 || (nv_env == 0 && (long long)args->n_seg * args->Hv * 4 <= sms);
   return narrow ? launch_chunk<16>(*args, stream) : launch_chunk<32>(*args, stream);
 }
 HE_API int he_gdn_chunk_args_size() { return (int)sizeof(GdnChunkArgs); }

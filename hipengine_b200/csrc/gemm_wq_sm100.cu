@@ -58,7 +58,55 @@ struct WqArgs {
   int x_stage_bytes;        // mt * 128 rounded up to 1 KB
   int q_stage_bytes;        // 128 rows x bytes per super-block row, rounded up to 1 KB
   int q_stages;
+  // all-gather -> GEMM (sequence-parallel activations): the rows of M-tile tm were written into the local activation
+  // buffer by rank tm % ag_world (peer stores of its norm kernel, then a stamp in ag_flags[that rank]); the activation
+  // producer waits -- bounded -- for the stamp of a tile's owner before the first load of the tile, so the GEMM
+  // starts on the rows that are already here while the others are still crossing the links.  ag_world 0: off.
+  const uint32_t* ag_flags;   // local [ag_world]
+  const uint32_t* ag_epoch;   // local: the stamp value this call waits for
+  int ag_world;
+  unsigned ag_wait_limit;
 };
+
+// GEMM -> reduce-scatter -> residual add (sequence-parallel residual): M-tile tm belongs to rank tm % world.
+// Every rank owns one symmetric region, mapped into all peers:
+//     stage  [world src][slots][128 x MT_MAX] bf16 : partial tiles pushed by rank `src` for the tiles this rank owns
+//                                                    (slot = (tm / world) * tiles_n + tn)
+//     flags  [slots][world][4] u32                 : epoch stamps per (tile, source rank, 32-row quarter)
+// Phase 1 (epilogue warps): the partial quarter goes straight into the owner's stage slot as bf16 (peer stores for
+// remote owners, fragment-major so a warp's store instruction covers 512 contiguous bytes), then a system fence and
+// the stamp.  Phase 2 (two collective warps per CTA, beside the pipeline for the whole kernel): for each owned
+// (tile, quarter) wait -- bounded -- for the world stamps, sum the slots in rank order in fp32 and add into the local
+// fp32 residual rows: bf16 on the wire, fp32 accumulation, no rounding of the sum.  The epoch lives in device memory
+// and is advanced by the last CTA to leave, so the kernel replays from CUDA graphs.  `phases` (bit 0 / 1) selects
+// the phases a launch runs: 3 in production; a single-GPU test runs the phases of several emulated ranks as
+// separate launches (all phase 1, then all phase 2) so that no launch waits for a later one.
+constexpr int RS_MAX_WORLD = 8;
+constexpr int RS_TILE_ELEMS = WN * MT_MAX;
+struct WqFuse {
+  __nv_bfloat16* stage[RS_MAX_WORLD];
+  uint32_t* flags[RS_MAX_WORLD];
+  uint32_t* sync;           // local [2]: epoch of the last finished call, CTAs that have left the current call
+  float* resid;             // local fp32 [M][ld_resid]; only rows of owned tiles are touched
+  long long ld_resid;
+  int world, rank, slots, phases;
+  unsigned wait_limit;
+  int reserved;
+};
+
+__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_cg_u4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
 
 struct __align__(8) WqBarriers {
   uint64_t x_full[XSTAGES];
@@ -79,7 +127,6 @@ __device__ __forceinline__ uint32_t prmt_b32(uint32_t a, uint32_t b, uint32_t se
   asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
   return r;
 }
-__device__ __forceinline__ __nv_bfloat162 bf162_bits(uint32_t v) { return *reinterpret_cast<__nv_bfloat162*>(&v); }
 __device__ __forceinline__ uint32_t bits_bf162(__nv_bfloat162 v) { return *reinterpret_cast<uint32_t*>(&v); }
 
 // Four small unsigned integers (< 128), one per byte of `b4`, become two bf16x2 registers holding
@@ -205,9 +252,62 @@ __device__ __forceinline__ TileCoord tile_coord(const WqArgs& g, int tile, int t
   return t;
 }
 
-__global__ void __launch_bounds__(NTHREADS_WQ, 1)
-gemm_wq_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmQ0,
-               const __grid_constant__ CUtensorMap tmQ1, const WqArgs g) {
+constexpr int WARP_COLL = WARP_UNPACK0 + N_UNPACK_WARPS;   // second collective warp of the reduce-scatter form
+constexpr int NTHREADS_WQ_RS = NTHREADS_WQ + 32;
+
+// Phase 2 of the reduce-scatter form for one warp: quarter q of owned tile (tm, tn).  Lane = weight row (output
+// column n); each 16-byte group holds 8 consecutive activation rows m of that column.
+__device__ __forceinline__ void rs_reduce_quarter(const WqArgs& g, const WqFuse& f, int tm, int tn, int tiles_n,
+                                                  int q) {
+  const int lane = threadIdx.x & 31, W = f.world;
+  const int slot = (tm / W) * tiles_n + tn;
+  const __nv_bfloat16* src0 = f.stage[f.rank] + (size_t)slot * RS_TILE_ELEMS + (size_t)q * 32 * MT_MAX;
+  const size_t src_stride = (size_t)f.slots * RS_TILE_ELEMS;
+  const int n = tn * WN + q * 32 + lane;
+  const int m0 = tm * g.mt;
+  const int m_lim = min(g.mt, g.M - m0);
+  if (n >= g.N) return;
+  float* hcol = f.resid + (size_t)m0 * f.ld_resid + n;
+#pragma unroll 1
+  for (int gi0 = 0; gi0 * 8 < m_lim; gi0 += 4) {
+    float acc[4][8];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[u][e] = 0.f;
+    for (int r = 0; r < W; ++r) {           // rank order: every owner sums the same way
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        v[u] = (gi0 + u) * 8 < m_lim ? ld_cg_u4(src0 + (size_t)r * src_stride + ((size_t)(gi0 + u) * 32 + lane) * 8)
+                                     : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const __nv_bfloat162* hv = reinterpret_cast<const __nv_bfloat162*>(&v[u]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 t2 = __bfloat1622float2(hv[e]);
+          acc[u][2 * e] += t2.x;
+          acc[u][2 * e + 1] += t2.y;
+        }
+      }
+    }
+    // fire-and-forget adds (performed at the L2, no value comes back): the warp never waits for the old residual,
+    // and an instruction of the warp covers 32 consecutive columns of one row
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const int m = (gi0 + u) * 8 + e;
+        if (m < m_lim)
+          asm volatile("red.global.add.f32 [%0], %1;" ::"l"(hcol + (size_t)m * f.ld_resid), "f"(acc[u][e]) : "memory");
+      }
+  }
+}
+
+template <bool RS>
+__device__ __forceinline__ void gemm_wq_body(const CUtensorMap& tmX, const CUtensorMap& tmQ0, const CUtensorMap& tmQ1,
+                                             const WqArgs& g, const WqFuse* f) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* qring = smem + XSTAGES * g.x_stage_bytes;
@@ -218,7 +318,7 @@ gemm_wq_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int mt = g.mt;
   const int tiles_m = (g.M + mt - 1) / mt, tiles_n = (g.N + WN - 1) / WN;
-  const int n_tiles = tiles_m * tiles_n * g.k_splits;
+  const int n_tiles = (RS && !(f->phases & 1)) ? 0 : tiles_m * tiles_n * g.k_splits;
   const int sb_all = g.K >> 8;
 
   if (threadIdx.x == 0) {
@@ -249,15 +349,34 @@ gemm_wq_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = bar->tmem_base;
+  uint32_t rs_epoch = 0;
+  if constexpr (RS) rs_epoch = *reinterpret_cast<volatile uint32_t*>(f->sync) + 1;
 
   if (warp == 0) {
     // ------------------------------------------------------------ activation tiles
     if (elect_one()) {
       tma_prefetch_desc(&tmX);
       uint32_t it = 0;
+      uint32_t ag_seen = 0;                     // owners whose rows are known to have arrived
+      const uint32_t ag_want = g.ag_world > 0 ? *reinterpret_cast<const volatile uint32_t*>(g.ag_epoch) : 0u;
       for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
         const TileCoord t = tile_coord(g, tile, tiles_m, sb_all);
         if (t.skip) continue;
+        if (g.ag_world > 0) {
+          const int owner = t.tm % g.ag_world;
+          if (!(ag_seen & (1u << owner))) {
+            unsigned polls = 0;
+            while ((int)(ld_acquire_sys_u32(g.ag_flags + owner) - ag_want) < 0) {
+              if (++polls > g.ag_wait_limit) {
+                if (g.status != nullptr) atomicCAS(g.status, 0, HE_ERR_WAIT_TIMEOUT);
+                break;
+              }
+              __nanosleep(100);
+            }
+            asm volatile("fence.proxy.async;" ::: "memory");   // rows written by a peer, read next by TMA
+            ag_seen |= 1u << owner;
+          }
+        }
         for (int kb = 4 * t.sb0; kb < 4 * t.sb1; ++kb, ++it) {
           const int s = it % XSTAGES;
           if (!mbar_wait(&bar->x_empty[s], ((it / XSTAGES) & 1) ^ 1, abort_flag, g.status, 301)) break;
@@ -325,7 +444,7 @@ gemm_wq_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         ++tcount;
       }
     }
-  } else if (warp >= WARP_UNPACK0) {
+  } else if (warp >= WARP_UNPACK0 && warp < WARP_COLL) {
     // ------------------------------------------------------------ unpack: raw blocks -> bf16 operand in TMEM
     const int set = (warp - WARP_UNPACK0) >> 2;          // k-block of every super-block this warp expands
     const int row = (warp & 3) * 32 + lane;              // weight row in the tile == TMEM lane
@@ -357,7 +476,7 @@ gemm_wq_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         }
       }
     }
-  } else if (warp >= 4) {
+  } else if (warp >= 4 && warp < 8) {
     // ------------------------------------------------------------ epilogue (warps 4..7): transposed store
     const int q = warp & 3;
     uint32_t tcount = 0;
@@ -378,6 +497,26 @@ gemm_wq_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         tmem_ld_32x32(t_row + c * 32, r);
         tmem_ld_wait();
         const int jn = min(32, m_lim - c * 32);
+        if constexpr (RS) {
+          // partial quarter -> the owner's stage slot, bf16, fragment-major (16-byte group gi = 4c + v of lane l at
+          // (gi * 32 + l) * 8): a store instruction of the warp covers 512 contiguous bytes on the link
+          const int W = f->world, owner = t.tm % W;
+          const int slot = (t.tm / W) * tiles_n + t.tn;
+          __nv_bfloat16* dst = f->stage[owner] + ((size_t)f->rank * f->slots + slot) * RS_TILE_ELEMS +
+                               (size_t)q * 32 * MT_MAX + ((size_t)(c * 4) * 32 + lane) * 8;
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 pk;
+            uint32_t* pw = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * e]),
+                                                        __uint_as_float(r[v * 8 + 2 * e + 1]));
+              pw[e] = *reinterpret_cast<uint32_t*>(&h2);
+            }
+            if (v * 8 < jn) *reinterpret_cast<uint4*>(dst + (size_t)v * 256) = pk;
+          }
+        } else
         if (n_ok) {
           if (g.epi == 0) {
             __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(g.C) + (size_t)(m0 + c * 32) * g.ldc + n;
@@ -402,7 +541,48 @@ gemm_wq_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar->d_empty[acc]);
+      if constexpr (RS) {
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) {
+          const int W = f->world;
+          const int slot = (t.tm / W) * tiles_n + t.tn;
+          st_release_sys_u32(f->flags[t.tm % W] + ((size_t)slot * W + f->rank) * 4 + q, rs_epoch);
+        }
+      }
       ++tcount;
+    }
+  } else if (RS && (warp == 3 || warp == WARP_COLL)) {
+    // ------------------------------------------------------------ collective warps (reduce-scatter form only)
+    // Units = (owned tile, quarter); this CTA's two warps take units b*2 + {0,1}, + 2*grid, ... and reduce whichever
+    // has its world stamps; they give up after wait_limit polls without progress.
+    if constexpr (RS) {
+      if (f->phases & 2) {
+        const int W = f->world;
+        const int owned_m = tiles_m > f->rank ? (tiles_m - f->rank + W - 1) / W : 0;
+        const int n_units = owned_m * tiles_n * 4;
+        const uint32_t* my_flags = f->flags[f->rank];
+        unsigned stall = 0;
+        int u = (int)blockIdx.x * 2 + (warp == 3 ? 0 : 1);
+        while (u < n_units) {
+          const int q = u & 3, ot = u >> 2;
+          const int tm = f->rank + W * (ot % owned_m), tn = ot / owned_m;
+          const int slot = (tm / W) * tiles_n + tn;
+          bool ready = true;
+          if (lane < W) ready = (int)(ld_acquire_sys_u32(my_flags + ((size_t)slot * W + lane) * 4 + q) - rs_epoch) >= 0;
+          if (__all_sync(0xffffffffu, ready)) {
+            rs_reduce_quarter(g, *f, tm, tn, tiles_n, q);
+            u += 2 * (int)gridDim.x;
+            stall = 0;
+          } else {
+            if (++stall > f->wait_limit || *abort_flag) {
+              if (lane == 0 && g.status != nullptr) atomicCAS(g.status, 0, HE_ERR_WAIT_TIMEOUT);
+              break;
+            }
+            __nanosleep(200);
+          }
+        }
+      }
     }
   }
 
@@ -413,6 +593,30 @@ gemm_wq_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+  if constexpr (RS) {
+    // the last CTA to leave a launch that ran the final phase publishes the new epoch for the next launch
+    if (threadIdx.x == 0 && (f->phases & 2)) {
+      __threadfence();
+      const unsigned prev = atomicAdd(f->sync + 1, 1u);
+      if (prev == gridDim.x - 1) {
+        f->sync[1] = 0;
+        f->sync[0] = rs_epoch;
+        __threadfence();
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(NTHREADS_WQ, 1)
+gemm_wq_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmQ0,
+               const __grid_constant__ CUtensorMap tmQ1, const WqArgs g) {
+  gemm_wq_body<false>(tmX, tmQ0, tmQ1, g, nullptr);
+}
+
+__global__ void __launch_bounds__(NTHREADS_WQ_RS, 1)
+gemm_wq_rs_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmQ0,
+                  const __grid_constant__ CUtensorMap tmQ1, const WqArgs g, const __grid_constant__ WqFuse f) {
+  gemm_wq_body<true>(tmX, tmQ0, tmQ1, g, &f);
 }
 
 // out[m][n] (+)= sum over splits, in split order (deterministic).  mode 0: fp32 store, 1: fp32 add in place.
@@ -510,7 +714,7 @@ int pick_mt(int M, bool grouped) {
 }
 
 int launch_wq(const void* A, long long lda, int a_cols, const void* B, int qtype, long long b_rows, WqArgs g,
-              int num_sms, cudaStream_t stream) {
+              int num_sms, cudaStream_t stream, const WqFuse* fuse = nullptr) {
   if (g.K % 256 != 0) return -HE_ERR_BAD_ARG;
   if (a_cols <= 0 || a_cols > g.K || a_cols % 8 != 0) return -HE_ERR_BAD_ARG;
   const int row_bytes = qtype == HE_Q4_K ? 144 : (qtype == HE_Q6_K ? 224 : 272);
@@ -524,11 +728,17 @@ int launch_wq(const void* A, long long lda, int a_cols, const void* B, int qtype
   if (rc != 0) return rc;
   rc = make_q_maps(&q0, &q1, B, qtype, b_rows, g.K);
   if (rc != 0) return rc;
-  cudaError_t e = cudaFuncSetAttribute(gemm_wq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_WQ);
-  if (e != cudaSuccess) return (int)e;
   const long long tiles = (long long)((g.M + g.mt - 1) / g.mt) * ((g.N + WN - 1) / WN) * g.k_splits;
   const int grid = (int)(tiles < num_sms ? tiles : num_sms);
-  gemm_wq_kernel<<<grid, NTHREADS_WQ, SMEM_WQ, stream>>>(tmX, q0, q1, g);
+  if (fuse != nullptr) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_wq_rs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_WQ);
+    if (e != cudaSuccess) return (int)e;
+    gemm_wq_rs_kernel<<<grid, NTHREADS_WQ_RS, SMEM_WQ, stream>>>(tmX, q0, q1, g, *fuse);
+  } else {
+    cudaError_t e = cudaFuncSetAttribute(gemm_wq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_WQ);
+    if (e != cudaSuccess) return (int)e;
+    gemm_wq_kernel<<<grid, NTHREADS_WQ, SMEM_WQ, stream>>>(tmX, q0, q1, g);
+  }
   HE_LAUNCH_CHECK();
   return 0;
 }
@@ -603,4 +813,54 @@ HE_API int he_gemm_q_splitk_det(const void* A, long long lda, const void* B, int
                                                                            g.k_splits, (float*)out, ldo, M, N, mode);
   HE_LAUNCH_CHECK();
   return 0;
+}
+
+// The plain quantised GEMM with the all-gather wait of sequence-parallel activations (see WqArgs::ag_flags): A's rows
+// of M-tile tm (tiles of he_gemm_q_mt(M) rows) were written by rank tm % ag_world, which then stamped ag_flags[rank]
+// with the value found in *ag_epoch.
+HE_API int he_gemm_q_mt(int M) { return pick_mt(M, false); }
+
+HE_API int he_gemm_q_ag(const void* A, long long lda, int a_cols, const void* B, int qtype, long long b_rows, void* C,
+                        long long ldc, int M, int N, int K, int epi, const void* ag_flags, const void* ag_epoch,
+                        int ag_world, unsigned ag_wait_limit, void* status, int num_sms, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (ag_world < 1 || ag_world > RS_MAX_WORLD || ag_flags == nullptr || ag_epoch == nullptr) return -HE_ERR_BAD_ARG;
+  WqArgs g = {};
+  g.C = C; g.ldc = ldc; g.M = M; g.N = N; g.K = K; g.epi = epi; g.qtype = qtype;
+  g.mt = pick_mt(M, false);
+  g.k_splits = 1;
+  g.sb_per = K >> 8;
+  g.status = (int*)status;
+  g.ag_flags = (const uint32_t*)ag_flags;
+  g.ag_epoch = (const uint32_t*)ag_epoch;
+  g.ag_world = ag_world;
+  g.ag_wait_limit = ag_wait_limit;
+  return launch_wq(A, lda, a_cols, B, qtype, b_rows, g, num_sms, stream);
+}
+
+// resid[owned rows][N] (fp32) += sum over ranks of A_rank[M][K] * W_rank[N][K]^T for the M-tiles this rank owns (tile
+// tm of he_gemm_q_mt(M) rows belongs to rank tm % world): the GEMM and the reduce-scatter over peer memory in one
+// kernel per rank (see WqFuse).  Every rank issues the same calls with the same M and N.
+HE_API int he_gemm_q_fuse_args_size() { return (int)sizeof(WqFuse); }
+HE_API int he_gemm_q_rs_tile_elems() { return RS_TILE_ELEMS; }
+
+HE_API int he_gemm_q_reduce_scatter(const void* A, long long lda, const void* B, int qtype, long long b_rows, int M,
+                                    int N, int K, const WqFuse* fuse, void* status, int num_sms,
+                                    cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  const WqFuse& f = *fuse;
+  const int mt = pick_mt(M, false);
+  const int tiles_m = (M + mt - 1) / mt, tiles_n = (N + WN - 1) / WN;
+  if (f.world < 1 || f.world > RS_MAX_WORLD || f.rank < 0 || f.rank >= f.world) return -HE_ERR_BAD_ARG;
+  if (((tiles_m + f.world - 1) / f.world) * tiles_n > f.slots) return -HE_ERR_BAD_ARG;
+  if (f.resid == nullptr || f.ld_resid < N || (f.phases & 3) == 0 || f.sync == nullptr) return -HE_ERR_BAD_ARG;
+  for (int r = 0; r < f.world; ++r)
+    if (f.stage[r] == nullptr || f.flags[r] == nullptr) return -HE_ERR_BAD_ARG;
+  WqArgs g = {};
+  g.C = nullptr; g.ldc = 0; g.M = M; g.N = N; g.K = K; g.epi = 5; g.qtype = qtype;
+  g.mt = mt;
+  g.k_splits = 1;
+  g.sb_per = K >> 8;
+  g.status = (int*)status;
+  return launch_wq(A, lda, K, B, qtype, b_rows, g, num_sms, stream, fuse);
 }

@@ -129,6 +129,11 @@ class HybridExecutor:
         self.small_rows = min(GEMV_MAX_ROWS, int(os.environ.get("HE_SMALL_ROWS", "6")))
         self.dw: Dict[str, DeviceWeight] = {}
         self.f32: Dict[str, torch.Tensor] = {}
+        # per-stage device timing of the tensor-core (many rows) path, off unless HE_STAGE_TIMING=1 (the role of the
+        # reference's stage timers, hipengine/runtime/qwen35_gguf_timing.py:1-80): CUDA events around each stage,
+        # read back once by stage_summary()
+        from ..utils.tracing import StageTimer
+        self.timer = StageTimer(enabled=os.environ.get("HE_STAGE_TIMING", "0") == "1")
         self._load(weights)
         self._alloc_state()
 
@@ -163,6 +168,16 @@ class HybridExecutor:
                 if ab.shape[1] % 256 == 0 and os.environ.get("HE_AB_Q8", "1") != "0":
                     raw = quantize(ab, GGMLType.Q8_0).reshape(ab.shape[0], -1).contiguous()
                     self.ab_q8[i] = K.to_device_weight(raw, GGMLType.Q8_0, ab.shape[0], ab.shape[1])
+
+    def _stage(self, name: str):
+        """Context manager timing one stage (a no-op when timing is off or the stream is being captured)."""
+        if self.timer.enabled and not torch.cuda.is_current_stream_capturing():
+            return self.timer.stage(name)
+        import contextlib
+        return contextlib.nullcontext()
+
+    def stage_summary(self) -> Dict[str, Dict[str, float]]:
+        return self.timer.summary()
 
     def W(self, i: int, slot: str) -> DeviceWeight:
         return self.dw[f"blk.{i}.{slot}"]
@@ -249,6 +264,19 @@ class HybridExecutor:
     def _sync_resid(self, h: torch.Tensor) -> None:
         return
 
+    # Tensor-core (many rows) path: the normalised bf16 rows the projections read, the residual buffer of a forward
+    # pass and its completion.  A sequence-parallel executor shards the residual by rows and overrides these.
+    def _norm_rows(self, h: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        xn = self.scratch.get("xn", (h.shape[0], self.cfg.hidden), torch.bfloat16)
+        K.rmsnorm_rows(h, w, xn, self.cfg.rms_eps)
+        return xn
+
+    def _resid_buffer(self, T: int) -> torch.Tensor:
+        return self.scratch.get("h", (T, self.cfg.hidden), torch.float32)
+
+    def _finish_resid(self, h: torch.Tensor) -> torch.Tensor:
+        return h
+
     # Row-parallel ("output") projections: h += x @ W^T.  A tensor-parallel executor overrides these two to
     # reduce the partial products across ranks before the residual add.
     def _out_small(self, x: torch.Tensor, w: DeviceWeight, h: torch.Tensor) -> None:
@@ -286,11 +314,12 @@ class HybridExecutor:
                              cfg.rms_eps)
         else:
             self._sync_resid(h)
-            xn = sc.get("xn", (T, cfg.hidden), torch.bfloat16)
-            K.rmsnorm_rows(h, self.F(i, "attn_norm.weight"), xn, cfg.rms_eps)
-            qf = self._proj(xn, self.W(i, "attn_q.weight"), "q", "q")
-            kf = self._proj(xn, self.W(i, "attn_k.weight"), "k", "k")
-            vf = self._proj(xn, self.W(i, "attn_v.weight"), "v", "k")
+            with self._stage("norm"):
+                xn = self._norm_rows(h, self.F(i, "attn_norm.weight"))
+            with self._stage("attn_qkv_gemm"):
+                qf = self._proj(xn, self.W(i, "attn_q.weight"), "q", "q")
+                kf = self._proj(xn, self.W(i, "attn_k.weight"), "k", "k")
+                vf = self._proj(xn, self.W(i, "attn_v.weight"), "v", "k")
         q_out = sc.get("q_out", (T, H, D), torch.bfloat16)
         gate = sc.get("gate_out", (T, H, D), torch.bfloat16) if cfg.gated_attention else None
         qn = self.f32.get(f"blk.{i}.attn_q_norm.weight") if cfg.qk_norm else None
@@ -298,11 +327,13 @@ class HybridExecutor:
         K.qkv_post(qf, kf, vf, qn, kn, q_out, gate, self.kv[i], self.block_table, b.slot, b.pos, H, Hkv, D, PAGE,
                    cfg.gated_attention, cfg.rope_dim, cfg.rope_theta, cfg.rms_eps)
         attn = sc.get("attn_out", (T, H * D), torch.bfloat16)
-        self._attend(i, q_out, gate, b, attn)
+        with self._stage("attn_core"):
+            self._attend(i, q_out, gate, b, attn)
         if small:
             self._out_small(attn, self.W(i, "attn_output.weight"), h)
         else:
-            self._out_big(attn, self.W(i, "attn_output.weight"), h, "o")
+            with self._stage("out_gemm"):
+                self._out_big(attn, self.W(i, "attn_output.weight"), h, "o")
 
     def _attend(self, i: int, q_out: torch.Tensor, gate: Optional[torch.Tensor], b: BatchDesc,
                 out: torch.Tensor) -> None:
@@ -360,10 +391,11 @@ class HybridExecutor:
                                  self.F(i, "attn_norm.weight"), cfg.rms_eps)
         else:
             self._sync_resid(h)
-            xn = sc.get("xn", (T, cfg.hidden), torch.bfloat16)
-            K.rmsnorm_rows(h, self.F(i, "attn_norm.weight"), xn, cfg.rms_eps)
-            qkv = self._proj(xn, self.W(i, "attn_qkv.weight"), "qkv", "q")
-            z = self._proj(xn, self.W(i, "attn_gate.weight"), "z", "q")
+            with self._stage("norm"):
+                xn = self._norm_rows(h, self.F(i, "attn_norm.weight"))
+            with self._stage("gdn_qkvz_gemm"):
+                qkv = self._proj(xn, self.W(i, "attn_qkv.weight"), "qkv", "q")
+                z = self._proj(xn, self.W(i, "attn_gate.weight"), "z", "q")
             if self.gemm_impl == "tcgen05" and (2 * Hv) % 8 == 0:
                 from ..ops import gemm as GM
                 ab = sc.get("ab_proj", (T, 2 * Hv), torch.float32)
@@ -386,6 +418,8 @@ class HybridExecutor:
             self._out_small(og, self.W(i, "ssm_out.weight"), h)
             return
         cj = journal["conv"][i] if journal is not None else None
+        _gdn_stage = self._stage("gdn_core")
+        _gdn_stage.__enter__()
         K.conv1d(qkv, self.F(i, "ssm_conv1d.weight"), self.conv_state[i], b.seg_start, b.seg_slot, b.tok_seg, conv, C,
                  update_state=journal is None, journal=cj)
         K.gdn_prepare(conv, a_p, b_p, self.F(i, "ssm_a").reshape(-1), self.F(i, "ssm_dt.bias").reshape(-1), decay, beta,
@@ -399,10 +433,12 @@ class HybridExecutor:
             K.gdn_scan(conv, decay, beta, self.gdn_state[i], b.seg_start, b.seg_slot, o, G, Hv,
                        write_state=journal is None, journal=gj)
         K.gdn_gated_norm(o, z, self.F(i, "ssm_norm.weight").reshape(-1), og, Hv, S, cfg.rms_eps)
+        _gdn_stage.__exit__(None, None, None)
         if small:
             self._out_small(og, self.W(i, "ssm_out.weight"), h)
         else:
-            self._out_big(og, self.W(i, "ssm_out.weight"), h, "o")
+            with self._stage("out_gemm"):
+                self._out_big(og, self.W(i, "ssm_out.weight"), h, "o")
 
     def _ffn(self, i: int, h: torch.Tensor, b: BatchDesc, small: bool) -> None:
         cfg, sc = self.cfg, self.scratch
@@ -422,8 +458,8 @@ class HybridExecutor:
             self._out_small(act, self.W(i, "ffn_down.weight"), h)
         else:
             self._sync_resid(h)
-            xn = sc.get("xn", (T, cfg.hidden), torch.bfloat16)
-            K.rmsnorm_rows(h, norm_w, xn, cfg.rms_eps)
+            with self._stage("norm"):
+                xn = self._norm_rows(h, norm_w)
             if self._use_splitk(T):
                 from ..ops import gemm as GM
                 gu = sc.get("ffn_gu_f32", (T, 2 * Fd), torch.float32)
@@ -431,11 +467,14 @@ class HybridExecutor:
                 GM.gemm_quant_splitk(xn, self.W(i, "ffn_up.weight"), gu[:, Fd:], sc)
             else:
                 gu = sc.get("ffn_gu", (T, 2 * Fd), torch.bfloat16)
-                self._gemm(xn, self.W(i, "ffn_gate.weight"), gu[:, :Fd], tag="g")
-                self._gemm(xn, self.W(i, "ffn_up.weight"), gu[:, Fd:], tag="g")
+                with self._stage("ffn_gateup_gemm"):
+                    self._gemm(xn, self.W(i, "ffn_gate.weight"), gu[:, :Fd], tag="g")
+                    self._gemm(xn, self.W(i, "ffn_up.weight"), gu[:, Fd:], tag="g")
             act = sc.get("ffn_act", (T, Fd), torch.bfloat16)
-            K.act_mul(gu, act, cfg.act)
-            self._out_big(act, self.W(i, "ffn_down.weight"), h, "d")
+            with self._stage("act_mul"):
+                K.act_mul(gu, act, cfg.act)
+            with self._stage("ffn_down_gemm"):
+                self._out_big(act, self.W(i, "ffn_down.weight"), h, "d")
 
     # ------------------------------------------------------------------ whole model
     def forward(self, b: BatchDesc, journal: Optional[dict] = None, h_out: Optional[torch.Tensor] = None,
@@ -446,7 +485,7 @@ class HybridExecutor:
         cfg = self.cfg
         T = b.T
         small = T <= self.small_rows
-        h = h_out if h_out is not None else self.scratch.get("h", (T, cfg.hidden), torch.float32)
+        h = h_out if h_out is not None else self._resid_buffer(T)
         K.embed(self.dw["token_embd.weight"], b.tokens, h, cfg.embed_scale)
         for i in range(cfg.n_layers):
             if cfg.is_full_attention_layer(i):
@@ -456,7 +495,7 @@ class HybridExecutor:
             self._ffn(i, h, b, small)
         if not defer_resid:
             self._sync_resid(h)
-        return h
+        return self._finish_resid(h)
 
     def logits(self, h_rows: torch.Tensor, out: Optional[torch.Tensor] = None,
                hidden_out: Optional[torch.Tensor] = None) -> torch.Tensor:

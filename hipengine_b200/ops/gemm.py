@@ -59,7 +59,7 @@ def _float_weight_bf16(w: DeviceWeight, scratch) -> torch.Tensor:
 
 
 def gemm_quant(x: torch.Tensor, w: DeviceWeight, out: torch.Tensor, scratch, row0: int = 0,
-               rows: Optional[int] = None, epi: Optional[int] = None) -> torch.Tensor:
+               rows: Optional[int] = None, epi: Optional[int] = None, ag=None) -> torch.Tensor:
     """out[M, rows] = x[M, K] @ W[row0:row0+rows]^T for a device-layout weight.
 
     Q4_K / Q6_K / Q8_0 weights are read as stored (raw blocks by TMA, expanded to bf16 operand tiles inside the
@@ -77,6 +77,17 @@ def gemm_quant(x: torch.Tensor, w: DeviceWeight, out: torch.Tensor, scratch, row
         epi = 0 if out.dtype == torch.bfloat16 else 1
     M, a_cols = x.shape        # fewer columns than the weight's (zero-padded) K read as zeros
     st = status_word(x.device)
+    if ag is not None:
+        # sequence-parallel activations: rows of M-tile tm were written by rank tm % world; the kernel's TMA
+        # producer waits for that rank's stamp before the first load of the tile (all-gather -> GEMM)
+        fl, ep, world, lim = ag
+        N.check(N.lib().he_gemm_q_ag(C.c_void_p(x.data_ptr()), C.c_longlong(x.stride(0)), C.c_int(a_cols),
+                                     C.c_void_p(w.ptr + row0 * _row_bytes(w)), C.c_int(w.qtype), C.c_longlong(rows),
+                                     C.c_void_p(out.data_ptr()), C.c_longlong(out.stride(0)), C.c_int(M),
+                                     C.c_int(rows), C.c_int(w.n_cols), C.c_int(epi), C.c_void_p(fl), C.c_void_p(ep),
+                                     C.c_int(world), C.c_uint(lim), C.c_void_p(st.data_ptr()),
+                                     C.c_int(N.num_sms()), _stream()), "he_gemm_q_ag")
+        return out
     N.check(N.lib().he_gemm_q(C.c_void_p(x.data_ptr()), C.c_longlong(x.stride(0)), C.c_int(a_cols),
                               C.c_void_p(w.ptr + row0 * _row_bytes(w)), C.c_int(w.qtype), C.c_longlong(rows),
                               C.c_void_p(out.data_ptr()), C.c_longlong(out.stride(0)), C.c_int(M), C.c_int(rows),

@@ -389,3 +389,217 @@ class PeerResidual:
         for p in getattr(self, "_owned_regions", []):
             L.he_comm_free(C.c_void_p(p))
         self._owned_regions = []
+
+
+class _RawCuda:
+    """Zero-copy handle of raw device memory for ``torch.as_tensor`` (the CUDA array interface)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+def tensor_from_ptr(ptr: int, shape, dtype: torch.dtype, device) -> torch.Tensor:
+    n = 1
+    for s in shape:
+        n *= s
+    nbytes = n * torch.empty(0, dtype=dtype).element_size()
+    raw = torch.as_tensor(_RawCuda(ptr, nbytes), device=device)
+    return raw.view(dtype).reshape(*shape)
+
+
+class _WqFuse(C.Structure):
+    _fields_ = [("stage", C.c_void_p * _MAX_WORLD), ("flags", C.c_void_p * _MAX_WORLD), ("sync", C.c_void_p),
+                ("resid", C.c_void_p), ("ld_resid", C.c_longlong), ("world", C.c_int), ("rank", C.c_int),
+                ("slots", C.c_int), ("phases", C.c_int), ("wait_limit", C.c_uint), ("reserved", C.c_int)]
+
+
+class _SpPushArgs(C.Structure):
+    _fields_ = [("dst", C.c_void_p * _MAX_WORLD), ("flags", C.c_void_p * _MAX_WORLD), ("state", C.c_void_p),
+                ("h", C.c_void_p), ("norm_w", C.c_void_p), ("ld_h", C.c_longlong), ("ld_dst", C.c_longlong),
+                ("eps", C.c_float), ("T", C.c_int), ("H", C.c_int), ("mt", C.c_int), ("world", C.c_int),
+                ("rank", C.c_int), ("mode", C.c_int)]
+
+
+class SeqParallel:
+    """Sequence-parallel tensor-parallel prefill over peer memory.
+
+    The fp32 residual is sharded by M-tiles (tile ``tm`` of ``mt`` rows belongs to rank ``tm % world``):
+
+    * ``gemm_rs``   : row-parallel projection, GEMM -> reduce-scatter -> residual add in ONE tcgen05 kernel per rank
+      (``csrc/gemm_wq_sm100.cu::gemm_wq_rs_kernel``): partial tiles leave the epilogue as bf16 peer stores into the
+      owner's stage, owners sum in fp32 straight into their residual rows;
+    * ``norm_push`` : RMSNorm of the owned rows written as bf16 into EVERY rank's activation buffer (the all-gather,
+      as peer stores of whole rows) + a stamp;
+    * the next column-parallel GEMM reads the gathered rows from local memory and waits, tile by tile inside its TMA
+      producer, for the stamp of each tile's owner (``ops/gemm.py::gemm_quant(..., ag=...)``).
+
+    The sharding contract follows the reference's planning notes (``docs/reference/TENSOR_PARALLEL.md:44-52,81-90``);
+    the reference itself is single-device.  Region per rank (CUDA IPC, single node): stage, reduce-scatter stamps,
+    activation rows, residual rows, all-gather stamps.
+    """
+
+    def __init__(self, ctx: DistContext, hidden: int, max_rows: int = 4096, wait_limit: int = 1 << 22,
+                 _regions: Optional[List[int]] = None):
+        L = N.lib()
+        assert L.he_gemm_q_fuse_args_size() == C.sizeof(_WqFuse), "ABI mismatch for WqFuse"
+        assert L.he_sp_push_args_size() == C.sizeof(_SpPushArgs), "ABI mismatch for SpPushArgs"
+        assert ctx.world <= _MAX_WORLD and hidden % 8 == 0
+        self.ctx, self.hidden, self.max_rows, self.wait_limit = ctx, hidden, max_rows, wait_limit
+        W = ctx.world
+        self.tile_elems = L.he_gemm_q_rs_tile_elems()
+        self.tiles_n = (hidden + 127) // 128
+        # slots for the finest tiling a call of up to max_rows rows can have (192-row tiles above 192 rows, one tile below)
+        mt_big = int(L.he_gemm_q_mt(C.c_int(max(max_rows, 192))))
+        self.slots = max(1, ((max_rows + mt_big - 1) // mt_big + W - 1) // W) * self.tiles_n
+        al = lambda b: (b + 1023) // 1024 * 1024
+        self.off_stage = 0
+        self.off_rsflags = al(W * self.slots * self.tile_elems * 2)
+        self.off_xn = self.off_rsflags + al(self.slots * W * 4 * 4)
+        self.off_h = self.off_xn + al(max_rows * hidden * 2)
+        self.off_agflags = self.off_h + al(max_rows * hidden * 4)
+        self.total_bytes = self.off_agflags + 1024
+        self._opened: List[int] = []
+        self._local = 0
+        if _regions is not None:
+            self._peer_ptrs = list(_regions)
+        else:
+            base = C.c_void_p()
+            N.check(L.he_comm_alloc(C.c_longlong(self.total_bytes), C.byref(base)), "he_comm_alloc")
+            self._local = base.value
+            self._peer_ptrs = [self._local] * W
+            if W > 1:
+                hsz = L.he_comm_ipc_handle_size()
+                handle = (C.c_char * hsz)()
+                N.check(L.he_comm_ipc_get(C.c_void_p(self._local), handle), "he_comm_ipc_get")
+                handles: List[bytes] = [b""] * W
+                dist.all_gather_object(handles, bytes(handle.raw), group=ctx.group)
+                for r in range(W):
+                    if r == ctx.rank:
+                        continue
+                    p = C.c_void_p()
+                    buf = (C.c_char * hsz).from_buffer_copy(handles[r])
+                    N.check(L.he_comm_ipc_open(buf, C.byref(p)), "he_comm_ipc_open")
+                    self._peer_ptrs[r] = p.value
+                    self._opened.append(p.value)
+        self.rs_sync = torch.zeros(2, dtype=torch.int32, device=ctx.device)
+        self.sp_state = torch.zeros(2, dtype=torch.int32, device=ctx.device)
+        self._views_ready = False
+        if _regions is None:
+            self._make_views()
+            if W > 1:
+                ctx.barrier()
+        self.rs_calls = 0
+        self.ag_pending = False
+
+    def _make_views(self) -> None:
+        me = self._peer_ptrs[self.ctx.rank]
+        dev = self.ctx.device
+        self.xn = tensor_from_ptr(me + self.off_xn, (self.max_rows, self.hidden), torch.bfloat16, dev)
+        self.h = tensor_from_ptr(me + self.off_h, (self.max_rows, self.hidden), torch.float32, dev)
+        self._views_ready = True
+
+    @classmethod
+    def emulated_group(cls, device, hidden: int, world: int, max_rows: int = 512) -> List["SeqParallel"]:
+        """``world`` instances in ONE process on one GPU wired to each other's regions; kernels must be run phase by
+        phase (all ranks' phase 1, then all phase 2) so that no launch waits for a later one."""
+        L = N.lib()
+        regions: List[int] = []
+        out: List[SeqParallel] = []
+        for r in range(world):
+            ctx = DistContext(r, world, 0, torch.device(device), None, "loopback")
+            inst = cls(ctx, hidden, max_rows, wait_limit=20000, _regions=[0] * world)
+            base = C.c_void_p()
+            N.check(L.he_comm_alloc(C.c_longlong(inst.total_bytes), C.byref(base)), "he_comm_alloc")
+            regions.append(base.value)
+            out.append(inst)
+        for inst in out:
+            inst._peer_ptrs = list(regions)
+            inst._make_views()
+        out[0]._owned_regions = regions
+        return out
+
+    # ------------------------------------------------------------------ tiling
+    def mt(self, rows: int) -> int:
+        return int(N.lib().he_gemm_q_mt(C.c_int(rows)))
+
+    def owned_rows(self, rows: int) -> List[int]:
+        mt, W, r = self.mt(rows), self.ctx.world, self.ctx.rank
+        out: List[int] = []
+        for tm in range(r, (rows + mt - 1) // mt, W):
+            out += list(range(tm * mt, min(rows, (tm + 1) * mt)))
+        return out
+
+    # ------------------------------------------------------------------ kernels
+    def gemm_rs(self, x: torch.Tensor, w: "K.DeviceWeight", rows: int, phases: int = 3) -> None:
+        """self.h[owned rows of the first ``rows``] += sum over ranks of x_rank[rows, K] @ W_rank[hidden, K]^T."""
+        assert x.dtype == torch.bfloat16 and x.shape[0] == rows and rows <= self.max_rows and x.stride(1) == 1
+        assert w.n_rows == self.hidden and w.n_cols == x.shape[1] and w.qtype in (8, 12, 14)
+        K._check_device(x)
+        a = _WqFuse()
+        for r, p in enumerate(self._peer_ptrs):
+            a.stage[r], a.flags[r] = p + self.off_stage, p + self.off_rsflags
+        a.sync = self.rs_sync.data_ptr()
+        a.resid, a.ld_resid = self.h.data_ptr(), self.h.stride(0)
+        a.world, a.rank, a.slots, a.phases, a.wait_limit = (self.ctx.world, self.ctx.rank, self.slots, phases,
+                                                            self.wait_limit)
+        st = K.status_tensor(x.device)
+        N.check(N.lib().he_gemm_q_reduce_scatter(
+            C.c_void_p(x.data_ptr()), C.c_longlong(x.stride(0)), C.c_void_p(w.ptr), C.c_int(w.qtype),
+            C.c_longlong(w.n_rows), C.c_int(rows), C.c_int(self.hidden), C.c_int(w.n_cols), C.byref(a),
+            C.c_void_p(st.data_ptr()), C.c_int(N.num_sms()), K._stream()), "he_gemm_q_reduce_scatter")
+        self.rs_calls += 1
+
+    def _push(self, rows: int, norm_w: Optional[torch.Tensor], eps: float, mode: int) -> None:
+        a = _SpPushArgs()
+        off = self.off_xn if mode == 0 else self.off_h
+        for r, p in enumerate(self._peer_ptrs):
+            a.dst[r], a.flags[r] = p + off, p + self.off_agflags
+        a.state = self.sp_state.data_ptr()
+        a.h, a.ld_h = self.h.data_ptr(), self.h.stride(0)
+        a.norm_w = norm_w.data_ptr() if norm_w is not None else None
+        a.ld_dst = self.hidden
+        a.eps, a.T, a.H, a.mt = eps, rows, self.hidden, self.mt(rows)
+        a.world, a.rank, a.mode = self.ctx.world, self.ctx.rank, mode
+        N.check(N.lib().he_sp_norm_push(C.byref(a), C.c_int(N.num_sms()), K._stream()), "he_sp_norm_push")
+        self.ag_pending = True
+
+    def norm_push(self, rows: int, norm_w: torch.Tensor, eps: float) -> torch.Tensor:
+        """RMSNorm of this rank's rows of ``self.h`` into every rank's activation buffer; returns the (local) buffer,
+        whose rows are complete once the consumers' all-gather wait (``ag_args``) or ``wait`` has passed."""
+        self._push(rows, norm_w, eps, 0)
+        return self.xn[:rows]
+
+    def gather_residual(self, rows: int) -> torch.Tensor:
+        """Copy this rank's residual rows to every rank and wait for the others': ``self.h[:rows]`` complete."""
+        self._push(rows, None, 0.0, 1)
+        self.wait()
+        return self.h[:rows]
+
+    def ag_args(self):
+        """(flags pointer, epoch pointer, world, wait limit) for the all-gather wait of a consumer GEMM."""
+        me = self._peer_ptrs[self.ctx.rank]
+        return (me + self.off_agflags, self.sp_state.data_ptr(), self.ctx.world, self.wait_limit)
+
+    def wait(self) -> None:
+        """Stream-ordered wait for every rank's last push (consumers other than the all-gather GEMM)."""
+        fl, ep, W, lim = self.ag_args()
+        st = K.status_tensor(self.ctx.device)
+        N.check(N.lib().he_sp_wait(C.c_void_p(fl), C.c_void_p(ep), C.c_int(W), C.c_uint(lim),
+                                   C.c_void_p(st.data_ptr()), K._stream()), "he_sp_wait")
+        self.ag_pending = False
+
+    def close(self) -> None:
+        L = N.lib()
+        torch.cuda.synchronize()
+        self.xn = self.h = None
+        if self.ctx.backend not in ("loopback", "none") and self.ctx.world > 1:
+            self.ctx.barrier()
+        for p in self._opened:
+            L.he_comm_ipc_close(C.c_void_p(p))
+        self._opened = []
+        if self._local:
+            L.he_comm_free(C.c_void_p(self._local))
+            self._local = 0
+        for p in getattr(self, "_owned_regions", []):
+            L.he_comm_free(C.c_void_p(p))
+        self._owned_regions = []

@@ -50,7 +50,7 @@ def main() -> int:
 
     report = {"world": ctx.world, "model": args.model}
     ok = True
-    ref = run(HybridExecutor(w, device=dev, max_slots=1, max_context=256))
+    ref = run(HybridExecutor(w, device=dev, max_slots=1, max_context=max(256, args.prompt + 64)))
     # the fp32 reference model (plain PyTorch, dequantised weights) of the same tokens: the gate every executor's
     # logits must pass (KL per row, top-1 agreement where the reference itself is decided)
     from ..ref.model import RefModel
@@ -65,7 +65,7 @@ def main() -> int:
         top1 = ((ref32.argmax(-1) == got.argmax(-1)) | ~decided).float().mean().item()
         return float(kl.max()), top1
     for comm in ("nccl", "fused"):
-        ex = TPHybridExecutor(w, ctx, comm=comm, max_slots=1, max_context=256)
+        ex = TPHybridExecutor(w, ctx, comm=comm, max_slots=1, max_context=max(256, args.prompt + 64))
         got = run(ex)
         K.check_status(dev)
         err = ((got - ref).abs().max() / ref.std()).item()
@@ -90,7 +90,7 @@ def main() -> int:
             r.set_rows([0], [first], [args.prompt])
             seq = []
             for _ in range(5):
-                r.step(1, 256)
+                r.step(1, max(256, args.prompt + 64))
                 seq.append(int(r.tokens[0]))
             K.check_status(dev)
             # the same tokens from eager steps through the gathered logits (the folded reductions and the merged
@@ -113,13 +113,15 @@ def main() -> int:
             # captured graphs hold library collectives: drop them before the process group goes away
             r.graphs.clear()
             del r
-            ex.close_comm()
             if ex.fused is not None:
                 ex.fused.close()
+            if ex.sp is not None:
+                report["seq_parallel_rs_calls"] = ex.sp.rs_calls
+                ok = ok and (ex.sp.rs_calls > 0 or args.prompt <= 128)
             if ex.fgemm is not None:
                 report["fused_gemm_calls"] = ex.fgemm.calls
-                ok = ok and ex.fgemm.calls > 0
                 ex.fgemm.close()
+            ex.close_comm()
         del ex
 
     # the public API as an SPMD job: every rank issues the same call; tokens must match a single-GPU engine

@@ -48,6 +48,7 @@ class TPHybridExecutor(HybridExecutor):
         self.peer = None
         self.peer_head = None
         self._pending = None
+        self.sp = None
         if self.comm == "fused" and ctx.world > 1:
             from .fused import FusedReducer, PeerResidual
             self.fused = FusedReducer(ctx, self.full_cfg.hidden, max_rows=GEMV_MAX_ROWS)
@@ -62,7 +63,12 @@ class TPHybridExecutor(HybridExecutor):
                     os.environ.get("HE_TP_FUSED_GEMM", "1") != "0":
                 from .fused import FusedGemmAllReduce
                 rows = min(8192, (self.max_context + 127) // 128 * 128)
-                self.fgemm = FusedGemmAllReduce(ctx, self.full_cfg.hidden, max_rows=rows)
+                if not self.full_cfg.is_moe and os.environ.get("HE_TP_SEQ_PARALLEL", "1") != "0":
+                    # prefill: residual sharded by rows; GEMM -> reduce-scatter and all-gather -> GEMM over peer memory
+                    from .fused import SeqParallel
+                    self.sp = SeqParallel(ctx, self.full_cfg.hidden, max_rows=rows)
+                else:
+                    self.fgemm = FusedGemmAllReduce(ctx, self.full_cfg.hidden, max_rows=rows)
 
     # ------------------------------------------------------------------ reductions
     def _sync_resid(self, h: torch.Tensor) -> None:
@@ -119,9 +125,51 @@ class TPHybridExecutor(HybridExecutor):
         self.ctx.all_reduce_(part)
         K.resid_add_f32(h, part)
 
+    # ------------------------------------------------------------------ sequence-parallel prefill
+    def _sp_on(self, h: torch.Tensor) -> bool:
+        return (self.sp is not None and h.shape[0] > self.SPLITK_MAX_ROWS and h.shape[0] <= self.sp.max_rows
+                and h.data_ptr() == self.sp.h.data_ptr())
+
+    def _resid_buffer(self, T: int) -> torch.Tensor:
+        if self.sp is not None and self.SPLITK_MAX_ROWS < T <= self.sp.max_rows and self.gemm_impl == "tcgen05":
+            return self.sp.h[:T]
+        return super()._resid_buffer(T)
+
+    def _norm_rows(self, h: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        if self._sp_on(h):
+            return self.sp.norm_push(h.shape[0], w, self.cfg.rms_eps)
+        return super()._norm_rows(h, w)
+
+    def _gemm(self, x: torch.Tensor, w: DeviceWeight, out: torch.Tensor, row0: int = 0, rows=None,
+              tag: str = "w") -> torch.Tensor:
+        if self.sp is not None and self.sp.ag_pending and x.data_ptr() == self.sp.xn.data_ptr():
+            from ..ops import gemm as GM
+            if GM.quant_gemm_ok(w) and self.gemm_impl == "tcgen05":
+                # the first reader of freshly pushed rows waits for their owners tile by tile inside the kernel;
+                # everything after it in the stream sees complete rows
+                self.sp.ag_pending = False
+                rows_ = w.n_rows - row0 if rows is None else rows
+                return GM.gemm_quant(x, w, out, self.scratch, row0=row0, rows=rows_, ag=self.sp.ag_args())
+            self.sp.wait()
+        return super()._gemm(x, w, out, row0=row0, rows=rows, tag=tag)
+
+    def _finish_resid(self, h: torch.Tensor) -> torch.Tensor:
+        if self._sp_on(h):
+            return self.sp.gather_residual(h.shape[0])
+        return h
+
     def _out_big(self, x: torch.Tensor, w: DeviceWeight, h: torch.Tensor, tag: str) -> None:
         if self.ctx.world == 1:
             return super()._out_big(x, w, h, tag)
+        if self._sp_on(h):
+            from ..ops import gemm as GM
+            if GM.quant_gemm_ok(w):
+                self.sp.gemm_rs(x, w, h.shape[0])
+            else:
+                y = self._gemm(x, w, self.scratch.get("y_bf", (x.shape[0], w.n_rows), torch.bfloat16), tag=tag)
+                self.ctx.all_reduce_(y)
+                K.resid_add_bf16(h, y)
+            return
         if self.fgemm is not None and self.fgemm.supports(x.shape[0], h):
             # GEMM, all-reduce over peer memory and residual add as one tcgen05 kernel per rank
             from ..ops import gemm as GM
@@ -185,10 +233,10 @@ class TPHybridExecutor(HybridExecutor):
         return out_ids
 
     def close_comm(self) -> None:
-        for obj in (self.peer, self.peer_head):
+        for obj in (self.peer, self.peer_head, self.sp):
             if obj is not None:
                 obj.close()
-        self.peer = self.peer_head = None
+        self.peer = self.peer_head = self.sp = None
 
 
 def build_tp_executor(cfg, seed: int, device, ctx: Optional[DistContext] = None, comm: Optional[str] = None,

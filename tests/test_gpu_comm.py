@@ -223,3 +223,89 @@ def test_vocab_parallel_argmax_merge_and_bounded_wait():
     assert torch.equal(outs[world - 1], cand.min(0).values)
     for g in group:
         g.close()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_sequence_parallel_gemm_reduce_scatter_norm_allgather_emulated(world):
+    """Sequence-parallel prefill on emulated ranks of one GPU, phase by phase: GEMM -> reduce-scatter -> residual add
+    (quantised weight read in place), RMSNorm + all-gather push, the all-gather wait of the consumer GEMM, and the
+    final residual gather -- each against plain fp32 PyTorch."""
+    from hipengine_b200.models.executor import _Scratch
+    from hipengine_b200.ops import gemm as G
+    from hipengine_b200.ops import kernels as K
+    from hipengine_b200.parallel.fused import SeqParallel
+    from hipengine_b200.quant import ggml as Q
+    T, H, Kq, N2 = 400, 512, 512, 384
+    group = SeqParallel.emulated_group("cuda", H, world, max_rows=512)
+    g = torch.Generator(device="cuda").manual_seed(world)
+    h0 = torch.randn(T, H, device="cuda", generator=g)
+    xs, dws, deqs = [], [], []
+    for q in range(world):
+        w = torch.randn(H, Kq, device="cuda", generator=g) * 0.05
+        raw = Q.quantize(w, Q.GGMLType.Q4_K)
+        deqs.append(Q.dequantize_torch(raw, Q.GGMLType.Q4_K, H, Kq))
+        dws.append(K.to_device_weight(raw, Q.GGMLType.Q4_K, H, Kq))
+        xs.append((torch.randn(T, Kq, device="cuda", generator=g) * 0.5).bfloat16())
+        group[q].h[:T].copy_(h0)
+    for ph in (1, 2):
+        for q in range(world):
+            group[q].gemm_rs(xs[q], dws[q], T, phases=ph)
+    torch.cuda.synchronize()
+    K.check_status()
+    want = h0.clone()
+    for q in range(world):
+        want += xs[q].float() @ deqs[q].t()
+    full = torch.zeros_like(want)
+    for q in range(world):
+        own = torch.tensor(group[q].owned_rows(T), device="cuda", dtype=torch.long)
+        other = torch.ones(T, dtype=torch.bool, device="cuda")
+        other[own] = False
+        got = group[q].h[:T]
+        assert torch.equal(got[other], h0[other])                      # rows of other owners untouched
+        if own.numel():
+            err = (got[own] - want[own]).abs().max() / want.abs().max()
+            assert err < 6e-3, (q, err)                                 # bf16 partials, fp32 sum
+            full[own] = got[own]
+    # RMSNorm + all-gather: every rank ends up with the same normalised rows of ALL owners
+    nw = torch.rand(H, device="cuda", generator=g) + 0.5
+    for q in range(world):
+        group[q].norm_push(T, nw, 1e-6)
+    for q in range(world):
+        group[q].wait()
+    torch.cuda.synchronize()
+    K.check_status()
+    ref_xn = (full * torch.rsqrt(full.pow(2).mean(-1, keepdim=True) + 1e-6) * nw)
+    for q in range(world):
+        assert torch.equal(group[q].xn[:T], group[0].xn[:T])
+        assert (group[q].xn[:T].float() - ref_xn).abs().max() < 0.02 * ref_xn.abs().max()
+    # consumer GEMM with the all-gather wait inside its TMA producer (stamps already present here)
+    w2 = torch.randn(N2, H, device="cuda", generator=g) * 0.05
+    raw2 = Q.quantize(w2, Q.GGMLType.Q4_K)
+    dw2 = K.to_device_weight(raw2, Q.GGMLType.Q4_K, N2, H)
+    out = torch.zeros(T, N2, device="cuda")
+    G.gemm_quant(group[1].xn[:T], dw2, out, _Scratch(torch.device("cuda")), ag=group[1].ag_args())
+    torch.cuda.synchronize()
+    K.check_status()
+    ref = group[1].xn[:T].float() @ Q.dequantize_torch(raw2, Q.GGMLType.Q4_K, N2, H).t()
+    assert (out - ref).norm() / ref.norm() < 6e-3
+    # a consumer whose owner never stamps gives up (bounded) and reports it
+    group[0].sp_state[0] += 1
+    out.zero_()
+    lim_args = list(group[0].ag_args())
+    lim_args[3] = 50
+    G.gemm_quant(group[0].xn[:T], dw2, out, _Scratch(torch.device("cuda")), ag=tuple(lim_args))
+    torch.cuda.synchronize()
+    assert int(K.status_tensor("cuda")[0].item()) == 1
+    K.status_tensor("cuda").zero_()
+    group[0].sp_state[0] -= 1
+    # final gather of the residual itself
+    for q in range(world):
+        group[q]._push(T, None, 0.0, 1)
+    for q in range(world):
+        group[q].wait()
+    torch.cuda.synchronize()
+    K.check_status()
+    for q in range(world):
+        assert torch.equal(group[q].h[:T], full)
+    for gq in group:
+        gq.close()
