@@ -144,10 +144,10 @@ def main() -> int:
                for _ in range(args.steps + args.warmup)]
     from hipengine_b200.models.decode_graph import DecodeGraphRunner
 
-    def build(tp: bool):
+    def build(tp: bool, comm=None):
         if tp:
             from hipengine_b200.parallel.tp import build_tp_executor
-            e = build_tp_executor(cfg, seed=0, device=dev, ctx=ctx, comm=args.tp_comm, max_slots=1,
+            e = build_tp_executor(cfg, seed=0, device=dev, ctx=ctx, comm=comm or args.tp_comm, max_slots=1,
                                   max_context=ctx_max)
         else:
             from hipengine_b200.models import make_executor
@@ -162,7 +162,9 @@ def main() -> int:
 
     def measure(ex, runner, n_warm, n_steps, sample_clocks):
         """n_warm untimed requests, then n_steps timed ones; device times are max over ranks."""
-        def one_request(prompt, ev):
+        tok_log = torch.zeros(args.gen_len, dtype=torch.int64, device=dev)
+
+        def one_request(prompt, ev, log=False):
             ex.reset_slot(0)
             ev[0].record()
             logits = ex.prefill(0, prompt)
@@ -172,14 +174,21 @@ def main() -> int:
             runner.ctx_len[:1].fill_(len(prompt))
             runner.publish(1)                       # first token -> tokens[0], pos -> len(prompt)
             ev[1].record()
-            for _ in range(args.gen_len - 1):
+            for j in range(args.gen_len - 1):
                 runner.step(1, ctx_max)
+                if log:
+                    tok_log[j].copy_(runner.tokens[0])
             ev[2].record()
 
         mk = lambda: [torch.cuda.Event(enable_timing=True) for _ in range(3)]
         for i in range(n_warm):
-            one_request(prompts[i % len(prompts)], mk())
+            # the last warm-up request (untimed) records its tokens: tensor-parallel ranks must generate the same ones
+            one_request(prompts[i % len(prompts)], mk(), log=(i == n_warm - 1))
         barrier()
+        agree = None
+        if world > 1 and mode == "tp":
+            allt = ctx.all_gather(tok_log)
+            agree = bool((allt == allt[0]).all())
         sampler = ClockSampler(local_rank)
         if rank == 0 and sample_clocks:
             sampler.start()
@@ -200,7 +209,7 @@ def main() -> int:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         prefill_ms, decode_ms = t.tolist()
         return {"prefill_ms": prefill_ms, "decode_ms": decode_ms, "wall_s": wall_s, "launches": launches,
-                "clocks": clocks}
+                "clocks": clocks, "ranks_agree": agree}
 
     t_build0 = time.time()
     ex, runner = build(tp=(mode == "tp"))
@@ -230,12 +239,34 @@ def main() -> int:
             if world > 1:
                 raise
 
+    nccl_base = None
+    if world > 1 and mode == "tp" and args.tp_comm == "fused" and not args.no_extra:
+        # the same tensor-parallel engine with every collective done by the library (NCCL all-reduce / all-gather
+        # after the kernels, nothing fused): the baseline the fused peer-memory paths are measured against
+        if runner is not None:
+            runner.graphs.clear()
+        close = getattr(ex, "close_comm", None)
+        if close is not None:
+            close()
+        runner = ex = None
+        torch.cuda.empty_cache()
+        try:
+            ex, runner = build(tp=True, comm="nccl")
+            mb = measure(ex, runner, 2, 1, False)
+            nccl_base = {"steps": 1, "warmup": 2, "decode_tok_s": round((args.gen_len - 1) / (mb["decode_ms"] / 1e3), 3),
+                         "prefill_tok_s": round(args.prompt_len / (mb["prefill_ms"] / 1e3), 2),
+                         "itl_ms": round(mb["decode_ms"] / (args.gen_len - 1), 4),
+                         "ttft_ms": round(mb["prefill_ms"], 3), "ranks_agree": mb["ranks_agree"]}
+        except Exception as exc:
+            nccl_base = {"error": f"{type(exc).__name__}: {exc}"}
+
     extra = None
     if world > 1 and not args.no_extra:
         # the other way to use the N GPUs, measured briefly for context: tp -> N independent replicas (aggregate
         # tokens/s, weak scaling); dp -> the single stream sharded over all GPUs
         other_tp = mode == "dp"
-        runner.graphs.clear()
+        if runner is not None:
+            runner.graphs.clear()
         runner = ex = None
         torch.cuda.empty_cache()
         try:
@@ -278,6 +309,9 @@ def main() -> int:
             line["other_parallelism"] = extra
         if mode == "tp":
             line["config"]["tp_comm"] = args.tp_comm
+            line["ranks_agree"] = m["ranks_agree"]
+        if nccl_base is not None:
+            line["nccl_baseline"] = nccl_base
         if args.layers:
             line["invalid"] = "truncated layer stack (debug run)"
         print(json.dumps(line))

@@ -162,6 +162,12 @@ TINY_HYBRID_TP = ModelConfig(arch="qwen35", n_layers=4, hidden=512, vocab=2048, 
                              qk_norm=True, full_attention_interval=4, ssm_groups=4, ssm_v_heads=8,
                              ssm_state=128, conv_kernel=4, max_context=4096)
 
+# The same at a geometry that splits over 2, 4 and 8 ranks (16 K-head groups -> 2 per rank at 8; 8 heads; 8 FFN blocks).
+SMALL_HYBRID_TP8 = ModelConfig(arch="qwen35", n_layers=4, hidden=512, vocab=2048, n_heads=8, n_kv_heads=2,
+                               head_dim=256, ffn=2048, rope_theta=1e7, rope_dim=64, gated_attention=True,
+                               qk_norm=True, full_attention_interval=4, ssm_groups=16, ssm_v_heads=32,
+                               ssm_state=128, conv_kernel=4, max_context=4096)
+
 TINY_HYBRID_MOE_TP = ModelConfig(arch="qwen35moe", n_layers=4, hidden=512, vocab=2048, n_heads=4, n_kv_heads=2,
                                  head_dim=256, ffn=0, rope_theta=1e7, rope_dim=64, gated_attention=True,
                                  qk_norm=True, full_attention_interval=4, ssm_groups=4, ssm_v_heads=8,
@@ -193,6 +199,7 @@ NAMED_CONFIGS: Dict[str, ModelConfig] = {
     "tiny-hybrid": TINY_HYBRID,
     "tiny-hybrid-moe": TINY_HYBRID_MOE,
     "tiny-hybrid-tp": TINY_HYBRID_TP,
+    "small-hybrid-tp8": SMALL_HYBRID_TP8,
     "tiny-hybrid-moe-tp": TINY_HYBRID_MOE_TP,
     "tiny-gemma4": TINY_GEMMA4,
     "qwen35-27b": QWEN35_27B,
