@@ -450,3 +450,138 @@ HE_API int he_sp_wait(const void* flags, const void* state, int world, unsigned 
   HE_LAUNCH_CHECK();
   return 0;
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// Reduce-scatter of token-ordered partial rows into the row-sharded residual (expert parallelism on top of the
+// sequence-parallel residual): every rank holds partial[T][H] fp32 -- the weighted outputs of ITS experts for every
+// token -- and each row's sum over ranks belongs to the row's owner (tile tm of mt rows -> rank tm % world).
+//   push   : rows owned by another rank go as bf16 into that rank's stage [src][owned row index][H] (peer stores of
+//            whole rows); the last CTA fences and stamps flags[owner][me];
+//   reduce : the owner waits (bounded) for the world-1 stamps and adds local fp32 partial + the staged rows (rank
+//            order, fp32) into its residual rows.
+namespace {
+
+struct SpRowsArgs {
+  __nv_bfloat16* stage[GEMV_MAX_WORLD];   // every rank's stage
+  uint32_t* flags[GEMV_MAX_WORLD];        // every rank's stamp array [world]
+  uint32_t* state;                        // local: [0] epoch of the last completed push, [1] CTAs done
+  const float* partial;                   // local [T][ld_p]
+  float* resid;                           // local [T][ld_h]: owned rows are updated
+  long long ld_p, ld_h;
+  int T, H, mt, world, rank, rows_cap;    // rows_cap: stage rows per source
+  unsigned wait_limit;
+  int* status;
+};
+
+__device__ __forceinline__ int sp_owned_index(int m, int mt, int W) { return (m / mt / W) * mt + m % mt; }
+
+__global__ void __launch_bounds__(256) sp_rows_push_kernel(const SpRowsArgs a) {
+  const int W = a.world, n8 = a.H / 8;
+  for (int m = blockIdx.x; m < a.T; m += gridDim.x) {
+    const int owner = (m / a.mt) % W;
+    if (owner == a.rank) continue;
+    __nv_bfloat16* dst = a.stage[owner] + ((size_t)a.rank * a.rows_cap + sp_owned_index(m, a.mt, W)) * a.H;
+    const float* src = a.partial + (size_t)m * a.ld_p;
+    for (int g = threadIdx.x; g < n8; g += blockDim.x) {
+      const float4 x0 = *reinterpret_cast<const float4*>(src + (size_t)g * 8);
+      const float4 x1 = *reinterpret_cast<const float4*>(src + (size_t)g * 8 + 4);
+      uint4 pk;
+      uint32_t* pw = reinterpret_cast<uint32_t*>(&pk);
+      __nv_bfloat162 h0 = __floats2bfloat162_rn(x0.x, x0.y), h1 = __floats2bfloat162_rn(x0.z, x0.w);
+      __nv_bfloat162 h2 = __floats2bfloat162_rn(x1.x, x1.y), h3 = __floats2bfloat162_rn(x1.z, x1.w);
+      pw[0] = *reinterpret_cast<uint32_t*>(&h0); pw[1] = *reinterpret_cast<uint32_t*>(&h1);
+      pw[2] = *reinterpret_cast<uint32_t*>(&h2); pw[3] = *reinterpret_cast<uint32_t*>(&h3);
+      *reinterpret_cast<uint4*>(dst + (size_t)g * 8) = pk;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const unsigned prev = atomicAdd(a.state + 1, 1u);
+    if (prev == gridDim.x - 1) {
+      a.state[1] = 0;
+      const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(a.state) + 1u;
+      __threadfence_system();
+      for (int q = 0; q < W; ++q) st_release_sys_u32(a.flags[q] + a.rank, epoch);
+      *reinterpret_cast<volatile uint32_t*>(a.state) = epoch;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) sp_rows_reduce_kernel(const SpRowsArgs a) {
+  const int W = a.world, n8 = a.H / 8;
+  const uint32_t want = *reinterpret_cast<const volatile uint32_t*>(a.state);
+  if ((int)threadIdx.x < W) {
+    unsigned polls = 0;
+    while ((int)(ld_acquire_sys_u32(a.flags[a.rank] + threadIdx.x) - want) < 0) {
+      if (++polls > a.wait_limit) {
+        if (a.status != nullptr) atomicCAS(a.status, 0, HE_ERR_WAIT_TIMEOUT);
+        break;
+      }
+      __nanosleep(100);
+    }
+  }
+  __syncthreads();
+  const int tiles_m = (a.T + a.mt - 1) / a.mt;
+  const int owned_tiles = tiles_m > a.rank ? (tiles_m - a.rank + W - 1) / W : 0;
+  for (int j = blockIdx.x; j < owned_tiles * a.mt; j += gridDim.x) {
+    const int m = (a.rank + W * (j / a.mt)) * a.mt + j % a.mt;
+    if (m >= a.T) continue;
+    const float* loc = a.partial + (size_t)m * a.ld_p;
+    float* hr = a.resid + (size_t)m * a.ld_h;
+    for (int g = threadIdx.x; g < n8; g += blockDim.x) {
+      float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int q = 0; q < W; ++q) {                 // rank order; the local contribution is exact fp32
+        if (q == a.rank) {
+          const float4 x0 = *reinterpret_cast<const float4*>(loc + (size_t)g * 8);
+          const float4 x1 = *reinterpret_cast<const float4*>(loc + (size_t)g * 8 + 4);
+          s[0] += x0.x; s[1] += x0.y; s[2] += x0.z; s[3] += x0.w;
+          s[4] += x1.x; s[5] += x1.y; s[6] += x1.z; s[7] += x1.w;
+        } else {
+          uint4 v;
+          const __nv_bfloat16* sp = a.stage[a.rank] + ((size_t)q * a.rows_cap + j) * a.H + (size_t)g * 8;
+          asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(sp));
+          const __nv_bfloat162* hv = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 t2 = __bfloat1622float2(hv[e]);
+            s[2 * e] += t2.x;
+            s[2 * e + 1] += t2.y;
+          }
+        }
+      }
+      float4* hp = reinterpret_cast<float4*>(hr + (size_t)g * 8);
+      float4 h0 = hp[0], h1 = hp[1];
+      h0.x += s[0]; h0.y += s[1]; h0.z += s[2]; h0.w += s[3];
+      h1.x += s[4]; h1.y += s[5]; h1.z += s[6]; h1.w += s[7];
+      hp[0] = h0;
+      hp[1] = h1;
+    }
+  }
+}
+
+}  // namespace
+
+HE_API int he_sp_rows_args_size() { return (int)sizeof(SpRowsArgs); }
+
+// phases bit 0: push, bit 1: reduce (3 in production; emulated ranks of one GPU run all pushes before any reduce).
+HE_API int he_sp_rows_reduce_scatter(const SpRowsArgs* args, int phases, int num_sms, cudaStream_t stream) {
+  const SpRowsArgs& a = *args;
+  if (a.T <= 0) return 0;
+  if (a.world < 1 || a.world > GEMV_MAX_WORLD || a.rank < 0 || a.rank >= a.world || a.mt <= 0 || a.H % 8 != 0)
+    return -HE_ERR_BAD_ARG;
+  const int tiles_m = (a.T + a.mt - 1) / a.mt;
+  if (((tiles_m + a.world - 1) / a.world) * a.mt > a.rows_cap) return -HE_ERR_BAD_ARG;
+  for (int q = 0; q < a.world; ++q)
+    if (a.stage[q] == nullptr || a.flags[q] == nullptr) return -HE_ERR_BAD_ARG;
+  int grid = a.T < 4 * num_sms ? a.T : 4 * num_sms;
+  if (phases & 1) {
+    sp_rows_push_kernel<<<grid, 256, 0, stream>>>(a);
+    HE_LAUNCH_CHECK();
+  }
+  if (phases & 2) {
+    sp_rows_reduce_kernel<<<grid, 256, 0, stream>>>(a);
+    HE_LAUNCH_CHECK();
+  }
+  return 0;
+}

@@ -271,6 +271,9 @@ class HybridExecutor:
         K.rmsnorm_rows(h, w, xn, self.cfg.rms_eps)
         return xn
 
+    def _xn_ready(self) -> None:
+        return
+
     def _resid_buffer(self, T: int) -> torch.Tensor:
         return self.scratch.get("h", (T, self.cfg.hidden), torch.float32)
 

@@ -134,8 +134,8 @@ def _moe_grouped(ex, i: int, h: torch.Tensor, target: torch.Tensor, T: int, norm
     e_lo, e_hi = rng or (0, E)
     El = e_hi - e_lo                      # local experts (all of them without expert parallelism)
     shared_here = L.has_shared and getattr(ex, "owns_shared_expert", True)
-    xn = sc.get("xn", (T, H), torch.bfloat16)
-    K.rmsnorm_rows(h, norm_w, xn, cfg.rms_eps)
+    xn = ex._norm_rows(h, norm_w)       # sequence-parallel executors gather the rows of all ranks here
+    ex._xn_ready()
     logits = sc.get("moe_logits", (T, L.n_logits_pad), torch.float32)
     GM.gemm_bf16(xn, L.r_hi, logits, epi=1)
     GM.gemm_bf16(xn, L.r_lo, logits, epi=2)

@@ -420,6 +420,13 @@ class _SpPushArgs(C.Structure):
                 ("rank", C.c_int), ("mode", C.c_int)]
 
 
+class _SpRowsArgs(C.Structure):
+    _fields_ = [("stage", C.c_void_p * _MAX_WORLD), ("flags", C.c_void_p * _MAX_WORLD), ("state", C.c_void_p),
+                ("partial", C.c_void_p), ("resid", C.c_void_p), ("ld_p", C.c_longlong), ("ld_h", C.c_longlong),
+                ("T", C.c_int), ("H", C.c_int), ("mt", C.c_int), ("world", C.c_int), ("rank", C.c_int),
+                ("rows_cap", C.c_int), ("wait_limit", C.c_uint), ("status", C.c_void_p)]
+
+
 class SeqParallel:
     """Sequence-parallel tensor-parallel prefill over peer memory.
 
@@ -457,7 +464,10 @@ class SeqParallel:
         self.off_xn = self.off_rsflags + al(self.slots * W * 4 * 4)
         self.off_h = self.off_xn + al(max_rows * hidden * 2)
         self.off_agflags = self.off_h + al(max_rows * hidden * 4)
-        self.total_bytes = self.off_agflags + 1024
+        self.off_rowflags = self.off_agflags + 1024
+        self.total_bytes = self.off_rowflags + 1024
+        assert L.he_sp_rows_args_size() == C.sizeof(_SpRowsArgs), "ABI mismatch for SpRowsArgs"
+        self.rows_cap = self.slots * self.tile_elems // hidden       # stage rows available per source rank
         self._opened: List[int] = []
         self._local = 0
         if _regions is not None:
@@ -483,6 +493,7 @@ class SeqParallel:
                     self._opened.append(p.value)
         self.rs_sync = torch.zeros(2, dtype=torch.int32, device=ctx.device)
         self.sp_state = torch.zeros(2, dtype=torch.int32, device=ctx.device)
+        self.rows_state = torch.zeros(2, dtype=torch.int32, device=ctx.device)
         self._views_ready = False
         if _regions is None:
             self._make_views()
@@ -548,6 +559,22 @@ class SeqParallel:
             C.c_longlong(w.n_rows), C.c_int(rows), C.c_int(self.hidden), C.c_int(w.n_cols), C.byref(a),
             C.c_void_p(st.data_ptr()), C.c_int(N.num_sms()), K._stream()), "he_gemm_q_reduce_scatter")
         self.rs_calls += 1
+
+    def rows_rs(self, partial: torch.Tensor, rows: int, phases: int = 3) -> None:
+        """self.h[owned rows] += sum over ranks of partial_rank[rows, hidden] (fp32, token order): the combine of
+        expert parallelism over the row-sharded residual (bf16 rows on the wire, fp32 sums on the owner)."""
+        assert partial.dtype == torch.float32 and partial.stride(1) == 1 and partial.shape[1] == self.hidden
+        a = _SpRowsArgs()
+        for r, p in enumerate(self._peer_ptrs):
+            a.stage[r], a.flags[r] = p + self.off_stage, p + self.off_rowflags
+        a.state = self.rows_state.data_ptr()
+        a.partial, a.ld_p = partial.data_ptr(), partial.stride(0)
+        a.resid, a.ld_h = self.h.data_ptr(), self.h.stride(0)
+        a.T, a.H, a.mt = rows, self.hidden, self.mt(rows)
+        a.world, a.rank, a.rows_cap, a.wait_limit = self.ctx.world, self.ctx.rank, self.rows_cap, self.wait_limit
+        a.status = K.status_tensor(self.ctx.device).data_ptr()
+        N.check(N.lib().he_sp_rows_reduce_scatter(C.byref(a), C.c_int(phases), C.c_int(N.num_sms()), K._stream()),
+                "he_sp_rows_reduce_scatter")
 
     def _push(self, rows: int, norm_w: Optional[torch.Tensor], eps: float, mode: int) -> None:
         a = _SpPushArgs()

@@ -63,7 +63,7 @@ class TPHybridExecutor(HybridExecutor):
                     os.environ.get("HE_TP_FUSED_GEMM", "1") != "0":
                 from .fused import FusedGemmAllReduce
                 rows = min(8192, (self.max_context + 127) // 128 * 128)
-                if not self.full_cfg.is_moe and os.environ.get("HE_TP_SEQ_PARALLEL", "1") != "0":
+                if os.environ.get("HE_TP_SEQ_PARALLEL", "1") != "0":
                     # prefill: residual sharded by rows; GEMM -> reduce-scatter and all-gather -> GEMM over peer memory
                     from .fused import SeqParallel
                     self.sp = SeqParallel(ctx, self.full_cfg.hidden, max_rows=rows)
@@ -113,6 +113,11 @@ class TPHybridExecutor(HybridExecutor):
     def _moe_reduce(self, h: torch.Tensor, part: torch.Tensor) -> None:
         """h += sum over ranks of the per-rank expert contributions ``part`` [T, hidden] fp32."""
         T = part.shape[0]
+        if self._sp_on(h):
+            # expert parallelism over the row-sharded residual: each rank's expert outputs are reduce-scattered to
+            # the rows' owners (peer stores of bf16 rows, fp32 sums)
+            self.sp.rows_rs(part, T)
+            return
         if self.peer is not None and T <= self.peer.max_rows and part.is_contiguous():
             self._sync_resid(h)
             self.peer.push_rows(part, T)
@@ -152,6 +157,11 @@ class TPHybridExecutor(HybridExecutor):
                 return GM.gemm_quant(x, w, out, self.scratch, row0=row0, rows=rows_, ag=self.sp.ag_args())
             self.sp.wait()
         return super()._gemm(x, w, out, row0=row0, rows=rows, tag=tag)
+
+    def _xn_ready(self) -> None:
+        """Readers of freshly pushed rows that are not the all-gather GEMM wait here (stream-ordered)."""
+        if self.sp is not None and self.sp.ag_pending:
+            self.sp.wait()
 
     def _finish_resid(self, h: torch.Tensor) -> torch.Tensor:
         if self._sp_on(h):

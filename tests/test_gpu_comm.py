@@ -309,3 +309,36 @@ def test_sequence_parallel_gemm_reduce_scatter_norm_allgather_emulated(world):
         assert torch.equal(group[q].h[:T], full)
     for gq in group:
         gq.close()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_rows_reduce_scatter_for_expert_parallel_combine_emulated(world):
+    """Token-ordered fp32 partial rows of every emulated rank are reduce-scattered into the row-sharded residual:
+    owned rows get h + sum over ranks (bf16 on the wire for remote rows), other rows stay untouched."""
+    from hipengine_b200.ops import kernels as K
+    from hipengine_b200.parallel.fused import SeqParallel
+    T, H = 450, 512
+    group = SeqParallel.emulated_group("cuda", H, world, max_rows=512)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    h0 = torch.randn(T, H, device="cuda", generator=g)
+    parts = [torch.randn(T, H, device="cuda", generator=g) for _ in range(world)]
+    for q in range(world):
+        group[q].h[:T].copy_(h0)
+    for ph in (1, 2):
+        for q in range(world):
+            group[q].rows_rs(parts[q], T, phases=ph)
+    torch.cuda.synchronize()
+    K.check_status()
+    for q in range(world):
+        own = torch.tensor(group[q].owned_rows(T), device="cuda", dtype=torch.long)
+        other = torch.ones(T, dtype=torch.bool, device="cuda")
+        other[own] = False
+        got = group[q].h[:T]
+        assert torch.equal(got[other], h0[other])
+        if own.numel():
+            want = h0[own].clone()
+            for r in range(world):
+                want += parts[r][own] if r == q else parts[r][own].bfloat16().float()
+            assert torch.allclose(got[own], want, atol=1e-5, rtol=1e-5)
+    for gq in group:
+        gq.close()
