@@ -34,6 +34,8 @@ class EngineLoop:
         self._fair_toggle = False
         self.ticks = 0
         self.recent_prefill: List[Dict[str, Any]] = []
+        # ranks of a parallel group take cancel / deadline decisions from rank 0 (see parallel/serving.py)
+        self.external_lifetimes = False
 
     # ------------------------------------------------------------------ front door
     def submit(self, req: GenerationRequest) -> RequestState:
@@ -58,7 +60,8 @@ class EngineLoop:
     def tick(self) -> int:
         """One scheduling round.  Returns the number of tokens (prompt + generated) processed."""
         self.ticks += 1
-        self._probe_lifetimes()
+        if not self.external_lifetimes:
+            self._probe_lifetimes()
         self.sched.admit_pending(self.runner.admit)
         for rs in self.sched.drain_rejected():
             self.on_event(rs)
@@ -90,6 +93,19 @@ class EngineLoop:
         return done
 
     # ------------------------------------------------------------------ phases
+    def expired(self) -> List[Tuple[int, str]]:
+        """(request id, reason) of every request whose cancellation token fired or whose deadline passed: what
+        ``_probe_lifetimes`` would cancel.  The leader of a parallel group turns these into broadcast commands."""
+        now = time.time()
+        out: List[Tuple[int, str]] = []
+        for rs in list(self.sched.active.values()) + list(self.sched.pending):
+            tok = rs.req.cancellation_token
+            if tok is not None and getattr(tok, "cancelled", False):
+                out.append((rs.rid, "cancelled"))
+            elif rs.req.deadline_at is not None and now >= rs.req.deadline_at:
+                out.append((rs.rid, "deadline_exceeded"))
+        return out
+
     def _probe_lifetimes(self) -> None:
         now = time.time()
         for rs in list(self.sched.active.values()) + list(self.sched.pending):

@@ -61,9 +61,14 @@ class _Command:
 
 
 class EngineService:
-    def __init__(self, loop: EngineLoop, config: EngineConfig, name: str = "he-engine-service"):
+    def __init__(self, loop: EngineLoop, config: EngineConfig, name: str = "he-engine-service", coordinator=None):
         self.loop = loop
         self.config = config
+        # parallel group: rank 0 publishes every tick's command batch, all ranks apply it (parallel/serving.py)
+        self.coord = coordinator
+        self.orphans: Dict[int, GenerationOutput] = {}      # follower: outputs finished before their caller arrived
+        if coordinator is not None:
+            self.loop.external_lifetimes = True
         self.commands: "queue.Queue[_Command]" = queue.Queue(maxsize=COMMAND_QUEUE_DEPTH)
         self.collectors: Dict[int, OutputCollector] = {}
         self.unhealthy: Optional[Dict[str, Any]] = None
@@ -209,6 +214,19 @@ class EngineService:
             self.collectors.pop(rs.rid, None)
             self.loop.sched.pop_finished(rs.rid)
 
+    def _on_event_follower(self, rs: RequestState) -> None:
+        """Follower ranks: deliver to a caller of the same request on this rank if there is one (SPMD use of the Python
+        API), otherwise keep the finished output for a short while in case the caller registers late."""
+        if rs.rid in self.collectors:
+            self._on_event(rs)
+            return
+        self.loop.sched.take_stream_tokens(rs)
+        if rs.status == FINISHED:
+            self.orphans[rs.rid] = self.loop.sched.make_output(rs)
+            self.loop.sched.pop_finished(rs.rid)
+            while len(self.orphans) > 256:
+                self.orphans.pop(next(iter(self.orphans)))
+
     def _serve(self, cmd: _Command) -> bool:
         """Returns False when the loop should stop."""
         try:
@@ -258,6 +276,12 @@ class EngineService:
             if dev is not None and getattr(dev, "type", "cpu") == "cuda" and dev.index is not None:
                 import torch
                 torch.cuda.set_device(dev)
+            if self.coord is not None:
+                if self.coord.is_leader:
+                    self._drive_leader()
+                else:
+                    self._drive_follower()
+                return
             while True:
                 drained = 0
                 while drained < 64:
@@ -274,6 +298,11 @@ class EngineService:
                     continue
                 self.loop.tick()
         except BaseException as exc:  # fatal: record, fail everything, stop
+            if self.coord is not None and self.coord.is_leader:
+                try:
+                    self.coord.publish({"cmds": [], "tick": False, "stop": True})   # never blocks on a follower
+                except Exception:
+                    pass
             tb = traceback.extract_tb(exc.__traceback__)
             loc = f"{tb[-1].filename}:{tb[-1].lineno}" if tb else "?"
             self.unhealthy = {"exception_type": type(exc).__name__, "message": str(exc), "location": loc,
@@ -291,6 +320,125 @@ class EngineService:
                                                         out.error))
                     col.finish(out)
             self.collectors.clear()
+
+
+    # ------------------------------------------------------------------ parallel group: leader / follower loops
+    _REPLICATED = ("submit", "cancel", "reset", "close")
+
+    def _apply_replicated(self, kind: str, payload) -> Any:
+        """The part of a command that every rank performs (device / scheduler state); returns its result."""
+        if kind == "submit":
+            return self.loop.submit(payload)
+        if kind == "cancel":
+            return self.loop.cancel(payload[0], payload[1])
+        if kind == "reset":
+            self.loop.fail_all("engine reset")
+            self.loop.runner.reset()
+            return None
+        if kind == "close":
+            self.loop.fail_all("engine closed")
+            self.loop.runner.close()
+            return None
+        raise ValueError(kind)
+
+    def _drive_leader(self) -> None:
+        from ..parallel.serving import portable_request
+        last_beat = time.time()
+        while True:
+            local: List[_Command] = []
+            while len(local) < 64:
+                try:
+                    local.append(self.commands.get_nowait())
+                except queue.Empty:
+                    break
+            wire: List[Tuple[str, Any]] = []
+            todo: List[Tuple[_Command, Any]] = []
+            for cmd in local:
+                if cmd.kind not in self._REPLICATED:
+                    self._serve(cmd)                      # snapshot / capacity: answered from rank 0's own state
+                elif cmd.kind == "submit":
+                    req, col = cmd.payload
+                    self.collectors[req.request_id] = col
+                    wire.append(("submit", portable_request(req)))
+                    todo.append((cmd, req))
+                else:
+                    wire.append((cmd.kind, cmd.payload))
+                    todo.append((cmd, cmd.payload))
+            expired = self.loop.expired()
+            for rid, reason in expired:
+                wire.append(("cancel", (rid, reason)))
+            self.coord.check_followers()      # a lost rank is found here, on the host, before the next launch
+            idle = self.loop.idle() and not wire
+            if idle:
+                if time.time() - last_beat > 1.0:          # heartbeat: followers learn that rank 0 is alive
+                    self.coord.publish({"cmds": [], "tick": False, "stop": False})
+                    last_beat = time.time()
+                self._wake.wait(timeout=0.05)
+                self._wake.clear()
+                continue
+            stop = any(k == "close" for k, _ in wire)
+            self.coord.publish({"cmds": wire, "tick": not stop, "stop": stop})
+            last_beat = time.time()
+            for cmd, payload in todo:
+                try:
+                    if cmd.kind == "submit":
+                        try:
+                            self.loop.submit(payload)
+                        except GenerationAdmissionRejected as exc:
+                            col = self.collectors.pop(payload.request_id, None)
+                            out = GenerationOutput(payload.request_id, list(payload.prompt_token_ids), [], None,
+                                                   FinishDetails("error", message=str(exc)), None, error=str(exc))
+                            if col is not None:
+                                col.put_chunk(GenerationStreamChunk(payload.request_id, [], None, True, out.finish,
+                                                                    None, None, str(exc)))
+                                col.finish(out)
+                        cmd.reply.put((True, None))
+                    else:
+                        cmd.reply.put((True, self._apply_replicated(cmd.kind, payload)))
+                except Exception as exc:
+                    try:
+                        cmd.reply.put_nowait((False, exc))
+                    except queue.Full:
+                        pass
+            for rid, reason in expired:
+                self.loop.cancel(rid, reason)
+            if stop:
+                return
+            self.loop.tick()
+
+    def _drive_follower(self) -> None:
+        self.loop.on_event = self._on_event_follower
+        while True:
+            # callers on this rank (SPMD use of the API) only register their collectors; rank 0's batch drives
+            while True:
+                try:
+                    cmd = self.commands.get_nowait()
+                except queue.Empty:
+                    break
+                if cmd.kind == "submit":
+                    req, col = cmd.payload
+                    done = self.orphans.pop(req.request_id, None)
+                    if done is not None:
+                        col.put_chunk(GenerationStreamChunk(req.request_id, list(done.token_ids), None, True,
+                                                            done.finish, None, done.telemetry, done.error))
+                        col.finish(done)
+                    else:
+                        self.collectors[req.request_id] = col
+                    cmd.reply.put((True, None))
+                elif cmd.kind in ("snapshot", "capacity"):
+                    self._serve(cmd)
+                else:
+                    cmd.reply.put((True, None))          # cancel / reset / close: decided by rank 0
+            batch = self.coord.receive()
+            for kind, payload in batch.get("cmds", []):
+                try:
+                    self._apply_replicated(kind, payload)
+                except GenerationAdmissionRejected:
+                    pass                                  # rank 0 rejected it too and told its caller
+            if batch.get("stop"):
+                return
+            if batch.get("tick"):
+                self.loop.tick()
 
 
 def build_engine(weights, backend: str, config: EngineConfig, tokenizer=None) -> EngineService:
@@ -320,11 +468,16 @@ def build_engine(weights, backend: str, config: EngineConfig, tokenizer=None) ->
         ex = TPHybridExecutor(weights.to(ctx.device), ctx, max_slots=n_slots + n_snap, max_context=max_ctx,
                               n_pages=n_pages)
         runner = GpuRunner(None, config, eos, executor=ex)
+        coord = None
+        if ctx.world > 1:
+            from ..parallel.serving import GroupCoordinator
+            coord = GroupCoordinator(ctx.rank, ctx.world)
+        return EngineService(EngineLoop(runner, config, tokenizer), config, coordinator=coord)
     else:
         from .gpu_runner import GpuRunner
         runner = GpuRunner(weights, config, eos)
     return EngineService(EngineLoop(runner, config, tokenizer), config)
 
 
-def engine_from_runner(runner, config: EngineConfig, tokenizer=None) -> EngineService:
-    return EngineService(EngineLoop(runner, config, tokenizer), config)
+def engine_from_runner(runner, config: EngineConfig, tokenizer=None, coordinator=None) -> EngineService:
+    return EngineService(EngineLoop(runner, config, tokenizer), config, coordinator=coordinator)

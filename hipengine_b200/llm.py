@@ -235,6 +235,14 @@ class LLM:
         info["prepare_seconds"] = time.time() - t0
         return info
 
+    def follow(self) -> None:
+        """Ranks other than 0 of a tensor/expert-parallel serving group: make the engine resident and execute the
+        command batches rank 0 publishes until it says stop (rank 0 owns HTTP, the scheduler and the sampler)."""
+        eng = self._get_engine()
+        if eng.coord is None or eng.coord.is_leader:
+            raise RuntimeError("follow() is for the non-zero ranks of a parallel serving group")
+        eng.thread.join()
+
     # ------------------------------------------------------------------ requests
     def _request(self, prompt: PromptLike, sp: SamplingParams, index: int) -> GenerationRequest:
         if isinstance(prompt, str):

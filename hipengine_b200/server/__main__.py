@@ -33,6 +33,9 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--request-timeout-ms", type=int, default=None)
     ap.add_argument("--stream-queue-max-chunks", type=int, default=16)
     ap.add_argument("--shutdown-grace-seconds", type=float, default=5.0)
+    ap.add_argument("--batch-window-ms", type=float, default=0.0,
+                    help="hold compatible requests up to this long so that they enter the engine together")
+    ap.add_argument("--max-batch-size", type=int, default=64, help="release a held group early at this size")
     ap.add_argument("--kv-storage", default="bf16", choices=["bf16"])
     ap.add_argument("--kv-pool-pages", type=int, default=None)
     ap.add_argument("--prefix-cache", default="radix", choices=["off", "radix"])
@@ -76,7 +79,8 @@ def configs_from_args(a):
                        api_key=a.api_key, chat_default_max_tokens=a.chat_default_max_tokens,
                        max_queued_requests=a.max_queued_requests, request_timeout_ms=a.request_timeout_ms,
                        stream_queue_max_chunks=a.stream_queue_max_chunks, metrics=a.metrics,
-                       max_chat_sessions=a.max_chat_sessions, shutdown_grace_seconds=a.shutdown_grace_seconds)
+                       max_chat_sessions=a.max_chat_sessions, shutdown_grace_seconds=a.shutdown_grace_seconds,
+                       batch_window_ms=a.batch_window_ms, max_batch_size=a.max_batch_size)
     srv.validate()
     return eng, srv
 
@@ -103,7 +107,15 @@ def main(argv: Optional[List[str]] = None) -> int:
               kv_cold_tier_bytes=int(a.kv_cold_tier_gib * (1 << 30)), kv_cold_tier_dir=a.kv_cold_tier_dir,
               tensor_parallel=a.tensor_parallel,
               expert_parallel=a.expert_parallel, engine_config=eng)
-    if a.eager_load or a.startup_chat_smoke:
+    import os
+    rank = int(os.environ.get("RANK", "0"))
+    if max(a.tensor_parallel, a.expert_parallel) > 1 and rank != 0:
+        # one HTTP server in front of the group: rank 0 serves, this rank follows its command batches
+        log.info("rank %d follows rank 0 (tensor_parallel=%d expert_parallel=%d)", rank, a.tensor_parallel,
+                 a.expert_parallel)
+        llm.follow()
+        return 0
+    if a.eager_load or a.startup_chat_smoke or max(a.tensor_parallel, a.expert_parallel) > 1:
         info = llm.prepare()
         log.info("LOAD_TIMING prepare=%.2fs capacity=%s", time.time() - t0, info)
     if a.startup_chat_smoke:

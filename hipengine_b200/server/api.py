@@ -45,6 +45,8 @@ class ServerConfig:
     max_chat_sessions: int = 256
     mtp_breaker_threshold: int = 3
     shutdown_grace_seconds: float = 5.0
+    batch_window_ms: float = 0.0             # hold compatible requests this long so they are released together
+    max_batch_size: int = 64                 # ... or until this many are waiting
 
     def validate(self) -> None:
         if self.max_queued_requests < 1:
@@ -91,27 +93,7 @@ class MTPCircuitBreaker:
                 "threshold": self.threshold}
 
 
-class GenerationGate:
-    """Bounded admission of HTTP requests to the engine (the role of ``_GenerationBatcher``): counts requests
-    in flight, refuses with 429 when the queue bound is hit, and drains on shutdown."""
-
-    def __init__(self, limit: int):
-        self.limit = limit
-        self.in_flight = 0
-        self.lock = threading.Lock()
-        self.closing = False
-
-    def enter(self) -> None:
-        with self.lock:
-            if self.closing:
-                raise APIError("engine_unavailable", "server is shutting down")
-            if self.in_flight >= self.limit:
-                raise APIError("engine_busy", f"{self.in_flight} requests already queued", retry_after=1.0)
-            self.in_flight += 1
-
-    def leave(self) -> None:
-        with self.lock:
-            self.in_flight = max(0, self.in_flight - 1)
+from .batcher import GenerationBatcher  # noqa: E402
 
 
 def _lp_chat(lps: Optional[List[TokenLogprob]], tok) -> Optional[Dict[str, Any]]:
@@ -190,7 +172,7 @@ def create_app(llm: LLM, config: Optional[ServerConfig] = None) -> FastAPI:
     cfg = config or ServerConfig()
     cfg.validate()
     metrics = ServerMetrics()
-    gate = GenerationGate(cfg.max_queued_requests)
+    gate = GenerationBatcher(cfg.max_queued_requests, cfg.batch_window_ms, cfg.max_batch_size)
 
     from contextlib import asynccontextmanager
 
@@ -198,7 +180,7 @@ def create_app(llm: LLM, config: Optional[ServerConfig] = None) -> FastAPI:
     async def lifespan(_app):
         yield
         # drain: refuse new work, give requests in flight a grace period, then close the engine
-        gate.closing = True
+        gate.drain()
         deadline = time.time() + cfg.shutdown_grace_seconds
         while gate.in_flight > 0 and time.time() < deadline:
             await asyncio.sleep(0.05)
@@ -278,6 +260,7 @@ def create_app(llm: LLM, config: Optional[ServerConfig] = None) -> FastAPI:
         h = llm.engine_service_health()
         body: Dict[str, Any] = {"ready": bool(h.get("healthy", True)), "engine": h, "model": cfg.served_model_name,
                                 "queue": {"in_flight": gate.in_flight, "limit": gate.limit},
+                                "batcher": gate.snapshot(),
                                 "parallelism": {"world_size": llm.config.parallel.tp * llm.config.parallel.ep,
                                                 "tensor_parallel": llm.config.parallel.tp,
                                                 "expert_parallel": llm.config.parallel.ep},
@@ -380,6 +363,12 @@ def create_app(llm: LLM, config: Optional[ServerConfig] = None) -> FastAPI:
         prompts = _prompts(req)
         cid, created = SE.new_id("cmpl"), int(time.time())
         gate.enter()
+        try:
+            await gate.admit(gate.compat_key("completions", bool(req.stream), sp.temperature == 0.0, bool(sp.logprobs),
+                                             bool(getattr(sp, "json_schema", None) or getattr(sp, "grammar", None))))
+        except BaseException:
+            gate.leave()
+            raise
         metrics.inc("he_http_requests_total", route="completions")
         live = req.stream and len(prompts) == 1 and req.n == 1 and not req.echo
         if live:
@@ -484,6 +473,12 @@ def create_app(llm: LLM, config: Optional[ServerConfig] = None) -> FastAPI:
             sp = replace(sp, speculative_mtp=False)
         cid, created = SE.new_id("chatcmpl"), int(time.time())
         gate.enter()
+        try:
+            await gate.admit(gate.compat_key("chat", bool(req.stream), sp.temperature == 0.0, bool(sp.logprobs),
+                                             bool(getattr(sp, "json_schema", None) or getattr(sp, "grammar", None))))
+        except BaseException:
+            gate.leave()
+            raise
         metrics.inc("he_http_requests_total", route="chat")
 
         def finish_session(msg: Dict[str, Any]) -> Optional[str]:

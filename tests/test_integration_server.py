@@ -146,3 +146,51 @@ def test_sessions_and_tokenize_and_metrics(client):
     assert "he_engine_decode_tokens_total" in m and "he_http_requests_total" in m
     caps = client.get("/v1/hipengine/capabilities").json()
     assert caps["features"]["tools"] and caps["limits"]["top_logprobs"] == 20
+
+
+def test_generation_batcher_groups_compatible_requests_within_the_window():
+    """Requests of one compatibility class that arrive inside the batch window are released together; another class
+    gets its own release; a full group is released at once; drain releases what is held."""
+    import asyncio
+    from hipengine_b200.server.batcher import GenerationBatcher
+    from hipengine_b200.server.errors import APIError
+
+    async def run():
+        b = GenerationBatcher(limit=8, window_ms=80.0, max_batch=3)
+        k_greedy = b.compat_key("chat", False, True, False, False)
+        k_sampled = b.compat_key("chat", False, False, False, False)
+        released = []
+
+        async def one(name, key, delay):
+            await asyncio.sleep(delay)
+            b.enter()
+            await b.admit(key)
+            released.append((name, round(asyncio.get_running_loop().time(), 2)))
+            b.leave()
+
+        t0 = asyncio.get_running_loop().time()
+        await asyncio.gather(one("a", k_greedy, 0.0), one("b", k_greedy, 0.02), one("s", k_sampled, 0.03))
+        times = dict(released)
+        assert abs(times["a"] - times["b"]) < 0.02 and times["a"] - t0 >= 0.07        # held, released together
+        assert times["s"] - t0 >= 0.10                                                  # its own window
+        snap = b.snapshot()
+        assert snap["batches"] == 2 and snap["max_batch_seen"] == 2 and snap["flush_window"] == 2
+        # a full group does not wait for the window
+        t1 = asyncio.get_running_loop().time()
+        await asyncio.gather(*[one(f"f{i}", k_greedy, 0.0) for i in range(3)])
+        assert asyncio.get_running_loop().time() - t1 < 0.05 and b.snapshot()["flush_full"] == 1
+        # bound + drain
+        for _ in range(8):
+            b.enter()
+        try:
+            b.enter()
+            raise AssertionError("expected engine_busy")
+        except APIError as exc:
+            assert exc.code == "engine_busy"
+        held = asyncio.ensure_future(b.admit(k_greedy))
+        await asyncio.sleep(0.01)
+        b.drain()
+        await asyncio.wait_for(held, 0.5)
+        assert b.snapshot()["flush_drain"] == 1 and b.closing
+
+    asyncio.run(run())
