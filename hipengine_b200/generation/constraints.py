@@ -171,6 +171,9 @@ class ToolCallConstraintSpec:
     mode: str = "auto"            # auto | required | specific
     specific: Optional[str] = None
     allow_think_prefix: bool = True
+    # tool definitions (JSON text of the OpenAI "tools" list): when present and the mode demands a call (required /
+    # specific), token masks from the in-tree grammar matcher enforce the call format while it is generated
+    tools_json: Optional[str] = None
 
 
 class ToolCallConstraintState:

@@ -30,6 +30,7 @@ class EngineLoop:
         enc = tokenizer.encode if tokenizer is not None else None
         self.sched = Scheduler(min(sc.max_active_requests, runner.max_slots), sc.max_pending_requests,
                                runner.eos_token_id, dec, enc)
+        self.sched.tokenizer = tokenizer
         self.on_event: Callable[[RequestState], None] = lambda rs: None
         self._fair_toggle = False
         self.ticks = 0

@@ -57,15 +57,22 @@ class BaseRunner:
             b = rs.thinking.close_bias()
             if b > 0 and rs.thinking.close_ids:
                 bias.append((rs.thinking.close_ids[0], b))
+        mask = None
+        if rs.grammar is not None and not rs.grammar.dead() and not (rs.thinking is not None and rs.thinking.thinking):
+            mask = rs.grammar.allowed_mask()
+            if mask.shape[0] != self.vocab:       # tokenizer and model vocabularies may differ in padding
+                full = torch.zeros(self.vocab, dtype=torch.bool)
+                full[:min(self.vocab, mask.shape[0])] = mask[:self.vocab]
+                mask = full
         return dict(logit_bias=bias, history=rs.generated, prompt=req.prompt_token_ids,
                     repetition_penalty=req.repetition_penalty, presence_penalty=req.presence_penalty,
-                    frequency_penalty=req.frequency_penalty, suppress=suppress)
+                    frequency_penalty=req.frequency_penalty, suppress=suppress, allowed_mask=mask)
 
     def _needs_processing(self, rs: RequestState) -> bool:
         req = rs.req
         return bool(req.logit_bias or req.suppress_token_ids or req.repetition_penalty != 1.0
                     or req.presence_penalty != 0.0 or req.frequency_penalty != 0.0
-                    or len(rs.generated) < req.min_tokens
+                    or len(rs.generated) < req.min_tokens or rs.grammar is not None
                     or (rs.thinking is not None and (rs.thinking.suppress_eos() or rs.thinking.close_bias() > 0)))
 
     def sample_host(self, rs: RequestState, logits: torch.Tensor) -> Tuple[int, Optional[TokenLogprob]]:

@@ -45,6 +45,7 @@ class RequestState:
     json_state: Optional[JsonObjectConstraintState] = None
     thinking: Optional[ThinkingBudgetState] = None
     tool_state: Optional[ToolCallConstraintState] = None
+    grammar: Any = None          # token-mask matcher of the tool-call grammar (generation/grammar.py), when enforced
     t_submit: float = field(default_factory=time.perf_counter)
     t_admit: float = 0.0
     t_first: float = 0.0
@@ -103,6 +104,7 @@ class Scheduler:
         self.max_pending = max_pending
         self.eos_token_id = eos_token_id
         self.decode_text = decode
+        self.tokenizer = None        # set by the engine loop: the grammar matcher needs the whole vocabulary
         self.encode_text = encode
         self.pending: Deque[RequestState] = deque()
         self.active: Dict[int, RequestState] = {}
@@ -139,6 +141,18 @@ class Scheduler:
             rs.json_state = JsonObjectConstraintState(self.decode_text, self.encode_text)
         if req.tool_call_constraint is not None and self.decode_text:
             rs.tool_state = ToolCallConstraintState(req.tool_call_constraint, self.decode_text)
+            spec = req.tool_call_constraint
+            if getattr(spec, "tools_json", None) and self.tokenizer is not None:
+                import json as _json
+                from .grammar import tool_call_matcher
+                try:
+                    rs.grammar = tool_call_matcher(
+                        _json.loads(spec.tools_json), self.tokenizer,
+                        req.eos_token_id if req.eos_token_id is not None else self.eos_token_id,
+                        allow_text_before=True, parallel=True,
+                        only=spec.specific if spec.mode == "specific" else None)
+                except ValueError:
+                    rs.grammar = None        # names the grammar cannot express: post-validation still applies
         self.pending.append(rs)
         self.counters["submitted"] += 1
         return rs
@@ -232,6 +246,7 @@ class Scheduler:
             rs.logprobs.append(logprob)
         self.counters["decode_tokens"] += 1
         req = rs.req
+        was_thinking = rs.thinking is not None and rs.thinking.thinking
         if rs.thinking is not None:
             rs.thinking.push(token)
             if rs.thinking.must_force_close():
@@ -240,6 +255,8 @@ class Scheduler:
             rs.json_state.push(token)
         if rs.tool_state is not None:
             rs.tool_state.push(token)
+        if rs.grammar is not None and not was_thinking:
+            rs.grammar.accept(token)          # the thinking block (and the token that closes it) is outside the grammar
         n = len(rs.generated)
         eos = req.eos_token_id if req.eos_token_id is not None else self.eos_token_id
         if n >= req.min_tokens:

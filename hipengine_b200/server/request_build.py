@@ -150,7 +150,12 @@ def build_chat(req: ChatCompletionRequest, tokenizer, arch: str, default_max: in
         if plan.tool_mode == "none":
             tools = None
         else:
-            constraint = ToolCallConstraintSpec(tuple(plan.tools), plan.tool_mode, plan.tool_specific)
+            import json as _json
+            strict = plan.tool_mode in ("required", "specific")
+            constraint = ToolCallConstraintSpec(
+                tuple(plan.tools), plan.tool_mode, plan.tool_specific,
+                tools_json=_json.dumps([t.model_dump() if hasattr(t, "model_dump") else t for t in req.tools])
+                if strict else None)
     elif req.tool_choice not in (None, "none", "auto"):
         raise APIError("unsupported_parameter", "tool_choice requires tools", "tool_choice")
 

@@ -132,3 +132,36 @@ def test_hybrid_model_through_the_engine():
         assert h["healthy"] and h["driver_alive"]
         snap = llm.live_loop_snapshot()
         assert snap["counters"]["finished"] >= 3
+
+
+def test_required_tool_call_is_grammar_constrained_token_by_token():
+    """With a tool choice that demands a call, the in-tree grammar matcher masks the logits of every step: a random
+    model (which would emit noise) produces text that is at every point a prefix of a well-formed tool call."""
+    import json
+    from hipengine_b200 import LLM, SamplingParams
+    from hipengine_b200.generation.constraints import ToolCallConstraintSpec
+    from hipengine_b200.generation.grammar import ToolCallAutomaton
+    from hipengine_b200.loading.synth import build_random_model
+    from hipengine_b200.models.config import TINY_DENSE
+    tools = [{"type": "function", "function": {"name": "lookup", "parameters": {
+        "type": "object", "properties": {"n": {"type": "integer"}, "flag": {"type": "boolean"}},
+        "required": ["n", "flag"]}}}]
+    llm = LLM(build_random_model(TINY_DENSE, seed=4, std=0.05), backend="cpu_reference", max_active_requests=2,
+              max_sequence_length=256)
+    try:
+        spec = ToolCallConstraintSpec(("lookup",), "required", None, tools_json=json.dumps(tools))
+        sp = SamplingParams(max_tokens=96, temperature=0.8, seed=7, tool_call_constraint=spec)
+        out = llm.generate_detailed(llm.tokenize("call the tool"), sp)[0]
+        text = llm._get_tokenizer().decode(out.token_ids)
+        auto = ToolCallAutomaton(tools)
+        s = auto.start_set
+        for ch in text:
+            s = auto.step(s, ch)
+            assert s is not None, text          # never leaves the grammar
+        free = SamplingParams(max_tokens=24, temperature=0.8, seed=7)
+        noise = llm._get_tokenizer().decode(llm.generate_detailed(llm.tokenize("call the tool"), free)[0].token_ids)
+        assert noise != text[:len(noise)]
+        if out.finish.reason in ("stop_eos", "stop"):
+            assert auto.accepting(s)
+    finally:
+        llm.close()

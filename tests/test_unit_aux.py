@@ -243,3 +243,50 @@ def test_radix_eviction_is_strict_lru_across_newly_exposed_leaves():
     assert radix.match(fresh + [1]).tokens == 16
     assert radix.match(old + [1]).tokens == 0
     pool.assert_conserved()
+
+
+def test_in_tree_tool_call_grammar_matcher():
+    """The automaton compiled from a tool list accepts exactly well-formed calls, token masks follow it through a
+    toy vocabulary, and end-of-sequence is allowed only on a complete match."""
+    import torch
+    from hipengine_b200.generation.grammar import ToolCallAutomaton, ToolCallMatcher
+    tools = [{"type": "function", "function": {"name": "get_weather", "parameters": {
+        "type": "object", "properties": {"city": {"type": "string"}, "days": {"type": "integer"},
+                                         "unit": {"enum": ["c", "f"]}}, "required": ["city"]}}},
+             {"type": "function", "function": {"name": "stop", "parameters": {"type": "object", "properties": {}}}}]
+    auto = ToolCallAutomaton(tools)
+
+    def accepts(text):
+        s = auto.start_set
+        for ch in text:
+            s = auto.step(s, ch)
+            if s is None:
+                return False
+        return auto.accepting(s)
+
+    good = "Let me check.<tool_call>\n<function=get_weather><parameter=city>Oslo</parameter><parameter=days>3" \
+           "</parameter></function>\n</tool_call>"
+    assert accepts(good)
+    assert accepts(good + "\n<tool_call><function=stop></function></tool_call>")          # parallel calls
+    assert accepts("<tool_call><function=get_weather><parameter=city>X</parameter><parameter=unit>f</parameter>"
+                   "</function></tool_call>")
+    assert not accepts(good.replace("get_weather", "get_wether"))                           # unknown function
+    assert not accepts(good.replace("<parameter=city>Oslo</parameter>", ""))                # required one missing
+    assert not accepts(good.replace(">3<", ">three<"))                                      # integer expected
+    assert not accepts(good[:-3])                                                           # incomplete
+    vocab = ["<eos>", "<tool_call>", "<function=", "get_weather", "stop", ">", "<parameter=", "city", "days",
+             "Oslo", "</parameter>", "</function>", "</tool_call>", "3", "x", "\n", "get_", "weather", "<", "/"]
+    m = ToolCallMatcher(ToolCallAutomaton(tools, allow_text_before=False), vocab, eos_token_id=0)
+    toks = lambda names: [vocab.index(n) for n in names]
+    mask = m.allowed_mask()
+    assert mask[vocab.index("<tool_call>")] and mask[vocab.index("<")] and not mask[vocab.index("x")] and not mask[0]
+    for t in toks(["<tool_call>", "<function=", "get_", "weather", ">", "<parameter=", "city", ">", "Oslo",
+                   "</parameter>"]):
+        assert m.allowed_mask()[t], vocab[t]
+        assert m.accept(t)
+    mask = m.allowed_mask()
+    assert mask[vocab.index("<parameter=")] and mask[vocab.index("</function>")] and not mask[vocab.index("Oslo")]
+    for t in toks(["</function>", "</tool_call>"]):
+        assert m.accept(t)
+    assert m.finished() and m.allowed_mask()[0]                 # end-of-sequence now allowed
+    assert isinstance(m.allowed_mask(), torch.Tensor) and not m.accept(vocab.index("x")) and m.dead()
