@@ -103,7 +103,7 @@ __device__ __forceinline__ void quant_store(const SmemView& s, int K, int r, int
 
 // (optional RMSNorm) + per-32 int8 quantisation.  With a norm and K <= 8192 the row is read once and kept in
 // registers between the statistics and the quantisation.
-template <int R>
+template <int R, bool COMM>
 __device__ void prologue(const HeGemvArgs& a, const SmemView& s, float* red) {
   const int K = a.K;
   const int n_groups = K / 8;
@@ -112,7 +112,7 @@ __device__ void prologue(const HeGemvArgs& a, const SmemView& s, float* red) {
   const bool one_pass = a.norm_w != nullptr && n_groups <= MAXG * nthr;
   // reduce mode (the launcher admits it only with the one-pass prologue and fp32 rows): the rows are the residual
   // stream, to which the partial rows pushed by every rank are added before anything else happens
-  const bool rin = (a.comm.mode & 2) != 0;
+  const bool rin = COMM && (a.comm.mode & 2) != 0;
   __shared__ int last_cta_s;
   uint32_t rin_tag = 0;
   int parity = 0;
@@ -303,7 +303,9 @@ struct Cursor {
   int left;     // units still to visit
 };
 
-template <int R, int NW>
+// COMM = false compiles the tensor-parallel push / reduce paths out (the single-GPU kernel carries none of their
+// registers or branches).
+template <int R, int NW, bool COMM>
 __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const __grid_constant__ HeGemvArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ float red[33];
@@ -387,7 +389,7 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const __grid_constant_
   for (int i = 0; i < a.n_slots - 1; ++i) issue();
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
-  const bool push = (a.comm.mode & 1) != 0;
+  const bool push = COMM && (a.comm.mode & 1) != 0;
   uint32_t push_seq = 0;
   size_t push_off = 0;                 // float offset of slot (parity, my rank) inside a receive region
   if (push) {
@@ -399,7 +401,7 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const __grid_constant_
     for (int q = 0; q < a.comm.world; ++q) ll_store(a.comm.recv[q] + off, v, push_seq + 1u);
   };
 
-  prologue<R>(a, s, red);
+  prologue<R, COMM>(a, s, red);
 
   const int t_row = lane >> bq_shift, bq = lane & (BQ - 1);
   float acc[R];
@@ -498,13 +500,13 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const __grid_constant_
   }
 }
 
-template <int R, int NW>
-int launch_nw(const HeGemvArgs& a, size_t smem, long long items, int num_sms, cudaStream_t stream) {
+template <int R, int NW, bool COMM>
+int launch_nw_c(const HeGemvArgs& a, size_t smem, long long items, int num_sms, cudaStream_t stream) {
   static size_t configured[64] = {};   // per device: the attribute belongs to the (function, device) pair
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
   if (smem > configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemv_kernel<R, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(gemv_kernel<R, NW, COMM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured[dev] = smem;
   }
@@ -527,9 +529,15 @@ int launch_nw(const HeGemvArgs& a, size_t smem, long long items, int num_sms, cu
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 1 : 0;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_kernel<R, NW>, a);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_kernel<R, NW, COMM>, a);
   if (e != cudaSuccess) return (int)e;
   return 0;
+}
+
+template <int R, int NW>
+int launch_nw(const HeGemvArgs& a, size_t smem, long long items, int num_sms, cudaStream_t stream) {
+  if (a.comm.mode != 0) return launch_nw_c<R, NW, true>(a, smem, items, num_sms, stream);
+  return launch_nw_c<R, NW, false>(a, smem, items, num_sms, stream);
 }
 
 template <int R>

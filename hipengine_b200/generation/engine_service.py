@@ -185,7 +185,11 @@ class EngineService:
         if self.closed:
             return
         try:
-            self._call("close")
+            if self.coord is not None and not self.coord.is_leader:
+                # a follower's engine is stopped by rank 0's stop batch; wait for it instead of asking
+                self.thread.join(timeout=self.config.command_timeout_seconds)
+            elif self.thread.is_alive():
+                self._call("close")
         except Exception:
             pass
         self.closed = True
@@ -436,6 +440,17 @@ class EngineService:
                 except GenerationAdmissionRejected:
                     pass                                  # rank 0 rejected it too and told its caller
             if batch.get("stop"):
+                # answer whatever this rank's own callers queued meanwhile (their close() waits for a reply)
+                while True:
+                    try:
+                        cmd = self.commands.get_nowait()
+                    except queue.Empty:
+                        break
+                    try:
+                        cmd.reply.put_nowait((True, None))
+                    except queue.Full:
+                        pass
+                self.stopped_by_leader = True
                 return
             if batch.get("tick"):
                 self.loop.tick()

@@ -500,7 +500,10 @@ class GpuRunner(BaseRunner):
                 "free_slots": len(self.free_slots), "kv_pool": self.pool.snapshot(),
                 "prefix_cache": self.radix.snapshot_stats(), "state_bytes": self.ex.state_bytes(),
                 "kv_bytes_per_token": self.cfg.kv_bytes_per_token(),
-                "recurrent_state_bytes_per_request": self.cfg.recurrent_state_bytes()}
+                "recurrent_state_bytes_per_request": self.cfg.recurrent_state_bytes(),
+                # resident weight bytes: the quantised device layouts (there is no widened copy of any of them)
+                "weight_bytes": sum(w.data.numel() * w.data.element_size() for w in
+                                    {id(w): w for w in self.ex.dw.values()}.values())}
 
     def snapshot(self) -> Dict[str, Any]:
         return {"pool": self.pool.snapshot(), "prefix": self.radix.snapshot_stats(), "graphs": dict(self.graphs.stats, kernels_per_graph=None),

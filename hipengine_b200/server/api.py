@@ -206,7 +206,7 @@ def create_app(llm: LLM, config: Optional[ServerConfig] = None) -> FastAPI:
     @app.exception_handler(APIError)
     async def _api_error(_: Request, exc: APIError):
         headers = {"Retry-After": str(int(max(1, exc.retry_after)))} if exc.retry_after else None
-        metrics.inc("he_http_errors_total", code=exc.code)
+        metrics.inc("hipengine_http_errors_total", code=exc.code)
         return JSONResponse(exc.body(), status_code=exc.status, headers=headers)
 
     @app.exception_handler(SessionError)
@@ -291,7 +291,7 @@ def create_app(llm: LLM, config: Optional[ServerConfig] = None) -> FastAPI:
                 cap = await run_blocking(llm.resident_capacity_estimate)
             except Exception:
                 pass
-        return PlainTextResponse(metrics.render(snap, cap, gate.in_flight), media_type="text/plain; version=0.0.4")
+        return PlainTextResponse(metrics.render(snap, cap, gate.in_flight, gate.snapshot()), media_type="text/plain; version=0.0.4")
 
     @app.get("/v1/hipengine/capabilities", dependencies=[Depends(auth)])
     async def capabilities():
@@ -369,7 +369,7 @@ def create_app(llm: LLM, config: Optional[ServerConfig] = None) -> FastAPI:
         except BaseException:
             gate.leave()
             raise
-        metrics.inc("he_http_requests_total", route="completions")
+        metrics.inc("hipengine_requests_total", route="completions")
         live = req.stream and len(prompts) == 1 and req.n == 1 and not req.echo
         if live:
             greq = llm._request(prompts[0], sp, 0)
@@ -406,7 +406,7 @@ def create_app(llm: LLM, config: Optional[ServerConfig] = None) -> FastAPI:
                 finally:
                     bridge.close()
                     gate.leave()
-                    metrics.inc("he_generated_tokens_total", n_out)
+                    metrics.inc("hipengine_generated_tokens_total", n_out)
             return StreamingResponse(gen(), media_type="text/event-stream")
         try:
             plist = [p for p in prompts for _ in range(req.n)]
@@ -423,7 +423,7 @@ def create_app(llm: LLM, config: Optional[ServerConfig] = None) -> FastAPI:
                 text = (p if isinstance(p, str) else t.decode(p)) + text
             choices.append({"index": i, "text": text, "finish_reason": o.finish_reason,
                             "logprobs": _lp_completion(o.logprobs, t)})
-        metrics.inc("he_generated_tokens_total", sum(len(o.token_ids) for o in outs))
+        metrics.inc("hipengine_generated_tokens_total", sum(len(o.token_ids) for o in outs))
         body = {"id": cid, "object": "text_completion", "created": created, "model": cfg.served_model_name,
                 "choices": choices, "usage": _usage(outs)}
         if req.stream:   # buffered SSE for multi-prompt / n>1 / echo
@@ -479,7 +479,7 @@ def create_app(llm: LLM, config: Optional[ServerConfig] = None) -> FastAPI:
         except BaseException:
             gate.leave()
             raise
-        metrics.inc("he_http_requests_total", route="chat")
+        metrics.inc("hipengine_requests_total", route="chat")
 
         def finish_session(msg: Dict[str, Any]) -> Optional[str]:
             if sid is not None:
@@ -561,7 +561,7 @@ def create_app(llm: LLM, config: Optional[ServerConfig] = None) -> FastAPI:
                 finally:
                     bridge.close()
                     gate.leave()
-                    metrics.inc("he_generated_tokens_total", n_out)
+                    metrics.inc("hipengine_generated_tokens_total", n_out)
             return StreamingResponse(gen(), media_type="text/event-stream")
 
         try:
@@ -583,7 +583,7 @@ def create_app(llm: LLM, config: Optional[ServerConfig] = None) -> FastAPI:
             choices.append(choice)
             if sp.speculative_mtp:
                 breaker.record(cfg.served_model_name, len(prompt_ids), ok=True)
-        metrics.inc("he_generated_tokens_total", sum(len(o.token_ids) for o in outs))
+        metrics.inc("hipengine_generated_tokens_total", sum(len(o.token_ids) for o in outs))
         body = {"id": cid, "object": "chat.completion", "created": created, "model": cfg.served_model_name,
                 "choices": choices, "usage": _usage(outs)}
         new_sid = finish_session(choices[0]["message"])

@@ -143,7 +143,8 @@ def test_sessions_and_tokenize_and_metrics(client):
     assert client.post("/v1/hipengine/detokenize", json={"tokens": t["tokens"]}).json()["text"] == "abc"
     assert client.post("/v1/hipengine/fit_context", json={"text": "abc"}).json()["fits"]
     m = client.get("/metrics").text
-    assert "he_engine_decode_tokens_total" in m and "he_http_requests_total" in m
+    assert "hipengine_completion_tokens_total" in m and "hipengine_requests_total" in m
+    assert "hipengine_generation_queue_depth" in m and "hipengine_request_completed_total" in m
     caps = client.get("/v1/hipengine/capabilities").json()
     assert caps["features"]["tools"] and caps["limits"]["top_logprobs"] == 20
 
