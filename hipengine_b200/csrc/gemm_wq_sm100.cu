@@ -19,6 +19,7 @@
 // Counterparts in the reference: hipengine/kernels/hip_gfx1100/quant/gguf_q4_k_prefill.hip:170-296 (raw 144-byte
 // blocks read inside the matrix-core loop), gguf_q8_0_prefill.hip, and the grouped expert form
 // quant/gguf_q4_k_selected_prefill.hip.
+#include <cstdlib>
 #include "common.cuh"
 #include "sm100.cuh"
 
@@ -51,6 +52,7 @@ struct WqArgs {
   int k_splits;             // >= 1
   int sb_per;               // super-blocks (256 columns) per split
   long long split_stride;   // epi 4: split ks stores at C + ks * split_stride
+  int pair;                 // 1: a work unit is one weight tile against two neighbouring M-tiles (see TileCoord)
   const int* tile_group;    // grouped mode: M-tile tm uses weight rows [tile_group[tm] * N, +N); < 0 skips the tile
   int* status;
   // ring geometry, set by the launcher: few activation rows leave room for a deep raw-block ring, which is what
@@ -129,21 +131,35 @@ __device__ __forceinline__ uint32_t prmt_b32(uint32_t a, uint32_t b, uint32_t se
 }
 __device__ __forceinline__ uint32_t bits_bf162(__nv_bfloat162 v) { return *reinterpret_cast<uint32_t*>(&v); }
 
-// Four small unsigned integers (< 128), one per byte of `b4`, become two bf16x2 registers holding
-// bf16(q * s + off) with a single rounding.  A byte (0x80 | q) placed under the exponent byte 0x3F is the fp32 number
-// 1 + q / 128 exactly, so the integer reaches fp32 with one byte permute; then one fp32 FMA,
-//     (1 + q / 128) * (128 s) + (off - 128 s) = q * s + off,
-// and one packing conversion per pair.  `s128` = 128 * s and `c` = off - 128 * s are per sub-block constants.  The
-// result equals the reference dequantisation (fp32) rounded once to bf16.
-__device__ __forceinline__ void bytes4_to_bf16(uint32_t b4, float s128, float c, uint32_t& o01, uint32_t& o23) {
-  const uint32_t q8 = b4 | 0x80808080u;
-  const float f0 = fmaf(__uint_as_float(prmt_b32(q8, 0x3Fu, 0x4055u)), s128, c);
-  const float f1 = fmaf(__uint_as_float(prmt_b32(q8, 0x3Fu, 0x4155u)), s128, c);
-  const float f2 = fmaf(__uint_as_float(prmt_b32(q8, 0x3Fu, 0x4255u)), s128, c);
-  const float f3 = fmaf(__uint_as_float(prmt_b32(q8, 0x3Fu, 0x4355u)), s128, c);
-  o01 = bits_bf162(__floats2bfloat162_rn(f0, f1));
-  o23 = bits_bf162(__floats2bfloat162_rn(f2, f3));
+// Packed fp32 pair helpers: sm_100 issues two fp32 FMAs as one instruction on a 64-bit register pair.
+__device__ __forceinline__ uint64_t pack_f2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
 }
+__device__ __forceinline__ uint32_t fma2_to_bf162(__half2 v, uint64_t s2, uint64_t c2) {
+  const float2 f = __half22float2(v);
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(pack_f2(f.x, f.y)), "l"(s2), "l"(c2));
+  float d0, d1;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(d0), "=f"(d1) : "l"(d));
+  return bits_bf162(__floats2bfloat162_rn(d0, d1));
+}
+
+// Four unsigned bytes v of `b4` become two bf16x2 registers holding bf16(v * s + off) with a single rounding.  A byte
+// under the high byte 0x64 is the fp16 number 1024 + v exactly, so ONE byte permute makes two operands; the
+// half -> float conversions and the FMAs run on the FMA pipe, which leaves the integer pipe (the busier one here) with
+// one instruction per pair and one packing conversion per pair:
+//     (1024 + v) * s + (off - 1024 s) = v * s + off.
+// `s2` = (s, s) and `c2` = (off - 1024 s) twice are per sub-block constants.  The sum is exact in fp32 up to the
+// rounding of the constant (2^-14 s), so the result is the reference dequantisation (fp32) rounded once to bf16.
+__device__ __forceinline__ void bytes4_to_bf16(uint32_t b4, uint64_t s2, uint64_t c2, uint32_t& o01, uint32_t& o23) {
+  const uint32_t MAGIC = 0x64646464u;
+  const uint32_t p0 = prmt_b32(b4, MAGIC, 0x5140u), p1 = prmt_b32(b4, MAGIC, 0x7362u);
+  o01 = fma2_to_bf162(*reinterpret_cast<const __half2*>(&p0), s2, c2);
+  o23 = fma2_to_bf162(*reinterpret_cast<const __half2*>(&p1), s2, c2);
+}
+__device__ __forceinline__ uint64_t dup_f2(float v) { return pack_f2(v, v); }
 
 // Q4_K, k-block c (0..3) of the super-block at `blk` (144 bytes): the 32 nibble bytes [16 + 32c, +32); low
 // nibbles are columns 0..31 (sub-block 2c), high nibbles columns 32..63 (sub-block 2c+1).  r[j] = columns 2j, 2j+1.
@@ -158,8 +174,11 @@ __device__ __forceinline__ void unpack_q4k(const uint8_t* blk, int c, uint32_t (
     scw = ((meta.w & 0x0F0F0F0Fu) | ((meta.y >> 2) & 0x30303030u)) >> (16 * (c - 2));
     mnw = (((meta.w >> 4) & 0x0F0F0F0Fu) | ((meta.z >> 2) & 0x30303030u)) >> (16 * (c - 2));
   }
-  const float s_lo = 128.f * dd.x * (float)(scw & 0xFFu), s_hi = 128.f * dd.x * (float)((scw >> 8) & 0xFFu);
-  const float c_lo = -dd.y * (float)(mnw & 0xFFu) - s_lo, c_hi = -dd.y * (float)((mnw >> 8) & 0xFFu) - s_hi;
+  // high nibbles are used in place (byte = 16 q): their scale is s / 16, exact
+  const float s_lo = dd.x * (float)(scw & 0xFFu), s_hi = 0.0625f * dd.x * (float)((scw >> 8) & 0xFFu);
+  const uint64_t s2_lo = dup_f2(s_lo), s2_hi = dup_f2(s_hi);
+  const uint64_t c2_lo = dup_f2(-dd.y * (float)(mnw & 0xFFu) - 1024.f * s_lo);
+  const uint64_t c2_hi = dup_f2(-dd.y * (float)((mnw >> 8) & 0xFFu) - 1024.f * s_hi);
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
     const uint4 qv = *reinterpret_cast<const uint4*>(blk + 16 + 32 * c + 16 * half);
@@ -167,8 +186,8 @@ __device__ __forceinline__ void unpack_q4k(const uint8_t* blk, int c, uint32_t (
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       // word i of this half holds columns 16*half + 4i .. +3 (low nibbles) and 32 + the same (high nibbles)
-      bytes4_to_bf16(w[i] & 0x0F0F0F0Fu, s_lo, c_lo, r[8 * half + 2 * i], r[8 * half + 2 * i + 1]);
-      bytes4_to_bf16((w[i] >> 4) & 0x0F0F0F0Fu, s_hi, c_hi, r[16 + 8 * half + 2 * i], r[16 + 8 * half + 2 * i + 1]);
+      bytes4_to_bf16(w[i] & 0x0F0F0F0Fu, s2_lo, c2_lo, r[8 * half + 2 * i], r[8 * half + 2 * i + 1]);
+      bytes4_to_bf16(w[i] & 0xF0F0F0F0u, s2_hi, c2_hi, r[16 + 8 * half + 2 * i], r[16 + 8 * half + 2 * i + 1]);
     }
   }
 }
@@ -191,11 +210,13 @@ __device__ __forceinline__ void unpack_q6k(const uint8_t* blk, int c, uint32_t (
       const uint4 la = *reinterpret_cast<const uint4*>(blk + half * 64 + 32 * t + 16 * u);
       const uint32_t lw[4] = {la.x, la.y, la.z, la.w};
       const float sv = d * (float)(int8_t)(scw >> (8 * (2 * t + u)));   // weight = sv * (stored - 32)
+      const uint64_t s2 = dup_f2(sv), c2 = dup_f2(-1056.f * sv);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const uint32_t nib = (cb ? (lw[i] >> 4) : lw[i]) & 0x0F0F0F0Fu;
-        const uint32_t q4 = nib | (((hw[4 * u + i] >> sh) & 0x03030303u) << 4);
-        bytes4_to_bf16(q4, 128.f * sv, -160.f * sv, r[16 * t + 8 * u + 2 * i], r[16 * t + 8 * u + 2 * i + 1]);
+        // the two high bits land on bits 4..5 of every byte with one shift (left or right by |sh - 4|)
+        const uint32_t hsh = sh >= 4 ? (hw[4 * u + i] >> (sh - 4)) : (hw[4 * u + i] << (4 - sh));
+        const uint32_t q6 = ((cb ? (lw[i] >> 4) : lw[i]) & 0x0F0F0F0Fu) | (hsh & 0x30303030u);
+        bytes4_to_bf16(q6, s2, c2, r[16 * t + 8 * u + 2 * i], r[16 * t + 8 * u + 2 * i + 1]);
       }
     }
   }
@@ -207,20 +228,17 @@ __device__ __forceinline__ void unpack_q80(const uint8_t* qst, int row, int c, u
   const uint8_t* plane = qst + (size_t)(c >> 1) * (WN * 128) + (size_t)row * 128;
   const uint32_t scw = *reinterpret_cast<const uint32_t*>(qst + 2 * WN * 128 + (size_t)row * 16 + 4 * c);
   const __half2 sc2 = *reinterpret_cast<const __half2*>(&scw);
-  const float ds[2] = {__low2float(sc2), __high2float(sc2)};
+  // the byte with its sign bit flipped is q + 128: weight = d * (v - 128), exact in fp32
+  const float d0 = __low2float(sc2), d1 = __high2float(sc2);
+  const uint64_t s2[2] = {dup_f2(d0), dup_f2(d1)}, c2[2] = {dup_f2(-1152.f * d0), dup_f2(-1152.f * d1)};
 #pragma unroll
   for (int j = 0; j < 4; ++j) {      // 16-byte chunk j of the k-block = chunk 4*(c&1) + j of the 128-byte row
     const int chunk = 4 * (c & 1) + j;
     const uint4 qv = *reinterpret_cast<const uint4*>(plane + ((chunk ^ (row & 7)) << 4));
     const uint32_t w[4] = {qv.x, qv.y, qv.z, qv.w};
-    const float d = ds[j >> 1];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float f0 = d * (float)(int8_t)(w[i] & 0xFFu), f1 = d * (float)(int8_t)((w[i] >> 8) & 0xFFu);
-      const float f2 = d * (float)(int8_t)((w[i] >> 16) & 0xFFu), f3 = d * (float)(int8_t)(w[i] >> 24);
-      r[8 * j + 2 * i] = bits_bf162(__floats2bfloat162_rn(f0, f1));
-      r[8 * j + 2 * i + 1] = bits_bf162(__floats2bfloat162_rn(f2, f3));
-    }
+    for (int i = 0; i < 4; ++i)
+      bytes4_to_bf16(w[i] ^ 0x80808080u, s2[j >> 1], c2[j >> 1], r[8 * j + 2 * i], r[8 * j + 2 * i + 1]);
   }
 }
 
@@ -228,8 +246,11 @@ __device__ __forceinline__ int q_row_bytes(int qtype) { return qtype == HE_Q4_K 
 
 // Tile walk shared by every role: tile index -> (split, m-tile, n-tile); M-fastest so that CTAs running at the
 // same time share the weight tile in L2.
+// In pair mode a work unit is one weight tile against TWO neighbouring M-tiles (tm, tm + 1): the weight tile is
+// expanded once and every operand stage feeds two MMAs, one per accumulator, which halves the expansion work per
+// FLOP.  `ntile` is 2 there (1 for the last unit of an odd tile count) and 1 otherwise.
 struct TileCoord {
-  int ks, tm, tn, b_row0, sb0, sb1;
+  int ks, tm, tn, b_row0, sb0, sb1, ntile;
   bool skip;
 };
 
@@ -238,8 +259,16 @@ __device__ __forceinline__ TileCoord tile_coord(const WqArgs& g, int tile, int t
   const int ksp = g.k_splits;
   t.ks = tile % ksp;
   const int mn = tile / ksp;
-  t.tm = mn % tiles_m;
-  t.tn = mn / tiles_m;
+  if (g.pair) {
+    const int units_m = (tiles_m + 1) >> 1;
+    t.tm = (mn % units_m) * 2;
+    t.tn = mn / units_m;
+    t.ntile = min(2, tiles_m - t.tm);
+  } else {
+    t.tm = mn % tiles_m;
+    t.tn = mn / tiles_m;
+    t.ntile = 1;
+  }
   t.b_row0 = t.tn * WN;
   t.skip = false;
   if (g.tile_group != nullptr) {
@@ -318,7 +347,8 @@ __device__ __forceinline__ void gemm_wq_body(const CUtensorMap& tmX, const CUten
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int mt = g.mt;
   const int tiles_m = (g.M + mt - 1) / mt, tiles_n = (g.N + WN - 1) / WN;
-  const int n_tiles = (RS && !(f->phases & 1)) ? 0 : tiles_m * tiles_n * g.k_splits;
+  const int units_m = g.pair ? (tiles_m + 1) >> 1 : tiles_m;
+  const int n_tiles = (RS && !(f->phases & 1)) ? 0 : units_m * tiles_n * g.k_splits;   // work units
   const int sb_all = g.K >> 8;
 
   if (threadIdx.x == 0) {
@@ -362,8 +392,8 @@ __device__ __forceinline__ void gemm_wq_body(const CUtensorMap& tmX, const CUten
       for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
         const TileCoord t = tile_coord(g, tile, tiles_m, sb_all);
         if (t.skip) continue;
-        if (g.ag_world > 0) {
-          const int owner = t.tm % g.ag_world;
+        for (int j = 0; j < t.ntile && g.ag_world > 0; ++j) {
+          const int owner = (t.tm + j) % g.ag_world;
           if (!(ag_seen & (1u << owner))) {
             unsigned polls = 0;
             while ((int)(ld_acquire_sys_u32(g.ag_flags + owner) - ag_want) < 0) {
@@ -377,12 +407,13 @@ __device__ __forceinline__ void gemm_wq_body(const CUtensorMap& tmX, const CUten
             ag_seen |= 1u << owner;
           }
         }
-        for (int kb = 4 * t.sb0; kb < 4 * t.sb1; ++kb, ++it) {
-          const int s = it % XSTAGES;
-          if (!mbar_wait(&bar->x_empty[s], ((it / XSTAGES) & 1) ^ 1, abort_flag, g.status, 301)) break;
-          mbar_expect_tx(&bar->x_full[s], (uint32_t)mt * BK * 2);
-          tma_load_2d(smem + s * g.x_stage_bytes, &tmX, &bar->x_full[s], kb * BK, t.tm * mt);
-        }
+        for (int kb = 4 * t.sb0; kb < 4 * t.sb1 && !*abort_flag; ++kb)
+          for (int j = 0; j < t.ntile; ++j, ++it) {
+            const int s = it % XSTAGES;
+            if (!mbar_wait(&bar->x_empty[s], ((it / XSTAGES) & 1) ^ 1, abort_flag, g.status, 301)) break;
+            mbar_expect_tx(&bar->x_full[s], (uint32_t)mt * BK * 2);
+            tma_load_2d(smem + s * g.x_stage_bytes, &tmX, &bar->x_full[s], kb * BK, (t.tm + j) * mt);
+          }
         if (*abort_flag) break;
       }
     }
@@ -416,32 +447,44 @@ __device__ __forceinline__ void gemm_wq_body(const CUtensorMap& tmX, const CUten
     // ------------------------------------------------------------ MMA issuer
     if (elect_one()) {
       const uint32_t idesc = umma_idesc_bf16(WN, mt);
-      uint32_t it = 0, tcount = 0;
+      uint32_t it = 0, ait = 0, ucount = 0;
+      uint32_t par = 0;                         // bit b: parity of the completed uses of accumulator b
       for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
         const TileCoord t = tile_coord(g, tile, tiles_m, sb_all);
         if (t.skip) continue;
-        const int acc = tcount & 1;
-        if (!mbar_wait(&bar->d_empty[acc], ((tcount >> 1) & 1) ^ 1, abort_flag, g.status, 303)) break;
+        // pair mode: tile j of the unit accumulates in buffer j; otherwise units alternate between the buffers so
+        // that the epilogue of one overlaps the main loop of the next
+        const int acc0 = g.pair ? 0 : (int)(ucount & 1);
+        bool ok = true;
+        for (int j = 0; j < t.ntile && ok; ++j)
+          ok = mbar_wait(&bar->d_empty[acc0 + j], ((par >> (acc0 + j)) & 1) ^ 1, abort_flag, g.status, 303);
+        if (!ok) break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * D_COLS;
         const int n_kb = 4 * (t.sb1 - t.sb0);
-        for (int kb = 0; kb < n_kb; ++kb, ++it) {
-          const int s = it % XSTAGES, a = it % N_SETS;
-          if (!mbar_wait(&bar->x_full[s], (it / XSTAGES) & 1, abort_flag, g.status, 304)) break;
-          if (!mbar_wait(&bar->a_full[a], (it / N_SETS) & 1, abort_flag, g.status, 305)) break;
-          tc_fence_after();
-          const uint32_t x_addr = smem_u32(smem + s * g.x_stage_bytes);
+        for (int kb = 0; kb < n_kb && ok; ++kb, ++ait) {
+          const int a = ait % N_SETS;
+          if (!mbar_wait(&bar->a_full[a], (ait / N_SETS) & 1, abort_flag, g.status, 305)) { ok = false; break; }
           const uint32_t a_tmem = tmem_base + A_COL0 + a * A_STAGE_COLS;
+          for (int j = 0; j < t.ntile; ++j, ++it) {
+            const int s = it % XSTAGES;
+            if (!mbar_wait(&bar->x_full[s], (it / XSTAGES) & 1, abort_flag, g.status, 304)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t x_addr = smem_u32(smem + s * g.x_stage_bytes);
+            const uint32_t d_tmem = tmem_base + (acc0 + j) * D_COLS;
 #pragma unroll
-          for (int k = 0; k < BK / UK; ++k)
-            umma_f16_ts(d_tmem, a_tmem + k * (UK / 2), umma_desc_k_sw128(x_addr + k * UK * 2), idesc,
-                        (kb > 0 || k > 0) ? 1u : 0u);
-          umma_commit(&bar->x_empty[s]);    // the smem stage and ...
-          umma_commit(&bar->a_empty[a]);    // ... the TMEM operand stage are free once these MMAs have read them
+            for (int k = 0; k < BK / UK; ++k)
+              umma_f16_ts(d_tmem, a_tmem + k * (UK / 2), umma_desc_k_sw128(x_addr + k * UK * 2), idesc,
+                          (kb > 0 || k > 0) ? 1u : 0u);
+            umma_commit(&bar->x_empty[s]);  // the smem stage is free once these MMAs have read it
+          }
+          umma_commit(&bar->a_empty[a]);    // ... and so is the TMEM operand stage
         }
-        if (*abort_flag) break;
-        umma_commit(&bar->d_full[acc]);
-        ++tcount;
+        if (!ok || *abort_flag) break;
+        for (int j = 0; j < t.ntile; ++j) {
+          umma_commit(&bar->d_full[acc0 + j]);
+          par ^= 1u << (acc0 + j);
+        }
+        ++ucount;
       }
     }
   } else if (warp >= WARP_UNPACK0 && warp < WARP_COLL) {
@@ -479,17 +522,22 @@ __device__ __forceinline__ void gemm_wq_body(const CUtensorMap& tmX, const CUten
   } else if (warp >= 4 && warp < 8) {
     // ------------------------------------------------------------ epilogue (warps 4..7): transposed store
     const int q = warp & 3;
-    uint32_t tcount = 0;
-    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+    uint32_t ucount = 0;
+    uint32_t par = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
       const TileCoord t = tile_coord(g, tile, tiles_m, sb_all);
       if (t.skip) continue;
-      const int acc = tcount & 1;
-      if (!mbar_wait(&bar->d_full[acc], (tcount >> 1) & 1, abort_flag, g.status, 308)) break;
+      for (int j = 0; j < t.ntile; ++j) {
+      const int acc = g.pair ? j : (int)(ucount & 1);
+      const int tmj = t.tm + j;                              // the M-tile held by this accumulator
+      if (!mbar_wait(&bar->d_full[acc], (par >> acc) & 1, abort_flag, g.status, 308)) { ok = false; break; }
+      par ^= 1u << acc;
       tc_fence_after();
       const int n = t.tn * WN + q * 32 + lane;               // output column of this thread
       const bool n_ok = n < g.N;
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * D_COLS;
-      const int m0 = t.tm * mt;
+      const int m0 = tmj * mt;
       const int m_lim = min(mt, g.M - m0);                   // live activation rows of this tile
 #pragma unroll 1
       for (int c = 0; c * 32 < m_lim; ++c) {
@@ -500,8 +548,8 @@ __device__ __forceinline__ void gemm_wq_body(const CUtensorMap& tmX, const CUten
         if constexpr (RS) {
           // partial quarter -> the owner's stage slot, bf16, fragment-major (16-byte group gi = 4c + v of lane l at
           // (gi * 32 + l) * 8): a store instruction of the warp covers 512 contiguous bytes on the link
-          const int W = f->world, owner = t.tm % W;
-          const int slot = (t.tm / W) * tiles_n + t.tn;
+          const int W = f->world, owner = tmj % W;
+          const int slot = (tmj / W) * tiles_n + t.tn;
           __nv_bfloat16* dst = f->stage[owner] + ((size_t)f->rank * f->slots + slot) * RS_TILE_ELEMS +
                                (size_t)q * 32 * MT_MAX + ((size_t)(c * 4) * 32 + lane) * 8;
 #pragma unroll
@@ -527,9 +575,13 @@ __device__ __forceinline__ void gemm_wq_body(const CUtensorMap& tmX, const CUten
             float* dst = reinterpret_cast<float*>(g.C) + (size_t)(m0 + c * 32) * g.ldc + n +
                          (g.epi == 4 ? (size_t)t.ks * (size_t)g.split_stride : (size_t)0);
             if (g.epi == 2) {
+              // one CTA owns the tile, so each element gets exactly one add (order-free, reproducible); the add is
+              // performed at the L2 and nothing comes back, so the warp never waits for the old value
 #pragma unroll
               for (int j = 0; j < 32; ++j)
-                if (j < jn) dst[(size_t)j * g.ldc] += __uint_as_float(r[j]);
+                if (j < jn)
+                  asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dst + (size_t)j * g.ldc), "f"(__uint_as_float(r[j]))
+                               : "memory");
             } else {
 #pragma unroll
               for (int j = 0; j < 32; ++j)
@@ -546,11 +598,12 @@ __device__ __forceinline__ void gemm_wq_body(const CUtensorMap& tmX, const CUten
         __syncwarp();
         if (lane == 0) {
           const int W = f->world;
-          const int slot = (t.tm / W) * tiles_n + t.tn;
-          st_release_sys_u32(f->flags[t.tm % W] + ((size_t)slot * W + f->rank) * 4 + q, rs_epoch);
+          const int slot = (tmj / W) * tiles_n + t.tn;
+          st_release_sys_u32(f->flags[tmj % W] + ((size_t)slot * W + f->rank) * 4 + q, rs_epoch);
         }
       }
-      ++tcount;
+      }
+      ++ucount;
     }
   } else if (RS && (warp == 3 || warp == WARP_COLL)) {
     // ------------------------------------------------------------ collective warps (reduce-scatter form only)
@@ -707,6 +760,16 @@ int make_q_maps(CUtensorMap* q0, CUtensorMap* q1, const void* B, int qtype, long
 
 constexpr size_t SMEM_WQ = (size_t)SMEM_BUDGET + sizeof(WqBarriers) + 1024;
 
+// HE_GEMMQ_PAIR=0 turns the two-tiles-per-weight-tile mode off (for comparisons).
+bool pair_mode_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("HE_GEMMQ_PAIR");
+    v = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return v != 0;
+}
+
 int pick_mt(int M, bool grouped) {
   if (grouped) return 128;
   if (M >= MT_MAX) return MT_MAX;
@@ -728,7 +791,9 @@ int launch_wq(const void* A, long long lda, int a_cols, const void* B, int qtype
   if (rc != 0) return rc;
   rc = make_q_maps(&q0, &q1, B, qtype, b_rows, g.K);
   if (rc != 0) return rc;
-  const long long tiles = (long long)((g.M + g.mt - 1) / g.mt) * ((g.N + WN - 1) / WN) * g.k_splits;
+  const int tiles_m = (g.M + g.mt - 1) / g.mt;
+  g.pair = (pair_mode_enabled() && g.tile_group == nullptr && g.k_splits == 1 && tiles_m >= 2) ? 1 : 0;
+  const long long tiles = (long long)(g.pair ? (tiles_m + 1) / 2 : tiles_m) * ((g.N + WN - 1) / WN) * g.k_splits;
   const int grid = (int)(tiles < num_sms ? tiles : num_sms);
   if (fuse != nullptr) {
     cudaError_t e = cudaFuncSetAttribute(gemm_wq_rs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_WQ);
