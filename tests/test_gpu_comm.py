@@ -225,8 +225,8 @@ def test_vocab_parallel_argmax_merge_and_bounded_wait():
         g.close()
 
 
-@pytest.mark.parametrize("world", [2, 4])
-def test_sequence_parallel_gemm_reduce_scatter_norm_allgather_emulated(world):
+@pytest.mark.parametrize("world,T", [(2, 400), (4, 400), (8, 1700)])
+def test_sequence_parallel_gemm_reduce_scatter_norm_allgather_emulated(world, T):
     """Sequence-parallel prefill on emulated ranks of one GPU, phase by phase: GEMM -> reduce-scatter -> residual add
     (quantised weight read in place), RMSNorm + all-gather push, the all-gather wait of the consumer GEMM, and the
     final residual gather -- each against plain fp32 PyTorch."""
@@ -235,8 +235,8 @@ def test_sequence_parallel_gemm_reduce_scatter_norm_allgather_emulated(world):
     from hipengine_b200.ops import kernels as K
     from hipengine_b200.parallel.fused import SeqParallel
     from hipengine_b200.quant import ggml as Q
-    T, H, Kq, N2 = 400, 512, 512, 384
-    group = SeqParallel.emulated_group("cuda", H, world, max_rows=512)
+    H, Kq, N2 = 512, 512, 384
+    group = SeqParallel.emulated_group("cuda", H, world, max_rows=2048)
     g = torch.Generator(device="cuda").manual_seed(world)
     h0 = torch.randn(T, H, device="cuda", generator=g)
     xs, dws, deqs = [], [], []
@@ -311,14 +311,14 @@ def test_sequence_parallel_gemm_reduce_scatter_norm_allgather_emulated(world):
         gq.close()
 
 
-@pytest.mark.parametrize("world", [2, 4])
-def test_rows_reduce_scatter_for_expert_parallel_combine_emulated(world):
+@pytest.mark.parametrize("world,T", [(2, 450), (4, 450), (8, 1650)])
+def test_rows_reduce_scatter_for_expert_parallel_combine_emulated(world, T):
     """Token-ordered fp32 partial rows of every emulated rank are reduce-scattered into the row-sharded residual:
     owned rows get h + sum over ranks (bf16 on the wire for remote rows), other rows stay untouched."""
     from hipengine_b200.ops import kernels as K
     from hipengine_b200.parallel.fused import SeqParallel
-    T, H = 450, 512
-    group = SeqParallel.emulated_group("cuda", H, world, max_rows=512)
+    H = 512
+    group = SeqParallel.emulated_group("cuda", H, world, max_rows=2048)
     g = torch.Generator(device="cuda").manual_seed(3)
     h0 = torch.randn(T, H, device="cuda", generator=g)
     parts = [torch.randn(T, H, device="cuda", generator=g) for _ in range(world)]
