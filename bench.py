@@ -115,6 +115,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the layer stack (marks the run invalid)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--no-mtp", action="store_true", help="N = 1: skip the speculative (NextN depth 3) cycle figures")
+    ap.add_argument("--mtp-depth", type=int, default=3)
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -239,6 +241,19 @@ def main() -> int:
             if world > 1:
                 raise
 
+    mtp = None
+    if world == 1 and not args.no_mtp and not args.no_graphs and cfg.is_hybrid and not getattr(cfg, "n_experts", 0):
+        # speculative decoding on the same geometry with a NextN block appended: cost of one captured cycle in units
+        # of an autoregressive step, tokens per cycle with the block's own drafts (random weights: near zero
+        # acceptance) and with the true continuation as drafts (every draft accepted: the upper bound)
+        runner.graphs.clear()
+        runner = ex = None
+        torch.cuda.empty_cache()
+        try:
+            mtp = run_mtp(args, cfg, dev, prompts[0], ctx_max)
+        except Exception as exc:
+            mtp = {"error": f"{type(exc).__name__}: {exc}"}
+
     nccl_base = None
     if world > 1 and mode == "tp" and args.tp_comm == "fused" and not args.no_extra:
         # the same tensor-parallel engine with every collective done by the library (NCCL all-reduce / all-gather
@@ -305,6 +320,8 @@ def main() -> int:
         }
         if e2e is not None:
             line["e2e"] = e2e
+        if mtp is not None:
+            line["mtp"] = mtp
         if extra is not None:
             line["other_parallelism"] = extra
         if mode == "tp":
@@ -331,6 +348,83 @@ def main() -> int:
         dist.destroy_process_group()
         dog.cancel()
     return 0
+
+
+def run_mtp(args, cfg, dev, prompt, ctx_max):
+    """NextN speculative cycle on the benchmark geometry (one request, greedy): device-timed figures."""
+    import torch
+    from dataclasses import replace
+    from hipengine_b200.loading.synth import build_random_model
+    from hipengine_b200.models import make_executor
+    from hipengine_b200.models.decode_graph import DecodeGraphRunner
+    from hipengine_b200.models.executor import make_batch
+    from hipengine_b200.ops import kernels as K
+    from hipengine_b200.speculative.mtp import GraphedMTPCycle
+    depth = args.mtp_depth
+    cfgm = replace(cfg, nextn_layers=1)
+    weights = build_random_model(cfgm, seed=0, device=dev, recipe="q4_k_m")
+    ex = make_executor(weights, device=dev, max_slots=1, max_context=ctx_max)
+    del weights
+    cyc = GraphedMTPCycle(ex, max_depth=depth, max_requests=1)
+    runner = DecodeGraphRunner(ex, max_rows=1)
+    b = make_batch([(0, 0, prompt)], dev)
+    h = ex.forward(b)
+    cyc.after_prefill(b, h)
+    last = int(ex.logits(h[b.T - 1:b.T]).argmax(-1))
+    pos = len(prompt)                                   # position of `last`
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+
+    def cycles(n, override=None):
+        nonlocal last, pos
+        toks = 0
+        for i in range(n):
+            ov = None if override is None else torch.tensor([override[toks:toks + depth]])
+            res, _ = cyc.cycle([0], [last], [pos], depth, draft_override=ov)
+            toks += len(res[0].tokens)
+            last, pos = res[0].tokens[-1], pos + len(res[0].tokens)
+        return toks
+
+    cycles(4)
+    n_cyc = 24
+    e0, e1 = ev(), ev()
+    torch.cuda.synchronize()
+    e0.record()
+    got = cycles(n_cyc)
+    e1.record()
+    torch.cuda.synchronize()
+    cycle_ms = e0.elapsed_time(e1) / n_cyc
+    # autoregressive steps from the same state (graph replay), recorded: they are the true continuation
+    snap = {"conv": {i: t[0].clone() for i, t in ex.conv_state.items()},
+            "gdn": {i: t[0].clone() for i, t in ex.gdn_state.items()}, "hp": cyc.h_prev[0].clone()}
+    n_ar = 8 * (depth + 1)
+    runner.set_rows([0], [last], [pos])
+    cont = torch.zeros(n_ar + 4, dtype=torch.int64, device=dev)
+    for j in range(4):
+        runner.step(1, ctx_max)
+        cont[j].copy_(runner.tokens[0])
+    e2, e3 = ev(), ev()
+    e2.record()
+    for j in range(n_ar):
+        runner.step(1, ctx_max)
+        cont[4 + j].copy_(runner.tokens[0])
+    e3.record()
+    torch.cuda.synchronize()
+    ar_ms = e2.elapsed_time(e3) / n_ar
+    # every draft accepted: rewind the recurrent state and feed the recorded continuation as drafts (eager cycle)
+    for i, t in ex.conv_state.items():
+        t[0].copy_(snap["conv"][i])
+    for i, t in ex.gdn_state.items():
+        t[0].copy_(snap["gdn"][i])
+    cyc.h_prev[0].copy_(snap["hp"])
+    forced = cycles(6, override=cont.tolist() + [0] * depth)
+    K.check_status(dev)
+    units = cycle_ms / ar_ms
+    return {"depth": depth, "ar_step_ms": round(ar_ms, 4), "cycle_ms": round(cycle_ms, 4),
+            "cycle_cost_ar_units": round(units, 3), "tokens_per_cycle_own_drafts": round(got / n_cyc, 3),
+            "tokens_per_cycle_all_accepted": round(forced / 6, 3),
+            "speedup_all_accepted": round((forced / 6) / units, 3),
+            "kernels_per_cycle_graph": list(cyc.graph_stats["kernels_per_graph"].values())[:1],
+            "graph": cyc.graph_stats["captures"], "note": "random weights: own drafts are almost never accepted"}
 
 
 def run_e2e(args, cfg, ex, prompts):

@@ -66,8 +66,24 @@ def _key(src: Path, flags: Sequence[str], cver: str) -> str:
     return h.hexdigest()
 
 
-def lib_path() -> Path:
-    return OUT_DIR / LIB_NAME
+def variant() -> str:
+    """Name of the library variant in use: '' (the product) or e.g. 'checked' (``HE_NATIVE_VARIANT``)."""
+    return os.environ.get("HE_NATIVE_VARIANT", "").strip()
+
+
+# extra compiler flags of the named variants
+VARIANT_FLAGS = {
+    # every index taken from device data is range-checked; a violation records a code in the bounds word
+    # (he_bounds_status) and skips the access instead of performing it
+    "checked": ["-DHE_BOUNDS_CHECK=1"],
+    # role cycle counters in the quantised GEMM (he_gemm_q_debug_counters)
+    "prof": ["-DHE_WQ_PROFILE=1"],
+}
+
+
+def lib_path(name: Optional[str] = None) -> Path:
+    v = variant() if name is None else name
+    return OUT_DIR / (LIB_NAME if not v else LIB_NAME.replace(".so", f"_{v}.so"))
 
 
 def build_plan(extra_flags: Sequence[str] = ()) -> Dict[str, object]:
@@ -77,17 +93,19 @@ def build_plan(extra_flags: Sequence[str] = ()) -> Dict[str, object]:
     return {"nvcc": nvcc, "flags": flags, "sources": [str(s) for s in sources()], "output": str(lib_path())}
 
 
-def build(verbose: bool = False, force: bool = False, extra_flags: Sequence[str] = (), jobs: int = 0) -> Path:
-    """Compile every source for sm_100a and link ``libhe_b200.so``.  Returns the library path."""
+def build(verbose: bool = False, force: bool = False, extra_flags: Sequence[str] = (), jobs: int = 0,
+          name: str = "") -> Path:
+    """Compile every source for sm_100a and link ``libhe_b200.so`` (or the variant ``libhe_b200_<name>.so`` with the
+    variant's flags plus ``extra_flags``).  Returns the library path."""
     nvcc = nvcc_path()
     if nvcc is None:
         raise RuntimeError("nvcc not found; set HE_NVCC or install the CUDA toolkit")
     OUT_DIR.mkdir(parents=True, exist_ok=True)
-    obj_dir = OUT_DIR / "obj"
+    obj_dir = OUT_DIR / ("obj" if not name else f"obj_{name}")
     obj_dir.mkdir(exist_ok=True)
-    flags = list(NVCC_FLAGS) + list(extra_flags)
+    flags = list(NVCC_FLAGS) + list(VARIANT_FLAGS.get(name, [])) + list(extra_flags)
     cver = _compiler_version(nvcc)
-    manifest_path = OUT_DIR / "manifest.json"
+    manifest_path = OUT_DIR / ("manifest.json" if not name else f"manifest_{name}.json")
     try:
         manifest = json.loads(manifest_path.read_text())
     except Exception:
@@ -114,9 +132,9 @@ def build(verbose: bool = False, force: bool = False, extra_flags: Sequence[str]
 
     if todo:
         with ThreadPoolExecutor(max_workers=jobs or min(8, os.cpu_count() or 4)) as ex:
-            for name, k in ex.map(compile_one, todo):
-                manifest[name] = k
-    lib = lib_path()
+            for src_name, k in ex.map(compile_one, todo):
+                manifest[src_name] = k
+    lib = lib_path(name)
     link_key = hashlib.sha256(("".join(manifest.get(s.name, "") for s in srcs)).encode()).hexdigest()
     if todo or not lib.exists() or manifest.get("__link__") != link_key:
         cmd = [nvcc, "-shared", "-o", str(lib)] + [str(o) for o in objs] + ["-Xcompiler", "-fPIC"]
@@ -131,5 +149,6 @@ def build(verbose: bool = False, force: bool = False, extra_flags: Sequence[str]
 
 
 if __name__ == "__main__":
-    p = build(verbose="-v" in sys.argv, force="--force" in sys.argv)
+    names = [a.split("=", 1)[1] for a in sys.argv if a.startswith("--variant=")]
+    p = build(verbose="-v" in sys.argv, force="--force" in sys.argv, name=names[0] if names else "")
     print(p)

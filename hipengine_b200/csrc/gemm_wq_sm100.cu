@@ -30,7 +30,8 @@ namespace {
 constexpr int WN = 128;                  // weight rows per tile (the MMA's M)
 constexpr int MT_MAX = 192;              // activation rows per tile (the MMA's N), multiple of 16
 constexpr int BK = 64, UK = 16;
-constexpr int XSTAGES = 5;                          // activation ring depth (stage = mt x 64 bf16, <= 24 KB)
+constexpr int XSTAGES = 5;                          // activation ring depth (stage = mt x 64 bf16, <= 24 KB); seven
+                                                    // stages (with three raw-block stages) measured slower in pair mode
 constexpr int QSTAGES_MAX = 12;                     // raw-block ring: as many stages as shared memory holds, up to 12
 constexpr int SMEM_BUDGET = 224 * 1024;             // dynamic shared memory the rings may use
 constexpr int N_SETS = 4;                           // unpack sets == TMEM operand stages == k-blocks per q-stage
@@ -38,9 +39,12 @@ constexpr int N_UNPACK_WARPS = 16;
 constexpr int WARP_UNPACK0 = 8;
 constexpr int NTHREADS_WQ = (WARP_UNPACK0 + N_UNPACK_WARPS) * 32;   // 768
 constexpr int TMEM_COLS = 512;
-constexpr int D_COLS = MT_MAX;                      // column stride between the two accumulators
-constexpr int A_COL0 = 2 * D_COLS;                  // first operand-stage column (384)
+constexpr int D_COLS = MT_MAX;                      // column stride between the two accumulators (tiles > 64 rows)
+constexpr int D_COLS_SMALL = 64;                    // ... for tiles of <= 64 activation rows
 constexpr int A_STAGE_COLS = 32;                    // 64 bf16 per lane
+constexpr int A_DEPTH_MAX = 3;                      // operand stages per unpack set (small tiles); 1 for large tiles
+constexpr int A_STAGES_MAX = N_SETS * A_DEPTH_MAX;  // 12 x 32 columns + 2 x 64 = 512
+constexpr int X_KB_WIDE = 4;                        // k-blocks per activation stage when the tile is small
 
 struct WqArgs {
   void* C;
@@ -55,9 +59,16 @@ struct WqArgs {
   int pair;                 // 1: a work unit is one weight tile against two neighbouring M-tiles (see TileCoord)
   const int* tile_group;    // grouped mode: M-tile tm uses weight rows [tile_group[tm] * N, +N); < 0 skips the tile
   int* status;
+  long long* dbg;           // optional cycle counters of CTA 0 (he_gemm_q_debug_counters), null in normal use
   // ring geometry, set by the launcher: few activation rows leave room for a deep raw-block ring, which is what
   // hides DRAM latency when the weight is streamed once (decode batches)
-  int x_stage_bytes;        // mt * 128 rounded up to 1 KB
+  int x_stage_bytes;        // x_kb * mt * 128 rounded up to 1 KB
+  int x_kb;                 // 64-column k-blocks per activation stage: 4 (a whole super-block) for tiles of <= 48
+                            // rows, else 1.  With few rows an MMA batch lasts tens of cycles, so a ring of single
+                            // k-blocks would be bound by the round trip of its own barriers, not by bandwidth
+  int a_depth;              // operand stages per unpack set: 3 for tiles of <= 64 rows (the accumulators need only
+                            // 2 x 64 TMEM columns then), else 1; a set expands super-block i + 1 .. i + depth - 1
+                            // while the MMAs of super-block i are still in flight
   int q_stage_bytes;        // 128 rows x bytes per super-block row, rounded up to 1 KB
   int q_stages;
   // all-gather -> GEMM (sequence-parallel activations): the rows of M-tile tm were written into the local activation
@@ -115,8 +126,8 @@ struct __align__(8) WqBarriers {
   uint64_t x_empty[XSTAGES];
   uint64_t q_full[QSTAGES_MAX];
   uint64_t q_empty[QSTAGES_MAX];
-  uint64_t a_full[N_SETS];
-  uint64_t a_empty[N_SETS];
+  uint64_t a_full[A_STAGES_MAX];
+  uint64_t a_empty[A_STAGES_MAX];
   uint64_t d_full[2];
   uint64_t d_empty[2];
   uint32_t tmem_base;
@@ -137,13 +148,31 @@ __device__ __forceinline__ uint64_t pack_f2(float lo, float hi) {
   asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
   return r;
 }
+// Role cycle counters (he_gemm_q_debug_counters) exist only in builds with -DHE_WQ_PROFILE=1: the product build
+// folds every `prof` flag to false, so the hot loops carry no extra registers or branches.
+#ifdef HE_WQ_PROFILE
+#define HE_WQ_PROF_ON true
+#else
+#define HE_WQ_PROF_ON false
+#endif
+
+#ifndef HE_WQ_SCALAR_FMA
+#define HE_WQ_SCALAR_FMA 0
+#endif
 __device__ __forceinline__ uint32_t fma2_to_bf162(__half2 v, uint64_t s2, uint64_t c2) {
   const float2 f = __half22float2(v);
+#if HE_WQ_SCALAR_FMA
+  float s, c, unused;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(s), "=f"(unused) : "l"(s2));
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(c), "=f"(unused) : "l"(c2));
+  return bits_bf162(__floats2bfloat162_rn(fmaf(f.x, s, c), fmaf(f.y, s, c)));
+#else
   uint64_t d;
   asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(pack_f2(f.x, f.y)), "l"(s2), "l"(c2));
   float d0, d1;
   asm("mov.b64 {%0, %1}, %2;" : "=f"(d0), "=f"(d1) : "l"(d));
   return bits_bf162(__floats2bfloat162_rn(d0, d1));
+#endif
 }
 
 // Four unsigned bytes v of `b4` become two bf16x2 registers holding bf16(v * s + off) with a single rounding.  A byte
@@ -242,6 +271,18 @@ __device__ __forceinline__ void unpack_q80(const uint8_t* qst, int row, int c, u
   }
 }
 
+// Cursor of a ring whose depth is a runtime value: stage index and phase bit advance without divisions.
+struct RingCursor {
+  int s = 0;
+  uint32_t ph = 0;
+  __device__ __forceinline__ void next(int depth) {
+    if (++s == depth) {
+      s = 0;
+      ph ^= 1u;
+    }
+  }
+};
+
 __device__ __forceinline__ int q_row_bytes(int qtype) { return qtype == HE_Q4_K ? 144 : (qtype == HE_Q6_K ? 224 : 272); }
 
 // Tile walk shared by every role: tile index -> (split, m-tile, n-tile); M-fastest so that CTAs running at the
@@ -334,7 +375,7 @@ __device__ __forceinline__ void rs_reduce_quarter(const WqArgs& g, const WqFuse&
   }
 }
 
-template <bool RS>
+template <bool RS, bool SMALL>
 __device__ __forceinline__ void gemm_wq_body(const CUtensorMap& tmX, const CUtensorMap& tmQ0, const CUtensorMap& tmQ1,
                                              const WqArgs& g, const WqFuse* f) {
   extern __shared__ uint8_t smem_raw[];
@@ -360,8 +401,11 @@ __device__ __forceinline__ void gemm_wq_body(const CUtensorMap& tmX, const CUten
       mbar_init(&bar->q_full[s], 1);
       mbar_init(&bar->q_empty[s], N_UNPACK_WARPS);
     }
-    for (int s = 0; s < N_SETS; ++s) {
-      mbar_init(&bar->a_full[s], N_UNPACK_WARPS / N_SETS);
+    // large tiles: one barrier pair per operand stage (a k-block, filled by the 4 warps of a set); small tiles: one
+    // pair per slot of a whole super-block (filled by all 16 warps), so that the MMA issuer -- a single thread, and
+    // the critical path when an MMA batch lasts tens of cycles -- waits and commits once per super-block
+    for (int s = 0; s < A_STAGES_MAX; ++s) {
+      mbar_init(&bar->a_full[s], SMALL ? N_UNPACK_WARPS : N_UNPACK_WARPS / N_SETS);
       mbar_init(&bar->a_empty[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -379,6 +423,11 @@ __device__ __forceinline__ void gemm_wq_body(const CUtensorMap& tmX, const CUten
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = bar->tmem_base;
+  // compile-time ring geometry (see WqArgs::x_kb / a_depth): the MMA issuer's index arithmetic is on the critical
+  // path when tiles are small, so no runtime divisors
+  constexpr int AD = SMALL ? A_DEPTH_MAX : 1, XKB = SMALL ? X_KB_WIDE : 1;
+  constexpr int d_cols = SMALL ? D_COLS_SMALL : D_COLS;   // accumulator stride
+  constexpr int a_col0 = 2 * d_cols;                      // first operand-stage column
   uint32_t rs_epoch = 0;
   if constexpr (RS) rs_epoch = *reinterpret_cast<volatile uint32_t*>(f->sync) + 1;
 
@@ -407,12 +456,15 @@ __device__ __forceinline__ void gemm_wq_body(const CUtensorMap& tmX, const CUten
             ag_seen |= 1u << owner;
           }
         }
-        for (int kb = 4 * t.sb0; kb < 4 * t.sb1 && !*abort_flag; ++kb)
+        // a stage holds XKB k-blocks of one M-tile (XKB > 1 only with one tile per unit)
+        for (int kb = 4 * t.sb0; kb < 4 * t.sb1 && !*abort_flag; kb += XKB)
           for (int j = 0; j < t.ntile; ++j, ++it) {
             const int s = it % XSTAGES;
             if (!mbar_wait(&bar->x_empty[s], ((it / XSTAGES) & 1) ^ 1, abort_flag, g.status, 301)) break;
-            mbar_expect_tx(&bar->x_full[s], (uint32_t)mt * BK * 2);
-            tma_load_2d(smem + s * g.x_stage_bytes, &tmX, &bar->x_full[s], kb * BK, (t.tm + j) * mt);
+            mbar_expect_tx(&bar->x_full[s], (uint32_t)(XKB * mt * BK * 2));
+            for (int u = 0; u < XKB; ++u)
+              tma_load_2d(smem + s * g.x_stage_bytes + u * mt * BK * 2, &tmX, &bar->x_full[s], (kb + u) * BK,
+                          (t.tm + j) * mt);
           }
         if (*abort_flag) break;
       }
@@ -423,12 +475,17 @@ __device__ __forceinline__ void gemm_wq_body(const CUtensorMap& tmX, const CUten
       tma_prefetch_desc(&tmQ0);
       const uint32_t rb = (uint32_t)q_row_bytes(g.qtype);
       uint32_t qit = 0;
+      RingCursor qc;
+      const bool qprof = HE_WQ_PROF_ON && g.dbg != nullptr && blockIdx.x == 0;
+      long long c_qe = 0, c_qall = qprof ? clock64() : 0;
       for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
         const TileCoord t = tile_coord(g, tile, tiles_m, sb_all);
         if (t.skip) continue;
-        for (int sb = t.sb0; sb < t.sb1; ++sb, ++qit) {
-          const int qs = qit % QS;
-          if (!mbar_wait(&bar->q_empty[qs], ((qit / QS) & 1) ^ 1, abort_flag, g.status, 302)) break;
+        for (int sb = t.sb0; sb < t.sb1; ++sb, ++qit, qc.next(QS)) {
+          const int qs = qc.s;
+          long long p0 = qprof ? clock64() : 0;
+          if (!mbar_wait(&bar->q_empty[qs], qc.ph ^ 1u, abort_flag, g.status, 302)) break;
+          if (qprof) c_qe += clock64() - p0;
           uint8_t* dst = qring + qs * g.q_stage_bytes;
           uint64_t* fb = &bar->q_full[qs];
           mbar_expect_tx(fb, WN * rb);
@@ -442,6 +499,7 @@ __device__ __forceinline__ void gemm_wq_body(const CUtensorMap& tmX, const CUten
         }
         if (*abort_flag) break;
       }
+      if (qprof) { g.dbg[16] = c_qe; g.dbg[17] = clock64() - c_qall; g.dbg[18] = qit; }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
@@ -449,6 +507,8 @@ __device__ __forceinline__ void gemm_wq_body(const CUtensorMap& tmX, const CUten
       const uint32_t idesc = umma_idesc_bf16(WN, mt);
       uint32_t it = 0, ait = 0, ucount = 0;
       uint32_t par = 0;                         // bit b: parity of the completed uses of accumulator b
+      const bool mprof = HE_WQ_PROF_ON && g.dbg != nullptr && blockIdx.x == 0;
+      long long c_af = 0, c_xf = 0, c_de = 0, c_all = mprof ? clock64() : 0;
       for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
         const TileCoord t = tile_coord(g, tile, tiles_m, sb_all);
         if (t.skip) continue;
@@ -456,28 +516,71 @@ __device__ __forceinline__ void gemm_wq_body(const CUtensorMap& tmX, const CUten
         // that the epilogue of one overlaps the main loop of the next
         const int acc0 = g.pair ? 0 : (int)(ucount & 1);
         bool ok = true;
+        long long d0 = mprof ? clock64() : 0;
         for (int j = 0; j < t.ntile && ok; ++j)
           ok = mbar_wait(&bar->d_empty[acc0 + j], ((par >> (acc0 + j)) & 1) ^ 1, abort_flag, g.status, 303);
         if (!ok) break;
+        if (mprof) c_de += clock64() - d0;
         tc_fence_after();
         const int n_kb = 4 * (t.sb1 - t.sb0);
-        for (int kb = 0; kb < n_kb && ok; ++kb, ++ait) {
-          const int a = ait % N_SETS;
-          if (!mbar_wait(&bar->a_full[a], (ait / N_SETS) & 1, abort_flag, g.status, 305)) { ok = false; break; }
-          const uint32_t a_tmem = tmem_base + A_COL0 + a * A_STAGE_COLS;
-          for (int j = 0; j < t.ntile; ++j, ++it) {
-            const int s = it % XSTAGES;
+        if constexpr (SMALL) {
+          // one super-block per iteration: slot sbi % AD of the operand ring, one activation stage (4 k-blocks)
+          const uint32_t d_tmem = tmem_base + acc0 * d_cols;
+          for (int sb = 0; sb < t.sb1 - t.sb0 && ok; ++sb, ait += N_SETS, ++it) {
+            const uint32_t sbi = ait / N_SETS;
+            const int slot = (int)(sbi % AD), s = it % XSTAGES;
+            long long m0 = 0;
+            if (mprof) m0 = clock64();
+            if (!mbar_wait(&bar->a_full[slot], (sbi / AD) & 1, abort_flag, g.status, 305)) { ok = false; break; }
+            if (mprof) { c_af += clock64() - m0; m0 = clock64(); }
             if (!mbar_wait(&bar->x_full[s], (it / XSTAGES) & 1, abort_flag, g.status, 304)) { ok = false; break; }
+            if (mprof) c_xf += clock64() - m0;
             tc_fence_after();
             const uint32_t x_addr = smem_u32(smem + s * g.x_stage_bytes);
-            const uint32_t d_tmem = tmem_base + (acc0 + j) * D_COLS;
+            const uint32_t a_tmem = tmem_base + a_col0 + slot * (N_SETS * A_STAGE_COLS);
 #pragma unroll
-            for (int k = 0; k < BK / UK; ++k)
-              umma_f16_ts(d_tmem, a_tmem + k * (UK / 2), umma_desc_k_sw128(x_addr + k * UK * 2), idesc,
-                          (kb > 0 || k > 0) ? 1u : 0u);
-            umma_commit(&bar->x_empty[s]);  // the smem stage is free once these MMAs have read it
+            for (int c = 0; c < N_SETS; ++c)
+#pragma unroll
+              for (int k = 0; k < BK / UK; ++k)
+                umma_f16_ts(d_tmem, a_tmem + c * A_STAGE_COLS + k * (UK / 2),
+                            umma_desc_k_sw128(x_addr + c * mt * BK * 2 + k * UK * 2), idesc,
+                            (sb > 0 || c > 0 || k > 0) ? 1u : 0u);
+            umma_commit(&bar->x_empty[s]);
+            umma_commit(&bar->a_empty[slot]);
           }
-          umma_commit(&bar->a_empty[a]);    // ... and so is the TMEM operand stage
+        } else {
+        for (int kb = 0; kb < n_kb && ok; ++kb, ++ait) {
+            // operand stage of k-block c of the unit-spanning super-block count sbi: set c, slot sbi % AD
+            const uint32_t sbi = ait / N_SETS;
+            const int a = (int)(ait % N_SETS) + N_SETS * (int)(sbi % AD);
+            long long m0 = 0;
+            if (mprof) m0 = clock64();
+            if (!mbar_wait(&bar->a_full[a], (sbi / AD) & 1, abort_flag, g.status, 305)) { ok = false; break; }
+            if (mprof) c_af += clock64() - m0;
+            const uint32_t a_tmem = tmem_base + a_col0 + a * A_STAGE_COLS;
+            const int u = kb % XKB;           // k-block inside the activation stage
+            for (int j = 0; j < t.ntile; ++j) {
+              const int s = it % XSTAGES;
+              if (mprof) m0 = clock64();
+              if (u == 0 && !mbar_wait(&bar->x_full[s], (it / XSTAGES) & 1, abort_flag, g.status, 304)) {
+                ok = false;
+                break;
+              }
+              if (mprof) c_xf += clock64() - m0;
+              tc_fence_after();
+              const uint32_t x_addr = smem_u32(smem + s * g.x_stage_bytes + u * mt * BK * 2);
+              const uint32_t d_tmem = tmem_base + (acc0 + j) * d_cols;
+  #pragma unroll
+              for (int k = 0; k < BK / UK; ++k)
+                umma_f16_ts(d_tmem, a_tmem + k * (UK / 2), umma_desc_k_sw128(x_addr + k * UK * 2), idesc,
+                            (kb > 0 || k > 0) ? 1u : 0u);
+              if (u == XKB - 1) {
+                umma_commit(&bar->x_empty[s]);  // the smem stage is free once these MMAs have read it
+                ++it;
+              }
+            }
+            umma_commit(&bar->a_empty[a]);    // ... and so is the TMEM operand stage
+          }
         }
         if (!ok || *abort_flag) break;
         for (int j = 0; j < t.ntile; ++j) {
@@ -486,38 +589,54 @@ __device__ __forceinline__ void gemm_wq_body(const CUtensorMap& tmX, const CUten
         }
         ++ucount;
       }
+      if (mprof) {
+        g.dbg[8] = c_af; g.dbg[9] = c_xf; g.dbg[10] = c_de; g.dbg[11] = clock64() - c_all; g.dbg[12] = ait;
+      }
     }
   } else if (warp >= WARP_UNPACK0 && warp < WARP_COLL) {
     // ------------------------------------------------------------ unpack: raw blocks -> bf16 operand in TMEM
     const int set = (warp - WARP_UNPACK0) >> 2;          // k-block of every super-block this warp expands
     const int row = (warp & 3) * 32 + lane;              // weight row in the tile == TMEM lane
-    const uint32_t a_tmem = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + A_COL0 + set * A_STAGE_COLS;
+    const uint32_t a_tmem0 = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + a_col0 + set * A_STAGE_COLS;
     const uint32_t rb = (uint32_t)q_row_bytes(g.qtype);
     uint32_t qit = 0;
+    RingCursor qc;
     bool ok = true;
+    const bool prof = HE_WQ_PROF_ON && g.dbg != nullptr && blockIdx.x == 0 && warp == WARP_UNPACK0;
+    long long c_q = 0, c_math = 0, c_a = 0, c_st = 0, t0 = 0, t1;
     for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
       const TileCoord t = tile_coord(g, tile, tiles_m, sb_all);
       if (t.skip) continue;
-      for (int sb = t.sb0; sb < t.sb1; ++sb, ++qit) {
-        const int qs = qit % QS;
-        if (!mbar_wait(&bar->q_full[qs], (qit / QS) & 1, abort_flag, g.status, 306)) { ok = false; break; }
+      for (int sb = t.sb0; sb < t.sb1; ++sb, ++qit, qc.next(QS)) {
+        const int qs = qc.s;
+        if (prof) t0 = clock64();
+        if (!mbar_wait(&bar->q_full[qs], qc.ph, abort_flag, g.status, 306)) { ok = false; break; }
+        if (prof) { t1 = clock64(); c_q += t1 - t0; t0 = t1; }
         const uint8_t* qst = qring + qs * g.q_stage_bytes;
         uint32_t r[32];
         if (g.qtype == HE_Q4_K) unpack_q4k(qst + (size_t)row * 144, set, r);
         else if (g.qtype == HE_Q6_K) unpack_q6k(qst + (size_t)row * 224, set, r);
         else unpack_q80(qst, row, set, r);
-        // the operand stage is reused every super-block: wait until the MMAs of the previous one have read it
-        if (!mbar_wait(&bar->a_empty[set], (qit & 1) ^ 1, abort_flag, g.status, 307)) { ok = false; break; }
+        // the set's operand stages are reused every AD super-blocks: wait until the MMAs that read this one
+        // AD super-blocks ago are done
+        const int a = SMALL ? (int)(qit % AD) : set + N_SETS * (int)(qit % AD);
+        if (prof) { t1 = clock64(); c_math += t1 - t0; t0 = t1; }
+        if (!mbar_wait(&bar->a_empty[a], ((qit / AD) & 1) ^ 1, abort_flag, g.status, 307)) { ok = false; break; }
+        if (prof) { t1 = clock64(); c_a += t1 - t0; t0 = t1; }
         tc_fence_after();
-        tmem_st_32x32(a_tmem, r);
+        tmem_st_32x32(a_tmem0 + (qit % AD) * (N_SETS * A_STAGE_COLS), r);
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) {
-          mbar_arrive(&bar->a_full[set]);
+          mbar_arrive(&bar->a_full[a]);
           mbar_arrive(&bar->q_empty[qs]);
         }
+        if (prof) { t1 = clock64(); c_st += t1 - t0; }
       }
+    }
+    if (prof && lane == 0) {
+      g.dbg[0] = c_q; g.dbg[1] = c_math; g.dbg[2] = c_a; g.dbg[3] = c_st; g.dbg[4] = qit;
     }
   } else if (warp >= 4 && warp < 8) {
     // ------------------------------------------------------------ epilogue (warps 4..7): transposed store
@@ -536,7 +655,7 @@ __device__ __forceinline__ void gemm_wq_body(const CUtensorMap& tmX, const CUten
       tc_fence_after();
       const int n = t.tn * WN + q * 32 + lane;               // output column of this thread
       const bool n_ok = n < g.N;
-      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * D_COLS;
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * d_cols;
       const int m0 = tmj * mt;
       const int m_lim = min(mt, g.M - m0);                   // live activation rows of this tile
 #pragma unroll 1
@@ -663,13 +782,19 @@ __device__ __forceinline__ void gemm_wq_body(const CUtensorMap& tmX, const CUten
 __global__ void __launch_bounds__(NTHREADS_WQ, 1)
 gemm_wq_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmQ0,
                const __grid_constant__ CUtensorMap tmQ1, const WqArgs g) {
-  gemm_wq_body<false>(tmX, tmQ0, tmQ1, g, nullptr);
+  gemm_wq_body<false, false>(tmX, tmQ0, tmQ1, g, nullptr);
+}
+
+__global__ void __launch_bounds__(NTHREADS_WQ, 1)
+gemm_wq_small_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmQ0,
+                     const __grid_constant__ CUtensorMap tmQ1, const WqArgs g) {
+  gemm_wq_body<false, true>(tmX, tmQ0, tmQ1, g, nullptr);
 }
 
 __global__ void __launch_bounds__(NTHREADS_WQ_RS, 1)
 gemm_wq_rs_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmQ0,
                   const __grid_constant__ CUtensorMap tmQ1, const WqArgs g, const __grid_constant__ WqFuse f) {
-  gemm_wq_body<true>(tmX, tmQ0, tmQ1, g, &f);
+  gemm_wq_body<true, false>(tmX, tmQ0, tmQ1, g, &f);
 }
 
 // out[m][n] (+)= sum over splits, in split order (deterministic).  mode 0: fp32 store, 1: fp32 add in place.
@@ -770,19 +895,39 @@ bool pair_mode_enabled() {
   return v != 0;
 }
 
+// HE_GEMMQ_SMALL=0 turns the deep-ring variant for tiles of <= 48 rows off (for comparisons).
+bool small_mode_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("HE_GEMMQ_SMALL");
+    v = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return v != 0;
+}
+
 int pick_mt(int M, bool grouped) {
   if (grouped) return 128;
   if (M >= MT_MAX) return MT_MAX;
   return (M + 15) & ~15;
 }
 
+long long* g_debug_counters = nullptr;
+
 int launch_wq(const void* A, long long lda, int a_cols, const void* B, int qtype, long long b_rows, WqArgs g,
               int num_sms, cudaStream_t stream, const WqFuse* fuse = nullptr) {
   if (g.K % 256 != 0) return -HE_ERR_BAD_ARG;
   if (a_cols <= 0 || a_cols > g.K || a_cols % 8 != 0) return -HE_ERR_BAD_ARG;
   const int row_bytes = qtype == HE_Q4_K ? 144 : (qtype == HE_Q6_K ? 224 : 272);
-  g.x_stage_bytes = (g.mt * BK * 2 + 1023) & ~1023;
+  g.dbg = g_debug_counters;
+  const bool small = small_mode_enabled() && g.mt <= 48 && g.tile_group == nullptr && fuse == nullptr;
+  g.x_kb = small ? X_KB_WIDE : 1;
+  g.a_depth = small ? A_DEPTH_MAX : 1;
+  g.x_stage_bytes = (g.x_kb * g.mt * BK * 2 + 1023) & ~1023;
   g.q_stage_bytes = (WN * row_bytes + 1023) & ~1023;
+  {
+    const int tiles_m0 = (g.M + g.mt - 1) / g.mt;
+    g.pair = (pair_mode_enabled() && g.tile_group == nullptr && g.k_splits == 1 && tiles_m0 >= 2) ? 1 : 0;
+  }
   g.q_stages = (SMEM_BUDGET - XSTAGES * g.x_stage_bytes) / g.q_stage_bytes;
   if (g.q_stages > QSTAGES_MAX) g.q_stages = QSTAGES_MAX;
   if (g.q_stages < 2) return -HE_ERR_BAD_ARG;
@@ -792,13 +937,17 @@ int launch_wq(const void* A, long long lda, int a_cols, const void* B, int qtype
   rc = make_q_maps(&q0, &q1, B, qtype, b_rows, g.K);
   if (rc != 0) return rc;
   const int tiles_m = (g.M + g.mt - 1) / g.mt;
-  g.pair = (pair_mode_enabled() && g.tile_group == nullptr && g.k_splits == 1 && tiles_m >= 2) ? 1 : 0;
   const long long tiles = (long long)(g.pair ? (tiles_m + 1) / 2 : tiles_m) * ((g.N + WN - 1) / WN) * g.k_splits;
   const int grid = (int)(tiles < num_sms ? tiles : num_sms);
   if (fuse != nullptr) {
     cudaError_t e = cudaFuncSetAttribute(gemm_wq_rs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_WQ);
     if (e != cudaSuccess) return (int)e;
     gemm_wq_rs_kernel<<<grid, NTHREADS_WQ_RS, SMEM_WQ, stream>>>(tmX, q0, q1, g, *fuse);
+  } else if (small) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_wq_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)SMEM_WQ);
+    if (e != cudaSuccess) return (int)e;
+    gemm_wq_small_kernel<<<grid, NTHREADS_WQ, SMEM_WQ, stream>>>(tmX, q0, q1, g);
   } else {
     cudaError_t e = cudaFuncSetAttribute(gemm_wq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_WQ);
     if (e != cudaSuccess) return (int)e;
@@ -809,6 +958,13 @@ int launch_wq(const void* A, long long lda, int a_cols, const void* B, int qtype
 }
 
 }  // namespace
+
+// Developer aid (builds with -DHE_WQ_PROFILE=1, a no-op otherwise): with a device array of >= 32 int64 set here, CTA 0
+// of every following quantised GEMM records the
+// cycles its roles spent waiting ([0..4] one unpack warp: raw-block wait, expansion, operand-stage wait, TMEM store,
+// super-blocks; [8..12] MMA issuer: operand wait, activation wait, accumulator wait, total, k-blocks; [16..18] raw
+// block producer: free-stage wait, total, stages).  Null (the default) turns it off.
+HE_API void he_gemm_q_debug_counters(void* dev_i64x32) { g_debug_counters = (long long*)dev_i64x32; }
 
 // C[M][N] = A[M][K] (bf16) * W[N][K]^T where W is `b_rows` rows in the device layout of `qtype` (Q4_K / Q6_K / Q8_0),
 // expanded to bf16 inside the pipeline.  epi: 0 bf16 store, 1 fp32 store, 2 fp32 accumulate into C.
@@ -868,6 +1024,13 @@ HE_API int he_gemm_q_splitk_det(const void* A, long long lda, const void* B, int
   g.mt = pick_mt(M, false);
   g.k_splits = (int)(plan & 0xffffffffll);
   g.sb_per = (int)(plan >> 32);
+  if (g.k_splits == 1) {
+    // enough tiles to fill the GPU without splitting: one CTA owns each output tile, so it stores (or adds, one add
+    // per element: order-free) straight into `out` and no reduction pass runs
+    g.C = out; g.ldc = ldo; g.epi = mode == 1 ? 2 : 1;
+    g.status = (int*)status;
+    return launch_wq(A, lda, K, B, qtype, b_rows, g, num_sms, stream);
+  }
   g.split_stride = (long long)M * N;
   g.tile_group = nullptr;
   g.status = (int*)status;

@@ -209,3 +209,222 @@ class MTPCycle(ChainVerifyCycle):
         txn.advance(Stage.DRAFTED)
         res = self._verify_accept_commit(txn, slots, positions, t0, drafts, temperature, seeds, counters)
         return res, txn
+
+
+class GraphedMTPCycle(MTPCycle):
+    """The greedy NextN cycle -- propose(K) -> verify -> accept -> commit -> cursor update -- captured as ONE CUDA
+    graph per (rows, depth, context bucket) and launched through the native cycle launcher with the full stage
+    mask; the only read-back is the accept counts (returned by the launcher) and the emitted ids.
+
+    Everything a cycle reads is resident on the device and advanced by the graph itself: slots, the last committed
+    token and its position per row, the per-slot hidden seed of the NextN block.  A following cycle over the same
+    rows needs no host -> device copy at all; rows are (re)installed only when the host's view of (slot, token,
+    position) differs from what the previous cycle left (admission, a finished row, a plain decode step between).
+    Sampled verification, override drafts and chains of more than 8 verify rows take the eager path of the parent.
+    Reference: ``hipengine/speculative/native_cycle_graph.cpp:1-300`` (one native call per cycle over a captured
+    graph, stage mask PROPOSE | VERIFY | ACCEPT | COMMIT | UPDATE_CURSORS).
+    """
+
+    def __init__(self, ex, max_depth: int = 3, max_requests: int = 8):
+        super().__init__(ex, max_depth, max_requests)
+        dev, cfg = ex.device, ex.cfg
+        R, Kd = max_requests, max_depth
+        T = self.max_rows
+        i32 = lambda *s: torch.zeros(*s, dtype=torch.int32, device=dev)
+        i64 = lambda *s: torch.zeros(*s, dtype=torch.int64, device=dev)
+        self.slot, self.slot64, self.tok, self.pos = i32(R), i64(R), i64(R), i32(R)
+        self.dpos, self.dctx, self.dcur = i32(Kd, R), i32(Kd, R), i64(Kd, R)
+        self.drafts, self.out = i64(R, Kd), i64(R, Kd + 1)
+        self.vtok, self.vslot, self.vpos, self.vctx = i64(T), i32(T), i32(T), i32(T)
+        self.hp = torch.zeros(R, cfg.hidden, dtype=torch.float32, device=dev)
+        self.hid_next = torch.zeros(Kd, R, cfg.hidden, dtype=torch.float32, device=dev)
+        self.vlogits = torch.empty(GEMV_MAX_ROWS, cfg.vocab, dtype=torch.float32, device=dev)
+        self.vhid = torch.empty(GEMV_MAX_ROWS, cfg.hidden, dtype=torch.float32, device=dev)
+        self.picked = torch.empty(R, cfg.hidden, dtype=torch.float32, device=dev)
+        self.seg_r = torch.arange(R + 1, dtype=torch.int32, device=dev)
+        self.graphs = {}
+        self._consts = {}
+        self._mirror = None                     # host view of (slots, tokens, positions) the device rows hold
+        self.graph_stats = {"captures": 0, "replays": 0, "installs": 0, "eager": 0, "kernels_per_graph": {}}
+
+    # ------------------------------------------------------------------ resident rows
+    def _install(self, slots, tokens, positions) -> None:
+        n = len(slots)
+        self.slot[:n].copy_(torch.tensor(slots, dtype=torch.int32), non_blocking=True)
+        self.slot64[:n].copy_(torch.tensor(slots, dtype=torch.int64), non_blocking=True)
+        self.tok[:n].copy_(torch.tensor(tokens, dtype=torch.int64), non_blocking=True)
+        self.pos[:n].copy_(torch.tensor(positions, dtype=torch.int32), non_blocking=True)
+        self.graph_stats["installs"] += 1
+
+    def _const(self, R: int, Kd: int):
+        key = (R, Kd)
+        c = self._consts.get(key)
+        if c is None:
+            dev = self.ex.device
+            T = R * (Kd + 1)
+            c = {"seg_start": torch.arange(R + 1, dtype=torch.int32, device=dev) * (Kd + 1),
+                 "tok_seg": torch.arange(T, dtype=torch.int32, device=dev) // (Kd + 1),
+                 "off": torch.arange(Kd + 1, dtype=torch.int32, device=dev)[None, :]}
+            if Kd != self.max_depth:            # contiguous [R, Kd] / [R, Kd + 1] buffers of their own
+                c["drafts_k"] = torch.zeros(R, Kd, dtype=torch.int64, device=dev)
+                c["out_k"] = torch.zeros(R, Kd + 1, dtype=torch.int64, device=dev)
+            self._consts[key] = c
+        return c
+
+    # ------------------------------------------------------------------ the cycle body (graph-safe: no host reads)
+    def _body(self, R: int, Kd: int, max_ctx: int) -> None:
+        ex = self.ex
+        c = self._const(R, Kd)
+        T = R * (Kd + 1)
+        slot, tok, pos = self.slot[:R], self.tok[:R], self.pos[:R]
+        # ---- propose: K passes of the NextN block
+        torch.index_select(self.h_prev, 0, self.slot64[:R], out=self.hp[:R])
+        cur, hp = tok, self.hp[:R]
+        for j in range(Kd):
+            torch.add(pos, j, out=self.dpos[j, :R])
+            torch.add(pos, j + 1, out=self.dctx[j, :R])
+            b = BatchDesc(cur, slot, self.dpos[j, :R], self.dctx[j, :R], self.seg_r[:R + 1], slot, self.seg_r[:R],
+                          R, R, max_ctx)
+            h = ex.nextn_forward(b, hp)
+            lg = ex.nextn_logits(h, hidden_out=self.hid_next[j, :R])
+            ex.greedy(lg[:R], self.dcur[j, :R])
+            self.drafts[:R, j].copy_(self.dcur[j, :R])
+            cur, hp = self.dcur[j, :R], self.hid_next[j, :R]
+        # ---- verify: target forward over [t0, d1 .. dK] per row, recurrent state journalled per verify row
+        vt = self.vtok[:T].view(R, Kd + 1)
+        vt[:, 0].copy_(tok)
+        vt[:, 1:].copy_(self.drafts[:R, :Kd])
+        self.vslot[:T].view(R, Kd + 1).copy_(slot[:, None].expand(R, Kd + 1))
+        torch.add(pos[:, None], c["off"], out=self.vpos[:T].view(R, Kd + 1))
+        torch.add(self.vpos[:T], 1, out=self.vctx[:T])
+        vb = BatchDesc(self.vtok[:T], self.vslot[:T], self.vpos[:T], self.vctx[:T], c["seg_start"], slot,
+                       c["tok_seg"], T, R, max_ctx)
+        journal = {"conv": {i: t[:T] for i, t in self.journal["conv"].items()},
+                   "gdn": {i: t[:T] for i, t in self.journal["gdn"].items()}}
+        h = ex.forward(vb, journal=journal)
+        ex.logits(h, out=self.vlogits[:T], hidden_out=self.vhid[:T])
+        # ---- accept + commit + cursors
+        tgt = self.am_ids[:T]
+        ex.greedy(self.vlogits[:T], tgt)
+        K.spec_accept_greedy(self.drafts[:R, :Kd] if Kd == self.max_depth else self._drafts_k(R, Kd),
+                             tgt.view(R, Kd + 1), self.n_accept[:R], self._out_k(R, Kd))
+        K.spec_commit(self.n_accept[:R], self._out_k(R, Kd), tok, pos, None, self.commit_row[:R],
+                      self.hidden_row[:R])
+        ex.commit_journal(journal, slot, self.commit_row[:R])
+        K.gather_rows_f32(self.vhid[:T], self.hidden_row[:R], self.picked[:R])
+        self.h_prev.index_copy_(0, self.slot64[:R], self.picked[:R])
+
+    def _drafts_k(self, R: int, Kd: int) -> torch.Tensor:
+        """Contiguous [R, Kd] view of the drafts for a depth below the maximum (own buffer per depth)."""
+        buf = self._const(R, Kd)["drafts_k"]
+        buf.copy_(self.drafts[:R, :Kd])
+        return buf
+
+    def _out_k(self, R: int, Kd: int) -> torch.Tensor:
+        if Kd == self.max_depth:
+            return self.out[:R]
+        return self._const(R, Kd)["out_k"]
+
+    def _snapshot(self, R: int):
+        ex = self.ex
+        sl = self.slot64[:R]
+        return {"tok": self.tok.clone(), "pos": self.pos.clone(), "hprev": self.h_prev[sl].clone(), "sl": sl,
+                "conv": {i: t[sl].clone() for i, t in ex.conv_state.items()},
+                "gdn": {i: t[sl].clone() for i, t in ex.gdn_state.items()}}
+
+    def _restore(self, s) -> None:
+        ex = self.ex
+        self.tok.copy_(s["tok"])
+        self.pos.copy_(s["pos"])
+        self.h_prev[s["sl"]] = s["hprev"]
+        for i, t in ex.conv_state.items():
+            t[s["sl"]] = s["conv"][i]
+        for i, t in ex.gdn_state.items():
+            t[s["sl"]] = s["gdn"][i]
+
+    # ------------------------------------------------------------------ one cycle
+    @torch.no_grad()
+    def cycle(self, slots, last_tokens, positions, depth, temperature=None, seeds=None, counters=None,
+              draft_override=None):
+        from ..core import runtime as RT
+        from ..models.decode_graph import ctx_bucket
+        ex = self.ex
+        R, Kd = len(slots), depth
+        sampled = temperature is not None and any(t > 0 for t in temperature)
+        if (sampled or draft_override is not None or R * (Kd + 1) > GEMV_MAX_ROWS or R > self.max_requests
+                or not 1 <= Kd <= self.max_depth):
+            self.graph_stats["eager"] += 1
+            self._mirror = None
+            return super().cycle(slots, last_tokens, positions, depth, temperature, seeds, counters, draft_override)
+        if self.journal is None:
+            self.journal = ex.alloc_journal(self.max_rows)
+        want = (tuple(slots), tuple(int(t) for t in last_tokens), tuple(int(p) for p in positions))
+        if want != self._mirror:
+            self._install(*want)
+        txn = SpecTransaction(list(range(R)))
+        for st in (Stage.RESERVED, Stage.TARGET_OPEN, Stage.PROVIDER_OPEN):
+            txn.advance(st)
+        key = (R, Kd, ctx_bucket(max(positions) + Kd + 1))
+        saved_small = ex.small_rows
+        ex.small_rows = GEMV_MAX_ROWS           # verify rows see the numerics of plain decode (see the parent)
+        try:
+            g = self.graphs.get(key)
+            if g is None:
+                snap = self._snapshot(R)
+                self._body(R, Kd, key[2])       # warm-up: scratch growth and function attributes settle here
+                torch.cuda.synchronize()
+                self._restore(snap)
+                k0 = K.launch_count()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    self._body(R, Kd, key[2])
+                self.graph_stats["kernels_per_graph"][key] = K.launch_count() - k0
+                self._restore(snap)
+                self.graphs[key] = g
+                self.graph_stats["captures"] += 1
+        finally:
+            ex.small_rows = saved_small
+        exec_h = RT.graph_exec_handle(g)
+        n_host = None
+        if exec_h:
+            ctl = RT.make_control(RT.STAGES_FULL_CYCLE, R, Kd, wait=True,
+                                  status_word=K.status_tensor(ex.device).data_ptr(),
+                                  n_accept=self.n_accept.data_ptr())
+            res = RT.cycle_launch(ctl, exec_h, torch.cuda.current_stream().cuda_stream)
+            if res.rc != 0:
+                raise RuntimeError(f"native cycle launch failed: rc={res.rc}")
+            if res.device_status != 0:
+                raise K.DeviceStatusError(f"device status {res.device_status} after a speculative cycle")
+            n_host = [int(res.n_accept[r]) for r in range(R)]
+        else:
+            g.replay()
+        K.add_launches(self.graph_stats["kernels_per_graph"][key])
+        self.graph_stats["replays"] += 1
+        for st in (Stage.DRAFTED, Stage.VERIFIED, Stage.ACCEPTED):
+            txn.advance(st)
+        out_host = self._out_k(R, Kd).tolist()          # the emitted ids: the cycle's one read-back besides counts
+        if n_host is None:
+            n_host = self.n_accept[:R].tolist()
+        txn.advance(Stage.READBACK)
+        txn.advance(Stage.COMMITTING)
+        txn.advance(Stage.COMMITTED)
+        res_l = []
+        new_tok, new_pos = [], []
+        for r in range(R):
+            n = int(n_host[r])
+            res_l.append(SpecCycleResult([int(x) for x in out_host[r][:n + 1]], Kd, n, list(txn.trace)))
+            new_tok.append(int(out_host[r][n]))
+            new_pos.append(int(positions[r]) + n + 1)
+            self.stats["drafted"] += Kd
+            self.stats["accepted"] += n
+        self.stats["cycles"] += 1
+        self._mirror = (tuple(slots), tuple(new_tok), tuple(new_pos))
+        return res_l, txn
+
+    def reset_slot(self, slot: int) -> None:
+        super().reset_slot(slot)
+        self._mirror = None
+
+    def after_prefill(self, batch, h) -> None:
+        super().after_prefill(batch, h)
+        self._mirror = None

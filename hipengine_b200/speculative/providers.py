@@ -128,8 +128,13 @@ def register_speculative_provider(name: str, factory: Callable) -> None:
 def _mtp_factory(ex, cfg: SpeculativeProviderConfig, max_requests: int):
     if not getattr(ex, "has_nextn", False):
         return None
-    from .mtp import MTPCycle
-    return MTPCycle(ex, max_depth=max(1, cfg.max_depth), max_requests=max_requests)
+    import os
+    from .mtp import GraphedMTPCycle, MTPCycle
+    # one captured graph per cycle on a single-GPU executor; the eager cycle elsewhere (HE_SPEC_GRAPH=0 forces it)
+    single = getattr(getattr(ex, "ctx", None), "world", 1) == 1
+    graphed = single and str(ex.device).startswith("cuda") and os.environ.get("HE_SPEC_GRAPH", "1") != "0"
+    cls = GraphedMTPCycle if graphed else MTPCycle
+    return cls(ex, max_depth=max(1, cfg.max_depth), max_requests=max_requests)
 
 
 def _prompt_lookup_factory(ex, cfg: SpeculativeProviderConfig, max_requests: int):

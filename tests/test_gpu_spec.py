@@ -137,6 +137,45 @@ def test_mtp_cycle_reproduces_greedy_decode(mode):
         assert accepted_total >= 9
 
 
+@pytest.mark.parametrize("n_req", [1, 2])
+def test_graphed_mtp_cycle_is_one_launch_and_reproduces_greedy_decode(n_req):
+    """propose -> verify -> accept -> commit -> cursor update as ONE captured graph launched through the native
+    cycle launcher: tokens equal plain greedy decoding, one capture and one row install serve every cycle."""
+    from hipengine_b200.core import runtime as RT
+    from hipengine_b200.models.executor import HybridExecutor, make_batch
+    from hipengine_b200.speculative.mtp import GraphedMTPCycle
+    w = build_random_model(CFG, seed=0, std=0.05).to("cuda")
+    prompts = [_prompt(24, seed=5), _prompt(31, seed=9)][:n_req]
+    n_new = 14
+    want = [_greedy_reference_tokens(w, p, n_new) for p in prompts]
+    ex = HybridExecutor(w, max_slots=3, max_context=256)
+    mtp = GraphedMTPCycle(ex, max_depth=3, max_requests=2)
+    slots = [2, 0][:n_req]
+    got = []
+    for slot, p in zip(slots, prompts):
+        b = make_batch([(slot, 0, p)], "cuda")
+        h = ex.forward(b)
+        mtp.after_prefill(b, h)
+        got.append([int(ex.logits(h[b.T - 1:b.T]).argmax(-1))])
+    launches0 = RT._lib().he_native_graph_launches()
+    cycles = 0
+    while min(len(g) for g in got) < n_new:
+        pos = [len(p) + len(g) - 1 for p, g in zip(prompts, got)]
+        res, txn = mtp.cycle(slots, [g[-1] for g in got], pos, 3)
+        assert txn.trace[-1] == "committed"
+        for g, r in zip(got, res):
+            assert 1 <= len(r.tokens) == r.accepted + 1 <= 4
+            g += r.tokens
+        cycles += 1
+    for g, wv in zip(got, want):
+        n = min(len(g), n_new)
+        assert g[:n] == wv[:n], (g, wv)
+    st = mtp.graph_stats
+    assert st["captures"] == 1 and st["replays"] == cycles and st["installs"] == 1 and st["eager"] == 0
+    assert RT._lib().he_native_graph_launches() - launches0 == cycles      # one native launch per cycle
+    assert list(st["kernels_per_graph"].values())[0] > 20
+
+
 def test_lookup_cycle_with_known_chains_needs_no_nextn_block():
     """Chain verify with host-supplied drafts on a checkpoint WITHOUT a NextN block: the true greedy continuation is
     accepted in full (plus the bonus token), a corrupted chain is cut at the first wrong token, and the committed
