@@ -179,15 +179,14 @@ def bench_attn_decode(ctx, H=24, Hkv=4, D=256, rows=1):
     pk = peaks()
     page = 16
     n_pages = (ctx + page - 1) // page
-    nvar = max(2, int(260e6 // (n_pages * 2 * Hkv * page * D * 2)) + 1)
-    caches = [(torch.randn(n_pages + 1, 2, Hkv, page, D, device="cuda") * 0.3).bfloat16() for _ in range(nvar)]
-    bt = (torch.arange(n_pages, device="cuda", dtype=torch.int32) + 1).reshape(1, -1).repeat(rows, 1).contiguous()
+    nvar = max(2, int(260e6 // (rows * n_pages * 2 * Hkv * page * D * 2)) + 1)
+    caches = [(torch.randn(rows * n_pages + 1, 2, Hkv, page, D, device="cuda") * 0.3).bfloat16() for _ in range(nvar)]
+    bt = (torch.arange(rows * n_pages, device="cuda", dtype=torch.int32) + 1).reshape(rows, n_pages).contiguous()
     slot = torch.arange(rows, device="cuda", dtype=torch.int32)
     ctx_len = torch.full((rows,), ctx, device="cuda", dtype=torch.int32)
     q = torch.randn(rows, H, D, device="cuda").bfloat16()
     gate = torch.randn(rows, H, D, device="cuda").bfloat16()
-    split_len = 64 if ctx <= 8192 else (128 if ctx <= 32768 else 256)
-    max_splits = (ctx + split_len - 1) // split_len
+    split_len, max_splits = Kn.attn_decode_split(ctx, rows, Hkv)
     part = torch.empty(Kn.attn_decode_scratch_floats(rows, H, max_splits, D), device="cuda")
     out = torch.empty(rows, H * D, device="cuda", dtype=torch.bfloat16)
     fn = lambda i: Kn.attn_decode(q, gate, caches[i], bt, slot, ctx_len, part, out, H, Hkv, D, page, split_len,
@@ -227,9 +226,50 @@ def bench_fused_allreduce_gemm(M, N, K, phases=7):
             "fused_ms": round(ms_f, 4), "gemm_plus_add_ms": round(ms_p, 4), "fused_tflops": round(tf / ms_f, 1)}
 
 
+def bench_decode_step(rows_list, model="qwen35-27b", ctx=1024, small_rows=None):
+    """Whole-model packed decode step (captured graph) at R concurrent rows, each at context `ctx`: the cost a
+    continuous-batching round or a verify chain pays.  `small_rows` overrides the row count up to which the int8 GEMV
+    path is taken (above it the split-K tensor-core path streams the quantised blocks once for all rows)."""
+    from hipengine_b200.loading.synth import build_random_model
+    from hipengine_b200.models import make_executor
+    from hipengine_b200.models.config import NAMED_CONFIGS
+    from hipengine_b200.models.decode_graph import DecodeGraphRunner
+    cfg = NAMED_CONFIGS[model]
+    R = max(rows_list)
+    w = build_random_model(cfg, seed=0, device="cuda", recipe="q4_k_m")
+    ex = make_executor(w, device="cuda", max_slots=R, max_context=ctx + 64)
+    del w
+    if small_rows is not None:
+        ex.small_rows = small_rows
+    runner = DecodeGraphRunner(ex, max_rows=R)
+    out = []
+    for r in rows_list:
+        runner.set_rows(list(range(r)), [7] * r, [ctx - 1] * r)
+        for _ in range(3):
+            runner.step(r, ctx + 48)
+        torch.cuda.synchronize()
+        n = 20
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            runner.step(r, ctx + 48)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / n
+        out.append({"kernel": f"decode_step[{model}]", "rows": r, "ctx": ctx, "small_rows": ex.small_rows,
+                    "ms_per_step": round(ms, 3), "tok_s_aggregate": round(r * 1e3 / ms, 1)})
+        runner.set_rows(list(range(r)), [7] * r, [ctx - 1] * r)
+    from hipengine_b200.ops import kernels as Kn
+    Kn.check_status()
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "gemmq", "gemv", "gdn", "conv", "attn", "fusedar", "all"])
+    ap.add_argument("what", choices=["gemm", "gemmq", "gemv", "gdn", "conv", "attn", "fusedar", "step", "all"])
+    ap.add_argument("--rows-list", default="1,2,4,8,16,32,64")
+    ap.add_argument("--model", default="qwen35-27b")
+    ap.add_argument("--small-rows", type=int, default=None)
     ap.add_argument("--t", type=int, default=4096)
     ap.add_argument("--ctx", type=int, default=4096)
     ap.add_argument("--m", type=int, default=4096)
@@ -254,6 +294,8 @@ def main():
         out.append(bench_conv(a.t))
     elif a.what == "attn":
         out.append(bench_attn_decode(a.ctx, rows=a.rows))
+    elif a.what == "step":
+        out += bench_decode_step([int(x) for x in a.rows_list.split(",")], a.model, a.ctx, a.small_rows)
     elif a.what == "fusedar":
         for ph in ([1, 3, 7] if a.phases == 0 else [a.phases]):
             out.append(bench_fused_allreduce_gemm(a.m, a.n, a.k, ph))

@@ -7,7 +7,10 @@
 // hipengine/kernels/hip_gfx1100/attention/paged_attn_decode.hip (chunk = KV block, reduce_threads = head_dim,
 // gate fused in the reducer) and the live-span oracle hipengine/kernels/cpu_reference/ops.py:2895-2997.
 // KV cache layout: [n_pages][2 (k,v)][Hkv][PAGE][D] bf16, addressed through block_table[slot][pos / PAGE].
+#include <cstdlib>
+
 #include "common.cuh"
+#include "sm100.cuh"
 
 using namespace he;
 
@@ -24,6 +27,7 @@ struct AttnDecArgs {
   int split_len, max_splits;
   int window;                 // > 0: only the last `window` keys are visible
   float scale;
+  int* status;                // optional status word: a bounded wait that gave up records its code here
 };
 
 namespace {
@@ -182,6 +186,262 @@ __global__ void __launch_bounds__(256) attn_decode_split_kernel(const AttnDecArg
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Tensor-core split kernel.  Same contract as attn_decode_split_kernel (one CTA per (row, kv head, key span), partial
+// outputs + (max, sum) per span), built so that the K/V bytes of a span are touched exactly once on every level:
+//   producer warp  : streams whole KV pages (16 keys x D) row by row with 1-D bulk copies into a ring of stages of
+//                    64 keys (rows padded by 16 bytes, which makes every ldmatrix conflict-free); first all K tiles
+//                    of the span, then all V tiles, so V is already in flight while the softmax statistics run;
+//   phase 1        : S = Q K^T with mma.sync m16n8k16 (the G <= 8 query heads of the group are the rows of the M
+//                    tile; warp w takes the w-th page of every stage), scores to shared memory;
+//   phase 2        : per-head max / sum over the span, P = exp(S - max) as bf16 rows in shared memory;
+//   phase 3        : O = P V, warp w owns D/4 output columns and walks every stage.
+// Reads of shared memory equal the bytes copied in; the span's keys never pass through registers as scalars.
+namespace mma_dec {
+
+constexpr int NCONS = 4;                    // consumer warps
+constexpr int NTHREADS = (NCONS + 1) * 32;  // + one producer warp
+constexpr int TILE_KEYS = 64;
+constexpr int MAX_STAGES = 5;
+
+template <int D>
+__host__ __device__ constexpr int pitch() { return D * 2 + 16; }
+// ring depth: one stage per tile the span has (K and V), at most five, and what ~170 KB of shared memory hold
+template <int D>
+__host__ __device__ inline int stages_for(int split_len) {
+  const int uses = 2 * ((split_len + TILE_KEYS - 1) / TILE_KEYS);
+  const int fit = (170 * 1024) / (TILE_KEYS * pitch<D>());
+  const int cap = fit < MAX_STAGES ? fit : MAX_STAGES;
+  return uses < cap ? uses : cap;
+}
+template <int D>
+__host__ __device__ inline size_t smem_bytes(int G, int split_len) {
+  return (size_t)stages_for<D>(split_len) * TILE_KEYS * pitch<D>() + 8 * (size_t)pitch<D>() +
+         8 * ((size_t)split_len * 2 + 16) + (size_t)G * split_len * 4 + 2 * MAX_STAGES * 8 + 16;
+}
+
+__device__ __forceinline__ void ldsm_x2(uint32_t addr, uint32_t& r0, uint32_t& r1) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+// D (16x8 fp32) += A (16x16 bf16, rows 8..15 zero: a1 = a3 = 0) * B (16x8 bf16)
+__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+  const uint32_t z = 0u;
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(z), "r"(a2), "r"(z), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void bulk_row(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               :
+               : "r"(sm100::smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(sm100::smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void cons_sync() { asm volatile("bar.sync 1, %0;" ::"n"(NCONS * 32) : "memory"); }
+
+template <int D, int G>
+__global__ void __launch_bounds__(NTHREADS) attn_decode_mma_kernel(const AttnDecArgs a) {
+  static_assert(G <= 8 && D % 64 == 0, "group of <= 8 query heads, head_dim a multiple of 64");
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  constexpr int PITCH = pitch<D>();
+  constexpr int STAGE = TILE_KEYS * PITCH;
+  const int sp = blockIdx.x, hk = blockIdx.y, r = blockIdx.z;
+  pdl_wait();
+  pdl_launch();
+  const int ctx = a.ctx_len[r];
+  const int start = (a.window > 0 && ctx > a.window) ? ctx - a.window : 0;
+  const int k0 = start + sp * a.split_len;
+  if (k0 >= ctx) return;
+  const int n = min(a.split_len, ctx - k0);
+  const int ntile = (n + TILE_KEYS - 1) / TILE_KEYS;
+  const int NST = stages_for<D>(a.split_len);
+  const int PP = a.split_len * 2 + 16;                 // pitch of a P row (bytes)
+  uint8_t* ring = smem_raw;
+  uint8_t* q_s = ring + (size_t)NST * STAGE;           // [8][PITCH] bf16 rows (rows >= G zero)
+  uint8_t* p_s = q_s + 8 * PITCH;                      // [8][PP] bf16 rows
+  float* sc = reinterpret_cast<float*>(p_s + 8 * (size_t)PP);     // [G][split_len]
+  uint64_t* full = reinterpret_cast<uint64_t*>(sc + (size_t)G * a.split_len);
+  uint64_t* empty = full + MAX_STAGES;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + MAX_STAGES);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int* bt = a.block_table + (size_t)a.slot[r] * a.max_pages;
+
+  if (tid == 0) {
+    for (int s = 0; s < NST; ++s) {
+      sm100::mbar_init(&full[s], 1);
+      sm100::mbar_init(&empty[s], NCONS);
+    }
+    *abort_flag = 0;
+    sm100::mbar_fence_init();
+  }
+  __syncthreads();
+
+  if (warp == NCONS) {
+    // ------------------------------------------------------------ producer: K tiles, then V tiles
+    int s = 0;
+    uint32_t ph = 0;
+    for (int u = 0; u < 2 * ntile; ++u) {
+      if (!sm100::mbar_wait(&empty[s], ph ^ 1u, abort_flag, a.status, 401)) break;
+      const int kv = u < ntile ? 0 : 1, tile = u < ntile ? u : u - ntile;
+      if (lane == 0) sm100::mbar_expect_tx(&full[s], (uint32_t)(TILE_KEYS * D * 2));
+      __syncwarp();
+#pragma unroll
+      for (int h2 = 0; h2 < TILE_KEYS / 32; ++h2) {
+        const int row = lane + 32 * h2;
+        // rows past the span re-read its last key: finite values that the zero probabilities then ignore
+        const int pos = k0 + min(tile * TILE_KEYS + row, n - 1);
+        const int pg = bt[pos / a.page];
+        const __nv_bfloat16* src =
+            a.kv_cache + ((((size_t)pg * 2 + kv) * a.Hkv + hk) * a.page + (pos % a.page)) * D;
+        bulk_row(ring + (size_t)s * STAGE + (size_t)row * PITCH, src, D * 2, &full[s]);
+      }
+      if (++s == NST) {
+        s = 0;
+        ph ^= 1u;
+      }
+    }
+    return;
+  }
+
+  // ------------------------------------------------------------ consumers
+  // Q rows of the group as bf16 (rows >= G and the P rows >= G stay zero)
+  for (int i = tid; i < 8 * (PITCH / 16); i += NCONS * 32) {
+    const int g = i / (PITCH / 16), c = i % (PITCH / 16);
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (g < G && c < D / 8) v = *reinterpret_cast<const uint4*>(a.q + ((size_t)r * a.H + hk * G + g) * D + c * 8);
+    *reinterpret_cast<uint4*>(q_s + (size_t)g * PITCH + c * 16) = v;
+  }
+  for (int i = tid; i < (8 - G) * (PP / 16); i += NCONS * 32) {
+    const int g = G + i / (PP / 16), c = i % (PP / 16);
+    *reinterpret_cast<uint4*>(p_s + (size_t)g * PP + c * 16) = make_uint4(0u, 0u, 0u, 0u);
+  }
+  cons_sync();
+
+  int s = 0;
+  uint32_t ph = 0;
+  bool ok = true;
+  // ---- phase 1: scores of 16 keys per warp and stage
+  {
+    // ldmatrix row addresses: Q (x2: k 0-7 | k 8-15 of rows 0-7), K (x4: keys 0-7 | 8-15, each k-lo | k-hi)
+    const uint32_t q_addr = sm100::smem_u32(q_s) + (lane & 7) * PITCH + ((lane >> 3) & 1) * 16;
+    const int k_row = warp * 16 + ((lane >> 4) & 1) * 8 + (lane & 7);
+    const int k_col = ((lane >> 3) & 1) * 16;
+    for (int t = 0; t < ntile && ok; ++t) {
+      if (!sm100::mbar_wait(&full[s], ph, abort_flag, a.status, 402)) { ok = false; break; }
+      const int key0 = t * TILE_KEYS + warp * 16;      // first key of this warp's page, relative to the span
+      if (key0 < n) {
+        const uint32_t k_addr = sm100::smem_u32(ring + (size_t)s * STAGE) + k_row * PITCH + k_col;
+        float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+        for (int ks = 0; ks < D / 16; ++ks) {
+          uint32_t a0, a2, b0, b1, b2, b3;
+          ldsm_x2(q_addr + ks * 32, a0, a2);
+          ldsm_x4(k_addr + ks * 32, b0, b1, b2, b3);
+          mma_16816(s0, a0, a2, b0, b1);
+          mma_16816(s1, a0, a2, b2, b3);
+        }
+        const int g = lane >> 2, kc = 2 * (lane & 3);
+        if (g < G) {
+          float* row = sc + (size_t)g * a.split_len + key0;
+          const float NEG = -INFINITY;
+          row[kc] = key0 + kc < n ? s0[0] * a.scale : NEG;
+          row[kc + 1] = key0 + kc + 1 < n ? s0[1] * a.scale : NEG;
+          row[8 + kc] = key0 + 8 + kc < n ? s1[0] * a.scale : NEG;
+          row[8 + kc + 1] = key0 + 8 + kc + 1 < n ? s1[1] * a.scale : NEG;
+        }
+      }
+      __syncwarp();
+      if (lane == 0) sm100::mbar_arrive(&empty[s]);
+      if (++s == NST) {
+        s = 0;
+        ph ^= 1u;
+      }
+    }
+  }
+  cons_sync();
+  if (*abort_flag) return;
+
+  // ---- phase 2: per-head softmax statistics of the span, P as bf16 rows
+  const int n16 = (n + 15) & ~15;                       // keys covered by the live pages
+  float* part_base = a.partial + (((size_t)r * a.H + hk * G) * a.max_splits + sp) * (D + 2);
+  for (int g = warp; g < G; g += NCONS) {
+    const float* srow = sc + (size_t)g * a.split_len;
+    __nv_bfloat16* prow = reinterpret_cast<__nv_bfloat16*>(p_s + (size_t)g * PP);
+    float m = -INFINITY;
+    for (int i = lane; i < n; i += 32) m = fmaxf(m, srow[i]);
+    m = warp_max(m);
+    float l = 0.f;
+    for (int i = lane; i < n16; i += 32) {
+      const float p = i < n ? __expf(srow[i] - m) : 0.f;
+      prow[i] = f32_to_bf16(p);
+      l += p;
+    }
+    l = warp_sum(l);
+    if (lane == 0) {
+      float* pb = part_base + (size_t)g * a.max_splits * (D + 2);
+      pb[D] = m;
+      pb[D + 1] = l;
+    }
+  }
+  cons_sync();
+
+  // ---- phase 3: O[:, warp's D/4 columns] = P V over every stage
+  constexpr int DW = D / NCONS;                          // output columns per warp
+  constexpr int NB = DW / 8;                             // 8-column blocks per warp
+  float o[NB][4];
+#pragma unroll
+  for (int j = 0; j < NB; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[j][e] = 0.f;
+  {
+    const uint32_t p_addr = sm100::smem_u32(p_s) + (lane & 7) * PP + ((lane >> 3) & 1) * 16;
+    // V (x4.trans): keys 0-7 | 8-15 of column block j, then of block j + 1
+    const int v_row = ((lane >> 3) & 1) * 8 + (lane & 7);
+    const int v_col = (warp * DW + ((lane >> 4) & 1) * 8) * 2;
+    for (int t = 0; t < ntile && ok; ++t) {
+      if (!sm100::mbar_wait(&full[s], ph, abort_flag, a.status, 403)) { ok = false; break; }
+      const uint32_t v_base = sm100::smem_u32(ring + (size_t)s * STAGE) + v_row * PITCH + v_col;
+#pragma unroll
+      for (int kk = 0; kk < TILE_KEYS / 16; ++kk) {
+        const int key0 = t * TILE_KEYS + kk * 16;
+        if (key0 < n) {
+          uint32_t a0, a2;
+          ldsm_x2(p_addr + key0 * 2, a0, a2);
+#pragma unroll
+          for (int j = 0; j < NB; j += 2) {
+            uint32_t b0, b1, b2, b3;
+            ldsm_x4_t(v_base + kk * 16 * PITCH + j * 16, b0, b1, b2, b3);
+            mma_16816(o[j], a0, a2, b0, b1);
+            mma_16816(o[j + 1], a0, a2, b2, b3);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) sm100::mbar_arrive(&empty[s]);
+      if (++s == NST) {
+        s = 0;
+        ph ^= 1u;
+      }
+    }
+  }
+  if (!ok) return;
+  const int g = lane >> 2;
+  if (g < G) {
+    float* pb = part_base + (size_t)g * a.max_splits * (D + 2) + warp * DW + 2 * (lane & 3);
+#pragma unroll
+    for (int j = 0; j < NB; ++j) *reinterpret_cast<float2*>(pb + j * 8) = make_float2(o[j][0], o[j][1]);
+  }
+}
+
+}  // namespace mma_dec
+
 // grid (H, R), block D.  Split statistics are staged in shared memory first, so the accumulation over splits
 // is a stream of independent loads instead of a chain of dependent ones.
 __global__ void attn_decode_reduce_kernel(const AttnDecArgs a) {
@@ -227,8 +487,42 @@ __global__ void attn_decode_reduce_kernel(const AttnDecArgs a) {
   a.out[(size_t)r * a.H * D + (size_t)h * D + d] = f32_to_bf16(o);
 }
 
+// HE_ATTN_DECODE=scalar keeps the CUDA-core split kernel (for comparisons).
+bool mma_decode_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("HE_ATTN_DECODE");
+    v = (e != nullptr && e[0] == 's') ? 0 : 1;
+  }
+  return v != 0;
+}
+
+template <int D, int G>
+int launch_split_mma(const AttnDecArgs& a, cudaStream_t stream) {
+  const size_t smem = mma_dec::smem_bytes<D>(G, a.split_len);
+  static size_t configured[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+  if (smem > configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(mma_dec::attn_decode_mma_kernel<D, G>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured[dev] = smem;
+  }
+  dim3 grid(a.max_splits, a.Hkv, a.R);
+  cudaError_t le = launch_pdl(mma_dec::attn_decode_mma_kernel<D, G>, grid, dim3(mma_dec::NTHREADS), smem, stream, a);
+  if (le != cudaSuccess) return (int)le;
+  return 0;
+}
+
 template <int D, int G>
 int launch_split(const AttnDecArgs& a, cudaStream_t stream) {
+  if constexpr (D >= 128 && G <= 8) {
+    // tensor-core kernel: whole 16-key pages, spans that are a multiple of 16 keys, rings that fit shared memory
+    if (mma_decode_enabled() && a.page == 16 && a.split_len % 16 == 0 &&
+        mma_dec::smem_bytes<D>(G, a.split_len) <= 220 * 1024)
+      return launch_split_mma<D, G>(a, stream);
+  }
   const size_t smem = ((size_t)G * D + (size_t)G * a.split_len + (size_t)NWARP * G * D) * sizeof(float);
   // the attribute belongs to the (function, device) pair: remember the largest value set per device
   static size_t configured[64] = {};

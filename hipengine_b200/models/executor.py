@@ -352,8 +352,7 @@ class HybridExecutor:
                                     self.block_table, slot, pos0, out[r0:r0 + n], H, Hkv, D, PAGE, cfg.scale())
                     r0 += n
                 return
-        split_len = 64 if b.max_ctx <= 8192 else (128 if b.max_ctx <= 32768 else 256)
-        max_splits = max(1, (b.max_ctx + split_len - 1) // split_len)
+        split_len, max_splits = K.attn_decode_split(b.max_ctx, T, Hkv)
         part = self.scratch.get("attn_part", (K.attn_decode_scratch_floats(T, H, max_splits, D),), torch.float32)
         K.attn_decode(q_out, gate, self.kv[i], self.block_table, b.slot, b.ctx_len, part, out, H, Hkv, D, PAGE,
                       split_len, max_splits, cfg.scale())

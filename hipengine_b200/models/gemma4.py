@@ -141,8 +141,8 @@ class Gemma4Executor(HybridExecutor):
                     r0 += n
                 return
         span = min(b.max_ctx, window) if window > 0 else b.max_ctx
-        split_len = 64 if span <= 8192 else (128 if span <= 32768 else 256)
-        max_splits = max(1, (span + split_len - 1) // split_len + (1 if window > 0 else 0))
+        split_len, max_splits = K.attn_decode_split(span, T, Hkv)
+        max_splits += 1 if window > 0 else 0
         part = self.scratch.get("attn_part", (K.attn_decode_scratch_floats(T, H, max_splits, D),), torch.float32)
         K.attn_decode(q_out, None, self.kv[i], self.block_table, b.slot, b.ctx_len, part, out, H, Hkv, D, PAGE,
                       split_len, max_splits, 1.0, window=window)

@@ -76,7 +76,7 @@ class _AttnDecArgs(C.Structure):
                 ("ctx_len", c_vp), ("partial", c_vp), ("out", c_vp),
                 ("R", C.c_int), ("H", C.c_int), ("Hkv", C.c_int), ("D", C.c_int), ("page", C.c_int),
                 ("max_pages", C.c_int), ("split_len", C.c_int), ("max_splits", C.c_int), ("window", C.c_int),
-                ("scale", C.c_float)]
+                ("scale", C.c_float), ("status", c_vp)]
 
 
 class _GdnDecodeArgs(C.Structure):
@@ -446,6 +446,16 @@ def state_commit(state: torch.Tensor, journal: torch.Tensor, seg_slot: torch.Ten
 
 # ----------------------------------------------------------------------------- attention
 
+def attn_decode_split(span: int, rows: int, Hkv: int) -> Tuple[int, int]:
+    """(split_len, max_splits) of the split-K decode attention for `rows` rows of up to `span` visible keys: spans
+    of whole 64-key tiles sized so that rows * Hkv * splits is about four CTAs per SM (one tile per CTA for a single
+    short row, up to 1024 keys per CTA for wide batches, where a CTA then streams its span through a deep ring)."""
+    want = 4 * 148
+    split_len = -(-(span * max(rows, 1) * Hkv) // want)
+    split_len = min(1024, max(64, ((split_len + 63) // 64) * 64))
+    return split_len, max(1, -(-span // split_len))
+
+
 def attn_decode_scratch_floats(R: int, H: int, max_splits: int, D: int) -> int:
     return R * H * max_splits * (D + 2)
 
@@ -461,6 +471,7 @@ def attn_decode(q: torch.Tensor, gate: Optional[torch.Tensor], kv_cache: torch.T
     a.R, a.H, a.Hkv, a.D, a.page = q.shape[0], H, Hkv, D, page
     a.max_pages = block_table.shape[1]
     a.split_len, a.max_splits, a.window, a.scale = split_len, max_splits, window, scale
+    a.status = status_tensor(q.device).data_ptr()
     assert partial.numel() >= attn_decode_scratch_floats(a.R, H, max_splits, D)
     N.check(N.lib().he_attn_decode(C.byref(a), _stream()), "he_attn_decode")
 

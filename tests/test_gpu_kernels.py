@@ -355,3 +355,54 @@ def test_gdn_chunked_scan_matches_reference(lens):
     scale_o, scale_s = want_o.abs().max(), want_s.abs().max()
     assert (out.cpu() - want_o).abs().max() / scale_o < 2e-2
     assert (state.cpu() - want_s).abs().max() / scale_s < 2e-2
+
+
+@pytest.mark.parametrize("D,H,Hkv,rows,ctxs,window", [
+    (256, 24, 4, 3, (1, 333, 1100), 0),          # 27B geometry: 6 query heads per KV head
+    (256, 8, 1, 2, (64, 2049), 0),               # 8 heads in one group, span ends on / just past a tile edge
+    (128, 8, 2, 4, (17, 500, 31, 4097), 0),
+    (512, 8, 2, 2, (700, 90), 0),                # head_dim 512 (Gemma 4 global layers)
+    (256, 8, 2, 2, (900, 300), 256),             # sliding window
+])
+def test_tensor_core_decode_attention_matches_fp32(K, D, H, Hkv, rows, ctxs, window):
+    """Split-K decode attention on mma.sync tiles (whole pages streamed by bulk copies) against fp32 PyTorch, with
+    the split sizes the engine would pick for one row and for a wide batch."""
+    page = 16
+    g = torch.Generator(device="cuda").manual_seed(D + H + rows)
+    max_ctx = max(ctxs)
+    mp = (max_ctx + page - 1) // page
+    cache = (torch.randn(rows * mp + 1, 2, Hkv, page, D, device="cuda", generator=g) * 0.5).bfloat16()
+    bt = (torch.randperm(rows * mp, device="cuda", generator=g).int() + 1).reshape(rows, mp).contiguous()
+    slot = torch.arange(rows, device="cuda", dtype=torch.int32)
+    ctx_len = torch.tensor(ctxs, device="cuda", dtype=torch.int32)
+    q = torch.randn(rows, H, D, device="cuda", generator=g).bfloat16()
+    gate = torch.randn(rows, H, D, device="cuda", generator=g).bfloat16()
+    scale = D ** -0.5
+    # fp32 reference per row
+    ref = torch.empty(rows, H, D, device="cuda")
+    G = H // Hkv
+    for r in range(rows):
+        n = ctxs[r]
+        pages = bt[r, : (n + page - 1) // page].long()
+        kk = cache[pages, 0].permute(1, 0, 2, 3).reshape(Hkv, -1, D)[:, :n].float()
+        vv = cache[pages, 1].permute(1, 0, 2, 3).reshape(Hkv, -1, D)[:, :n].float()
+        if window > 0 and n > window:
+            kk, vv = kk[:, n - window:], vv[:, n - window:]
+        for h in range(H):
+            s = (kk[h // G] @ q[r, h].float()) * scale
+            p = torch.softmax(s, -1)
+            ref[r, h] = p @ vv[h // G]
+    ref = R.bf16_round(ref) * torch.sigmoid(gate.float())
+    span = min(max_ctx, window) if window > 0 else max_ctx
+    for batch_rows in (1, 64):                    # split sizes of a single row and of a wide batch
+        split_len, max_splits = K.attn_decode_split(span, batch_rows, Hkv)
+        max_splits += 1 if window > 0 else 0
+        part = torch.full((K.attn_decode_scratch_floats(rows, H, max_splits, D),), float("nan"), device="cuda")
+        out = torch.empty(rows, H * D, device="cuda", dtype=torch.bfloat16)
+        K.attn_decode(q, gate, cache, bt, slot, ctx_len, part, out, H, Hkv, D, page, split_len, max_splits, scale,
+                      window=window)
+        torch.cuda.synchronize()
+        K.check_status()
+        got = out.float().reshape(rows, H, D)
+        assert torch.isfinite(got).all()
+        assert torch.allclose(got, ref, atol=2e-2, rtol=2e-2), (split_len, (got - ref).abs().max())
