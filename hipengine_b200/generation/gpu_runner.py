@@ -75,6 +75,14 @@ class GpuRunner(BaseRunner):
         self.pool.evict_hook = self.radix.evict
         self.free_slots = list(range(self.max_slots - 1, -1, -1))
         self.free_snaps = list(range(self.max_slots + self.n_snap - 1, self.max_slots - 1, -1))
+        # every traffic-scaled device resource besides KV pages (which the pool accounts for with its own credits) is
+        # claimed through the ledger: a request is admitted only if its whole claim set fits
+        from ..kvcache.ledger import ResourceLedger
+        self.ledger = ResourceLedger()
+        self.ledger.register("state_slots", self.max_slots)
+        self.ledger.register("snapshot_slots", self.n_snap)
+        self._claims: Dict[str, Any] = {}
+        self._snap_claims: Dict[int, Any] = {}
         self.graphs = DecodeGraphRunner(self.ex, max_rows=self.max_slots, use_graphs=config.use_cuda_graphs)
         self.resident_key: Tuple[int, ...] = ()
         self.pinned_ids = torch.zeros(max(self.max_slots, 8), dtype=torch.int64).pin_memory()
@@ -98,11 +106,17 @@ class GpuRunner(BaseRunner):
     def _free_snapshot(self, sid: int) -> None:
         if sid not in self.free_snaps:
             self.free_snaps.append(sid)
+        claim = self._snap_claims.pop(sid, None)
+        if claim is not None:
+            self.ledger.release(claim)
 
     def _alloc_snapshot(self) -> Optional[int]:
         if self.free_snaps:
-            return self.free_snaps.pop()
-        sid = self.radix.evict_snapshot()
+            from ..kvcache.ledger import ResourceClaim
+            sid = self.free_snaps.pop()
+            self._snap_claims[sid] = self.ledger.acquire(f"snapshot:{sid}", [ResourceClaim("snapshot_slots", 1)])
+            return sid
+        sid = self.radix.evict_snapshot()      # reuses a slot that is already claimed
         return sid
 
     def _copy_state(self, src: int, dst: int) -> None:
@@ -221,7 +235,10 @@ class GpuRunner(BaseRunner):
         if total > self.max_context:
             raise GenerationAdmissionRejected(
                 f"context_overflow: prompt {rs.prompt_len} + max_tokens {rs.req.max_tokens} exceeds {self.max_context}")
-        if not self.free_slots:
+        from ..kvcache.ledger import ResourceClaim, ResourceUnavailable
+        try:
+            claim = self.ledger.acquire(str(rs.rid), [ResourceClaim("state_slots", 1)])
+        except ResourceUnavailable:
             return False
         prompt = rs.req.prompt_token_ids
         match = self.radix.match(prompt, require_snapshot=self.cfg.is_hybrid) if self.use_prefix else None
@@ -232,9 +249,11 @@ class GpuRunner(BaseRunner):
         try:
             lease = self.pool.admit(rs.rid, total, shared_prefix=shared, now_tokens=rs.prompt_len)
         except PoolExhausted:
+            self.ledger.release(claim)
             if self.pool.pages_for(total) > self.pool.n_pages - self.pool.reserved:
                 raise GenerationAdmissionRejected("context_overflow: request exceeds the whole KV pool") from None
             return False
+        self._claims[str(rs.rid)] = claim
         slot = self.free_slots.pop()
         rs.slot = slot
         rs.runner_data = lease
@@ -478,6 +497,9 @@ class GpuRunner(BaseRunner):
             rs.runner_data = None
         if rs.slot is not None and rs.slot not in self.free_slots and rs.slot < self.max_slots:
             self.free_slots.append(rs.slot)
+        claim = self._claims.pop(str(rs.rid), None)
+        if claim is not None:
+            self.ledger.release(claim)
         if rs.rid in self.resident_key:
             self.resident_key = ()
 
@@ -493,11 +515,19 @@ class GpuRunner(BaseRunner):
         self.radix.clear()
         self.free_slots = list(range(self.max_slots - 1, -1, -1))
         self.free_snaps = list(range(self.max_slots + self.n_snap - 1, self.max_slots - 1, -1))
+        for claim in self._claims.values():
+            self.ledger.release(claim)
+        self._claims.clear()
+        for claim in self._snap_claims.values():
+            self.ledger.release(claim)
+        self._snap_claims.clear()
         self.resident_key = ()
 
     def capacity(self) -> Dict[str, Any]:
         return {"backend": "cuda_sm100a", "max_slots": self.max_slots, "max_context": self.max_context,
                 "free_slots": len(self.free_slots), "kv_pool": self.pool.snapshot(),
+                "resources": self.ledger.snapshot(),
+                "speculative": self.mtp.capability().as_dict() if self.mtp is not None else None,
                 "prefix_cache": self.radix.snapshot_stats(), "state_bytes": self.ex.state_bytes(),
                 "kv_bytes_per_token": self.cfg.kv_bytes_per_token(),
                 "recurrent_state_bytes_per_request": self.cfg.recurrent_state_bytes(),

@@ -205,6 +205,30 @@ class LLM:
             raise TypeError(f"unsupported model argument {type(m)}")
         return self._weights
 
+    @property
+    def startup(self) -> Dict[str, Any]:
+        """Record of how the engine came up: stages in order with their durations, checks, device memory (the
+        start-up block of the server's readiness document; ``LOAD_TIMING`` in the reference's logs)."""
+        st = self.__dict__.get("_startup")
+        if st is None:
+            st = self.__dict__["_startup"] = {"model_loaded": False, "warmup_complete": False, "eager_load": False,
+                                              "stages": [], "timings_s": {}, "checks": {}, "memory": {}, "error": None}
+        return st
+
+    def _stage(self, name: str, fn):
+        st = self.startup
+        t0 = time.time()
+        try:
+            out = fn()
+        except Exception as exc:
+            st["stages"].append({"name": name, "seconds": round(time.time() - t0, 3), "ok": False})
+            st["error"] = f"{name}: {type(exc).__name__}: {exc}"
+            raise
+        dt = round(time.time() - t0, 3)
+        st["stages"].append({"name": name, "seconds": dt, "ok": True})
+        st["timings_s"][name] = dt
+        return out
+
     def _get_engine(self):
         if self._closed:
             raise RuntimeError("LLM is closed")
@@ -212,7 +236,21 @@ class LLM:
             with self._lock:
                 if self._engine is None:
                     from .generation.engine_service import build_engine
-                    self._engine = build_engine(self._load_weights(), self.backend, self.config, self._get_tokenizer())
+                    w = self._stage("load_weights", self._load_weights)
+                    tok = self._stage("tokenizer", self._get_tokenizer)
+                    self._engine = self._stage("build_engine",
+                                               lambda: build_engine(w, self.backend, self.config, tok))
+                    st = self.startup
+                    st["model_loaded"] = True
+                    st["checks"]["native_library"] = "loaded" if self.backend == "cuda_sm100a" else "not_needed"
+                    if self.backend == "cuda_sm100a":
+                        try:
+                            import torch
+                            free, total = torch.cuda.mem_get_info()
+                            st["memory"] = {"device_total_bytes": int(total), "device_free_bytes": int(free),
+                                            "torch_allocated_bytes": int(torch.cuda.memory_allocated())}
+                        except Exception:
+                            pass
         return self._engine
 
     def _get_tokenizer(self):
@@ -230,10 +268,15 @@ class LLM:
     def prepare(self) -> Dict[str, Any]:
         """Make the engine resident now (weights uploaded, KV pool and scratch reserved)."""
         t0 = time.time()
+        self.startup["eager_load"] = True
         eng = self._get_engine()
         info = eng.capacity()
         info["prepare_seconds"] = time.time() - t0
         return info
+
+    def mark_warm(self) -> None:
+        """Called after a start-up smoke request went through: graphs are captured and scratch is sized."""
+        self.startup["warmup_complete"] = True
 
     def follow(self) -> None:
         """Ranks other than 0 of a tensor/expert-parallel serving group: make the engine resident and execute the

@@ -117,11 +117,13 @@ def main(argv: Optional[List[str]] = None) -> int:
         return 0
     if a.eager_load or a.startup_chat_smoke or max(a.tensor_parallel, a.expert_parallel) > 1:
         info = llm.prepare()
-        log.info("LOAD_TIMING prepare=%.2fs capacity=%s", time.time() - t0, info)
+        log.info("LOAD_TIMING prepare=%.2fs stages=%s capacity=%s", time.time() - t0,
+                 {s["name"]: s["seconds"] for s in llm.startup["stages"]}, info)
     if a.startup_chat_smoke:
         from ..llm import SamplingParams
         out = llm.chat([{"role": "user", "content": "ping"}], SamplingParams(max_tokens=4))
         log.info("startup chat smoke: %d tokens, finish=%s", len(out.token_ids), out.finish.reason)
+        llm.mark_warm()
     app = create_app(llm, srv)
     import uvicorn
     uvicorn.run(app, host=a.host, port=a.port, log_level=a.log_level)

@@ -257,22 +257,22 @@ def create_app(llm: LLM, config: Optional[ServerConfig] = None) -> FastAPI:
 
     @app.get("/ready")
     async def ready():
+        from .readiness import build_readiness
         h = llm.engine_service_health()
-        body: Dict[str, Any] = {"ready": bool(h.get("healthy", True)), "engine": h, "model": cfg.served_model_name,
-                                "queue": {"in_flight": gate.in_flight, "limit": gate.limit},
-                                "batcher": gate.snapshot(),
-                                "parallelism": {"world_size": llm.config.parallel.tp * llm.config.parallel.ep,
-                                                "tensor_parallel": llm.config.parallel.tp,
-                                                "expert_parallel": llm.config.parallel.ep},
-                                "uptime_seconds": time.time() - state["started"]}
+        cap = live = None
+        err = None
         if llm._engine is not None and h.get("healthy"):
             try:
                 cap = await run_blocking(llm.resident_capacity_estimate)
-                body["context"] = {"max_context_tokens": cap.get("max_context")}
-                body["kv_capacity"] = {"pool": cap.get("kv_pool"), "prefix_cache": cap.get("prefix_cache")}
+                live = await run_blocking(llm.live_loop_snapshot)
             except Exception as exc:
-                body["ready"] = False
-                body["reason"] = str(exc)
+                err = str(exc)
+        mcfg = getattr(llm._weights, "config", None) if getattr(llm, "_weights", None) is not None else \
+            getattr(getattr(llm, "model", None), "cfg", None)
+        body = build_readiness(model_id=cfg.served_model_name, health=h, startup=llm.startup, capacity=cap, live=live,
+                               config=llm.config, server_cfg=cfg, gate=gate,
+                               sessions={"count": len(sessions.sessions), "max": cfg.max_chat_sessions}, started=state["started"],
+                               model_cfg=mcfg, error=err)
         return JSONResponse(body, status_code=200 if body["ready"] else 503)
 
     @app.get("/v1/models", dependencies=[Depends(auth)])

@@ -1,7 +1,6 @@
 """Speculative decoding: contracts, transaction stages, the exact sampling law, planner, serving admission and the
 NextN/MTP chain cycle on the GPU executor."""
-from .contracts import (AcceptResult, CandidateChain, SpecCycleResult, SpecRequestPlan,  # noqa: F401
-                        SpeculativeCapability)
+from .contracts import SpecCycleResult, SpeculativeCapability  # noqa: F401
 from .policy import plan_draft_depth  # noqa: F401
 from .sampling import (acceptance_probability, residual_distribution,  # noqa: F401
                        sampled_accept_from_distributions)

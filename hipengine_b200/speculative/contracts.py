@@ -1,13 +1,13 @@
 """Value types shared by drafters, verifiers and the engine loop.
 
 Scope follows the reference's speculative contracts (``hipengine/speculative/contracts.py`` /
-``interfaces.py``: capability, request plan, candidate graph rows, accept result) reduced to chain candidates,
-the only shape the NextN/MTP drafter produces.
+``interfaces.py``) reduced to what chain speculation needs: the capability a provider reports (shown by the
+runner's capacity and the server's readiness document) and the result of one cycle.
 """
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import List, Optional, Tuple
+from typing import Any, Dict, List, Optional, Tuple
 
 
 @dataclass(frozen=True)
@@ -19,34 +19,12 @@ class SpeculativeCapability:
     attachment: str = "trailing_block"        # the drafter is the checkpoint's own NextN block
     transaction_mode: str = "journal"         # recurrent state is journalled per verify row and committed by copy
     sampling_modes: Tuple[str, ...] = ("greedy", "sampled")
+    graph_capture: bool = False               # the whole cycle replays as one captured graph (greedy chains)
 
-
-@dataclass
-class SpecRequestPlan:
-    rid: int
-    depth: int                  # K draft tokens this cycle
-    start_position: int         # position of the chain's first token (the last committed one)
-    sampling_mode: str          # greedy | sampled
-    max_emit: int               # tokens the request may still emit
-
-
-@dataclass
-class CandidateChain:
-    """One request's verify rows: ``tokens[0]`` is committed, ``tokens[1:]`` are drafts."""
-    rid: int
-    tokens: List[int]
-    positions: List[int]
-
-    @property
-    def depth(self) -> int:
-        return len(self.tokens) - 1
-
-
-@dataclass
-class AcceptResult:
-    accepted: int               # drafts accepted (0..K)
-    emitted: List[int]          # accepted drafts + the bonus token
-    commit_row: int             # verify row whose recurrent state becomes live
+    def as_dict(self) -> Dict[str, Any]:
+        return {"provider": self.provider, "max_depth": self.max_depth, "widths": list(self.widths),
+                "attachment": self.attachment, "transaction_mode": self.transaction_mode,
+                "sampling_modes": list(self.sampling_modes), "graph_capture": self.graph_capture}
 
 
 @dataclass

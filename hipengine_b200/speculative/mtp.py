@@ -19,7 +19,7 @@ import torch
 
 from ..models.executor import GEMV_MAX_ROWS, BatchDesc, make_batch
 from ..ops import kernels as K
-from .contracts import SpecCycleResult
+from .contracts import SpecCycleResult, SpeculativeCapability
 from .transaction import SpecTransaction, Stage
 
 
@@ -40,6 +40,10 @@ class ChainVerifyCycle:
         self.hidden_row = torch.zeros(max_requests, dtype=torch.int32, device=dev)
         self.am_ids = torch.zeros(self.max_rows, dtype=torch.int64, device=dev)
         self.stats = {"cycles": 0, "drafted": 0, "accepted": 0}
+
+    def capability(self) -> SpeculativeCapability:
+        return SpeculativeCapability(provider="host_drafts", max_depth=self.max_depth,
+                                     widths=tuple(range(1, self.max_requests + 1)), attachment="none")
 
     # hooks of drafters that keep device state per slot (the NextN block does)
     def reset_slot(self, slot: int) -> None:
@@ -142,6 +146,11 @@ class MTPCycle(ChainVerifyCycle):
         assert ex.has_nextn, "checkpoint has no NextN block"
         super().__init__(ex, max_depth, max_requests)
         self.h_prev = torch.zeros(ex.max_slots, ex.cfg.hidden, dtype=torch.float32, device=ex.device)  # per slot
+
+    def capability(self) -> SpeculativeCapability:
+        return SpeculativeCapability(provider="nextn_mtp", max_depth=self.max_depth,
+                                     widths=tuple(range(1, self.max_requests + 1)),
+                                     graph_capture=isinstance(self, GraphedMTPCycle))
 
     def _after_commit(self, slot_t: torch.Tensor, hid: torch.Tensor, R: int) -> None:
         picked = self.ex.scratch.get("mtp_pick", (R, self.ex.cfg.hidden), torch.float32)

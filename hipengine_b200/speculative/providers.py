@@ -95,6 +95,10 @@ class LookupCycle:
         self.stats = self.verify.stats
         self.stats.update({"proposed_rows": 0, "empty_rows": 0, "skipped_cycles": 0})
 
+    def capability(self):
+        from dataclasses import replace
+        return replace(self.verify.capability(), provider=type(self.drafter).__name__)
+
     def reset_slot(self, slot: int) -> None:
         pass
 

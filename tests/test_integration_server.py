@@ -34,7 +34,14 @@ def _sse(resp):
 
 def test_health_ready_models_auth(client):
     assert client.get("/health").json() == {"status": "ok"}
-    assert client.get("/ready").status_code == 200
+    r = client.get("/ready")
+    assert r.status_code == 200
+    body = r.json()
+    assert body["object"] == "hipengine.readiness" and body["ready"] is True and body["status"] == "ready"
+    for key in ("engine_service", "model", "startup", "context", "kv_capacity", "prefix_cache", "graph_cache",
+                "queue", "batcher", "sessions", "parallelism", "diagnostics"):
+        assert key in body, key
+    assert "kv_capability" in body["model"] and "stages" in body["startup"]
     assert client.get("/v1/models").json()["data"][0]["id"] == "tiny"
     r = client.get("/v1/models", headers={"Authorization": "Bearer wrong"})
     assert r.status_code == 401 and r.json()["error"]["code"] == "unauthorized"
