@@ -115,6 +115,9 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the layer stack (marks the run invalid)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--batch", type=int, default=1,
+                    help="concurrent sequences per stream: each is prefilled on its own, then all decode together as one "
+                         "packed step per token (continuous-batching steady state)")
     ap.add_argument("--no-mtp", action="store_true", help="N = 1: skip the speculative (NextN depth 3) cycle figures")
     ap.add_argument("--mtp-depth", type=int, default=3)
     args = ap.parse_args()
@@ -143,20 +146,23 @@ def main() -> int:
     mode = args.parallelism if world > 1 else "single"
     gen = torch.Generator().manual_seed(1234 + (rank if mode == "dp" else 0))
     prompts = [torch.randint(0, cfg.vocab, (args.prompt_len,), generator=gen).tolist()
-               for _ in range(args.steps + args.warmup)]
+               for _ in range(max(args.steps + args.warmup, args.batch))]
+    B = max(1, args.batch)
+    if B > 1:
+        ctx_max = args.prompt_len + args.gen_len + 16
     from hipengine_b200.models.decode_graph import DecodeGraphRunner
 
     def build(tp: bool, comm=None):
         if tp:
             from hipengine_b200.parallel.tp import build_tp_executor
-            e = build_tp_executor(cfg, seed=0, device=dev, ctx=ctx, comm=comm or args.tp_comm, max_slots=1,
+            e = build_tp_executor(cfg, seed=0, device=dev, ctx=ctx, comm=comm or args.tp_comm, max_slots=B,
                                   max_context=ctx_max)
         else:
             from hipengine_b200.models import make_executor
             weights = build_random_model(cfg, seed=0, device=dev, recipe="q4_k_m")
-            e = make_executor(weights, device=dev, max_slots=1, max_context=ctx_max)
+            e = make_executor(weights, device=dev, max_slots=B, max_context=ctx_max)
             del weights
-        return e, DecodeGraphRunner(e, max_rows=1, use_graphs=not args.no_graphs)
+        return e, DecodeGraphRunner(e, max_rows=B, use_graphs=not args.no_graphs)
 
     def barrier():
         ctx.barrier()
@@ -166,7 +172,28 @@ def main() -> int:
         """n_warm untimed requests, then n_steps timed ones; device times are max over ranks."""
         tok_log = torch.zeros(args.gen_len, dtype=torch.int64, device=dev)
 
+        def one_batch(step_i, ev, log=False):
+            """B sequences: prefill each (its own slot), then gen_len - 1 packed decode steps of B rows."""
+            for sl in range(B):
+                ex.reset_slot(sl)
+            ev[0].record()
+            for sl in range(B):
+                logits = ex.prefill(sl, prompts[(step_i + sl) % len(prompts)])
+                ex.greedy(logits, runner.next_ids[sl:sl + 1])
+            runner.slot[:B].copy_(torch.arange(B, dtype=torch.int32, device=dev))
+            runner.pos[:B].fill_(args.prompt_len - 1)
+            runner.ctx_len[:B].fill_(args.prompt_len)
+            runner.publish(B)
+            ev[1].record()
+            for j in range(args.gen_len - 1):
+                runner.step(B, ctx_max)
+                if log:
+                    tok_log[j].copy_(runner.tokens[0])
+            ev[2].record()
+
         def one_request(prompt, ev, log=False):
+            if B > 1:
+                return one_batch(prompts.index(prompt) if prompt in prompts else 0, ev, log)
             ex.reset_slot(0)
             ev[0].record()
             logits = ex.prefill(0, prompt)
@@ -218,13 +245,13 @@ def main() -> int:
     torch.cuda.synchronize()
     build_s = time.time() - t_build0
     m = measure(ex, runner, args.warmup, args.steps, True)
-    streams = world if mode == "dp" else 1          # independent request streams in flight
+    streams = (world if mode == "dp" else 1) * B    # independent sequences in flight
     n_dec = (args.gen_len - 1) * args.steps * streams
     decode_tok_s = n_dec / (m["decode_ms"] / 1e3)
     prefill_tok_s = args.prompt_len * args.steps * streams / (m["prefill_ms"] / 1e3)
 
     e2e = None
-    if not args.no_e2e:
+    if not args.no_e2e and B == 1:
         try:
             mine = run_e2e(args, cfg, ex, prompts)
             # replicas run side by side: tokens add up, the slowest replica sets the time
@@ -242,7 +269,7 @@ def main() -> int:
                 raise
 
     mtp = None
-    if world == 1 and not args.no_mtp and not args.no_graphs and cfg.is_hybrid and not getattr(cfg, "n_experts", 0):
+    if world == 1 and B == 1 and not args.no_mtp and not args.no_graphs and cfg.is_hybrid and not getattr(cfg, "n_experts", 0):
         # speculative decoding on the same geometry with a NextN block appended: cost of one captured cycle in units
         # of an autoregressive step, tokens per cycle with the block's own drafts (random weights: near zero
         # acceptance) and with the true continuation as drafts (every draft accepted: the upper bound)
@@ -300,8 +327,10 @@ def main() -> int:
     if rank == 0:
         par = {"single": "single", "dp": f"dp{world}", "tp": f"tp{world}"}[mode]
         base_dec, base_pre, label = BASELINES.get(args.model, (None, None, args.model))
+        if B > 1:
+            base_dec = base_pre = None          # the published figures are single-sequence runs
         line = {
-            "metric": f"decode_tok_s ({label}, bf16 KV, batch 1 per stream, {args.prompt_len} prefill + "
+            "metric": f"decode_tok_s ({label}, bf16 KV, batch {B} per stream, {args.prompt_len} prefill + "
                       f"{args.gen_len} decode)",
             "value": round(decode_tok_s, 3), "unit": "tok/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round((m["prefill_ms"] + m["decode_ms"]) / args.steps, 3),
@@ -315,6 +344,7 @@ def main() -> int:
             "prefill_vs_baseline": round(prefill_tok_s / base_pre, 3) if base_pre else None,
             "ttft_ms": round(m["prefill_ms"] / args.steps, 3),
             "itl_ms": round(m["decode_ms"] / ((args.gen_len - 1) * args.steps), 4),
+            "batch": B,
             "wall_s": round(m["wall_s"], 3), "build_s": round(build_s, 2),
             "clocks": m["clocks"], "gpu_launches": int(m["launches"]) * (world if mode == "dp" else 1),
         }

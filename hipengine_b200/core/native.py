@@ -49,6 +49,18 @@ def lib() -> ctypes.CDLL:
     return _LIB
 
 
+def bounds_status(reset: bool = True):
+    """(code, site, index, limit) recorded by the range checks of the ``checked`` library variant, (0, 0, 0, 0) when
+    clean, or None when the loaded library is the product build (which has no checks)."""
+    out = (ctypes.c_int * 4)()
+    rc = lib().he_bounds_status(out, ctypes.c_int(1 if reset else 0))
+    if rc == -1:
+        return None
+    if rc < 0:
+        raise RuntimeError("he_bounds_status: reading the device words failed")
+    return tuple(int(v) for v in out)
+
+
 def stream_ptr(stream: Optional[torch.cuda.Stream] = None) -> ctypes.c_void_p:
     s = stream if stream is not None else torch.cuda.current_stream()
     return ctypes.c_void_p(s.cuda_stream)

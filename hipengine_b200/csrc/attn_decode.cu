@@ -68,7 +68,7 @@ __global__ void __launch_bounds__(256) attn_decode_split_kernel(const AttnDecArg
       for (int g = 0; g < G; ++g) acc[g] = 0.f;
       if (tk < n) {
         const int pos = k0 + tk;
-        const int pg = bt[pos / a.page];
+        const int pg = bt[HE_INDEX_OK(pos / a.page, a.max_pages, HE_SITE_ATTN_DECODE_PAGE) ? pos / a.page : 0];
         const __nv_bfloat16* kr = a.kv_cache + ((((size_t)pg * 2 + 0) * a.Hkv + hk) * a.page + (pos % a.page)) * D;
 #pragma unroll
         for (int c = 0; c < D / 64; ++c) {
@@ -139,7 +139,7 @@ __global__ void __launch_bounds__(256) attn_decode_split_kernel(const AttnDecArg
     const int tk = t0 + tgrp;
     if (tk < n) {
       const int pos = k0 + tk;
-      const int pg = bt[pos / a.page];
+      const int pg = bt[HE_INDEX_OK(pos / a.page, a.max_pages, HE_SITE_ATTN_DECODE_PAGE) ? pos / a.page : 0];
       const __nv_bfloat16* vr = a.kv_cache + ((((size_t)pg * 2 + 1) * a.Hkv + hk) * a.page + (pos % a.page)) * D;
       float p[G];
 #pragma unroll
@@ -297,7 +297,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_mma_kernel(const AttnDec
         const int row = lane + 32 * h2;
         // rows past the span re-read its last key: finite values that the zero probabilities then ignore
         const int pos = k0 + min(tile * TILE_KEYS + row, n - 1);
-        const int pg = bt[pos / a.page];
+        const int pg = bt[HE_INDEX_OK(pos / a.page, a.max_pages, HE_SITE_ATTN_DECODE_PAGE) ? pos / a.page : 0];
         const __nv_bfloat16* src =
             a.kv_cache + ((((size_t)pg * 2 + kv) * a.Hkv + hk) * a.page + (pos % a.page)) * D;
         bulk_row(ring + (size_t)s * STAGE + (size_t)row * PITCH, src, D * 2, &full[s]);

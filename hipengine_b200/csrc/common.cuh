@@ -36,6 +36,56 @@ enum HeStatus : int {
     if (_e != cudaSuccess) return (int)_e;                  \
   } while (0)
 
+// ---------------------------------------------------------------- range checks of the "checked" library variant
+// Built with -DHE_BOUNDS_CHECK=1 (library variant "checked"), every index that a kernel takes from device data
+// (token ids, block-table pages, expert ids, row selectors) is tested against its limit before it is used; a violation
+// records {HE_ERR_BOUNDS, site, index, limit} in a per-translation-unit device word and the access is skipped or the
+// index clamped -- never performed out of range.  he_bounds_status() collects the words.  In the product build
+// HE_INDEX_OK() is the constant true and none of this exists.  (The role compute-sanitizer's memcheck would play;
+// the reference plans the same status-word build for its bounds checks.)
+enum HeBoundsSite : int {
+  HE_SITE_EMBED_TOKEN = 1,
+  HE_SITE_KV_WRITE_PAGE = 2,
+  HE_SITE_ATTN_DECODE_PAGE = 3,
+  HE_SITE_MOE_EXPERT_ID = 4,
+  HE_SITE_GATHER_ROW = 5,
+  HE_SITE_STATE_SLOT = 6,
+};
+
+#if defined(HE_BOUNDS_CHECK) && defined(__CUDACC__)
+typedef int (*HeBoundsReader)(int* out4, int reset);
+extern "C" void he_bounds_register_reader(HeBoundsReader fn);   // runtime.cpp
+namespace he {
+static __device__ int g_bounds_word[4];
+__device__ __forceinline__ bool bounds_ok(long long idx, long long lim, int site) {
+  if (idx >= 0 && idx < lim) return true;
+  if (atomicCAS(&g_bounds_word[0], 0, (int)HE_ERR_BOUNDS) == 0) {
+    g_bounds_word[1] = site;
+    g_bounds_word[2] = (int)idx;
+    g_bounds_word[3] = (int)lim;
+  }
+  return false;
+}
+static int bounds_read_tu(int* out4, int reset) {
+  int w[4] = {0, 0, 0, 0};
+  if (cudaMemcpyFromSymbol(w, g_bounds_word, sizeof(w)) != cudaSuccess) return -1;
+  if (reset && w[0] != 0) {
+    const int z[4] = {0, 0, 0, 0};
+    cudaMemcpyToSymbol(g_bounds_word, z, sizeof(z));
+  }
+  for (int i = 0; i < 4; ++i) out4[i] = w[i];
+  return w[0];
+}
+struct BoundsRegistration {
+  BoundsRegistration() { he_bounds_register_reader(&bounds_read_tu); }
+};
+static BoundsRegistration g_bounds_registration;   // internal linkage: one per translation unit
+}  // namespace he
+#define HE_INDEX_OK(idx, lim, site) (he::bounds_ok((long long)(idx), (long long)(lim), (site)))
+#else
+#define HE_INDEX_OK(idx, lim, site) (true)
+#endif
+
 namespace he {
 
 __device__ __forceinline__ float bf16_to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }

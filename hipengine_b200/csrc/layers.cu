@@ -181,6 +181,7 @@ __global__ void qkv_post_kernel(const QkvArgs a) {
     }
   } else {
     const int s = a.slot[t];
+    if (!HE_INDEX_OK(p / a.page, a.max_pages, HE_SITE_KV_WRITE_PAGE)) return;
     const int page_id = a.block_table[(size_t)s * a.max_pages + p / a.page];
     const size_t off = ((((size_t)page_id * 2 + (kind - 1)) * a.Hkv + h) * a.page + (p % a.page)) * D + d;
     a.kv_cache[off] = f32_to_bf16(x);

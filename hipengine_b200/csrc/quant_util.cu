@@ -141,7 +141,7 @@ __global__ void embed_kernel(const uint8_t* __restrict__ w, int qtype, long long
   const int t = blockIdx.x;
   if (t >= n_tok) return;
   long long id = ids[t];
-  if (id < 0 || id >= vocab) id = 0;
+  if (!HE_INDEX_OK(id, vocab, HE_SITE_EMBED_TOKEN) || id < 0 || id >= vocab) id = 0;
   for (int e = threadIdx.x; e < K; e += blockDim.x)
     out[(size_t)t * K + e] = dequant_elem(w, qtype, id, K, e) * scale;
 }

@@ -135,3 +135,30 @@ HE_API int he_launch_sequence(void* const* graph_execs, int n, void* stream, int
   return 0;
 }
 HE_API uint64_t he_native_graph_launches(void) { return g_launches.load(); }
+
+// ---------------------------------------------------------------- bounds words of the "checked" library variant
+// Every .cu file of a build with -DHE_BOUNDS_CHECK=1 registers a reader of its device-side bounds word here (static
+// initialiser); he_bounds_status() asks them all.  Returns -1 in the product build (no readers), else the first
+// non-zero code found (out4 = {code, site, index, limit}) or 0; `reset` clears what was read.
+namespace {
+typedef int (*HeBoundsReader)(int* out4, int reset);
+HeBoundsReader g_bounds_readers[64];
+int g_n_bounds_readers = 0;
+}  // namespace
+
+extern "C" __attribute__((visibility("default"))) void he_bounds_register_reader(HeBoundsReader fn) {
+  if (g_n_bounds_readers < 64) g_bounds_readers[g_n_bounds_readers++] = fn;
+}
+
+HE_API int he_bounds_status(int* out4, int reset) {
+  if (g_n_bounds_readers == 0) return -1;
+  int first[4] = {0, 0, 0, 0};
+  for (int i = 0; i < g_n_bounds_readers; ++i) {
+    int w[4] = {0, 0, 0, 0};
+    const int rc = g_bounds_readers[i](w, reset);
+    if (rc < 0) return -2;
+    if (rc != 0 && first[0] == 0) std::memcpy(first, w, sizeof(first));
+  }
+  if (out4 != nullptr) std::memcpy(out4, first, sizeof(first));
+  return first[0];
+}
