@@ -10,7 +10,16 @@ measured at the client from the SSE frames, and the server's prefix-cache counte
     python -m hipengine_b200.benchmark.serving_load --model qwen35-27b --requests 256 --concurrency 64
 
 The server runs in this process (uvicorn on a background thread, 127.0.0.1) unless ``--url`` points at one that is
-already running.  Requests use ``/v1/completions`` with token-id prompts, so no tokenizer noise enters the timing.
+already running.  ``--endpoint completions`` sends token-id prompts to ``/v1/completions`` (no tokenizer noise in the
+timing); ``--endpoint chat`` sends one user message of random text to ``/v1/chat/completions`` (prompt length is then
+approximate: the template adds a few tokens).
+
+A tensor-parallel group is served by launching this module under ``torch.distributed.run`` with
+``--tensor-parallel N``: rank 0 runs the HTTP server, the scheduler and the load generator, the other ranks follow
+its command batches; ``--mtp on`` turns speculative decoding (NextN block, ``--mtp-depth`` drafts) on.
+
+    python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29600 \
+        -m hipengine_b200.benchmark.serving_load --model qwen35-27b-mtp --tensor-parallel 8 --mtp on --endpoint chat
 """
 from __future__ import annotations
 
@@ -38,13 +47,25 @@ def build_prompts(n: int, vocab: int, min_len: int, max_len: int, shared_prefix:
     return out
 
 
-async def _one(session, url: str, model: str, prompt: List[int], max_tokens: int, rec: Dict[str, Any]) -> None:
-    body = {"model": model, "prompt": prompt, "max_tokens": max_tokens, "stream": True, "temperature": 0.0,
+def _as_text(ids: List[int]) -> str:
+    """Random lower-case text with one character per requested token (a byte-level tokenizer maps it 1:1)."""
+    return "".join(chr(97 + (t % 26)) for t in ids)
+
+
+async def _one(session, url: str, model: str, prompt: List[int], max_tokens: int, rec: Dict[str, Any],
+               endpoint: str = "completions") -> None:
+    body = {"model": model, "max_tokens": max_tokens, "stream": True, "temperature": 0.0,
             "ignore_eos": True, "stream_options": {"include_usage": True}}
+    if endpoint == "chat":
+        body["messages"] = [{"role": "user", "content": _as_text(prompt)}]
+        path = "/v1/chat/completions"
+    else:
+        body["prompt"] = prompt
+        path = "/v1/completions"
     t0 = time.perf_counter()
     stamps: List[float] = []
     try:
-        async with session.post(url + "/v1/completions", json=body) as resp:
+        async with session.post(url + path, json=body) as resp:
             rec["status"] = resp.status
             async for raw in resp.content:
                 line = raw.decode().strip()
@@ -53,7 +74,9 @@ async def _one(session, url: str, model: str, prompt: List[int], max_tokens: int
                 ev = json.loads(line[6:])
                 if ev.get("usage"):
                     rec["usage"] = ev["usage"]
-                if ev.get("choices") and ev["choices"][0].get("text") is not None:
+                ch = ev["choices"][0] if ev.get("choices") else None
+                d = (ch.get("delta") or {}) if ch is not None else {}
+                if ch is not None and (ch.get("text") is not None or d.get("content") or d.get("reasoning_content")):
                     stamps.append(time.perf_counter())
     except Exception as exc:
         rec["error"] = f"{type(exc).__name__}: {exc}"
@@ -61,7 +84,7 @@ async def _one(session, url: str, model: str, prompt: List[int], max_tokens: int
 
 
 async def run_load(url: str, model: str, prompts: List[List[int]], arrivals: List[float], concurrency: int,
-                   max_tokens: int) -> List[Dict[str, Any]]:
+                   max_tokens: int, endpoint: str = "completions") -> List[Dict[str, Any]]:
     import aiohttp
     sem = asyncio.Semaphore(concurrency)
     recs: List[Dict[str, Any]] = [{} for _ in prompts]
@@ -71,7 +94,7 @@ async def run_load(url: str, model: str, prompts: List[List[int]], arrivals: Lis
         async def task(i: int) -> None:
             await asyncio.sleep(max(0.0, arrivals[i] - (time.perf_counter() - start)))
             async with sem:
-                await _one(session, url, model, prompts[i], max_tokens, recs[i])
+                await _one(session, url, model, prompts[i], max_tokens, recs[i], endpoint)
         await asyncio.gather(*[task(i) for i in range(len(prompts))])
     for r in recs:
         r["t0"] = start
@@ -101,10 +124,11 @@ def summarise(recs: List[Dict[str, Any]], wall_s: float) -> Dict[str, Any]:
             "cached_prompt_tokens": cached, "prompt_tokens": prompt_toks}
 
 
-def _serve_in_thread(llm, served_name: str, port: int):
+def _serve_in_thread(llm, served_name: str, port: int, batch_window_ms: float = 0.0):
     import uvicorn
     from ..server.api import ServerConfig, create_app
-    app = create_app(llm, ServerConfig(served_model_name=served_name, max_queued_requests=4096))
+    app = create_app(llm, ServerConfig(served_model_name=served_name, max_queued_requests=4096,
+                                       batch_window_ms=batch_window_ms))
     server = uvicorn.Server(uvicorn.Config(app, host="127.0.0.1", port=port, log_level="warning"))
     th = threading.Thread(target=server.run, daemon=True)
     th.start()
@@ -130,28 +154,50 @@ def main(argv: Optional[List[str]] = None) -> int:
     ap.add_argument("--output-tokens", type=int, default=256)
     ap.add_argument("--max-active", type=int, default=64)
     ap.add_argument("--mtp", default="off", choices=["off", "on"])
+    ap.add_argument("--mtp-depth", type=int, default=3)
+    ap.add_argument("--endpoint", default="completions", choices=["completions", "chat"])
+    ap.add_argument("--tensor-parallel", type=int, default=1)
+    ap.add_argument("--batch-window-ms", type=float, default=0.0)
     ap.add_argument("--seed", type=int, default=0)
     a = ap.parse_args(argv)
     llm = server = None
     url = a.url
     vocab = 32000
+    import os
+    rank = int(os.environ.get("RANK", "0"))
     if url is None:
         from ..llm import LLM
         llm = LLM(a.model, backend=a.backend, max_active_requests=a.max_active,
-                  max_sequence_length=a.max_prompt + a.output_tokens + 64, prefix_cache="radix",
-                  speculative_mtp_serving=a.mtp)
+                  max_sequence_length=a.max_prompt + a.output_tokens + 128, prefix_cache="radix",
+                  speculative_mtp_serving=a.mtp, speculative_candidate_budget=a.mtp_depth,
+                  tensor_parallel=a.tensor_parallel)
+        if a.tensor_parallel > 1 and rank != 0:
+            llm.follow()            # returns when rank 0 closes the group
+            return 0
         llm.prepare()
         vocab = llm.vocab_size
-        server, _ = _serve_in_thread(llm, a.model, a.port)
+        server, _ = _serve_in_thread(llm, a.model, a.port, a.batch_window_ms)
         url = f"http://127.0.0.1:{a.port}"
     prompts = build_prompts(a.requests, vocab, a.min_prompt, a.max_prompt, a.shared_prefix, a.seed)
     arrivals = poisson_arrivals(a.requests, a.rate, a.seed)
     t0 = time.perf_counter()
-    recs = asyncio.run(run_load(url, a.model, prompts, arrivals, a.concurrency, a.output_tokens))
+    recs = asyncio.run(run_load(url, a.model, prompts, arrivals, a.concurrency, a.output_tokens, a.endpoint))
     out = summarise(recs, time.perf_counter() - t0)
+    if llm is not None:
+        try:
+            snap = llm.live_loop_snapshot()
+            run = snap.get("runner") or snap
+            out["server"] = {k: run.get(k) for k in ("prefix_hits", "prefix_hit_tokens", "spec_cycles", "spec_drafted",
+                                                     "spec_accepted") if k in run}
+            mtp = getattr(getattr(llm._engine.loop, "runner", None), "mtp", None)
+            if mtp is not None:
+                out["server"]["mtp"] = dict(mtp.stats)
+        except Exception as exc:        # the load figures stand on their own
+            out["server"] = {"error": str(exc)}
     out["config"] = {"model": a.model, "concurrency": a.concurrency, "rate_per_s": a.rate,
                      "prompt_range": [a.min_prompt, a.max_prompt], "shared_prefix": a.shared_prefix,
-                     "output_tokens": a.output_tokens, "mtp": a.mtp, "page_tokens": 16}
+                     "output_tokens": a.output_tokens, "mtp": a.mtp, "mtp_depth": a.mtp_depth, "page_tokens": 16,
+                     "endpoint": a.endpoint, "tensor_parallel": a.tensor_parallel}
     errs = [r.get("error") for r in recs if r.get("error")]
     if errs:
         out["first_error"] = errs[0]

@@ -203,6 +203,9 @@ NAMED_CONFIGS: Dict[str, ModelConfig] = {
     "tiny-hybrid-moe-tp": TINY_HYBRID_MOE_TP,
     "tiny-gemma4": TINY_GEMMA4,
     "qwen35-27b": QWEN35_27B,
+    # the same geometries with the checkpoint's trailing NextN (MTP) block, for speculative serving runs
+    "qwen35-27b-mtp": replace(QWEN35_27B, nextn_layers=1),
+    "tiny-hybrid-mtp": replace(TINY_HYBRID, nextn_layers=1),
     "qwen35-35b-a3b": QWEN35_35B_A3B,
     "gemma4-26b-a4b": GEMMA4_26B_A4B,
 }
