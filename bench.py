@@ -115,6 +115,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the layer stack (marks the run invalid)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--no-prefill-graphs", action="store_true",
+                    help="issue the prefill forward eagerly instead of replaying it from a CUDA graph per shape")
     ap.add_argument("--batch", type=int, default=1,
                     help="concurrent sequences per stream: each is prefilled on its own, then all decode together as one "
                          "packed step per token (continuous-batching steady state)")
@@ -126,6 +128,8 @@ def main() -> int:
     if args.warmup < 3 and not args.layers:
         args.warmup = 3
 
+    if not args.no_prefill_graphs and not args.no_graphs:
+        os.environ.setdefault("HE_PREFILL_GRAPH", "1")
     import torch
     import torch.distributed as dist
     from hipengine_b200.core import native
@@ -326,6 +330,8 @@ def main() -> int:
 
     if rank == 0:
         par = {"single": "single", "dp": f"dp{world}", "tp": f"tp{world}"}[mode]
+        if mode == "tp" and getattr(cfg, "n_experts", 0):
+            par += f"+ep{world}"              # attention / GDN tensor-parallel, experts dealt out by rank
         base_dec, base_pre, label = BASELINES.get(args.model, (None, None, args.model))
         if B > 1:
             base_dec = base_pre = None          # the published figures are single-sequence runs
@@ -339,7 +345,8 @@ def main() -> int:
             "data": "synthetic (random-init N(0,0.02) weights quantized to Q4_K_M-style GGUF blocks, uniform random prompt ids)",
             "config": {"model": args.model, "global_batch": streams, "seq_len": args.prompt_len,
                        "gen_len": args.gen_len, "parallelism": par, "layers": cfg.n_layers,
-                       "l2": "inputs larger than L2 (weight stream ~15 GB/step)", "cuda_graphs": not args.no_graphs},
+                       "l2": "inputs larger than L2 (weight stream ~15 GB/step)", "cuda_graphs": not args.no_graphs,
+                       "prefill_graph": os.environ.get("HE_PREFILL_GRAPH", "0") == "1"},
             "prefill_tok_s": round(prefill_tok_s, 2),
             "prefill_vs_baseline": round(prefill_tok_s / base_pre, 3) if base_pre else None,
             "ttft_ms": round(m["prefill_ms"] / args.steps, 3),

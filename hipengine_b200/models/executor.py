@@ -605,8 +605,19 @@ class HybridExecutor:
 
     # ------------------------------------------------------------------ convenience (tests, smoke, bench)
     @torch.no_grad()
-    def prefill(self, slot: int, tokens: Sequence[int], start_pos: int = 0, chunk: int = 4096) -> torch.Tensor:
-        """Prefill one request; returns the fp32 logits of its last row [1, vocab]."""
+    def prefill(self, slot: int, tokens: Sequence[int], start_pos: int = 0, chunk: int = 4096,
+                graph: Optional[bool] = None) -> torch.Tensor:
+        """Prefill one request; returns the fp32 logits of its last row [1, vocab].
+
+        With ``graph`` (default: ``HE_PREFILL_GRAPH=1``) a single-chunk prefill is replayed from a CUDA graph keyed by
+        (slot, start position, rows): the first call of a key runs eagerly, the second captures, later ones copy the
+        token ids into the graph's input buffer and launch once.  The forward of a sharded model is hundreds of
+        short launches per layer group; with eight ranks driven by eight Python processes the host, not the GPUs,
+        sets the pace of an eager prefill, and a replayed graph takes the host out of it."""
+        if graph is None:
+            graph = os.environ.get("HE_PREFILL_GRAPH", "0") == "1"
+        if graph and 0 < len(tokens) <= chunk:
+            return self._prefill_graphed(slot, tokens, start_pos)
         last_h = None
         for c0 in range(0, len(tokens), chunk):
             ids = tokens[c0:c0 + chunk]
@@ -614,6 +625,34 @@ class HybridExecutor:
             h = self.forward(b)
             last_h = h[b.T - 1:b.T]
         return self.logits(last_h)
+
+    def _prefill_graphed(self, slot: int, tokens: Sequence[int], start_pos: int) -> torch.Tensor:
+        T = len(tokens)
+        key = (slot, start_pos, T)
+        cache = self.__dict__.setdefault("_prefill_graphs", {})
+        ent = cache.get(key)
+        if ent is None:
+            # first sight of the shape: eager (sizes the scratch, sets function attributes), remember it
+            cache[key] = {"seen": 1}
+            return self.prefill(slot, tokens, start_pos, graph=False)
+        if "graph" not in ent:
+            b = make_batch([(slot, start_pos, [0] * T)], self.device)
+            ent["tok"] = b.tokens
+            ent["stage"] = torch.empty(T, dtype=torch.int64).pin_memory()
+            ent["logits"] = torch.empty(1, self.cfg.vocab, dtype=torch.float32, device=self.device)
+            torch.cuda.synchronize()
+            k0 = K.launch_count()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                h = self.forward(b)
+                self.logits(h[T - 1:T], out=ent["logits"])
+            ent["kernels"] = K.launch_count() - k0
+            ent["graph"], ent["batch"] = g, b
+        ent["stage"].copy_(torch.as_tensor(tokens, dtype=torch.int64))
+        ent["tok"].copy_(ent["stage"], non_blocking=True)
+        ent["graph"].replay()
+        K.add_launches(ent["kernels"])
+        return ent["logits"]
 
     @torch.no_grad()
     def forward_logits(self, slot: int, tokens: Sequence[int], start_pos: int = 0) -> torch.Tensor:

@@ -166,3 +166,24 @@ def test_27b_width_layers_match_fp32_reference():
     top1 = (agree | ~decided).float().mean().item()
     rel = ((got - ref_logits).norm() / ref_logits.norm()).item()
     assert kl.max() < 0.05 and top1 >= 0.9 and rel < 0.08, (kl.max().item(), top1, rel)
+
+
+def test_graph_replayed_prefill_equals_eager_prefill():
+    """A single-chunk prefill replayed from a CUDA graph (keyed by slot, start position and row count) produces the
+    logits and the state of the eager prefill, for token ids that change from call to call."""
+    from hipengine_b200.models.executor import HybridExecutor
+    cfg = TINY_HYBRID
+    w = build_random_model(cfg, seed=7, std=0.05).to("cuda")
+    ex = HybridExecutor(w, max_slots=2, max_context=512)
+    ex_ref = HybridExecutor(w, max_slots=2, max_context=512)
+    g = torch.Generator().manual_seed(8)
+    for call in range(4):                       # call 0 eager, call 1 captures, calls 2.. replay
+        toks = torch.randint(0, cfg.vocab, (300,), generator=g).tolist()
+        ex.reset_slot(1)
+        ex_ref.reset_slot(1)
+        got = ex.prefill(1, toks, graph=True).clone()
+        want = ex_ref.prefill(1, toks, graph=False)
+        assert torch.equal(got, want), call
+        nxt = int(want.argmax(-1))
+        assert torch.equal(ex.forward_logits(1, [nxt], 300), ex_ref.forward_logits(1, [nxt], 300))
+    assert "graph" in ex._prefill_graphs[(1, 0, 300)]
