@@ -226,6 +226,94 @@ def bench_fused_allreduce_gemm(M, N, K, phases=7):
             "fused_ms": round(ms_f, 4), "gemm_plus_add_ms": round(ms_p, 4), "fused_tflops": round(tf / ms_f, 1)}
 
 
+def bench_sustained(M, N, K, qtype="q4_k", secs=2.5):
+    """Seconds-long loops of the quantised GEMM, the bf16 tcgen05 GEMM and cuBLAS on one shape with the SM clock and
+    board power sampled (read-only nvidia-smi query) every 100 ms: what the kernels sustain under the power cap."""
+    import statistics
+    import subprocess
+    import time
+    from hipengine_b200.models.executor import _Scratch
+    from hipengine_b200.ops import gemm as G
+    from hipengine_b200.ops import kernels as Kn
+    from hipengine_b200.quant import ggml as Q
+    t = {"q4_k": Q.GGMLType.Q4_K, "q6_k": Q.GGMLType.Q6_K, "q8_0": Q.GGMLType.Q8_0}[qtype]
+    raw = Q.quantize(torch.randn(N, K, device="cuda") * 0.02, t)
+    dws = [Kn.to_device_weight(raw.clone(), t, N, K) for _ in range(8)]
+    wb = [(torch.randn(N, K, device="cuda") * 0.02).bfloat16() for _ in range(3)]
+    x = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+    sc = _Scratch(torch.device("cuda", torch.cuda.current_device()))
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+
+    def run(name, fn):
+        for i in range(5):
+            fn(i)
+        torch.cuda.synchronize()
+        p = subprocess.Popen(["nvidia-smi", f"--id={torch.cuda.current_device()}", "--query-gpu=clocks.sm,power.draw",
+                              "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE, text=True)
+        time.sleep(0.3)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n, t0 = 0, time.time()
+        e0.record()
+        while time.time() - t0 < secs:
+            for i in range(50):
+                fn(n + i)
+            n += 50
+            torch.cuda.synchronize()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / n
+        p.terminate()
+        rows = [l.split(",") for l in p.communicate()[0].strip().splitlines()[3:] if "," in l]
+        ck = [float(r[0]) for r in rows]
+        pw = [float(r[1]) for r in rows]
+        return {"kernel": name, "M": M, "N": N, "K": K, "ms": round(ms, 4), "tflops": round(2.0 * M * N * K / ms / 1e9, 1),
+                "sm_mhz_median": statistics.median(ck) if ck else None,
+                "power_w_median": statistics.median(pw) if pw else None, "launches": n}
+
+    res = [run(f"sustained gemm_quant[{qtype}]", lambda i: G.gemm_quant(x, dws[i % 8], out, sc)),
+           run("sustained gemm_bf16 (tcgen05)", lambda i: G.gemm_bf16(x, wb[i % 3], out)),
+           run("sustained torch.matmul (cuBLAS)", lambda i: torch.matmul(x, wb[i % 3].t(), out=out))]
+    G.check_status()
+    return res
+
+
+def gemm_role_counters(M, N, K, qtype="q4_k"):
+    """Cycle counters of CTA 0's roles in the quantised GEMM (library variant `prof`: HE_NATIVE_VARIANT=prof after
+    `python -m hipengine_b200.core.build --variant=prof`); a no-op table in the product build."""
+    import ctypes as C
+    from hipengine_b200.core import native as Nn
+    from hipengine_b200.models.executor import _Scratch
+    from hipengine_b200.ops import gemm as G
+    from hipengine_b200.ops import kernels as Kn
+    from hipengine_b200.quant import ggml as Q
+    t = {"q4_k": Q.GGMLType.Q4_K, "q6_k": Q.GGMLType.Q6_K, "q8_0": Q.GGMLType.Q8_0}[qtype]
+    raw = Q.quantize(torch.randn(N, K, device="cuda") * 0.02, t)
+    dws = [Kn.to_device_weight(raw.clone(), t, N, K) for _ in range(3)]
+    x = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+    sc = _Scratch(torch.device("cuda", torch.cuda.current_device()))
+    if M > 128:
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        fn = lambda i: G.gemm_quant(x, dws[i], out, sc)
+    else:
+        out = torch.empty(M, N, device="cuda")
+        fn = lambda i: G.gemm_quant_splitk(x, dws[i], out, sc)
+    for i in range(3):
+        fn(i)
+    torch.cuda.synchronize()
+    dbg = torch.zeros(32, dtype=torch.int64, device="cuda")
+    Nn.lib().he_gemm_q_debug_counters(C.c_void_p(dbg.data_ptr()))
+    fn(0)
+    torch.cuda.synchronize()
+    Nn.lib().he_gemm_q_debug_counters(C.c_void_p(0))
+    d = dbg.tolist()
+    return {"kernel": f"gemm_quant[{qtype}] role cycles of CTA 0", "M": M, "N": N, "K": K,
+            "unpack_warp": {"raw_block_wait": d[0], "expand": d[1], "operand_stage_wait": d[2], "tmem_store": d[3],
+                            "super_blocks": d[4]},
+            "mma_issuer": {"operand_wait": d[8], "activation_wait": d[9], "accumulator_wait": d[10], "total": d[11],
+                           "k_blocks": d[12]},
+            "raw_block_producer": {"free_stage_wait": d[16], "total": d[17], "stages": d[18]}}
+
+
 def bench_decode_step(rows_list, model="qwen35-27b", ctx=1024, small_rows=None):
     """Whole-model packed decode step (captured graph) at R concurrent rows, each at context `ctx`: the cost a
     continuous-batching round or a verify chain pays.  `small_rows` overrides the row count up to which the int8 GEMV
@@ -266,7 +354,8 @@ def bench_decode_step(rows_list, model="qwen35-27b", ctx=1024, small_rows=None):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "gemmq", "gemv", "gdn", "conv", "attn", "fusedar", "step", "all"])
+    ap.add_argument("what", choices=["gemm", "gemmq", "gemv", "gdn", "conv", "attn", "fusedar", "step", "sustained",
+                                     "roles", "all"])
     ap.add_argument("--rows-list", default="1,2,4,8,16,32,64")
     ap.add_argument("--model", default="qwen35-27b")
     ap.add_argument("--small-rows", type=int, default=None)
@@ -294,6 +383,10 @@ def main():
         out.append(bench_conv(a.t))
     elif a.what == "attn":
         out.append(bench_attn_decode(a.ctx, rows=a.rows))
+    elif a.what == "sustained":
+        out += bench_sustained(a.m, a.n, a.k, a.qtype)
+    elif a.what == "roles":
+        out.append(gemm_role_counters(a.m, a.n, a.k, a.qtype))
     elif a.what == "step":
         out += bench_decode_step([int(x) for x in a.rows_list.split(",")], a.model, a.ctx, a.small_rows)
     elif a.what == "fusedar":
