@@ -229,6 +229,23 @@ class LLM:
         st["timings_s"][name] = dt
         return out
 
+    def _admit(self, weights) -> None:
+        """Plan contract + memory preflight before the engine (KV pool, state slots, scratch) is built; the report
+        goes into the start-up record, a rejection raises with every reason listed."""
+        from .loading.admission import admit
+        free = None
+        if self.backend == "cuda_sm100a":
+            try:
+                import torch
+                f, _total = torch.cuda.mem_get_info()
+                on_dev = any(t.raw.is_cuda for t in list(weights.tensors.values())[:1])
+                free = int(f) + (int(weights.nbytes()) if on_dev else 0)
+            except Exception:
+                free = None
+        rep = admit(weights, self.config, free_bytes=free, strict=True)
+        self.startup["checks"]["admission"] = {k: rep[k] for k in ("admitted", "plan_complete", "plan_digest",
+                                                                   "planned_weights", "widened_to_bf16", "memory")}
+
     def _get_engine(self):
         if self._closed:
             raise RuntimeError("LLM is closed")
@@ -237,6 +254,7 @@ class LLM:
                 if self._engine is None:
                     from .generation.engine_service import build_engine
                     w = self._stage("load_weights", self._load_weights)
+                    self._stage("admission", lambda: self._admit(w))
                     tok = self._stage("tokenizer", self._get_tokenizer)
                     self._engine = self._stage("build_engine",
                                                lambda: build_engine(w, self.backend, self.config, tok))

@@ -290,3 +290,41 @@ def test_in_tree_tool_call_grammar_matcher():
         assert m.accept(t)
     assert m.finished() and m.allowed_mask()[0]                 # end-of-sequence now allowed
     assert isinstance(m.allowed_mask(), torch.Tensor) and not m.accept(vocab.index("x")) and m.dead()
+
+
+def test_artifact_admission_plan_contract_and_memory_preflight():
+    """Admission lists what cannot be served (missing tensors, block types without a reader, rows that are not whole
+    blocks, a pool that does not fit) before anything is built; a servable checkpoint gets a plan digest."""
+    import pytest
+    import torch
+    from hipengine_b200.config import EngineConfig
+    from hipengine_b200.loading.admission import ArtifactRejected, admit, build_role_manifest, plan_contract, role_of
+    from hipengine_b200.loading.synth import build_random_model
+    from hipengine_b200.loading.weights import ModelWeights
+    from hipengine_b200.models.config import TINY_HYBRID
+    from hipengine_b200.quant.ggml import GGMLType
+    assert role_of("blk.7.ffn_down.weight") == "ffn_down" and role_of("token_embd.weight") == "token_embd"
+    w = build_random_model(TINY_HYBRID, seed=0)
+    cfg = EngineConfig.from_env()
+    rep = admit(w, cfg, free_bytes=10 ** 12)
+    assert rep["admitted"] and rep["plan_complete"] and len(rep["plan_digest"]) == 16
+    assert "ffn_down" in rep["role_manifest"] and rep["memory"]["fits"]
+    assert admit(w, cfg, free_bytes=10 ** 12)["plan_digest"] == rep["plan_digest"]        # deterministic
+    man = build_role_manifest(w)
+    assert sum(man["attn_norm"].values()) == TINY_HYBRID.n_layers
+    # does not fit
+    with pytest.raises(ArtifactRejected) as e:
+        admit(w, cfg, free_bytes=1 << 20)
+    assert "GiB free" in str(e.value) and e.value.report["memory"]["fits"] is False
+    # a missing tensor and a block type nobody reads
+    t = dict(w.tensors)
+    t.pop("blk.0.attn_norm.weight")
+    bad = ModelWeights(w.config, t, dict(w.metadata))
+    pc = plan_contract(bad)
+    assert not pc.is_complete and pc.unsupported[0].slot == "blk.0.attn_norm.weight"
+    q = t["blk.1.ffn_down.weight"]
+    t["blk.1.ffn_down.weight"] = type(q)(q.name, 99 if 99 in GGMLType._value2member_map_ else GGMLType.Q5_K, q.shape, q.raw)
+    pc2 = plan_contract(ModelWeights(w.config, t, dict(w.metadata)))
+    assert pc2.digest != rep["plan_digest"]
+    with pytest.raises(ArtifactRejected):
+        admit(bad, cfg, free_bytes=10 ** 12)
