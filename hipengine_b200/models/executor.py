@@ -164,7 +164,12 @@ class HybridExecutor:
             a_name, b_name = f"blk.{i}.ssm_alpha.weight", f"blk.{i}.ssm_beta.weight"
             if a_name in self.f32 and b_name in self.f32:
                 ab = torch.cat([self.f32[a_name], self.f32[b_name]], 0).contiguous()
-                self.ab_bf16[i] = ab.to(torch.bfloat16).contiguous()
+                # rows padded with zeros to a multiple of 8 so that the tensor-core GEMM takes any head count (six value
+                # heads per rank at eight-way tensor parallelism would otherwise fall to the scalar kernel, which
+                # walks all 4096 activation rows once per output column)
+                pad = (-ab.shape[0]) % 8
+                abp = torch.cat([ab, ab.new_zeros(pad, ab.shape[1])], 0) if pad else ab
+                self.ab_bf16[i] = abp.to(torch.bfloat16).contiguous()
                 if ab.shape[1] % 256 == 0 and os.environ.get("HE_AB_Q8", "1") != "0":
                     raw = quantize(ab, GGMLType.Q8_0).reshape(ab.shape[0], -1).contiguous()
                     self.ab_q8[i] = K.to_device_weight(raw, GGMLType.Q8_0, ab.shape[0], ab.shape[1])
@@ -398,11 +403,11 @@ class HybridExecutor:
             with self._stage("gdn_qkvz_gemm"):
                 qkv = self._proj(xn, self.W(i, "attn_qkv.weight"), "qkv", "q")
                 z = self._proj(xn, self.W(i, "attn_gate.weight"), "z", "q")
-            if self.gemm_impl == "tcgen05" and (2 * Hv) % 8 == 0:
+            if self.gemm_impl == "tcgen05" and i in self.ab_bf16:
                 from ..ops import gemm as GM
-                ab = sc.get("ab_proj", (T, 2 * Hv), torch.float32)
+                ab = sc.get("ab_proj", (T, self.ab_bf16[i].shape[0]), torch.float32)
                 GM.gemm_bf16(xn, self.ab_bf16[i], ab)
-                a_p, b_p = ab[:, :Hv], ab[:, Hv:]
+                a_p, b_p = ab[:, :Hv], ab[:, Hv:2 * Hv]
             else:
                 K.small_gemm_f32(xn, self.F(i, "ssm_alpha.weight"), a_p)
                 K.small_gemm_f32(xn, self.F(i, "ssm_beta.weight"), b_p)

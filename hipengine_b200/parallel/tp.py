@@ -54,11 +54,17 @@ class TPHybridExecutor(HybridExecutor):
             self.fused = FusedReducer(ctx, self.full_cfg.hidden, max_rows=GEMV_MAX_ROWS)
             # decode: the all-reduce of a row-parallel projection is folded into the GEMVs around it (push from the
             # epilogue, sum in the next prologue), and the greedy head merges (max, id) pairs over peer memory
-            if os.environ.get("HE_TP_FOLD", "1") != "0" and self.full_cfg.hidden % 8 == 0 \
+            # Every CTA of the consumer GEMV reads the partial rows of all ranks (world x 40 KB of tagged words for the
+            # 27B width), so the fold pays up to four ranks (2 ranks: 30.7 vs 33.9 us per GEMV pair) and loses at
+            # eight (4.52 vs 4.19 ms per decode step), where the stand-alone push/reduce kernel stays the default.
+            fold_default = "1" if ctx.world <= 4 else "0"
+            if os.environ.get("HE_TP_FOLD", fold_default) != "0" and self.full_cfg.hidden % 8 == 0 \
                     and self.full_cfg.hidden <= 8192:
                 self.peer = PeerResidual(ctx, self.full_cfg.hidden, max_rows=GEMV_MAX_ROWS)
-                self.peer_head = PeerResidual(ctx, 1, max_rows=64)
                 self._pending = None          # (residual tensor, rows) of a push not yet summed into the residual
+            if os.environ.get("HE_TP_PEER_HEAD", "1") != "0":
+                # the (max, id) merge of the greedy head does not depend on the fold: no logits gather at any world
+                self.peer_head = PeerResidual(ctx, 1, max_rows=64)
             if self.gemm_impl == "tcgen05" and self.full_cfg.hidden % 8 == 0 and \
                     os.environ.get("HE_TP_FUSED_GEMM", "1") != "0":
                 from .fused import FusedGemmAllReduce

@@ -45,6 +45,16 @@ def test_decode_path_matches_reference(cfg):
     assert kl.max() < 0.05 and top1 >= 0.8 and rel < 0.4, (kl.max().item(), top1, rel)
 
 
+def test_prefill_with_six_value_heads_uses_padded_gate_projection():
+    """Six value heads (the per-rank count of the 27B at eight-way tensor parallelism) make the alpha/beta projection
+    12 rows wide: it is padded to 16 rows and stays on the tensor-core GEMM."""
+    from dataclasses import replace
+    cfg = replace(TINY_HYBRID, ssm_v_heads=6, ssm_groups=2)
+    kl, top1, ref_logits, got = _compare(cfg, 40, 3)
+    assert torch.isfinite(got).all()
+    assert kl.max() < 0.05 and top1 >= 0.8, (kl.max().item(), top1)
+
+
 @pytest.mark.parametrize("cfg", [TINY_DENSE, TINY_HYBRID], ids=["dense", "hybrid"])
 def test_prefill_path_matches_reference(cfg):
     kl, top1, ref_logits, got = _compare(cfg, 40, 3)
