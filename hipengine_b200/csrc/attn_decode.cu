@@ -202,7 +202,10 @@ namespace mma_dec {
 constexpr int NCONS = 4;                    // consumer warps
 constexpr int NTHREADS = (NCONS + 1) * 32;  // + one producer warp
 constexpr int TILE_KEYS = 64;
-constexpr int MAX_STAGES = 5;
+constexpr int MAX_STAGES = 5;        // barrier slots
+constexpr int RING_STAGES = 2;       // stages in use: with two stages (~68 KB for head_dim 256) three CTAs share an SM
+                                     // and hide each other's phase changes; one CTA with a five-stage ring left the
+                                     // SM at 8 % warp occupancy and 20 % of DRAM bandwidth
 
 template <int D>
 __host__ __device__ constexpr int pitch() { return D * 2 + 16; }
@@ -211,7 +214,7 @@ template <int D>
 __host__ __device__ inline int stages_for(int split_len) {
   const int uses = 2 * ((split_len + TILE_KEYS - 1) / TILE_KEYS);
   const int fit = (170 * 1024) / (TILE_KEYS * pitch<D>());
-  const int cap = fit < MAX_STAGES ? fit : MAX_STAGES;
+  const int cap = fit < RING_STAGES ? fit : RING_STAGES;
   return uses < cap ? uses : cap;
 }
 template <int D>

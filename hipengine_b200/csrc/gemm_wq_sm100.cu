@@ -942,6 +942,19 @@ int launch_wq(const void* A, long long lda, int a_cols, const void* B, int qtype
   if (fuse != nullptr) {
     cudaError_t e = cudaFuncSetAttribute(gemm_wq_rs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_WQ);
     if (e != cudaSuccess) return (int)e;
+    // CTAs of this kernel wait for stamps written by CTAs of other ranks, so the whole grid has to be resident at
+    // once: refuse a grid the device cannot hold (the caller then takes GEMM + library collective); the waits stay
+    // bounded either way
+    static int resident_per_sm[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    if (resident_per_sm[dev] == 0) {
+      int n = 0;
+      e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, gemm_wq_rs_kernel, NTHREADS_WQ_RS, SMEM_WQ);
+      if (e != cudaSuccess) return (int)e;
+      resident_per_sm[dev] = n > 0 ? n : -1;
+    }
+    if (resident_per_sm[dev] < 0 || (long long)grid > (long long)resident_per_sm[dev] * num_sms) return -HE_ERR_BAD_ARG;
     gemm_wq_rs_kernel<<<grid, NTHREADS_WQ_RS, SMEM_WQ, stream>>>(tmX, q0, q1, g, *fuse);
   } else if (small) {
     cudaError_t e = cudaFuncSetAttribute(gemm_wq_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
