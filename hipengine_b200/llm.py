@@ -121,6 +121,11 @@ class LLM:
         self.model = model
         self.backend = self._resolve_backend(backend, device)
         self.profile = ExecutionProfile.parse(execution_profile)
+        if kv_storage in ("auto", None):
+            kv_storage = "bf16"
+        if kv_storage != "bf16":
+            # the writer and both attention readers exist for bf16 pages only: refuse instead of silently storing bf16
+            raise ValueError(f"kv_storage={kv_storage!r} is not supported by this build (bf16 only)")
         base = engine_config or EngineConfig.from_env()
         self.config = replace(
             base,

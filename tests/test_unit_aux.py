@@ -328,3 +328,11 @@ def test_artifact_admission_plan_contract_and_memory_preflight():
     assert pc2.digest != rep["plan_digest"]
     with pytest.raises(ArtifactRejected):
         admit(bad, cfg, free_bytes=10 ** 12)
+
+
+def test_unsupported_kv_storage_is_refused_not_ignored():
+    import pytest
+    from hipengine_b200 import LLM
+    with pytest.raises(ValueError, match="kv_storage"):
+        LLM("tiny-dense", backend="cpu_reference", kv_storage="int8")
+    assert LLM("tiny-dense", backend="cpu_reference", kv_storage="auto").config.kv.storage == "bf16"
