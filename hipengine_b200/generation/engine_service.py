@@ -73,6 +73,10 @@ class EngineService:
         self.collectors: Dict[int, OutputCollector] = {}
         self.unhealthy: Optional[Dict[str, Any]] = None
         self.closed = False
+        # bounded ring of recent engine events (submits, finishes, errors): attached to the unhealthy report and to
+        # snapshot(), so a failed server can say what it was doing
+        from ..utils.tracing import FlightRecorder
+        self.recorder = FlightRecorder(capacity=256)
         self._wake = threading.Event()
         self.loop.on_event = self._on_event
         self.thread = threading.Thread(target=self._drive, name=name, daemon=True)
@@ -106,6 +110,8 @@ class EngineService:
     def submit(self, req: GenerationRequest, stream: bool = False) -> OutputCollector:
         col = OutputCollector(self.config.scheduler.stream_mailbox, stream)
         col.rid = req.request_id
+        self.recorder.record("submit", rid=req.request_id, prompt_tokens=len(req.prompt_token_ids),
+                             max_tokens=req.max_tokens, stream=bool(stream))
         self._call("submit", (req, col))
         return col
 
@@ -168,7 +174,10 @@ class EngineService:
             return False
 
     def snapshot(self) -> Dict[str, Any]:
-        return self._call("snapshot")
+        snap = self._call("snapshot")
+        if isinstance(snap, dict):
+            snap["recent_events"] = self.recorder.dump(last=16)
+        return snap
 
     def capacity(self) -> Dict[str, Any]:
         return self._call("capacity")
@@ -214,6 +223,8 @@ class EngineService:
             col.put_chunk(GenerationStreamChunk(rs.rid, toks, None, finished, rs.finish if finished else None, lps,
                                                 rs.telemetry if finished else None, rs.error))
         if finished:
+            self.recorder.record("finish", rid=rs.rid, reason=getattr(rs.finish, "reason", None), tokens=rs.emitted,
+                                 error=rs.error)
             col.finish(self.loop.sched.make_output(rs))
             self.collectors.pop(rs.rid, None)
             self.loop.sched.pop_finished(rs.rid)
@@ -312,6 +323,8 @@ class EngineService:
             self.unhealthy = {"exception_type": type(exc).__name__, "message": str(exc), "location": loc,
                               "cause_type": type(exc.__cause__).__name__ if exc.__cause__ else None,
                               "request_ids": list(self.loop.sched.active), "at": time.time()}
+            self.recorder.record("fatal", exception=type(exc).__name__, message=str(exc), location=loc)
+            self.unhealthy["recent_events"] = self.recorder.dump(last=32)
             try:
                 self.loop.fail_all(f"engine_unavailable: {type(exc).__name__}: {exc}")
             except Exception:

@@ -83,6 +83,9 @@ class GpuRunner(BaseRunner):
         self.ledger.register("snapshot_slots", self.n_snap)
         self._claims: Dict[str, Any] = {}
         self._snap_claims: Dict[int, Any] = {}
+        # kernel launches of the native library per phase (prefill / decode / speculative), part of snapshot()
+        from ..utils.tracing import LaunchCensus
+        self.census = LaunchCensus()
         self.graphs = DecodeGraphRunner(self.ex, max_rows=self.max_slots, use_graphs=config.use_cuda_graphs)
         self.resident_key: Tuple[int, ...] = ()
         self.pinned_ids = torch.zeros(max(self.max_slots, 8), dtype=torch.int64).pin_memory()
@@ -284,8 +287,12 @@ class GpuRunner(BaseRunner):
             self._write_block_table(rs.slot, lease, before)
 
     # ------------------------------------------------------------------ prefill
-    @torch.no_grad()
     def prefill(self, work: List[Tuple[RequestState, int]]) -> Dict[int, Tuple[int, Optional[TokenLogprob]]]:
+        with self.census.region("prefill"):
+            return self._prefill_impl(work)
+
+    @torch.no_grad()
+    def _prefill_impl(self, work: List[Tuple[RequestState, int]]) -> Dict[int, Tuple[int, Optional[TokenLogprob]]]:
         out: Dict[int, Tuple[int, Optional[TokenLogprob]]] = {}
         interval = self.config.kv.snapshot_interval_tokens if self.n_snap else 0
         # split every chunk at snapshot boundaries, then run the sub-chunks round by round as packed batches
@@ -403,8 +410,12 @@ class GpuRunner(BaseRunner):
         return TokenLogprob(tok, float(clp[0].item()), top)
 
     # ------------------------------------------------------------------ decode
-    @torch.no_grad()
     def decode(self, rows: List[RequestState]) -> List[Tuple[int, Optional[TokenLogprob]]]:
+        with self.census.region("decode"):
+            return self._decode_impl(rows)
+
+    @torch.no_grad()
+    def _decode_impl(self, rows: List[RequestState]) -> List[Tuple[int, Optional[TokenLogprob]]]:
         R = len(rows)
         key = tuple(rs.rid for rs in rows)
         for rs in rows:
@@ -445,8 +456,12 @@ class GpuRunner(BaseRunner):
                                      requested=True)
         return d.use_mtp
 
-    @torch.no_grad()
     def speculative_cycle(self, rows: List[RequestState]):
+        with self.census.region("speculative_cycle"):
+            return self._speculative_cycle_impl(rows)
+
+    @torch.no_grad()
+    def _speculative_cycle_impl(self, rows: List[RequestState]):
         from ..speculative.contracts import SpecCycleResult
         from ..speculative.policy import plan_draft_depth
         if len(rows) > self.mtp.max_requests:
@@ -536,5 +551,5 @@ class GpuRunner(BaseRunner):
                                     {id(w): w for w in self.ex.dw.values()}.values())}
 
     def snapshot(self) -> Dict[str, Any]:
-        return {"pool": self.pool.snapshot(), "prefix": self.radix.snapshot_stats(), "graphs": dict(self.graphs.stats, kernels_per_graph=None),
+        return {"launch_census": self.census.report(), "pool": self.pool.snapshot(), "prefix": self.radix.snapshot_stats(), "graphs": dict(self.graphs.stats, kernels_per_graph=None),
                 **self.stats}

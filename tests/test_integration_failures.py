@@ -93,3 +93,17 @@ def test_missing_rank_is_detected_by_collective_timeout():
         p.join(timeout=30)
     assert res[1] == "left"
     assert res[0].startswith("detected"), res
+
+
+def test_unhealthy_report_carries_recent_engine_events():
+    """The flight recorder rides on the unhealthy report: a failed engine says what it was doing."""
+    cfg = _cfg()
+    eng = engine_from_runner(_Exploding(cfg), cfg, None)
+    try:
+        out = eng.generate([GenerationRequest(prompt_token_ids=[1, 2, 3], max_tokens=4, ignore_eos=True)])[0]
+        assert out.error
+        assert eng.unhealthy is not None
+        kinds = [e["kind"] for e in eng.unhealthy["recent_events"]]
+        assert "submit" in kinds and kinds[-1] == "fatal"
+    finally:
+        eng.close()

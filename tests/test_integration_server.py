@@ -202,3 +202,65 @@ def test_generation_batcher_groups_compatible_requests_within_the_window():
         assert b.snapshot()["flush_drain"] == 1 and b.closing
 
     asyncio.run(run())
+
+
+def test_replica_router_balances_sticks_to_prefixes_and_fails_over():
+    """Two in-process replica servers (CPU reference backend) behind the router: requests with the same prompt prefix
+    land on the same replica, others spread by load, a dead replica is taken out of rotation."""
+    import threading
+    import time
+
+    import requests
+    import uvicorn
+
+    from hipengine_b200.llm import LLM
+    from hipengine_b200.server.api import ServerConfig, create_app
+    from hipengine_b200.server.router import Router, create_router_app, prompt_key
+
+    assert prompt_key({"prompt": "x" * 10}) is None and prompt_key({"prompt": "y" * 600}) == prompt_key({"prompt": "y" * 700})
+    servers, llms = [], []
+
+    def serve(app, port):
+        srv = uvicorn.Server(uvicorn.Config(app, host="127.0.0.1", port=port, log_level="warning"))
+        threading.Thread(target=srv.run, daemon=True).start()
+        for _ in range(200):
+            if srv.started:
+                break
+            time.sleep(0.05)
+        servers.append(srv)
+        return srv
+
+    try:
+        for port in (8061, 8062):
+            llm = LLM("tiny-dense", backend="cpu_reference", max_active_requests=2, max_sequence_length=1024)
+            llms.append(llm)
+            serve(create_app(llm, ServerConfig(served_model_name="tiny-dense")), port)
+        router = Router(["http://127.0.0.1:8061", "http://127.0.0.1:8062", "http://127.0.0.1:8069"], backoff_s=60.0)
+        serve(create_router_app(router), 8060)
+        base = "http://127.0.0.1:8060"
+        assert requests.get(base + "/health").json()["replicas"] == 3
+        shared = "p" * 600
+        for i in range(4):                                   # same prefix -> same replica
+            r = requests.post(base + "/v1/completions", json={"model": "tiny-dense", "prompt": shared + str(i),
+                                                              "max_tokens": 2, "temperature": 0.0})
+            assert r.status_code == 200 and r.json()["choices"][0]["text"] is not None
+        served = [rep.served for rep in router.replicas]
+        assert sorted(served)[-1] == 4 and router.stats["affinity_hits"] == 3
+        for i in range(4):                                   # distinct prompts spread; the dead replica is skipped
+            r = requests.post(base + "/v1/completions", json={"model": "tiny-dense", "prompt": chr(65 + i) * 700,
+                                                              "max_tokens": 2, "temperature": 0.0})
+            assert r.status_code == 200
+        assert router.replicas[2].served == 0 and router.replicas[2].failed >= 1
+        assert min(router.replicas[0].served, router.replicas[1].served) >= 2
+        # streaming passes through
+        with requests.post(base + "/v1/completions", json={"model": "tiny-dense", "prompt": "z" * 100, "max_tokens": 3,
+                                                            "stream": True}, stream=True) as r:
+            lines = [l for l in r.iter_lines() if l.startswith(b"data: ")]
+        assert lines[-1] == b"data: [DONE]" and len(lines) >= 2
+        ready = requests.get(base + "/ready")
+        assert ready.status_code == 200 and ready.json()["ready_replicas"] == 2
+    finally:
+        for s in servers:
+            s.should_exit = True
+        for l in llms:
+            l.close()
