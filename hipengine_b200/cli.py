@@ -1,4 +1,4 @@
-"""``hipengine-b200`` command line: ``serve`` / ``chat`` / ``bench`` / ``version``
+"""``hipengine-b200`` command line: ``serve`` / ``router`` / ``chat`` / ``bench`` / ``version``
 (the reference's ``hipengine serve / chat / bench / version``, ``hipengine/cli.py:21-104``)."""
 from __future__ import annotations
 
@@ -9,7 +9,7 @@ from typing import List, Optional
 def main(argv: Optional[List[str]] = None) -> int:
     argv = list(sys.argv[1:] if argv is None else argv)
     if not argv or argv[0] in ("-h", "--help"):
-        print("usage: hipengine-b200 {serve,chat,bench,build,version} [options]")
+        print("usage: hipengine-b200 {serve,router,chat,bench,build,version} [options]")
         return 0
     cmd, rest = argv[0], argv[1:]
     if cmd == "version":
@@ -19,6 +19,9 @@ def main(argv: Optional[List[str]] = None) -> int:
     if cmd == "serve":
         from .server.__main__ import main as serve_main
         return serve_main(rest)
+    if cmd == "router":
+        from .server.router import main as router_main
+        return router_main(rest)
     if cmd == "chat":
         from .chat_cli import main as chat_main
         return chat_main(rest)
