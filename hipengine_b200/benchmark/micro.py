@@ -226,6 +226,50 @@ def bench_fused_allreduce_gemm(M, N, K, phases=7):
             "fused_ms": round(ms_f, 4), "gemm_plus_add_ms": round(ms_p, 4), "fused_tflops": round(tf / ms_f, 1)}
 
 
+def bench_seq_parallel_loopback(M, N, K, qtype="q4_k"):
+    """The sequence-parallel prefill kernels on the 1-rank loopback form (world = 1: this GPU is the owner of every
+    tile and its own peer): GEMM -> reduce-scatter -> residual add in one tcgen05 kernel, RMSNorm + all-gather push,
+    and the consumer GEMM with the all-gather wait in its TMA producer -- the form an ncu capture may run on."""
+    from hipengine_b200.models.executor import _Scratch
+    from hipengine_b200.ops import gemm as G
+    from hipengine_b200.ops import kernels as Kn
+    from hipengine_b200.parallel.fused import SeqParallel
+    from hipengine_b200.quant import ggml as Q
+    t = {"q4_k": Q.GGMLType.Q4_K, "q6_k": Q.GGMLType.Q6_K, "q8_0": Q.GGMLType.Q8_0}[qtype]
+    sp = SeqParallel.emulated_group("cuda", N, 1, max_rows=M)[0]
+    raw = Q.quantize(torch.randn(N, K, device="cuda") * 0.02, t)
+    nvar = max(2, int(260e6 // (N * Q.row_bytes(t, K))) + 1)
+    dws = [Kn.to_device_weight(raw.clone(), t, N, K) for _ in range(nvar)]
+    x = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+    sp.h[:M].normal_()
+    ms_rs = time_launches(lambda i: sp.gemm_rs(x, dws[i], M), nvar)
+    nw = torch.ones(N, device="cuda")
+    ms_np = time_launches(lambda i: sp.norm_push(M, nw, 1e-6), nvar)
+    sp.wait()
+    raw2 = Q.quantize(torch.randn(K, N, device="cuda") * 0.02, t) if N % 256 == 0 else None
+    out = []
+    tf = 2.0 * M * N * K / 1e9
+    out.append({"kernel": f"gemm_q_reduce_scatter[{qtype}, world=1]", "M": M, "N": N, "K": K, "ms": round(ms_rs, 4),
+                "tflops": round(tf / ms_rs, 1)})
+    out.append({"kernel": "rmsnorm_allgather_push[world=1]", "T": M, "H": N, "ms": round(ms_np, 4),
+                "GBps": round(M * N * (4 + 2) / ms_np / 1e6, 1)})
+    if raw2 is not None:
+        dw2 = [Kn.to_device_weight(raw2.clone(), t, K, N) for _ in range(nvar)]
+        sc = _Scratch(torch.device("cuda", torch.cuda.current_device()))
+        y = torch.empty(M, K, device="cuda", dtype=torch.bfloat16)
+
+        def ag(i):
+            sp.norm_push(M, nw, 1e-6)
+            sp.ag_pending = False
+            G.gemm_quant(sp.xn[:M], dw2[i], y, sc, ag=sp.ag_args())
+        ms_ag = time_launches(ag, nvar)
+        out.append({"kernel": f"norm_push + allgather_wait_gemm_q[{qtype}, world=1]", "M": M, "N": K, "K": N,
+                    "ms": round(ms_ag, 4), "tflops_of_the_gemm": round(tf / max(ms_ag - ms_np, 1e-6), 1)})
+    Kn.check_status()
+    sp.close()
+    return out
+
+
 def bench_sustained(M, N, K, qtype="q4_k", secs=2.5):
     """Seconds-long loops of the quantised GEMM, the bf16 tcgen05 GEMM and cuBLAS on one shape with the SM clock and
     board power sampled (read-only nvidia-smi query) every 100 ms: what the kernels sustain under the power cap."""
@@ -354,8 +398,8 @@ def bench_decode_step(rows_list, model="qwen35-27b", ctx=1024, small_rows=None):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "gemmq", "gemv", "gdn", "conv", "attn", "fusedar", "step", "sustained",
-                                     "roles", "all"])
+    ap.add_argument("what", choices=["gemm", "gemmq", "gemv", "gdn", "conv", "attn", "fusedar", "seqpar", "step",
+                                     "sustained", "roles", "all"])
     ap.add_argument("--rows-list", default="1,2,4,8,16,32,64")
     ap.add_argument("--model", default="qwen35-27b")
     ap.add_argument("--small-rows", type=int, default=None)
@@ -383,6 +427,8 @@ def main():
         out.append(bench_conv(a.t))
     elif a.what == "attn":
         out.append(bench_attn_decode(a.ctx, rows=a.rows))
+    elif a.what == "seqpar":
+        out += bench_seq_parallel_loopback(a.m, a.n, a.k, a.qtype)
     elif a.what == "sustained":
         out += bench_sustained(a.m, a.n, a.k, a.qtype)
     elif a.what == "roles":
