@@ -336,3 +336,14 @@ def test_unsupported_kv_storage_is_refused_not_ignored():
     with pytest.raises(ValueError, match="kv_storage"):
         LLM("tiny-dense", backend="cpu_reference", kv_storage="int8")
     assert LLM("tiny-dense", backend="cpu_reference", kv_storage="auto").config.kv.storage == "bf16"
+
+
+def test_decode_attention_split_policy():
+    """One 64-key tile per CTA for a single short row, spans up to 1024 keys for wide batches, always whole tiles."""
+    from hipengine_b200.ops.kernels import attn_decode_split
+    assert attn_decode_split(4096, 1, 4) == (64, 64)
+    sl, ns = attn_decode_split(4096, 16, 4)
+    assert sl % 64 == 0 and 256 <= sl <= 512 and ns == -(-4096 // sl)
+    assert attn_decode_split(4096, 64, 4)[0] == 1024
+    assert attn_decode_split(262144, 1, 4) == (1024, 256)
+    assert attn_decode_split(1, 1, 1) == (64, 1)
