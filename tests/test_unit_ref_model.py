@@ -59,7 +59,7 @@ def test_moe_route_ties_prefer_lower_id():
 
 
 def test_tiny_dense_greedy_generation_config1():
-    """BASELINE config 1: 32-token prompt, 16 greedy tokens, logits finite and reproducible."""
+    """Tiny dense benchmark config: 32-token prompt, 16 greedy tokens, logits finite and reproducible."""
     w = build_random_model(TINY_DENSE, seed=0)
     m = RefModel(w)
     g = torch.Generator().manual_seed(0)
