@@ -49,12 +49,23 @@ class KVConfig:
     storage: str = "bf16"                   # bf16 | int8 (per token/head scales)
     pool_pages: Optional[int] = None        # None: sized from free memory
     memory_reserve_mib: int = 3072          # never admit below this free-memory floor
+    pool_budget_mib: Optional[int] = None   # size the page pool from a memory budget (pool_pages wins when both are set)
     prefix_cache: str = "radix"             # off | radix
     snapshot_interval_tokens: int = 2048    # hybrid recurrent-state snapshot cadence for prefix reuse
     max_snapshots: int = 16
     cold_tier_bytes: int = 0                # > 0: evicted prefix blocks go to a host / disk tier (``kvcache/tiering.py``)
     cold_tier_dir: Optional[str] = None     # None: host memory; a path: one file per object
     cold_restore_prefill_tok_s: float = 16000.0   # recompute rate the restore economics compare against
+
+
+def resolve_pool_pages(kv: "KVConfig", kv_bytes_per_token: int, n_slots: int, pages_per_slot: int) -> int:
+    """Pages of the KV pool: an explicit count wins, then a memory budget, else every slot at full context (twice
+    that with the prefix cache on, so cached prefixes do not starve admissions) plus the null page."""
+    if kv.pool_pages:
+        return int(kv.pool_pages)
+    if kv.pool_budget_mib and kv_bytes_per_token > 0:
+        return max(2, int(kv.pool_budget_mib * (1 << 20) // (kv.page_tokens * kv_bytes_per_token)) + 1)
+    return n_slots * pages_per_slot * (2 if kv.prefix_cache != "off" else 1) + 1
 
 
 @dataclass(frozen=True)

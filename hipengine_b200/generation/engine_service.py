@@ -492,7 +492,8 @@ def build_engine(weights, backend: str, config: EngineConfig, tokenizer=None) ->
         max_ctx = min(config.max_sequence_length, weights.config.max_context)
         pages_per_slot = (max_ctx + config.kv.page_tokens - 1) // config.kv.page_tokens
         n_slots = config.scheduler.max_active_requests
-        n_pages = config.kv.pool_pages or (n_slots * pages_per_slot * (2 if config.kv.prefix_cache != "off" else 1) + 1)
+        from ..config import resolve_pool_pages
+        n_pages = resolve_pool_pages(config.kv, weights.config.kv_bytes_per_token(), n_slots, pages_per_slot)
         ex = TPHybridExecutor(weights.to(ctx.device), ctx, max_slots=n_slots + n_snap, max_context=max_ctx,
                               n_pages=n_pages)
         runner = GpuRunner(None, config, eos, executor=ex)

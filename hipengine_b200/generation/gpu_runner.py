@@ -40,7 +40,8 @@ class GpuRunner(BaseRunner):
         self.use_prefix = config.kv.prefix_cache != "off"
         self.n_snap = config.kv.max_snapshots if (self.use_prefix and self.cfg.is_hybrid) else 0
         pages_per_slot = (self.max_context + self.page - 1) // self.page
-        n_pages = config.kv.pool_pages or (self.max_slots * pages_per_slot * (2 if self.use_prefix else 1) + 1)
+        from ..config import resolve_pool_pages
+        n_pages = resolve_pool_pages(config.kv, self.cfg.kv_bytes_per_token(), self.max_slots, pages_per_slot)
         if executor is not None:
             self.ex = executor
             self.max_slots = min(self.max_slots, executor.max_slots)

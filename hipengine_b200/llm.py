@@ -117,8 +117,9 @@ class LLM:
                  kv_storage: str = "bf16", tensor_parallel: int = 1, expert_parallel: int = 1,
                  engine_command_timeout_seconds: float = 300.0, seed: int = 0, tokenizer: Any = None,
                  engine_config: Optional[EngineConfig] = None, device: Optional[str] = None,
-                 weights_recipe: str = "q4_k_m"):
+                 weights_recipe: str = "q4_k_m", expected_quant: Optional[str] = None):
         self.model = model
+        self._expected_quant = expected_quant
         self.backend = self._resolve_backend(backend, device)
         self.profile = ExecutionProfile.parse(execution_profile)
         if kv_storage in ("auto", None):
@@ -247,7 +248,8 @@ class LLM:
                 free = int(f) + (int(weights.nbytes()) if on_dev else 0)
             except Exception:
                 free = None
-        rep = admit(weights, self.config, free_bytes=free, strict=True)
+        rep = admit(weights, self.config, free_bytes=free, strict=True,
+                    expected_quant=getattr(self, "_expected_quant", None))
         self.startup["checks"]["admission"] = {k: rep[k] for k in ("admitted", "plan_complete", "plan_digest",
                                                                    "planned_weights", "widened_to_bf16", "memory")}
 

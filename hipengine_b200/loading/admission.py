@@ -144,21 +144,34 @@ def memory_preflight(weights, engine_config, free_bytes: Optional[int], contract
     max_ctx = min(engine_config.max_sequence_length, cfg.max_context)
     pages_per_slot = -(-max_ctx // kvc.page_tokens)
     n_slots = sched.max_active_requests
-    n_pages = kvc.pool_pages or (n_slots * pages_per_slot * (2 if kvc.prefix_cache != "off" else 1) + 1)
+    from ..config import resolve_pool_pages
+    n_pages = resolve_pool_pages(kvc, cfg.kv_bytes_per_token(), n_slots, pages_per_slot)
     kv_bytes = n_pages * kvc.page_tokens * cfg.kv_bytes_per_token()
     n_snap = kvc.max_snapshots if (kvc.prefix_cache != "off" and cfg.is_hybrid) else 0
     state_bytes = (n_slots + n_snap) * cfg.recurrent_state_bytes()
     # scratch of one 4096-row prefill chunk: a dozen [rows, widest projection] bf16/fp32 buffers + logits rows
     widest = max(cfg.hidden, 2 * getattr(cfg, "ffn", cfg.hidden), getattr(cfg, "linear_qkv_width", 0) or 0)
     scratch_bytes = 4096 * widest * 2 * 6 + 4096 * cfg.hidden * 4 * 4 + 64 * cfg.vocab * 4
+    reserve_bytes = int(getattr(kvc, "memory_reserve_mib", 0)) << 20    # what has to stay free after everything
     need = pc.resident_bytes + kv_bytes + state_bytes + scratch_bytes
-    fits = free_bytes is None or need <= free_bytes
+    fits = free_bytes is None or need + reserve_bytes <= free_bytes
     return {"weight_bytes": pc.resident_bytes, "kv_pool_bytes": int(kv_bytes), "kv_pool_pages": int(n_pages),
             "recurrent_state_bytes": int(state_bytes), "scratch_estimate_bytes": int(scratch_bytes),
-            "required_bytes": int(need), "free_bytes": free_bytes, "fits": bool(fits)}
+            "required_bytes": int(need), "reserve_bytes": reserve_bytes, "free_bytes": free_bytes, "fits": bool(fits)}
 
 
-def admit(weights, engine_config, free_bytes: Optional[int] = None, strict: bool = True) -> Dict[str, Any]:
+def dominant_block_type(weights) -> str:
+    """Block type holding most of the checkpoint's bytes among its matrices (what ``--quant`` is checked against)."""
+    by: Dict[str, int] = {}
+    for t in weights.tensors.values():
+        if len(t.shape) >= 2:
+            k = GGMLType(t.ggml_type).name
+            by[k] = by.get(k, 0) + int(t.raw.numel())
+    return max(by, key=by.get) if by else "-"
+
+
+def admit(weights, engine_config, free_bytes: Optional[int] = None, strict: bool = True,
+          expected_quant: Optional[str] = None) -> Dict[str, Any]:
     """Full admission report; raises ``ArtifactRejected`` (when ``strict``) if the plan is incomplete or does not fit."""
     pc = plan_contract(weights)
     mem = memory_preflight(weights, engine_config, free_bytes, pc)
@@ -167,10 +180,13 @@ def admit(weights, engine_config, free_bytes: Optional[int] = None, strict: bool
               "unsupported": [u.as_dict() for u in pc.unsupported[:32]], "memory": mem,
               "role_manifest": build_role_manifest(weights)}
     reasons = [f"{u.slot} ({u.qtype}): {u.operation}: {u.reason}" for u in pc.unsupported[:8]]
+    report["dominant_block_type"] = dominant_block_type(weights)
+    if expected_quant and expected_quant.upper().replace("_M", "").replace("_S", "") != report["dominant_block_type"]:
+        reasons.append(f"expected {expected_quant} weights, the checkpoint is mostly {report['dominant_block_type']}")
     if not mem["fits"]:
         reasons.append(f"needs {mem['required_bytes'] / 2**30:.1f} GiB (weights {mem['weight_bytes'] / 2**30:.1f}, KV "
                        f"{mem['kv_pool_bytes'] / 2**30:.1f}, state {mem['recurrent_state_bytes'] / 2**30:.1f}), "
-                       f"{(free_bytes or 0) / 2**30:.1f} GiB free")
+                       f"{mem['reserve_bytes'] / 2**30:.1f} to stay free, {(free_bytes or 0) / 2**30:.1f} GiB free")
     report["admitted"] = not reasons
     if reasons and strict:
         raise ArtifactRejected(reasons, report)

@@ -33,11 +33,23 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--request-timeout-ms", type=int, default=None)
     ap.add_argument("--stream-queue-max-chunks", type=int, default=16)
     ap.add_argument("--shutdown-grace-seconds", type=float, default=5.0)
-    ap.add_argument("--batch-window-ms", type=float, default=0.0,
-                    help="hold compatible requests up to this long so that they enter the engine together")
+    ap.add_argument("--batch-window-ms", "--generation-batch-window-ms", dest="batch_window_ms", type=float,
+                    default=0.0, help="hold compatible requests up to this long so that they enter the engine together")
     ap.add_argument("--max-batch-size", type=int, default=64, help="release a held group early at this size")
     ap.add_argument("--kv-storage", default="bf16", choices=["bf16"])
-    ap.add_argument("--kv-pool-pages", type=int, default=None)
+    ap.add_argument("--kv-pool-pages", "--kv-pool-initial-pages", dest="kv_pool_pages", type=int, default=None)
+    ap.add_argument("--kv-pool-memory-budget-mib", type=int, default=None,
+                    help="size the KV page pool from a memory budget instead of a page count")
+    ap.add_argument("--startup-min-free-mib", type=int, default=None,
+                    help="refuse to start unless this much device memory stays free after weights, KV pool and state")
+    ap.add_argument("--eager-load-prompt", default="ping", help="prompt of the start-up smoke request")
+    ap.add_argument("--eager-load-max-tokens", type=int, default=4)
+    ap.add_argument("--replay-dir", default=None, help="write every admitted request as a JSON line into this directory")
+    ap.add_argument("--replay-redaction", default="hash", choices=["none", "hash", "drop"])
+    ap.add_argument("--quant", default=None, help="expected dominant block type of the checkpoint (e.g. Q4_K); a "
+                                                  "mismatch is refused by the artifact admission")
+    ap.add_argument("--debug", action="store_true", help="log level debug")
+    ap.add_argument("--log-color", default="auto", choices=["auto", "always", "never"])
     ap.add_argument("--prefix-cache", default="radix", choices=["off", "radix"])
     ap.add_argument("--prefix-snapshot-interval", type=int, default=2048)
     ap.add_argument("--prefix-max-snapshots", type=int, default=16)
@@ -74,13 +86,17 @@ def configs_from_args(a):
                                   max_active_requests=a.max_active_requests,
                                   stream_mailbox=max(16, a.stream_queue_max_chunks * 4)),
         kv=KVConfig(storage=a.kv_storage, pool_pages=a.kv_pool_pages, prefix_cache=a.prefix_cache,
+                    memory_reserve_mib=(a.startup_min_free_mib if a.startup_min_free_mib is not None
+                                        else KVConfig().memory_reserve_mib),
+                    pool_budget_mib=a.kv_pool_memory_budget_mib,
                     snapshot_interval_tokens=a.prefix_snapshot_interval, max_snapshots=a.prefix_max_snapshots))
     srv = ServerConfig(served_model_name=a.served_model_name or str(a.model).rstrip("/").split("/")[-1],
                        api_key=a.api_key, chat_default_max_tokens=a.chat_default_max_tokens,
                        max_queued_requests=a.max_queued_requests, request_timeout_ms=a.request_timeout_ms,
                        stream_queue_max_chunks=a.stream_queue_max_chunks, metrics=a.metrics,
                        max_chat_sessions=a.max_chat_sessions, shutdown_grace_seconds=a.shutdown_grace_seconds,
-                       batch_window_ms=a.batch_window_ms, max_batch_size=a.max_batch_size)
+                       batch_window_ms=a.batch_window_ms, max_batch_size=a.max_batch_size,
+                       replay_dir=a.replay_dir, replay_redaction=a.replay_redaction)
     srv.validate()
     return eng, srv
 
@@ -93,7 +109,12 @@ def main(argv: Optional[List[str]] = None) -> int:
         from dataclasses import asdict
         print(json.dumps({"engine": asdict(eng), "server": asdict(srv)}, indent=1, default=str))
         return 0
-    logging.basicConfig(level=a.log_level.upper(), format="%(asctime)s %(levelname)s %(name)s: %(message)s")
+    level = "DEBUG" if a.debug else a.log_level.upper()
+    color = a.log_color == "always" or (a.log_color == "auto" and sys.stderr.isatty())
+    fmt = "%(asctime)s %(levelname)s %(name)s: %(message)s"
+    if color:
+        fmt = "\033[2m%(asctime)s\033[0m \033[1m%(levelname)s\033[0m %(name)s: %(message)s"
+    logging.basicConfig(level=level, format=fmt)
     log = logging.getLogger("hipengine_b200.server")
     from ..llm import LLM
     from .api import create_app
@@ -106,7 +127,7 @@ def main(argv: Optional[List[str]] = None) -> int:
               speculative_provider=a.speculative_provider,
               kv_cold_tier_bytes=int(a.kv_cold_tier_gib * (1 << 30)), kv_cold_tier_dir=a.kv_cold_tier_dir,
               tensor_parallel=a.tensor_parallel,
-              expert_parallel=a.expert_parallel, engine_config=eng)
+              expert_parallel=a.expert_parallel, engine_config=eng, expected_quant=a.quant)
     import os
     rank = int(os.environ.get("RANK", "0"))
     if max(a.tensor_parallel, a.expert_parallel) > 1 and rank != 0:
@@ -121,7 +142,8 @@ def main(argv: Optional[List[str]] = None) -> int:
                  {s["name"]: s["seconds"] for s in llm.startup["stages"]}, info)
     if a.startup_chat_smoke:
         from ..llm import SamplingParams
-        out = llm.chat([{"role": "user", "content": "ping"}], SamplingParams(max_tokens=4))
+        out = llm.chat([{"role": "user", "content": a.eager_load_prompt}],
+                       SamplingParams(max_tokens=a.eager_load_max_tokens))
         log.info("startup chat smoke: %d tokens, finish=%s", len(out.token_ids), out.finish.reason)
         llm.mark_warm()
     app = create_app(llm, srv)

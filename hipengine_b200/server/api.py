@@ -47,6 +47,8 @@ class ServerConfig:
     shutdown_grace_seconds: float = 5.0
     batch_window_ms: float = 0.0             # hold compatible requests this long so they are released together
     max_batch_size: int = 64                 # ... or until this many are waiting
+    replay_dir: Optional[str] = None         # request replay log (server/replay.py)
+    replay_redaction: str = "hash"           # none | hash | drop
 
     def validate(self) -> None:
         if self.max_queued_requests < 1:
@@ -55,6 +57,8 @@ class ServerConfig:
             raise ValueError("stream_queue_max_chunks must be >= 1")
         if self.metrics not in (None, "prometheus"):
             raise ValueError("metrics must be None or 'prometheus'")
+        if self.replay_redaction not in ("none", "hash", "drop"):
+            raise ValueError("replay_redaction must be none, hash or drop")
 
 
 class MTPCircuitBreaker:
@@ -188,6 +192,19 @@ def create_app(llm: LLM, config: Optional[ServerConfig] = None) -> FastAPI:
 
     app = FastAPI(title="hipengine_b200", version="0.1.0", lifespan=lifespan)
     sessions = ChatSessionStore(cfg.max_chat_sessions)
+    replay = None
+    if cfg.replay_dir:
+        from .replay import ReplayLog
+        replay = ReplayLog(cfg.replay_dir, cfg.replay_redaction)
+
+    def replay_request(cid: str, route: str, req_model) -> float:
+        if replay is not None:
+            replay.request(cid, route, req_model.model_dump(exclude_none=True))
+        return time.time()
+
+    def replay_outcome(cid: str, t0: float, reason, prompt_tokens: int, completion_tokens: int, error=None) -> None:
+        if replay is not None:
+            replay.outcome(cid, reason, prompt_tokens, completion_tokens, time.time() - t0, error)
     breaker = MTPCircuitBreaker(cfg.mtp_breaker_threshold)
     state = {"started": time.time(), "ready": False, "startup": []}
     app.state.llm, app.state.cfg, app.state.metrics, app.state.sessions, app.state.breaker = llm, cfg, metrics, sessions, breaker
@@ -362,6 +379,7 @@ def create_app(llm: LLM, config: Optional[ServerConfig] = None) -> FastAPI:
         sp = with_timeout(build_completion_params(req, t, cfg.completion_default_max_tokens))
         prompts = _prompts(req)
         cid, created = SE.new_id("cmpl"), int(time.time())
+        t_req = replay_request(cid, "completions", req)
         gate.enter()
         try:
             await gate.admit(gate.compat_key("completions", bool(req.stream), sp.temperature == 0.0, bool(sp.logprobs),
@@ -407,6 +425,7 @@ def create_app(llm: LLM, config: Optional[ServerConfig] = None) -> FastAPI:
                     bridge.close()
                     gate.leave()
                     metrics.inc("hipengine_generated_tokens_total", n_out)
+                    replay_outcome(cid, t_req, "stream", len(greq.prompt_token_ids), n_out)
             return StreamingResponse(gen(), media_type="text/event-stream")
         try:
             plist = [p for p in prompts for _ in range(req.n)]
@@ -426,6 +445,8 @@ def create_app(llm: LLM, config: Optional[ServerConfig] = None) -> FastAPI:
         metrics.inc("hipengine_generated_tokens_total", sum(len(o.token_ids) for o in outs))
         body = {"id": cid, "object": "text_completion", "created": created, "model": cfg.served_model_name,
                 "choices": choices, "usage": _usage(outs)}
+        replay_outcome(cid, t_req, choices[0]["finish_reason"] if choices else None, body["usage"]["prompt_tokens"],
+                       body["usage"]["completion_tokens"])
         if req.stream:   # buffered SSE for multi-prompt / n>1 / echo
             async def buffered():
                 for c in choices:
@@ -472,6 +493,7 @@ def create_app(llm: LLM, config: Optional[ServerConfig] = None) -> FastAPI:
             from dataclasses import replace
             sp = replace(sp, speculative_mtp=False)
         cid, created = SE.new_id("chatcmpl"), int(time.time())
+        t_req = replay_request(cid, "chat", req)
         gate.enter()
         try:
             await gate.admit(gate.compat_key("chat", bool(req.stream), sp.temperature == 0.0, bool(sp.logprobs),
@@ -562,6 +584,7 @@ def create_app(llm: LLM, config: Optional[ServerConfig] = None) -> FastAPI:
                     bridge.close()
                     gate.leave()
                     metrics.inc("hipengine_generated_tokens_total", n_out)
+                    replay_outcome(cid, t_req, final_reason, len(prompt_ids), n_out)
             return StreamingResponse(gen(), media_type="text/event-stream")
 
         try:
@@ -586,6 +609,8 @@ def create_app(llm: LLM, config: Optional[ServerConfig] = None) -> FastAPI:
         metrics.inc("hipengine_generated_tokens_total", sum(len(o.token_ids) for o in outs))
         body = {"id": cid, "object": "chat.completion", "created": created, "model": cfg.served_model_name,
                 "choices": choices, "usage": _usage(outs)}
+        replay_outcome(cid, t_req, choices[0]["finish_reason"] if choices else None, body["usage"]["prompt_tokens"],
+                       body["usage"]["completion_tokens"])
         new_sid = finish_session(choices[0]["message"])
         if new_sid:
             body["session"] = {"id": new_sid}

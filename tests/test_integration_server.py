@@ -264,3 +264,55 @@ def test_replica_router_balances_sticks_to_prefixes_and_fails_over():
             s.should_exit = True
         for l in llms:
             l.close()
+
+
+def test_replay_log_records_requests_with_redaction(tmp_path):
+    """--replay-dir writes one JSON line per admitted request and one per outcome; with the default redaction the
+    prompt text is replaced by a hash and its length."""
+    import json
+    from fastapi.testclient import TestClient
+    from hipengine_b200.llm import LLM
+    from hipengine_b200.server.api import ServerConfig, create_app
+    from hipengine_b200.server.__main__ import build_parser, configs_from_args
+    a = build_parser().parse_args(["--model", "tiny-dense", "--replay-dir", str(tmp_path), "--generation-batch-window-ms", "2",
+                                   "--kv-pool-memory-budget-mib", "64", "--startup-min-free-mib", "128", "--quant", "Q4_K"])
+    eng_cfg, srv_cfg = configs_from_args(a)
+    assert srv_cfg.replay_dir == str(tmp_path) and srv_cfg.batch_window_ms == 2.0
+    assert eng_cfg.kv.pool_budget_mib == 64 and eng_cfg.kv.memory_reserve_mib == 128
+    llm = LLM("tiny-dense", backend="cpu_reference", max_active_requests=2, max_sequence_length=256)
+    try:
+        with TestClient(create_app(llm, ServerConfig(served_model_name="tiny-dense", replay_dir=str(tmp_path)))) as c:
+            r = c.post("/v1/completions", json={"model": "tiny-dense", "prompt": "a secret prompt", "max_tokens": 3,
+                                                "temperature": 0.0})
+            assert r.status_code == 200
+            r = c.post("/v1/chat/completions", json={"model": "tiny-dense", "max_tokens": 3,
+                                                     "messages": [{"role": "user", "content": "another secret"}]})
+            assert r.status_code == 200
+        lines = []
+        for f in tmp_path.iterdir():
+            lines += [json.loads(l) for l in f.read_text().splitlines()]
+        kinds = [l["kind"] for l in lines]
+        assert kinds.count("request") == 2 and kinds.count("outcome") == 2
+        text = json.dumps(lines)
+        assert "secret" not in text and "sha256" in text
+        out = [l for l in lines if l["kind"] == "outcome"][0]
+        assert out["completion_tokens"] == 3 and out["prompt_tokens"] > 0
+    finally:
+        llm.close()
+
+
+def test_pool_budget_and_expected_quant_in_admission():
+    from hipengine_b200.config import EngineConfig, KVConfig, resolve_pool_pages
+    from dataclasses import replace
+    kv = KVConfig(pool_budget_mib=64)
+    assert resolve_pool_pages(kv, kv_bytes_per_token=4096, n_slots=4, pages_per_slot=64) == 64 * (1 << 20) // (16 * 4096) + 1
+    assert resolve_pool_pages(replace(kv, pool_pages=77), 4096, 4, 64) == 77
+    import pytest
+    from hipengine_b200.loading.admission import ArtifactRejected, admit
+    from hipengine_b200.loading.synth import build_random_model
+    from hipengine_b200.models.config import TINY_DENSE
+    w = build_random_model(TINY_DENSE, seed=0)
+    rep = admit(w, EngineConfig.from_env(), free_bytes=10 ** 12, expected_quant=None)
+    with pytest.raises(ArtifactRejected, match="expected"):
+        admit(w, EngineConfig.from_env(), free_bytes=10 ** 12, expected_quant="Q2_K")
+    assert admit(w, EngineConfig.from_env(), free_bytes=10 ** 12, expected_quant=rep["dominant_block_type"])["admitted"]
