@@ -495,6 +495,11 @@ class GpuRunner(BaseRunner):
             for rs, c in zip(rows, res):
                 self.mtp.drafter.observe(list(rs.req.prompt_token_ids) + rs.generated + list(c.tokens))
         for rs, c in zip(rows, res):
+            # KV rollback: the cycle reserved pages for every draft; keep those of the accepted prefix (+ the next
+            # token) and hand the rest back to the request's credit
+            lease = rs.runner_data
+            if lease is not None:
+                self.pool.truncate_pages(lease, rs.position + c.accepted + 1)
             rs.sample_counter += 2 * (depth + 1)
             rs.telemetry.d2h_bytes += 8 * (depth + 2)
             rs.telemetry.h2d_bytes += 24 * (depth + 1)

@@ -1,9 +1,10 @@
-"""Global paged KV pool: host-side page accounting with refcounts, leases and copy-on-write.
+"""Global paged KV pool: host-side page accounting with refcounts, credit reservations and leases.
 
 State machine and API follow the reference's ``GlobalKVPoolSet``
 (``hipengine/kvcache/global_pool.py:26-34`` page states, ``:225-283`` append/truncate,
-``:466`` copy_on_write, ``:480-498`` in-flight epochs, ``:506-518`` cache retain/release,
-``:593`` assert_conserved).  Pages are ``page_tokens`` (16 by default) tokens wide; the device tensors they
+``:480-498`` in-flight epochs, ``:506-518`` cache retain/release, ``:593`` assert_conserved).  Prefixes are shared
+at page boundaries only and a request always owns its last, partial page, so no page is ever written while shared
+and the reference's copy-on-write step has nothing to do here.  Pages are ``page_tokens`` (16 by default) tokens wide; the device tensors they
 index live in the executor (one ``[n_pages, 2, Hkv, page, D]`` tensor per full-attention layer), so a page
 id addresses the same slot in every layer.  Page 0 is reserved as a write sink for padded rows.
 """
@@ -58,7 +59,7 @@ class PagePool:
         self.leases: Dict[int, KVLease] = {}
         self.epoch = 0
         self.evict_hook: Optional[Callable[[int], List[int]]] = None  # asks the prefix cache to give pages back
-        self.stats = {"grants": 0, "cow": 0, "evictions": 0, "peak_used": 0}
+        self.stats = {"grants": 0, "truncated": 0, "evictions": 0, "peak_used": 0}
 
     # -- queries
     def pages_for(self, tokens: int) -> int:
@@ -162,22 +163,8 @@ class PagePool:
         lease.credit += len(dropped)
         self.credit_total += len(dropped)
         lease.tokens = min(lease.tokens, keep_tokens)
+        self.stats["truncated"] += len(dropped)
         return dropped
-
-    def copy_on_write(self, lease: KVLease, page_index: int) -> Tuple[int, int]:
-        """Make page ``page_index`` of the lease private.  Returns (old_page, new_page); caller copies the bytes."""
-        old = lease.pages[page_index]
-        if self.refcount[old] == 1 and not self.cached[old]:
-            return old, old
-        new = self._take(1)[0]
-        self.refcount[new] = 1
-        self._unref(old)
-        lease.pages[page_index] = new
-        if page_index < lease.n_shared:
-            # everything after a privatised page must also be private; callers only COW the last shared page
-            lease.n_shared = page_index
-        self.stats["cow"] += 1
-        return old, new
 
     def release(self, owner: int) -> None:
         lease = self.leases.pop(owner, None)

@@ -107,7 +107,7 @@ class ServerMetrics:
             emit("hipengine_kv_pool_current_bytes", (pool.get("pages_used") or 0) * page_bytes)
             emit("hipengine_kv_pool_high_water_observed_bytes", (pool.get("peak_used") or 0) * page_bytes)
             emit("hipengine_resident_kv_total_bytes", (pool.get("pages_total") or 0) * page_bytes)
-        for k in ("pages_credit", "leases", "grants", "cow", "evictions"):
+        for k in ("pages_credit", "leases", "grants", "truncated", "evictions"):
             emit(f"hipengine_kv_pool_{k}", pool.get(k))
         pref = capacity.get("prefix_cache", {})
         for k in ("nodes", "lookups", "hits", "hit_tokens", "inserted_pages", "evicted_pages"):

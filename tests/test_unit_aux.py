@@ -347,3 +347,22 @@ def test_decode_attention_split_policy():
     assert attn_decode_split(4096, 64, 4)[0] == 1024
     assert attn_decode_split(262144, 1, 4) == (1024, 256)
     assert attn_decode_split(1, 1, 1) == (64, 1)
+
+
+def test_pool_truncation_returns_speculative_pages_to_the_lease_credit():
+    """A speculative cycle reserves pages for every draft; what the accepted prefix does not need goes back to the
+    request's credit, and the next cycle takes it from there (page conservation holds throughout)."""
+    from hipengine_b200.kvcache.pool import PagePool
+    pool = PagePool(n_pages=32, page_tokens=16)
+    lease = pool.admit(7, total_tokens=200, shared_prefix=[], now_tokens=40)     # 3 pages now, credit for the rest
+    credit0 = lease.credit
+    pool.append_pages(lease, 40 + 3 * 16)                                          # drafts reach three pages further
+    assert len(lease.pages) == 6 and lease.credit == credit0 - 3
+    dropped = pool.truncate_pages(lease, 41 + 1)                                   # one token accepted
+    assert len(dropped) == 3 and len(lease.pages) == 3 and lease.credit == credit0
+    pool.assert_conserved()
+    pool.append_pages(lease, 40 + 2 * 16)
+    assert len(lease.pages) == 5 and lease.credit == credit0 - 2 and pool.stats["truncated"] == 3
+    pool.assert_conserved()
+    pool.release(7)
+    pool.assert_conserved()
