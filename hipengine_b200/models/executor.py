@@ -83,10 +83,18 @@ class _Scratch:
     bounds the retired bytes by the live bytes.
     """
 
-    def __init__(self, device):
+    CANARY_BYTES = 256
+    CANARY_BYTE = 0xA5
+
+    def __init__(self, device, canaries: Optional[bool] = None):
         self.device = device
         self.bufs: Dict[str, torch.Tensor] = {}
         self.retired: List[torch.Tensor] = []
+        # canary words behind every buffer (HE_SCRATCH_CANARY=1 or canaries=True): a kernel that writes past the
+        # extent it was given lands in them, and check_canaries() names the buffer -- the host-side check that stands
+        # in for a memory checker on the scratch arena
+        self.canaries = (os.environ.get("HE_SCRATCH_CANARY", "0") == "1") if canaries is None else canaries
+        self._raw: Dict[str, torch.Tensor] = {}
 
     def get(self, name: str, shape, dtype) -> torch.Tensor:
         n = 1
@@ -95,16 +103,34 @@ class _Scratch:
         cur = self.bufs.get(name)
         if cur is None or cur.numel() < n or cur.dtype != dtype:
             if cur is not None:
-                self.retired.append(cur)
+                self.retired.append(self._raw.get(name, cur))
                 if cur.dtype == dtype:
                     n_alloc = max(n, 2 * cur.numel())
                 else:
                     n_alloc = n
             else:
                 n_alloc = n
-            cur = torch.empty(max(n_alloc, 1), dtype=dtype, device=self.device)
+            n_alloc = max(n_alloc, 1)
+            if self.canaries:
+                esz = torch.empty(0, dtype=dtype).element_size()
+                pad = -(-self.CANARY_BYTES // esz)
+                raw = torch.empty(n_alloc + pad, dtype=dtype, device=self.device)
+                raw[n_alloc:].view(torch.uint8).fill_(self.CANARY_BYTE)
+                self._raw[name] = raw
+                cur = raw[:n_alloc]
+            else:
+                cur = torch.empty(n_alloc, dtype=dtype, device=self.device)
             self.bufs[name] = cur
         return cur[:n].view(*shape)
+
+    def check_canaries(self) -> List[str]:
+        """Names of the buffers whose trailing canary words were overwritten (empty when clean or canaries are off)."""
+        bad = []
+        for name, raw in self._raw.items():
+            n = self.bufs[name].numel()
+            if not bool((raw[n:].view(torch.uint8) == self.CANARY_BYTE).all()):
+                bad.append(name)
+        return bad
 
     def retired_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self.retired)

@@ -48,6 +48,7 @@ def test_outputs_do_not_depend_on_scratch_contents(cfg):
     from hipengine_b200.ops import kernels as K
     w = build_random_model(cfg, seed=2, std=0.05).to("cuda")
     ex = make_executor(w, device="cuda", max_slots=2, max_context=512)
+    ex.scratch.canaries = True                 # canary words behind every scratch buffer, checked at the end
     prompt = torch.randint(0, cfg.vocab, (200,), generator=torch.Generator().manual_seed(4)).tolist()
     first = _run(ex, prompt, rows=24)
     torch.cuda.synchronize()
@@ -58,3 +59,4 @@ def test_outputs_do_not_depend_on_scratch_contents(cfg):
     for a, b in zip(first, second):
         assert torch.isfinite(b).all()
         assert torch.equal(a, b)
+    assert len(ex.scratch._raw) > 5 and ex.scratch.check_canaries() == []      # nothing wrote past its extent

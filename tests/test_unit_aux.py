@@ -366,3 +366,39 @@ def test_pool_truncation_returns_speculative_pages_to_the_lease_credit():
     pool.assert_conserved()
     pool.release(7)
     pool.assert_conserved()
+
+
+def test_every_environment_switch_is_documented():
+    """docs/ENVS.md lists every HE_* variable the source reads (getenv / os.environ)."""
+    import re
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    doc = (root / "docs" / "ENVS.md").read_text()
+    pat = re.compile(r"""(?:getenv\(\s*"|environ(?:\.get|\.setdefault)?\(\s*"|environ\[\s*"|"\s*in\s+e\b.*?|e\[")(HE_[A-Z0-9_]+)""")
+    used = set()
+    files = list((root / "hipengine_b200").rglob("*.py")) + list((root / "hipengine_b200" / "csrc").glob("*.c*")) + \
+        [root / "bench.py", root / "__graft_entry__.py"]
+    for f in files:
+        text = f.read_text(errors="ignore")
+        used |= set(pat.findall(text))
+        used |= set(re.findall(r'if "(HE_[A-Z0-9_]+)" in e', text))
+    missing = sorted(v for v in used if f"`{v}`" not in doc)
+    assert not missing, f"undocumented environment switches: {missing}"
+    assert len(used) >= 25
+
+
+def test_scratch_canaries_detect_a_write_past_the_extent():
+    import torch
+    from hipengine_b200.models.executor import _Scratch
+    sc = _Scratch(torch.device("cpu"), canaries=True)
+    a = sc.get("a", (4, 8), torch.float32)
+    b = sc.get("b", (16,), torch.bfloat16)
+    a.fill_(1.0)
+    b.fill_(2.0)
+    assert sc.check_canaries() == []
+    sc._raw["b"][16] = 7.0                      # one element past the buffer
+    assert sc.check_canaries() == ["b"]
+    big = sc.get("a", (64, 8), torch.float32)   # growth keeps the old buffer retired and re-arms the canary
+    big.zero_()
+    assert "a" not in sc.check_canaries() and len(sc.retired) == 1
+    assert _Scratch(torch.device("cpu"), canaries=False).check_canaries() == []
