@@ -49,6 +49,11 @@ struct HeGemvArgs {
   int slot_bytes;   // bytes of one ring slot = rg * row_stride
   int* status;      // device status word (may be null)
   HeGemvComm comm;  // mode 0: unused
+  // Optional image of the normalised + quantised activation rows in exactly the kernel's shared-memory layout
+  // (he_gemv_prequant): the CTAs copy it instead of each running the prologue over all R rows.  With several rows the
+  // per-CTA prologue (R x K elements and a block reduction per row, in every CTA of every launch) costs more than
+  // the dot products of the small projections.
+  const uint8_t* x_image;
 };
 
 namespace {
@@ -294,6 +299,58 @@ __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint3
 
 __device__ __forceinline__ float apply_act(float g, int epi) { return epi == 3 ? silu_f(g) : gelu_tanh_f(g); }
 
+// One CTA per activation row: (optional RMSNorm) + per-32 int8 quantisation of row blockIdx.x into `image`, which has
+// the layout of gemv_kernel's shared-memory activation area for R rows (xq | dx | sx | inv_rms).
+__global__ void __launch_bounds__(512) gemv_prequant_kernel(const void* __restrict__ x, int x_dtype, long long x_stride,
+                                                            const float* __restrict__ norm_w, float eps, int K, int R,
+                                                            uint8_t* __restrict__ image) {
+  __shared__ float red[33];
+  const int r = blockIdx.x, nb = K >> 8, n_groups = K / 8;
+  // let the consumer GEMV start right away (it only prefetches weights until its own wait, which this grid's
+  // completion releases), then wait: the rows come from the previous kernel, and the image may still be read by it
+  pdl_launch();
+  pdl_wait();
+  SmemView s;
+  s.xq_row = nb * hegemv::XQ_STRIDE;
+  s.sc_row = nb * 8;
+  s.xq = reinterpret_cast<int8_t*>(image);
+  s.dx = reinterpret_cast<float*>(image + (size_t)R * s.xq_row);
+  s.sx = s.dx + (size_t)R * s.sc_row;
+  s.inv_rms = s.sx + (size_t)R * s.sc_row;
+  const size_t base = (size_t)r * x_stride;
+  float inv_rms = 1.f;
+  if (norm_w != nullptr) {
+    float ss = 0.f;
+    for (int g = threadIdx.x; g < n_groups; g += blockDim.x) {
+      float v[8];
+      load8(x, x_dtype, base + (size_t)g * 8, v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
+    }
+    ss = block_sum(ss, red);
+    inv_rms = rsqrtf(ss / (float)K + eps);
+  }
+  if (threadIdx.x == 0) s.inv_rms[r] = inv_rms;
+  for (int g0 = 0; g0 < n_groups; g0 += blockDim.x) {
+    const int g = g0 + threadIdx.x;
+    const bool valid = g < n_groups;
+    float v[8];
+    if (valid) {
+      load8(x, x_dtype, base + (size_t)g * 8, v);
+      if (norm_w != nullptr) {
+        const float4* wp = reinterpret_cast<const float4*>(norm_w + (size_t)g * 8);
+        const float4 w0 = __ldg(wp), w1 = __ldg(wp + 1);
+        v[0] *= inv_rms * w0.x; v[1] *= inv_rms * w0.y; v[2] *= inv_rms * w0.z; v[3] *= inv_rms * w0.w;
+        v[4] *= inv_rms * w1.x; v[5] *= inv_rms * w1.y; v[6] *= inv_rms * w1.z; v[7] *= inv_rms * w1.w;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = 0.f;
+    }
+    quant_store(s, K, r, g, valid, v);
+  }
+}
+
 // Cursor over this warp's units: item index (global), unit within item, ring slot and its phase parity.
 struct Cursor {
   int item;     // global item id
@@ -401,7 +458,20 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const __grid_constant_
     for (int q = 0; q < a.comm.world; ++q) ll_store(a.comm.recv[q] + off, v, push_seq + 1u);
   };
 
-  prologue<R, COMM>(a, s, red);
+  if (a.x_image != nullptr) {
+    // rows already normalised and quantised by he_gemv_prequant (complete: griddepcontrol.wait above): copy the image
+    const uint32_t img16 = ((uint32_t)R * s.xq_row + (uint32_t)R * s.sc_row * 8 + 64) >> 4;
+    const uint4* src = reinterpret_cast<const uint4*>(a.x_image);
+    uint4* dst = reinterpret_cast<uint4*>(smem);
+    for (uint32_t i = threadIdx.x; i < img16; i += blockDim.x) {
+      uint4 v;
+      asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(src + i));
+      dst[i] = v;
+    }
+    __syncthreads();
+  } else {
+    prologue<R, COMM>(a, s, red);
+  }
 
   const int t_row = lane >> bq_shift, bq = lane & (BQ - 1);
   float acc[R];
@@ -605,9 +675,26 @@ int launch_gemv(HeGemvArgs a, int num_sms, cudaStream_t stream) {
 // Launch the fused GEMV.  `args` is a host pointer to HeGemvArgs (copied by value into the launch).
 // K must be a multiple of 256.  Returns -HE_ERR_BAD_ARG when the activation rows plus the staging rings do
 // not fit shared memory (callers then split the activation rows over two launches).
+// Bytes of the activation image of R rows of K columns (what he_gemv_prequant writes and he_gemv copies).
+HE_API long long he_gemv_image_bytes(int R, int K) {
+  const long long nb = K >> 8;
+  return (((long long)R * nb * hegemv::XQ_STRIDE + (long long)R * nb * 8 * 8 + 64 + 127) / 128) * 128;
+}
+
+// image <- (optional RMSNorm with norm_w) + per-32 int8 quantisation of the R rows x[r][0..K).  K % 256 == 0.
+HE_API int he_gemv_prequant(const void* x, int x_dtype, long long x_stride, const float* norm_w, float eps, int K,
+                            int R, void* image, cudaStream_t stream) {
+  if (K % 256 != 0 || R < 1 || R > 8 || x == nullptr || image == nullptr) return -HE_ERR_BAD_ARG;
+  cudaError_t le = launch_pdl(gemv_prequant_kernel, dim3(R), dim3(512), 0, stream, x, x_dtype, x_stride, norm_w, eps,
+                              K, R, (uint8_t*)image);
+  if (le != cudaSuccess) return (int)le;
+  return 0;
+}
+
 HE_API int he_gemv(const HeGemvArgs* args, int num_sms, cudaStream_t stream) {
   const HeGemvArgs& a = *args;
   if (a.K % 256 != 0 || a.n_seg < 1 || a.n_seg > 4 || a.R < 1 || a.R > 8) return -HE_ERR_BAD_ARG;
+  if (a.x_image != nullptr && a.comm.mode != 0) return -HE_ERR_BAD_ARG;   // the reduce prologue computes its rows
   if (a.comm.mode != 0) {
     const HeGemvComm& c = a.comm;
     if (c.world < 2 || c.world > GEMV_MAX_WORLD || c.rank < 0 || c.rank >= c.world || c.state == nullptr ||

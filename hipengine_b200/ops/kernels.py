@@ -8,7 +8,8 @@ from __future__ import annotations
 
 import ctypes as C
 from dataclasses import dataclass
-from typing import List, Optional, Sequence, Tuple
+import os
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
@@ -38,7 +39,7 @@ COMM_PUSH, COMM_REDUCE = 1, 2
 class _GemvArgs(C.Structure):
     _fields_ = [("seg", _GemvSeg * 4), ("n_seg", C.c_int), ("K", C.c_int), ("R", C.c_int), ("x_dtype", C.c_int),
                 ("x", c_vp), ("x_stride", c_ll), ("norm_w", c_vp), ("eps", C.c_float), ("n_slots", C.c_int),
-                ("rg", C.c_int), ("slot_bytes", C.c_int), ("status", c_vp), ("comm", GemvComm)]
+                ("rg", C.c_int), ("slot_bytes", C.c_int), ("status", c_vp), ("comm", GemvComm), ("x_image", c_vp)]
 
 
 class _QkvArgs(C.Structure):
@@ -211,6 +212,22 @@ class GemvSegment:
     w2: Optional[DeviceWeight] = None
 
 
+_GEMV_IMAGES: Dict[Tuple[str, int], torch.Tensor] = {}
+# rows from which the activation rows are normalised + quantised once per launch by a small kernel instead of by every
+# CTA of the GEMV (HE_GEMV_PREQUANT_ROWS; 0 = never): measured on the 27B, the per-CTA prologue is ~2.6 ms per extra
+# row of a decode step
+PREQUANT_MIN_ROWS = int(os.environ.get("HE_GEMV_PREQUANT_ROWS", "2"))
+
+
+def _gemv_image(device: torch.device, nbytes: int) -> torch.Tensor:
+    """Persistent buffer for the activation image (kept for the life of the process: captured graphs bake it in)."""
+    key = (str(device), nbytes)
+    t = _GEMV_IMAGES.get(key)
+    if t is None:
+        t = _GEMV_IMAGES[key] = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    return t
+
+
 def gemv(x: torch.Tensor, segs: Sequence[GemvSegment], norm_w: Optional[torch.Tensor] = None,
          eps: float = 1e-6, comm: Optional[GemvComm] = None) -> None:
     """Fused [RMSNorm] + int8 activation quantize + quantized GEMV + epilogue for 1..8 rows.
@@ -244,6 +261,14 @@ def gemv(x: torch.Tensor, segs: Sequence[GemvSegment], norm_w: Optional[torch.Te
     a.status = _status_ptr(x.device)
     if comm is not None:
         a.comm = comm
+    elif PREQUANT_MIN_ROWS and R >= PREQUANT_MIN_ROWS:
+        L = N.lib()
+        L.he_gemv_image_bytes.restype = C.c_longlong
+        img = _gemv_image(x.device, int(L.he_gemv_image_bytes(C.c_int(R), C.c_int(K))))
+        N.check(L.he_gemv_prequant(c_vp(x.data_ptr()), C.c_int(_dt(x)), c_ll(x.stride(0)), c_vp(_p(norm_w)),
+                                   C.c_float(eps), C.c_int(K), C.c_int(R), c_vp(img.data_ptr()), _stream()),
+                "he_gemv_prequant")
+        a.x_image = img.data_ptr()
     rc = N.lib().he_gemv(C.byref(a), C.c_int(N.num_sms()), _stream())
     if rc == -3 and R > 1 and comm is None:
         # activation rows + staging rings do not fit shared memory: run the rows in two halves
