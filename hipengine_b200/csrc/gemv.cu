@@ -458,7 +458,7 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const __grid_constant_
     for (int q = 0; q < a.comm.world; ++q) ll_store(a.comm.recv[q] + off, v, push_seq + 1u);
   };
 
-  if (a.x_image != nullptr) {
+  if (R >= 2 && a.x_image != nullptr) {   // single-row launches keep the in-CTA prologue (he_gemv refuses an image)
     // rows already normalised and quantised by he_gemv_prequant (complete: griddepcontrol.wait above): copy the image
     const uint32_t img16 = ((uint32_t)R * s.xq_row + (uint32_t)R * s.sc_row * 8 + 64) >> 4;
     const uint4* src = reinterpret_cast<const uint4*>(a.x_image);
@@ -694,7 +694,8 @@ HE_API int he_gemv_prequant(const void* x, int x_dtype, long long x_stride, cons
 HE_API int he_gemv(const HeGemvArgs* args, int num_sms, cudaStream_t stream) {
   const HeGemvArgs& a = *args;
   if (a.K % 256 != 0 || a.n_seg < 1 || a.n_seg > 4 || a.R < 1 || a.R > 8) return -HE_ERR_BAD_ARG;
-  if (a.x_image != nullptr && a.comm.mode != 0) return -HE_ERR_BAD_ARG;   // the reduce prologue computes its rows
+  // the reduce prologue computes its rows itself; one row is cheaper to quantise in the CTA than to copy
+  if (a.x_image != nullptr && (a.comm.mode != 0 || a.R < 2)) return -HE_ERR_BAD_ARG;
   if (a.comm.mode != 0) {
     const HeGemvComm& c = a.comm;
     if (c.world < 2 || c.world > GEMV_MAX_WORLD || c.rank < 0 || c.rank >= c.world || c.state == nullptr ||

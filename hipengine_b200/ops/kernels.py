@@ -261,7 +261,7 @@ def gemv(x: torch.Tensor, segs: Sequence[GemvSegment], norm_w: Optional[torch.Te
     a.status = _status_ptr(x.device)
     if comm is not None:
         a.comm = comm
-    elif PREQUANT_MIN_ROWS and R >= PREQUANT_MIN_ROWS:
+    elif PREQUANT_MIN_ROWS and R >= max(2, PREQUANT_MIN_ROWS):
         L = N.lib()
         L.he_gemv_image_bytes.restype = C.c_longlong
         img = _gemv_image(x.device, int(L.he_gemv_image_bytes(C.c_int(R), C.c_int(K))))
