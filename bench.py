@@ -402,7 +402,9 @@ def run_mtp(args, cfg, dev, prompt, ctx_max):
     weights = build_random_model(cfgm, seed=0, device=dev, recipe="q4_k_m")
     ex = make_executor(weights, device=dev, max_slots=1, max_context=ctx_max)
     del weights
-    cyc = GraphedMTPCycle(ex, max_depth=depth, max_requests=1)
+    from hipengine_b200.speculative.draft_vocab import resolve_hot_vocab_rows
+    hot_rows = resolve_hot_vocab_rows("auto", cfgm.vocab)
+    cyc = GraphedMTPCycle(ex, max_depth=depth, max_requests=1, draft_head_rows=hot_rows)
     runner = DecodeGraphRunner(ex, max_rows=1)
     b = make_batch([(0, 0, prompt)], dev)
     h = ex.forward(b)
@@ -411,12 +413,12 @@ def run_mtp(args, cfg, dev, prompt, ctx_max):
     pos = len(prompt)                                   # position of `last`
     ev = lambda: torch.cuda.Event(enable_timing=True)
 
-    def cycles(n, override=None):
+    def cycles(n, override=None, small=False):
         nonlocal last, pos
         toks = 0
         for i in range(n):
             ov = None if override is None else torch.tensor([override[toks:toks + depth]])
-            res, _ = cyc.cycle([0], [last], [pos], depth, draft_override=ov)
+            res, _ = cyc.cycle([0], [last], [pos], depth, draft_override=ov, small_head=small)
             toks += len(res[0].tokens)
             last, pos = res[0].tokens[-1], pos + len(res[0].tokens)
         return toks
@@ -430,6 +432,17 @@ def run_mtp(args, cfg, dev, prompt, ctx_max):
     e1.record()
     torch.cuda.synchronize()
     cycle_ms = e0.elapsed_time(e1) / n_cyc
+    # the same cycle drafting with the leading slice of the head (hot-vocabulary draft head; verification unchanged)
+    hot_ms = None
+    if cyc.draft_head_rows > 0:
+        cycles(3, small=True)
+        e4, e5 = ev(), ev()
+        torch.cuda.synchronize()
+        e4.record()
+        cycles(n_cyc, small=True)
+        e5.record()
+        torch.cuda.synchronize()
+        hot_ms = e4.elapsed_time(e5) / n_cyc
     # autoregressive steps from the same state (graph replay), recorded: they are the true continuation
     snap = {"conv": {i: t[0].clone() for i, t in ex.conv_state.items()},
             "gdn": {i: t[0].clone() for i, t in ex.gdn_state.items()}, "hp": cyc.h_prev[0].clone()}
@@ -461,7 +474,10 @@ def run_mtp(args, cfg, dev, prompt, ctx_max):
             "tokens_per_cycle_all_accepted": round(forced / 6, 3),
             "speedup_all_accepted": round((forced / 6) / units, 3),
             "kernels_per_cycle_graph": list(cyc.graph_stats["kernels_per_graph"].values())[:1],
-            "graph": cyc.graph_stats["captures"], "note": "random weights: own drafts are almost never accepted"}
+            "graph": cyc.graph_stats["captures"],
+            "hot_vocab": None if hot_ms is None else {"rows": cyc.draft_head_rows, "cycle_ms": round(hot_ms, 4),
+                                                      "cycle_cost_ar_units": round(hot_ms / ar_ms, 3)},
+            "note": "random weights: own drafts are almost never accepted"}
 
 
 def run_e2e(args, cfg, ex, prompts):

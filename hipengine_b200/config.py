@@ -73,6 +73,7 @@ class SpeculativeConfig:
     mode: str = "off"                       # off | mtp | prompt_lookup | ngram (``speculative/providers.py``)
     draft_depth: int = 3
     adaptive_depth: bool = False
+    hot_vocab: str = "off"                  # NextN draft head slice: off | auto | row count (``speculative/draft_vocab.py``)
 
 
 @dataclass(frozen=True)

@@ -101,10 +101,17 @@ class GpuRunner(BaseRunner):
             from ..speculative.providers import SpeculativeProviderConfig, build_speculative_provider
             self.mtp = build_speculative_provider(
                 self.ex, SpeculativeProviderConfig(name=config.speculative.mode,
-                                                   max_depth=max(1, config.speculative.draft_depth)),
+                                                   max_depth=max(1, config.speculative.draft_depth),
+                                                   hot_vocab=config.speculative.hot_vocab),
                 max_requests=min(self.max_slots, 8))
         self.supports_mtp = self.mtp is not None
         self.spec_uses_history = self.mtp is not None and hasattr(self.mtp, "drafter")
+        # hot-vocabulary draft head: per-request rule over the request's own committed tokens decides, cycle by
+        # cycle, whether the NextN draft may score only the leading slice of the head
+        self.draft_vocab = None
+        if getattr(self.mtp, "draft_head_rows", 0) > 0:
+            from ..speculative.draft_vocab import DraftVocabBook
+            self.draft_vocab = DraftVocabBook(self.mtp.draft_head_rows)
 
     # ------------------------------------------------------------------ snapshots
     def _free_snapshot(self, sid: int) -> None:
@@ -480,6 +487,9 @@ class GpuRunner(BaseRunner):
         kw = {}
         if self.spec_uses_history:
             kw["histories"] = [list(rs.req.prompt_token_ids) + rs.generated for rs in rows]
+        if self.draft_vocab is not None:
+            kw["small_head"] = self.draft_vocab.decide(
+                [self.draft_vocab.fits(rs.rid, rs.req.prompt_token_ids, rs.generated, rs.last_token) for rs in rows])
         try:
             got = self.mtp.cycle([rs.slot for rs in rows], [rs.last_token for rs in rows],
                                  [rs.position - 1 for rs in rows], depth,
@@ -521,6 +531,8 @@ class GpuRunner(BaseRunner):
         claim = self._claims.pop(str(rs.rid), None)
         if claim is not None:
             self.ledger.release(claim)
+        if self.draft_vocab is not None:
+            self.draft_vocab.drop(rs.rid)
         if rs.rid in self.resident_key:
             self.resident_key = ()
 
@@ -542,6 +554,8 @@ class GpuRunner(BaseRunner):
         for claim in self._snap_claims.values():
             self.ledger.release(claim)
         self._snap_claims.clear()
+        if self.draft_vocab is not None:
+            self.draft_vocab.clear()
         self.resident_key = ()
 
     def capacity(self) -> Dict[str, Any]:
@@ -558,4 +572,5 @@ class GpuRunner(BaseRunner):
 
     def snapshot(self) -> Dict[str, Any]:
         return {"launch_census": self.census.report(), "pool": self.pool.snapshot(), "prefix": self.radix.snapshot_stats(), "graphs": dict(self.graphs.stats, kernels_per_graph=None),
+                "draft_vocab": self.draft_vocab.as_dict() if self.draft_vocab is not None else None,
                 **self.stats}

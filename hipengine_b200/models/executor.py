@@ -598,15 +598,22 @@ class HybridExecutor:
         return h
 
     def nextn_logits(self, h_rows: torch.Tensor, out: Optional[torch.Tensor] = None,
-                     hidden_out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """Draft head: shared_head_norm (or output_norm) + shared head (or the model's head) over <= 8 rows."""
+                     hidden_out: Optional[torch.Tensor] = None, head_rows: int = 0) -> torch.Tensor:
+        """Draft head: shared_head_norm (or output_norm) + shared head (or the model's head) over <= 8 rows.
+
+        ``head_rows`` > 0 scores only the first ``head_rows`` vocabulary rows (hot-vocabulary draft head,
+        ``speculative/draft_vocab.py``): rows are contiguous in every device layout, so the slice is the same buffer
+        with a smaller row count and the logits come back as [R, head_rows]."""
         cfg = self.cfg
         i = cfg.n_layers
         R = h_rows.shape[0]
         norm_w = self.f32.get(f"blk.{i}.nextn.shared_head_norm.weight", self.f32["output_norm.weight"])
         head = self.dw.get(f"blk.{i}.nextn.shared_head_head.weight", self.dw["output.weight"])
+        if 0 < head_rows < head.n_rows:
+            head = K.DeviceWeight(head.qtype, int(head_rows), head.n_cols, head.data)
         if out is None:
-            out = self.scratch.get("nx_logits", (R, head.n_rows), torch.float32)
+            out = self.scratch.get("nx_logits" if head_rows <= 0 else "nx_logits_hot", (R, head.n_rows),
+                                   torch.float32)
         if hidden_out is not None:
             K.rmsnorm_rows(h_rows, norm_w, hidden_out, cfg.rms_eps)
         for r0 in range(0, R, GEMV_MAX_ROWS):

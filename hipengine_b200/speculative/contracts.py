@@ -20,11 +20,13 @@ class SpeculativeCapability:
     transaction_mode: str = "journal"         # recurrent state is journalled per verify row and committed by copy
     sampling_modes: Tuple[str, ...] = ("greedy", "sampled")
     graph_capture: bool = False               # the whole cycle replays as one captured graph (greedy chains)
+    draft_head_rows: int = 0                  # hot-vocabulary draft head: rows of the head slice (0: full head only)
 
     def as_dict(self) -> Dict[str, Any]:
         return {"provider": self.provider, "max_depth": self.max_depth, "widths": list(self.widths),
                 "attachment": self.attachment, "transaction_mode": self.transaction_mode,
-                "sampling_modes": list(self.sampling_modes), "graph_capture": self.graph_capture}
+                "sampling_modes": list(self.sampling_modes), "graph_capture": self.graph_capture,
+                "draft_head_rows": self.draft_head_rows}
 
 
 @dataclass

@@ -142,15 +142,19 @@ class ChainVerifyCycle:
 
 
 class MTPCycle(ChainVerifyCycle):
-    def __init__(self, ex, max_depth: int = 3, max_requests: int = 8):
+    def __init__(self, ex, max_depth: int = 3, max_requests: int = 8, draft_head_rows: int = 0):
         assert ex.has_nextn, "checkpoint has no NextN block"
         super().__init__(ex, max_depth, max_requests)
         self.h_prev = torch.zeros(ex.max_slots, ex.cfg.hidden, dtype=torch.float32, device=ex.device)  # per slot
+        # hot-vocabulary draft head: rows of the head slice a cycle may draft with (0: always the full head); the
+        # caller says per cycle, with ``small_head=True``, that every row's recent tokens lie inside the slice
+        self.draft_head_rows = int(draft_head_rows) if 0 < int(draft_head_rows) < ex.cfg.vocab else 0
 
     def capability(self) -> SpeculativeCapability:
         return SpeculativeCapability(provider="nextn_mtp", max_depth=self.max_depth,
                                      widths=tuple(range(1, self.max_requests + 1)),
-                                     graph_capture=isinstance(self, GraphedMTPCycle))
+                                     graph_capture=isinstance(self, GraphedMTPCycle),
+                                     draft_head_rows=self.draft_head_rows)
 
     def _after_commit(self, slot_t: torch.Tensor, hid: torch.Tensor, R: int) -> None:
         picked = self.ex.scratch.get("mtp_pick", (R, self.ex.cfg.hidden), torch.float32)
@@ -182,11 +186,12 @@ class MTPCycle(ChainVerifyCycle):
     @torch.no_grad()
     def cycle(self, slots: Sequence[int], last_tokens: Sequence[int], positions: Sequence[int], depth: int,
               temperature: Optional[Sequence[float]] = None, seeds: Optional[Sequence[int]] = None,
-              counters: Optional[Sequence[int]] = None, draft_override: Optional[torch.Tensor] = None
-              ) -> Tuple[List[SpecCycleResult], SpecTransaction]:
+              counters: Optional[Sequence[int]] = None, draft_override: Optional[torch.Tensor] = None,
+              small_head: bool = False) -> Tuple[List[SpecCycleResult], SpecTransaction]:
         """positions[r] = position of last_tokens[r].  temperature None/0 -> greedy verification.
         ``draft_override`` (int64 [R, depth]) replaces the NextN proposals after they are computed (the block
-        still runs, so its KV stays in step); used to test acceptance paths with known chains."""
+        still runs, so its KV stays in step); used to test acceptance paths with known chains.
+        ``small_head`` drafts with the first ``draft_head_rows`` rows of the head (verification is unchanged)."""
         ex, cfg, dev = self.ex, self.ex.cfg, self.ex.device
         R, Kd = len(slots), depth
         assert 1 <= Kd <= self.max_depth and R <= self.max_requests
@@ -206,7 +211,7 @@ class MTPCycle(ChainVerifyCycle):
             b = make_batch([(s, p + j, [0]) for s, p in zip(slots, positions)], dev)
             b.tokens = cur
             h = ex.nextn_forward(b, hprev)
-            lg = ex.nextn_logits(h, hidden_out=hid_next)
+            lg = ex.nextn_logits(h, hidden_out=hid_next, head_rows=self.draft_head_rows if small_head else 0)
             for r0 in range(0, R, GEMV_MAX_ROWS):
                 r1 = min(R, r0 + GEMV_MAX_ROWS)
                 ex.greedy(lg[r0:r1], ids[r0:r1])
@@ -222,8 +227,8 @@ class MTPCycle(ChainVerifyCycle):
 
 class GraphedMTPCycle(MTPCycle):
     """The greedy NextN cycle -- propose(K) -> verify -> accept -> commit -> cursor update -- captured as ONE CUDA
-    graph per (rows, depth, context bucket) and launched through the native cycle launcher with the full stage
-    mask; the only read-back is the accept counts (returned by the launcher) and the emitted ids.
+    graph per (rows, depth, context bucket, draft-head rows) and launched through the native cycle launcher with
+    the full stage mask; the only read-back is the accept counts (returned by the launcher) and the emitted ids.
 
     Everything a cycle reads is resident on the device and advanced by the graph itself: slots, the last committed
     token and its position per row, the per-slot hidden seed of the NextN block.  A following cycle over the same
@@ -234,8 +239,8 @@ class GraphedMTPCycle(MTPCycle):
     graph, stage mask PROPOSE | VERIFY | ACCEPT | COMMIT | UPDATE_CURSORS).
     """
 
-    def __init__(self, ex, max_depth: int = 3, max_requests: int = 8):
-        super().__init__(ex, max_depth, max_requests)
+    def __init__(self, ex, max_depth: int = 3, max_requests: int = 8, draft_head_rows: int = 0):
+        super().__init__(ex, max_depth, max_requests, draft_head_rows)
         dev, cfg = ex.device, ex.cfg
         R, Kd = max_requests, max_depth
         T = self.max_rows
@@ -281,7 +286,7 @@ class GraphedMTPCycle(MTPCycle):
         return c
 
     # ------------------------------------------------------------------ the cycle body (graph-safe: no host reads)
-    def _body(self, R: int, Kd: int, max_ctx: int) -> None:
+    def _body(self, R: int, Kd: int, max_ctx: int, head_rows: int = 0) -> None:
         ex = self.ex
         c = self._const(R, Kd)
         T = R * (Kd + 1)
@@ -295,7 +300,7 @@ class GraphedMTPCycle(MTPCycle):
             b = BatchDesc(cur, slot, self.dpos[j, :R], self.dctx[j, :R], self.seg_r[:R + 1], slot, self.seg_r[:R],
                           R, R, max_ctx)
             h = ex.nextn_forward(b, hp)
-            lg = ex.nextn_logits(h, hidden_out=self.hid_next[j, :R])
+            lg = ex.nextn_logits(h, hidden_out=self.hid_next[j, :R], head_rows=head_rows)
             ex.greedy(lg[:R], self.dcur[j, :R])
             self.drafts[:R, j].copy_(self.dcur[j, :R])
             cur, hp = self.dcur[j, :R], self.hid_next[j, :R]
@@ -354,7 +359,7 @@ class GraphedMTPCycle(MTPCycle):
     # ------------------------------------------------------------------ one cycle
     @torch.no_grad()
     def cycle(self, slots, last_tokens, positions, depth, temperature=None, seeds=None, counters=None,
-              draft_override=None):
+              draft_override=None, small_head=False):
         from ..core import runtime as RT
         from ..models.decode_graph import ctx_bucket
         ex = self.ex
@@ -364,7 +369,8 @@ class GraphedMTPCycle(MTPCycle):
                 or not 1 <= Kd <= self.max_depth):
             self.graph_stats["eager"] += 1
             self._mirror = None
-            return super().cycle(slots, last_tokens, positions, depth, temperature, seeds, counters, draft_override)
+            return super().cycle(slots, last_tokens, positions, depth, temperature, seeds, counters, draft_override,
+                                 small_head)
         if self.journal is None:
             self.journal = ex.alloc_journal(self.max_rows)
         want = (tuple(slots), tuple(int(t) for t in last_tokens), tuple(int(p) for p in positions))
@@ -373,20 +379,21 @@ class GraphedMTPCycle(MTPCycle):
         txn = SpecTransaction(list(range(R)))
         for st in (Stage.RESERVED, Stage.TARGET_OPEN, Stage.PROVIDER_OPEN):
             txn.advance(st)
-        key = (R, Kd, ctx_bucket(max(positions) + Kd + 1))
+        head_rows = self.draft_head_rows if small_head else 0
+        key = (R, Kd, ctx_bucket(max(positions) + Kd + 1), head_rows)
         saved_small = ex.small_rows
         ex.small_rows = GEMV_MAX_ROWS           # verify rows see the numerics of plain decode (see the parent)
         try:
             g = self.graphs.get(key)
             if g is None:
                 snap = self._snapshot(R)
-                self._body(R, Kd, key[2])       # warm-up: scratch growth and function attributes settle here
+                self._body(R, Kd, key[2], head_rows)   # warm-up: scratch growth and function attributes settle
                 torch.cuda.synchronize()
                 self._restore(snap)
                 k0 = K.launch_count()
                 g = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g):
-                    self._body(R, Kd, key[2])
+                    self._body(R, Kd, key[2], head_rows)
                 self.graph_stats["kernels_per_graph"][key] = K.launch_count() - k0
                 self._restore(snap)
                 self.graphs[key] = g

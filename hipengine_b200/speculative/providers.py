@@ -25,6 +25,7 @@ class SpeculativeProviderConfig:
     min_ngram: int = 2
     max_ngram: int = 4
     table_entries: int = 1 << 16      # ngram provider: bound of the shared table
+    hot_vocab: object = "off"         # mtp provider: off | auto | rows of the draft head slice (draft_vocab.py)
 
 
 class PromptLookupDrafter:
@@ -138,7 +139,10 @@ def _mtp_factory(ex, cfg: SpeculativeProviderConfig, max_requests: int):
     single = getattr(getattr(ex, "ctx", None), "world", 1) == 1
     graphed = single and str(ex.device).startswith("cuda") and os.environ.get("HE_SPEC_GRAPH", "1") != "0"
     cls = GraphedMTPCycle if graphed else MTPCycle
-    return cls(ex, max_depth=max(1, cfg.max_depth), max_requests=max_requests)
+    from .draft_vocab import resolve_hot_vocab_rows
+    # the head slice is a row prefix of the full head: a vocabulary-sharded head (tensor parallel) has none
+    rows = resolve_hot_vocab_rows(cfg.hot_vocab, ex.cfg.vocab) if single else 0
+    return cls(ex, max_depth=max(1, cfg.max_depth), max_requests=max_requests, draft_head_rows=rows)
 
 
 def _prompt_lookup_factory(ex, cfg: SpeculativeProviderConfig, max_requests: int):

@@ -108,6 +108,37 @@ def test_mtp_serving_matches_plain_greedy_and_reports_cycles():
         spec.close()
 
 
+def test_mtp_hot_vocab_serving_keeps_greedy_tokens_and_counts_head_choices():
+    """The hot-vocabulary draft head through the public API: the per-request rule picks the head cycle by cycle,
+    the tokens stay those of plain greedy decoding, and finished requests leave no rule behind."""
+    from dataclasses import replace
+    from hipengine_b200 import LLM, SamplingParams
+    from hipengine_b200.loading.synth import build_random_model
+    from hipengine_b200.models.config import TINY_HYBRID
+    w = build_random_model(replace(TINY_HYBRID, nextn_layers=1), seed=4, std=0.05).to("cuda")
+    plain = LLM(w, backend="cuda_sm100a", max_active_requests=2, max_sequence_length=256, prefix_cache="off")
+    spec = LLM(w, backend="cuda_sm100a", max_active_requests=2, max_sequence_length=256, prefix_cache="off",
+               speculative_mtp_serving="on", speculative_candidate_budget=3, mtp_hot_vocab=1536)
+    try:
+        g = torch.Generator().manual_seed(11)
+        prompts = [torch.randint(0, 1536, (n,), generator=g).tolist() for n in (12, 31)]     # inside the slice
+        sp = SamplingParams(max_tokens=14, ignore_eos=True)
+        a = plain.generate_detailed(prompts, sp)
+        b = spec.generate_detailed(prompts, sp)
+        for x, y in zip(a, b):
+            assert x.token_ids == y.token_ids
+        runner = spec._get_engine().loop.runner
+        book = runner.draft_vocab
+        assert book is not None and book.rows == 1536 and len(book) == 0
+        st = book.as_dict()
+        assert st["small_head_cycles"] + st["full_head_cycles"] >= 1
+        assert runner.capacity()["speculative"]["draft_head_rows"] == 1536
+        assert runner.snapshot()["draft_vocab"]["rows"] == 1536
+    finally:
+        plain.close()
+        spec.close()
+
+
 def test_cold_tier_brings_an_evicted_prefix_back():
     """A small pool forces the radix cache to evict the first prompt's blocks; with the cold tier on they are
     offloaded (KV rows + recurrent-state snapshots) and restored at the next admission, and the continuation is the

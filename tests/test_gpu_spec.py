@@ -176,6 +176,44 @@ def test_graphed_mtp_cycle_is_one_launch_and_reproduces_greedy_decode(n_req):
     assert list(st["kernels_per_graph"].values())[0] > 20
 
 
+@pytest.mark.parametrize("graphed", [False, True], ids=["eager", "graph"])
+def test_hot_vocab_draft_head_scores_a_row_prefix_and_keeps_greedy_output(graphed):
+    """Drafting with the leading slice of the head: the slice's logits are the full head's first rows, every draft
+    lies inside the slice, the emitted tokens are still those of plain greedy decoding (verification uses the full
+    head), and the graphed cycle keeps one graph per head choice."""
+    from hipengine_b200.models.executor import HybridExecutor, make_batch
+    from hipengine_b200.speculative.draft_vocab import resolve_hot_vocab_rows
+    from hipengine_b200.speculative.mtp import GraphedMTPCycle, MTPCycle
+    rows = resolve_hot_vocab_rows(CFG.vocab // 4, CFG.vocab)
+    assert 0 < rows < CFG.vocab and rows % 64 == 0
+    w = build_random_model(CFG, seed=0, std=0.05).to("cuda")
+    prompt = _prompt(24, seed=5)
+    n_new = 14
+    want = _greedy_reference_tokens(w, prompt, n_new)
+    ex = HybridExecutor(w, max_slots=1, max_context=256)
+    mtp = (GraphedMTPCycle if graphed else MTPCycle)(ex, max_depth=3, max_requests=1, draft_head_rows=rows)
+    assert mtp.capability().as_dict()["draft_head_rows"] == rows
+    b = make_batch([(0, 0, prompt)], "cuda")
+    h = ex.forward(b)
+    mtp.after_prefill(b, h)
+    full = ex.nextn_logits(h[:4]).clone()
+    part = ex.nextn_logits(h[:4], head_rows=rows).clone()
+    assert part.shape == (4, rows) and torch.allclose(part, full[:, :rows], rtol=1e-5, atol=1e-6)
+    got = [int(ex.logits(h[b.T - 1:b.T]).argmax(-1))]
+    cycle_no = 0
+    while len(got) < n_new:
+        small = cycle_no % 3 != 2                           # every third cycle drafts with the full head
+        res, txn = mtp.cycle([0], [got[-1]], [len(prompt) + len(got) - 1], 3, small_head=small)
+        assert txn.trace[-1] == "committed"
+        if graphed and small:
+            assert int(mtp.drafts[0].max()) < rows
+        got += res[0].tokens
+        cycle_no += 1
+    assert got[:n_new] == want, (got, want)
+    if graphed:
+        assert mtp.graph_stats["captures"] == 2 and mtp.graph_stats["eager"] == 0
+
+
 def test_lookup_cycle_with_known_chains_needs_no_nextn_block():
     """Chain verify with host-supplied drafts on a checkpoint WITHOUT a NextN block: the true greedy continuation is
     accepted in full (plus the bonus token), a corrupted chain is cut at the first wrong token, and the committed

@@ -402,3 +402,35 @@ def test_scratch_canaries_detect_a_write_past_the_extent():
     big.zero_()
     assert "a" not in sc.check_canaries() and len(sc.retired) == 1
     assert _Scratch(torch.device("cpu"), canaries=False).check_canaries() == []
+
+
+def test_hot_vocab_rows_setting_and_recent_miss_rule():
+    """The draft head slice: setting resolution, and the per-request rule that reads committed tokens only."""
+    from hipengine_b200.speculative.draft_vocab import (DEFAULT_ROWS, DraftVocabBook, DraftVocabRule,
+                                                        resolve_hot_vocab_rows)
+    assert resolve_hot_vocab_rows("off", 248320) == 0 and resolve_hot_vocab_rows(None, 248320) == 0
+    assert resolve_hot_vocab_rows("auto", 248320) == DEFAULT_ROWS
+    assert resolve_hot_vocab_rows("auto", 2048) == 1024             # a slice that covers everything is no slice
+    assert resolve_hot_vocab_rows("1000", 2048) == 960              # whole work items
+    assert resolve_hot_vocab_rows(32, 2048) == 0
+    rule = DraftVocabRule(rows=100, window=8)
+    prompt = [1, 2, 3, 150, 4, 5]                                   # one miss at index 3
+    assert rule.catch_up(prompt, []) == 6
+    assert rule.fits(5) and not rule.fits(150) and not rule.fits(-1)
+    gen = [7, 120]                                                  # second miss at index 7: two inside the window
+    assert rule.catch_up(prompt, gen) == 2 and not rule.fits(7)
+    gen += [1] * 3
+    rule.catch_up(prompt, gen)
+    assert not rule.fits(1)                                         # miss at 3 is among the last 8 of 11 scanned
+    gen += [1]
+    rule.catch_up(prompt, gen)
+    assert rule.fits(1)                                             # 3 + 8 < 12: only one miss left in the window
+    assert rule.catch_up(prompt, gen) == 0                          # append-only: nothing new, nothing read
+    assert rule.catch_up([1, 2], []) == 2 and rule.fits(2)          # a shorter history is another request
+    book = DraftVocabBook(rows=100, window=8)
+    fits = [book.fits("a", [1, 2, 3], [], 3), book.fits("b", [1, 200, 300], [], 3)]
+    assert fits == [True, False] and book.decide(fits) is False and book.decide(fits[:1]) is True
+    assert book.as_dict()["small_head_cycles"] == 1 and book.as_dict()["full_head_cycles"] == 1 and len(book) == 2
+    book.drop("a")
+    book.clear()
+    assert len(book) == 0
