@@ -362,7 +362,9 @@ struct Cursor {
 
 // COMM = false compiles the tensor-parallel push / reduce paths out (the single-GPU kernel carries none of their
 // registers or branches).
-template <int R, int NW, bool COMM>
+// P2 (batches of 2+ rows, no peer communication): a lane owns half a block of TWO weight rows of the staged unit
+// instead of one block of one row, so every activation word it loads serves two rows (see gemv_rows.cuh).
+template <int R, int NW, bool COMM, bool P2>
 __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const __grid_constant__ HeGemvArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ float red[33];
@@ -473,88 +475,186 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const __grid_constant_
     prologue<R, COMM>(a, s, red);
   }
 
-  const int t_row = lane >> bq_shift, bq = lane & (BQ - 1);
-  float acc[R];
-  Cursor cc{gw, 0, 0, 0u, my_units};
-  ItemLoc L = pL;
-  RowRef rr;
-  while (cc.left > 0) {
-    issue();
-    if (cc.uk == 0) {
-      L = locate(a, cc.item, rg_shift);
-      rr = row_of(a, L, t_row, rg);
+  if constexpr (P2) {
+    // lane = (row pair tp, block bq2 of the unit, half hsel of the block); rows tp and tp + rg/2 of the item: for a
+    // gate/up pair segment these are gate row n and up row n, so the activation epilogue needs no shuffle
+    const int hsel = lane & 1, bq2 = (lane >> 1) & (BQ - 1), tp = lane >> (bq_shift + 1), hp = rg >> 1;
+    float accA[R], accB[R];
+    Cursor cc{gw, 0, 0, 0u, my_units};
+    ItemLoc L = pL;
+    RowRef rA, rB;
+    while (cc.left > 0) {
+      issue();
+      if (cc.uk == 0) {
+        L = locate(a, cc.item, rg_shift);
+        rA = row_of(a, L, tp, rg);
+        rB = row_of(a, L, tp + hp, rg);
 #pragma unroll
-      for (int r = 0; r < R; ++r) acc[r] = 0.f;
-      const HeGemvSeg& fsg = a.seg[L.si];
-      if (fsg.qtype != HE_Q4_K && fsg.qtype != HE_Q6_K && fsg.qtype != HE_Q8_0 && fsg.epi < 3) {
-        // float-weight rows: the whole warp walks each row with coalesced loads (nothing was staged for them)
-        for (int t = 0; t < rg; ++t) {
-          const RowRef fr = row_of(a, L, t, rg);
-          if (!fr.valid) break;
-          float fa[R];
+        for (int r = 0; r < R; ++r) accA[r] = accB[r] = 0.f;
+        const HeGemvSeg& fsg = a.seg[L.si];
+        if (fsg.qtype != HE_Q4_K && fsg.qtype != HE_Q6_K && fsg.qtype != HE_Q8_0 && fsg.epi < 3) {
+          // float-weight rows: the whole warp walks each row with coalesced loads (nothing was staged for them)
+          for (int t = 0; t < rg; ++t) {
+            const RowRef fr = row_of(a, L, t, rg);
+            if (!fr.valid) break;
+            float fa[R];
 #pragma unroll
-          for (int r = 0; r < R; ++r) fa[r] = 0.f;
-          hegemv::row_float_coop<R>(fr.w + (size_t)fr.n * (size_t)hegemv::row_bytes_dev(fr.qt, K), fr.qt, K, a.x,
-                                    a.x_dtype, a.x_stride, a.norm_w, s, lane, fa);
+            for (int r = 0; r < R; ++r) fa[r] = 0.f;
+            hegemv::row_float_coop<R>(fr.w + (size_t)fr.n * (size_t)hegemv::row_bytes_dev(fr.qt, K), fr.qt, K, a.x,
+                                      a.x_dtype, a.x_stride, a.norm_w, s, lane, fa);
 #pragma unroll
-          for (int r = 0; r < R; ++r) {
-            const float v = warp_sum(fa[r]);
-            if (lane == 0) {
-              const size_t off = (size_t)r * fsg.out_stride + fr.n;
-              if (push) push_store(r, fr.n, v);
-              else if (fsg.epi == 0) reinterpret_cast<float*>(fsg.out)[off] = v;
-              else if (fsg.epi == 1) reinterpret_cast<__nv_bfloat16*>(fsg.out)[off] = f32_to_bf16(v);
-              else reinterpret_cast<float*>(fsg.out)[off] += v;
+            for (int r = 0; r < R; ++r) {
+              const float v = warp_sum(fa[r]);
+              if (lane == 0) {
+                const size_t off = (size_t)r * fsg.out_stride + fr.n;
+                if (fsg.epi == 0) reinterpret_cast<float*>(fsg.out)[off] = v;
+                else if (fsg.epi == 1) reinterpret_cast<__nv_bfloat16*>(fsg.out)[off] = f32_to_bf16(v);
+                else reinterpret_cast<float*>(fsg.out)[off] += v;
+              }
             }
           }
         }
       }
-    }
-    const bool float_item = !(rr.qt == HE_Q4_K || rr.qt == HE_Q6_K || rr.qt == HE_Q8_0) && a.seg[L.si].epi < 3;
-    if (!sm100::mbar_wait(&bars[warp][cc.slot], cc.parity, &abort_flag, a.status, 201)) break;
-    const int blk0 = cc.uk << bq_shift, nblk = min(BQ, nb - blk0);
-    if (bq < nblk && !float_item) {
-      const int b = blk0 + bq;
-      const uint8_t* rowp = ring + (uint32_t)cc.slot * a.slot_bytes + (uint32_t)t_row * row_stride;
-      if (rr.qt == HE_Q4_K) hegemv::block_q4k<R>(rowp + bq * 144, b, s, acc);
-      else if (rr.qt == HE_Q6_K) hegemv::block_q6k<R>(rowp + bq * 224, b, s, acc);
-      else if (rr.qt == HE_Q8_0) hegemv::block_q80<R>(rowp + bq * 256, rowp + nblk * 256 + bq * 16, b, s, acc);
-      else {
-        const uint32_t es = rr.qt == HE_F32 ? 4 : 2;
-        hegemv::block_float<R>(rr.w + (size_t)rr.n * (size_t)hegemv::row_bytes_dev(rr.qt, K) + (size_t)b * 256 * es,
-                               rr.qt, b, a.x, a.x_dtype, a.x_stride, a.norm_w, s, acc);
+      const bool quant_item = rA.qt == HE_Q4_K || rA.qt == HE_Q6_K || rA.qt == HE_Q8_0;
+      if (!sm100::mbar_wait(&bars[warp][cc.slot], cc.parity, &abort_flag, a.status, 201)) break;
+      const int blk0 = cc.uk << bq_shift, nblk = min(BQ, nb - blk0);
+      if (bq2 < nblk && quant_item) {
+        const int b = blk0 + bq2;
+        const uint8_t* slot = ring + (uint32_t)cc.slot * a.slot_bytes;
+        const uint8_t* pa = slot + (uint32_t)tp * row_stride;
+        const uint8_t* pb = slot + (uint32_t)(tp + hp) * row_stride;
+        if (rA.qt == HE_Q4_K) hegemv::half_q4k_x2<R>(pa + bq2 * 144, pb + bq2 * 144, b, hsel, s, accA, accB);
+        else if (rA.qt == HE_Q6_K) hegemv::half_q6k_x2<R>(pa + bq2 * 224, pb + bq2 * 224, b, hsel, s, accA, accB);
+        else
+          hegemv::half_q80_x2<R>(pa + bq2 * 256, pa + nblk * 256 + bq2 * 16, pb + bq2 * 256,
+                                 pb + nblk * 256 + bq2 * 16, b, hsel, s, accA, accB);
       }
-    }
-    __syncwarp();   // every lane is done reading the slot before it may be refilled in the next iteration
-    if (cc.uk == upi - 1 && !float_item) {
-      const HeGemvSeg& sg = a.seg[L.si];
-#pragma unroll
-      for (int r = 0; r < R; ++r) {
-        float v = acc[r];
-        for (int o = 1; o < BQ; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        acc[r] = v;
-      }
-      if (sg.epi >= 3) {
-        const int hp = rg >> 1;
+      __syncwarp();   // every lane is done reading the slot before it may be refilled in the next iteration
+      if (cc.uk == upi - 1 && quant_item) {
+        const HeGemvSeg& sg = a.seg[L.si];
 #pragma unroll
         for (int r = 0; r < R; ++r) {
-          const float up = __shfl_sync(0xffffffffu, acc[r], (lane + hp * BQ) & 31);
-          if (bq == 0 && t_row < hp && rr.valid)
-            reinterpret_cast<__nv_bfloat16*>(sg.out)[(size_t)r * sg.out_stride + rr.n] =
-                f32_to_bf16(apply_act(acc[r], sg.epi) * up);
+          float va = accA[r], vb = accB[r];
+          for (int o = 1; o < 2 * BQ; o <<= 1) {
+            va += __shfl_xor_sync(0xffffffffu, va, o);
+            vb += __shfl_xor_sync(0xffffffffu, vb, o);
+          }
+          accA[r] = va;
+          accB[r] = vb;
         }
-      } else if (bq == 0 && rr.valid) {
+        if ((lane & (2 * BQ - 1)) == 0) {
+          if (sg.epi >= 3) {
+            if (rA.valid) {
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
-          const size_t off = (size_t)r * sg.out_stride + rr.n;
-          if (push) push_store(r, rr.n, acc[r]);
-          else if (sg.epi == 0) reinterpret_cast<float*>(sg.out)[off] = acc[r];
-          else if (sg.epi == 1) reinterpret_cast<__nv_bfloat16*>(sg.out)[off] = f32_to_bf16(acc[r]);
-          else reinterpret_cast<float*>(sg.out)[off] += acc[r];
+              for (int r = 0; r < R; ++r)
+                reinterpret_cast<__nv_bfloat16*>(sg.out)[(size_t)r * sg.out_stride + rA.n] =
+                    f32_to_bf16(apply_act(accA[r], sg.epi) * accB[r]);
+            }
+          } else {
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+              if (rA.valid) {
+                const size_t off = (size_t)r * sg.out_stride + rA.n;
+                if (sg.epi == 0) reinterpret_cast<float*>(sg.out)[off] = accA[r];
+                else if (sg.epi == 1) reinterpret_cast<__nv_bfloat16*>(sg.out)[off] = f32_to_bf16(accA[r]);
+                else reinterpret_cast<float*>(sg.out)[off] += accA[r];
+              }
+              if (rB.valid) {
+                const size_t off = (size_t)r * sg.out_stride + rB.n;
+                if (sg.epi == 0) reinterpret_cast<float*>(sg.out)[off] = accB[r];
+                else if (sg.epi == 1) reinterpret_cast<__nv_bfloat16*>(sg.out)[off] = f32_to_bf16(accB[r]);
+                else reinterpret_cast<float*>(sg.out)[off] += accB[r];
+              }
+            }
+          }
         }
       }
+      advance(cc);
     }
-    advance(cc);
+  } else {
+    const int t_row = lane >> bq_shift, bq = lane & (BQ - 1);
+    float acc[R];
+    Cursor cc{gw, 0, 0, 0u, my_units};
+    ItemLoc L = pL;
+    RowRef rr;
+    while (cc.left > 0) {
+      issue();
+      if (cc.uk == 0) {
+        L = locate(a, cc.item, rg_shift);
+        rr = row_of(a, L, t_row, rg);
+  #pragma unroll
+        for (int r = 0; r < R; ++r) acc[r] = 0.f;
+        const HeGemvSeg& fsg = a.seg[L.si];
+        if (fsg.qtype != HE_Q4_K && fsg.qtype != HE_Q6_K && fsg.qtype != HE_Q8_0 && fsg.epi < 3) {
+          // float-weight rows: the whole warp walks each row with coalesced loads (nothing was staged for them)
+          for (int t = 0; t < rg; ++t) {
+            const RowRef fr = row_of(a, L, t, rg);
+            if (!fr.valid) break;
+            float fa[R];
+  #pragma unroll
+            for (int r = 0; r < R; ++r) fa[r] = 0.f;
+            hegemv::row_float_coop<R>(fr.w + (size_t)fr.n * (size_t)hegemv::row_bytes_dev(fr.qt, K), fr.qt, K, a.x,
+                                      a.x_dtype, a.x_stride, a.norm_w, s, lane, fa);
+  #pragma unroll
+            for (int r = 0; r < R; ++r) {
+              const float v = warp_sum(fa[r]);
+              if (lane == 0) {
+                const size_t off = (size_t)r * fsg.out_stride + fr.n;
+                if (push) push_store(r, fr.n, v);
+                else if (fsg.epi == 0) reinterpret_cast<float*>(fsg.out)[off] = v;
+                else if (fsg.epi == 1) reinterpret_cast<__nv_bfloat16*>(fsg.out)[off] = f32_to_bf16(v);
+                else reinterpret_cast<float*>(fsg.out)[off] += v;
+              }
+            }
+          }
+        }
+      }
+      const bool float_item = !(rr.qt == HE_Q4_K || rr.qt == HE_Q6_K || rr.qt == HE_Q8_0) && a.seg[L.si].epi < 3;
+      if (!sm100::mbar_wait(&bars[warp][cc.slot], cc.parity, &abort_flag, a.status, 201)) break;
+      const int blk0 = cc.uk << bq_shift, nblk = min(BQ, nb - blk0);
+      if (bq < nblk && !float_item) {
+        const int b = blk0 + bq;
+        const uint8_t* rowp = ring + (uint32_t)cc.slot * a.slot_bytes + (uint32_t)t_row * row_stride;
+        if (rr.qt == HE_Q4_K) hegemv::block_q4k<R>(rowp + bq * 144, b, s, acc);
+        else if (rr.qt == HE_Q6_K) hegemv::block_q6k<R>(rowp + bq * 224, b, s, acc);
+        else if (rr.qt == HE_Q8_0) hegemv::block_q80<R>(rowp + bq * 256, rowp + nblk * 256 + bq * 16, b, s, acc);
+        else {
+          const uint32_t es = rr.qt == HE_F32 ? 4 : 2;
+          hegemv::block_float<R>(rr.w + (size_t)rr.n * (size_t)hegemv::row_bytes_dev(rr.qt, K) + (size_t)b * 256 * es,
+                                 rr.qt, b, a.x, a.x_dtype, a.x_stride, a.norm_w, s, acc);
+        }
+      }
+      __syncwarp();   // every lane is done reading the slot before it may be refilled in the next iteration
+      if (cc.uk == upi - 1 && !float_item) {
+        const HeGemvSeg& sg = a.seg[L.si];
+  #pragma unroll
+        for (int r = 0; r < R; ++r) {
+          float v = acc[r];
+          for (int o = 1; o < BQ; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+          acc[r] = v;
+        }
+        if (sg.epi >= 3) {
+          const int hp = rg >> 1;
+  #pragma unroll
+          for (int r = 0; r < R; ++r) {
+            const float up = __shfl_sync(0xffffffffu, acc[r], (lane + hp * BQ) & 31);
+            if (bq == 0 && t_row < hp && rr.valid)
+              reinterpret_cast<__nv_bfloat16*>(sg.out)[(size_t)r * sg.out_stride + rr.n] =
+                  f32_to_bf16(apply_act(acc[r], sg.epi) * up);
+          }
+        } else if (bq == 0 && rr.valid) {
+  #pragma unroll
+          for (int r = 0; r < R; ++r) {
+            const size_t off = (size_t)r * sg.out_stride + rr.n;
+            if (push) push_store(r, rr.n, acc[r]);
+            else if (sg.epi == 0) reinterpret_cast<float*>(sg.out)[off] = acc[r];
+            else if (sg.epi == 1) reinterpret_cast<__nv_bfloat16*>(sg.out)[off] = f32_to_bf16(acc[r]);
+            else reinterpret_cast<float*>(sg.out)[off] += acc[r];
+          }
+        }
+      }
+      advance(cc);
+    }
   }
   if (push) {
     // the words carry their own tag, so nothing has to be published: the last CTA of the grid only advances the
@@ -570,13 +670,13 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const __grid_constant_
   }
 }
 
-template <int R, int NW, bool COMM>
+template <int R, int NW, bool COMM, bool P2>
 int launch_nw_c(const HeGemvArgs& a, size_t smem, long long items, int num_sms, cudaStream_t stream) {
   static size_t configured[64] = {};   // per device: the attribute belongs to the (function, device) pair
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
   if (smem > configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemv_kernel<R, NW, COMM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(gemv_kernel<R, NW, COMM, P2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured[dev] = smem;
   }
@@ -599,15 +699,18 @@ int launch_nw_c(const HeGemvArgs& a, size_t smem, long long items, int num_sms, 
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 1 : 0;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_kernel<R, NW, COMM>, a);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_kernel<R, NW, COMM, P2>, a);
   if (e != cudaSuccess) return (int)e;
   return 0;
 }
 
 template <int R, int NW>
-int launch_nw(const HeGemvArgs& a, size_t smem, long long items, int num_sms, cudaStream_t stream) {
-  if (a.comm.mode != 0) return launch_nw_c<R, NW, true>(a, smem, items, num_sms, stream);
-  return launch_nw_c<R, NW, false>(a, smem, items, num_sms, stream);
+int launch_nw(const HeGemvArgs& a, size_t smem, long long items, int num_sms, cudaStream_t stream, bool p2) {
+  if (a.comm.mode != 0) return launch_nw_c<R, NW, true, false>(a, smem, items, num_sms, stream);
+  if constexpr (R >= 2) {
+    if (p2) return launch_nw_c<R, NW, false, true>(a, smem, items, num_sms, stream);
+  }
+  return launch_nw_c<R, NW, false, false>(a, smem, items, num_sms, stream);
 }
 
 template <int R>
@@ -665,9 +768,18 @@ int launch_gemv(HeGemvArgs a, int num_sms, cudaStream_t stream) {
     items += (a.seg[i].n_rows + per - 1) / per;
   }
   const size_t smem = x_bytes + (size_t)n_slots * nw * a.slot_bytes;
-  if (nw == 16) return launch_nw<R, 16>(a, smem, items, num_sms, stream);
-  if (nw == 12) return launch_nw<R, 12>(a, smem, items, num_sms, stream);
-  return launch_nw<R, 8>(a, smem, items, num_sms, stream);
+  // two weight rows per lane for batches of 2+ rows (HE_GEMV_PAIR=0: one block of one row per lane as for one row);
+  // a gate/up pair segment qualifies when both weights have the same block type, float rows take the warp-wide path
+  static const bool pair_env = []() { const char* e = getenv("HE_GEMV_PAIR"); return !(e != nullptr && e[0] == '0'); }();
+  bool p2 = R >= 2 && pair_env && a.comm.mode == 0;
+  for (int i = 0; i < a.n_seg && p2; ++i) {
+    const HeGemvSeg& sg = a.seg[i];
+    const bool quant = sg.qtype == HE_Q4_K || sg.qtype == HE_Q6_K || sg.qtype == HE_Q8_0;
+    if (sg.epi >= 3 && (!quant || sg.qtype2 != sg.qtype)) p2 = false;
+  }
+  if (nw == 16) return launch_nw<R, 16>(a, smem, items, num_sms, stream, p2);
+  if (nw == 12) return launch_nw<R, 12>(a, smem, items, num_sms, stream, p2);
+  return launch_nw<R, 8>(a, smem, items, num_sms, stream, p2);
 }
 
 }  // namespace

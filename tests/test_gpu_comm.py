@@ -173,10 +173,16 @@ def test_folded_decode_allreduce_push_epilogue_and_reduce_prologue(world):
         K.check_status()
         want = torch.zeros(R, n2, device="cuda")
         K.gemv(h_ref, [K.GemvSegment(w_next, want)], norm_w=nw)
+        # the reference rows come from the plain multi-row kernel, whose lanes split the blocks differently from the
+        # communicating kernel's: equal up to fp32 summation order; the replicas themselves are bit-identical
+        tol_h = 1e-5 * h_ref.abs().max().item()
+        tol_o = 1e-4 * want.abs().max().item()
         for q in range(world):
             assert not torch.equal(hs[q], before[q])
-            assert torch.equal(hs[q], h_ref), (rnd, q, (hs[q] - h_ref).abs().max())     # bit-identical replicas
-            assert torch.equal(outs[q], want), (rnd, q)
+            assert torch.equal(hs[q], hs[0]) and torch.equal(outs[q], outs[0]), (rnd, q)
+            assert torch.allclose(hs[q], h_ref, atol=tol_h, rtol=1e-5), (rnd, q, (hs[q] - h_ref).abs().max())
+            assert torch.allclose(outs[q], want, atol=tol_o, rtol=1e-3), (rnd, q, (outs[q] - want).abs().max())
+        h_ref = hs[0].clone()                 # the next round starts from what the ranks hold
     # stand-alone producer / consumer on the same regions
     part = [torch.randn(2, width, device="cuda") for _ in range(world)]
     for q in range(world):

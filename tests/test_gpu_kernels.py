@@ -43,6 +43,57 @@ def test_gemv_matches_dequant_matmul(K, t, rows):
         assert torch.allclose(out, ref_q, atol=2e-4 * ref.abs().max().item() + 1e-5, rtol=2e-3)
 
 
+@pytest.mark.parametrize("t", [Q.GGMLType.Q4_K, Q.GGMLType.Q6_K, Q.GGMLType.Q8_0])
+@pytest.mark.parametrize("n,k", [(9600, 5120), (4736, 5120), (1027, 1280)], ids=["rg8", "rg4", "rg2"])
+def test_gemv_multi_row_pair_lanes_at_every_rows_per_item(K, t, n, k):
+    """Batches of 2+ rows run with two weight rows per lane; the three shapes make the launcher pick 8, 4 and 2 weight
+    rows per work item (the lane map differs for each).  Checked against the same int8-activation reference as the
+    single-row kernel, with the fused norm, an odd row count at the end and the accumulate epilogue."""
+    rows = 4
+    dw, deq, _ = _qweight(K, t, n, k, seed=7)
+    x = torch.randn(rows, k, device="cuda")
+    nw = torch.rand(k, device="cuda") + 0.5
+    out = torch.zeros(rows, n, device="cuda")
+    K.gemv(x, [K.GemvSegment(dw, out)], norm_w=nw)
+    xn = R.rmsnorm(x, nw)
+    xq, dx = R.q8_1_quantize(xn)
+    xr = (xq.float().reshape(rows, k // 32, 32) * dx[..., None]).reshape(rows, k)
+    ref_q = xr @ deq.t()
+    tol = 5e-4 * ref_q.abs().max().item() + 1e-5      # an activation on a rounding boundary may quantise either way
+    assert torch.allclose(out, ref_q, atol=tol, rtol=2e-3), (out - ref_q).abs().max()
+    one = torch.zeros(1, n, device="cuda")
+    K.gemv(x[2:3], [K.GemvSegment(dw, one)], norm_w=nw)                      # the single-row kernel on row 2
+    assert torch.allclose(out[2:3], one, atol=tol, rtol=2e-3)
+    acc = torch.ones(rows, n, device="cuda")
+    K.gemv(x, [K.GemvSegment(dw, acc, K.EPI_ADD_F32)], norm_w=nw)
+    assert torch.allclose(acc, ref_q + 1.0, atol=tol, rtol=2e-3)
+
+
+@pytest.mark.parametrize("rows", [2, 5])
+def test_gemv_multi_row_gate_up_pair_and_mixed_segments(K, rows):
+    """Gate/up pair segment of one block type (both rows of a pair sit in one lane) beside a plain segment of another
+    type and a float segment in the same launch."""
+    k, f, n1, n2 = 1024, 1030, 520, 24
+    wg, dg, _ = _qweight(K, Q.GGMLType.Q4_K, f, k, 3, std=0.2)
+    wu, du, _ = _qweight(K, Q.GGMLType.Q4_K, f, k, 4, std=0.2)
+    w1, d1, _ = _qweight(K, Q.GGMLType.Q6_K, n1, k, 5)
+    w2, d2, _ = _qweight(K, Q.GGMLType.F32, n2, k, 6)
+    h = torch.randn(rows, k, device="cuda") * 2
+    nw = torch.rand(k, device="cuda") + 0.5
+    act = torch.zeros(rows, f, device="cuda", dtype=torch.bfloat16)
+    o1 = torch.zeros(rows, n1, device="cuda")
+    o2 = torch.zeros(rows, n2, device="cuda")
+    K.gemv(h, [K.GemvSegment(wg, act, K.EPI_SILU_MUL, wu), K.GemvSegment(w1, o1), K.GemvSegment(w2, o2)], norm_w=nw)
+    xn = R.rmsnorm(h, nw)
+    xq, dx = R.q8_1_quantize(xn)
+    xr = (xq.float().reshape(rows, k // 32, 32) * dx[..., None]).reshape(rows, k)
+    ref = R.swiglu(xr @ dg.t(), xr @ du.t())
+    assert (act.float() - ref).abs().max() < 0.01 * ref.abs().max() + 0.02
+    r1 = xr @ d1.t()
+    assert torch.allclose(o1, r1, atol=2e-4 * r1.abs().max().item() + 1e-5, rtol=2e-3)
+    assert torch.allclose(o2, xn @ d2.t(), atol=1e-3, rtol=1e-3)
+
+
 def test_gemv_norm_prologue_multi_segment_and_epilogues(K):
     k, n1, n2, f = 512, 256, 40, 384
     w1, d1, _ = _qweight(K, Q.GGMLType.Q4_K, n1, k, 1)
