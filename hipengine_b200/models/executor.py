@@ -150,11 +150,12 @@ class HybridExecutor:
         self.gemm_impl = gemm_impl or os.environ.get("HE_GEMM", "tcgen05")
         self.scratch = _Scratch(self.device)
         # packed batches of up to small_rows rows take the quantised GEMV path, larger ones the tensor-core path
-        # (the int8 GEMV costs ~2.6 ms per extra row on the 27B geometry; the split-K tensor-core path streams the
+        # (the int8 GEMV costs ~1.65 ms per extra row on the 27B geometry; the split-K tensor-core path streams the
         # same quantised blocks once for any row count up to 128)
-        # measured on the 27B: a packed step costs 7.6 / 10.2 / 12.8 / 18.5 ms at 2 / 3 / 4 / 6 rows on the GEMV path
-        # and 13.7-15.0 ms at 4-6 rows on the tensor-core path, so the switch is above four rows
-        self.small_rows = min(GEMV_MAX_ROWS, int(os.environ.get("HE_SMALL_ROWS", "4")))
+        # measured on the 27B: a packed step costs 7.0 / 8.7 / 10.3 / 11.7 / 14.0 / 18.5 ms at 2 / 3 / 4 / 5 / 6 / 8
+        # rows on the GEMV path and 13.3 / 13.6 / 14.2 ms at 5 / 6 / 8 rows on the tensor-core path, so the switch is
+        # above five rows
+        self.small_rows = min(GEMV_MAX_ROWS, int(os.environ.get("HE_SMALL_ROWS", "5")))
         self.dw: Dict[str, DeviceWeight] = {}
         self.f32: Dict[str, torch.Tensor] = {}
         # per-stage device timing of the tensor-core (many rows) path, off unless HE_STAGE_TIMING=1 (the role of the
