@@ -220,7 +220,10 @@ PREQUANT_MIN_ROWS = int(os.environ.get("HE_GEMV_PREQUANT_ROWS", "2"))
 
 
 def _gemv_image(device: torch.device, nbytes: int) -> torch.Tensor:
-    """Persistent buffer for the activation image (kept for the life of the process: captured graphs bake it in)."""
+    """Persistent buffer for the activation image (kept for the life of the process: captured graphs bake it in).
+    One buffer per device and size serves every launch because the launches of a device are issued on one stream
+    (the engine's driver thread owns it): the pre-pass of the next launch waits for the GEMV before it.  A caller that
+    drives one device from several streams at once must not share it (``HE_GEMV_PREQUANT_ROWS=0`` avoids the buffer)."""
     key = (str(device), nbytes)
     t = _GEMV_IMAGES.get(key)
     if t is None:
