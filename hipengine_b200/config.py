@@ -11,7 +11,7 @@ from __future__ import annotations
 import os
 from dataclasses import dataclass, field, replace
 from enum import Enum
-from typing import Optional
+from typing import Any, Optional
 
 
 class ExecutionProfile(str, Enum):
@@ -74,6 +74,7 @@ class SpeculativeConfig:
     draft_depth: int = 3
     adaptive_depth: bool = False
     hot_vocab: str = "off"                  # NextN draft head slice: off | auto | row count (``speculative/draft_vocab.py``)
+    draft_model: Any = None                 # Gemma 4: the assistant (MTP) head artifact (path, loaded weights or "random")
 
 
 @dataclass(frozen=True)

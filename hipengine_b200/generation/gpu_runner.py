@@ -102,7 +102,8 @@ class GpuRunner(BaseRunner):
             self.mtp = build_speculative_provider(
                 self.ex, SpeculativeProviderConfig(name=config.speculative.mode,
                                                    max_depth=max(1, config.speculative.draft_depth),
-                                                   hot_vocab=config.speculative.hot_vocab),
+                                                   hot_vocab=config.speculative.hot_vocab,
+                                                   draft_model=config.speculative.draft_model),
                 max_requests=min(self.max_slots, 8))
         self.supports_mtp = self.mtp is not None
         self.spec_uses_history = self.mtp is not None and hasattr(self.mtp, "drafter")

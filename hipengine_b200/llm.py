@@ -112,7 +112,8 @@ class LLM:
                  execution_profile: Any = None, max_active_requests: int = 8,
                  max_sequence_length: Optional[int] = None, prefix_cache: str = "radix",
                  speculative_mtp_serving: str = "off", speculative_candidate_budget: int = 3,
-                 speculative_provider: str = "mtp", mtp_hot_vocab: Any = None, kv_cold_tier_bytes: int = 0,
+                 speculative_provider: str = "mtp", mtp_hot_vocab: Any = None, draft_model: Any = None,
+                 kv_cold_tier_bytes: int = 0,
                  kv_cold_tier_dir: Optional[str] = None,
                  kv_storage: str = "bf16", tensor_parallel: int = 1, expert_parallel: int = 1,
                  engine_command_timeout_seconds: float = 300.0, seed: int = 0, tokenizer: Any = None,
@@ -140,7 +141,9 @@ class LLM:
                                 mode=speculative_provider if speculative_mtp_serving not in ("off", None) else "off",
                                 draft_depth=int(speculative_candidate_budget),
                                 hot_vocab=str(mtp_hot_vocab) if mtp_hot_vocab is not None
-                                else base.speculative.hot_vocab),
+                                else base.speculative.hot_vocab,
+                                draft_model=draft_model if draft_model is not None
+                                else base.speculative.draft_model),
             parallel=replace(base.parallel, tp=int(tensor_parallel), ep=int(expert_parallel)),
             command_timeout_seconds=float(engine_command_timeout_seconds),
         )

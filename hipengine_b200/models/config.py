@@ -194,6 +194,56 @@ TINY_GEMMA4 = ModelConfig(arch="gemma4", n_layers=6, hidden=256, vocab=2048, n_h
                           n_experts=8, n_experts_used=2, expert_ffn=128, final_softcap=30.0,
                           embed_scale=16.0, act="gelu_tanh", tie_embeddings=True, max_context=2048)
 
+@dataclass(frozen=True)
+class AssistantConfig:
+    """Gemma 4 assistant (MTP) head: a separate four-block draft model with no K/V projections of its own.  Every
+    block attends against the backbone's KV of one of its last two layers (a sliding block reads layer ``n - 2``, a
+    full-attention block layer ``n - 1``), so head count, KV heads, head width, window and RoPE of a block are those
+    of the backbone layer it reads.  Contract: the reference's ``docs/reference/GEMMA4-ASSISTANT-MTP.md:36-60``
+    (hyperparameters) and ``:62-80`` (tensor layout)."""
+    arch: str = "gemma4-assistant"
+    n_blocks: int = 4
+    hidden: int = 1024                   # the head's own width
+    backbone_hidden: int = 2816          # the target's width (``embedding_length_out``)
+    ffn: int = 8192
+    n_heads: int = 16
+    vocab: int = 262144
+    swa_blocks: Tuple[bool, ...] = (True, True, True, False)
+    rms_eps: float = 1e-6
+
+    def backbone_layer(self, il: int, backbone: ModelConfig) -> int:
+        return backbone.n_layers - 2 if self.swa_blocks[il] else backbone.n_layers - 1
+
+    def check_pairing(self, backbone: ModelConfig) -> None:
+        """The head is only meaningful against the backbone it was trained with: refuse a mismatch before loading."""
+        errs = []
+        if backbone.arch != "gemma4":
+            errs.append(f"backbone arch {backbone.arch!r} is not gemma4")
+        if self.backbone_hidden != backbone.hidden:
+            errs.append(f"embedding_length_out {self.backbone_hidden} != backbone width {backbone.hidden}")
+        if self.n_heads != backbone.n_heads:
+            errs.append(f"head count {self.n_heads} != backbone's {backbone.n_heads}")
+        if self.vocab != backbone.vocab:
+            errs.append(f"vocabulary {self.vocab} != backbone's {backbone.vocab}")
+        if len(self.swa_blocks) != self.n_blocks:
+            errs.append("sliding-window pattern length != block count")
+        if backbone.n_layers >= 2 and backbone.arch == "gemma4":
+            if backbone.is_global_layer(backbone.n_layers - 2) or not backbone.is_global_layer(backbone.n_layers - 1):
+                errs.append("backbone's last two layers are not (sliding, global)")
+        if (2 * self.backbone_hidden) % 256 or self.hidden % 256 or self.ffn % 256:
+            errs.append("widths must be multiples of the 256-element block")
+        if errs:
+            raise ValueError("assistant head does not pair with this backbone: " + "; ".join(errs))
+
+
+GEMMA4_26B_ASSISTANT = AssistantConfig()
+TINY_GEMMA4_ASSISTANT = AssistantConfig(hidden=256, backbone_hidden=256, ffn=512, n_heads=4, vocab=2048)
+
+NAMED_ASSISTANTS: Dict[str, AssistantConfig] = {
+    "gemma4-26b-a4b": GEMMA4_26B_ASSISTANT,
+    "tiny-gemma4": TINY_GEMMA4_ASSISTANT,
+}
+
 NAMED_CONFIGS: Dict[str, ModelConfig] = {
     "tiny-dense": TINY_DENSE,
     "tiny-hybrid": TINY_HYBRID,

@@ -85,7 +85,8 @@ class Gemma4Ref:
         moe = R.rmsnorm(moe, m.W(i, "post_ffw_norm_2.weight"), eps)
         return R.rmsnorm(dense + moe, m.W(i, "post_ffw_norm.weight"), eps)
 
-    def forward_hidden(self, tokens: torch.Tensor, st) -> torch.Tensor:
+    def forward_raw(self, tokens: torch.Tensor, st) -> torch.Tensor:
+        """Residual rows after the last block, before the output norm (what the assistant head is seeded with)."""
         m, cfg = self.m, self.cfg
         T = tokens.shape[0]
         pos = torch.arange(st.pos, st.pos + T, device=m.device)
@@ -96,4 +97,61 @@ class Gemma4Ref:
             h = h + a
             h = (h + self.ffn(i, h)) * m.W(i, "layer_output_scale.weight").reshape(())
         st.pos += T
-        return R.rmsnorm(h, m.w["output_norm.weight"], cfg.rms_eps)
+        return h
+
+    def forward_hidden(self, tokens: torch.Tensor, st) -> torch.Tensor:
+        return R.rmsnorm(self.forward_raw(tokens, st), self.m.w["output_norm.weight"], self.cfg.rms_eps)
+
+
+class AssistantRef:
+    """fp32 reference of the Gemma 4 assistant (MTP) head: four post-norm blocks with no K/V of their own, each
+    attending with scale 1.0 against the backbone's cached K/V of layer ``n - 2`` (sliding blocks) or ``n - 1`` (the
+    full-attention block).  One step maps (token, backbone hidden row) to (logits, next hidden row); every step of a
+    draft uses the same position (the number of tokens the backbone has processed) and the same keys.
+    Specification: the reference's ``docs/reference/GEMMA4-ASSISTANT-MTP.md:82-150`` (forward) and ``:152-200`` (KV
+    binding); its implementation is ``hipengine/runtime/gemma4_assistant.py``."""
+
+    def __init__(self, head_weights, backbone_ref: Gemma4Ref):
+        self.acfg = head_weights.config
+        self.bb = backbone_ref
+        self.bcfg = backbone_ref.cfg
+        dev = backbone_ref.m.device
+        self.w = {n: t.dequant().to(device=dev, dtype=torch.float32) for n, t in head_weights.tensors.items()}
+
+    def step(self, token: int, h_backbone: torch.Tensor, st) -> tuple:
+        """``st`` is the backbone's state after it processed ``st.pos`` tokens; ``token`` is the token sampled from
+        its last row and ``h_backbone`` [Hb] the raw hidden of that row (or the previous step's second result)."""
+        a, b, w = self.acfg, self.bcfg, self.w
+        eps = a.rms_eps
+        pos = torch.tensor([st.pos], device=h_backbone.device)
+        x = self.bb.m.w["token_embd.weight"][int(token)].to(torch.float32) * b.embed_scale     # the BACKBONE's table
+        cur = torch.cat([x, h_backbone.to(torch.float32)])[None] @ w["nextn.pre_projection.weight"].t()
+        for il in range(a.n_blocks):
+            bl = a.backbone_layer(il, b)
+            D = b.layer_head_dim(bl)
+            p = f"blk.{il}."
+            q = (R.rmsnorm(cur, w[p + "attn_norm.weight"], eps) @ w[p + "attn_q.weight"].t()).reshape(1, a.n_heads, D)
+            q = R.rmsnorm(q, w[p + "attn_q_norm.weight"], eps)
+            n_rot, theta, denom = self.bb.rope_params(bl)
+            q = rope_partial_proportional(q, pos, n_rot, theta, denom)
+            o = R.causal_gqa_attention(q, st.k[bl], st.v[bl], pos, 1.0, window=b.layer_window(bl))
+            attn = o.reshape(1, a.n_heads * D) @ w[p + "attn_output.weight"].t()      # wo BEFORE the post norm
+            attn_out = R.rmsnorm(attn, w[p + "post_attention_norm.weight"], eps) + cur
+            f_in = R.rmsnorm(attn_out, w[p + "ffn_norm.weight"], eps)
+            ffn = R.swiglu(f_in @ w[p + "ffn_gate.weight"].t(), f_in @ w[p + "ffn_up.weight"].t(), "gelu_tanh")
+            ffn = R.rmsnorm(ffn @ w[p + "ffn_down.weight"].t(), w[p + "post_ffw_norm.weight"], eps)
+            cur = (ffn + attn_out) * w[p + "layer_output_scale.weight"].reshape(())
+        cur = R.rmsnorm(cur, w["output_norm.weight"], eps)
+        logits = (cur @ w["token_embd.weight"].t())[0]          # the HEAD's table, tied output
+        h_next = (cur @ w["nextn.post_projection.weight"].t())[0]
+        return logits, h_next
+
+    def draft(self, token: int, h_backbone: torch.Tensor, st, n: int) -> list:
+        """Greedy chain of ``n`` proposals after ``token`` (the hidden recurs through the post-projection)."""
+        out = []
+        h = h_backbone
+        for _ in range(n):
+            lg, h = self.step(token, h, st)
+            token = int(lg.argmax())
+            out.append(token)
+        return out

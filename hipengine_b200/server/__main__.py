@@ -61,7 +61,10 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--fair-prefill-burst-chunks", type=int, default=1)
     ap.add_argument("--speculative-mtp-serving", default="off", choices=["off", "auto", "on"])
     ap.add_argument("--speculative-candidate-budget", type=int, default=3)
-    ap.add_argument("--speculative-provider", default="mtp", choices=["mtp", "prompt_lookup", "ngram"])
+    ap.add_argument("--speculative-provider", default="mtp", choices=["mtp", "gemma4_mtp", "prompt_lookup", "ngram"])
+    ap.add_argument("--draft-model", default=None,
+                    help="Gemma 4: path of the assistant (MTP) head GGUF (general.architecture gemma4-assistant), or "
+                         "'random' for a random-init head of the matching geometry")
     ap.add_argument("--mtp-hot-vocab", default="off",
                     help="NextN draft head slice: off | auto (98304 rows) | row count; verification keeps the full head")
     ap.add_argument("--kv-cold-tier-gib", type=float, default=0.0,
@@ -126,7 +129,7 @@ def main(argv: Optional[List[str]] = None) -> int:
               max_active_requests=a.max_active_requests, max_sequence_length=a.max_context_tokens,
               prefix_cache=a.prefix_cache, speculative_mtp_serving=a.speculative_mtp_serving,
               speculative_candidate_budget=a.speculative_candidate_budget,
-              speculative_provider=a.speculative_provider, mtp_hot_vocab=a.mtp_hot_vocab,
+              speculative_provider=a.speculative_provider, mtp_hot_vocab=a.mtp_hot_vocab, draft_model=a.draft_model,
               kv_cold_tier_bytes=int(a.kv_cold_tier_gib * (1 << 30)), kv_cold_tier_dir=a.kv_cold_tier_dir,
               tensor_parallel=a.tensor_parallel,
               expert_parallel=a.expert_parallel, engine_config=eng, expected_quant=a.quant)

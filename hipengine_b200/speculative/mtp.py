@@ -52,8 +52,9 @@ class ChainVerifyCycle:
     def after_prefill(self, batch: BatchDesc, h: torch.Tensor) -> None:
         pass
 
-    def _after_commit(self, slot_t: torch.Tensor, hid: torch.Tensor, R: int) -> None:
-        pass
+    def _after_commit(self, slot_t: torch.Tensor, hid: torch.Tensor, R: int, raw: Optional[torch.Tensor] = None) -> None:
+        """``hid``: post-norm hidden rows of the verify forward, ``raw``: its residual rows before the output norm;
+        ``self.hidden_row[:R]`` indexes the row whose logits produced each request's last emitted token."""
 
     def _verify_accept_commit(self, txn: SpecTransaction, slots, positions, t0: torch.Tensor, drafts: torch.Tensor,
                               temperature, seeds, counters) -> List[SpecCycleResult]:
@@ -109,7 +110,7 @@ class ChainVerifyCycle:
         tok_t = torch.empty(R, dtype=torch.int64, device=dev)
         K.spec_commit(self.n_accept[:R], out, tok_t, pos_t, None, self.commit_row[:R], self.hidden_row[:R])
         ex.commit_journal(journal, vb.seg_slot, self.commit_row[:R])
-        self._after_commit(slot_t, hid, R)
+        self._after_commit(slot_t, hid, R, raw=h)
         txn.advance(Stage.COMMITTED)
         res = []
         for r in range(R):
@@ -156,7 +157,7 @@ class MTPCycle(ChainVerifyCycle):
                                      graph_capture=isinstance(self, GraphedMTPCycle),
                                      draft_head_rows=self.draft_head_rows)
 
-    def _after_commit(self, slot_t: torch.Tensor, hid: torch.Tensor, R: int) -> None:
+    def _after_commit(self, slot_t: torch.Tensor, hid: torch.Tensor, R: int, raw: Optional[torch.Tensor] = None) -> None:
         picked = self.ex.scratch.get("mtp_pick", (R, self.ex.cfg.hidden), torch.float32)
         K.gather_rows_f32(hid, self.hidden_row[:R], picked)
         self.h_prev.index_copy_(0, slot_t, picked)

@@ -26,6 +26,7 @@ class SpeculativeProviderConfig:
     max_ngram: int = 4
     table_entries: int = 1 << 16      # ngram provider: bound of the shared table
     hot_vocab: object = "off"         # mtp provider: off | auto | rows of the draft head slice (draft_vocab.py)
+    draft_model: object = None        # gemma4_mtp provider: path of the assistant head GGUF, loaded weights, or "random"
 
 
 class PromptLookupDrafter:
@@ -130,7 +131,37 @@ def register_speculative_provider(name: str, factory: Callable) -> None:
     _PROVIDERS[name] = factory
 
 
+def _gemma4_mtp_factory(ex, cfg: SpeculativeProviderConfig, max_requests: int):
+    """Gemma 4 backbone + its assistant head (a separate artifact named by ``draft_model``)."""
+    if getattr(getattr(ex, "cfg", None), "arch", "") != "gemma4" or cfg.draft_model in (None, "", "off"):
+        return None
+    if getattr(getattr(ex, "ctx", None), "world", 1) != 1:
+        return None                      # the head reads the backbone's KV heads of one rank's shard only
+    from ..loading.weights import ModelWeights
+    from ..models.gemma4_assistant import Gemma4AssistantHead
+    from .gemma4_mtp import AssistantMTPCycle
+    dm = cfg.draft_model
+    if isinstance(dm, ModelWeights):
+        weights = dm
+    elif dm == "random":
+        from ..loading.gemma4 import build_random_assistant
+        from ..models.config import AssistantConfig, NAMED_ASSISTANTS
+        acfg = next((a for a in NAMED_ASSISTANTS.values()
+                     if a.backbone_hidden == ex.cfg.hidden and a.vocab == ex.cfg.vocab and a.n_heads == ex.cfg.n_heads),
+                    None) or AssistantConfig(hidden=max(256, ex.cfg.hidden // 4 // 256 * 256),
+                                             backbone_hidden=ex.cfg.hidden, ffn=2 * ex.cfg.hidden // 256 * 256,
+                                             n_heads=ex.cfg.n_heads, vocab=ex.cfg.vocab)
+        weights = build_random_assistant(acfg, ex.cfg, seed=0, device=ex.device)
+    else:
+        from ..loading.gemma4 import load_assistant_gguf
+        weights = load_assistant_gguf(dm, ex.cfg, device=ex.device)
+    head = Gemma4AssistantHead(ex, weights, max_rows=max_requests)
+    return AssistantMTPCycle(ex, head, max_depth=max(1, cfg.max_depth), max_requests=max_requests)
+
+
 def _mtp_factory(ex, cfg: SpeculativeProviderConfig, max_requests: int):
+    if getattr(getattr(ex, "cfg", None), "arch", "") == "gemma4":
+        return _gemma4_mtp_factory(ex, cfg, max_requests)     # this family's MTP head is the assistant artifact
     if not getattr(ex, "has_nextn", False):
         return None
     import os
@@ -156,6 +187,7 @@ def _ngram_factory(ex, cfg: SpeculativeProviderConfig, max_requests: int):
 
 def register_builtin_speculative_providers() -> List[str]:
     register_speculative_provider("mtp", _mtp_factory)
+    register_speculative_provider("gemma4_mtp", _gemma4_mtp_factory)
     register_speculative_provider("prompt_lookup", _prompt_lookup_factory)
     register_speculative_provider("ngram", _ngram_factory)
     return sorted(_PROVIDERS)

@@ -434,3 +434,60 @@ def test_hot_vocab_rows_setting_and_recent_miss_rule():
     book.drop("a")
     book.clear()
     assert len(book) == 0
+
+
+def test_gemma4_assistant_head_pairing_artifact_round_trip_and_reference(tmp_path):
+    """The assistant (MTP) head: pairing checks, GGUF round trip with validation, and properties of the fp32
+    reference that the specification states (same position and keys for every step of a draft, the backbone's
+    embedding table on the way in, a sliding block sees the last window - 1 keys)."""
+    from dataclasses import replace
+    import torch
+    from hipengine_b200.loading.gemma4 import (assistant_tensor_names, build_random_assistant, load_assistant_gguf,
+                                                validate_assistant)
+    from hipengine_b200.loading.synth import build_random_model, write_gguf
+    from hipengine_b200.models.config import (GEMMA4_26B_A4B, GEMMA4_26B_ASSISTANT, TINY_GEMMA4,
+                                              TINY_GEMMA4_ASSISTANT, TINY_HYBRID)
+    from hipengine_b200.ref.gemma4 import AssistantRef
+    from hipengine_b200.ref.model import RefModel, RefState
+    GEMMA4_26B_ASSISTANT.check_pairing(GEMMA4_26B_A4B)
+    assert [GEMMA4_26B_ASSISTANT.backbone_layer(i, GEMMA4_26B_A4B) for i in range(4)] == [28, 28, 28, 29]
+    with pytest.raises(ValueError, match="not gemma4"):
+        TINY_GEMMA4_ASSISTANT.check_pairing(TINY_HYBRID)
+    with pytest.raises(ValueError, match="backbone width"):
+        replace(TINY_GEMMA4_ASSISTANT, backbone_hidden=512).check_pairing(TINY_GEMMA4)
+    hw = build_random_assistant(TINY_GEMMA4_ASSISTANT, TINY_GEMMA4, seed=2, std=0.05)
+    assert sorted(hw.tensors) == sorted(assistant_tensor_names(TINY_GEMMA4_ASSISTANT)) and len(hw.tensors) == 48
+    path = write_gguf(hw, tmp_path / "assistant.gguf")
+    back = load_assistant_gguf(path, TINY_GEMMA4)
+    assert replace(back.config, rms_eps=1e-6) == TINY_GEMMA4_ASSISTANT            # eps travels as fp32
+    assert all(torch.equal(back[n].raw.reshape(-1), hw[n].raw.reshape(-1)) for n in hw.tensors)
+    broken = type(hw)(hw.config, {k: v for k, v in hw.tensors.items() if k != "blk.2.attn_q.weight"}, hw.metadata)
+    with pytest.raises(ValueError, match="missing blk.2.attn_q.weight"):
+        validate_assistant(broken, TINY_GEMMA4)
+    # ---- reference behaviour
+    w = build_random_model(TINY_GEMMA4, seed=1, std=0.05)
+    ref = RefModel(w)
+    st = RefState()
+    toks = torch.randint(0, 2048, (40,), generator=torch.Generator().manual_seed(0))
+    h = ref._gemma.forward_raw(toks, st)
+    k_before = {i: t.clone() for i, t in st.k.items()}
+    ar = AssistantRef(hw, ref._gemma)
+    lg, hn = ar.step(7, h[-1], st)
+    assert lg.shape == (2048,) and hn.shape == (256,) and torch.isfinite(lg).all()
+    assert st.pos == 40 and all(torch.equal(st.k[i], k_before[i]) for i in st.k)       # the head writes no KV
+    d1 = ar.draft(7, h[-1], st, 3)
+    assert d1 == ar.draft(7, h[-1], st, 3) and len(d1) == 3                          # stateless: same draft again
+    lg2, _ = ar.step(8, h[-1], st)
+    assert not torch.allclose(lg, lg2)                                                # the token matters
+    # keys older than the window do not reach a sliding block; the full block still sees them
+    st2 = st.clone()
+    st2.k[4][:8] += 5.0                    # layer n-2 (sliding, window 32): rows 0..7 are outside (40-32, 40]
+    lg3, _ = ar.step(7, h[-1], st2)
+    assert torch.allclose(lg, lg3)
+    st2.k[4][9] += 5.0                     # key 9 = position - window + 1: the oldest one a sliding block sees
+    lg4, _ = ar.step(7, h[-1], st2)
+    assert not torch.allclose(lg, lg4)
+    st3 = st.clone()
+    st3.k[5][:8] += 5.0                    # layer n-1 (full attention)
+    lg5, _ = ar.step(7, h[-1], st3)
+    assert not torch.allclose(lg, lg5)

@@ -97,7 +97,7 @@ def test_prompt_lookup_and_ngram_drafters_and_registry():
     assert g.propose([99, 10, 11], 2) == [12, 13]       # learnt from another request
     g.observe(list(range(100, 140)))
     assert len(g.table) <= 4                            # bounded
-    assert register_builtin_speculative_providers() == ["mtp", "ngram", "prompt_lookup"]
+    assert register_builtin_speculative_providers() == ["gemma4_mtp", "mtp", "ngram", "prompt_lookup"]
     assert "prompt_lookup" in speculative_provider_names()
 
     class _NoNextN:
