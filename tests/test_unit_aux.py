@@ -491,3 +491,26 @@ def test_gemma4_assistant_head_pairing_artifact_round_trip_and_reference(tmp_pat
     st3.k[5][:8] += 5.0                    # layer n-1 (full attention)
     lg5, _ = ar.step(7, h[-1], st3)
     assert not torch.allclose(lg, lg5)
+
+
+def test_speculative_options_reach_the_engine_config():
+    """--mtp-hot-vocab / --draft-model / the gemma4_mtp provider name travel from the flags and the LLM keywords
+    into the speculative configuration the runner reads."""
+    from hipengine_b200.llm import LLM
+    from hipengine_b200.server.__main__ import build_parser
+    a = build_parser().parse_args(["--model", "tiny-dense", "--speculative-mtp-serving", "on", "--speculative-provider",
+                                   "gemma4_mtp", "--draft-model", "/models/mtp-head.gguf", "--mtp-hot-vocab", "auto"])
+    assert (a.speculative_provider, a.draft_model, a.mtp_hot_vocab) == ("gemma4_mtp", "/models/mtp-head.gguf", "auto")
+    llm = LLM("tiny-dense", backend="cpu_reference", max_active_requests=2, max_sequence_length=128,
+              speculative_mtp_serving="on", speculative_provider="gemma4_mtp", draft_model="/models/mtp-head.gguf",
+              mtp_hot_vocab=4096)
+    try:
+        sc = llm.config.speculative
+        assert (sc.mode, sc.draft_model, sc.hot_vocab) == ("gemma4_mtp", "/models/mtp-head.gguf", "4096")
+    finally:
+        llm.close()
+    off = LLM("tiny-dense", backend="cpu_reference", max_active_requests=2, max_sequence_length=128)
+    try:
+        assert off.config.speculative.mode == "off" and off.config.speculative.draft_model is None
+    finally:
+        off.close()
