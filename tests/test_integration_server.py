@@ -316,3 +316,58 @@ def test_pool_budget_and_expected_quant_in_admission():
     with pytest.raises(ArtifactRejected, match="expected"):
         admit(w, EngineConfig.from_env(), free_bytes=10 ** 12, expected_quant="Q2_K")
     assert admit(w, EngineConfig.from_env(), free_bytes=10 ** 12, expected_quant=rep["dominant_block_type"])["admitted"]
+
+
+class _InProcessTransport:
+    """The chat client's transport over a FastAPI TestClient (no sockets)."""
+
+    def __init__(self, client):
+        self.c = client
+
+    def get(self, path):
+        return self.c.get(path).json()
+
+    def stream(self, path, body):
+        with self.c.stream("POST", path, json=body) as r:
+            assert r.status_code == 200, r.read()
+            for line in r.iter_lines():
+                if line.startswith("data: "):
+                    yield line[6:]
+
+
+def test_chat_client_streams_turns_keeps_the_transcript_and_reports_server_side_stats(tmp_path):
+    import io
+    import json
+    from fastapi.testclient import TestClient
+    from hipengine_b200.chat_cli import ChatClient, Settings, run_repl
+    from hipengine_b200.llm import LLM
+    from hipengine_b200.server.api import ServerConfig, create_app
+    llm = LLM("tiny-dense", backend="cpu_reference", max_active_requests=2, max_sequence_length=512)
+    try:
+        with TestClient(create_app(llm, ServerConfig(served_model_name="tiny-dense"))) as tc:
+            c = ChatClient(_InProcessTransport(tc), settings=Settings(max_tokens=6, temperature=0.0, think=False))
+            assert c.discover_model() == "tiny-dense"
+            pieces = list(c.stream_turn("hello there"))
+            assert pieces and all(p.kind in ("content", "reasoning", "tool_call") for p in pieces)
+            st = c.last
+            assert st.completion_tokens == 6 and st.prompt_tokens > 0 and st.finish_reason == "length"
+            assert st.ttft_ms is not None and st.decode_tok_s is not None and "tok/s" in st.line()
+            assert [m["role"] for m in c.messages] == ["user", "assistant"]
+            b = c.bench(2)
+            assert b["turns"] == 2 and b["completion_tokens"] == 12 and b["ttft_ms_median"] is not None
+            assert [m["role"] for m in c.messages] == ["user", "assistant"]          # bench leaves the transcript
+            assert c.usage.turns == 3
+            # the command loop: settings, a turn, retry, undo, save, status, unknown command
+            out = io.StringIO()
+            f = tmp_path / "t.json"
+            rc = run_repl(c, ["/max 4", "/system be brief", "second question", "/retry", "/undo", "/usage",
+                              f"/save {f}", "/status", "/nope", "/max x", "/quit", "never reached"], out)
+            text = out.getvalue()
+            assert rc == 0 and text.count("tok/s") == 2                                # the turn and its retry
+            assert "unknown command" in text and "error:" in text and "never reached" not in text
+            assert c.settings.max_tokens == 4 and c.settings.system == "be brief" and c.last.completion_tokens == 4
+            saved = json.loads(f.read_text())
+            assert saved["system"] == "be brief" and [m["role"] for m in saved["messages"]] == ["user", "assistant"]
+            assert '"status"' in text or '"ready"' in text or '"engine"' in text
+    finally:
+        llm.close()
