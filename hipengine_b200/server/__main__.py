@@ -114,12 +114,9 @@ def main(argv: Optional[List[str]] = None) -> int:
         from dataclasses import asdict
         print(json.dumps({"engine": asdict(eng), "server": asdict(srv)}, indent=1, default=str))
         return 0
+    from . import log_style
     level = "DEBUG" if a.debug else a.log_level.upper()
-    color = a.log_color == "always" or (a.log_color == "auto" and sys.stderr.isatty())
-    fmt = "%(asctime)s %(levelname)s %(name)s: %(message)s"
-    if color:
-        fmt = "\033[2m%(asctime)s\033[0m \033[1m%(levelname)s\033[0m %(name)s: %(message)s"
-    logging.basicConfig(level=level, format=fmt)
+    log_style.install(level, log_style.want_color(a.log_color, sys.stderr.isatty()))
     log = logging.getLogger("hipengine_b200.server")
     from ..llm import LLM
     from .api import create_app
@@ -143,8 +140,13 @@ def main(argv: Optional[List[str]] = None) -> int:
         return 0
     if a.eager_load or a.startup_chat_smoke or max(a.tensor_parallel, a.expert_parallel) > 1:
         info = llm.prepare()
-        log.info("LOAD_TIMING prepare=%.2fs stages=%s capacity=%s", time.time() - t0,
-                 {s["name"]: s["seconds"] for s in llm.startup["stages"]}, info)
+        log_style.log_lines(log, log_style.load_timing_rows(llm.startup))
+        log.info("LOAD_TIMING prepare=%.2fs", time.time() - t0)
+        log_style.log_lines(log, log_style.startup_summary(
+            srv.served_model_name, llm.backend, info if isinstance(info, dict) else None, llm.startup,
+            {"tensor_parallel": a.tensor_parallel, "expert_parallel": a.expert_parallel,
+             "prefix_cache": a.prefix_cache, "speculative": a.speculative_mtp_serving,
+             "mtp_hot_vocab": a.mtp_hot_vocab, "draft_model": a.draft_model, "kv_storage": a.kv_storage}))
     if a.startup_chat_smoke:
         from ..llm import SamplingParams
         out = llm.chat([{"role": "user", "content": a.eager_load_prompt}],

@@ -106,6 +106,18 @@ def build_chat(req: ChatCompletionRequest, tokenizer, arch: str, default_max: in
     if req.top_logprobs is not None and not (0 <= req.top_logprobs <= 20):
         raise APIError("unsupported_parameter", "top_logprobs must be in [0, 20]", "top_logprobs")
     validate_messages(req.messages)
+    # media parts are parsed under hard limits first; the text-only models served here cannot use them, and dropping
+    # them silently would answer another question than the one asked
+    from .multimodal import MediaError, extract_media
+    try:
+        media = extract_media(req.messages)
+    except MediaError as exc:
+        raise APIError("invalid_request", str(exc), exc.param) from None
+    if media:
+        raise APIError("unsupported_feature",
+                       f"the served model is text-only: {len(media)} media part(s) were validated but cannot be used",
+                       f"messages[{media[0].message_index}].content[{media[0].part_index}]",
+                       extra={"media": [m.as_dict() for m in media]})
     plan = ResultPlan(hard_error=req.invalid_tool_call_error_mode == "hard_error")
 
     # ---- thinking controls

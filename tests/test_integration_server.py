@@ -371,3 +371,61 @@ def test_chat_client_streams_turns_keeps_the_transcript_and_reports_server_side_
             assert '"status"' in text or '"ready"' in text or '"engine"' in text
     finally:
         llm.close()
+
+
+def _png(w, h):
+    import struct
+    import zlib
+    ihdr = struct.pack(">IIBBBBB", w, h, 8, 2, 0, 0, 0)
+    chunk = lambda t, d: struct.pack(">I", len(d)) + t + d + struct.pack(">I", zlib.crc32(t + d))
+    return b"\x89PNG\r\n\x1a\n" + chunk(b"IHDR", ihdr) + chunk(b"IDAT", zlib.compress(b"\0" * 4)) + chunk(b"IEND", b"")
+
+
+def test_media_parts_are_parsed_under_limits_and_refused_by_the_text_only_server():
+    import base64
+    import struct
+    from fastapi.testclient import TestClient
+    from hipengine_b200.llm import LLM
+    from hipengine_b200.server.api import ServerConfig, create_app
+    from hipengine_b200.server.multimodal import MediaError, MediaLimits, extract_media, sniff_image
+    url = lambda raw, mime="image/png": f"data:{mime};base64," + base64.b64encode(raw).decode()
+    msg = lambda *parts: [{"role": "user", "content": list(parts)}]
+    img = lambda u: {"type": "image_url", "image_url": {"url": u}}
+    got = extract_media(msg({"type": "text", "text": "what is this"}, img(url(_png(640, 480)))))
+    assert [(m.kind, m.mime, m.width, m.height, m.part_index) for m in got] == [("image", "image/png", 640, 480, 1)]
+    gif = b"GIF89a" + struct.pack("<HH", 12, 7) + b"\0" * 8
+    jpg = b"\xff\xd8\xff\xe0\x00\x10JFIF\0" + b"\0" * 9 + b"\xff\xc0\x00\x11\x08" + struct.pack(">HH", 30, 40) + b"\0" * 12
+    assert sniff_image(gif) == ("image/gif", 12, 7) and sniff_image(jpg) == ("image/jpeg", 40, 30)
+    assert sniff_image(b"not an image at all") == (None, None, None)
+    for bad, needle in [
+        (img("https://example.com/cat.png"), "not fetched"),
+        (img(url(_png(640, 480), "image/jpeg")), "does not match"),
+        (img("data:image/png;base64,@@@@"), "not valid base64"),
+        (img(url(_png(70000, 10))), "exceeds the limit"),
+        (img(url(b"plain text", "image/png")), "unrecognised image"),
+        ({"type": "image_url"}, "no URL"),
+    ]:
+        with pytest.raises(MediaError, match=needle) as ei:
+            extract_media(msg(bad))
+        assert ei.value.param == "messages[0].content[0]"
+    with pytest.raises(MediaError, match="more than 2 media parts"):
+        extract_media(msg(*[img(url(_png(8, 8)))] * 3), MediaLimits(max_parts=2))
+    with pytest.raises(MediaError, match="exceeds 64 bytes"):
+        extract_media(msg(img(url(_png(8, 8) + b"\0" * 100))), MediaLimits(max_image_bytes=64))
+    llm = LLM("tiny-dense", backend="cpu_reference", max_active_requests=2, max_sequence_length=256)
+    try:
+        with TestClient(create_app(llm, ServerConfig(served_model_name="tiny-dense"))) as c:
+            body = {"model": "tiny-dense", "max_tokens": 3, "messages": msg({"type": "text", "text": "hi"},
+                                                                           img(url(_png(32, 32))))}
+            r = c.post("/v1/chat/completions", json=body)
+            assert r.status_code == 501, r.text
+            e = r.json()["error"]
+            assert e["code"] == "unsupported_feature" and e["param"] == "messages[0].content[1]"
+            assert e["hipengine"]["media"][0]["width"] == 32
+            body["messages"] = msg(img("http://10.0.0.1/x.png"))
+            r = c.post("/v1/chat/completions", json=body)
+            assert r.status_code == 400 and "not fetched" in r.json()["error"]["message"]
+            body["messages"] = msg({"type": "text", "text": "text parts alone are fine"})
+            assert c.post("/v1/chat/completions", json=body).status_code == 200
+    finally:
+        llm.close()

@@ -514,3 +514,36 @@ def test_speculative_options_reach_the_engine_config():
         assert off.config.speculative.mode == "off" and off.config.speculative.draft_model is None
     finally:
         off.close()
+
+
+def test_log_style_formatter_load_timing_rows_and_startup_summary():
+    import logging
+    from hipengine_b200.server import log_style as L
+    assert L.want_color("always", False) and not L.want_color("auto", False) and not L.want_color("never", True)
+    rec = logging.LogRecord("he.server", logging.WARNING, __file__, 1, "pool at %d%%", (93,), None)
+    plain, col = L.StyledFormatter(False).format(rec), L.StyledFormatter(True).format(rec)
+    assert plain.endswith("WARNING he.server: pool at 93%") and "\x1b[" not in plain
+    assert "\x1b[33m" in col and "pool at 93%" in col and col.endswith("pool at 93%")
+    assert L.human_bytes(15 * 2 ** 30) == "15.00 GiB" and L.human_bytes(512) == "512 B" and L.human_bytes(None) == "-"
+    startup = {"stages": [{"name": "load_weights", "seconds": 3.0, "ok": True},
+                          {"name": "build_engine", "seconds": 1.0, "ok": False}],
+               "error": "build_engine: RuntimeError: x", "memory": {"device_free_bytes": 2 ** 36,
+                                                                     "device_total_bytes": 3 * 2 ** 36},
+               "warmup_complete": False}
+    rows = L.load_timing_rows(startup)
+    assert rows[0] == "LOAD_TIMING stage=load_weights seconds=3.000 share=75.0% ok"
+    assert rows[1].endswith("FAILED") and rows[2].startswith("LOAD_TIMING total seconds=4.000") and "error=" in rows[2]
+    cap = {"max_context": 8192, "max_slots": 8, "weight_bytes": 15 * 2 ** 30, "kv_bytes_per_token": 65536,
+           "kv_pool": {"pages_total": 4096, "page_tokens": 16},
+           "speculative": {"provider": "nextn_mtp", "max_depth": 3, "graph_capture": True, "draft_head_rows": 98304}}
+    text = "\n".join(L.startup_summary("qwen", "cuda_sm100a", cap, startup, {"tensor_parallel": 8, "prefix_cache": "off",
+                                                                               "draft_model": None}))
+    assert "weights 15.00 GiB" in text and "KV pool 4096 pages x 16 tokens (4.00 GiB)" in text
+    assert "speculative provider nextn_mtp depth 3 (one graph per cycle), draft head slice 98304 rows" in text
+    assert "option tensor_parallel=8" in text and "prefix_cache" not in text and "draft_model" not in text
+    assert "64.00 GiB free of 192.00 GiB" in text and "not warmed up" in text
+    L.install("INFO", False)
+    L.install("INFO", False)                                  # idempotent: one styled handler, not two
+    assert sum(1 for h in logging.getLogger().handlers if getattr(h, "_he_styled", False)) == 1
+    for h in [h for h in logging.getLogger().handlers if getattr(h, "_he_styled", False)]:
+        logging.getLogger().removeHandler(h)
