@@ -72,7 +72,7 @@ def resolve_pool_pages(kv: "KVConfig", kv_bytes_per_token: int, n_slots: int, pa
 class SpeculativeConfig:
     mode: str = "off"                       # off | mtp | prompt_lookup | ngram (``speculative/providers.py``)
     draft_depth: int = 3
-    adaptive_depth: bool = False
+    adaptive_depth: bool = True             # shrink the draft depth to what the measured acceptance rate pays for
     hot_vocab: str = "off"                  # NextN draft head slice: off | auto | row count (``speculative/draft_vocab.py``)
     draft_model: Any = None                 # Gemma 4: the assistant (MTP) head artifact (path, loaded weights or "random")
 

@@ -480,7 +480,8 @@ class GpuRunner(BaseRunner):
             remaining = rs.remaining()
             room = rs.total_budget_tokens - rs.position
             depth = min(depth, plan_draft_depth(self.mtp.max_depth, remaining, room, rs.telemetry.speculative_drafted,
-                                                rs.telemetry.speculative_accepted))
+                                                rs.telemetry.speculative_accepted,
+                                                adaptive=self.config.speculative.adaptive_depth))
         if depth < 1:
             return [SpecCycleResult([t], 0, 0) for t, _ in self.decode(rows)]
         for rs in rows:

@@ -71,6 +71,13 @@ def test_planner_and_serving_rules():
     assert plan_draft_depth(3, 100, 100, drafted=300, accepted=0) == 0        # nothing ever accepted: stop drafting
     assert plan_draft_depth(3, 100, 100, drafted=300, accepted=270) == 3
     assert abs(expected_tokens(0.5, 2) - 1.75) < 1e-9
+    from hipengine_b200.speculative.policy import break_even_accept_rate, cycle_cost
+    assert abs(cycle_cost(3) - 2.32) < 1e-9                                   # measured: 2.33 autoregressive steps
+    assert abs(break_even_accept_rate(1) - 0.44) < 1e-6                       # 1 + a = 1.44
+    assert 0.6 < break_even_accept_rate(3) < 0.7 and break_even_accept_rate(3, 0.5, 0.6) == 1.0
+    assert plan_draft_depth(3, 100, 100, drafted=300, accepted=120) == 0       # 40 % acceptance does not pay here
+    assert plan_draft_depth(3, 100, 100, drafted=300, accepted=120, adaptive=False) == 3
+    assert plan_draft_depth(3, 100, 100, drafted=300, accepted=180) >= 1       # 60 % does
     ok = resolve_mtp_serving_plan("on", True, 0.0, False, False, False)
     assert ok.use_mtp and ok.sampling_mode == "greedy"
     assert resolve_mtp_serving_plan("on", True, 0.7, False, False, False).sampling_mode == "sampled"
