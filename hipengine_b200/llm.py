@@ -387,6 +387,67 @@ class LLM:
             sps = replace(sps, speculative_mtp=True)
         return self.generate_detailed(prompts, sps)
 
+    def stream_speculative_mtp_detailed(self, prompt: PromptLike, sampling_params: Optional[SamplingParams] = None
+                                        ) -> Iterator[GenerationStreamChunk]:
+        """Stream one request through the speculative path: a chunk carries the 1 .. depth + 1 tokens a cycle
+        committed (``hipengine/llm.py:859`` of the reference)."""
+        yield from self.stream_detailed(prompt, replace(sampling_params or SamplingParams(), speculative_mtp=True))
+
+    def generate_speculative_detailed(self, prompts, sampling_params=None) -> List[GenerationOutput]:
+        """Speculative decoding with whichever provider the engine was built with (NextN block, assistant head,
+        prompt lookup, n-gram table); an engine without one raises instead of silently decoding step by step."""
+        if self.config.speculative.mode in ("off", "", None):
+            raise ValueError("this engine was built without a speculative provider "
+                             "(speculative_mtp_serving / speculative_provider)")
+        return self.generate_speculative_mtp_detailed(prompts, sampling_params)
+
+    def resolve_speculative_mtp_serving_plan(self, sampling_params: Optional[SamplingParams] = None,
+                                             breaker_open: bool = False):
+        """Would a request with these parameters take the speculative path, and if not, why
+        (``hipengine/llm.py:1041``; rules in ``speculative/serving.py``)."""
+        from .speculative.serving import resolve_mtp_serving_plan
+        sp = sampling_params or SamplingParams()
+        mode = self.config.speculative.mode
+        eng = self._get_engine()
+        runner = getattr(getattr(eng, "loop", None), "runner", None)
+        # the runner's rule (``generation/runner.py::_needs_processing``) as far as it can be read off the parameters
+        processed = bool(sp.logit_bias or sp.suppress_token_ids or sp.repetition_penalty != 1.0
+                         or sp.presence_penalty != 0.0 or sp.frequency_penalty != 0.0 or sp.min_tokens
+                         or sp.grammar is not None or sp.tool_call_constraint is not None)
+        return resolve_mtp_serving_plan("off" if mode in ("off", "", None) else "on",
+                                        bool(getattr(runner, "supports_mtp", False)), float(sp.temperature or 0.0),
+                                        processed, bool(sp.forced_tokens_pending), bool(sp.logprobs),
+                                        breaker_open=breaker_open, depth=self.config.speculative.draft_depth,
+                                        requested=True)
+
+    def submit_independent_batches_detailed(self, batches: Sequence[Sequence[PromptLike]], sampling_params=None
+                                            ) -> List[List[GenerationOutput]]:
+        """Several caller-side batches admitted together: the engine batches continuously across all of them, the
+        outputs come back grouped as they were submitted (``hipengine/llm.py:577``)."""
+        flat = [p for b in batches for p in b]
+        if isinstance(sampling_params, (list, tuple)):
+            if len(sampling_params) != len(batches):
+                raise ValueError("one SamplingParams per batch (or a single one for all) is expected")
+            sps = [sp or SamplingParams() for b, sp in zip(batches, sampling_params) for _ in b]
+        else:
+            sps = [sampling_params or SamplingParams()] * len(flat)
+        outs = self.generate_detailed(flat, sps) if flat else []
+        grouped, i = [], 0
+        for b in batches:
+            grouped.append(outs[i:i + len(b)])
+            i += len(b)
+        return grouped
+
+    def fit_context(self, prompt: PromptLike, max_tokens: Optional[int] = None) -> Dict[str, Any]:
+        """Does ``prompt`` (text or token ids) fit the served context, and how many tokens may follow it."""
+        n = len(self.tokenize(prompt)) if isinstance(prompt, str) else len(list(prompt))
+        mx = int(self.resident_capacity_estimate().get("max_context") or self.config.max_sequence_length)
+        room = max(0, mx - n)
+        out = {"prompt_tokens": n, "max_context": mx, "max_new_tokens": room, "fits": n < mx}
+        if max_tokens is not None:
+            out["fits_with_max_tokens"] = n + int(max_tokens) <= mx
+        return out
+
     # ------------------------------------------------------------------ tokenizer helpers
     def tokenize(self, text: str) -> List[int]:
         return self._get_tokenizer().encode(text)

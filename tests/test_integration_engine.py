@@ -165,3 +165,43 @@ def test_required_tool_call_is_grammar_constrained_token_by_token():
             assert auto.accepting(s)
     finally:
         llm.close()
+
+
+def test_llm_batches_fit_context_and_speculative_plan_helpers():
+    """Host-side helpers of the public API: grouped submission of several batches, the context-fit estimate, the
+    serving-plan question, and the refusal to run 'speculative' generation on an engine without a provider."""
+    from hipengine_b200.llm import LLM, SamplingParams
+    llm = LLM("tiny-dense", backend="cpu_reference", max_active_requests=4, max_sequence_length=128)
+    try:
+        sp = SamplingParams(max_tokens=3, ignore_eos=True)
+        flat = llm.generate_detailed([[1, 2, 3], [4, 5], [6, 7, 8, 9]], sp)
+        grouped = llm.submit_independent_batches_detailed([[[1, 2, 3], [4, 5]], [], [[6, 7, 8, 9]]], sp)
+        assert [len(g) for g in grouped] == [2, 0, 1]
+        assert [o.token_ids for g in grouped for o in g] == [o.token_ids for o in flat]
+        per_batch = llm.submit_independent_batches_detailed([[[1, 2, 3]], [[4, 5]]],
+                                                            [sp, SamplingParams(max_tokens=5, ignore_eos=True)])
+        assert [len(g[0].token_ids) for g in per_batch] == [3, 5]
+        with pytest.raises(ValueError, match="one SamplingParams per batch"):
+            llm.submit_independent_batches_detailed([[[1]], [[2]]], [sp])
+        fit = llm.fit_context(list(range(100)), max_tokens=40)
+        assert fit == {"prompt_tokens": 100, "max_context": 128, "max_new_tokens": 28, "fits": True,
+                       "fits_with_max_tokens": False}
+        assert llm.fit_context("hello")["prompt_tokens"] == llm.count_tokens("hello")
+        assert not llm.fit_context(list(range(128)))["fits"]
+        plan = llm.resolve_speculative_mtp_serving_plan(sp)
+        assert not plan.use_mtp and plan.reason == "disabled"
+        with pytest.raises(ValueError, match="without a speculative provider"):
+            llm.generate_speculative_detailed([[1, 2, 3]], sp)
+        chunks = list(llm.stream_speculative_mtp_detailed([1, 2, 3], sp))       # falls back to step-by-step decoding
+        assert [t for c in chunks for t in c.token_ids] == flat[0].token_ids
+    finally:
+        llm.close()
+    spec = LLM("tiny-dense", backend="cpu_reference", max_active_requests=2, max_sequence_length=128,
+               speculative_mtp_serving="on", speculative_provider="prompt_lookup")
+    try:
+        p = spec.resolve_speculative_mtp_serving_plan(SamplingParams(max_tokens=3))
+        assert p.reason in ("ok", "no_nextn_block")                                # the CPU runner has no verifier
+        assert spec.resolve_speculative_mtp_serving_plan(SamplingParams(logit_bias={5: 2.0})).reason in (
+            "sampler_not_reproducible", "no_nextn_block")
+    finally:
+        spec.close()
