@@ -10,6 +10,32 @@ import pytest
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
+TIERS = ("unit", "integration", "gpu", "dist", "zz")
+
+
+def pytest_addoption(parser):
+    parser.addoption("--suite", default="all", choices=["unit", "integration", "gpu", "dist", "all"],
+                     help="run one tier of the test files (test_<tier>_<subject>.py); default: all")
+
+
+def _tier_of(path: str) -> str:
+    name = os.path.basename(path)
+    for t in TIERS:
+        if name.startswith(f"test_{t}_"):
+            return t
+    return "unit"
+
+
+@pytest.fixture(autouse=True)
+def _restore_he_environment():
+    """Every ``HE_*`` switch a test sets is put back afterwards, so tests cannot leak configuration into each other."""
+    before = {k: v for k, v in os.environ.items() if k.startswith("HE_")}
+    yield
+    for k in [k for k in os.environ if k.startswith("HE_") and k not in before]:
+        del os.environ[k]
+    os.environ.update(before)
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (B200)")
     config.addinivalue_line("markers", "dist: spawns multiple ranks")
@@ -17,6 +43,13 @@ def pytest_configure(config):
 
 
 def pytest_collection_modifyitems(config, items):
+    suite = config.getoption("--suite")
+    if suite != "all":
+        keep = [it for it in items if _tier_of(str(it.fspath)) == suite]
+        drop = [it for it in items if _tier_of(str(it.fspath)) != suite]
+        if drop:
+            config.hook.pytest_deselected(items=drop)
+            items[:] = keep
     try:
         import torch
         has_gpu = torch.cuda.is_available()
