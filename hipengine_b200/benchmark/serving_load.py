@@ -159,6 +159,8 @@ def main(argv: Optional[List[str]] = None) -> int:
     ap.add_argument("--tensor-parallel", type=int, default=1)
     ap.add_argument("--batch-window-ms", type=float, default=0.0)
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--gpu-sampler", action="store_true",
+                    help="sample device memory, SM clock, power and throttle reasons over NVML (read-only) during the load")
     a = ap.parse_args(argv)
     llm = server = None
     url = a.url
@@ -180,9 +182,16 @@ def main(argv: Optional[List[str]] = None) -> int:
         url = f"http://127.0.0.1:{a.port}"
     prompts = build_prompts(a.requests, vocab, a.min_prompt, a.max_prompt, a.shared_prefix, a.seed)
     arrivals = poisson_arrivals(a.requests, a.rate, a.seed)
+    sampler = None
+    if a.gpu_sampler:
+        from ..utils.nvml_sampler import NvmlSampler
+        sampler = NvmlSampler(device_index=int(os.environ.get("LOCAL_RANK", "0"))).start()
     t0 = time.perf_counter()
     recs = asyncio.run(run_load(url, a.model, prompts, arrivals, a.concurrency, a.output_tokens, a.endpoint))
     out = summarise(recs, time.perf_counter() - t0)
+    if sampler is not None:
+        sampler.stop()
+        out["gpu"] = sampler.summary()
     if llm is not None:
         try:
             snap = llm.live_loop_snapshot()

@@ -547,3 +547,50 @@ def test_log_style_formatter_load_timing_rows_and_startup_summary():
     assert sum(1 for h in logging.getLogger().handlers if getattr(h, "_he_styled", False)) == 1
     for h in [h for h in logging.getLogger().handlers if getattr(h, "_he_styled", False)]:
         logging.getLogger().removeHandler(h)
+
+
+def test_nvml_sampler_against_a_fake_nvml_reads_only():
+    """Memory / clock / power / throttle-reason sampling over an injected NVML: peaks and medians are reported, only
+    getters are ever called, and a box without a driver yields an error string instead of an exception."""
+    import time
+    from types import SimpleNamespace
+    from hipengine_b200.utils.nvml_sampler import NvmlSampler, decode_reasons
+
+    class FakeNvml:
+        def __init__(self):
+            self.calls, self.n = [], 0
+
+        def __getattr__(self, name):                       # any setter (or unknown call) would land here
+            raise AssertionError(f"unexpected NVML call {name}")
+
+        def nvmlInit(self): self.calls.append("init")
+        def nvmlShutdown(self): self.calls.append("shutdown")
+        def nvmlDeviceGetHandleByIndex(self, i): return ("h", i)
+        def nvmlDeviceGetMaxClockInfo(self, h, kind): return 1965
+
+        def nvmlDeviceGetMemoryInfo(self, h):
+            self.n += 1
+            return SimpleNamespace(used=(10 + self.n) << 30, total=180 << 30)
+
+        def nvmlDeviceGetClockInfo(self, h, kind): return 1965 if self.n % 2 else 1500
+        def nvmlDeviceGetPowerUsage(self, h): return 985000
+        def nvmlDeviceGetCurrentClocksEventReasons(self, h): return 0x4 if self.n > 1 else 0x1
+
+    fake = FakeNvml()
+    s = NvmlSampler(device_index=3, interval_s=0.01, nvml=fake).start()
+    deadline = time.time() + 5
+    while len(s.samples) < 4 and time.time() < deadline:
+        time.sleep(0.01)
+    s.stop()
+    rep = s.summary()
+    assert rep["samples"] >= 4 and rep["mem_peak_bytes"] == (10 + rep["samples"]) << 30
+    assert rep["sm_max_mhz"] == 1965 and rep["sm_min_mhz"] == 1500 and rep["power_w"] == 985.0
+    assert rep["reasons"] == ["sw_power_cap"] and rep["rejecting_reasons"] == []
+    assert fake.calls == ["init", "shutdown"]
+    assert decode_reasons(0x8 | 0x40 | 0x1) == ["hw_slowdown", "hw_thermal_slowdown"]
+
+    class NoDriver:
+        def nvmlInit(self): raise RuntimeError("driver not loaded")
+    with NvmlSampler(nvml=NoDriver()) as dead:
+        pass
+    assert dead.summary()["samples"] == 0 and "driver not loaded" in dead.summary()["error"]
