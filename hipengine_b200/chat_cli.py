@@ -16,8 +16,8 @@ import statistics
 import sys
 import time
 import urllib.request
-from dataclasses import dataclass, field
-from typing import Any, Callable, Dict, Iterable, Iterator, List, Optional, TextIO
+from dataclasses import dataclass
+from typing import Any, Dict, Iterable, Iterator, List, Optional, TextIO
 
 HELP = ("/status  readiness document      /usage  token totals           /bench [N]  N timed turns (default 3)\n"
         "/think   toggle thinking          /system TEXT  system prompt    /max N      max tokens per turn\n"

@@ -12,7 +12,6 @@ from __future__ import annotations
 import ctypes
 import os
 import threading
-from pathlib import Path
 from typing import Optional
 
 import torch

@@ -3,7 +3,7 @@ launch sequences.  The Python structs mirror ``csrc/he_cycle_abi.h`` and are siz
 from __future__ import annotations
 
 import ctypes as C
-from typing import List, Optional, Sequence, Tuple
+from typing import Optional, Sequence, Tuple
 
 from . import native as N
 

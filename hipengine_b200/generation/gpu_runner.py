@@ -10,7 +10,6 @@ prefill is split at ``snapshot_interval_tokens`` and the state is copied into a 
 """
 from __future__ import annotations
 
-import time
 from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 import torch

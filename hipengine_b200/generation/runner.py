@@ -10,7 +10,6 @@ decode graphs, paged pool, radix prefix cache with recurrent-state snapshots).
 """
 from __future__ import annotations
 
-import time
 from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 import torch

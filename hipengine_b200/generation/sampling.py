@@ -9,8 +9,7 @@ counter-based uniform, so a CPU run and a GPU run draw the same token from the s
 """
 from __future__ import annotations
 
-import math
-from typing import Dict, Iterable, List, Optional, Sequence, Tuple
+from typing import Iterable, List, Optional, Sequence, Tuple
 
 import torch
 

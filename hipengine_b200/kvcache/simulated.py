@@ -7,7 +7,7 @@ the production bookkeeping.  Reference: ``hipengine/kvcache/simulated.py:53,313`
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Sequence
+from typing import Dict, Optional, Sequence
 
 from .pool import KVLease, PagePool, PoolExhausted
 from .radix import PrefixCompatibilityKey, RadixCache

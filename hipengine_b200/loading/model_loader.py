@@ -11,8 +11,7 @@ nothing is ever downloaded (``hipengine/loading/hf_cache.py`` has the same rule)
 """
 from __future__ import annotations
 
-from pathlib import Path
-from typing import Dict, Optional
+from typing import Dict
 
 import numpy as np
 import torch

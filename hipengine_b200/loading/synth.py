@@ -10,7 +10,6 @@ existing in fp32.  ``write_gguf`` serialises the same bytes to a GGUF file.
 """
 from __future__ import annotations
 
-import math
 from pathlib import Path
 from typing import Dict, Optional
 

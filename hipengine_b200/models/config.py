@@ -9,8 +9,8 @@ geometries mirror the identities the reference pins in
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field, replace
-from typing import Any, Dict, Optional, Tuple
+from dataclasses import dataclass, replace
+from typing import Dict, Optional, Tuple
 
 
 @dataclass(frozen=True)

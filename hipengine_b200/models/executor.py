@@ -15,9 +15,8 @@ launch; above that the projections run on the tcgen05 GEMM.
 """
 from __future__ import annotations
 
-import math
 import os
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch

@@ -9,7 +9,7 @@ from __future__ import annotations
 import ctypes as C
 from dataclasses import dataclass
 import os
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import Dict, Optional, Sequence, Tuple
 
 import torch
 

@@ -15,7 +15,7 @@ import datetime
 import pickle
 import time
 from dataclasses import replace
-from typing import Any, Dict, List, Optional
+from typing import Any, Dict, Optional
 
 import torch.distributed as dist
 

@@ -15,7 +15,6 @@ is written for clarity, not speed.
 """
 from __future__ import annotations
 
-import math
 from typing import Optional, Tuple
 
 import torch

@@ -12,11 +12,10 @@ queue applies back-pressure (429 + Retry-After).
 from __future__ import annotations
 
 import asyncio
-import json
 import threading
 import time
-from dataclasses import dataclass, field
-from typing import Any, AsyncIterator, Dict, List, Optional, Tuple
+from dataclasses import dataclass
+from typing import Any, Dict, List, Optional, Tuple
 
 from fastapi import Depends, FastAPI, Request
 from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse

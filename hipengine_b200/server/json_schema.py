@@ -8,7 +8,7 @@ not, if / then / else and local ``$ref`` (``#/...``).  Unknown keywords are igno
 from __future__ import annotations
 
 import re
-from typing import Any, Dict, List, Optional
+from typing import Any, List, Optional
 
 _TYPES = {
     "object": lambda v: isinstance(v, dict),

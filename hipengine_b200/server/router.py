@@ -15,7 +15,6 @@ balancer, prefix-aware, in-tree.
 from __future__ import annotations
 
 import argparse
-import asyncio
 import hashlib
 import json
 import time

@@ -14,7 +14,7 @@ any checkpoint (no NextN block needed).  Reference counterparts: ``hipengine/spe
 from __future__ import annotations
 
 from collections import OrderedDict
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Callable, Dict, List, Optional, Sequence, Tuple
 
 

@@ -10,9 +10,8 @@ exercisable without a real vocabulary.
 """
 from __future__ import annotations
 
-import json
 import re
-from typing import Any, Dict, Iterable, List, Mapping, Optional, Sequence
+from typing import Any, Dict, List, Mapping, Optional, Sequence
 
 QWEN_SPLIT_REGEX = (r"(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}| ?[^\s\p{L}\p{N}]+[\r\n]*|"
                     r"\s*[\r\n]+|\s+(?!\S)|\s+")
