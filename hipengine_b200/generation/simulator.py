@@ -32,9 +32,14 @@ class SimulatedRunner(BaseRunner):
     def __init__(self, config: EngineConfig, vocab: int = 1024, kv_capacity_tokens: int = 1 << 20,
                  prefill_us_per_token: float = 90.0, decode_us_base: float = 8000.0, decode_us_per_row: float = 150.0,
                  fail_decode_for: Sequence[int] = (), fail_decode_admission: Sequence[int] = (),
-                 eos_token_id: Optional[int] = None):
-        """``fail_decode_for``: request ids whose next decode raises a contained failure;
-        ``fail_decode_admission``: the same, naming requests by admission order (0 = first admitted)."""
+                 eos_token_id: Optional[int] = None, spec_depth: int = 0, spec_accept_rate: float = 0.0,
+                 spec_max_requests: int = 8):
+        """``fail_decode_for``: request ids whose next decode (or speculative cycle) raises a contained failure;
+        ``fail_decode_admission``: the same, naming requests by admission order (0 = first admitted).
+        ``spec_depth`` > 0 makes the runner speculative: a cycle drafts ``spec_depth`` tokens, each draft matches the
+        true continuation with probability ``spec_accept_rate`` (a deterministic draw per request and position), and
+        the accepted prefix plus one token is emitted -- always the tokens plain decoding would have produced, so a
+        speculative run must equal a plain one (the reference's ``SpeculativeCycleSimulator`` plays this role)."""
         self.config = config
         self.vocab = vocab
         self.eos_token_id = eos_token_id
@@ -49,6 +54,10 @@ class SimulatedRunner(BaseRunner):
         self.admitted = 0
         self.free_slots = list(range(self.max_slots - 1, -1, -1))
         self.trace: List[Tuple[str, float, int]] = []
+        self.spec_depth, self.spec_accept_rate = int(spec_depth), float(spec_accept_rate)
+        self.spec_max_requests = int(spec_max_requests)
+        self.supports_mtp = self.spec_depth > 0
+        self.spec_stats = {"cycles": 0, "drafted": 0, "accepted": 0, "fallback_steps": 0}
 
     def admit(self, rs: RequestState) -> bool:
         if rs.total_budget_tokens > self.max_context:
@@ -86,6 +95,46 @@ class SimulatedRunner(BaseRunner):
         self.now_us += self.c_base + self.c_row * len(rows)
         self.trace.append(("decode", self.now_us, len(rows)))
         return [(_tok(rs.req.prompt_token_ids, len(rs.generated), self.vocab), None) for rs in rows]
+
+    # ------------------------------------------------------------------ speculative cycles
+    def speculative_eligible(self, rs: RequestState) -> bool:
+        from ..speculative.serving import resolve_mtp_serving_plan
+        return resolve_mtp_serving_plan("on", self.supports_mtp, rs.req.temperature, self._needs_processing(rs),
+                                        bool(rs.forced), bool(rs.req.logprobs), depth=self.spec_depth).use_mtp
+
+    def _draft_matches(self, rs: RequestState, index: int) -> bool:
+        h = hashlib.blake2b(repr(("draft", rs.rid, index)).encode(), digest_size=8).digest()
+        return int.from_bytes(h, "little") / 2.0 ** 64 < self.spec_accept_rate
+
+    def speculative_cycle(self, rows: List[RequestState]):
+        from ..speculative.contracts import SpecCycleResult
+        from ..speculative.policy import cycle_cost, plan_draft_depth
+        bad = [rs.rid for rs in rows if rs.rid in self.fail_decode_for]
+        if bad:
+            self.fail_decode_for -= set(bad)
+            raise ExecutionFailure(bad, "verify", "injected verify failure", "partial")
+        depth = self.spec_depth
+        for rs in rows:
+            depth = min(depth, plan_draft_depth(self.spec_depth, rs.remaining(), rs.total_budget_tokens - rs.position,
+                                                rs.telemetry.speculative_drafted, rs.telemetry.speculative_accepted,
+                                                adaptive=self.config.speculative.adaptive_depth))
+        if depth < 1 or len(rows) > self.spec_max_requests:
+            self.spec_stats["fallback_steps"] += 1
+            return [SpecCycleResult([t], 0, 0) for t, _ in self.decode(rows)]
+        self.now_us += (self.c_base + self.c_row * len(rows)) * cycle_cost(depth)
+        self.trace.append(("spec_cycle", self.now_us, len(rows)))
+        out = []
+        for rs in rows:
+            base = len(rs.generated)
+            n = 0
+            while n < depth and self._draft_matches(rs, base + n):
+                n += 1
+            toks = [_tok(rs.req.prompt_token_ids, base + i, self.vocab) for i in range(n + 1)]
+            out.append(SpecCycleResult(toks, depth, n))
+            self.spec_stats["drafted"] += depth
+            self.spec_stats["accepted"] += n
+        self.spec_stats["cycles"] += 1
+        return out
 
     def release(self, rs: RequestState) -> None:
         if rs.runner_data is not None:

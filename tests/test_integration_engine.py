@@ -205,3 +205,77 @@ def test_llm_batches_fit_context_and_speculative_plan_helpers():
             "sampler_not_reproducible", "no_nextn_block")
     finally:
         spec.close()
+
+
+def _sim_engine(spec_depth=0, accept=0.0, **kw):
+    from dataclasses import replace
+    from hipengine_b200.config import EngineConfig, SchedulerConfig, SpeculativeConfig
+    from hipengine_b200.generation.engine_service import engine_from_runner
+    from hipengine_b200.generation.simulator import SimulatedRunner
+    cfg = EngineConfig(max_sequence_length=512, scheduler=SchedulerConfig(max_active_requests=4),
+                       speculative=SpeculativeConfig(mode="mtp" if spec_depth else "off", draft_depth=max(spec_depth, 1)))
+    runner = SimulatedRunner(cfg, spec_depth=spec_depth, spec_accept_rate=accept, **kw)
+    return engine_from_runner(runner, cfg, None), runner
+
+
+@pytest.mark.parametrize("accept", [0.0, 0.6, 1.0])
+def test_speculative_cycles_on_the_simulated_runner_equal_plain_decoding(accept):
+    """The loop's speculative path on the host: multi-token commits, clipping at max_tokens, a stop sequence and an
+    EOS that fall inside a cycle, telemetry and counters -- and token-for-token equality with plain decoding."""
+    from hipengine_b200.generation.types import GenerationRequest
+    plain, _ = _sim_engine()
+    try:
+        base = plain.generate([GenerationRequest(prompt_token_ids=list(range(5, 25)), max_tokens=23, ignore_eos=True)])[0]
+    finally:
+        plain.close()
+    cont = base.token_ids
+    assert len(cont) == 23
+    reqs = lambda: [
+        GenerationRequest(prompt_token_ids=list(range(5, 25)), max_tokens=23, ignore_eos=True),
+        GenerationRequest(prompt_token_ids=list(range(5, 25)), max_tokens=7, ignore_eos=True),
+        GenerationRequest(prompt_token_ids=list(range(5, 25)), max_tokens=23, ignore_eos=True,
+                          stop_token_sequences=((cont[9], cont[10]),)),
+        GenerationRequest(prompt_token_ids=list(range(5, 25)), max_tokens=23, eos_token_id=cont[12]),
+    ]
+    plain, _ = _sim_engine()
+    try:
+        want = plain.generate(reqs())
+    finally:
+        plain.close()
+    spec, runner = _sim_engine(spec_depth=3, accept=accept)
+    try:
+        got = spec.generate(reqs())
+        for w, g in zip(want, got):
+            assert g.error is None and g.token_ids == w.token_ids and g.finish.reason == w.finish.reason
+        assert [len(g.token_ids) for g in got][:2] == [23, 7] and got[2].finish.reason == "stop"
+        assert len(got[2].token_ids) < 23 and len(got[3].token_ids) <= 13
+        full = got[0].telemetry
+        assert full.speculative_cycles >= 1 and full.speculative_drafted >= 3
+        if accept == 1.0:
+            assert full.speculative_accepted == full.speculative_drafted or full.speculative_cycles <= 7
+            assert full.speculative_cycles <= 8                    # ~4 tokens per cycle
+        if accept == 0.0:
+            assert full.speculative_accepted == 0
+        assert all(w.telemetry.speculative_cycles == 0 for w in want)
+        snap = spec.loop.snapshot()
+        assert snap["counters"]["spec_cycles"] >= 4 and runner.spec_stats["cycles"] >= 1
+    finally:
+        spec.close()
+
+
+def test_speculative_failure_is_contained_and_processed_requests_decode_step_by_step():
+    from hipengine_b200.generation.types import GenerationRequest
+    spec, runner = _sim_engine(spec_depth=3, accept=0.8, fail_decode_admission=[1])
+    try:
+        outs = spec.generate([GenerationRequest(prompt_token_ids=list(range(10 + i)), max_tokens=9, ignore_eos=True)
+                              for i in range(3)])
+        errs = [o for o in outs if o.error]
+        assert len(errs) == 1 and "execution_failed[verify/partial]" in errs[0].error
+        assert all(len(o.token_ids) == 9 for o in outs if not o.error)
+        cycles_before = runner.spec_stats["cycles"]
+        biased = spec.generate([GenerationRequest(prompt_token_ids=[1, 2, 3], max_tokens=6, ignore_eos=True,
+                                                  logit_bias=((7, 1.5),))])[0]
+        assert biased.error is None and len(biased.token_ids) == 6 and biased.telemetry.speculative_cycles == 0
+        assert runner.spec_stats["cycles"] == cycles_before         # a processed request never entered a cycle
+    finally:
+        spec.close()
