@@ -279,3 +279,33 @@ def test_speculative_failure_is_contained_and_processed_requests_decode_step_by_
         assert runner.spec_stats["cycles"] == cycles_before         # a processed request never entered a cycle
     finally:
         spec.close()
+
+
+def test_load_scenario_in_virtual_time_shows_when_drafting_pays():
+    """Virtual-time load over the simulated runner with the measured cycle costs: a high acceptance rate raises the
+    throughput, a low one is caught by the adaptive planner (drafting stops after its observation window) so that
+    it costs little."""
+    from dataclasses import replace
+    from hipengine_b200.config import EngineConfig, SchedulerConfig, SpeculativeConfig
+    from hipengine_b200.generation.simulator import SimulatedRunner, poisson_arrivals, run_load_scenario
+    from hipengine_b200.generation.types import GenerationRequest
+
+    def run(depth, accept, adaptive=True):
+        cfg = EngineConfig(max_sequence_length=2048, scheduler=SchedulerConfig(max_active_requests=4),
+                           speculative=SpeculativeConfig(mode="mtp" if depth else "off", draft_depth=max(depth, 1),
+                                                         adaptive_depth=adaptive))
+        reqs = [GenerationRequest(prompt_token_ids=list(range(3, 3 + 64 + i)), max_tokens=400, ignore_eos=True)
+                for i in range(4)]
+        runner = SimulatedRunner(cfg, spec_depth=depth, spec_accept_rate=accept)
+        res = run_load_scenario(cfg, reqs, poisson_arrivals(4, 50.0, seed=1), max_concurrent=4, runner=runner)
+        assert res.completed == 4 and res.total_tokens == 1600
+        return res.summary()["tok_per_s"], runner.spec_stats
+
+    plain, _ = run(0, 0.0)
+    good, st_good = run(3, 0.9)
+    poor, st_poor = run(3, 0.2)
+    stubborn, _ = run(3, 0.2, adaptive=False)
+    assert good > 1.25 * plain, (good, plain)
+    assert st_good["accepted"] / st_good["drafted"] > 0.8
+    assert poor > 0.85 * plain and poor > 1.3 * stubborn, (poor, plain, stubborn)
+    assert st_poor["fallback_steps"] > st_poor["cycles"]           # the planner stopped drafting
