@@ -594,3 +594,16 @@ def test_nvml_sampler_against_a_fake_nvml_reads_only():
     with NvmlSampler(nvml=NoDriver()) as dead:
         pass
     assert dead.summary()["samples"] == 0 and "driver not loaded" in dead.summary()["error"]
+
+
+def test_command_line_dispatch(capsys):
+    from hipengine_b200 import __version__, cli
+    assert cli.main(["version"]) == 0 and __version__ in capsys.readouterr().out
+    assert cli.main([]) == 0 and "serve" in capsys.readouterr().out
+    assert cli.main(["nonsense"]) == 2
+    for argv in (["bench", "serving", "--help"], ["serve", "--help"], ["chat", "--help"], ["router", "--help"],
+                 ["bench", "micro", "--help"], ["bench", "--help"]):
+        with pytest.raises(SystemExit) as ei:
+            cli.main(argv)
+        assert ei.value.code == 0, argv
+        assert "usage" in capsys.readouterr().out.lower()
