@@ -119,6 +119,17 @@ class CpuReferenceRunner(BaseRunner):
         self.max_context = min(config.max_sequence_length, self.cfg.max_context)
         self.states: Dict[int, Any] = {}
         self.last_logits: Dict[int, torch.Tensor] = {}
+        # NextN (MTP) speculative decoding on the host: the oracle of the GPU cycle (``speculative/mtp.py``).  Per
+        # request: the draft block's own KV state and the post-norm hidden of the row that produced the last token.
+        self.config = config
+        self.spec_depth = 0
+        if (config.speculative.mode == "mtp" and self.cfg.nextn_layers > 0
+                and f"blk.{self.cfg.n_layers}.nextn.eh_proj.weight" in self.model.w):
+            self.spec_depth = max(1, int(config.speculative.draft_depth))
+        self.supports_mtp = self.spec_depth > 0
+        self.draft_states: Dict[int, Any] = {}
+        self.h_prev: Dict[int, torch.Tensor] = {}
+        self.spec_stats = {"cycles": 0, "drafted": 0, "accepted": 0}
 
     def admit(self, rs: RequestState) -> bool:
         if rs.total_budget_tokens > self.max_context:
@@ -127,6 +138,9 @@ class CpuReferenceRunner(BaseRunner):
         if len(self.states) >= self.max_slots:
             return False
         self.states[rs.rid] = self.model.new_state()
+        if self.supports_mtp:
+            self.draft_states[rs.rid] = self.model.new_state()
+            self.h_prev[rs.rid] = torch.zeros(self.cfg.hidden)
         rs.slot = len(self.states) - 1
         return True
 
@@ -135,7 +149,18 @@ class CpuReferenceRunner(BaseRunner):
         out: Dict[int, Tuple[int, Optional[TokenLogprob]]] = {}
         for rs, n in work:
             toks = rs.req.prompt_token_ids[rs.prefilled:rs.prefilled + n]
-            logits, _ = self.model.forward(torch.tensor(toks, dtype=torch.long), self.states[rs.rid])
+            if self.supports_mtp:
+                # the draft block sees every prompt row: token j with the hidden of position j - 1
+                st = self.states[rs.rid]
+                pos0 = st.pos
+                hid = self.model.forward_hidden(torch.tensor(toks, dtype=torch.long), st)
+                logits = self.model.logits_from_hidden(hid)
+                for j, t in enumerate(toks):
+                    self.model.nextn_step(int(t), self.h_prev[rs.rid] if j == 0 else hid[j - 1], pos0 + j,
+                                          self.draft_states[rs.rid])
+                self.h_prev[rs.rid] = hid[-1].clone()
+            else:
+                logits, _ = self.model.forward(torch.tensor(toks, dtype=torch.long), self.states[rs.rid])
             if rs.prefilled + n >= rs.prompt_len:
                 out[rs.rid] = self.sample_host(rs, logits[-1])
         return out
@@ -144,15 +169,79 @@ class CpuReferenceRunner(BaseRunner):
     def decode(self, rows: List[RequestState]) -> List[Tuple[int, Optional[TokenLogprob]]]:
         res = []
         for rs in rows:
-            logits, _ = self.model.forward(torch.tensor([rs.last_token], dtype=torch.long), self.states[rs.rid])
+            if self.supports_mtp:
+                # keep the draft block in step on plain steps too (a request may alternate between the two paths)
+                st = self.states[rs.rid]
+                pos = st.pos
+                hid = self.model.forward_hidden(torch.tensor([rs.last_token], dtype=torch.long), st)
+                logits = self.model.logits_from_hidden(hid)
+                self._truncate_draft(rs.rid, pos)
+                self.model.nextn_step(int(rs.last_token), self.h_prev[rs.rid], pos, self.draft_states[rs.rid])
+                self.h_prev[rs.rid] = hid[-1].clone()
+            else:
+                logits, _ = self.model.forward(torch.tensor([rs.last_token], dtype=torch.long), self.states[rs.rid])
             res.append(self.sample_host(rs, logits[-1]))
         return res
 
+    # ------------------------------------------------------------------ NextN speculative cycles (greedy)
+    def speculative_eligible(self, rs: RequestState) -> bool:
+        from ..speculative.serving import resolve_mtp_serving_plan
+        d = resolve_mtp_serving_plan("on", self.supports_mtp, rs.req.temperature, self._needs_processing(rs),
+                                     bool(rs.forced), bool(rs.req.logprobs), depth=self.spec_depth)
+        return d.use_mtp and d.sampling_mode == "greedy"
+
+    def _truncate_draft(self, rid: int, n_rows: int) -> None:
+        """Positions rewind: the draft block's KV keeps the rows below ``n_rows`` only."""
+        ds = self.draft_states[rid]
+        for i in list(ds.k):
+            ds.k[i], ds.v[i] = ds.k[i][:n_rows], ds.v[i][:n_rows]
+
+    @torch.no_grad()
+    def speculative_cycle(self, rows: List[RequestState]):
+        """Draft K tokens with the NextN block, verify them with one target forward on a copy of the state, accept
+        the longest matching prefix, commit by running the accepted tokens through the live state.  The same cycle
+        as ``speculative/mtp.py::MTPCycle`` (seed = hidden of the row that produced the last token; the draft
+        block's KV below the cycle's first position is kept, the rest is rewritten by the next cycle)."""
+        from ..speculative.contracts import SpecCycleResult
+        from ..speculative.policy import plan_draft_depth
+        from ..speculative.sampling import greedy_accept
+        out = []
+        for rs in rows:
+            depth = plan_draft_depth(self.spec_depth, rs.remaining(), rs.total_budget_tokens - rs.position,
+                                     rs.telemetry.speculative_drafted, rs.telemetry.speculative_accepted,
+                                     adaptive=self.config.speculative.adaptive_depth)
+            if depth < 1:
+                tok, _ = self.decode([rs])[0]
+                out.append(SpecCycleResult([tok], 0, 0))
+                continue
+            st, rid = self.states[rs.rid], rs.rid
+            p = st.pos                                       # position of the last committed (not yet fed) token
+            self._truncate_draft(rid, p)
+            cur, hp, drafts = int(rs.last_token), self.h_prev[rid], []
+            for j in range(depth):
+                lg, hp = self.model.nextn_step(cur, hp, p + j, self.draft_states[rid])
+                cur = int(lg.argmax())
+                drafts.append(cur)
+            chain = torch.tensor([int(rs.last_token)] + drafts, dtype=torch.long)
+            target = self.model.logits_from_hidden(self.model.forward_hidden(chain, st.clone())).argmax(-1).tolist()
+            n, emitted = greedy_accept(drafts, target)
+            hid = self.model.forward_hidden(chain[:n + 1], st)          # commit: the live state advances by n + 1
+            self.h_prev[rid] = hid[n].clone()
+            out.append(SpecCycleResult([int(t) for t in emitted], depth, n))
+            self.spec_stats["cycles"] += 1
+            self.spec_stats["drafted"] += depth
+            self.spec_stats["accepted"] += n
+        return out
+
     def release(self, rs: RequestState) -> None:
         self.states.pop(rs.rid, None)
+        self.draft_states.pop(rs.rid, None)
+        self.h_prev.pop(rs.rid, None)
 
     def reset(self) -> None:
         self.states.clear()
+        self.draft_states.clear()
+        self.h_prev.clear()
 
     def capacity(self) -> Dict[str, Any]:
         return {"backend": "cpu_reference", "max_slots": self.max_slots, "max_context": self.max_context,

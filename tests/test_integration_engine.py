@@ -309,3 +309,33 @@ def test_load_scenario_in_virtual_time_shows_when_drafting_pays():
     assert st_good["accepted"] / st_good["drafted"] > 0.8
     assert poor > 0.85 * plain and poor > 1.3 * stubborn, (poor, plain, stubborn)
     assert st_poor["fallback_steps"] > st_poor["cycles"]           # the planner stopped drafting
+
+
+def test_nextn_speculative_decoding_on_the_cpu_reference_backend_equals_plain_greedy():
+    """The host oracle of the NextN cycle through the public API: same tokens as plain greedy decoding for hybrid
+    requests of different lengths, cycles and drafts in the telemetry, requests that are not eligible (sampled,
+    biased) decode step by step on the same engine with the draft block kept in step."""
+    from hipengine_b200.llm import LLM, SamplingParams
+    kw = dict(backend="cpu_reference", max_active_requests=3, max_sequence_length=128, prefix_cache="off")
+    plain = LLM("tiny-hybrid-mtp", **kw)
+    spec = LLM("tiny-hybrid-mtp", speculative_mtp_serving="on", speculative_candidate_budget=3, **kw)
+    try:
+        prompts = [list(range(7, 7 + n)) for n in (5, 19)]
+        sp = SamplingParams(max_tokens=11, ignore_eos=True)
+        a = plain.generate_detailed(prompts, sp)
+        b = spec.generate_detailed(prompts, sp)
+        for x, y in zip(a, b):
+            assert y.error is None and x.token_ids == y.token_ids and len(y.token_ids) == 11
+        assert all(o.telemetry.speculative_cycles >= 3 and o.telemetry.speculative_drafted >= 3 for o in b)
+        assert all(o.telemetry.speculative_cycles == 0 for o in a)
+        assert spec.resolve_speculative_mtp_serving_plan(sp).use_mtp
+        runner = spec._get_engine().loop.runner
+        assert runner.spec_stats["cycles"] >= 6 and not runner.states and not runner.draft_states
+        biased = SamplingParams(max_tokens=6, ignore_eos=True, logit_bias={9: 3.0})
+        assert spec.generate_detailed(prompts[:1], biased)[0].token_ids == plain.generate_detailed(prompts[:1], biased)[0].token_ids
+        cycles = runner.spec_stats["cycles"]
+        sampled = spec.generate_detailed(prompts[:1], SamplingParams(max_tokens=6, temperature=0.8, seed=5, ignore_eos=True))[0]
+        assert len(sampled.token_ids) == 6 and runner.spec_stats["cycles"] == cycles     # sampled: no host cycle
+    finally:
+        plain.close()
+        spec.close()
