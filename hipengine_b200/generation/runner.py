@@ -126,10 +126,43 @@ class CpuReferenceRunner(BaseRunner):
         if (config.speculative.mode == "mtp" and self.cfg.nextn_layers > 0
                 and f"blk.{self.cfg.n_layers}.nextn.eh_proj.weight" in self.model.w):
             self.spec_depth = max(1, int(config.speculative.draft_depth))
+        # Gemma 4: the assistant head (a separate artifact, ``config.speculative.draft_model``) drafts from the raw
+        # hidden of the row that produced the last token against the backbone's own KV (``ref/gemma4.py``)
+        self.assistant = None
+        dm = config.speculative.draft_model
+        if (config.speculative.mode in ("mtp", "gemma4_mtp") and self.cfg.arch == "gemma4"
+                and dm not in (None, "", "off")):
+            from ..loading.weights import ModelWeights
+            from ..ref.gemma4 import AssistantRef
+            if isinstance(dm, ModelWeights):
+                head_w = dm
+            elif dm == "random":
+                from ..loading.gemma4 import build_random_assistant
+                from ..models.config import NAMED_ASSISTANTS
+                acfg = next(a for a in NAMED_ASSISTANTS.values()
+                            if a.backbone_hidden == self.cfg.hidden and a.vocab == self.cfg.vocab)
+                head_w = build_random_assistant(acfg, self.cfg, seed=0)
+            else:
+                from ..loading.gemma4 import load_assistant_gguf
+                head_w = load_assistant_gguf(dm, self.cfg)
+            self.assistant = AssistantRef(head_w, self.model._gemma)
+            self.spec_depth = max(1, int(config.speculative.draft_depth))
         self.supports_mtp = self.spec_depth > 0
         self.draft_states: Dict[int, Any] = {}
         self.h_prev: Dict[int, torch.Tensor] = {}
         self.spec_stats = {"cycles": 0, "drafted": 0, "accepted": 0}
+
+    def _rows(self, toks, st):
+        """(seed rows, logits) of a forward over ``toks``: the seed of a draft is the post-norm hidden for the NextN
+        block and the raw hidden (before the output norm) for the assistant head."""
+        from ..ref import ops as R
+        t = torch.tensor(list(toks), dtype=torch.long)
+        if self.assistant is not None:
+            raw = self.model._gemma.forward_raw(t, st)
+            hid = R.rmsnorm(raw, self.model.w["output_norm.weight"], self.cfg.rms_eps)
+            return raw, self.model.logits_from_hidden(hid)
+        hid = self.model.forward_hidden(t, st)
+        return hid, self.model.logits_from_hidden(hid)
 
     def admit(self, rs: RequestState) -> bool:
         if rs.total_budget_tokens > self.max_context:
@@ -139,7 +172,8 @@ class CpuReferenceRunner(BaseRunner):
             return False
         self.states[rs.rid] = self.model.new_state()
         if self.supports_mtp:
-            self.draft_states[rs.rid] = self.model.new_state()
+            if self.assistant is None:
+                self.draft_states[rs.rid] = self.model.new_state()
             self.h_prev[rs.rid] = torch.zeros(self.cfg.hidden)
         rs.slot = len(self.states) - 1
         return True
@@ -153,11 +187,11 @@ class CpuReferenceRunner(BaseRunner):
                 # the draft block sees every prompt row: token j with the hidden of position j - 1
                 st = self.states[rs.rid]
                 pos0 = st.pos
-                hid = self.model.forward_hidden(torch.tensor(toks, dtype=torch.long), st)
-                logits = self.model.logits_from_hidden(hid)
-                for j, t in enumerate(toks):
-                    self.model.nextn_step(int(t), self.h_prev[rs.rid] if j == 0 else hid[j - 1], pos0 + j,
-                                          self.draft_states[rs.rid])
+                hid, logits = self._rows(toks, st)
+                if self.assistant is None:
+                    for j, t in enumerate(toks):
+                        self.model.nextn_step(int(t), self.h_prev[rs.rid] if j == 0 else hid[j - 1], pos0 + j,
+                                              self.draft_states[rs.rid])
                 self.h_prev[rs.rid] = hid[-1].clone()
             else:
                 logits, _ = self.model.forward(torch.tensor(toks, dtype=torch.long), self.states[rs.rid])
@@ -173,10 +207,10 @@ class CpuReferenceRunner(BaseRunner):
                 # keep the draft block in step on plain steps too (a request may alternate between the two paths)
                 st = self.states[rs.rid]
                 pos = st.pos
-                hid = self.model.forward_hidden(torch.tensor([rs.last_token], dtype=torch.long), st)
-                logits = self.model.logits_from_hidden(hid)
-                self._truncate_draft(rs.rid, pos)
-                self.model.nextn_step(int(rs.last_token), self.h_prev[rs.rid], pos, self.draft_states[rs.rid])
+                hid, logits = self._rows([rs.last_token], st)
+                if self.assistant is None:
+                    self._truncate_draft(rs.rid, pos)
+                    self.model.nextn_step(int(rs.last_token), self.h_prev[rs.rid], pos, self.draft_states[rs.rid])
                 self.h_prev[rs.rid] = hid[-1].clone()
             else:
                 logits, _ = self.model.forward(torch.tensor([rs.last_token], dtype=torch.long), self.states[rs.rid])
@@ -216,16 +250,20 @@ class CpuReferenceRunner(BaseRunner):
                 continue
             st, rid = self.states[rs.rid], rs.rid
             p = st.pos                                       # position of the last committed (not yet fed) token
-            self._truncate_draft(rid, p)
-            cur, hp, drafts = int(rs.last_token), self.h_prev[rid], []
-            for j in range(depth):
-                lg, hp = self.model.nextn_step(cur, hp, p + j, self.draft_states[rid])
-                cur = int(lg.argmax())
-                drafts.append(cur)
-            chain = torch.tensor([int(rs.last_token)] + drafts, dtype=torch.long)
-            target = self.model.logits_from_hidden(self.model.forward_hidden(chain, st.clone())).argmax(-1).tolist()
+            if self.assistant is not None:
+                # every step of a draft at the same position, against the backbone's KV as it stands
+                drafts = self.assistant.draft(int(rs.last_token), self.h_prev[rid], st, depth)
+            else:
+                self._truncate_draft(rid, p)
+                cur, hp, drafts = int(rs.last_token), self.h_prev[rid], []
+                for j in range(depth):
+                    lg, hp = self.model.nextn_step(cur, hp, p + j, self.draft_states[rid])
+                    cur = int(lg.argmax())
+                    drafts.append(cur)
+            chain = [int(rs.last_token)] + drafts
+            target = self._rows(chain, st.clone())[1].argmax(-1).tolist()
             n, emitted = greedy_accept(drafts, target)
-            hid = self.model.forward_hidden(chain[:n + 1], st)          # commit: the live state advances by n + 1
+            hid, _ = self._rows(chain[:n + 1], st)                      # commit: the live state advances by n + 1
             self.h_prev[rid] = hid[n].clone()
             out.append(SpecCycleResult([int(t) for t in emitted], depth, n))
             self.spec_stats["cycles"] += 1

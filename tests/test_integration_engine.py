@@ -339,3 +339,29 @@ def test_nextn_speculative_decoding_on_the_cpu_reference_backend_equals_plain_gr
     finally:
         plain.close()
         spec.close()
+
+
+def test_gemma4_assistant_head_speculative_decoding_on_the_cpu_reference_backend():
+    """The host oracle of the Gemma 4 assistant-head cycle through the public API: plain greedy tokens, cycles in the
+    telemetry, the head given as loaded weights."""
+    from hipengine_b200.llm import LLM, SamplingParams
+    from hipengine_b200.loading.gemma4 import build_random_assistant
+    from hipengine_b200.models.config import TINY_GEMMA4, TINY_GEMMA4_ASSISTANT
+    hw = build_random_assistant(TINY_GEMMA4_ASSISTANT, TINY_GEMMA4, seed=6, std=0.05)
+    kw = dict(backend="cpu_reference", max_active_requests=2, max_sequence_length=128, prefix_cache="off")
+    plain = LLM("tiny-gemma4", **kw)
+    spec = LLM("tiny-gemma4", speculative_mtp_serving="on", speculative_provider="gemma4_mtp", draft_model=hw,
+               speculative_candidate_budget=2, **kw)
+    try:
+        prompts = [list(range(11, 11 + n)) for n in (6, 40)]                 # the second one exceeds the window
+        sp = SamplingParams(max_tokens=7, ignore_eos=True)
+        a = plain.generate_detailed(prompts, sp)
+        b = spec.generate_detailed(prompts, sp)
+        for x, y in zip(a, b):
+            assert y.error is None and x.token_ids == y.token_ids
+        assert all(o.telemetry.speculative_cycles >= 2 and o.telemetry.speculative_drafted >= 2 for o in b)
+        runner = spec._get_engine().loop.runner
+        assert runner.assistant is not None and runner.spec_stats["cycles"] >= 4 and not runner.draft_states
+    finally:
+        plain.close()
+        spec.close()
