@@ -111,7 +111,9 @@ class CpuReferenceRunner(BaseRunner):
 
     def __init__(self, weights, config: EngineConfig, eos_token_id: Optional[int] = None):
         from ..ref.model import RefModel
-        self.model = RefModel(weights)
+        # the host backend keeps K/V exact unless INT8 storage was asked for (then every stored row goes through the
+        # per-token-and-head INT8 format, the oracle of that storage mode)
+        self.model = RefModel(weights, kv_storage="int8" if config.kv.storage == "int8" else "fp32")
         self.cfg = weights.config
         self.vocab = self.cfg.vocab
         self.eos_token_id = eos_token_id

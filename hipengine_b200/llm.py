@@ -125,9 +125,12 @@ class LLM:
         self.profile = ExecutionProfile.parse(execution_profile)
         if kv_storage in ("auto", None):
             kv_storage = "bf16"
-        if kv_storage != "bf16":
-            # the writer and both attention readers exist for bf16 pages only: refuse instead of silently storing bf16
-            raise ValueError(f"kv_storage={kv_storage!r} is not supported by this build (bf16 only)")
+        if kv_storage not in ("bf16", "int8"):
+            raise ValueError(f"kv_storage={kv_storage!r} is unknown (bf16 | int8)")
+        if kv_storage == "int8" and self.backend != "cpu_reference":
+            # the GPU writer and both attention readers exist for bf16 pages only (the INT8 format is defined and
+            # served by the host reference backend): refuse instead of silently storing bf16
+            raise ValueError("kv_storage='int8' is not supported by the cuda_sm100a backend of this build (bf16 only)")
         base = engine_config or EngineConfig.from_env()
         self.config = replace(
             base,

@@ -55,6 +55,8 @@ class Gemma4Ref:
         n_rot, theta, denom = self.rope_params(i)
         q = rope_partial_proportional(q, pos, n_rot, theta, denom)
         k_n = rope_partial_proportional(k_n, pos, n_rot, theta, denom)
+        if m.kv_storage != "fp32":
+            k_n, v = R.kv_store_roundtrip(k_n, m.kv_storage), R.kv_store_roundtrip(v, m.kv_storage)
         st.k[i] = k_n if i not in st.k else torch.cat([st.k[i], k_n], 0)
         st.v[i] = v if i not in st.v else torch.cat([st.v[i], v], 0)
         o = R.causal_gqa_attention(q, st.k[i], st.v[i], pos, 1.0, window=cfg.layer_window(i))

@@ -37,8 +37,11 @@ class RefState:
 
 
 class RefModel:
-    def __init__(self, weights: ModelWeights, dtype=torch.float32, device="cpu"):
+    def __init__(self, weights: ModelWeights, dtype=torch.float32, device="cpu", kv_storage: str = "fp32"):
+        """``kv_storage``: ``fp32`` keeps K/V exact (the oracle of the kernels), ``bf16`` / ``int8`` pass every stored
+        row through that storage format first (``ref/ops.py::kv_store_roundtrip``)."""
         self.cfg = weights.config
+        self.kv_storage = kv_storage
         self.device = torch.device(device)
         self.w: Dict[str, torch.Tensor] = {}
         for name, t in weights.tensors.items():
@@ -83,6 +86,8 @@ class RefModel:
         ks = st.k if k_store is None else k_store
         vs = st.v if v_store is None else v_store
         key = i if layer_key is None else layer_key
+        if self.kv_storage != "fp32":
+            k, v = R.kv_store_roundtrip(k, self.kv_storage), R.kv_store_roundtrip(v, self.kv_storage)
         ks[key] = k if key not in ks else torch.cat([ks[key], k], 0)
         vs[key] = v.to(torch.float32) if key not in vs else torch.cat([vs[key], v.to(torch.float32)], 0)
         o = R.causal_gqa_attention(q, ks[key], vs[key], pos, cfg.scale())

@@ -202,3 +202,33 @@ def q8_1_quantize(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     inv = torch.where(d > 0, 1.0 / d, torch.zeros_like(d))
     qv = torch.round(xb * inv[..., None]).clamp(-127, 127).to(torch.int8)
     return qv.reshape(shp), d
+
+
+# ----------------------------------------------------------------------------- INT8 KV storage (per token and head)
+def kv_int8_quantize(x: torch.Tensor, scale_dtype: torch.dtype = torch.float16) -> Tuple[torch.Tensor, torch.Tensor]:
+    """K or V rows [..., D] -> (int8 values [..., D], one scale per row in ``scale_dtype``).
+
+    Symmetric, per (token, head): ``scale = amax / 127`` rounded to the scale type FIRST, then ``q = rint(x / scale)``
+    clipped to +-127, so that a reader multiplying by the stored scale reproduces exactly what the writer meant.  This
+    is the reference's default INT8 KV format (``hipengine/kvcache/spans.py``: granularity ``per_token_head``, fp16 or
+    fp32 scales; oracle ``hipengine/kernels/cpu_reference/ops.py:1313-1910``)."""
+    xf = x.to(torch.float32)
+    amax = xf.abs().amax(-1)
+    scale = (amax / 127.0).to(scale_dtype)
+    sf = scale.to(torch.float32)
+    inv = torch.where(sf > 0, 1.0 / sf, torch.zeros_like(sf))
+    q = torch.round(xf * inv[..., None]).clamp(-127, 127).to(torch.int8)
+    return q, scale
+
+
+def kv_int8_dequantize(q: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    return q.to(torch.float32) * scale.to(torch.float32)[..., None]
+
+
+def kv_store_roundtrip(x: torch.Tensor, storage: str, scale_dtype: torch.dtype = torch.float16) -> torch.Tensor:
+    """What attention reads back after ``x`` went through the KV store: bf16 rounding, or INT8 with a per-row scale."""
+    if storage == "int8":
+        return kv_int8_dequantize(*kv_int8_quantize(x, scale_dtype))
+    if storage == "bf16":
+        return x.to(torch.bfloat16).to(torch.float32)
+    return x.to(torch.float32)

@@ -36,7 +36,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--batch-window-ms", "--generation-batch-window-ms", dest="batch_window_ms", type=float,
                     default=0.0, help="hold compatible requests up to this long so that they enter the engine together")
     ap.add_argument("--max-batch-size", type=int, default=64, help="release a held group early at this size")
-    ap.add_argument("--kv-storage", default="bf16", choices=["bf16"])
+    ap.add_argument("--kv-storage", default="bf16", choices=["bf16", "int8"],
+                    help="int8 (per token and head, fp16 scales) is served by the cpu_reference backend only")
     ap.add_argument("--kv-pool-pages", "--kv-pool-initial-pages", dest="kv_pool_pages", type=int, default=None)
     ap.add_argument("--kv-pool-memory-budget-mib", type=int, default=None,
                     help="size the KV page pool from a memory budget instead of a page count")

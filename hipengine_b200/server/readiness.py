@@ -20,7 +20,10 @@ def kv_capability(cfg, kv_cfg) -> Dict[str, Any]:
     return {
         "storage": {"bf16": {"supported": True, "evidence": "tests/test_gpu_kernels.py (paged write + decode), "
                                                              "tests/test_gpu_executor.py (end to end vs fp32)"},
-                    "int8": {"supported": False, "reason": "no int8 writer/reader kernels in this build"}},
+                    "int8": {"supported": False, "granularity": "per_token_head", "scale_dtype": "float16",
+                             "reason": "no int8 writer / reader kernels for sm_100a in this build; the format is "
+                                       "defined by ref/ops.py::kv_int8_quantize and served by the cpu_reference "
+                                       "backend only"}},
         "selected_storage": getattr(kv_cfg, "storage", "bf16"),
         "page_tokens": int(getattr(kv_cfg, "page_tokens", 16)),
         "layout": "[pages][k|v][kv_heads][page_tokens][head_dim] bf16, block table per slot",

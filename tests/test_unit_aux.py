@@ -334,8 +334,55 @@ def test_unsupported_kv_storage_is_refused_not_ignored():
     import pytest
     from hipengine_b200 import LLM
     with pytest.raises(ValueError, match="kv_storage"):
-        LLM("tiny-dense", backend="cpu_reference", kv_storage="int8")
+        LLM("tiny-dense", backend="cpu_reference", kv_storage="fp8")
     assert LLM("tiny-dense", backend="cpu_reference", kv_storage="auto").config.kv.storage == "bf16"
+    from hipengine_b200.server.readiness import kv_capability
+    from hipengine_b200.config import KVConfig
+    from hipengine_b200.models.config import TINY_DENSE
+    cap = kv_capability(TINY_DENSE, KVConfig())["storage"]
+    assert cap["bf16"]["supported"] and not cap["int8"]["supported"] and cap["int8"]["granularity"] == "per_token_head"
+
+
+def test_int8_kv_format_and_the_host_backend_that_serves_it():
+    """INT8 KV per token and head: the quantiser's error bound, exact reproduction of what the reader sees, and the
+    cpu_reference backend generating with that storage (close to exact-KV logits; the same engine API)."""
+    import torch
+    from hipengine_b200 import LLM, SamplingParams
+    from hipengine_b200.loading.synth import build_random_model
+    from hipengine_b200.models.config import TINY_HYBRID
+    from hipengine_b200.ref import ops as R
+    from hipengine_b200.ref.model import RefModel
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(7, 3, 64, generator=g) * torch.tensor([0.01, 1.0, 30.0])[None, :, None]
+    q, sc = R.kv_int8_quantize(x)
+    assert q.dtype == torch.int8 and sc.dtype == torch.float16 and sc.shape == (7, 3)
+    deq = R.kv_int8_dequantize(q, sc)
+    assert ((deq - x).abs() <= sc.float()[..., None] * 0.5 + 1e-7).all()           # half a step per element
+    assert int(q.abs().max()) == 127 and torch.equal(R.kv_store_roundtrip(x, "int8"), deq)
+    zero = torch.zeros(2, 1, 8)
+    assert torch.equal(R.kv_int8_dequantize(*R.kv_int8_quantize(zero)), zero)     # an all-zero row stays zero
+    q32, sc32 = R.kv_int8_quantize(x, torch.float32)
+    assert sc32.dtype == torch.float32 and (R.kv_int8_dequantize(q32, sc32) - x).abs().max() <= deq.sub(x).abs().max() + 1e-3
+    w = build_random_model(TINY_HYBRID, seed=3, std=0.05)
+    toks = torch.randint(0, TINY_HYBRID.vocab, (48,), generator=g)
+    exact, _ = RefModel(w).forward(toks)
+    int8, _ = RefModel(w, kv_storage="int8").forward(toks)
+    p, qq = torch.log_softmax(exact.double(), -1), torch.log_softmax(int8.double(), -1)
+    kl = (p.exp() * (p - qq)).sum(-1)
+    assert 0 < float(kl.max()) < 0.01 and (exact.argmax(-1) == int8.argmax(-1)).float().mean() > 0.9
+    llm = LLM(w, backend="cpu_reference", kv_storage="int8", max_active_requests=2, max_sequence_length=128)
+    try:
+        assert llm.config.kv.storage == "int8"
+        out = llm.generate_detailed([toks[:20].tolist()], SamplingParams(max_tokens=5, ignore_eos=True))[0]
+        assert out.error is None and len(out.token_ids) == 5
+        assert llm._get_engine().loop.runner.model.kv_storage == "int8"
+    finally:
+        llm.close()
+    import hipengine_b200.llm as L
+    if not torch.cuda.is_available():
+        return
+    with pytest.raises(ValueError, match="bf16 only"):
+        L.LLM("tiny-dense", backend="cuda_sm100a", kv_storage="int8")
 
 
 def test_decode_attention_split_policy():
