@@ -149,6 +149,12 @@ class CpuReferenceRunner(BaseRunner):
                 head_w = load_assistant_gguf(dm, self.cfg)
             self.assistant = AssistantRef(head_w, self.model._gemma)
             self.spec_depth = max(1, int(config.speculative.draft_depth))
+        # host drafters over the token history (no draft network): the same classes the GPU provider uses
+        self.lookup = None
+        if config.speculative.mode in ("prompt_lookup", "ngram"):
+            from ..speculative.providers import NGramCacheDrafter, PromptLookupDrafter
+            self.lookup = PromptLookupDrafter() if config.speculative.mode == "prompt_lookup" else NGramCacheDrafter()
+            self.spec_depth = max(1, int(config.speculative.draft_depth))
         self.supports_mtp = self.spec_depth > 0
         self.draft_states: Dict[int, Any] = {}
         self.h_prev: Dict[int, torch.Tensor] = {}
@@ -174,7 +180,7 @@ class CpuReferenceRunner(BaseRunner):
             return False
         self.states[rs.rid] = self.model.new_state()
         if self.supports_mtp:
-            if self.assistant is None:
+            if self.assistant is None and self.lookup is None:
                 self.draft_states[rs.rid] = self.model.new_state()
             self.h_prev[rs.rid] = torch.zeros(self.cfg.hidden)
         rs.slot = len(self.states) - 1
@@ -190,7 +196,7 @@ class CpuReferenceRunner(BaseRunner):
                 st = self.states[rs.rid]
                 pos0 = st.pos
                 hid, logits = self._rows(toks, st)
-                if self.assistant is None:
+                if self.assistant is None and self.lookup is None:
                     for j, t in enumerate(toks):
                         self.model.nextn_step(int(t), self.h_prev[rs.rid] if j == 0 else hid[j - 1], pos0 + j,
                                               self.draft_states[rs.rid])
@@ -210,7 +216,7 @@ class CpuReferenceRunner(BaseRunner):
                 st = self.states[rs.rid]
                 pos = st.pos
                 hid, logits = self._rows([rs.last_token], st)
-                if self.assistant is None:
+                if self.assistant is None and self.lookup is None:
                     self._truncate_draft(rs.rid, pos)
                     self.model.nextn_step(int(rs.last_token), self.h_prev[rs.rid], pos, self.draft_states[rs.rid])
                 self.h_prev[rs.rid] = hid[-1].clone()
@@ -252,7 +258,16 @@ class CpuReferenceRunner(BaseRunner):
                 continue
             st, rid = self.states[rs.rid], rs.rid
             p = st.pos                                       # position of the last committed (not yet fed) token
-            if self.assistant is not None:
+            if self.lookup is not None:
+                history = list(rs.req.prompt_token_ids) + rs.generated
+                drafts = [int(t) for t in self.lookup.propose(history, depth)]
+                if not drafts:                               # nothing repeats: a plain step is cheaper than a verify
+                    tok, _ = self.decode([rs])[0]
+                    self.lookup.observe(history + [tok])
+                    out.append(SpecCycleResult([tok], 0, 0))
+                    continue
+                depth = len(drafts)
+            elif self.assistant is not None:
                 # every step of a draft at the same position, against the backbone's KV as it stands
                 drafts = self.assistant.draft(int(rs.last_token), self.h_prev[rid], st, depth)
             else:
@@ -267,6 +282,8 @@ class CpuReferenceRunner(BaseRunner):
             n, emitted = greedy_accept(drafts, target)
             hid, _ = self._rows(chain[:n + 1], st)                      # commit: the live state advances by n + 1
             self.h_prev[rid] = hid[n].clone()
+            if self.lookup is not None:
+                self.lookup.observe(list(rs.req.prompt_token_ids) + rs.generated + [int(t) for t in emitted])
             out.append(SpecCycleResult([int(t) for t in emitted], depth, n))
             self.spec_stats["cycles"] += 1
             self.spec_stats["drafted"] += depth

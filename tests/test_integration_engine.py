@@ -365,3 +365,27 @@ def test_gemma4_assistant_head_speculative_decoding_on_the_cpu_reference_backend
     finally:
         plain.close()
         spec.close()
+
+
+@pytest.mark.parametrize("provider", ["prompt_lookup", "ngram"])
+def test_history_drafters_on_the_cpu_reference_backend(provider):
+    """prompt_lookup / ngram on the host backend: a repetitive prompt gives proposals, the accepted ones shorten the
+    run, and the tokens stay those of plain greedy decoding."""
+    from hipengine_b200.llm import LLM, SamplingParams
+    kw = dict(backend="cpu_reference", max_active_requests=2, max_sequence_length=256, prefix_cache="off")
+    plain = LLM("tiny-dense", **kw)
+    spec = LLM("tiny-dense", speculative_mtp_serving="on", speculative_provider=provider,
+               speculative_candidate_budget=3, **kw)
+    try:
+        prompts = [[5, 6, 7, 8, 9] * 6, list(range(30, 47))]
+        sp = SamplingParams(max_tokens=12, ignore_eos=True)
+        a = plain.generate_detailed(prompts, sp)
+        b = spec.generate_detailed(prompts, sp)
+        for x, y in zip(a, b):
+            assert y.error is None and x.token_ids == y.token_ids
+        runner = spec._get_engine().loop.runner
+        assert runner.lookup is not None and runner.spec_stats["cycles"] >= 1          # the repetitive prompt drafted
+        assert b[0].telemetry.speculative_drafted >= 1
+    finally:
+        plain.close()
+        spec.close()
