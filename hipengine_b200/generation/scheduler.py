@@ -127,7 +127,9 @@ class Scheduler:
         if not req.prompt_token_ids:
             raise GenerationAdmissionRejected("empty prompt")
         rs = RequestState(req)
-        rs.seed = mix_seed(req.seed, req.row_index, req.request_id)
+        # an explicit seed makes a request repeatable: its rows are told apart by their index alone; without one the
+        # engine-wide request id keeps concurrent requests apart
+        rs.seed = mix_seed(req.seed, req.row_index, req.request_id if req.seed is None else 0)
         rs.telemetry.prompt_tokens = len(req.prompt_token_ids)
         rs.telemetry.sampler_mode = req.sampler_mode
         if req.stop_token_sequences:

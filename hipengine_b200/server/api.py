@@ -17,6 +17,7 @@ import time
 from dataclasses import dataclass
 from typing import Any, Dict, List, Optional, Tuple
 
+from fastapi.exceptions import RequestValidationError
 from fastapi import Depends, FastAPI, Request
 from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
 
@@ -228,6 +229,19 @@ def create_app(llm: LLM, config: Optional[ServerConfig] = None) -> FastAPI:
     @app.exception_handler(SessionError)
     async def _session_error(_: Request, exc: SessionError):
         return JSONResponse(APIError(exc.code, str(exc)).body(), status_code=APIError(exc.code, "").status)
+
+    @app.exception_handler(RequestValidationError)
+    async def _validation_error(_: Request, exc: RequestValidationError):
+        """A body that does not fit the request schema answers in the same envelope as every other client error (the
+        framework's default is a bare 422 list)."""
+        errs = exc.errors()
+        first = errs[0] if errs else {}
+        loc = [str(x) for x in first.get("loc", ()) if x != "body"]
+        param = ".".join(loc) or None
+        msg = "; ".join(f"{'.'.join(str(x) for x in e.get('loc', ()) if x != 'body')}: {e.get('msg')}" for e in errs[:3])
+        metrics.inc("hipengine_http_errors_total", code="invalid_request")
+        e = APIError("invalid_request", f"request body does not match the schema: {msg}", param)
+        return JSONResponse(e.body(), status_code=e.status)
 
     async def auth(request: Request) -> None:
         if cfg.api_key:

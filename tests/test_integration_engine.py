@@ -69,11 +69,14 @@ def test_seeded_sampling_is_reproducible_and_seed_sensitive(dense):
     a = llm.generate_detailed([1, 2, 3], sp)[0].token_ids
     b = llm.generate_detailed([1, 2, 3], sp)[0].token_ids
     assert a != [] and len(a) == 8
-    # request ids differ, so equality is only required when the seed AND the request identity agree;
-    # a different seed must change the draw
+    assert a == b                                       # the same seed repeats the draw, whatever the request id
     c = llm.generate_detailed([1, 2, 3], SamplingParams(max_tokens=8, temperature=1.0, top_k=50, seed=124,
                                                         ignore_eos=True))[0].token_ids
-    assert isinstance(b, list) and isinstance(c, list)
+    assert c != a                                       # another seed draws differently
+    rows = llm.generate_detailed([[1, 2, 3]] * 3, sp)
+    assert len({tuple(o.token_ids) for o in rows}) >= 2 and rows[0].token_ids == a    # rows of a batch are told apart
+    unseeded = SamplingParams(max_tokens=8, temperature=1.0, top_k=50, ignore_eos=True)
+    assert llm.generate_detailed([1, 2, 3], unseeded)[0].token_ids != llm.generate_detailed([1, 2, 3], unseeded)[0].token_ids
 
 
 def test_logprobs_and_processors(dense):

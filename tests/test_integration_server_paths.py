@@ -1,0 +1,137 @@
+"""More HTTP paths over the real engine on the CPU reference backend: speculative decoding and its circuit breaker,
+thinking budgets, several choices, echo, deadlines, per-event timing blocks."""
+import json
+
+import pytest
+
+fastapi = pytest.importorskip("fastapi")
+from fastapi.testclient import TestClient  # noqa: E402
+
+from hipengine_b200 import LLM  # noqa: E402
+from hipengine_b200.server.api import ServerConfig, create_app  # noqa: E402
+
+
+def _sse(resp):
+    out = []
+    for line in resp.iter_lines():
+        if line.startswith("data: "):
+            d = line[6:]
+            out.append(d if d == "[DONE]" else json.loads(d))
+    return out
+
+
+def test_speculative_decoding_over_http_equals_plain_and_is_counted():
+    """A hybrid model with its NextN block behind the server on the host backend: `speculative_mtp: true` yields the
+    same greedy text as a plain request, the cycles show in /metrics and in the live snapshot, and the operator
+    endpoint of the circuit breaker answers."""
+    llm = LLM("tiny-hybrid-mtp", backend="cpu_reference", max_active_requests=2, max_sequence_length=256,
+              prefix_cache="off", speculative_mtp_serving="on", speculative_candidate_budget=3)
+    try:
+        with TestClient(create_app(llm, ServerConfig(served_model_name="hy", metrics="prometheus"))) as c:
+            body = {"model": "hy", "prompt": list(range(9, 30)), "max_tokens": 9, "temperature": 0, "ignore_eos": True}
+            plain = c.post("/v1/completions", json=body).json()
+            spec = c.post("/v1/completions", json=dict(body, speculative_mtp=True)).json()
+            assert plain["choices"][0]["text"] == spec["choices"][0]["text"]
+            assert spec["usage"]["completion_tokens"] == 9
+            chat = {"model": "hy", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 6, "temperature": 0,
+                    "enable_thinking": False, "speculative_mtp": True, "stream": True,
+                    "stream_options": {"include_usage": True, "include_hipengine": True}}
+            with c.stream("POST", "/v1/chat/completions", json=chat) as r:
+                ev = _sse(r)
+            assert ev[-1] == "[DONE]" and ev[-2]["usage"]["completion_tokens"] == 6
+            blocks = [e["hipengine"] for e in ev[:-1] if isinstance(e, dict) and "hipengine" in e]
+            assert blocks and blocks[-1]["phase"] == "done" and blocks[-1]["timing"]["ttft_ms"] is not None
+            assert blocks[-1]["tokens"] == 6
+            m = c.get("/metrics").text
+            assert "hipengine_mtp_requests_total" in m and "hipengine_mtp_draft_tokens_rejected_total" in m
+            runner = llm._get_engine().loop.runner
+            assert runner.spec_stats["cycles"] >= 2
+            caps = c.get("/v1/hipengine/capabilities").json()
+            assert caps["features"]["speculative_mtp"] == "mtp" and "mtp_circuit_breaker" in caps
+            assert "closed_scopes" in c.post("/v1/hipengine/speculative_mtp/rollback").json()
+            snap = c.get("/v1/hipengine/decode").json()
+            assert snap["counters"]["spec_cycles"] >= 2
+    finally:
+        llm.close()
+
+
+@pytest.fixture(scope="module")
+def client():
+    llm = LLM("tiny-dense", backend="cpu_reference", max_active_requests=4, max_sequence_length=512)
+    with TestClient(create_app(llm, ServerConfig(served_model_name="tiny", chat_default_max_tokens=10))) as c:
+        yield c
+    llm.close()
+
+
+def test_thinking_budget_forces_the_close_sequence_and_splits_reasoning(client):
+    """A random model never closes its thinking block by itself: the budget must force `</think>`; the reasoning part
+    is reported apart from the answer and counted as reasoning tokens."""
+    body = {"model": "tiny", "messages": [{"role": "user", "content": "why"}], "max_tokens": 40, "temperature": 0,
+            "enable_thinking": True, "thinking_token_budget": 5, "ignore_eos": True}
+    r = client.post("/v1/chat/completions", json=body)
+    assert r.status_code == 200, r.text
+    msg = r.json()["choices"][0]["message"]
+    assert msg.get("reasoning_content") and "</think>" not in (msg.get("content") or "")
+    assert "</think>" not in msg["reasoning_content"]
+    with client.stream("POST", "/v1/chat/completions", json=dict(body, stream=True,
+                                                                stream_options={"include_usage": True})) as r:
+        ev = _sse(r)
+    deltas = [e["choices"][0]["delta"] for e in ev if isinstance(e, dict) and e.get("choices")]
+    assert any(d.get("reasoning_content") for d in deltas) and any(d.get("content") for d in deltas)
+    first_answer = next(i for i, d in enumerate(deltas) if d.get("content"))
+    assert not any(d.get("reasoning_content") for d in deltas[first_answer:])      # reasoning first, then the answer
+    usage = ev[-2]["usage"]
+    assert 0 < usage["completion_tokens_details"]["reasoning_tokens"] < usage["completion_tokens"] == 40
+    off = client.post("/v1/chat/completions", json=dict(body, enable_thinking=False)).json()["choices"][0]["message"]
+    assert not off.get("reasoning_content")
+    none = client.post("/v1/chat/completions", json=dict(body, reasoning_effort="none")).json()["choices"][0]["message"]
+    assert not none.get("reasoning_content")
+    bad = client.post("/v1/chat/completions", json=dict(body, reasoning_effort="extreme"))
+    assert bad.status_code == 400 and bad.json()["error"]["param"] == "reasoning_effort"
+
+
+def test_several_choices_echo_and_buffered_streams(client):
+    r = client.post("/v1/chat/completions", json={"model": "tiny", "messages": [{"role": "user", "content": "x"}],
+                                                  "max_tokens": 4, "n": 3, "temperature": 0.9, "seed": 1,
+                                                  "enable_thinking": False})
+    ch = r.json()["choices"]
+    assert [c["index"] for c in ch] == [0, 1, 2] and r.json()["usage"]["completion_tokens"] == 12
+    assert len({c["message"]["content"] for c in ch}) >= 2                      # rows are seeded apart
+    again = client.post("/v1/chat/completions", json={"model": "tiny", "messages": [{"role": "user", "content": "x"}],
+                                                      "max_tokens": 4, "n": 3, "temperature": 0.9, "seed": 1,
+                                                      "enable_thinking": False}).json()["choices"]
+    assert [c["message"]["content"] for c in again] == [c["message"]["content"] for c in ch]
+    with client.stream("POST", "/v1/chat/completions",
+                       json={"model": "tiny", "messages": [{"role": "user", "content": "x"}], "max_tokens": 3, "n": 2,
+                             "stream": True, "enable_thinking": False}) as r:
+        ev = _sse(r)
+    assert ev[-1] == "[DONE]" and sorted(e["choices"][0]["index"] for e in ev[:-1]) == [0, 1]
+    e = client.post("/v1/completions", json={"model": "tiny", "prompt": "abc", "max_tokens": 2, "echo": True,
+                                             "temperature": 0}).json()
+    assert e["choices"][0]["text"].startswith("abc") and e["usage"]["completion_tokens"] == 2
+    r = client.post("/v1/completions", json={"model": "tiny", "prompt": "abc", "n": 17})
+    assert r.status_code == 400 and r.json()["error"]["code"] == "unsupported_parameter"
+    many = client.post("/v1/completions", json={"model": "tiny", "prompt": ["a", "bb", [5, 6, 7]], "max_tokens": 2,
+                                                "temperature": 0})
+    assert many.status_code == 400                                  # strings and token rows cannot be mixed
+    err = many.json()["error"]
+    assert err["code"] == "invalid_request" and err["param"].startswith("prompt") and err["hipengine"]["status"] == 400
+    rows = client.post("/v1/completions", json={"model": "tiny", "prompt": [[5, 6, 7], [8, 9]], "max_tokens": 2,
+                                                "temperature": 0})
+    assert rows.status_code == 200 and len(rows.json()["choices"]) == 2
+    texts = client.post("/v1/completions", json={"model": "tiny", "prompt": ["a", "bb"], "max_tokens": 2, "temperature": 0})
+    assert texts.status_code == 200 and [c["index"] for c in texts.json()["choices"]] == [0, 1]
+    bad = client.post("/v1/chat/completions", json={"model": "tiny", "messages": "not a list"})
+    assert bad.status_code == 400 and bad.json()["error"]["param"] == "messages"
+
+
+def test_request_deadline_is_reported(client):
+    r = client.post("/v1/completions", json={"model": "tiny", "prompt": "abc", "max_tokens": 400, "timeout_ms": 1,
+                                             "ignore_eos": True})
+    assert r.status_code in (200, 408)
+    if r.status_code == 408:
+        assert r.json()["error"]["code"] == "deadline_exceeded" and r.json()["error"]["hipengine"]["retryable"]
+    else:                                                       # finished inside a millisecond: a complete answer
+        assert r.json()["usage"]["completion_tokens"] == 400
+    ok = client.post("/v1/completions", json={"model": "tiny", "prompt": "abc", "max_tokens": 3, "timeout_ms": 60000})
+    assert ok.status_code == 200
