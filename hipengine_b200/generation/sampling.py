@@ -24,7 +24,8 @@ def splitmix64(z: int) -> int:
 
 
 def mix_seed(seed: Optional[int], row_index: int, request_id: int) -> int:
-    """Deterministic per-row seed; ``None`` seeds still separate rows and requests."""
+    """Deterministic per-row seed; ``None`` seeds still separate rows and requests.  The scheduler passes request id
+    0 for an explicitly seeded request, so that the same seed repeats the same draws in another request."""
     base = 0x5DEECE66D if seed is None else int(seed) & MASK64
     return splitmix64(splitmix64(base ^ (row_index * 0x9E3779B97F4A7C15 & MASK64)) ^ (request_id & MASK64))
 
