@@ -151,7 +151,10 @@ class Scheduler:
                     rs.grammar = tool_call_matcher(
                         _json.loads(spec.tools_json), self.tokenizer,
                         req.eos_token_id if req.eos_token_id is not None else self.eos_token_id,
-                        allow_text_before=True, parallel=True,
+                        # the definitions travel only when the tool choice demands a call (required / a named
+                        # function): then nothing but calls is admitted -- free text first would let a model that
+                        # does not want to call talk forever
+                        allow_text_before=False, parallel=True,
                         only=spec.specific if spec.mode == "specific" else None)
                 except ValueError:
                     rs.grammar = None        # names the grammar cannot express: post-validation still applies

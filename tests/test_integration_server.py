@@ -121,7 +121,11 @@ def test_tools_required_not_satisfied(client):
     r = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "time?"}], "tools": tools,
                                                   "tool_choice": "required", "max_tokens": 4, "temperature": 0,
                                                   "enable_thinking": False})
-    assert r.json()["choices"][0]["finish_details"]["reason"] == "tool_required_not_satisfied"
+    # four tokens cannot hold a call: the grammar-forced opening is cut off by the length limit, which is reported as
+    # an unsatisfied requirement or as an invalid (unterminated) call, never as a successful one
+    ch = r.json()["choices"][0]
+    assert ch["finish_details"]["reason"] in ("tool_required_not_satisfied", "invalid_tool_call")
+    assert ch["finish_reason"] == "length" and not ch["message"].get("tool_calls")
     r = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "x"}], "tools": tools,
                                                   "tool_choice": {"type": "function", "function": {"name": "nope"}}})
     assert r.status_code == 400

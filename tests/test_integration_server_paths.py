@@ -135,3 +135,44 @@ def test_request_deadline_is_reported(client):
         assert r.json()["usage"]["completion_tokens"] == 400
     ok = client.post("/v1/completions", json={"model": "tiny", "prompt": "abc", "max_tokens": 3, "timeout_ms": 60000})
     assert ok.status_code == 200
+
+
+@pytest.fixture(scope="module")
+def wide_client():
+    llm = LLM("tiny-dense", backend="cpu_reference", max_active_requests=2, max_sequence_length=1024)
+    with TestClient(create_app(llm, ServerConfig(served_model_name="tiny"))) as c:
+        yield c
+    llm.close()
+
+
+def test_required_tool_call_over_http_is_parsed_and_streamed(wide_client):
+    """A parameterless tool under `tool_choice: required`: the grammar leaves one possible text, which a random model
+    then has to produce; the server parses it into `tool_calls` (blocking) and `delta.tool_calls` (streaming)."""
+    client = wide_client
+    tools = [{"type": "function", "function": {"name": "get_time", "parameters": {"type": "object"}}}]
+    body = {"model": "tiny", "messages": [{"role": "user", "content": "time?"}], "tools": tools,
+            "tool_choice": "required", "max_tokens": 120, "temperature": 0.7, "seed": 3, "enable_thinking": False}
+    r = client.post("/v1/chat/completions", json=body)
+    assert r.status_code == 200, r.text
+    ch = r.json()["choices"][0]
+    assert ch["finish_reason"] == "tool_calls", ch
+    call = ch["message"]["tool_calls"][0]
+    assert call["type"] == "function" and call["function"]["name"] == "get_time" and call["id"]
+    assert json.loads(call["function"]["arguments"]) == {} and ch["message"]["content"] is None
+    with client.stream("POST", "/v1/chat/completions", json=dict(body, stream=True)) as resp:
+        ev = _sse(resp)
+    deltas = [e["choices"][0] for e in ev if isinstance(e, dict) and e.get("choices")]
+    calls = [tc for d in deltas for tc in (d["delta"].get("tool_calls") or [])]
+    by_index = {}
+    for tc in calls:
+        by_index.setdefault(tc["index"], []).append(tc)
+    assert sorted(by_index) == list(range(len(by_index))) and by_index       # parallel calls get consecutive indices
+    for parts in by_index.values():
+        assert parts[0]["function"]["name"] == "get_time" and parts[0]["type"] == "function"   # the name comes first
+        assert len({p["id"] for p in parts}) == 1                             # one id for all chunks of a call
+        assert json.loads("".join(p["function"].get("arguments", "") for p in parts)) == {}
+    assert deltas[-1]["finish_reason"] == "tool_calls"
+    named = dict(body, tool_choice={"type": "function", "function": {"name": "get_time"}})
+    assert client.post("/v1/chat/completions", json=named).json()["choices"][0]["finish_reason"] == "tool_calls"
+    none = client.post("/v1/chat/completions", json=dict(body, tool_choice="none", max_tokens=5)).json()["choices"][0]
+    assert none["finish_reason"] in ("length", "stop") and not none["message"].get("tool_calls")
