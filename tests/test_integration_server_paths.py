@@ -176,3 +176,38 @@ def test_required_tool_call_over_http_is_parsed_and_streamed(wide_client):
     assert client.post("/v1/chat/completions", json=named).json()["choices"][0]["finish_reason"] == "tool_calls"
     none = client.post("/v1/chat/completions", json=dict(body, tool_choice="none", max_tokens=5)).json()["choices"][0]
     assert none["finish_reason"] in ("length", "stop") and not none["message"].get("tool_calls")
+
+
+def test_stop_strings_logit_bias_choice_and_refused_parameters(client):
+    base = {"model": "tiny", "prompt": "abc", "max_tokens": 12, "temperature": 0, "ignore_eos": True}
+    full = client.post("/v1/completions", json=base).json()["choices"][0]
+    assert full["finish_reason"] == "length"
+    # stop strings are lowered to token sequences: one made of forced byte tokens ends the text before it
+    z = client.post("/v1/hipengine/tokenize", json={"text": "Z"}).json()["tokens"][0]
+    r = client.post("/v1/completions", json=dict(base, logit_bias={str(z): 100}, stop=["ZZZ"])).json()["choices"][0]
+    assert r["finish_reason"] == "stop" and r["text"] == ""
+    # a large bias on one token makes the greedy continuation that token
+    tok = client.post("/v1/hipengine/tokenize", json={"text": "Z"}).json()["tokens"][0]
+    biased = client.post("/v1/completions", json=dict(base, max_tokens=4, logit_bias={str(tok): 100})).json()
+    assert biased["choices"][0]["text"] == "ZZZZ"
+    bad = client.post("/v1/completions", json=dict(base, logit_bias={"not-a-token": 1}))
+    assert bad.status_code == 400
+    # guided_choice validates the result: a random model does not answer with one of the choices
+    chat = {"model": "tiny", "messages": [{"role": "user", "content": "pick"}], "max_tokens": 4, "temperature": 0,
+            "enable_thinking": False}
+    g = client.post("/v1/chat/completions", json=dict(chat, guided_choice=["yes", "no"])).json()["choices"][0]
+    assert g["finish_details"]["reason"] == "schema_violation"
+    ok = client.post("/v1/chat/completions", json=dict(chat, max_tokens=3, guided_choice=["yes", "no"],
+                                                       logit_bias={str(client.post("/v1/hipengine/tokenize", json={"text": "n"}).json()["tokens"][0]): 100}))
+    assert ok.status_code == 200
+    # refused before generation
+    for extra, param in (({"grammar": "root ::= 'a'"}, "grammar"), ({"guided_grammar": "x"}, "grammar"),
+                         ({"response_format": {"type": "yaml"}}, "response_format"),
+                         ({"guided_regex": "("}, "guided_regex"), ({"top_logprobs": 3}, "top_logprobs"),
+                         ({"logprobs": True, "top_logprobs": 21}, "top_logprobs")):
+        r = client.post("/v1/chat/completions", json=dict(chat, **extra))
+        assert r.status_code == 400 and r.json()["error"]["param"] == param, (extra, r.text)
+    lp = client.post("/v1/chat/completions", json=dict(chat, logprobs=True, top_logprobs=2)).json()["choices"][0]
+    assert len(lp["logprobs"]["content"]) == 4 and len(lp["logprobs"]["content"][0]["top_logprobs"]) == 2
+    t = client.post("/v1/hipengine/tokenize", json={"messages": [{"role": "user", "content": "hi"}]}).json()
+    assert t["count"] > 2 and client.post("/v1/hipengine/count_tokens", json={"text": "hello"}).json()["count"] == 5
