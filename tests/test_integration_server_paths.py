@@ -211,3 +211,39 @@ def test_stop_strings_logit_bias_choice_and_refused_parameters(client):
     assert len(lp["logprobs"]["content"]) == 4 and len(lp["logprobs"]["content"][0]["top_logprobs"]) == 2
     t = client.post("/v1/hipengine/tokenize", json={"messages": [{"role": "user", "content": "hi"}]}).json()
     assert t["count"] > 2 and client.post("/v1/hipengine/count_tokens", json={"text": "hello"}).json()["count"] == 5
+
+
+def test_full_queue_answers_429_with_retry_after():
+    import threading
+    import time
+    llm = LLM("tiny-dense", backend="cpu_reference", max_active_requests=2, max_sequence_length=1024)
+    try:
+        with TestClient(create_app(llm, ServerConfig(served_model_name="tiny", max_queued_requests=1))) as c:
+            c.post("/v1/completions", json={"model": "tiny", "prompt": "warm", "max_tokens": 2})      # engine resident
+            done = {}
+
+            def long_one():
+                done["r"] = c.post("/v1/completions", json={"model": "tiny", "prompt": "abc", "max_tokens": 500,
+                                                            "ignore_eos": True, "temperature": 0})
+            t = threading.Thread(target=long_one)
+            t.start()
+            time.sleep(0.15)                      # the long request is inside the gate before the probes start
+            busy = None
+            deadline = time.time() + 10
+            while time.time() < deadline and t.is_alive():
+                r = c.post("/v1/completions", json={"model": "tiny", "prompt": "x", "max_tokens": 1})
+                if r.status_code == 429:
+                    busy = r
+                    break
+                time.sleep(0.005)
+            t.join(timeout=60)
+            assert done["r"].status_code == 200 and done["r"].json()["usage"]["completion_tokens"] == 500
+            assert busy is not None, "the second request was never refused while the first one ran"
+            assert busy.json()["error"]["code"] == "engine_busy" and int(busy.headers["Retry-After"]) >= 1
+            assert busy.json()["error"]["hipengine"]["retryable"] is True
+            after = c.post("/v1/completions", json={"model": "tiny", "prompt": "x", "max_tokens": 1})
+            assert after.status_code == 200                                     # the queue has room again
+            ready = c.get("/ready").json()
+            assert ready["batcher"]["rejected_busy"] >= 1 and ready["batcher"]["in_flight"] == 0
+    finally:
+        llm.close()
