@@ -654,3 +654,30 @@ def test_command_line_dispatch(capsys):
             cli.main(argv)
         assert ei.value.code == 0, argv
         assert "usage" in capsys.readouterr().out.lower()
+
+
+def test_scheduler_policies_trade_first_token_latency_against_decode_smoothness():
+    """Under a burst of long prompts arriving while others decode, `protect_ttft` must reach first tokens sooner and
+    `protect_decode` must keep the inter-token latency tail lower; every policy produces the same tokens."""
+    import random
+
+    def run(policy, **kw):
+        cfg = EngineConfig(max_sequence_length=8192,
+                           scheduler=SchedulerConfig(policy=policy, max_active_requests=16, max_pending_requests=256,
+                                                     max_prefill_chunk_tokens=1024, round_prefill_token_budget=1024,
+                                                     **kw),
+                           kv=KVConfig(prefix_cache="off"))
+        rng = random.Random(5)
+        reqs = [GenerationRequest(prompt_token_ids=[rng.randrange(1000) for _ in range(rng.randrange(1500, 4000))],
+                                  max_tokens=96, ignore_eos=True) for _ in range(24)]
+        res = run_load_scenario(cfg, reqs, poisson_arrivals(24, rate_per_s=12.0, seed=2), max_concurrent=16)
+        assert res.completed == 24 and res.total_tokens == 24 * 96
+        return res.summary()
+
+    dec, ttft = run("protect_decode"), run("protect_ttft")
+    fair, budget = run("fair", fair_prefill_burst_chunks=2), run("token_budget", round_decode_row_budget=8)
+    assert ttft["ttft_p50_ms"] < dec["ttft_p50_ms"], (ttft, dec)
+    assert dec["itl_p99_ms"] <= ttft["itl_p99_ms"], (dec, ttft)
+    for s in (fair, budget):
+        assert s["tokens"] == dec["tokens"] and s["ttft_p99_ms"] > 0 and s["itl_p50_ms"] > 0
+    assert min(dec["ttft_p50_ms"], ttft["ttft_p50_ms"]) <= fair["ttft_p50_ms"] <= max(dec["ttft_p99_ms"], ttft["ttft_p99_ms"])
