@@ -330,7 +330,17 @@ def create_app(llm: LLM, config: Optional[ServerConfig] = None) -> FastAPI:
                              "thinking_controls": True, "prefix_cache": llm.config.kv.prefix_cache,
                              "speculative_mtp": llm.config.speculative.mode, "sessions": True},
                 "limits": {"max_queued_requests": cfg.max_queued_requests, "top_logprobs": 20, "n": 16},
-                "mtp_circuit_breaker": breaker.snapshot()}
+                "mtp_circuit_breaker": breaker.snapshot(), "model_family": _family()}
+
+    def _family() -> Optional[Dict[str, Any]]:
+        """The served family's declaration (layer schedule, block types read in place, providers, KV storage)."""
+        from ..models.registry import plugin_for
+        w = getattr(llm, "_weights", None)
+        mcfg = getattr(w, "config", None) or getattr(getattr(llm, "model", None), "cfg", None)
+        try:
+            return plugin_for(arch()).describe(mcfg)
+        except KeyError:
+            return None
 
     @app.get("/v1/hipengine/decode", dependencies=[Depends(auth)])
     async def decode_state():

@@ -681,3 +681,22 @@ def test_scheduler_policies_trade_first_token_latency_against_decode_smoothness(
     for s in (fair, budget):
         assert s["tokens"] == dec["tokens"] and s["ttft_p99_ms"] > 0 and s["itl_p50_ms"] > 0
     assert min(dec["ttft_p50_ms"], ttft["ttft_p50_ms"]) <= fair["ttft_p50_ms"] <= max(dec["ttft_p99_ms"], ttft["ttft_p99_ms"])
+
+
+def test_model_family_declarations_cover_the_loader_and_describe_a_geometry():
+    from hipengine_b200.loading.model_loader import SUPPORTED_ARCHS
+    from hipengine_b200.models.config import GEMMA4_26B_A4B, NAMED_CONFIGS, QWEN35_27B
+    from hipengine_b200.models.registry import plugin_for, supported_architectures
+    assert sorted(SUPPORTED_ARCHS) == supported_architectures()            # every loadable architecture is declared
+    d = plugin_for("qwen35").describe(QWEN35_27B)
+    assert d["layers"] == {"full": 16, "linear": 48} and d["ffn"] == "dense" and "mtp" not in d["speculative_providers"]
+    assert "mtp" in plugin_for("qwen35").describe(NAMED_CONFIGS["qwen35-27b-mtp"])["speculative_providers"]
+    g = plugin_for("gemma4").describe(GEMMA4_26B_A4B)
+    assert g["layers"] == {"global": 5, "sliding": 25} and g["ffn"] == "moe" and g["chat_template"] == "gemma"
+    assert "gemma4_mtp" in g["speculative_providers"] and g["tensor_parallel"] is False
+    with pytest.raises(KeyError, match="supported"):
+        plugin_for("mamba")
+    import importlib
+    for arch in supported_architectures():
+        mod, cls = plugin_for(arch).executor.rsplit(".", 1)
+        assert hasattr(importlib.import_module(mod), cls)
