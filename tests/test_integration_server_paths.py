@@ -247,3 +247,18 @@ def test_full_queue_answers_429_with_retry_after():
             assert ready["batcher"]["rejected_busy"] >= 1 and ready["batcher"]["in_flight"] == 0
     finally:
         llm.close()
+
+
+def test_serving_load_harness_runs_against_its_own_server_on_the_host_backend(capsys):
+    """The Poisson load generator end to end: it brings up the server in a thread, drives it over real sockets and
+    prints one JSON line; with speculative decoding on the host backend the server block reports the cycles."""
+    from hipengine_b200.benchmark.serving_load import main
+    rc = main(["--model", "tiny-hybrid-mtp", "--backend", "cpu_reference", "--requests", "5", "--concurrency", "2",
+               "--rate", "40", "--min-prompt", "12", "--max-prompt", "40", "--shared-prefix", "4", "--output-tokens", "6",
+               "--max-active", "2", "--port", "18997", "--mtp", "on", "--mtp-depth", "2", "--endpoint", "chat",
+               "--gpu-sampler"])
+    assert rc == 0
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert out["completed"] == 5 and out["failed"] == 0 and out["generated_tok_per_s"] > 0
+    assert out["ttft_p50_ms"] > 0 and out["config"]["endpoint"] == "chat" and out["config"]["mtp"] == "on"
+    assert "gpu" in out and ("error" in out["gpu"] or out["gpu"]["samples"] >= 0)
