@@ -700,3 +700,15 @@ def test_model_family_declarations_cover_the_loader_and_describe_a_geometry():
     for arch in supported_architectures():
         mod, cls = plugin_for(arch).executor.rsplit(".", 1)
         assert hasattr(importlib.import_module(mod), cls)
+
+
+def test_server_entry_point_prints_its_resolved_configuration(capsys):
+    import json
+    from hipengine_b200.server.__main__ import main
+    rc = main(["--model", "tiny-dense", "--info", "--kv-storage", "int8", "--prefill-decode-policy", "fair",
+               "--max-active-requests", "3", "--batch-window-ms", "1.5", "--speculative-mtp-serving", "auto",
+               "--mtp-hot-vocab", "auto", "--log-color", "never"])
+    assert rc == 0
+    doc = json.loads(capsys.readouterr().out)
+    assert doc["engine"]["kv"]["storage"] == "int8" and doc["engine"]["scheduler"]["policy"] == "fair"
+    assert doc["engine"]["scheduler"]["max_active_requests"] == 3 and doc["server"]["batch_window_ms"] == 1.5
