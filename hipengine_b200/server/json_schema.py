@@ -139,22 +139,52 @@ def validate(instance: Any, schema: Any, root: Optional[Any] = None, path: str =
     return errs
 
 
+# keywords that constrain instances and that ``validate`` does not implement: ignoring them would accept outputs the
+# caller's schema forbids, so a schema using them is refused
+UNSUPPORTED_KEYWORDS = ("patternProperties", "propertyNames", "dependentRequired", "dependentSchemas", "dependencies",
+                        "contains", "minContains", "maxContains", "unevaluatedProperties", "unevaluatedItems",
+                        "$dynamicRef", "$recursiveRef", "contentEncoding", "contentMediaType", "contentSchema")
+_SCHEMA_MAPS = ("properties", "$defs", "definitions")
+_SCHEMA_SINGLE = ("items", "additionalProperties", "not", "if", "then", "else")
+_SCHEMA_LISTS = ("allOf", "anyOf", "oneOf", "prefixItems")
+
+
 def check_schema(schema: Any) -> None:
-    """Reject schemas this validator cannot honour (raises ``SchemaError``)."""
-    def walk(node: Any) -> None:
-        if isinstance(node, dict):
-            if "$ref" in node:
-                _resolve(schema, node["$ref"])
-            if "pattern" in node:
-                try:
-                    re.compile(node["pattern"])
-                except re.error as exc:
-                    raise SchemaError(f"bad pattern: {exc}") from None
-            for v in node.values():
-                walk(v)
-        elif isinstance(node, list):
-            for v in node:
-                walk(v)
+    """Reject schemas this validator cannot honour (raises ``SchemaError``): a non-local ``$ref`` or one that does not
+    resolve, a pattern that does not compile, an unknown type name, a constraining keyword outside the subset.  The
+    walk follows the positions where JSON Schema puts subschemas, so a *property* that happens to be called
+    ``contains`` or ``type`` is not mistaken for a keyword."""
+    def walk(node: Any, where: str) -> None:
+        if isinstance(node, bool):
+            return
+        if not isinstance(node, dict):
+            raise SchemaError(f"{where}: a schema must be an object or a boolean")
+        for k in UNSUPPORTED_KEYWORDS:
+            if k in node:
+                raise SchemaError(f"{where}: keyword {k!r} is not supported")
+        if "$ref" in node:
+            _resolve(schema, node["$ref"])
+        if "pattern" in node:
+            try:
+                re.compile(node["pattern"])
+            except (re.error, TypeError) as exc:
+                raise SchemaError(f"{where}: bad pattern: {exc}") from None
+        if "type" in node:
+            types = node["type"] if isinstance(node["type"], list) else [node["type"]]
+            for t in types:
+                if t not in _TYPES:
+                    raise SchemaError(f"{where}: unknown type {t!r}")
+        for k in _SCHEMA_MAPS:
+            if isinstance(node.get(k), dict):
+                for name, sub in node[k].items():
+                    walk(sub, f"{where}/{k}/{name}")
+        for k in _SCHEMA_SINGLE:
+            if k in node:
+                walk(node[k], f"{where}/{k}")
+        for k in _SCHEMA_LISTS:
+            if isinstance(node.get(k), list):
+                for n, sub in enumerate(node[k]):
+                    walk(sub, f"{where}/{k}/{n}")
     if not isinstance(schema, (dict, bool)):
         raise SchemaError("schema must be an object or boolean")
-    walk(schema)
+    walk(schema, "#")
