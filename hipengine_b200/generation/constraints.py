@@ -64,6 +64,89 @@ class ForcedTokenQueue:
             self.reason = reason
 
 
+_LITERALS = ("true", "false", "null")
+
+
+def json_closing_suffix(text: str) -> str:
+    """Suffix that completes ``text``, a prefix of a JSON document, into a parseable one.
+
+    One pass over the characters keeps, per open container, what is expected next (object: key / colon / value /
+    comma-or-end; array: value / comma-or-end) and whether a string, a literal or a number is in progress."""
+    stack: List[List[str]] = []            # [kind "{" or "[", state]
+    in_str = esc = False
+    str_is_key = False
+    scalar = ""                            # literal or number in progress
+
+    def value_done() -> None:
+        if stack:
+            stack[-1][1] = "comma"
+
+    for ch in text:
+        if in_str:
+            if esc:
+                esc = False
+            elif ch == "\\":
+                esc = True
+            elif ch == '"':
+                in_str = False
+                if str_is_key:
+                    stack[-1][1] = "colon"
+                else:
+                    value_done()
+            continue
+        if scalar:
+            if ch in "+-.0123456789eEtrufalsn" and not ch.isspace():
+                scalar += ch
+                continue
+            scalar = ""
+            value_done()
+        if ch.isspace():
+            continue
+        if ch == '"':
+            in_str = True
+            str_is_key = bool(stack) and stack[-1][0] == "{" and stack[-1][1] in ("key", "key_or_end")
+        elif ch == "{":
+            stack.append(["{", "key_or_end"])
+        elif ch == "[":
+            stack.append(["[", "value_or_end"])
+        elif ch in "}]":
+            if stack:
+                stack.pop()
+            value_done()
+        elif ch == ":":
+            if stack:
+                stack[-1][1] = "value"
+        elif ch == ",":
+            if stack:
+                stack[-1][1] = "key" if stack[-1][0] == "{" else "value"
+        else:
+            scalar = ch
+    out = ""
+    if in_str:
+        if esc:
+            out += "\\"                   # a lone backslash would escape the closing quote
+        out += '"'
+        if str_is_key:
+            out += ": null"
+    elif scalar:
+        lit = next((l for l in _LITERALS if l.startswith(scalar)), None)
+        if lit is not None:
+            out += lit[len(scalar):]
+        elif scalar[-1] in "+-.eE":
+            out += "0"
+    for depth in range(len(stack) - 1, -1, -1):
+        kind, state = stack[depth]
+        if depth == len(stack) - 1 and not in_str and not scalar:
+            if state == "colon":
+                out += ": null"
+            elif state == "value":
+                out += " null"
+            elif state == "key":
+                out += ' "_": null'        # after a trailing comma an object needs one more member
+        out += "}" if kind == "{" else "]"
+    return out
+
+
 class JsonObjectConstraintState:
     """Tracks whether the decoded text so far is a prefix of one JSON object and when it is complete.
 
@@ -89,30 +172,10 @@ class JsonObjectConstraintState:
                 pass
 
     def closing_suffix(self) -> str:
-        """Shortest suffix that closes open strings / arrays / objects of the current text."""
-        text = self.decode(self.ids)
-        stack: List[str] = []
-        in_str = esc = False
-        for ch in text:
-            if in_str:
-                if esc:
-                    esc = False
-                elif ch == "\\":
-                    esc = True
-                elif ch == '"':
-                    in_str = False
-                continue
-            if ch == '"':
-                in_str = True
-            elif ch in "{[":
-                stack.append("}" if ch == "{" else "]")
-            elif ch in "}]" and stack:
-                stack.pop()
-        out = '"' if in_str else ""
-        stripped = text.rstrip()
-        if not in_str and stripped.endswith((",", ":")):
-            out += " null" if stripped.endswith(":") else ""
-        return out + "".join(reversed(stack))
+        """Shortest suffix that makes the current text (a prefix of one JSON object) parse: closes an open string,
+        completes a cut literal or number, supplies the value a key or a colon is waiting for, drops into ``null``
+        after a trailing comma, and closes the open arrays / objects."""
+        return json_closing_suffix(self.decode(self.ids))
 
     def forced_close_tokens(self) -> List[int]:
         if not self.decode(self.ids).strip():
