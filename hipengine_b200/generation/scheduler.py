@@ -276,9 +276,11 @@ class Scheduler:
             rs.stop.push(token)
         if rs.json_state is not None and rs.json_state.complete:
             return self._finish(rs, FinishDetails("stop", message="json_object_closed"))
-        if rs.json_state is not None and not rs.forced and rs.remaining() <= 8 and not rs.json_state.complete:
+        if rs.json_state is not None and not rs.forced and not rs.json_state.complete and rs.remaining() <= 64:
+            # close while the closing suffix still fits: it grows by at most a few tokens per generated token (a new
+            # key adds `": null`), so eight tokens of slack are kept between its length and the room that is left
             close = rs.json_state.forced_close_tokens()
-            if close and len(close) <= rs.remaining():
+            if close and len(close) <= rs.remaining() <= len(close) + 8:
                 rs.forced.extend(close, "json_close_forcing")
         if n >= req.max_tokens:
             return self._finish(rs, FinishDetails("length"))

@@ -87,3 +87,31 @@ def test_json_object_state_detects_completion_and_forces_a_close():
     for ch in "]}":
         st.push(ord(ch))
     assert st.complete and dec(st.forced_close_tokens()) == ""
+
+
+def test_json_mode_forces_a_parseable_close_before_the_token_budget_runs_out():
+    """The scheduler's commit path with JSON close forcing, fed a scripted byte stream: however deep the nesting is
+    when the budget nears its end, the forced suffix still fits and the finished text parses as an object."""
+    from hipengine_b200.generation.scheduler import Scheduler
+    from hipengine_b200.generation.types import GenerationRequest
+    enc = lambda s: [ord(c) for c in s]
+    dec = lambda ids: "".join(chr(i) for i in ids)
+    scripts = ['{"k": [[[[[[1, 2, {"deep": {"er": [true, fal',
+               '{"a": "a long string value that never closes by itself and keeps going and going',
+               '{"list": [1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12, 13, 14, 15, 16, 17, 18, 19, 20, 21,',
+               '{"x": {"y": {"z": {"w": {"v": {"u": {"t": {"s": {"r": {"q": {"p": {"o":']
+    for script in scripts:
+        for budget in (len(script) + 4, len(script) + 12, 40):
+            sched = Scheduler(4, 16, eos_token_id=None, decode=dec, encode=enc)
+            rs = sched.submit(GenerationRequest(prompt_token_ids=[1], max_tokens=budget, ignore_eos=True,
+                                                json_object_close_forcing=True))
+            sched.active[rs.rid] = rs
+            stream = iter(enc(script) + [ord("1")] * budget)
+            done = False
+            while not done:
+                tok = rs.forced.pop() if rs.forced else next(stream)
+                done = sched.record_token(rs, tok)
+            text = dec(rs.generated)
+            assert len(rs.generated) <= budget
+            obj = json.loads(text)
+            assert isinstance(obj, dict), text
