@@ -712,3 +712,30 @@ def test_server_entry_point_prints_its_resolved_configuration(capsys):
     doc = json.loads(capsys.readouterr().out)
     assert doc["engine"]["kv"]["storage"] == "int8" and doc["engine"]["scheduler"]["policy"] == "fair"
     assert doc["engine"]["scheduler"]["max_active_requests"] == 3 and doc["server"]["batch_window_ms"] == 1.5
+
+
+def test_radix_cache_compatibility_key_ttl_tenant_quota_and_snapshot_matches():
+    from hipengine_b200.kvcache.radix import PrefixCompatibilityKey, RadixCache
+    now = [100.0]
+    key = PrefixCompatibilityKey(model="m", quant="q4_k_m")
+    rc = RadixCache(page_tokens=4, compat=key, ttl_seconds=10.0, tenant_quota_pages=3, clock=lambda: now[0])
+    retained, freed = [], []
+    rc.on_retain = retained.extend
+    rc.on_snapshot_free = freed.append
+    toks = list(range(20))
+    assert rc.insert(toks, [11, 12, 13, 14, 15], snapshots={8: 70}, tenant="a") == 3       # quota: three pages only
+    assert retained == [11, 12, 13] and rc.tenant_pages["a"] == 3
+    m = rc.match(toks + [99])
+    assert m.tokens == 12 and m.pages == [11, 12, 13]
+    assert rc.match(toks[:12]).tokens == 8                     # never the whole prompt: one token must remain
+    snap = rc.match(toks + [99], require_snapshot=True)
+    assert snap.tokens == 8 and snap.snapshot == 70            # the deepest boundary that carries recurrent state
+    assert rc.match(toks + [99], compat=PrefixCompatibilityKey(model="m", quant="q8_0")).tokens == 0
+    assert rc.match(toks + [99], compat=key).tokens == 12
+    assert rc.insert(toks, [21, 22, 23], snapshots={8: 71}, tenant="b") == 0 and freed == [71]   # duplicates are given back
+    assert rc.insert([50, 51, 52, 53, 54], [31], tenant="b") == 1 and rc.tenant_pages["b"] == 1  # b has its own quota
+    now[0] += 11.0
+    assert rc.match(toks + [99]).tokens == 0                   # entries older than the TTL are not served
+    st = rc.snapshot_stats()
+    assert st["hits"] == 4 and st["lookups"] == 6
+    rc.assert_consistent()
