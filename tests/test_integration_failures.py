@@ -107,3 +107,59 @@ def test_unhealthy_report_carries_recent_engine_events():
         assert "submit" in kinds and kinds[-1] == "fatal"
     finally:
         eng.close()
+
+
+class _Stuck(SimulatedRunner):
+    """A runner whose decode blocks the driver thread (a wedged device from the front end's point of view)."""
+    def __init__(self, cfg, gate):
+        super().__init__(cfg)
+        self.gate = gate
+
+    def decode(self, rows):
+        self.gate.wait(timeout=20)
+        return super().decode(rows)
+
+
+def test_command_that_is_not_served_in_time_raises_instead_of_blocking():
+    import threading
+    from dataclasses import replace
+    from hipengine_b200.generation.engine_service import EngineCommandTimeout
+    gate = threading.Event()
+    cfg = replace(_cfg(), command_timeout_seconds=0.3)
+    eng = engine_from_runner(_Stuck(cfg, gate), cfg, None)
+    try:
+        col = eng.submit(GenerationRequest(prompt_token_ids=[1, 2, 3], max_tokens=3, ignore_eos=True))
+        time.sleep(0.2)                                        # the driver is now inside the stuck decode
+        t0 = time.time()
+        with pytest.raises(EngineCommandTimeout, match="snapshot"):
+            eng.snapshot()
+        assert 0.25 < time.time() - t0 < 3.0                   # after the liveness budget, not forever
+        gate.set()
+        assert col.done.wait(timeout=10) and len(col.output.token_ids) == 3      # the engine itself was fine
+        assert isinstance(eng.snapshot(), dict)
+    finally:
+        gate.set()
+        eng.close()
+
+
+def test_stream_many_interleaves_requests_and_delivers_every_token_once():
+    cfg = _cfg()
+    eng = engine_from_runner(SimulatedRunner(cfg), cfg, None)
+    try:
+        reqs = [GenerationRequest(prompt_token_ids=list(range(5 + i)), max_tokens=4 + i, ignore_eos=True) for i in range(3)]
+        want = [o.token_ids for o in eng.generate([GenerationRequest(prompt_token_ids=list(r.prompt_token_ids),
+                                                                     max_tokens=r.max_tokens, ignore_eos=True)
+                                                   for r in reqs])]
+        got = {0: [], 1: [], 2: []}
+        order = []
+        finished = set()
+        for i, ch in eng.stream_many(reqs):
+            assert i not in finished
+            got[i] += ch.token_ids
+            order.append(i)
+            if ch.finished:
+                finished.add(i)
+        assert [got[i] for i in range(3)] == want and finished == {0, 1, 2}
+        assert order != sorted(order)                          # chunks of different requests interleave
+    finally:
+        eng.close()
