@@ -327,6 +327,20 @@ class LLM:
         else:
             ids = [int(t) for t in prompt]
             text = None
+        # token ids index the embedding table on the device: an id outside the vocabulary must never get there
+        if not ids:
+            raise ValueError("the prompt is empty")
+        vocab = self.vocab_size
+        lo, hi = min(ids), max(ids)
+        if lo < 0 or hi >= vocab:
+            raise ValueError(f"prompt token id {lo if lo < 0 else hi} is outside the vocabulary [0, {vocab})")
+        # the same for every other field whose ids are fed back to the model or index a logits row
+        for field_name, values in (("forced_tokens_pending", sp.forced_tokens_pending),
+                                   ("suppress_token_ids", sp.suppress_token_ids),
+                                   ("logit_bias", [t for t, _ in (sp.logit_bias or ())])):
+            bad = [int(t) for t in values if not 0 <= int(t) < vocab]
+            if bad:
+                raise ValueError(f"{field_name}: token id {bad[0]} is outside the vocabulary [0, {vocab})")
         return GenerationRequest.from_sampling(ids, sp, prompt_text=text, row_index=index)
 
     def generate_detailed(self, prompts: Union[PromptLike, Sequence[PromptLike]],

@@ -230,6 +230,23 @@ def create_app(llm: LLM, config: Optional[ServerConfig] = None) -> FastAPI:
     async def _session_error(_: Request, exc: SessionError):
         return JSONResponse(APIError(exc.code, str(exc)).body(), status_code=APIError(exc.code, "").status)
 
+    @app.exception_handler(ValueError)
+    async def _bad_value(_: Request, exc: ValueError):
+        """``LLM`` refuses malformed requests (empty prompt, token ids outside the vocabulary, a bad sampler value)
+        with ``ValueError`` before anything reaches the engine: the client's error."""
+        metrics.inc("hipengine_http_errors_total", code="invalid_request")
+        e = APIError("invalid_request", str(exc))
+        return JSONResponse(e.body(), status_code=e.status)
+
+    @app.exception_handler(Exception)
+    async def _unexpected(_: Request, exc: Exception):
+        """Anything a route did not turn into an API error still answers in the envelope (500, not retryable)."""
+        import logging
+        logging.getLogger("hipengine_b200.server").exception("unhandled error in a route")
+        metrics.inc("hipengine_http_errors_total", code="internal_error")
+        e = APIError("internal_error", f"{type(exc).__name__}: {exc}")
+        return JSONResponse(e.body(), status_code=e.status)
+
     @app.exception_handler(RequestValidationError)
     async def _validation_error(_: Request, exc: RequestValidationError):
         """A body that does not fit the request schema answers in the same envelope as every other client error (the

@@ -58,6 +58,17 @@ def _bias(logit_bias) -> Dict[int, float]:
     return out
 
 
+def _params(**kw) -> SamplingParams:
+    """``SamplingParams`` from request fields; a value the sampler refuses (negative temperature, top_p outside (0, 1],
+    a negative count ...) is the client's error, not the server's."""
+    try:
+        if int(kw.get("max_tokens", 1)) < 1:
+            raise ValueError("max_tokens must be at least 1 (a request always produces a token)")
+        return SamplingParams(**kw)
+    except (ValueError, TypeError) as exc:
+        raise APIError("unsupported_parameter", f"invalid sampling parameter: {exc}") from None
+
+
 def validate_messages(messages: Sequence[Any]) -> None:
     """Role and tool-transcript rules (``hipengine/server/chat_validation.py``)."""
     if not messages:
@@ -83,7 +94,7 @@ def build_completion_params(req: CompletionRequest, tokenizer, default_max: int 
     if req.n < 1 or req.n > 16:
         raise APIError("unsupported_parameter", "n must be in [1, 16]", "n")
     deadline = time.time() + req.timeout_ms / 1e3 if req.timeout_ms else None
-    return SamplingParams(
+    return _params(
         max_tokens=req.max_tokens if req.max_tokens is not None else default_max,
         temperature=req.temperature if req.temperature is not None else 1.0,
         top_p=req.top_p if req.top_p is not None else 1.0, top_k=req.top_k or 0, min_p=req.min_p or 0.0,
@@ -226,7 +237,7 @@ def build_chat(req: ChatCompletionRequest, tokenizer, arch: str, default_max: in
             if req.min_answer_tokens:
                 hard_cap = min(hard_cap, max(0, max_tokens - int(req.min_answer_tokens)))
     deadline = time.time() + req.timeout_ms / 1e3 if req.timeout_ms else None
-    sp = SamplingParams(
+    sp = _params(
         max_tokens=max_tokens, temperature=req.temperature if req.temperature is not None else 1.0,
         top_p=req.top_p if req.top_p is not None else 1.0, top_k=req.top_k or 0, min_p=req.min_p or 0.0,
         presence_penalty=req.presence_penalty, frequency_penalty=req.frequency_penalty,

@@ -392,3 +392,18 @@ def test_history_drafters_on_the_cpu_reference_backend(provider):
     finally:
         plain.close()
         spec.close()
+
+
+def test_python_api_refuses_ids_outside_the_vocabulary(dense):
+    _, llm = dense
+    vocab = llm.vocab_size
+    for prompt, sp, needle in (([1, vocab], SamplingParams(max_tokens=2), "prompt token id"),
+                               ([-1, 2], SamplingParams(max_tokens=2), "prompt token id"),
+                               ([], SamplingParams(max_tokens=2), "empty"),
+                               ([1, 2], SamplingParams(max_tokens=2, forced_tokens_pending=(vocab + 5,)), "forced_tokens_pending"),
+                               ([1, 2], SamplingParams(max_tokens=2, suppress_token_ids=(vocab,)), "suppress_token_ids"),
+                               ([1, 2], SamplingParams(max_tokens=2, logit_bias={vocab: 1.0}), "logit_bias")):
+        with pytest.raises(ValueError, match=needle):
+            llm.generate_detailed([prompt], sp)
+    assert len(llm.generate_detailed([[1, 2, 3]], SamplingParams(max_tokens=2, ignore_eos=True))[0].token_ids) == 2
+    assert llm.engine_service_health()["healthy"]

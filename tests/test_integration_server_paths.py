@@ -262,3 +262,25 @@ def test_serving_load_harness_runs_against_its_own_server_on_the_host_backend(ca
     assert out["completed"] == 5 and out["failed"] == 0 and out["generated_tok_per_s"] > 0
     assert out["ttft_p50_ms"] > 0 and out["config"]["endpoint"] == "chat" and out["config"]["mtp"] == "on"
     assert "gpu" in out and ("error" in out["gpu"] or out["gpu"]["samples"] >= 0)
+
+
+def test_malformed_requests_are_client_errors_and_never_reach_the_engine(client):
+    """Token ids outside the vocabulary (prompt, bias, suppression), an empty prompt, zero or negative max_tokens and
+    sampler values out of range all answer 400 in the envelope, and the engine stays healthy afterwards (an id that
+    reached the embedding table would index device memory out of range)."""
+    base = {"model": "tiny", "prompt": "a", "max_tokens": 2}
+    for patch, needle in (({"prompt": [5, 999999]}, "outside the vocabulary"), ({"prompt": [[5, -1]]}, "outside the vocabulary"),
+                          ({"prompt": ""}, "empty"), ({"max_tokens": 0}, "max_tokens"), ({"max_tokens": -5}, "max_tokens"),
+                          ({"temperature": -1}, "temperature"), ({"top_p": 0}, "top_p"),
+                          ({"logit_bias": {"999999": 5}}, "outside the vocabulary"),
+                          ({"logit_bias": {"5": 500}}, "logit_bias")):
+        r = client.post("/v1/completions", json=dict(base, **patch))
+        assert r.status_code == 400 and needle in r.json()["error"]["message"], (patch, r.text)
+        assert r.json()["error"]["hipengine"]["retryable"] is False
+    with client.stream("POST", "/v1/completions", json=dict(base, prompt=[5, 999999], stream=True)) as r:
+        assert r.status_code == 400
+    r = client.post("/v1/completions", content=b"{not json", headers={"Content-Type": "application/json"})
+    assert r.status_code == 400 and r.json()["error"]["code"] == "invalid_request"
+    assert client.post("/v1/completions", json=base).status_code == 200
+    ready = client.get("/ready").json()
+    assert ready["ready"] and ready["engine_service"]["healthy"]
