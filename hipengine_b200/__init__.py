@@ -1,7 +1,7 @@
 """hipengine_b200: a Blackwell-native (sm_100a) LLM inference and serving engine.
 
 Public surface mirrors the reference package root (``hipengine/__init__.py:20-34``):
-``LLM``, ``SamplingParams``, ``ExecutionProfile``, ``ResidentPreparationError``.
+``LLM``, ``SamplingParams``, ``ExecutionProfile``, ``ResidentPreparationError``, ``UnsupportedModalityError``.
 Unlike the reference, PyTorch is the framework layer here, so importing the
 package imports torch; the heavy pieces (CUDA extension, server) load lazily.
 """
@@ -13,6 +13,7 @@ _LAZY = {
     "LLM": "hipengine_b200.llm",
     "SamplingParams": "hipengine_b200.llm",
     "ResidentPreparationError": "hipengine_b200.llm",
+    "UnsupportedModalityError": "hipengine_b200.llm",
     "ExecutionProfile": "hipengine_b200.config",
     "EngineConfig": "hipengine_b200.config",
 }

@@ -27,6 +27,10 @@ class ResidentPreparationError(RuntimeError):
     """Raised when the engine cannot become resident (weights / KV / scratch do not fit, or no device)."""
 
 
+class UnsupportedModalityError(NotImplementedError):
+    """Raised by the entry points of modalities this engine does not serve (it is a text-generation engine)."""
+
+
 @dataclass(frozen=True)
 class SamplingParams:
     """Every sampler / finish / constraint knob of a request (``hipengine/llm.py:196-343``)."""
@@ -436,6 +440,28 @@ class LLM:
                                         processed, bool(sp.forced_tokens_pending), bool(sp.logprobs),
                                         breaker_open=breaker_open, depth=self.config.speculative.draft_depth,
                                         requested=True)
+
+    # ------------------------------------------------------------------ modalities that are not served
+    def _no_modality(self, what: str, ref: str):
+        raise UnsupportedModalityError(
+            f"{what} is not served by this engine: it runs text decoders (Qwen3.5 hybrid dense / MoE, Gemma 4, "
+            f"Qwen3 / Llama-shaped dense and MoE) and has no encoder, codec or diffusion stack (reference: {ref})")
+
+    def generate_multimodal_detailed(self, *args, **kwargs):
+        """Image / video + text generation (reference ``hipengine/llm.py:611``): not served; raises."""
+        self._no_modality("multimodal generation", "hipengine/llm.py:611")
+
+    def transcribe(self, *args, **kwargs):
+        """Speech to text (reference ``hipengine/llm.py:632``): not served; raises."""
+        self._no_modality("speech transcription", "hipengine/llm.py:632")
+
+    def synthesize(self, *args, **kwargs):
+        """Text to speech (reference ``hipengine/llm.py:645``): not served; raises."""
+        self._no_modality("speech synthesis", "hipengine/llm.py:645")
+
+    def generate_song(self, *args, **kwargs):
+        """Lyrics + style to audio (reference ``hipengine/llm.py:664``): not served; raises."""
+        self._no_modality("song generation", "hipengine/llm.py:664")
 
     def submit_independent_batches_detailed(self, batches: Sequence[Sequence[PromptLike]], sampling_params=None
                                             ) -> List[List[GenerationOutput]]:

@@ -19,6 +19,7 @@ from typing import Any, Dict, List, Optional, Tuple
 
 from fastapi.exceptions import RequestValidationError
 from fastapi import Depends, FastAPI, Request
+from starlette.exceptions import HTTPException as StarletteHTTPException
 from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
 
 from ..generation.types import GenerationOutput, GenerationRequest, TokenLogprob
@@ -247,6 +248,14 @@ def create_app(llm: LLM, config: Optional[ServerConfig] = None) -> FastAPI:
         e = APIError("internal_error", f"{type(exc).__name__}: {exc}")
         return JSONResponse(e.body(), status_code=e.status)
 
+    @app.exception_handler(StarletteHTTPException)
+    async def _http_error(request: Request, exc: StarletteHTTPException):
+        """An unknown path or a wrong method answers in the envelope too (the framework's default is ``{"detail": ..}``)."""
+        code = {404: "not_found", 405: "method_not_allowed"}.get(exc.status_code, "invalid_request")
+        metrics.inc("hipengine_http_errors_total", code=code)
+        body = APIError(code, f"{request.method} {request.url.path}: {exc.detail}").body()
+        return JSONResponse(body, status_code=exc.status_code, headers=getattr(exc, "headers", None))
+
     @app.exception_handler(RequestValidationError)
     async def _validation_error(_: Request, exc: RequestValidationError):
         """A body that does not fit the request schema answers in the same envelope as every other client error (the
@@ -412,6 +421,28 @@ def create_app(llm: LLM, config: Optional[ServerConfig] = None) -> FastAPI:
             acc.cached_tokens += o.telemetry.cached_prompt_tokens
         return acc.usage()
 
+    @app.post("/v1/audio/songs", dependencies=[Depends(auth)])
+    async def audio_songs(request: Request):
+        """Song generation (lyrics + style -> audio) is a separate diffusion / codec pipeline in the reference
+        (``hipengine/server/api.py:7732``); this engine serves text models only and says so with 501."""
+        raise APIError("unsupported_feature", "song generation is not served by this engine (text generation only: "
+                                              "/v1/completions, /v1/chat/completions)")
+
+    def stream_request(prompt_ids, sp):
+        """The engine request of a live stream, checked BEFORE the response starts: a malformed prompt or one that
+        cannot fit the served context answers with its HTTP status instead of an error event inside a 200 stream.  The
+        caller holds a place in the admission gate; it is given back when the check refuses."""
+        try:
+            greq = llm._request(prompt_ids, sp, 0)
+            fit = llm.fit_context(greq.prompt_token_ids, greq.max_tokens)
+            if not fit.get("fits_with_max_tokens", True):
+                raise APIError("context_overflow", f"context_overflow: prompt {fit['prompt_tokens']} + max_tokens "
+                                                   f"{greq.max_tokens} exceeds max context {fit['max_context']}")
+            return greq, engine()
+        except BaseException:
+            gate.leave()
+            raise
+
     @app.post("/v1/completions", dependencies=[Depends(auth)])
     async def completions(req: CompletionRequest, request: Request):
         check_model(req.model)
@@ -430,8 +461,7 @@ def create_app(llm: LLM, config: Optional[ServerConfig] = None) -> FastAPI:
         metrics.inc("hipengine_requests_total", route="completions")
         live = req.stream and len(prompts) == 1 and req.n == 1 and not req.echo
         if live:
-            greq = llm._request(prompts[0], sp, 0)
-            eng = engine()
+            greq, eng = stream_request(prompts[0], sp)
             opts = req.stream_options
             timing = SE.StreamTimingTracker()
 
@@ -553,8 +583,7 @@ def create_app(llm: LLM, config: Optional[ServerConfig] = None) -> FastAPI:
             return None
 
         if req.stream and req.n == 1:
-            greq = llm._request(prompt_ids, sp, 0)
-            eng = engine()
+            greq, eng = stream_request(prompt_ids, sp)
             opts = req.stream_options
             timing = SE.StreamTimingTracker()
 

@@ -28,6 +28,8 @@ CODES: Dict[str, tuple] = {
     "model_unavailable": (404, "invalid_request_error", False),
     "routing_failed": (502, "server_error", True),
     "unauthorized": (401, "authentication_error", False),
+    "not_found": (404, "invalid_request_error", False),
+    "method_not_allowed": (405, "invalid_request_error", False),
 }
 
 

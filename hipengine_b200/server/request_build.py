@@ -58,6 +58,15 @@ def _bias(logit_bias) -> Dict[int, float]:
     return out
 
 
+def _deadline(timeout_ms: Optional[int]) -> Optional[float]:
+    """Wall-clock deadline of a request's ``timeout_ms``; zero or absent means none, a negative value is refused."""
+    if timeout_ms is None or timeout_ms == 0:
+        return None
+    if timeout_ms < 0:
+        raise APIError("unsupported_parameter", "timeout_ms must be >= 0", "timeout_ms")
+    return time.time() + timeout_ms / 1e3
+
+
 def _params(**kw) -> SamplingParams:
     """``SamplingParams`` from request fields; a value the sampler refuses (negative temperature, top_p outside (0, 1],
     a negative count ...) is the client's error, not the server's."""
@@ -93,7 +102,7 @@ def validate_messages(messages: Sequence[Any]) -> None:
 def build_completion_params(req: CompletionRequest, tokenizer, default_max: int = 16) -> SamplingParams:
     if req.n < 1 or req.n > 16:
         raise APIError("unsupported_parameter", "n must be in [1, 16]", "n")
-    deadline = time.time() + req.timeout_ms / 1e3 if req.timeout_ms else None
+    deadline = _deadline(req.timeout_ms)
     return _params(
         max_tokens=req.max_tokens if req.max_tokens is not None else default_max,
         temperature=req.temperature if req.temperature is not None else 1.0,
@@ -236,7 +245,7 @@ def build_chat(req: ChatCompletionRequest, tokenizer, arch: str, default_max: in
             hard_cap = max(0, int(budget))
             if req.min_answer_tokens:
                 hard_cap = min(hard_cap, max(0, max_tokens - int(req.min_answer_tokens)))
-    deadline = time.time() + req.timeout_ms / 1e3 if req.timeout_ms else None
+    deadline = _deadline(req.timeout_ms)
     sp = _params(
         max_tokens=max_tokens, temperature=req.temperature if req.temperature is not None else 1.0,
         top_p=req.top_p if req.top_p is not None else 1.0, top_k=req.top_k or 0, min_p=req.min_p or 0.0,

@@ -284,3 +284,46 @@ def test_malformed_requests_are_client_errors_and_never_reach_the_engine(client)
     assert client.post("/v1/completions", json=base).status_code == 200
     ready = client.get("/ready").json()
     assert ready["ready"] and ready["engine_service"]["healthy"]
+
+
+def test_refused_streams_answer_with_a_status_and_do_not_hold_the_admission_gate():
+    """A live stream is checked before its response starts: a bad prompt or one that cannot fit the context is a 400,
+    not an error event inside a 200 stream, and each refusal gives its place in the admission gate back (a gate of two
+    places still serves after many refusals)."""
+    llm = LLM("tiny-dense", backend="cpu_reference", max_active_requests=2, max_sequence_length=128)
+    try:
+        with TestClient(create_app(llm, ServerConfig(served_model_name="tiny", max_queued_requests=2))) as c:
+            for _ in range(4):
+                for body in ({"prompt": [5, 999999]}, {"prompt": [7] * 200}, {"prompt": ""}):
+                    with c.stream("POST", "/v1/completions", json=dict({"model": "tiny", "max_tokens": 2, "stream": True},
+                                                                       **body)) as r:
+                        r.read()
+                        assert r.status_code == 400 and r.headers["content-type"].startswith("application/json")
+                chat = {"model": "tiny", "messages": [{"role": "user", "content": "x " * 300}], "max_tokens": 4, "stream": True}
+                with c.stream("POST", "/v1/chat/completions", json=chat) as r:
+                    r.read()
+                    assert r.status_code == 400 and r.json()["error"]["code"] == "context_overflow"
+            with c.stream("POST", "/v1/completions", json={"model": "tiny", "prompt": "ab", "max_tokens": 3, "stream": True}) as r:
+                ev = _sse(r)
+            assert r.status_code == 200 and ev[-1] == "[DONE]"
+            assert c.post("/v1/completions", json={"model": "tiny", "prompt": "ab", "max_tokens": 2}).status_code == 200
+    finally:
+        llm.close()
+
+
+def test_unknown_paths_unserved_modalities_and_bad_timeouts_answer_in_the_envelope(client):
+    r = client.get("/v1/nope")
+    assert r.status_code == 404 and r.json()["error"]["code"] == "not_found" and "/v1/nope" in r.json()["error"]["message"]
+    r = client.get("/v1/completions")
+    assert r.status_code == 405 and r.json()["error"]["code"] == "method_not_allowed"
+    r = client.post("/v1/audio/songs", json={"model": "tiny", "lyrics": "la", "style": "pop"})
+    assert r.status_code == 501 and r.json()["error"]["code"] == "unsupported_feature"
+    r = client.post("/v1/completions", json={"model": "tiny", "prompt": "a", "max_tokens": 2, "timeout_ms": -5})
+    assert r.status_code == 400 and r.json()["error"]["param"] == "timeout_ms"
+    assert client.post("/v1/completions", json={"model": "tiny", "prompt": "a", "max_tokens": 2, "timeout_ms": 0}
+                       ).status_code == 200                                          # zero means no deadline
+    from hipengine_b200 import UnsupportedModalityError
+    llm = client.app.state.llm
+    for fn in (llm.generate_multimodal_detailed, llm.transcribe, llm.synthesize, llm.generate_song):
+        with pytest.raises(UnsupportedModalityError, match="not served"):
+            fn("x")
