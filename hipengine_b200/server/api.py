@@ -712,7 +712,10 @@ def create_app(llm: LLM, config: Optional[ServerConfig] = None) -> FastAPI:
 
     @app.post("/v1/hipengine/sessions/{sid}/rollback", dependencies=[Depends(auth)])
     async def rollback_session(sid: str, body: Optional[Dict[str, Any]] = None):
-        s = sessions.rollback(sid, int((body or {}).get("turns", 1)))
+        turns = (body or {}).get("turns", 1)
+        if isinstance(turns, bool) or not isinstance(turns, int) or turns < 0:
+            raise APIError("unsupported_parameter", "turns must be a non-negative integer", "turns")
+        s = sessions.rollback(sid, turns)
         return {"id": s.id, "turns": s.turns, "messages": len(s.messages)}
 
     @app.get("/v1/hipengine/sessions/{sid}/snapshot", dependencies=[Depends(auth)])

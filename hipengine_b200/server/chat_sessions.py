@@ -22,6 +22,25 @@ class SessionError(ValueError):
         self.code = code
 
 
+_ROLES = ("system", "developer", "user", "assistant", "tool")
+
+
+def _check_transcript(msgs: Any) -> None:
+    """A restored transcript must be what a chat request could have stored: a list of ``{role, content, ...}``
+    objects with a known role and text (or parts, or nothing beside tool calls) as content.  Refusing it at restore
+    time keeps a malformed document from becoming a session that fails on every later use."""
+    if not isinstance(msgs, list):
+        raise SessionError("invalid_continuation", "snapshot 'messages' must be a list")
+    for i, m in enumerate(msgs):
+        if not isinstance(m, dict) or m.get("role") not in _ROLES:
+            raise SessionError("invalid_continuation", f"snapshot messages[{i}] has no supported role")
+        c = m.get("content")
+        if not (c is None or isinstance(c, str) or (isinstance(c, list) and all(isinstance(x, dict) for x in c))):
+            raise SessionError("invalid_continuation", f"snapshot messages[{i}].content must be text or a list of parts")
+        if "tool_calls" in m and not isinstance(m["tool_calls"], list):
+            raise SessionError("invalid_continuation", f"snapshot messages[{i}].tool_calls must be a list")
+
+
 @dataclass
 class ChatSession:
     id: str
@@ -116,7 +135,14 @@ class ChatSessionStore:
         if tokenizer_meta and doc.get("tokenizer") and doc["tokenizer"].get("vocab_size") not in (
                 None, tokenizer_meta.get("vocab_size")):
             raise SessionError("invalid_continuation", "snapshot was taken with a different tokenizer")
-        body = doc.get("session") or {}
-        s = self.create(body.get("messages") or [])
-        s.turns = int(body.get("turns", 0))
+        body = doc.get("session")
+        if not isinstance(body, dict):
+            raise SessionError("invalid_continuation", "snapshot has no 'session' object")
+        msgs = body.get("messages") or []
+        _check_transcript(msgs)
+        turns = body.get("turns", 0)
+        if isinstance(turns, bool) or not isinstance(turns, int) or turns < 0:
+            raise SessionError("invalid_continuation", "snapshot 'turns' must be a non-negative integer")
+        s = self.create(msgs)
+        s.turns = turns
         return s

@@ -327,3 +327,27 @@ def test_unknown_paths_unserved_modalities_and_bad_timeouts_answer_in_the_envelo
     for fn in (llm.generate_multimodal_detailed, llm.transcribe, llm.synthesize, llm.generate_song):
         with pytest.raises(UnsupportedModalityError, match="not served"):
             fn("x")
+
+
+def test_session_documents_and_rollback_counts_are_validated(client):
+    """A snapshot whose transcript could not have come from a chat request is refused when it is restored (not turned
+    into a session that fails on every later use), and a rollback count must be a non-negative integer."""
+    chat = {"model": "tiny", "messages": [{"role": "user", "content": "a"}], "max_tokens": 3, "enable_thinking": False}
+    sid = client.post("/v1/chat/completions", json=dict(chat, session={"create": True})).json()["session"]["id"]
+    snap = client.get(f"/v1/hipengine/sessions/{sid}/snapshot").json()
+    assert snap["session"]["turns"] == 1 and len(snap["session"]["messages"]) == 2
+    for patch in ({"messages": "x"}, {"messages": [{"role": "robot", "content": "x"}]}, {"messages": [{"role": "user", "content": 5}]},
+                  {"messages": ["x"]}, {"turns": -1}, {"turns": "many"},
+                  {"messages": [{"role": "assistant", "content": None, "tool_calls": "f"}]}):
+        r = client.post("/v1/hipengine/sessions/restore", json=dict(snap, session=dict(snap["session"], **patch)))
+        assert r.status_code == 400 and r.json()["error"]["code"] == "invalid_continuation", (patch, r.text)
+    assert client.post("/v1/hipengine/sessions/restore", json=dict(snap, session=None)).status_code == 400
+    rid = client.post("/v1/hipengine/sessions/restore", json=snap).json()
+    assert rid["turns"] == 1
+    r = client.post("/v1/chat/completions", json=dict(chat, session=rid["id"]))          # the restored session continues
+    assert r.status_code == 200 and r.json()["usage"]["prompt_tokens"] > 26
+    for bad in (-1, "two", 1.5, True):
+        r = client.post(f"/v1/hipengine/sessions/{sid}/rollback", json={"turns": bad})
+        assert r.status_code == 400 and r.json()["error"]["param"] == "turns", bad
+    assert client.post(f"/v1/hipengine/sessions/{sid}/rollback", json={"turns": 0}).json()["turns"] == 1
+    assert client.post(f"/v1/hipengine/sessions/{sid}/rollback").json() == {"id": sid, "turns": 0, "messages": 0}
