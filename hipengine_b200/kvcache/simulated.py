@@ -45,7 +45,7 @@ class SimulatedKVBackend:
             self.writes[p] = self.page
 
     def publish_prefix(self, prompt: Sequence[int], lease: KVLease) -> int:
-        n = (len(prompt) // self.page) * self.page
+        n = (len(prompt) // self.page) * self.page if self.use_prefix else 0
         if n:
             self.radix.insert(list(prompt[:n]), lease.pages[:n // self.page])
         return n

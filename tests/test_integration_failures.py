@@ -163,3 +163,56 @@ def test_stream_many_interleaves_requests_and_delivers_every_token_once():
         assert order != sorted(order)                          # chunks of different requests interleave
     finally:
         eng.close()
+
+
+@pytest.mark.parametrize("policy", ["protect_decode", "protect_ttft", "fair", "token_budget"])
+@pytest.mark.parametrize("prefix", ["radix", "off"])
+def test_churn_of_submits_cancels_and_contained_failures_leaves_the_books_balanced(policy, prefix):
+    """Sixty requests with shared prefixes arrive at random, a third are cancelled at random moments (pending, in
+    prefill, in decode), three fail inside decode, the pool is small enough to evict cached prefixes and to make
+    admissions wait.  When the loop runs dry every request has finished exactly once, every slot is back, no lease or
+    page credit is left, the only pages in use are the prefix cache's, and clearing the cache frees the whole pool."""
+    import random
+    from hipengine_b200.config import EngineConfig, KVConfig, SchedulerConfig
+    from hipengine_b200.generation.engine_loop import EngineLoop
+    from hipengine_b200.generation.scheduler import GenerationAdmissionRejected
+    from hipengine_b200.generation.simulator import SimulatedRunner
+    from hipengine_b200.generation.types import GenerationRequest
+    rng = random.Random(7)
+    cfg = EngineConfig(max_sequence_length=256, kv=KVConfig(prefix_cache=prefix),
+                       scheduler=SchedulerConfig(max_active_requests=4, policy=policy, max_pending_requests=16))
+    runner = SimulatedRunner(cfg, kv_capacity_tokens=1024, fail_decode_admission=[3, 11, 17])
+    loop = EngineLoop(runner, cfg)
+    finished = []
+    loop.on_event = lambda rs: finished.append(rs.rid) if rs.finish is not None else None
+    shared = [rng.randrange(5, 900) for _ in range(48)]
+    live, refused = [], 0
+    for _ in range(400):
+        r = rng.random()
+        if r < 0.35 and len(live) + refused < 60:
+            head = shared[:rng.choice([16, 32, 48])] if rng.random() < 0.5 else []
+            prompt = head + [rng.randrange(5, 900) for _ in range(rng.randrange(1, 40))]
+            try:
+                live.append(loop.submit(GenerationRequest(prompt_token_ids=prompt, max_tokens=rng.randrange(1, 60),
+                                                          ignore_eos=True)).rid)
+            except GenerationAdmissionRejected:
+                refused += 1                                   # the pending queue was full
+        elif r < 0.45 and live:
+            loop.cancel(rng.choice(live))                      # may name a finished request: a no-op
+        loop.tick()
+        runner.kv.radix.assert_consistent()
+    for _ in range(5000):
+        if loop.idle():
+            break
+        loop.tick()
+    assert loop.idle() and sorted(finished) == sorted(live)    # each exactly once
+    c = loop.sched.counters
+    assert c["finished"] == len(live) and c["failed"] == 3 and c["cancelled"] >= 5
+    assert (c["cached_prompt_tokens"] > 0) == (prefix == "radix")
+    assert sorted(runner.free_slots) == [0, 1, 2, 3]
+    snap = runner.kv.pool.snapshot()
+    assert snap["leases"] == 0 and snap["pages_credit"] == 0 and snap["pages_used"] == snap["pages_cached"]
+    assert (snap["pages_cached"] > 0) == (prefix == "radix")
+    runner.kv.radix.clear()                                    # hands its pages back through the release hook
+    snap = runner.kv.pool.snapshot()
+    assert snap["pages_free"] == snap["pages_total"] and snap["pages_used"] == 0
