@@ -166,22 +166,24 @@ def test_stream_many_interleaves_requests_and_delivers_every_token_once():
 
 
 @pytest.mark.parametrize("policy", ["protect_decode", "protect_ttft", "fair", "token_budget"])
-@pytest.mark.parametrize("prefix", ["radix", "off"])
-def test_churn_of_submits_cancels_and_contained_failures_leaves_the_books_balanced(policy, prefix):
+@pytest.mark.parametrize("prefix,spec_depth", [("radix", 0), ("off", 0), ("radix", 3)])
+def test_churn_of_submits_cancels_and_contained_failures_leaves_the_books_balanced(policy, prefix, spec_depth):
     """Sixty requests with shared prefixes arrive at random, a third are cancelled at random moments (pending, in
-    prefill, in decode), three fail inside decode, the pool is small enough to evict cached prefixes and to make
+    prefill, in decode), three fail inside decode (or inside a speculative cycle's verify), the pool is small enough to evict cached prefixes and to make
     admissions wait.  When the loop runs dry every request has finished exactly once, every slot is back, no lease or
     page credit is left, the only pages in use are the prefix cache's, and clearing the cache frees the whole pool."""
     import random
-    from hipengine_b200.config import EngineConfig, KVConfig, SchedulerConfig
+    from hipengine_b200.config import EngineConfig, KVConfig, SchedulerConfig, SpeculativeConfig
     from hipengine_b200.generation.engine_loop import EngineLoop
     from hipengine_b200.generation.scheduler import GenerationAdmissionRejected
     from hipengine_b200.generation.simulator import SimulatedRunner
     from hipengine_b200.generation.types import GenerationRequest
     rng = random.Random(7)
     cfg = EngineConfig(max_sequence_length=256, kv=KVConfig(prefix_cache=prefix),
-                       scheduler=SchedulerConfig(max_active_requests=4, policy=policy, max_pending_requests=16))
-    runner = SimulatedRunner(cfg, kv_capacity_tokens=1024, fail_decode_admission=[3, 11, 17])
+                       scheduler=SchedulerConfig(max_active_requests=4, policy=policy, max_pending_requests=16),
+                       speculative=SpeculativeConfig(mode="mtp" if spec_depth else "off", draft_depth=max(1, spec_depth)))
+    runner = SimulatedRunner(cfg, kv_capacity_tokens=1024, fail_decode_admission=[3, 11, 17], spec_depth=spec_depth,
+                             spec_accept_rate=0.6)
     loop = EngineLoop(runner, cfg)
     finished = []
     loop.on_event = lambda rs: finished.append(rs.rid) if rs.finish is not None else None
@@ -208,6 +210,7 @@ def test_churn_of_submits_cancels_and_contained_failures_leaves_the_books_balanc
     assert loop.idle() and sorted(finished) == sorted(live)    # each exactly once
     c = loop.sched.counters
     assert c["finished"] == len(live) and c["failed"] == 3 and c["cancelled"] >= 5
+    assert (c["spec_cycles"] > 0) == (spec_depth > 0)        # failures inside a verify are contained the same way
     assert (c["cached_prompt_tokens"] > 0) == (prefix == "radix")
     assert sorted(runner.free_slots) == [0, 1, 2, 3]
     snap = runner.kv.pool.snapshot()
