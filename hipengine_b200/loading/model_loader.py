@@ -64,6 +64,48 @@ def config_from_gguf(info: GGUFModelInfo) -> ModelConfig:
     return ModelConfig(**kw)
 
 
+def describe_model_source(model) -> Dict[str, object]:
+    """What ``model`` names, found without reading a tensor: a built-in random-init geometry, or a GGUF file whose
+    header gives the architecture, the geometry, the histogram of block types and the bytes the weights will take.
+    ``{"error": ...}`` when it is neither (nothing is ever downloaded) or when the header cannot serve this engine.
+    The server's ``--info`` prints it, so a wrong path or an unsupported file shows before any load is attempted."""
+    from pathlib import Path
+    from ..models.config import NAMED_CONFIGS
+    from ..models.registry import plugin_for
+
+    def geometry(cfg: ModelConfig) -> Dict[str, object]:
+        out = {"arch": cfg.arch, "layers": cfg.n_layers, "hidden": cfg.hidden, "vocab": cfg.vocab,
+               "ffn": "moe" if cfg.is_moe else "dense", "nextn_layers": cfg.nextn_layers,
+               "max_context": cfg.max_context}
+        try:
+            out["family"] = plugin_for(cfg.arch).describe(cfg)
+        except KeyError:
+            out["family"] = None
+        return out
+
+    name = str(model)
+    files = discover_gguf_files(name)
+    if files:
+        try:
+            info = scan_gguf(files[0])
+            cfg = config_from_gguf(info)
+        except Exception as e:                                  # a truncated header, an unsupported architecture
+            return {"source": "gguf", "path": str(files[0]), "error": f"{type(e).__name__}: {e}"}
+        hist: Dict[str, int] = {}
+        for t in info.tensors.values():
+            hist[t.ggml_type.name] = hist.get(t.ggml_type.name, 0) + t.nbytes
+        return {"source": "gguf", "path": str(files[0]), "files": len(files), "file_bytes": files[0].stat().st_size,
+                "gguf_version": info.version, "tensors": info.tensor_count, "weight_bytes": info.total_tensor_nbytes,
+                "bytes_by_block_type": dict(sorted(hist.items(), key=lambda kv: -kv[1])),
+                "name": info.get("general.name"), **geometry(cfg)}
+    if Path(name).exists():
+        return {"source": "path", "path": name, "error": "no *.gguf file there"}
+    if name in NAMED_CONFIGS:
+        return {"source": "built-in geometry (random weights)", "name": name, **geometry(NAMED_CONFIGS[name])}
+    return {"source": "unknown", "error": f"{name!r} is neither a local GGUF path nor a built-in geometry "
+                                          f"({sorted(NAMED_CONFIGS)})"}
+
+
 def load_gguf_model(path, device="cpu", pin: bool = False, validate: bool = True) -> ModelWeights:
     files = discover_gguf_files(path)
     if not files:

@@ -113,8 +113,10 @@ def main(argv: Optional[List[str]] = None) -> int:
     if a.info:
         import json
         from dataclasses import asdict
-        print(json.dumps({"engine": asdict(eng), "server": asdict(srv)}, indent=1, default=str))
-        return 0
+        from ..loading.model_loader import describe_model_source
+        model = describe_model_source(a.model)
+        print(json.dumps({"model": model, "engine": asdict(eng), "server": asdict(srv)}, indent=1, default=str))
+        return 2 if "error" in model else 0
     from . import log_style
     level = "DEBUG" if a.debug else a.log_level.upper()
     log_style.install(level, log_style.want_color(a.log_color, sys.stderr.isatty()))

@@ -89,3 +89,37 @@ def test_local_only_model_resolution(tmp_path, monkeypatch):
     import pytest
     with pytest.raises(ModelNotFound, match="never downloaded"):
         resolve_model_path("org/absent")
+
+
+def test_model_source_is_described_from_the_header_alone(tmp_path, capsys):
+    """The server's ``--info`` names what ``--model`` is before anything is loaded: a GGUF file by its header
+    (architecture, geometry, bytes per block type), a built-in geometry by name, and an error with exit code 2 for a
+    path that is neither, a directory without a GGUF file, a truncated file or an unsupported architecture."""
+    import json
+    from hipengine_b200.loading.gguf import GGUFWriter
+    from hipengine_b200.loading.model_loader import describe_model_source
+    from hipengine_b200.server.__main__ import main
+    w = build_random_model(TINY_HYBRID, seed=0)
+    p = write_gguf(w, tmp_path / "hy.gguf")
+    d = describe_model_source(p)
+    assert d["source"] == "gguf" and d["arch"] == "qwen35" and d["layers"] == TINY_HYBRID.n_layers
+    assert d["tensors"] == len(w.tensors) and d["weight_bytes"] == sum(d["bytes_by_block_type"].values())
+    assert d["weight_bytes"] <= d["file_bytes"] and "Q4_K" in d["bytes_by_block_type"]
+    assert d["family"]["layers"] == {"full": 1, "linear": 3}
+    assert describe_model_source(tmp_path)["path"].endswith("hy.gguf")          # a directory holding the file
+    assert describe_model_source("tiny-dense")["source"].startswith("built-in")
+    assert "error" in describe_model_source(tmp_path / "missing.gguf")
+    empty = tmp_path / "empty_dir"
+    empty.mkdir()
+    assert "no *.gguf" in describe_model_source(empty)["error"]
+    cut = tmp_path / "cut.gguf"
+    cut.write_bytes(p.read_bytes()[:100])
+    assert "error" in describe_model_source(cut)
+    other = GGUFWriter(tmp_path / "other.gguf", "mamba")
+    other.add_tensor("x", torch.zeros(2, 32), GGMLType.F32)
+    other.write()
+    assert "unsupported GGUF architecture" in describe_model_source(tmp_path / "other.gguf")["error"]
+    assert main(["--model", str(p), "--info"]) == 0
+    assert json.loads(capsys.readouterr().out)["model"]["arch"] == "qwen35"
+    assert main(["--model", str(tmp_path / "missing.gguf"), "--info"]) == 2
+    assert "neither" in json.loads(capsys.readouterr().out)["model"]["error"]
