@@ -263,6 +263,36 @@ def test_replica_router_balances_sticks_to_prefixes_and_fails_over():
         assert lines[-1] == b"data: [DONE]" and len(lines) >= 2
         ready = requests.get(base + "/ready")
         assert ready.status_code == 200 and ready.json()["ready_replicas"] == 2
+        # a chat session lives in ONE replica: the router learns its owner from the creating response (blocking and
+        # streamed) and pins every later request that names it, whatever the load says
+        chat = {"model": "tiny-dense", "messages": [{"role": "user", "content": "hello"}], "max_tokens": 2,
+                "enable_thinking": False}
+        sids = [requests.post(base + "/v1/chat/completions", json=dict(chat, session={"create": True})).json()["session"]["id"]]
+        with requests.post(base + "/v1/chat/completions", json=dict(chat, session={"create": True}, stream=True),
+                           stream=True) as r:
+            text = b"".join(r.iter_content(None)).decode()
+        sids.append(text.split('"session":{"id":"')[1].split('"')[0])
+        sids.append(requests.post(base + f"/v1/hipengine/sessions/{sids[0]}/fork").json()["id"])
+        assert all(s in router.session_owner for s in sids)
+        assert router.session_owner[sids[2]] == router.session_owner[sids[0]]
+        for s in sids * 3:
+            r = requests.post(base + "/v1/chat/completions", json=dict(chat, session=s))
+            assert r.status_code == 200 and r.json()["session"]["id"] == s, r.text
+        assert router.stats["session_pins"] >= 9
+        listed = requests.get(base + "/v1/hipengine/sessions").json()["sessions"]
+        assert {e["id"] for e in listed} >= set(sids) and all(e["replica"].startswith("http://127.0.0.1:806") for e in listed)
+        assert requests.delete(base + f"/v1/hipengine/sessions/{sids[1]}").json()["deleted"]
+        # an unserved feature is the replica's ANSWER: passed through, the replica stays in rotation
+        failed = [rep.failed for rep in router.replicas]
+        r = requests.post(base + "/v1/audio/songs", json={"model": "tiny-dense", "lyrics": "la"})
+        assert r.status_code == 501 and r.json()["error"]["code"] == "unsupported_feature"
+        assert [rep.failed for rep in router.replicas] == failed
+        assert requests.post(base + "/v1/completions", json={"model": "tiny-dense", "prompt": "ok", "max_tokens": 1}).status_code == 200
+        # nothing left to route to: the envelope, not a bare message
+        for rep in router.replicas:
+            rep.down_until = time.time() + 60
+        r = requests.post(base + "/v1/completions", json={"model": "tiny-dense", "prompt": "ok", "max_tokens": 1})
+        assert r.status_code == 502 and r.json()["error"]["code"] == "routing_failed" and r.json()["error"]["hipengine"]["retryable"]
     finally:
         for s in servers:
             s.should_exit = True
@@ -433,3 +463,63 @@ def test_media_parts_are_parsed_under_limits_and_refused_by_the_text_only_server
             assert c.post("/v1/chat/completions", json=body).status_code == 200
     finally:
         llm.close()
+
+
+def test_router_retries_a_failed_request_elsewhere_and_lets_the_last_failure_stand():
+    """Stand-in replicas: one answers 500 to every generation request, one answers 200.  The router retries the 500 on
+    the other replica and keeps the failing one in rotation (its /ready decides, not one failed request); when every
+    replica fails, the client gets the last replica's own error body, not a routing error."""
+    import threading
+    import time
+
+    import requests
+    import uvicorn
+    from fastapi import FastAPI
+    from fastapi.responses import JSONResponse
+
+    from hipengine_b200.server.errors import APIError
+    from hipengine_b200.server.router import Router, create_router_app, session_of
+
+    assert session_of("/v1/hipengine/sessions/sess_ab12/fork", {}) == "sess_ab12"
+    assert session_of("/v1/chat/completions", {"session": {"id": "sess_1"}}) == "sess_1"
+    assert session_of("/v1/chat/completions", {"continuation_id": "sess_2"}) == "sess_2"
+    assert session_of("/v1/chat/completions", {"session": {"create": True}}) is None
+    mode = {"good_fails": False}
+    bad, good = FastAPI(), FastAPI()
+
+    @bad.post("/v1/completions")
+    async def _bad():
+        return JSONResponse(APIError("execution_failed", "device fault on replica A").body(), status_code=500)
+
+    @good.post("/v1/completions")
+    async def _good():
+        if mode["good_fails"]:
+            return JSONResponse(APIError("execution_failed", "device fault on replica B").body(), status_code=500)
+        return {"choices": [{"text": "fine"}]}
+
+    servers = []
+    try:
+        for app, port in ((bad, 8071), (good, 8072)):
+            srv = uvicorn.Server(uvicorn.Config(app, host="127.0.0.1", port=port, log_level="warning"))
+            threading.Thread(target=srv.run, daemon=True).start()
+            servers.append(srv)
+        router = Router(["http://127.0.0.1:8071", "http://127.0.0.1:8072"], backoff_s=60.0)
+        srv = uvicorn.Server(uvicorn.Config(create_router_app(router), host="127.0.0.1", port=8070, log_level="warning"))
+        threading.Thread(target=srv.run, daemon=True).start()
+        servers.append(srv)
+        for _ in range(200):
+            if all(s.started for s in servers):
+                break
+            time.sleep(0.05)
+        for _ in range(4):
+            r = requests.post("http://127.0.0.1:8070/v1/completions", json={"prompt": "x"})
+            assert r.status_code == 200 and r.json()["choices"][0]["text"] == "fine"
+        assert router.stats["retries"] >= 1 and router.replicas[0].failed >= 1
+        assert router.replicas[0].available(time.time())                   # still in rotation
+        mode["good_fails"] = True
+        r = requests.post("http://127.0.0.1:8070/v1/completions", json={"prompt": "x"})
+        assert r.status_code == 500 and r.json()["error"]["code"] == "execution_failed"
+        assert "device fault on replica" in r.json()["error"]["message"]
+    finally:
+        for s in servers:
+            s.should_exit = True
