@@ -167,8 +167,13 @@ class EngineService:
                     raise EngineUnavailable("engine stopped while streaming")
                 time.sleep(0.001)
 
-    def cancel(self, rid: int, reason: str = "cancelled") -> bool:
+    def cancel(self, rid: int, reason: str = "cancelled", wait: bool = True) -> bool:
+        """Cancel a request.  With ``wait=False`` the command is only posted (the driver serves it before its next
+        tick) and the answer is True: for callers that must not wait for a tick, such as an event loop."""
         try:
+            if not wait:
+                self._call("cancel", (rid, reason), wait=False)
+                return True
             return bool(self._call("cancel", (rid, reason)))
         except EngineUnavailable:
             return False

@@ -484,7 +484,12 @@ class LLM:
     def fit_context(self, prompt: PromptLike, max_tokens: Optional[int] = None) -> Dict[str, Any]:
         """Does ``prompt`` (text or token ids) fit the served context, and how many tokens may follow it."""
         n = len(self.tokenize(prompt)) if isinstance(prompt, str) else len(list(prompt))
-        mx = int(self.resident_capacity_estimate().get("max_context") or self.config.max_sequence_length)
+        mx = getattr(self, "_served_context", None)
+        if mx is None:
+            # fixed once the engine is built; asked once, because the answer comes from the driver thread between two
+            # ticks and a route handler must not wait for a tick on every request
+            mx = int(self.resident_capacity_estimate().get("max_context") or self.config.max_sequence_length)
+            self._served_context = mx
         room = max(0, mx - n)
         out = {"prompt_tokens": n, "max_context": mx, "max_new_tokens": room, "fits": n < mx}
         if max_tokens is not None:

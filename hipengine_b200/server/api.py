@@ -472,7 +472,7 @@ def create_app(llm: LLM, config: Optional[ServerConfig] = None) -> FastAPI:
                 try:
                     async for ch in bridge:
                         if await request.is_disconnected():
-                            eng.cancel(greq.request_id)
+                            eng.cancel(greq.request_id, wait=False)
                             break
                         if ch.error:
                             yield SE.sse(APIError(classify_engine_error(ch.error), ch.error).body())
@@ -598,7 +598,7 @@ def create_app(llm: LLM, config: Optional[ServerConfig] = None) -> FastAPI:
                 try:
                     async for ch in bridge:
                         if await request.is_disconnected():
-                            eng.cancel(greq.request_id)
+                            eng.cancel(greq.request_id, wait=False)
                             break
                         if ch.error:
                             yield SE.sse(APIError(classify_engine_error(ch.error), ch.error).body())

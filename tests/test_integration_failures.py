@@ -219,3 +219,32 @@ def test_churn_of_submits_cancels_and_contained_failures_leaves_the_books_balanc
     runner.kv.radix.clear()                                    # hands its pages back through the release hook
     snap = runner.kv.pool.snapshot()
     assert snap["pages_free"] == snap["pages_total"] and snap["pages_used"] == 0
+
+
+def test_posted_cancel_ends_a_stream_without_the_caller_waiting_for_a_tick():
+    """``cancel(..., wait=False)`` only posts the command (what the HTTP routes do from the event loop when a client
+    disconnects); the driver serves it before its next tick, the stream ends with the cancel reason, nothing stays
+    active, and the context fit used by the stream pre-check is asked from the driver only once."""
+    from hipengine_b200 import LLM, SamplingParams
+    llm = LLM("tiny-dense", backend="cpu_reference", max_active_requests=2, max_sequence_length=512)
+    try:
+        eng = llm._get_engine()
+        req = llm._request(list(range(5, 25)), SamplingParams(max_tokens=400, ignore_eos=True), 0)
+        seen, last = 0, None
+        for ch in eng.stream(req):
+            seen += len(ch.token_ids)
+            last = ch
+            if seen == 3:
+                assert eng.cancel(req.request_id, wait=False) is True
+        assert last.finished and last.finish.reason == "cancelled" and 3 <= seen < 400
+        snap = llm.live_loop_snapshot()
+        assert snap["active"] == 0 and snap["pending"] == 0 and snap["counters"]["cancelled"] == 1
+        assert eng.cancel(req.request_id) is False                      # already gone: the waiting form says so
+        calls = []
+        real = llm.resident_capacity_estimate
+        llm.resident_capacity_estimate = lambda: calls.append(1) or real()
+        llm._served_context = None
+        assert [llm.fit_context([1] * n, 10)["fits_with_max_tokens"] for n in (10, 502, 503)] == [True, True, False]
+        assert len(calls) == 1
+    finally:
+        llm.close()
