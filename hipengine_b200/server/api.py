@@ -396,11 +396,19 @@ def create_app(llm: LLM, config: Optional[ServerConfig] = None) -> FastAPI:
 
     @app.post("/v1/hipengine/fit_context", dependencies=[Depends(auth)])
     async def fit_context(req: TokenizeRequest):
+        """Does this input fit the served context, how many tokens may follow it, and (with ``max_tokens``) would a
+        request asking for that many be admitted.  The reference's route of the same name
+        (``hipengine/server/api.py:7664``) answers the same question from its own tokenizer count."""
+        if req.max_tokens is not None and req.max_tokens < 1:
+            raise APIError("unsupported_parameter", "max_tokens must be >= 1", "max_tokens")
         r = await tokenize(req)
-        cap = await run_blocking(llm.resident_capacity_estimate)
-        mx = cap.get("max_context") or 0
-        return {"prompt_tokens": r["count"], "max_context": mx, "max_new_tokens": max(0, mx - r["count"]),
-                "fits": r["count"] < mx}
+        fit = await run_blocking(llm.fit_context, r["tokens"], req.max_tokens)
+        kind = "chat" if req.messages else "text"
+        out = {"object": "hipengine.fit_context", "input_type": kind, "requested_max_tokens": req.max_tokens, **fit}
+        if kind == "chat":
+            out["chat_default_max_tokens"] = cfg.chat_default_max_tokens
+            out["fits_with_default_max_tokens"] = fit["prompt_tokens"] + cfg.chat_default_max_tokens <= fit["max_context"]
+        return out
 
     # ------------------------------------------------------------------ completions
     def _prompts(req: CompletionRequest) -> List[Any]:

@@ -125,6 +125,7 @@ class TokenizeRequest(_Base):
     text: Optional[str] = None
     prompt: Optional[str] = None
     messages: Optional[List[ChatMessage]] = None
+    max_tokens: Optional[int] = None            # fit_context: would prompt + max_tokens fit?
 
 
 class DetokenizeRequest(_Base):

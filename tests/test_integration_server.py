@@ -152,7 +152,15 @@ def test_sessions_and_tokenize_and_metrics(client):
     assert r.status_code in (400, 410)
     t = client.post("/v1/hipengine/tokenize", json={"text": "abc"}).json()
     assert client.post("/v1/hipengine/detokenize", json={"tokens": t["tokens"]}).json()["text"] == "abc"
-    assert client.post("/v1/hipengine/fit_context", json={"text": "abc"}).json()["fits"]
+    fit = client.post("/v1/hipengine/fit_context", json={"text": "abc"}).json()
+    assert fit["fits"] and fit["object"] == "hipengine.fit_context" and fit["input_type"] == "text"
+    mx = fit["max_context"]
+    fit = client.post("/v1/hipengine/fit_context", json={"text": "abc", "max_tokens": mx - 3}).json()
+    assert fit["fits_with_max_tokens"] and fit["prompt_tokens"] == 3 and fit["max_new_tokens"] == mx - 3
+    assert not client.post("/v1/hipengine/fit_context", json={"text": "abc", "max_tokens": mx - 2}).json()["fits_with_max_tokens"]
+    fit = client.post("/v1/hipengine/fit_context", json={"messages": [{"role": "user", "content": "hi"}]}).json()
+    assert fit["input_type"] == "chat" and fit["chat_default_max_tokens"] > 0 and "fits_with_default_max_tokens" in fit
+    assert client.post("/v1/hipengine/fit_context", json={"text": "abc", "max_tokens": 0}).status_code == 400
     m = client.get("/metrics").text
     assert "hipengine_completion_tokens_total" in m and "hipengine_requests_total" in m
     assert "hipengine_generation_queue_depth" in m and "hipengine_request_completed_total" in m
